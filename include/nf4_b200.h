@@ -1,0 +1,204 @@
+/*
+ * nf4_b200.h -- C ABI of the B200 (sm_100a) NF4 quantized-linear library.
+ *
+ * The reference crate (Rust, CPU) has no FFI today: its boundary is the Rust API of
+ * `src/quantize.rs` and the NF4-resident modules of `src/qwennet.rs`.  Each entry
+ * point below names the reference method whose body would call it (file:line within
+ * the reference crate).  Plain pointers and sizes only; no exceptions, aborts or
+ * device traps cross this boundary.
+ *
+ * Conventions
+ *   - Every function returns an int32 status: 0 = NF4_OK, negative = failure.  The
+ *     failing call's message is kept per host thread: nf4_last_error().
+ *   - `*_dev` entry points take DEVICE pointers and enqueue on `stream`
+ *     (a cudaStream_t passed as void*; NULL = the legacy default stream).  They never
+ *     synchronise and never allocate.
+ *   - `*_host` entry points take HOST pointers; they copy in, run the same kernels,
+ *     copy out and return when the result is in the caller's buffer.
+ *   - Device buffers must be 16-byte aligned (anything cudaMalloc returns is).
+ *   - Read-only calls on one weight handle may run concurrently from several host
+ *     threads (the reference moves modules across its block-executor threads,
+ *     src/blockexec.rs:11-17); give each thread its own stream and workspace.
+ */
+#ifndef NF4_B200_H
+#define NF4_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define NF4_API __attribute__((visibility("default")))
+#else
+#define NF4_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NF4_BLOCK_SIZE 64 /* src/quantize.rs:37 */
+
+/* status codes */
+#define NF4_OK 0
+#define NF4_ERR_INVALID_ARG (-1)
+#define NF4_ERR_CUDA (-2)
+#define NF4_ERR_OOM (-3)
+#define NF4_ERR_UNSUPPORTED (-4)
+#define NF4_ERR_TIMEOUT (-5)   /* a bounded device-side wait gave up */
+#define NF4_ERR_NO_DEVICE (-6)
+
+/* Weight orientation of a linear layer. */
+#define NF4_LAYOUT_OUT_IN 0 /* W [d_out, d_in] row-major, quantized along d_in (the measured configs) */
+#define NF4_LAYOUT_IN_OUT 1 /* W [d_in, d_out] row-major, flat 64-blocks: Burn's Linear (src/qwennet.rs:2196-2211) */
+
+/* Element type of x, y and the LoRA factors. */
+#define NF4_DTYPE_BF16 0
+#define NF4_DTYPE_F32 1
+
+/* ---------------------------------------------------------------- misc -- */
+
+/* Library version (major*10000 + minor*100 + patch). */
+NF4_API int32_t nf4_version(void);
+
+/* Message of the last failing call on this host thread ("" if none). */
+NF4_API const char *nf4_last_error(void);
+
+/* Number of kernels this library has launched in this process (all threads). */
+NF4_API uint64_t nf4_kernel_launch_count(void);
+
+/* Diagnostic: runs the kernels' threshold bisection and the reference's literal
+ * sixteen-way scan (src/quantize.rs:208-219) on `count` consecutive f32 bit patterns
+ * starting at `first_bits` (only NaNs and |v| <= 65536 are compared: a normalised value
+ * never exceeds 1) and returns how many disagree. */
+NF4_API int32_t nf4_selfcheck_code_selection(uint64_t first_bits, uint64_t count, uint64_t *mismatches);
+
+/* The sixteen NF4 levels, src/quantize.rs:49-66. */
+NF4_API void nf4_levels(float out16[16]);
+
+/* Byte accounting, src/quantize.rs:391-399 (PackedNf4Tensor::estimated_resident_bytes). */
+NF4_API uint64_t nf4_estimated_resident_bytes(uint64_t len, int32_t double_quantized);
+NF4_API uint64_t nf4_num_blocks(uint64_t len);
+NF4_API uint64_t nf4_packed_bytes(uint64_t len);
+
+/* ------------------------------------------------- quantize / dequantize -- */
+
+/* Blockwise-absmax NF4 quantization of a flat f32 buffer into packed nibbles (two per
+ * byte, low nibble first) and one f32 absmax per 64-block.
+ * Replaces PackedNf4Tensor::quantize, src/quantize.rs:262-279 (codes from
+ * Nf4Tensor::quantize, :99-124; nearest level, :208-219).
+ *   values [len] f32, packed [ceil(len/2)] u8, absmax [ceil(len/64)] f32. */
+NF4_API int32_t nf4_quantize_dev(const float *values, uint64_t len, uint8_t *packed, float *absmax,
+                         void *stream);
+NF4_API int32_t nf4_quantize_host(const float *values, uint64_t len, uint8_t *packed, float *absmax);
+
+/* Same quantization, one code per byte (the simulated form): Nf4Tensor::quantize,
+ * src/quantize.rs:99-124.  codes [len] u8. */
+NF4_API int32_t nf4_quantize_unpacked_dev(const float *values, uint64_t len, uint8_t *codes,
+                                  float *absmax, void *stream);
+
+/* Second-level ("double") quantization of the block scales to 8 bits.
+ * Replaces with_double_quantization, src/quantize.rs:129-149 and :284-309.
+ *   scale_codes [nblocks] u8, scale_of_scales: one f32 (device memory for _dev). */
+NF4_API int32_t nf4_double_quantize_dev(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
+                                float *scale_of_scales, void *stream);
+NF4_API int32_t nf4_double_quantize_host(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
+                                 float *scale_of_scales);
+
+/* Reconstruct f32 values: out[i] = level[code(i)] * block_scale(i / 64).
+ * Replaces PackedNf4Tensor::dequantize, src/quantize.rs:355-366 (block_scale :341-351).
+ * Exactly one scale form is given: `absmax` (f32 per block), or `scale_codes` +
+ * `scale_of_scales` (double-quantized; `scale_of_scales` points at one f32). */
+NF4_API int32_t nf4_dequantize_dev(const uint8_t *packed, uint64_t len, const float *absmax,
+                           const uint8_t *scale_codes, const float *scale_of_scales, float *out,
+                           void *stream);
+NF4_API int32_t nf4_dequantize_host(const uint8_t *packed, uint64_t len, const float *absmax,
+                            const uint8_t *scale_codes, const float *scale_of_scales, float *out);
+
+/* One code per byte variant: Nf4Tensor::dequantize, src/quantize.rs:178-185. */
+NF4_API int32_t nf4_dequantize_unpacked_dev(const uint8_t *codes, uint64_t len, const float *absmax,
+                                    const uint8_t *scale_codes, const float *scale_of_scales,
+                                    float *out, void *stream);
+
+/* Quantize then reconstruct in place of a weight: the error a frozen NF4 weight carries.
+ * Replaces quantize_dequantize_tensor, src/quantize.rs:404-416 (and the body of
+ * Nf4Quantizer::map_float, :469-493).  `workspace` must hold
+ * nf4_quantize_dequantize_workspace_bytes(len) bytes of device memory. */
+NF4_API uint64_t nf4_quantize_dequantize_workspace_bytes(uint64_t len);
+NF4_API int32_t nf4_quantize_dequantize_dev(const float *values, uint64_t len, int32_t double_quantization,
+                                    float *out, void *workspace, uint64_t workspace_bytes,
+                                    void *stream);
+NF4_API int32_t nf4_quantize_dequantize_host(const float *values, uint64_t len,
+                                     int32_t double_quantization, float *out);
+
+/* ------------------------------------------------------- QLoRA forward -- */
+
+/* Arguments of one NF4 / QLoRA linear forward
+ *     y = x * dequant(W)^T (+ bias) (+ lora_scale * (x * A^T) * B^T).
+ * Replaces Nf4Linear::forward, src/qwennet.rs:238-241, and QloraLinear::forward,
+ * src/qwennet.rs:325-344 (adapter: LoraAdapter::forward, src/quantize.rs:620-624).
+ * All pointers are device pointers. */
+typedef struct nf4_linear_args {
+    uint32_t struct_bytes;      /* sizeof(nf4_linear_args), checked */
+    int32_t layout;             /* NF4_LAYOUT_* */
+    int32_t io_dtype;           /* NF4_DTYPE_*: type of x, y, lora_a, lora_b */
+    int32_t reserved0;
+    uint64_t rows;              /* leading dims of x flattened (src/qwennet.rs:329) */
+    uint64_t d_in;
+    uint64_t d_out;
+    const void *x;              /* [rows, d_in] */
+    const uint8_t *packed;      /* ceil(d_in*d_out/2) bytes */
+    const float *absmax;        /* f32 scales, or NULL when double-quantized */
+    const uint8_t *scale_codes; /* u8 scales (double-quantized), or NULL */
+    const float *scale_of_scales; /* one f32 in device memory, or NULL */
+    const float *bias;          /* [d_out] f32, or NULL */
+    const void *lora_a;         /* OUT_IN: [r, d_in];  IN_OUT: [d_in, r];  NULL = no adapter */
+    const void *lora_b;         /* OUT_IN: [d_out, r]; IN_OUT: [r, d_out] */
+    uint32_t lora_rank;
+    float lora_scale;           /* (alpha / rank) as f32, applied last (src/quantize.rs:623) */
+    void *y;                    /* [rows, ldy] */
+    uint64_t ldy;               /* row stride of y in elements; 0 means d_out */
+    void *workspace;            /* nf4_linear_workspace_bytes() bytes, 256-byte aligned */
+    uint64_t workspace_bytes;
+} nf4_linear_args;
+
+/* Scratch the forward needs for these sizes (the LoRA intermediate x*A^T). */
+NF4_API uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
+                                    uint32_t lora_rank);
+
+NF4_API int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream);
+
+/* ------------------------------------------------ resident weight handles -- */
+
+/* An NF4 weight resident in device memory (what Nf4Linear holds in `packed`,
+ * src/qwennet.rs:168-178).  Immutable after creation; free with nf4_weight_free. */
+typedef struct nf4_weight nf4_weight;
+
+/* Quantize host f32 values on the device and keep the result resident.
+ * Nf4Linear::from_values, src/qwennet.rs:198-205 (double_quantization = 1 there). */
+NF4_API int32_t nf4_weight_from_values_host(const float *values, uint64_t d_in, uint64_t d_out,
+                                    int32_t layout, int32_t double_quantization,
+                                    nf4_weight **out);
+/* Upload an already-packed weight.  Nf4Linear::from_packed, src/qwennet.rs:182-194. */
+NF4_API int32_t nf4_weight_from_packed_host(const uint8_t *packed, const float *absmax,
+                                    const uint8_t *scale_codes, float scale_of_scales,
+                                    uint64_t d_in, uint64_t d_out, int32_t layout,
+                                    nf4_weight **out);
+NF4_API void nf4_weight_free(nf4_weight *w);
+NF4_API uint64_t nf4_weight_resident_bytes(const nf4_weight *w); /* src/quantize.rs:370-376 */
+/* Copy the packed bytes / scales back (PartialEq and dequantize() on the Rust side). */
+NF4_API int32_t nf4_weight_download_host(const nf4_weight *w, uint8_t *packed, float *absmax,
+                                 uint8_t *scale_codes, float *scale_of_scales);
+/* Nf4Linear::dequantized_weight, src/qwennet.rs:230-236. */
+NF4_API int32_t nf4_weight_dequantize_host(const nf4_weight *w, float *out);
+
+/* Forward with host activations: x [rows, d_in] -> y [rows, d_out], element type
+ * `io_dtype`.  `lora_a`/`lora_b` (host, may be NULL) use the layout's orientation. */
+NF4_API int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint64_t rows,
+                                       int32_t io_dtype, const float *bias, const void *lora_a,
+                                       const void *lora_b, uint32_t lora_rank, float lora_scale,
+                                       void *y);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NF4_B200_H */

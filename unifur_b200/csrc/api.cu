@@ -1,0 +1,521 @@
+// C ABI of the NF4 B200 library: argument checks, error reporting, host-pointer
+// wrappers and resident weight handles.  Kernels live in the other .cu files.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "kernels.cuh"
+
+namespace nf4 {
+
+namespace {
+thread_local std::string t_last_error;
+std::atomic<uint64_t> g_launches{0};
+}  // namespace
+
+int32_t fail(int32_t code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    t_last_error = buf;
+    return code;
+}
+
+int32_t check_cuda(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return NF4_OK;
+    const int32_t code = (e == cudaErrorMemoryAllocation) ? NF4_ERR_OOM
+                         : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver)
+                             ? NF4_ERR_NO_DEVICE
+                             : NF4_ERR_CUDA;
+    return fail(code, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+
+// Grow-only device scratch owned by one host thread; the host-pointer entry points
+// stage through it so repeated calls do not pay cudaMalloc/cudaFree.
+struct Arena {
+    void *ptr = nullptr;
+    size_t cap = 0;
+    int device = -1;
+    int32_t reserve(size_t bytes) {
+        int dev = 0;
+        NF4_CUDA_TRY(cudaGetDevice(&dev));
+        if (ptr && dev == device && cap >= bytes) return NF4_OK;
+        if (ptr) {
+            cudaFree(ptr);
+            ptr = nullptr;
+            cap = 0;
+        }
+        size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+        NF4_CUDA_TRY(cudaMalloc(&ptr, want));
+        cap = want;
+        device = dev;
+        return NF4_OK;
+    }
+    ~Arena() {
+        // The CUDA context may already be gone at thread exit; ignore the result.
+        if (ptr) cudaFree(ptr);
+    }
+};
+thread_local Arena t_arena;
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Carves aligned sub-buffers out of the arena.
+struct Carver {
+    uint8_t *base;
+    size_t off = 0;
+    explicit Carver(void *p) : base(static_cast<uint8_t *>(p)) {}
+    template <class T>
+    T *take(size_t count) {
+        off = align_up(off, 256);
+        T *p = reinterpret_cast<T *>(base + off);
+        off += count * sizeof(T);
+        return p;
+    }
+};
+
+inline size_t dtype_bytes(int32_t dt) { return dt == NF4_DTYPE_F32 ? 4 : 2; }
+
+int32_t validate_linear(const nf4_linear_args *a) {
+    if (!a) return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: null args");
+    if (a->struct_bytes != sizeof(nf4_linear_args))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: struct_bytes %u != %zu",
+                    a->struct_bytes, sizeof(nf4_linear_args));
+    if (a->layout != NF4_LAYOUT_OUT_IN && a->layout != NF4_LAYOUT_IN_OUT)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: bad layout %d", a->layout);
+    if (a->io_dtype != NF4_DTYPE_BF16 && a->io_dtype != NF4_DTYPE_F32)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: bad io_dtype %d", a->io_dtype);
+    if (a->d_in == 0 || a->d_out == 0)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: zero d_in/d_out");
+    if (a->rows && (!a->x || !a->y)) return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: null x/y");
+    if (!a->packed) return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: null packed weight");
+    if ((a->absmax != nullptr) == (a->scale_codes != nullptr))
+        return fail(NF4_ERR_INVALID_ARG,
+                    "nf4_linear_forward: give either absmax or scale_codes+scale_of_scales");
+    if (a->scale_codes && !a->scale_of_scales)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: scale_codes without scale_of_scales");
+    if ((a->lora_a != nullptr) != (a->lora_b != nullptr))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: lora_a and lora_b go together");
+    if (a->lora_a && a->lora_rank == 0)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: adapter with rank 0");
+    if (a->ldy != 0 && a->ldy < a->d_out)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: ldy < d_out");
+    const uint64_t need = nf4_linear_workspace_bytes(a->rows, a->d_in, a->d_out,
+                                                     a->lora_a ? a->lora_rank : 0);
+    if (need && (!a->workspace || a->workspace_bytes < need))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: workspace %llu < %llu bytes",
+                    (unsigned long long)a->workspace_bytes, (unsigned long long)need);
+    if (need && (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: workspace not 256-byte aligned");
+    return NF4_OK;
+}
+
+}  // namespace
+}  // namespace nf4
+
+using namespace nf4;
+
+struct nf4_weight {
+    uint64_t d_in = 0, d_out = 0, len = 0, nblocks = 0;
+    int32_t layout = 0;
+    int device = 0;
+    bool double_quantized = false;
+    uint8_t *packed = nullptr;
+    float *absmax = nullptr;
+    uint8_t *scale_codes = nullptr;
+    float *scale_of_scales = nullptr;  // one f32, device
+};
+
+extern "C" {
+
+int32_t nf4_version(void) { return 100; }
+
+const char *nf4_last_error(void) { return t_last_error.c_str(); }
+
+uint64_t nf4_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void nf4_levels(float out16[16]) { std::memcpy(out16, h_level_bits, sizeof(h_level_bits)); }
+
+int32_t nf4_selfcheck_code_selection(uint64_t first_bits, uint64_t count, uint64_t *mismatches) {
+    if (!mismatches) return fail(NF4_ERR_INVALID_ARG, "nf4_selfcheck_code_selection: null pointer");
+    NF4_TRY(t_arena.reserve(256));
+    unsigned long long *d = static_cast<unsigned long long *>(t_arena.ptr);
+    NF4_CUDA_TRY(cudaMemsetAsync(d, 0, 8, 0));
+    NF4_TRY(selfcheck_codes(first_bits, count, d, 0));
+    unsigned long long h = 0;
+    NF4_CUDA_TRY(cudaMemcpy(&h, d, 8, cudaMemcpyDeviceToHost));
+    *mismatches = h;
+    return NF4_OK;
+}
+
+uint64_t nf4_num_blocks(uint64_t len) { return (len + kBlock - 1) / kBlock; }
+
+uint64_t nf4_packed_bytes(uint64_t len) { return (len + 1) / 2; }
+
+uint64_t nf4_estimated_resident_bytes(uint64_t len, int32_t double_quantized) {
+    const uint64_t blocks = nf4_num_blocks(len);
+    return nf4_packed_bytes(len) + (double_quantized ? blocks + 4 : 4 * blocks);
+}
+
+// ---- device-pointer entry points ------------------------------------------
+
+int32_t nf4_quantize_dev(const float *values, uint64_t len, uint8_t *packed, float *absmax,
+                         void *stream) {
+    return quantize_packed(values, len, packed, absmax, static_cast<cudaStream_t>(stream));
+}
+
+int32_t nf4_quantize_unpacked_dev(const float *values, uint64_t len, uint8_t *codes,
+                                  float *absmax, void *stream) {
+    return quantize_unpacked(values, len, codes, absmax, static_cast<cudaStream_t>(stream));
+}
+
+int32_t nf4_double_quantize_dev(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
+                                float *scale_of_scales, void *stream) {
+    return double_quantize(absmax, nblocks, scale_codes, scale_of_scales,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int32_t nf4_dequantize_dev(const uint8_t *packed, uint64_t len, const float *absmax,
+                           const uint8_t *scale_codes, const float *scale_of_scales, float *out,
+                           void *stream) {
+    return dequantize_packed(packed, len, absmax, scale_codes, scale_of_scales, out,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int32_t nf4_dequantize_unpacked_dev(const uint8_t *codes, uint64_t len, const float *absmax,
+                                    const uint8_t *scale_codes, const float *scale_of_scales,
+                                    float *out, void *stream) {
+    return dequantize_unpacked(codes, len, absmax, scale_codes, scale_of_scales, out,
+                               static_cast<cudaStream_t>(stream));
+}
+
+uint64_t nf4_quantize_dequantize_workspace_bytes(uint64_t len) {
+    // one code per byte + f32 absmax + u8 scale codes + scale of scales, each 256-aligned
+    const uint64_t nb = nf4_num_blocks(len);
+    return align_up(len, 256) + align_up(nb * 4, 256) + align_up(nb, 256) + 256;
+}
+
+int32_t nf4_quantize_dequantize_dev(const float *values, uint64_t len, int32_t double_quantization,
+                                    float *out, void *workspace, uint64_t workspace_bytes,
+                                    void *stream) {
+    if (len == 0) return NF4_OK;
+    if (!workspace || workspace_bytes < nf4_quantize_dequantize_workspace_bytes(len))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_quantize_dequantize: workspace too small");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint64_t nb = nf4_num_blocks(len);
+    Carver cv(workspace);
+    uint8_t *codes = cv.take<uint8_t>(len);
+    float *absmax = cv.take<float>(nb);
+    uint8_t *scodes = cv.take<uint8_t>(nb);
+    float *sos = cv.take<float>(1);
+    NF4_TRY(quantize_unpacked(values, len, codes, absmax, s));  // the simulated form, :411
+    if (double_quantization) {
+        NF4_TRY(double_quantize(absmax, nb, scodes, sos, s));
+        return dequantize_unpacked(codes, len, nullptr, scodes, sos, out, s);
+    }
+    return dequantize_unpacked(codes, len, absmax, nullptr, nullptr, out, s);
+}
+
+uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
+                                    uint32_t lora_rank) {
+    (void)d_in;
+    (void)d_out;
+    const uint64_t a = decode_workspace_bytes(rows, lora_rank);
+    const uint64_t b = prefill_workspace_bytes(rows, lora_rank);
+    return a > b ? a : b;
+}
+
+int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
+    NF4_TRY(validate_linear(args));
+    if (args->rows == 0) return NF4_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (decode_supported(*args)) return decode_forward(*args, s);
+    if (prefill_supported(*args)) return prefill_forward(*args, s);
+    return fail(NF4_ERR_UNSUPPORTED,
+                "nf4_linear_forward: no kernel for layout=%d dtype=%d rows=%llu d_in=%llu "
+                "d_out=%llu (there is no CPU fallback)",
+                args->layout, args->io_dtype, (unsigned long long)args->rows,
+                (unsigned long long)args->d_in, (unsigned long long)args->d_out);
+}
+
+// ---- host-pointer entry points ------------------------------------------------
+
+int32_t nf4_quantize_host(const float *values, uint64_t len, uint8_t *packed, float *absmax) {
+    if (len == 0) return NF4_OK;
+    if (!values || !packed || !absmax)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_quantize_host: null pointer");
+    const uint64_t nb = nf4_num_blocks(len), pb = nf4_packed_bytes(len);
+    NF4_TRY(t_arena.reserve(align_up(len * 4, 256) + align_up(pb, 256) + align_up(nb * 4, 256)));
+    Carver cv(t_arena.ptr);
+    float *d_v = cv.take<float>(len);
+    uint8_t *d_p = cv.take<uint8_t>(pb);
+    float *d_a = cv.take<float>(nb);
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_v, values, len * 4, cudaMemcpyHostToDevice, 0));
+    NF4_TRY(quantize_packed(d_v, len, d_p, d_a, 0));
+    NF4_CUDA_TRY(cudaMemcpyAsync(packed, d_p, pb, cudaMemcpyDeviceToHost, 0));
+    NF4_CUDA_TRY(cudaMemcpyAsync(absmax, d_a, nb * 4, cudaMemcpyDeviceToHost, 0));
+    return check_cuda(cudaStreamSynchronize(0), "nf4_quantize_host sync");
+}
+
+int32_t nf4_double_quantize_host(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
+                                 float *scale_of_scales) {
+    if (!scale_of_scales) return fail(NF4_ERR_INVALID_ARG, "nf4_double_quantize_host: null pointer");
+    if (nblocks == 0) {
+        *scale_of_scales = 0.0f;
+        return NF4_OK;
+    }
+    if (!absmax || !scale_codes)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_double_quantize_host: null pointer");
+    NF4_TRY(t_arena.reserve(align_up(nblocks * 4, 256) + align_up(nblocks, 256) + 256));
+    Carver cv(t_arena.ptr);
+    float *d_a = cv.take<float>(nblocks);
+    uint8_t *d_c = cv.take<uint8_t>(nblocks);
+    float *d_s = cv.take<float>(1);
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_a, absmax, nblocks * 4, cudaMemcpyHostToDevice, 0));
+    NF4_TRY(double_quantize(d_a, nblocks, d_c, d_s, 0));
+    NF4_CUDA_TRY(cudaMemcpyAsync(scale_codes, d_c, nblocks, cudaMemcpyDeviceToHost, 0));
+    NF4_CUDA_TRY(cudaMemcpyAsync(scale_of_scales, d_s, 4, cudaMemcpyDeviceToHost, 0));
+    return check_cuda(cudaStreamSynchronize(0), "nf4_double_quantize_host sync");
+}
+
+int32_t nf4_dequantize_host(const uint8_t *packed, uint64_t len, const float *absmax,
+                            const uint8_t *scale_codes, const float *scale_of_scales, float *out) {
+    if (len == 0) return NF4_OK;
+    if (!packed || !out) return fail(NF4_ERR_INVALID_ARG, "nf4_dequantize_host: null pointer");
+    if ((absmax != nullptr) == (scale_codes != nullptr) || (scale_codes && !scale_of_scales))
+        return fail(NF4_ERR_INVALID_ARG,
+                    "nf4_dequantize_host: give either absmax or scale_codes+scale_of_scales");
+    const uint64_t nb = nf4_num_blocks(len), pb = nf4_packed_bytes(len);
+    NF4_TRY(t_arena.reserve(align_up(len * 4, 256) + align_up(pb, 256) + align_up(nb * 4, 256) + 256));
+    Carver cv(t_arena.ptr);
+    float *d_o = cv.take<float>(len);
+    uint8_t *d_p = cv.take<uint8_t>(pb);
+    float *d_a = cv.take<float>(nb);  // f32 scales, or the u8 codes in the same space
+    float *d_s = cv.take<float>(1);
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_p, packed, pb, cudaMemcpyHostToDevice, 0));
+    if (absmax) {
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, absmax, nb * 4, cudaMemcpyHostToDevice, 0));
+        NF4_TRY(dequantize_packed(d_p, len, d_a, nullptr, nullptr, d_o, 0));
+    } else {
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, scale_codes, nb, cudaMemcpyHostToDevice, 0));
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_s, scale_of_scales, 4, cudaMemcpyHostToDevice, 0));
+        NF4_TRY(dequantize_packed(d_p, len, nullptr, reinterpret_cast<uint8_t *>(d_a), d_s, d_o, 0));
+    }
+    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, len * 4, cudaMemcpyDeviceToHost, 0));
+    return check_cuda(cudaStreamSynchronize(0), "nf4_dequantize_host sync");
+}
+
+int32_t nf4_quantize_dequantize_host(const float *values, uint64_t len,
+                                     int32_t double_quantization, float *out) {
+    if (len == 0) return NF4_OK;
+    if (!values || !out) return fail(NF4_ERR_INVALID_ARG, "nf4_quantize_dequantize_host: null pointer");
+    const uint64_t ws = nf4_quantize_dequantize_workspace_bytes(len);
+    NF4_TRY(t_arena.reserve(2 * align_up(len * 4, 256) + ws + 256));
+    Carver cv(t_arena.ptr);
+    float *d_v = cv.take<float>(len);
+    float *d_o = cv.take<float>(len);
+    uint8_t *d_w = cv.take<uint8_t>(ws);
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_v, values, len * 4, cudaMemcpyHostToDevice, 0));
+    NF4_TRY(nf4_quantize_dequantize_dev(d_v, len, double_quantization, d_o, d_w, ws, nullptr));
+    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, len * 4, cudaMemcpyDeviceToHost, 0));
+    return check_cuda(cudaStreamSynchronize(0), "nf4_quantize_dequantize_host sync");
+}
+
+// ---- resident weight handles -----------------------------------------------------
+
+static int32_t weight_alloc(uint64_t d_in, uint64_t d_out, int32_t layout, bool dq,
+                            nf4_weight **out) {
+    if (!out) return fail(NF4_ERR_INVALID_ARG, "nf4_weight: null out");
+    *out = nullptr;
+    if (d_in == 0 || d_out == 0) return fail(NF4_ERR_INVALID_ARG, "nf4_weight: zero dimension");
+    if (layout != NF4_LAYOUT_OUT_IN && layout != NF4_LAYOUT_IN_OUT)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_weight: bad layout %d", layout);
+    nf4_weight *w = new (std::nothrow) nf4_weight();
+    if (!w) return fail(NF4_ERR_OOM, "nf4_weight: host allocation failed");
+    w->d_in = d_in;
+    w->d_out = d_out;
+    w->len = d_in * d_out;
+    w->nblocks = nf4_num_blocks(w->len);
+    w->layout = layout;
+    w->double_quantized = dq;
+    int32_t st = check_cuda(cudaGetDevice(&w->device), "cudaGetDevice");
+    if (st == NF4_OK) st = check_cuda(cudaMalloc(&w->packed, nf4_packed_bytes(w->len)), "cudaMalloc packed");
+    if (st == NF4_OK) st = check_cuda(cudaMalloc(&w->absmax, w->nblocks * 4), "cudaMalloc absmax");
+    if (st == NF4_OK && dq) {
+        st = check_cuda(cudaMalloc(&w->scale_codes, w->nblocks), "cudaMalloc scale codes");
+        if (st == NF4_OK) st = check_cuda(cudaMalloc(&w->scale_of_scales, 256), "cudaMalloc sos");
+    }
+    if (st != NF4_OK) {
+        nf4_weight_free(w);
+        return st;
+    }
+    *out = w;
+    return NF4_OK;
+}
+
+int32_t nf4_weight_from_values_host(const float *values, uint64_t d_in, uint64_t d_out,
+                                    int32_t layout, int32_t double_quantization,
+                                    nf4_weight **out) {
+    if (!values) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_from_values_host: null values");
+    nf4_weight *w = nullptr;
+    NF4_TRY(weight_alloc(d_in, d_out, layout, double_quantization != 0, &w));
+    int32_t st = t_arena.reserve(w->len * 4);
+    if (st == NF4_OK) {
+        float *d_v = static_cast<float *>(t_arena.ptr);
+        st = check_cuda(cudaMemcpyAsync(d_v, values, w->len * 4, cudaMemcpyHostToDevice, 0), "H2D values");
+        if (st == NF4_OK) st = quantize_packed(d_v, w->len, w->packed, w->absmax, 0);
+        if (st == NF4_OK && w->double_quantized)
+            st = double_quantize(w->absmax, w->nblocks, w->scale_codes, w->scale_of_scales, 0);
+        if (st == NF4_OK) st = check_cuda(cudaStreamSynchronize(0), "nf4_weight_from_values_host sync");
+    }
+    if (st == NF4_OK && w->double_quantized) {
+        // The f32 scales are not part of a double-quantized weight (src/quantize.rs:304-307).
+        cudaFree(w->absmax);
+        w->absmax = nullptr;
+    }
+    if (st != NF4_OK) {
+        nf4_weight_free(w);
+        return st;
+    }
+    *out = w;
+    return NF4_OK;
+}
+
+int32_t nf4_weight_from_packed_host(const uint8_t *packed, const float *absmax,
+                                    const uint8_t *scale_codes, float scale_of_scales,
+                                    uint64_t d_in, uint64_t d_out, int32_t layout,
+                                    nf4_weight **out) {
+    if (!packed) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_from_packed_host: null packed");
+    if ((absmax != nullptr) == (scale_codes != nullptr))
+        return fail(NF4_ERR_INVALID_ARG,
+                    "nf4_weight_from_packed_host: give either absmax or scale_codes");
+    nf4_weight *w = nullptr;
+    NF4_TRY(weight_alloc(d_in, d_out, layout, scale_codes != nullptr, &w));
+    int32_t st = check_cuda(cudaMemcpy(w->packed, packed, nf4_packed_bytes(w->len), cudaMemcpyHostToDevice), "H2D packed");
+    if (st == NF4_OK && absmax)
+        st = check_cuda(cudaMemcpy(w->absmax, absmax, w->nblocks * 4, cudaMemcpyHostToDevice), "H2D absmax");
+    if (st == NF4_OK && scale_codes) {
+        st = check_cuda(cudaMemcpy(w->scale_codes, scale_codes, w->nblocks, cudaMemcpyHostToDevice), "H2D scale codes");
+        if (st == NF4_OK)
+            st = check_cuda(cudaMemcpy(w->scale_of_scales, &scale_of_scales, 4, cudaMemcpyHostToDevice), "H2D sos");
+        cudaFree(w->absmax);
+        w->absmax = nullptr;
+    }
+    if (st != NF4_OK) {
+        nf4_weight_free(w);
+        return st;
+    }
+    *out = w;
+    return NF4_OK;
+}
+
+void nf4_weight_free(nf4_weight *w) {
+    if (!w) return;
+    cudaFree(w->packed);
+    cudaFree(w->absmax);
+    cudaFree(w->scale_codes);
+    cudaFree(w->scale_of_scales);
+    delete w;
+}
+
+uint64_t nf4_weight_resident_bytes(const nf4_weight *w) {
+    return w ? nf4_estimated_resident_bytes(w->len, w->double_quantized) : 0;
+}
+
+int32_t nf4_weight_download_host(const nf4_weight *w, uint8_t *packed, float *absmax,
+                                 uint8_t *scale_codes, float *scale_of_scales) {
+    if (!w) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_download_host: null weight");
+    if (packed)
+        NF4_CUDA_TRY(cudaMemcpy(packed, w->packed, nf4_packed_bytes(w->len), cudaMemcpyDeviceToHost));
+    if (w->double_quantized) {
+        if (absmax) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_download_host: weight is double-quantized, it has no f32 scales");
+        if (scale_codes)
+            NF4_CUDA_TRY(cudaMemcpy(scale_codes, w->scale_codes, w->nblocks, cudaMemcpyDeviceToHost));
+        if (scale_of_scales)
+            NF4_CUDA_TRY(cudaMemcpy(scale_of_scales, w->scale_of_scales, 4, cudaMemcpyDeviceToHost));
+    } else {
+        if (scale_codes || scale_of_scales)
+            return fail(NF4_ERR_INVALID_ARG, "nf4_weight_download_host: weight has f32 scales, not u8 codes");
+        if (absmax)
+            NF4_CUDA_TRY(cudaMemcpy(absmax, w->absmax, w->nblocks * 4, cudaMemcpyDeviceToHost));
+    }
+    return NF4_OK;
+}
+
+int32_t nf4_weight_dequantize_host(const nf4_weight *w, float *out) {
+    if (!w || !out) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_dequantize_host: null pointer");
+    NF4_TRY(t_arena.reserve(w->len * 4));
+    float *d_o = static_cast<float *>(t_arena.ptr);
+    NF4_TRY(dequantize_packed(w->packed, w->len, w->absmax, w->scale_codes, w->scale_of_scales, d_o, 0));
+    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, w->len * 4, cudaMemcpyDeviceToHost, 0));
+    return check_cuda(cudaStreamSynchronize(0), "nf4_weight_dequantize_host sync");
+}
+
+int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint64_t rows,
+                                       int32_t io_dtype, const float *bias, const void *lora_a,
+                                       const void *lora_b, uint32_t lora_rank, float lora_scale,
+                                       void *y) {
+    if (!w) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_linear_forward_host: null weight");
+    if (rows == 0) return NF4_OK;
+    if (!x || !y) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_linear_forward_host: null x/y");
+    if (io_dtype != NF4_DTYPE_BF16 && io_dtype != NF4_DTYPE_F32)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_weight_linear_forward_host: bad io_dtype");
+    if ((lora_a != nullptr) != (lora_b != nullptr))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_weight_linear_forward_host: lora_a and lora_b go together");
+    const size_t eb = dtype_bytes(io_dtype);
+    const uint32_t r = lora_a ? lora_rank : 0;
+    const uint64_t ws = nf4_linear_workspace_bytes(rows, w->d_in, w->d_out, r);
+    const size_t xb = rows * w->d_in * eb, yb = rows * w->d_out * eb;
+    const size_t ab = (size_t)r * w->d_in * eb, bb = (size_t)r * w->d_out * eb;
+    NF4_TRY(t_arena.reserve(align_up(xb, 256) + align_up(yb, 256) + align_up(ab, 256) +
+                            align_up(bb, 256) + align_up(w->d_out * 4, 256) + ws + 1024));
+    Carver cv(t_arena.ptr);
+    uint8_t *d_x = cv.take<uint8_t>(xb);
+    uint8_t *d_y = cv.take<uint8_t>(yb);
+    uint8_t *d_a = cv.take<uint8_t>(ab);
+    uint8_t *d_b = cv.take<uint8_t>(bb);
+    float *d_bias = cv.take<float>(w->d_out);
+    uint8_t *d_ws = cv.take<uint8_t>(ws);
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_x, x, xb, cudaMemcpyHostToDevice, 0));
+    if (r) {
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, lora_a, ab, cudaMemcpyHostToDevice, 0));
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_b, lora_b, bb, cudaMemcpyHostToDevice, 0));
+    }
+    if (bias) NF4_CUDA_TRY(cudaMemcpyAsync(d_bias, bias, w->d_out * 4, cudaMemcpyHostToDevice, 0));
+    nf4_linear_args a;
+    std::memset(&a, 0, sizeof(a));
+    a.struct_bytes = sizeof(a);
+    a.layout = w->layout;
+    a.io_dtype = io_dtype;
+    a.rows = rows;
+    a.d_in = w->d_in;
+    a.d_out = w->d_out;
+    a.x = d_x;
+    a.packed = w->packed;
+    a.absmax = w->absmax;
+    a.scale_codes = w->scale_codes;
+    a.scale_of_scales = w->scale_of_scales;
+    a.bias = bias ? d_bias : nullptr;
+    a.lora_a = r ? d_a : nullptr;
+    a.lora_b = r ? d_b : nullptr;
+    a.lora_rank = r;
+    a.lora_scale = lora_scale;
+    a.y = d_y;
+    a.ldy = w->d_out;
+    a.workspace = ws ? d_ws : nullptr;
+    a.workspace_bytes = ws;
+    NF4_TRY(nf4_linear_forward_dev(&a, nullptr));
+    NF4_CUDA_TRY(cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, 0));
+    return check_cuda(cudaStreamSynchronize(0), "nf4_weight_linear_forward_host sync");
+}
+
+}  // extern "C"

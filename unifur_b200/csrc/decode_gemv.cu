@@ -1,0 +1,6 @@
+#include "kernels.cuh"
+namespace nf4 {
+bool decode_supported(const nf4_linear_args &) { return false; }
+uint64_t decode_workspace_bytes(uint64_t, uint32_t) { return 0; }
+int32_t decode_forward(const nf4_linear_args &, cudaStream_t) { return fail(NF4_ERR_UNSUPPORTED, "decode: not built"); }
+}

@@ -1,0 +1,33 @@
+// Internal kernel-launcher interface between the C ABI (api.cu) and the kernel files.
+#pragma once
+#include "nf4_common.cuh"
+
+namespace nf4 {
+
+// quantize.cu
+int32_t quantize_packed(const float *values, uint64_t len, uint8_t *packed, float *absmax,
+                        cudaStream_t stream);
+int32_t quantize_unpacked(const float *values, uint64_t len, uint8_t *codes, float *absmax,
+                          cudaStream_t stream);
+int32_t dequantize_packed(const uint8_t *packed, uint64_t len, const float *absmax,
+                          const uint8_t *scale_codes, const float *scale_of_scales, float *out,
+                          cudaStream_t stream);
+int32_t dequantize_unpacked(const uint8_t *codes, uint64_t len, const float *absmax,
+                            const uint8_t *scale_codes, const float *scale_of_scales, float *out,
+                            cudaStream_t stream);
+int32_t double_quantize(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
+                        float *scale_of_scales, cudaStream_t stream);
+int32_t selfcheck_codes(uint64_t first_bits, uint64_t count, unsigned long long *mismatches_dev,
+                        cudaStream_t stream);
+
+// decode_gemv.cu: rows <= 16, NF4_LAYOUT_OUT_IN, bf16 activations.
+bool decode_supported(const nf4_linear_args &a);
+uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank);
+int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);
+
+// prefill_gemm.cu: tcgen05 GEMM, NF4_LAYOUT_OUT_IN, bf16 activations.
+bool prefill_supported(const nf4_linear_args &a);
+uint64_t prefill_workspace_bytes(uint64_t rows, uint32_t lora_rank);
+int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream);
+
+}  // namespace nf4

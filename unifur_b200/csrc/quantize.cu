@@ -1,0 +1,326 @@
+// Blockwise-absmax NF4 quantize / dequantize / double-quantize kernels (sm_100a).
+//
+// All four are HBM-bound streaming kernels: 4.5625 algorithmic bytes per value
+// (4 B of f32 on one side, 0.5 B of nibbles + 4/64 B of absmax on the other).
+// Layout: values and outputs are flat arrays; a thread owns 8 consecutive values
+// (one 32-byte sector of f32, one 32-bit word of nibbles), 8 lanes own one
+// 64-value block, a warp owns 4 blocks, and warps stride over the array.
+#include "nf4_common.cuh"
+
+namespace nf4 {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarpsPerCta = kThreads / 32;
+constexpr int kValsPerLane = 8;
+constexpr int kValsPerWarp = 32 * kValsPerLane;  // 256 values = 4 blocks
+
+__device__ __forceinline__ float group8_max(float m) {
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+    return m;
+}
+
+// Full 64-blocks only: `nfull` blocks starting at values[0].  PACKED selects nibble
+// packing (two codes per byte) versus one code per byte.
+template <bool PACKED>
+__global__ void __launch_bounds__(kThreads)
+quantize_full_kernel(const float4 *__restrict__ values, uint64_t nfull,
+                     uint8_t *__restrict__ codes, float *__restrict__ absmax) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = (uint64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const uint64_t nwarps = (uint64_t)gridDim.x * kWarpsPerCta;
+    const uint64_t nchunks = (nfull + 3) / 4;  // one warp-chunk = 4 blocks
+    for (uint64_t chunk = warp; chunk < nchunks; chunk += nwarps) {
+        const uint64_t blk = chunk * 4 + (lane >> 3);
+        const bool live = blk < nfull;
+        const uint64_t g = chunk * 32 + lane;  // group of 8 values
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        if (live) {
+            a = __ldcs(values + 2 * g);
+            b = __ldcs(values + 2 * g + 1);
+        }
+        float m = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                        fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+        // fold from 0.0 with maxNum: NaNs drop out exactly as f32::max does
+        m = fmaxf(0.0f, m);
+        m = group8_max(m);
+        if (!live) continue;
+        const uint32_t c0 = code_of(a.x, m), c1 = code_of(a.y, m), c2 = code_of(a.z, m),
+                       c3 = code_of(a.w, m), c4 = code_of(b.x, m), c5 = code_of(b.y, m),
+                       c6 = code_of(b.z, m), c7 = code_of(b.w, m);
+        if (PACKED) {
+            const uint32_t word = c0 | (c1 << 4) | (c2 << 8) | (c3 << 12) | (c4 << 16) |
+                                  (c5 << 20) | (c6 << 24) | (c7 << 28);
+            reinterpret_cast<uint32_t *>(codes)[g] = word;
+        } else {
+            uint2 w;
+            w.x = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+            w.y = c4 | (c5 << 8) | (c6 << 16) | (c7 << 24);
+            reinterpret_cast<uint2 *>(codes)[g] = w;
+        }
+        if ((lane & 7u) == 0) absmax[blk] = m;
+    }
+}
+
+// Generic path: any alignment, any length.  One warp per block, two values per lane.
+// Used for the ragged last block and for buffers that are not 16-byte aligned.
+template <bool PACKED>
+__global__ void __launch_bounds__(kThreads)
+quantize_generic_kernel(const float *__restrict__ values, uint64_t len, uint64_t first_block,
+                        uint64_t nblocks, uint8_t *__restrict__ codes,
+                        float *__restrict__ absmax) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warp = (uint64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const uint64_t nwarps = (uint64_t)gridDim.x * kWarpsPerCta;
+    for (uint64_t i = warp; i < nblocks; i += nwarps) {
+        const uint64_t blk = first_block + i;
+        const uint64_t e0 = blk * kBlock + 2 * lane;
+        const bool h0 = e0 < len, h1 = e0 + 1 < len;
+        const float x0 = h0 ? values[e0] : 0.0f;
+        const float x1 = h1 ? values[e0 + 1] : 0.0f;
+        float m = fmaxf(0.0f, fmaxf(h0 ? fabsf(x0) : 0.0f, h1 ? fabsf(x1) : 0.0f));
+        #pragma unroll
+        for (int s = 1; s < 32; s <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, s));
+        const uint32_t c0 = h0 ? code_of(x0, m) : 0u;
+        const uint32_t c1 = h1 ? code_of(x1, m) : 0u;  // a missing partner leaves the nibble 0
+        if (PACKED) {
+            if (h0) codes[e0 >> 1] = (uint8_t)(c0 | (c1 << 4));
+        } else {
+            if (h0) codes[e0] = (uint8_t)c0;
+            if (h1) codes[e0 + 1] = (uint8_t)c1;
+        }
+        if (lane == 0) absmax[blk] = m;
+    }
+}
+
+// ---- dequantize -------------------------------------------------------------
+
+__device__ __forceinline__ float block_scale(const float *__restrict__ absmax,
+                                             const uint8_t *__restrict__ scale_codes, float sos,
+                                             uint64_t blk) {
+    return absmax ? __ldg(absmax + blk) : dq_scale(__ldg(scale_codes + blk), sos);
+}
+
+template <bool PACKED>
+__global__ void __launch_bounds__(kThreads)
+dequantize_full_kernel(const uint8_t *__restrict__ codes, uint64_t nfull,
+                       const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
+                       const float *__restrict__ scale_of_scales, float4 *__restrict__ out) {
+    __shared__ float s_levels[16];
+    if (threadIdx.x < 16) s_levels[threadIdx.x] = __uint_as_float(c_level_bits[threadIdx.x]);
+    __syncthreads();
+    const float sos = scale_of_scales ? __ldg(scale_of_scales) : 0.0f;
+    const uint64_t ngroups = nfull * 8;  // 8 values per group
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t g = (uint64_t)blockIdx.x * kThreads + threadIdx.x; g < ngroups; g += stride) {
+        uint32_t c[8];
+        if (PACKED) {
+            const uint32_t w = __ldcs(reinterpret_cast<const uint32_t *>(codes) + g);
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) c[i] = (w >> (4 * i)) & 15u;
+        } else {
+            const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(codes) + g);
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                c[i] = (w.x >> (8 * i)) & 15u;
+                c[4 + i] = (w.y >> (8 * i)) & 15u;
+            }
+        }
+        const float s = block_scale(absmax, scale_codes, sos, g >> 3);
+        float4 a, b;
+        a.x = __fmul_rn(s_levels[c[0]], s);
+        a.y = __fmul_rn(s_levels[c[1]], s);
+        a.z = __fmul_rn(s_levels[c[2]], s);
+        a.w = __fmul_rn(s_levels[c[3]], s);
+        b.x = __fmul_rn(s_levels[c[4]], s);
+        b.y = __fmul_rn(s_levels[c[5]], s);
+        b.z = __fmul_rn(s_levels[c[6]], s);
+        b.w = __fmul_rn(s_levels[c[7]], s);
+        __stcs(out + 2 * g, a);
+        __stcs(out + 2 * g + 1, b);
+    }
+}
+
+template <bool PACKED>
+__global__ void __launch_bounds__(kThreads)
+dequantize_generic_kernel(const uint8_t *__restrict__ codes, uint64_t len, uint64_t first,
+                          const float *__restrict__ absmax,
+                          const uint8_t *__restrict__ scale_codes,
+                          const float *__restrict__ scale_of_scales, float *__restrict__ out) {
+    const float sos = scale_of_scales ? __ldg(scale_of_scales) : 0.0f;
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i = first + (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < len; i += stride) {
+        uint32_t c;
+        if (PACKED) {
+            const uint32_t byte = codes[i >> 1];
+            c = (i & 1u) ? (byte >> 4) : (byte & 15u);
+        } else {
+            c = codes[i] & 15u;
+        }
+        const float s = block_scale(absmax, scale_codes, sos, i / kBlock);
+        out[i] = __fmul_rn(__uint_as_float(c_level_bits[c]), s);
+    }
+}
+
+// ---- double quantization ------------------------------------------------------
+
+// Pass 1: max over the (non-negative, never-NaN) block scales.  Their f32 bit patterns
+// order like unsigned integers, so one atomicMax on the bits per warp is exact.
+__global__ void __launch_bounds__(kThreads)
+scale_max_kernel(const float *__restrict__ absmax, uint64_t nblocks, uint32_t *max_bits) {
+    float m = 0.0f;
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < nblocks; i += stride)
+        m = fmaxf(m, __ldg(absmax + i));
+    #pragma unroll
+    for (int s = 1; s < 32; s <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, s));
+    if ((threadIdx.x & 31u) == 0) atomicMax(max_bits, __float_as_uint(m));
+}
+
+// Pass 2: c = round_half_away(s / max * 255) clamped to [0, 255]; 0 when max == 0
+// (src/quantize.rs:294-301).  A NaN quotient (inf / inf) casts to 0 as Rust's `as u8`.
+__global__ void __launch_bounds__(kThreads)
+scale_encode_kernel(const float *__restrict__ absmax, uint64_t nblocks,
+                    const float *__restrict__ max_scale_ptr, uint8_t *__restrict__ scale_codes) {
+    const float max_scale = *max_scale_ptr;
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < nblocks; i += stride) {
+        uint32_t c = 0;
+        if (max_scale != 0.0f) {
+            float q = roundf(__fmul_rn(__fdiv_rn(__ldg(absmax + i), max_scale), 255.0f));
+            q = fminf(fmaxf(q, 0.0f), 255.0f);  // NaN -> 0 through fmaxf
+            c = (uint32_t)q;
+        }
+        scale_codes[i] = (uint8_t)c;
+    }
+}
+
+int grid_for(uint64_t work_items, int per_cta, int max_waves) {
+    uint64_t ctas = (work_items + per_cta - 1) / per_cta;
+    uint64_t cap = (uint64_t)kNumSMs * max_waves;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    return (int)ctas;
+}
+
+template <bool PACKED>
+int32_t quantize_impl(const float *values, uint64_t len, uint8_t *codes, float *absmax,
+                      cudaStream_t stream) {
+    if (len == 0) return NF4_OK;
+    if (!values || !codes || !absmax) return fail(NF4_ERR_INVALID_ARG, "nf4_quantize: null pointer");
+    const uint64_t nblocks = (len + kBlock - 1) / kBlock;
+    const bool fast = aligned16(values) && aligned16(codes) && ((uintptr_t)absmax % 4 == 0);
+    uint64_t nfull = fast ? len / kBlock : 0;
+    if (nfull) {
+        const int grid = grid_for((nfull + 3) / 4, kWarpsPerCta, 8);
+        quantize_full_kernel<PACKED><<<grid, kThreads, 0, stream>>>(
+            reinterpret_cast<const float4 *>(values), nfull, codes, absmax);
+        count_launch();
+    }
+    if (nfull < nblocks) {
+        const uint64_t rest = nblocks - nfull;
+        const int grid = grid_for(rest, kWarpsPerCta, 8);
+        quantize_generic_kernel<PACKED><<<grid, kThreads, 0, stream>>>(values, len, nfull, rest,
+                                                                      codes, absmax);
+        count_launch();
+    }
+    return check_cuda(cudaGetLastError(), "nf4_quantize launch");
+}
+
+template <bool PACKED>
+int32_t dequantize_impl(const uint8_t *codes, uint64_t len, const float *absmax,
+                        const uint8_t *scale_codes, const float *scale_of_scales, float *out,
+                        cudaStream_t stream) {
+    if (len == 0) return NF4_OK;
+    if (!codes || !out) return fail(NF4_ERR_INVALID_ARG, "nf4_dequantize: null pointer");
+    if ((absmax != nullptr) == (scale_codes != nullptr))
+        return fail(NF4_ERR_INVALID_ARG,
+                    "nf4_dequantize: give either absmax or scale_codes+scale_of_scales");
+    if (scale_codes && !scale_of_scales)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_dequantize: scale_codes without scale_of_scales");
+    const bool fast = aligned16(codes) && aligned16(out);
+    const uint64_t nfull = fast ? len / kBlock : 0;
+    if (nfull) {
+        const int grid = grid_for(nfull * 8, kThreads, 8);
+        dequantize_full_kernel<PACKED><<<grid, kThreads, 0, stream>>>(
+            codes, nfull, absmax, scale_codes, scale_of_scales, reinterpret_cast<float4 *>(out));
+        count_launch();
+    }
+    if (nfull * kBlock < len) {
+        const uint64_t rest = len - nfull * kBlock;
+        const int grid = grid_for(rest, kThreads, 8);
+        dequantize_generic_kernel<PACKED><<<grid, kThreads, 0, stream>>>(
+            codes, len, nfull * kBlock, absmax, scale_codes, scale_of_scales, out);
+        count_launch();
+    }
+    return check_cuda(cudaGetLastError(), "nf4_dequantize launch");
+}
+
+}  // namespace
+
+int32_t quantize_packed(const float *values, uint64_t len, uint8_t *packed, float *absmax,
+                        cudaStream_t stream) {
+    return quantize_impl<true>(values, len, packed, absmax, stream);
+}
+
+int32_t quantize_unpacked(const float *values, uint64_t len, uint8_t *codes, float *absmax,
+                          cudaStream_t stream) {
+    return quantize_impl<false>(values, len, codes, absmax, stream);
+}
+
+int32_t dequantize_packed(const uint8_t *packed, uint64_t len, const float *absmax,
+                          const uint8_t *scale_codes, const float *scale_of_scales, float *out,
+                          cudaStream_t stream) {
+    return dequantize_impl<true>(packed, len, absmax, scale_codes, scale_of_scales, out, stream);
+}
+
+int32_t dequantize_unpacked(const uint8_t *codes, uint64_t len, const float *absmax,
+                            const uint8_t *scale_codes, const float *scale_of_scales, float *out,
+                            cudaStream_t stream) {
+    return dequantize_impl<false>(codes, len, absmax, scale_codes, scale_of_scales, out, stream);
+}
+
+int32_t double_quantize(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
+                        float *scale_of_scales, cudaStream_t stream) {
+    if (!scale_of_scales) return fail(NF4_ERR_INVALID_ARG, "nf4_double_quantize: null scale_of_scales");
+    NF4_CUDA_TRY(cudaMemsetAsync(scale_of_scales, 0, sizeof(float), stream));
+    if (nblocks == 0) return NF4_OK;
+    if (!absmax || !scale_codes)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_double_quantize: null pointer");
+    const int grid = grid_for(nblocks, kThreads * 4, 4);
+    scale_max_kernel<<<grid, kThreads, 0, stream>>>(absmax, nblocks,
+                                                    reinterpret_cast<uint32_t *>(scale_of_scales));
+    scale_encode_kernel<<<grid_for(nblocks, kThreads, 8), kThreads, 0, stream>>>(
+        absmax, nblocks, scale_of_scales, scale_codes);
+    count_launch(2);
+    return check_cuda(cudaGetLastError(), "nf4_double_quantize launch");
+}
+
+// ---- exhaustive self-check of the threshold bisection against the literal scan ----
+// Walks `count` consecutive f32 bit patterns from `first_bits` and counts disagreements
+// over the bisection's domain: NaNs and every value with |v| <= 65536.
+__global__ void __launch_bounds__(kThreads)
+selfcheck_codes_kernel(uint64_t first_bits, uint64_t count, unsigned long long *mismatches) {
+    unsigned long long bad = 0;
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < count; i += stride) {
+        const uint32_t bits = (uint32_t)(first_bits + i);
+        const uint32_t mag = bits & 0x7fffffffu;
+        if (mag > 0x47800000u && mag <= 0x7f800000u) continue;  // 65536 < |v| <= inf
+        const float v = __uint_as_float(bits);
+        bad += code_of_normalized(v) != code_by_scan(v);
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
+int32_t selfcheck_codes(uint64_t first_bits, uint64_t count, unsigned long long *mismatches_dev,
+                        cudaStream_t stream) {
+    selfcheck_codes_kernel<<<kNumSMs * 8, kThreads, 0, stream>>>(first_bits, count, mismatches_dev);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "selfcheck launch");
+}
+
+}  // namespace nf4
