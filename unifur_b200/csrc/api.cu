@@ -229,9 +229,12 @@ uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out
                                     uint32_t lora_rank) {
     (void)d_in;
     (void)d_out;
-    const uint64_t a = decode_workspace_bytes(rows, lora_rank);
+    uint64_t need = decode_workspace_bytes(rows, lora_rank);
     const uint64_t b = prefill_workspace_bytes(rows, lora_rank);
-    return a > b ? a : b;
+    const uint64_t c = generic_workspace_bytes(rows, lora_rank);
+    if (b > need) need = b;
+    if (c > need) need = c;
+    return need;
 }
 
 int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
@@ -240,11 +243,7 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (decode_supported(*args)) return decode_forward(*args, s);
     if (prefill_supported(*args)) return prefill_forward(*args, s);
-    return fail(NF4_ERR_UNSUPPORTED,
-                "nf4_linear_forward: no kernel for layout=%d dtype=%d rows=%llu d_in=%llu "
-                "d_out=%llu (there is no CPU fallback)",
-                args->layout, args->io_dtype, (unsigned long long)args->rows,
-                (unsigned long long)args->d_in, (unsigned long long)args->d_out);
+    return generic_forward(*args, s);
 }
 
 // ---- host-pointer entry points ------------------------------------------------

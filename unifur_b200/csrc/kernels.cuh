@@ -25,6 +25,12 @@ bool decode_supported(const nf4_linear_args &a);
 uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank);
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);
 
+int32_t decode_error_flag(int *host_value);
+
+// generic_linear.cu: any layout / dtype / shape on CUDA cores (exact f32 weights).
+uint64_t generic_workspace_bytes(uint64_t rows, uint32_t lora_rank);
+int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream);
+
 // prefill_gemm.cu: tcgen05 GEMM, NF4_LAYOUT_OUT_IN, bf16 activations.
 bool prefill_supported(const nf4_linear_args &a);
 uint64_t prefill_workspace_bytes(uint64_t rows, uint32_t lora_rank);

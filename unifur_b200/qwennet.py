@@ -1,0 +1,104 @@
+"""Host-side mirror of the NF4-resident modules of the reference's ``src/qwennet.rs``
+(``Nf4Linear`` :168-242, ``QloraLinear`` :318-345, ``QwenLinear`` :305-435) over the C ABI."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import LAYOUT_IN_OUT, LAYOUT_OUT_IN
+from .quantize import LoraAdapter, LoraConfig, PackedNf4Tensor, linear_forward
+
+
+class Nf4Linear:
+    """A frozen NF4-resident linear.  ``forward`` is "dequantize, then matmul" fused into
+    one kernel: the f32 weight is never materialised (the reference rebuilds it on every
+    call, src/qwennet.rs:230-241).
+
+    ``layout`` is ``LAYOUT_IN_OUT`` for the reference's ``[d_input, d_output]`` row-major
+    weight (blocks along the flat index) or ``LAYOUT_OUT_IN`` for ``[d_output, d_input]``
+    with blocks along ``d_input``."""
+
+    def __init__(self, packed: PackedNf4Tensor, d_input: int, d_output: int,
+                 bias: Optional[torch.Tensor] = None, layout: int = LAYOUT_IN_OUT):
+        if packed.len() != d_input * d_output:
+            raise ValueError(f"weight of shape [{d_input}, {d_output}] carries {packed.len()} values")
+        self._packed, self._d_input, self._d_output = packed, d_input, d_output
+        self.bias = bias
+        self.layout = layout
+
+    @staticmethod
+    def from_packed(packed: PackedNf4Tensor, d_input: int, d_output: int,
+                    bias: Optional[torch.Tensor] = None, layout: int = LAYOUT_IN_OUT) -> "Nf4Linear":
+        return Nf4Linear(packed, d_input, d_output, bias, layout)
+
+    @staticmethod
+    def from_values(values: torch.Tensor, d_input: int, d_output: int,
+                    layout: int = LAYOUT_IN_OUT, double_quantization: bool = True) -> "Nf4Linear":
+        """src/qwennet.rs:198-205 (double-quantized there)."""
+        packed = PackedNf4Tensor.quantize(values)
+        if double_quantization:
+            packed = packed.with_double_quantization()
+        return Nf4Linear(packed, d_input, d_output, None, layout)
+
+    def d_input(self) -> int:
+        return self._d_input
+
+    def d_output(self) -> int:
+        return self._d_output
+
+    def resident_bytes(self) -> int:
+        return self._packed.resident_bytes()
+
+    def packed(self) -> PackedNf4Tensor:
+        return self._packed
+
+    def dequantized_weight(self) -> torch.Tensor:
+        shape = (self._d_input, self._d_output) if self.layout == LAYOUT_IN_OUT \
+            else (self._d_output, self._d_input)
+        return self._packed.dequantize().view(shape)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return linear_forward(x, self._packed, self._d_input, self._d_output, self.layout,
+                              bias=self.bias)
+
+
+class QloraLinear:
+    """Frozen packed-NF4 base plus a trainable low-rank adapter (src/qwennet.rs:318-345).
+
+    With ``LAYOUT_IN_OUT`` the adapter factors have the reference's shapes
+    ``A [d_in, r]``, ``B [r, d_out]``; with ``LAYOUT_OUT_IN`` they are ``A [r, d_in]``,
+    ``B [d_out, r]``."""
+
+    def __init__(self, base: Nf4Linear, lora_a: torch.Tensor, lora_b: torch.Tensor, scaling: float):
+        self.base, self.lora_a, self.lora_b, self.scaling = base, lora_a, lora_b, float(scaling)
+
+    @staticmethod
+    def with_adapter(base: Nf4Linear, adapter: LoraAdapter) -> "QloraLinear":
+        a, b = adapter.a(), adapter.b()
+        if base.layout == LAYOUT_OUT_IN:
+            a, b = a.t().contiguous(), b.t().contiguous()
+        return QloraLinear(base, a, b, adapter.scaling())
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return linear_forward(x, self.base.packed(), self.base.d_input(), self.base.d_output(),
+                              self.base.layout, bias=self.base.bias, lora_a=self.lora_a,
+                              lora_b=self.lora_b, lora_scale=self.scaling)
+
+    def resident_bytes(self) -> int:
+        """src/qwennet.rs:362-366."""
+        r = self.lora_a.shape[0] if self.base.layout == LAYOUT_OUT_IN else self.lora_a.shape[1]
+        return self.base.resident_bytes() + 4 * (self.base.d_input() + self.base.d_output()) * r
+
+
+def with_lora(base: Nf4Linear, rank: int, alpha: float, generator=None) -> QloraLinear:
+    """``QwenLinear::with_lora`` (src/qwennet.rs:419-434): attach a fresh zero-B adapter.
+    Rank 0 and non-finite alpha are refused as ``QwenLoraConfig::validate`` does."""
+    if rank < 1:
+        raise ValueError("LoRA rank must be at least 1")
+    if not (alpha == alpha and abs(alpha) != float("inf")):
+        raise ValueError("LoRA alpha must be finite")
+    cfg = LoraConfig.new(base.d_input(), base.d_output(), rank).with_alpha(alpha)
+    return QloraLinear.with_adapter(base, LoraAdapter.new(cfg, base.packed().codes.device,
+                                                         generator=generator))
