@@ -1,0 +1,470 @@
+#!/usr/bin/env python
+"""Benchmark of the NF4 quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (the configuration the headline metric is quoted on): the QLoRA decode GEMV
+y = x W^T + s (x A^T) B^T with x bf16 [M, 4096] for M in {1, 4, 16}, W NF4 [11008, 4096]
+(block 64, f32 absmax, N(0, 0.02^2)), LoRA rank 16 (A, B ~ N(0, 0.01^2)), s = 2.0.
+One step = the three M passes.  Inputs are seeded synthetic data of those shapes.
+
+`value` is the effective HBM bandwidth: algorithmic bytes of the three passes (packed
+nibbles + absmax + A + B + x + y) divided by device time, with everything resident in HBM;
+eight distinct weight copies (203 MB, larger than the 126 MB L2) are rotated so every pass
+streams its weight from HBM.  `e2e` is the same metric through the host-pointer C ABI
+(pinned host x in, host y out, copies inside the timed region).
+
+With N > 1 (torchrun) every rank owns one [11008, 4096] column shard of an N-times wider
+layer and the ranks all-gather y over NCCL (weak scaling).
+
+`--impl reference` times the reference's CPU algorithm for the same step on the host cores:
+dequantize the packed weight to f32 (single-threaded scalar loop, as the reference's
+PackedNf4Tensor::dequantize), then f32 matmuls on all cores (torch stands in for
+burn-ndarray's matrixmultiply), as Nf4Linear::forward / QloraLinear::forward do.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+K, N, RANK, SCALE = 4096, 11008, 16, 2.0
+MS = (1, 4, 16)
+N_COPIES = 8
+METRIC = "nf4_qlora_decode_effective_hbm_bandwidth"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+
+
+def algorithmic_bytes(m: int) -> int:
+    """Bytes one decode pass must move: packed codes, absmax, A, B, x, y (bf16 in/out)."""
+    return N * K // 2 + N * K // 64 * 4 + RANK * K * 2 + N * RANK * 2 + m * K * 2 + m * N * 2
+
+
+STEP_BYTES = sum(algorithmic_bytes(m) for m in MS)
+WORKLOAD = ("QLoRA decode GEMV: x bf16 [M in {1,4,16}, 4096], W NF4 [11008, 4096] block 64 "
+            "f32 absmax, LoRA rank 16, scale 2.0; one step = the three M passes")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the bench runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        mhz, mx, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx = float(r[1])
+                for name, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        if not mhz:
+            return {"sm_mhz": None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": 0}
+        busy = [m for m in mhz if m >= 0.5 * max(mhz)]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# --------------------------------------------------------------------------- reference arm
+def cpu_reference_setup(seed: int = 2):
+    """Seeded config-2 inputs on the host, quantized by the CPU oracle."""
+    import torch
+    from oracle import nf4_oracle as o
+
+    o.build()
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal(N * K) * 0.02).astype(np.float32)
+    packed, absmax = o.quantize_packed(w)
+    rng = np.random.default_rng(3)
+    a = o.round_bf16(rng.standard_normal((K, RANK)) * 0.01)   # reference shape A [d_in, r]
+    b = o.round_bf16(rng.standard_normal((RANK, N)) * 0.01)   # B [r, d_out]
+    rng = np.random.default_rng(4)
+    xs = {m: torch.from_numpy(o.round_bf16(rng.standard_normal((m, K)))) for m in MS}
+    return dict(packed=packed, absmax=absmax, a=torch.from_numpy(a), b=torch.from_numpy(b), xs=xs)
+
+
+def cpu_reference_step(st, rows: int = N) -> None:
+    """One step of the reference's CPU algorithm over the first `rows` output columns: per pass,
+    rebuild the f32 weight (src/qwennet.rs:230-236 -> src/quantize.rs:355-366), linear
+    (src/qwennet.rs:240), then the adapter's three ops (src/quantize.rs:620-624) and the sum
+    (src/qwennet.rs:343)."""
+    import torch
+    from oracle import nf4_oracle as o
+
+    for m in MS:
+        w = torch.from_numpy(o.dequantize_packed(st["packed"][: rows * K // 2], rows * K,
+                                                 st["absmax"][: rows * K // 64])).view(rows, K)
+        x = st["xs"][m]
+        y = x @ w.t()
+        y = y + ((x @ st["a"]) @ st["b"][:, :rows]) * np.float32(SCALE)
+        st["sink"] = float(y[0, 0])
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    st = cpu_reference_setup()
+    t0 = time.perf_counter()
+    cpu_reference_step(st)  # sizing probe (also the first warm-up step)
+    t_full = time.perf_counter() - t0
+    budget_s = 150.0
+    rows = N
+    total_steps = args.steps + args.warmup
+    if t_full * total_steps > budget_s:
+        rows = max(64, int(N * budget_s / (t_full * total_steps)) // 64 * 64)
+    for _ in range(max(args.warmup - 1, 0)):
+        cpu_reference_step(st, rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_step(st, rows)
+    dt = time.perf_counter() - t0
+    step_bytes = STEP_BYTES * rows / N
+    value = step_bytes * args.steps / dt / 1e9
+    cores = torch.get_num_threads()
+    sample = (f"each step = the three M passes over the first {rows} of {N} weight rows "
+              f"(scalar single-thread dequantize + torch f32 matmul on {cores} threads)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "host": "cpu"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------- own arm
+def run_own(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from unifur_b200 import _lib
+    from unifur_b200.quantize import PackedNf4Tensor
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the NF4 library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    hbm_peak, _tf_peak, peak_kind = measured_peaks()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+
+    # ---- resident data: eight weight copies, adapter, activations --------------------
+    weights = []
+    for c in range(N_COPIES):
+        g = torch.Generator(device=dev).manual_seed(2 + c + 1000 * rank)
+        w = torch.randn(N * K, device=dev, generator=g) * 0.02
+        weights.append(PackedNf4Tensor.quantize(w))
+        del w
+    g = torch.Generator(device=dev).manual_seed(3)
+    lora_a = (torch.randn(RANK, K, device=dev, generator=g) * 0.01).bfloat16()
+    lora_b = (torch.randn(N, RANK, device=dev, generator=g) * 0.01).bfloat16()
+    g = torch.Generator(device=dev).manual_seed(4)
+    xs = {m: torch.randn(m, K, device=dev, generator=g).bfloat16() for m in MS}
+    ys = {m: torch.zeros(m, N, device=dev, dtype=torch.bfloat16) for m in MS}
+    ygs = {m: torch.zeros(world, m, N, device=dev, dtype=torch.bfloat16) for m in MS}
+    ws_bytes = max(int(lib.nf4_linear_workspace_bytes(m, K, N, RANK)) for m in MS)
+    workspaces = {m: torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev) for m in MS}
+
+    def make_args(c, m):
+        a = _lib.LinearArgs()
+        a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+        a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16
+        a.rows, a.d_in, a.d_out = m, K, N
+        a.x = xs[m].data_ptr()
+        a.packed = weights[c].codes.data_ptr()
+        a.absmax = weights[c].absmax.data_ptr()
+        a.lora_a, a.lora_b = lora_a.data_ptr(), lora_b.data_ptr()
+        a.lora_rank, a.lora_scale = RANK, SCALE
+        a.y, a.ldy = ys[m].data_ptr(), N
+        a.workspace, a.workspace_bytes = workspaces[m].data_ptr(), workspaces[m].numel()
+        return a
+
+    call_args = {(c, m): make_args(c, m) for c in range(N_COPIES) for m in MS}
+
+    def step(i: int) -> None:
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        c = i % N_COPIES
+        for m in MS:
+            _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m)]), stream))
+            if world > 1:
+                dist.all_gather_into_tensor(ygs[m], ys[m])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up, then K steps captured in one CUDA graph ---------------------------------
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(max(args.warmup, 3)):
+            step(i)
+    barrier()
+    launches0 = _lib.launch_count()
+    launch_mode = "cuda-graph"
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(args.steps):
+                step(i)
+    except Exception as e:  # capture refused (e.g. a collective that cannot be captured)
+        graph = None
+        launch_mode = f"eager ({type(e).__name__})"
+        torch.cuda.synchronize()
+    gpu_launches = _lib.launch_count() - launches0
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph is not None:
+        with torch.cuda.stream(side):
+            graph.replay()  # one untimed replay: graph upload
+        barrier()
+        with torch.cuda.stream(side):
+            e0.record()
+            graph.replay()
+            e1.record()
+    else:
+        launches0 = _lib.launch_count()
+        barrier()
+        with torch.cuda.stream(side):
+            e0.record()
+            for i in range(args.steps):
+                step(i)
+            e1.record()
+        gpu_launches = _lib.launch_count() - launches0
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    value = STEP_BYTES * args.steps * world / (total_ms * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel (decode GEMV incl. its LoRA pre-pass) ----------
+    per_launch_ms = total_ms / (args.steps * len(MS))
+    achieved = (STEP_BYTES / len(MS)) / (per_launch_ms * 1e-3) / 1e9
+    roofline = {
+        "kernel": "decode_kernel (+ lora_t_kernel pre-pass), mean over M in {1,4,16}",
+        "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+        "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
+        "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+        "algorithmic_bytes_per_launch": STEP_BYTES // len(MS),
+        "traffic": None,
+    }
+
+    # ---- end to end through the host-pointer C ABI ------------------------------------------
+    e2e = None
+    cpu_baseline = None
+    extras = {}
+    if True:
+        handles = []
+        vp = ctypes.c_void_p
+        for c in range(N_COPIES):
+            h = vp()
+            codes = weights[c].codes.cpu().numpy()
+            absmax = weights[c].absmax.cpu().numpy()
+            _lib.check(lib.nf4_weight_from_packed_host(
+                codes.ctypes.data_as(vp), absmax.ctypes.data_as(vp), None, 0.0, K, N,
+                _lib.LAYOUT_OUT_IN, ctypes.byref(h)))
+            a_h, b_h = lora_a.cpu().contiguous(), lora_b.cpu().contiguous()
+            _lib.check(lib.nf4_weight_attach_lora_host(h, vp(a_h.data_ptr()), vp(b_h.data_ptr()),
+                                                       RANK, SCALE, _lib.DTYPE_BF16))
+            handles.append(h)
+        x_host = {m: xs[m].cpu().pin_memory() for m in MS}
+        y_host = {m: torch.zeros(m, N, dtype=torch.bfloat16).pin_memory() for m in MS}
+
+        def host_step(i):
+            h = handles[i % N_COPIES]
+            for m in MS:
+                _lib.check(lib.nf4_weight_linear_forward_host(
+                    h, vp(x_host[m].data_ptr()), m, _lib.DTYPE_BF16, None, None, None, 0, 0.0,
+                    vp(y_host[m].data_ptr())))
+
+        for i in range(max(args.warmup, 3)):
+            host_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            host_step(i)
+        torch.cuda.synchronize()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {
+            "value": STEP_BYTES * args.steps * world / float(dt.item()) / 1e9, "unit": UNIT,
+            "h2d_bytes_per_step": sum(m * K * 2 for m in MS),
+            "d2h_bytes_per_step": sum(m * N * 2 for m in MS),
+            "api": "nf4_weight_linear_forward_host (pinned host x in, host y out, synchronous)",
+        }
+        for h in handles:
+            lib.nf4_weight_free(h)
+
+    # ---- other kernels of the path (not part of `value`) -----------------------------------
+    if rank == 0:
+        extras = aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind)
+
+    # ---- CPU baseline beside it (rank 0, one GPU only) -----------------------------------------
+    if rank == 0 and world == 1:
+        st = cpu_reference_setup()
+        cpu_reference_step(st)
+        reps = 2
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            cpu_reference_step(st)
+        cdt = (time.perf_counter() - t0) / reps
+        cpu_baseline = {
+            "value": STEP_BYTES / cdt / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"{reps} full steps after 1 warm-up: scalar single-thread dequantize + torch "
+                      f"f32 matmul on {torch.get_num_threads()} threads, {cdt:.2f} s per step",
+        }
+
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 tensor-core MMA on bf16 activations, f32 accumulate, bf16 out",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD,
+                       "cache": f"{N_COPIES} distinct weight copies "
+                                f"({N_COPIES * algorithmic_bytes(1) / 1e6:.0f} MB > 126 MB L2) rotated "
+                                "per step",
+                       "launch": launch_mode,
+                       "sharding": "none" if world == 1 else
+                       f"{world} column shards of a [{world * N}, {K}] layer, NCCL all-gather of y"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": int(gpu_launches), "clocks": clocks,
+            "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
+        }
+        line.update(extras)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def time_loop(torch, fn, iters: int, warm: int = 5) -> float:
+    """Mean milliseconds per call of fn(i), CUDA events on the current stream."""
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind):
+    """Quantize / dequantize of the 4096x4096 round-trip configuration, reported in GB/s."""
+    out = {}
+    n = 4096 * 4096
+    reps = 4  # 4 x 67 MB inputs rotate through more than the L2
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    g = torch.Generator(device=dev).manual_seed(1)
+    vals = [torch.randn(n, device=dev, generator=g) * 0.02 for _ in range(reps)]
+    packed = [torch.zeros(n // 2, dtype=torch.uint8, device=dev) for _ in range(reps)]
+    absmax = [torch.zeros(n // 64, dtype=torch.float32, device=dev) for _ in range(reps)]
+    ms_q = time_loop(torch, lambda i: _lib.check(lib.nf4_quantize_dev(
+        p(vals[i % reps]), n, p(packed[i % reps]), p(absmax[i % reps]), stream())), 40)
+    ms_d = time_loop(torch, lambda i: _lib.check(lib.nf4_dequantize_dev(
+        p(packed[i % reps]), n, p(absmax[i % reps]), None, None, p(vals[i % reps]), stream())), 40)
+    b = n * 4.5625
+    for name, ms in (("quantize", ms_q), ("dequantize", ms_d)):
+        gbs = b / (ms * 1e-3) / 1e9
+        out[name] = {"workload": "4096x4096 f32, block 64", "us": ms * 1e3, "GB/s": gbs,
+                     "frac": gbs / hbm_peak, "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes": int(b)}
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_own(args)
+
+
+if __name__ == "__main__":
+    main()

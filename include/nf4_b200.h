@@ -141,7 +141,7 @@ typedef struct nf4_linear_args {
     uint32_t struct_bytes;      /* sizeof(nf4_linear_args), checked */
     int32_t layout;             /* NF4_LAYOUT_* */
     int32_t io_dtype;           /* NF4_DTYPE_*: type of x, y, lora_a, lora_b */
-    int32_t reserved0;
+    int32_t y_f32;              /* 0: y has io_dtype; 1: y is f32 whatever io_dtype is */
     uint64_t rows;              /* leading dims of x flattened (src/qwennet.rs:329) */
     uint64_t d_in;
     uint64_t d_out;
@@ -191,8 +191,17 @@ NF4_API int32_t nf4_weight_download_host(const nf4_weight *w, uint8_t *packed, f
 /* Nf4Linear::dequantized_weight, src/qwennet.rs:230-236. */
 NF4_API int32_t nf4_weight_dequantize_host(const nf4_weight *w, float *out);
 
+/* Keep a LoRA adapter resident beside the weight (QwenLinear::with_lora,
+ * src/qwennet.rs:419-434; QloraLinear holds `adapter` next to `base`, :318-322).  The
+ * factors are copied to the device once; later forwards that pass lora_a == NULL use them.
+ * Factor orientation follows the weight's layout; element type is `io_dtype`.
+ * Attaching again replaces the adapter; rank 0 detaches it. */
+NF4_API int32_t nf4_weight_attach_lora_host(nf4_weight *w, const void *lora_a, const void *lora_b,
+                                    uint32_t lora_rank, float lora_scale, int32_t io_dtype);
+
 /* Forward with host activations: x [rows, d_in] -> y [rows, d_out], element type
- * `io_dtype`.  `lora_a`/`lora_b` (host, may be NULL) use the layout's orientation. */
+ * `io_dtype`.  `lora_a`/`lora_b` (host, may be NULL) use the layout's orientation; when they are NULL and
+ * an adapter of the same element type is attached to the weight, that adapter is used. */
 NF4_API int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint64_t rows,
                                        int32_t io_dtype, const float *bias, const void *lora_a,
                                        const void *lora_b, uint32_t lora_rank, float lora_scale,

@@ -27,7 +27,7 @@ def rel_l2(got, ref):
 
 
 def run_forward(layout, dtype, x, packed, absmax, d_in, d_out, bias=None, lora_a=None, lora_b=None,
-                scale=0.0, scale_codes=None, sos=None):
+                scale=0.0, scale_codes=None, sos=None, y_f32=False):
     L = lib()
     tdt = torch.bfloat16 if dtype == _lib.DTYPE_BF16 else torch.float32
     rows = x.shape[0]
@@ -42,12 +42,12 @@ def run_forward(layout, dtype, x, packed, absmax, d_in, d_out, bias=None, lora_a
     if lora_a is not None:
         rank = lora_a.shape[0] if layout == _lib.LAYOUT_OUT_IN else lora_a.shape[1]
         d_la, d_lb = dev(lora_a, tdt), dev(lora_b, tdt)
-    y = torch.full((rows, d_out), 777.0, dtype=tdt, device=DEV)
+    y = torch.full((rows, d_out), 777.0, dtype=torch.float32 if y_f32 else tdt, device=DEV)
     wsb = int(L.nf4_linear_workspace_bytes(rows, d_in, d_out, rank))
     ws = torch.zeros(max(wsb, 256), dtype=torch.uint8, device=DEV)
     a = _lib.LinearArgs()
     a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
-    a.layout, a.io_dtype = layout, dtype
+    a.layout, a.io_dtype, a.y_f32 = layout, dtype, int(y_f32)
     a.rows, a.d_in, a.d_out = rows, d_in, d_out
     a.x, a.packed = d_x.data_ptr(), d_p.data_ptr()
     a.absmax = d_am.data_ptr() if d_am is not None else None
@@ -80,24 +80,28 @@ def make_case(oracle, seed, M, K, N, r, dq=False, bias=False, w_std=0.02, ab_std
     return dict(x=x, packed=packed, absmax=None if dq else absmax, sc=sc, sos=sos, la=la, lb=lb, bias=b)
 
 
-def check_out_in(oracle, c, M, K, N, scale, tol=REL_L2_BF16, dtype=None):
-    dtype = _lib.DTYPE_BF16 if dtype is None else dtype
+def check_out_in(oracle, c, M, K, N, scale, tol=REL_L2_BF16):
+    """bf16 activations, W [N, K].  The kernel's own error is measured on its f32 output (bar:
+    rel. L2 <= 1e-3); the bf16 output must then be that result rounded once to bf16, up to one
+    bf16 ulp where the f32 sums differ in their last bits (partial sums meet through
+    shared-memory adds whose order is not fixed)."""
     ref = oracle.qlora_forward_bnb(c["x"], c["packed"], c["absmax"], N, K, c["la"], c["lb"], scale,
                                    c["bias"], c["sc"], c["sos"] if c["sos"] is not None else 0.0)
-    got = run_forward(_lib.LAYOUT_OUT_IN, dtype, c["x"], c["packed"], c["absmax"], K, N,
-                      bias=c["bias"], lora_a=c["la"], lora_b=c["lb"], scale=scale,
-                      scale_codes=c["sc"], sos=c["sos"])
-    err = rel_l2(got, ref)
-    # bf16 output rounding alone contributes ~2^-9/sqrt(3) relative; the bar covers both
-    assert err <= tol + (2.4e-3 if dtype == _lib.DTYPE_BF16 else 0.0), err
-    return got, ref
-
-
-def unrounded_error(got_bf16, ref):
-    """Error with the unavoidable bf16 rounding of y removed: compare against ref rounded to bf16."""
-    import torch as T
-    ref_b = T.from_numpy(ref.astype(np.float32)).bfloat16().float().numpy()
-    return rel_l2(got_bf16, ref_b.astype(np.float64))
+    kw = dict(bias=c["bias"], lora_a=c["la"], lora_b=c["lb"], scale=scale, scale_codes=c["sc"],
+              sos=c["sos"])
+    y32 = run_forward(_lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16, c["x"], c["packed"], c["absmax"], K, N,
+                      y_f32=True, **kw)
+    err = rel_l2(y32, ref)
+    assert err <= tol, err
+    y16 = run_forward(_lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16, c["x"], c["packed"], c["absmax"], K, N,
+                      **kw)
+    once = torch.from_numpy(y32).bfloat16().float().numpy()
+    # one bf16 ulp, plus the f32 reassociation noise of a sum whose terms are ~max|y| (matters
+    # only for outputs that cancel to almost zero)
+    ulp = np.abs(once) * 2.0 ** -7 + 4e-6 * np.abs(once).max()
+    assert np.all(np.abs(y16 - once) <= ulp)
+    assert np.mean(y16 != once) < 0.02
+    return y16, ref
 
 
 @pytest.mark.parametrize("M", [1, 4, 16])
@@ -105,9 +109,7 @@ def test_decode_config_shapes(oracle, M):
     # config 2 at full size: K = 4096, N = 11008, rank 16, scale 2.0
     K, N, r = 4096, 11008, 16
     c = make_case(oracle, 2, M, K, N, r)
-    got, ref = check_out_in(oracle, c, M, K, N, 2.0)
-    # with y's own bf16 rounding taken out, the kernel must sit inside the 1e-3 bar
-    assert unrounded_error(got, ref) <= REL_L2_BF16
+    check_out_in(oracle, c, M, K, N, 2.0)
 
 
 @pytest.mark.parametrize("M,K,N,r,dq,bias", [
@@ -123,8 +125,7 @@ def test_decode_config_shapes(oracle, M):
 ])
 def test_decode_edge_shapes(oracle, M, K, N, r, dq, bias):
     c = make_case(oracle, 1000 + M + K + N, M, K, N, r, dq=dq, bias=bias)
-    got, ref = check_out_in(oracle, c, M, K, N, 1.5)
-    assert unrounded_error(got, ref) <= REL_L2_BF16
+    check_out_in(oracle, c, M, K, N, 1.5)
 
 
 def test_lora_only_and_base_only_terms(oracle):
@@ -134,8 +135,7 @@ def test_lora_only_and_base_only_terms(oracle):
     z = dict(c)
     z["packed"] = np.full_like(c["packed"], 0x77)
     z["absmax"] = np.zeros_like(c["absmax"])
-    got, ref = check_out_in(oracle, z, M, K, N, 2.0)
-    assert unrounded_error(got, ref) <= REL_L2_BF16
+    check_out_in(oracle, z, M, K, N, 2.0)
     # zero B: attaching the adapter is an exact no-op (qwentrain.rs:1089-1112)
     nb = dict(c)
     nb["lb"] = np.zeros_like(c["lb"])
@@ -214,7 +214,8 @@ def test_host_weight_handle_forward(oracle):
                                                     vp(lbb), r, 2.0, vp(yb)))
         got = torch.from_numpy(yb).view(torch.bfloat16).float().numpy()
         ref = oracle.qlora_forward_bnb(x, packed, None, N, K, la, lb, 2.0, None, sc, sos)
-        assert unrounded_error(got, ref) <= REL_L2_BF16
+        # the result has been rounded to bf16 once (2^-9 relative at most per element)
+        assert rel_l2(got, ref) <= REL_L2_BF16 + 2.0 ** -9
     finally:
         L.nf4_weight_free(h)
 

@@ -33,7 +33,7 @@ class LinearArgs(C.Structure):
         ("struct_bytes", C.c_uint32),
         ("layout", C.c_int32),
         ("io_dtype", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("y_f32", C.c_int32),
         ("rows", C.c_uint64),
         ("d_in", C.c_uint64),
         ("d_out", C.c_uint64),
@@ -86,6 +86,7 @@ SIGNATURES = {
     "nf4_weight_resident_bytes": (_u64, [_vp]),
     "nf4_weight_download_host": (_i32, [_vp, _vp, _vp, _vp, _vp]),
     "nf4_weight_dequantize_host": (_i32, [_vp, _vp]),
+    "nf4_weight_attach_lora_host": (_i32, [_vp, _vp, _vp, _u32, _f32, _i32]),
     "nf4_weight_linear_forward_host": (_i32, [_vp, _vp, _u64, _i32, _vp, _vp, _vp, _u32, _f32,
                                               _vp]),
 }

@@ -94,6 +94,8 @@ int32_t validate_linear(const nf4_linear_args *a) {
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: bad layout %d", a->layout);
     if (a->io_dtype != NF4_DTYPE_BF16 && a->io_dtype != NF4_DTYPE_F32)
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: bad io_dtype %d", a->io_dtype);
+    if (a->y_f32 != 0 && a->y_f32 != 1)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: y_f32 must be 0 or 1");
     if (a->d_in == 0 || a->d_out == 0)
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: zero d_in/d_out");
     if (a->rows && (!a->x || !a->y)) return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: null x/y");
@@ -133,6 +135,11 @@ struct nf4_weight {
     float *absmax = nullptr;
     uint8_t *scale_codes = nullptr;
     float *scale_of_scales = nullptr;  // one f32, device
+    // resident adapter (optional)
+    void *lora_a = nullptr, *lora_b = nullptr;
+    uint32_t lora_rank = 0;
+    float lora_scale = 0.0f;
+    int32_t lora_dtype = 0;
 };
 
 extern "C" {
@@ -423,6 +430,8 @@ void nf4_weight_free(nf4_weight *w) {
     cudaFree(w->absmax);
     cudaFree(w->scale_codes);
     cudaFree(w->scale_of_scales);
+    cudaFree(w->lora_a);
+    cudaFree(w->lora_b);
     delete w;
 }
 
@@ -459,6 +468,29 @@ int32_t nf4_weight_dequantize_host(const nf4_weight *w, float *out) {
     return check_cuda(cudaStreamSynchronize(0), "nf4_weight_dequantize_host sync");
 }
 
+int32_t nf4_weight_attach_lora_host(nf4_weight *w, const void *lora_a, const void *lora_b,
+                                    uint32_t lora_rank, float lora_scale, int32_t io_dtype) {
+    if (!w) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_attach_lora_host: null weight");
+    cudaFree(w->lora_a);
+    cudaFree(w->lora_b);
+    w->lora_a = w->lora_b = nullptr;
+    w->lora_rank = 0;
+    if (lora_rank == 0) return NF4_OK;
+    if (!lora_a || !lora_b) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_attach_lora_host: null factors");
+    if (io_dtype != NF4_DTYPE_BF16 && io_dtype != NF4_DTYPE_F32)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_weight_attach_lora_host: bad io_dtype");
+    const size_t eb = dtype_bytes(io_dtype);
+    const size_t ab = (size_t)lora_rank * w->d_in * eb, bb = (size_t)lora_rank * w->d_out * eb;
+    NF4_CUDA_TRY(cudaMalloc(&w->lora_a, ab));
+    NF4_CUDA_TRY(cudaMalloc(&w->lora_b, bb));
+    NF4_CUDA_TRY(cudaMemcpy(w->lora_a, lora_a, ab, cudaMemcpyHostToDevice));
+    NF4_CUDA_TRY(cudaMemcpy(w->lora_b, lora_b, bb, cudaMemcpyHostToDevice));
+    w->lora_rank = lora_rank;
+    w->lora_scale = lora_scale;
+    w->lora_dtype = io_dtype;
+    return NF4_OK;
+}
+
 int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint64_t rows,
                                        int32_t io_dtype, const float *bias, const void *lora_a,
                                        const void *lora_b, uint32_t lora_rank, float lora_scale,
@@ -471,10 +503,16 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
     if ((lora_a != nullptr) != (lora_b != nullptr))
         return fail(NF4_ERR_INVALID_ARG, "nf4_weight_linear_forward_host: lora_a and lora_b go together");
     const size_t eb = dtype_bytes(io_dtype);
-    const uint32_t r = lora_a ? lora_rank : 0;
+    const bool resident = !lora_a && w->lora_rank && w->lora_dtype == io_dtype;
+    if (resident) {
+        lora_rank = w->lora_rank;
+        lora_scale = w->lora_scale;
+    }
+    const uint32_t r = (lora_a || resident) ? lora_rank : 0;
     const uint64_t ws = nf4_linear_workspace_bytes(rows, w->d_in, w->d_out, r);
     const size_t xb = rows * w->d_in * eb, yb = rows * w->d_out * eb;
-    const size_t ab = (size_t)r * w->d_in * eb, bb = (size_t)r * w->d_out * eb;
+    const size_t ab = resident ? 0 : (size_t)r * w->d_in * eb;
+    const size_t bb = resident ? 0 : (size_t)r * w->d_out * eb;
     NF4_TRY(t_arena.reserve(align_up(xb, 256) + align_up(yb, 256) + align_up(ab, 256) +
                             align_up(bb, 256) + align_up(w->d_out * 4, 256) + ws + 1024));
     Carver cv(t_arena.ptr);
@@ -485,7 +523,7 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
     float *d_bias = cv.take<float>(w->d_out);
     uint8_t *d_ws = cv.take<uint8_t>(ws);
     NF4_CUDA_TRY(cudaMemcpyAsync(d_x, x, xb, cudaMemcpyHostToDevice, 0));
-    if (r) {
+    if (r && !resident) {
         NF4_CUDA_TRY(cudaMemcpyAsync(d_a, lora_a, ab, cudaMemcpyHostToDevice, 0));
         NF4_CUDA_TRY(cudaMemcpyAsync(d_b, lora_b, bb, cudaMemcpyHostToDevice, 0));
     }
@@ -504,8 +542,8 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
     a.scale_codes = w->scale_codes;
     a.scale_of_scales = w->scale_of_scales;
     a.bias = bias ? d_bias : nullptr;
-    a.lora_a = r ? d_a : nullptr;
-    a.lora_b = r ? d_b : nullptr;
+    a.lora_a = r ? (resident ? w->lora_a : (void *)d_a) : nullptr;
+    a.lora_b = r ? (resident ? w->lora_b : (void *)d_b) : nullptr;
     a.lora_rank = r;
     a.lora_scale = lora_scale;
     a.y = d_y;

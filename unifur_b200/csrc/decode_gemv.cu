@@ -48,7 +48,8 @@ struct DecodeParams {
     const float *bias;
     const float *t;  // [M][rank] f32 = x A^T, or null
     const __nv_bfloat16 *lora_b;
-    __nv_bfloat16 *y;
+    void *y;
+    uint32_t y_f32;
     uint64_t ldy;
     uint32_t M, K, N, rank;
     float lora_scale;
@@ -172,7 +173,9 @@ decode_kernel(const DecodeParams p) {
                         v = fmaf(dot, p.lora_scale, v);  // scale applied last
                     }
                     if (p.bias) v += __ldg(p.bias + row0 + row);
-                    p.y[(size_t)m * p.ldy + row0 + row] = __float2bfloat16_rn(v);
+                    const size_t o = (size_t)m * p.ldy + row0 + row;
+                    if (p.y_f32) static_cast<float *>(p.y)[o] = v;
+                    else static_cast<__nv_bfloat16 *>(p.y)[o] = __float2bfloat16_rn(v);
                 }
                 rs[row * MP + m] = 0.0f;
             }
@@ -355,7 +358,7 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     const void *scales = dq ? (const void *)a.scale_codes : (const void *)a.absmax;
     if (!aligned16(a.x) || !aligned16(a.packed) || !aligned16(scales)) return false;
     if (rank && !aligned16(a.lora_b)) return false;
-    if (reinterpret_cast<uintptr_t>(a.y) & 1u) return false;
+    if (reinterpret_cast<uintptr_t>(a.y) & (a.y_f32 ? 3u : 1u)) return false;
 
     const uint32_t K = (uint32_t)a.d_in, N = (uint32_t)a.d_out;
     const uint32_t nchunks = K / kChunk;
@@ -397,7 +400,8 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     p.scale_of_scales = a.scale_of_scales;
     p.bias = a.bias;
     p.lora_b = static_cast<const __nv_bfloat16 *>(a.lora_b);
-    p.y = static_cast<__nv_bfloat16 *>(a.y);
+    p.y = a.y;
+    p.y_f32 = (uint32_t)a.y_f32;
     p.ldy = a.ldy ? a.ldy : a.d_out;
     p.M = (uint32_t)a.rows;
     p.K = K;

@@ -41,6 +41,7 @@ struct GenericParams {
     uint32_t rank;
     float lora_scale;
     int32_t layout;
+    int32_t y_f32;
 };
 
 __device__ __forceinline__ float weight_at(const GenericParams &p, uint64_t flat, float sos) {
@@ -82,7 +83,8 @@ __device__ __forceinline__ void finish(const GenericParams &p, uint64_t m, uint6
         acc = fmaf(dot, p.lora_scale, acc);
     }
     if (p.bias) acc += __ldg(p.bias + n);
-    static_cast<T *>(p.y)[m * p.ldy + n] = from_f32<T>(acc);
+    if (p.y_f32) static_cast<float *>(p.y)[m * p.ldy + n] = acc;
+    else static_cast<T *>(p.y)[m * p.ldy + n] = from_f32<T>(acc);
 }
 
 // W [d_out, d_in]: one warp per output column n, lanes stride over k (coalesced nibbles).
@@ -183,6 +185,7 @@ int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.rank = a.lora_a ? a.lora_rank : 0;
     p.lora_scale = a.lora_scale;
     p.layout = a.layout;
+    p.y_f32 = a.y_f32;
     return a.io_dtype == NF4_DTYPE_F32 ? run<float>(p, stream) : run<__nv_bfloat16>(p, stream);
 }
 
