@@ -68,6 +68,30 @@ def measured_peaks():
         return 6650.0, 1590.0, "fallback"
 
 
+def usable_cores() -> int:
+    """Host cores this process may really use: the affinity mask, capped by a cgroup CPU quota."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except Exception:
+        n = os.cpu_count() or 1
+    for path in ("/sys/fs/cgroup/cpu.max", "/sys/fs/cgroup/cpu/cpu.cfs_quota_us"):
+        try:
+            with open(path) as f:
+                parts = f.read().split()
+            if path.endswith("cpu.max"):
+                if parts[0] != "max":
+                    n = min(n, max(1, int(float(parts[0]) / float(parts[1]) + 0.5)))
+            else:
+                quota = int(parts[0])
+                if quota > 0:
+                    with open("/sys/fs/cgroup/cpu/cpu.cfs_period_us") as f:
+                        n = min(n, max(1, int(quota / int(f.read().split()[0]) + 0.5)))
+            break
+        except Exception:
+            continue
+    return max(1, n)
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the bench runs."""
 
@@ -127,6 +151,7 @@ def cpu_reference_setup(seed: int = 2):
     from oracle import nf4_oracle as o
 
     o.build()
+    torch.set_num_threads(min(usable_cores(), 64))
     rng = np.random.default_rng(seed)
     w = (rng.standard_normal(N * K) * 0.02).astype(np.float32)
     packed, absmax = o.quantize_packed(w)

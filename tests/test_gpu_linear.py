@@ -244,3 +244,57 @@ def test_python_mirror_reads_like_the_reference(oracle):
     p2 = PackedNf4Tensor.quantize(w)
     assert p1 == p2 and p1.with_double_quantization() == p2.with_double_quantization()
     assert p1.resident_bytes() == 64 * 8 // 2 + 8 * 4
+
+
+# ------------------------------------------------------------------ prefill (tcgen05) path
+@pytest.mark.parametrize("M,K,N,r,dq,bias", [
+    (256, 256, 128, 0, False, False),     # one tile, four k-stages
+    (17, 64, 8, 0, False, False),         # smallest shape the tensor-core path takes
+    (300, 512, 200, 16, False, True),     # ragged in both M and N, adapter narrower than a chunk
+    (512, 1024, 384, 64, True, True),     # double-quantized scales, full-chunk adapter
+    (257, 192, 136, 80, False, False),    # adapter wider than one 64-chunk
+    (128, 3584, 512, 16, True, False),    # Qwen2-7B k/v projection
+])
+def test_prefill_shapes(oracle, M, K, N, r, dq, bias):
+    c = make_case(oracle, 5000 + M + K + N, M, K, N, r, dq=dq, bias=bias)
+    check_out_in(oracle, c, M, K, N, 2.0)
+
+
+def test_prefill_config3_slice(oracle):
+    # config 3 (M = 2048, K = 4096, rank 64) on a 1024-column slice of its N = 14336: several
+    # persistent tiles per CTA, the full K loop and the fused adapter
+    M, K, N, r = 2048, 4096, 1024, 64
+    c = make_case(oracle, 5, M, K, N, r)
+    check_out_in(oracle, c, M, K, N, 2.0)
+
+
+def test_prefill_linearity_at_full_config3_size(oracle):
+    # size-independent property at the full config-3 size (N = 14336): the forward is linear
+    # in x, so y(x1 + x2) = y(x1) + y(x2) up to rounding, and y(0) = bias-free zero
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+
+    M, K, N, r = 2048, 4096, 14336, 64
+    g = torch.Generator(device=DEV).manual_seed(5)
+    w = torch.randn(N * K, device=DEV, generator=g) * 0.02
+    packed = PackedNf4Tensor.quantize(w)
+    del w
+    a = (torch.randn(r, K, device=DEV, generator=g) * 0.01).bfloat16()
+    b = (torch.randn(N, r, device=DEV, generator=g) * 0.01).bfloat16()
+    x1 = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    x2 = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+    xs = (x1.float() + x2.float()).bfloat16()
+    y = lambda x: linear_forward(x, packed, K, N, _lib.LAYOUT_OUT_IN, lora_a=a, lora_b=b,
+                                 lora_scale=2.0).float()
+    y1, y2, ys = y(x1), y(x2), y(xs)
+    # x1 + x2 was itself rounded to bf16, so compare against the forward of the exact residual
+    resid = (xs.float() - x1.float() - x2.float()).bfloat16()
+    yr = y(resid)
+    err = (ys - y1 - y2 - yr).norm() / ys.norm()
+    assert err.item() < 6e-3  # four bf16 output roundings
+    assert y(torch.zeros_like(x1)).abs().max().item() == 0.0
+    # a slice of rows against the oracle (f64) to pin absolute values at this size
+    rows = slice(1000, 1016)
+    deq = packed.dequantize().view(N, K)[:256].double()
+    ref = x1[rows].double() @ deq.t() + 2.0 * (x1[rows].double() @ a.double().t()) @ b[:256].double().t()
+    got = y1[rows, :256].double()
+    assert ((got - ref).norm() / ref.norm()).item() < 1e-3 + 2.0 ** -9

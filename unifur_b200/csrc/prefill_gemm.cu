@@ -1,6 +1,632 @@
+// Prefill path: y[M, N] = x * dequant(W)^T (+bias) (+ s * (x A^T) B^T) for many rows of x,
+// W stored as packed NF4 [N, K] with 64-blocks along K.  A dense contraction: tensor-core
+// bound, built on tcgen05.mma with the accumulator in tensor memory (TMEM).
+//
+// Roles inside one persistent CTA (one per SM, 448 threads):
+//   warp 0      TMA producer: x tiles [256 rows x 64 k] (bf16, 128B-swizzled, K-major) into a
+//               5-deep shared-memory ring; after the K loop the same ring carries the LoRA
+//               intermediate T (bf16 hi / lo halves) so the adapter is just more k-steps.
+//   warp 1      owns TMEM (alloc/dealloc) and issues every tcgen05.mma from one thread.
+//   warps 2-5   epilogue: TMEM -> registers -> (+bias) -> bf16/f32 -> shared -> TMA store.
+//   warps 6-13  dequantisers, two groups of 128 threads taking alternate k-stages.  A thread
+//               owns one weight row: it reads that row's 32 packed bytes and block scale
+//               straight from global memory (L2), expands the nibbles with byte-permute
+//               lookups held in registers, multiplies by the scale in f16x2 and writes the 64
+//               f16 values into its TMEM lane with tcgen05.st.  The MMA takes A (the weight
+//               tile, 128 rows) from TMEM and B (the activations) from shared memory, so the
+//               dequantised weight never touches shared memory.
+//
+// The MMA computes D[n, m] = sum_k W[n, k] x[m, k]: weight rows are the MMA's M (TMEM lanes),
+// activation rows its N (256 accumulator columns).  Operand types are f16 (weights) x bf16
+// (activations) with f32 accumulation; rounding the dequantised weight to bf16 instead would
+// cost ~1.6e-3 relative error, above the 1e-3 parity bar, while f16 costs ~3e-4.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
 #include "kernels.cuh"
+#include "ptx.cuh"
+
 namespace nf4 {
-bool prefill_supported(const nf4_linear_args &) { return false; }
-uint64_t prefill_workspace_bytes(uint64_t, uint32_t) { return 0; }
-int32_t prefill_forward(const nf4_linear_args &, cudaStream_t) { return fail(NF4_ERR_UNSUPPORTED, "prefill: not built"); }
+
+__device__ int g_prefill_error = 0;  // set when a bounded wait gives up
+
+namespace {
+
+constexpr int BM = 128;        // weight rows per tile (MMA M, TMEM lanes)
+constexpr int BN = 256;        // activation rows per tile (MMA N, accumulator columns)
+constexpr int BK = 64;         // k per stage = one quantization block = one 128B swizzle row
+constexpr int kXStages = 5;    // shared-memory ring for the B operand
+constexpr int kAStages = 4;    // TMEM ring for the A operand
+constexpr int kAStageCols = BK / 2;  // 32 columns: two f16 per 32-bit cell
+constexpr int kAccCols = BN;
+constexpr int kTmemCols = 512;
+constexpr int kXStageBytes = BN * BK * 2;  // 32 KB
+constexpr int kEpiRows = 32;               // activation rows per epilogue chunk
+constexpr int kThreads = 14 * 32;
+constexpr uint32_t kSpin = 1u << 22;
+
+// barrier slots
+constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kXStages, kBarAFull = kBarXEmpty + kXStages,
+              kBarAEmpty = kBarAFull + kAStages, kBarAccFull = kBarAEmpty + kAStages,
+              kBarAccEmpty = kBarAccFull + 1, kNumBars = kBarAccEmpty + 1;
+
+struct PrefillParams {
+    const uint8_t *codes;
+    const float *absmax;
+    const uint8_t *scale_codes;
+    const float *scale_of_scales;
+    const float *bias;
+    const __nv_bfloat16 *lora_b;  // [N][rank]
+    uint32_t M, N, K, rank;
+    uint32_t lora_chunks;  // ceil(rank / 64); T is [M][2 * 64 * lora_chunks] (hi halves, then lo)
+    uint32_t m_tiles, n_tiles;
+};
+
+// ---- descriptors -----------------------------------------------------------------
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 B apart,
+// 8-row groups 1024 B apart (SBO), version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_byte_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_byte_addr & 0x3FFFFu) >> 4);  // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                              // LBO (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // SBO, bits [32,46)
+    d |= (uint64_t)1 << 46;                              // descriptor version
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
 }
+
+// Instruction descriptor for kind::f16: f32 accumulate, K-major A and B.
+// a_fmt / b_fmt: 0 = f16, 1 = bf16.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t m,
+                                                  uint32_t n) {
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- TMEM load / store (32 lanes x 32-bit, 32 consecutive columns) -------------------
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
+        "%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
+        "%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// ---- nibble -> f16 expansion with byte-permute lookups --------------------------------
+// The sixteen f16 levels are split into a table of high bytes and a table of low bytes, four
+// registers each.  One prmt looks four nibbles up in an 8-entry half table; a third prmt picks,
+// per nibble, the half its top bit names; a last pair interleaves high and low bytes.
+struct LevelTables {
+    uint32_t hi[4], lo[4];
+};
+
+__device__ __forceinline__ LevelTables make_level_tables() {
+    LevelTables t;
+    #pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint32_t h = 0, l = 0;
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t bits = __half_as_ushort(
+                __float2half_rn(__uint_as_float(c_level_bits[4 * q + i])));
+            h |= (bits >> 8) << (8 * i);
+            l |= (bits & 0xffu) << (8 * i);
+        }
+        t.hi[q] = h;
+        t.lo[q] = l;
+    }
+    return t;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Four nibbles (bits 0..15 of `w4`) -> two f16x2 registers {e0,e1}, {e2,e3}.
+__device__ __forceinline__ void expand4(const LevelTables &t, uint32_t w4, uint32_t &out01,
+                                        uint32_t &out23) {
+    const uint32_t sel = w4 & 0x7777u;
+    const uint32_t pick = ((w4 & 0x8888u) >> 1) | 0x3210u;
+    const uint32_t h = prmt(prmt(t.hi[0], t.hi[1], sel), prmt(t.hi[2], t.hi[3], sel), pick);
+    const uint32_t l = prmt(prmt(t.lo[0], t.lo[1], sel), prmt(t.lo[2], t.lo[3], sel), pick);
+    out01 = prmt(l, h, 0x5140u);
+    out23 = prmt(l, h, 0x7362u);
+}
+
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// One stage of one weight row: 32 packed bytes + scale -> 32 registers of f16x2.
+__device__ __forceinline__ void expand_row(const LevelTables &t, const uint4 &c0, const uint4 &c1,
+                                           float scale, uint32_t (&out)[32]) {
+    const __half2 s2 = __float2half2_rn(scale);
+    const uint32_t s = *reinterpret_cast<const uint32_t *>(&s2);
+    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        uint32_t a, b, c, d;
+        expand4(t, w[i], a, b);
+        expand4(t, w[i] >> 16, c, d);
+        out[4 * i + 0] = hmul2(a, s);
+        out[4 * i + 1] = hmul2(b, s);
+        out[4 * i + 2] = hmul2(c, s);
+        out[4 * i + 3] = hmul2(d, s);
+    }
+}
+
+struct RowStage {
+    uint4 c0, c1;  // the row's 64 packed codes of one k-stage
+    float scale;
+};
+
+template <bool YF32>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t,
+               const __grid_constant__ CUtensorMap tmap_y, const PrefillParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled operand tiles
+    uint8_t *smem = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *x_ring = smem;                                   // kXStages * 32 KB
+    uint8_t *epi = smem + kXStages * kXStageBytes;            // 2 staging buffers
+    constexpr int kEpiBufBytes = kEpiRows * BM * (YF32 ? 4 : 2);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(epi + 2 * kEpiBufBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t bar0 = ptx::smem_addr(bars);
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+
+    const uint32_t k_stages = p.K / BK;
+    const uint32_t stages_per_tile = k_stages + 2 * p.lora_chunks;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    const uint32_t my_tiles = blockIdx.x < total_tiles
+                                  ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kXStages; ++s) {
+            ptx::mbar_init(bar(kBarXFull + s), 1);
+            ptx::mbar_init(bar(kBarXEmpty + s), 1);
+        }
+        for (int s = 0; s < kAStages; ++s) {
+            ptx::mbar_init(bar(kBarAFull + s), 4);
+            ptx::mbar_init(bar(kBarAEmpty + s), 1);
+        }
+        ptx::mbar_init(bar(kBarAccFull), 1);
+        ptx::mbar_init(bar(kBarAccEmpty), 4);
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+        ptx::prefetch_tmap(&tmap_x);
+        ptx::prefetch_tmap(&tmap_y);
+        if (p.lora_chunks) ptx::prefetch_tmap(&tmap_t);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_acc = tmem_base;                 // columns [0, 256)
+    const uint32_t tmem_a = tmem_base + kAccCols;        // kAStages x 32 columns
+
+    bool ok = true;
+
+    if (warp == 0) {
+        // ============================ TMA producer ============================
+        if (lane == 0) {
+            uint32_t cnt = 0;
+            for (uint32_t i = 0; i < my_tiles && ok; ++i) {
+                const uint32_t tile = blockIdx.x + i * gridDim.x;
+                const uint32_t m0 = (tile % p.m_tiles) * BN;
+                for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
+                    const uint32_t s = cnt % kXStages, ph = (cnt / kXStages) & 1u;
+                    if (!ptx::mbar_wait_bounded(bar(kBarXEmpty + s), ph ^ 1u, kSpin)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(bar(kBarXFull + s), kXStageBytes);
+                    const uint32_t dst = ptx::smem_addr(x_ring + s * kXStageBytes);
+                    if (ks < k_stages)
+                        ptx::tma_load_2d(dst, &tmap_x, (int32_t)(ks * BK), (int32_t)m0,
+                                         bar(kBarXFull + s));
+                    else
+                        ptx::tma_load_2d(dst, &tmap_t, (int32_t)((ks - k_stages) * BK), (int32_t)m0,
+                                         bar(kBarXFull + s));
+                }
+            }
+            if (!ok) atomicExch(&g_prefill_error, 1);
+        }
+    } else if (warp == 1) {
+        // ============================= MMA issuer =============================
+        if (lane == 0) {
+            constexpr uint32_t idesc_main = make_idesc(0, 1, BM, BN);  // f16 x bf16
+            constexpr uint32_t idesc_lora = make_idesc(1, 1, BM, BN);  // bf16 x bf16
+            uint32_t cnt = 0;
+            for (uint32_t i = 0; i < my_tiles && ok; ++i) {
+                // the epilogue must have drained the previous tile's accumulator
+                if (!ptx::mbar_wait_bounded(bar(kBarAccEmpty), (i & 1u) ^ 1u, kSpin)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
+                    const uint32_t sx = cnt % kXStages, phx = (cnt / kXStages) & 1u;
+                    const uint32_t sa = cnt % kAStages, pha = (cnt / kAStages) & 1u;
+                    if (!ptx::mbar_wait_bounded(bar(kBarXFull + sx), phx, kSpin) ||
+                        !ptx::mbar_wait_bounded(bar(kBarAFull + sa), pha, kSpin)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint64_t bdesc =
+                        make_kmajor_sw128_desc(ptx::smem_addr(x_ring + sx * kXStageBytes));
+                    const bool lora = ks >= k_stages;
+                    uint32_t nk16 = BK / 16;
+                    if (lora) {
+                        const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
+                        const uint32_t left = p.rank - chunk * 64;
+                        nk16 = ((left < 64 ? left : 64) + 15) / 16;
+                    }
+                    for (uint32_t j = 0; j < nk16; ++j) {
+                        // +32 bytes of K inside the swizzled row = +2 in the encoded address
+                        ptx::mma_ts_f16(tmem_acc, tmem_a + sa * kAStageCols + j * 8, bdesc + 2 * j,
+                                        lora ? idesc_lora : idesc_main, (ks | j) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(bar(kBarXEmpty + sx));
+                    ptx::tc_commit(bar(kBarAEmpty + sa));
+                }
+                if (ok) ptx::tc_commit(bar(kBarAccFull));
+            }
+            if (!ok) atomicExch(&g_prefill_error, 2);
+        }
+    } else if (warp < 6) {
+        // ============================== epilogue ==============================
+        const uint32_t q = warp & 3u;  // TMEM lane quarter this warp may touch
+        const uint32_t row_in_tile = q * 32 + lane;
+        const uint32_t epi_leader = (warp == 2 && lane == 0);
+        for (uint32_t i = 0; i < my_tiles && ok; ++i) {
+            const uint32_t tile = blockIdx.x + i * gridDim.x;
+            const uint32_t n0 = (tile / p.m_tiles) * BM, m0 = (tile % p.m_tiles) * BN;
+            const uint32_t n = n0 + row_in_tile;
+            const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+            ok = ptx::mbar_wait_bounded(bar(kBarAccFull), i & 1u, kSpin);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            for (uint32_t c = 0; c < BN / kEpiRows; ++c) {
+                uint8_t *buf = epi + (c & 1u) * kEpiBufBytes;
+                // the TMA store that last read this buffer must be done with it
+                if (epi_leader) ptx::tma_store_wait_read<1>();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                uint32_t v[32];
+                tmem_ld32(tmem_acc + ((q * 32) << 16) + c * kEpiRows, v);
+                ptx::tmem_wait_ld();
+                if (c == BN / kEpiRows - 1) {
+                    // accumulator fully read: hand it back to the MMA warp
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty));
+                }
+                // staging layout: [kEpiRows activation rows][BM weight rows]
+                #pragma unroll
+                for (int r = 0; r < 32; ++r) {
+                    const float f = __uint_as_float(v[r]) + bias;
+                    if (YF32)
+                        reinterpret_cast<float *>(buf)[r * BM + row_in_tile] = f;
+                    else
+                        reinterpret_cast<__nv_bfloat16 *>(buf)[r * BM + row_in_tile] =
+                            __float2bfloat16_rn(f);
+                }
+                ptx::fence_proxy_async();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (epi_leader) {
+                    ptx::tma_store_2d(&tmap_y, ptx::smem_addr(buf), (int32_t)n0,
+                                      (int32_t)(m0 + c * kEpiRows));
+                    ptx::tma_store_commit();
+                }
+            }
+        }
+        if (epi_leader) ptx::tma_store_wait<0>();
+        if (!ok && lane == 0) atomicExch(&g_prefill_error, 3);
+    } else {
+        // ============================ dequantisers ============================
+        const uint32_t group = (warp - 6) >> 2;           // 0 or 1: takes stages of that parity
+        const uint32_t q = warp & 3u;                      // TMEM lane quarter
+        const uint32_t row_in_tile = q * 32 + lane;
+        const LevelTables tables = make_level_tables();
+        const float sos = p.scale_codes ? __ldg(p.scale_of_scales) : 0.0f;
+        const uint32_t blocks_per_row = p.K / 64;
+        const uint64_t total = (uint64_t)my_tiles * stages_per_tile;
+
+        auto fetch = [&](uint64_t cnt, RowStage &rs) {
+            rs.c0 = rs.c1 = make_uint4(0, 0, 0, 0);
+            rs.scale = 0.0f;
+            if (cnt >= total) return;
+            const uint32_t i = (uint32_t)(cnt / stages_per_tile), ks = (uint32_t)(cnt % stages_per_tile);
+            const uint32_t tile = blockIdx.x + i * gridDim.x;
+            const uint32_t n = (tile / p.m_tiles) * BM + row_in_tile;
+            if (n >= p.N || ks >= k_stages) return;  // adapter stages are read when emitted
+            const uint4 *src = reinterpret_cast<const uint4 *>(
+                p.codes + (size_t)n * (p.K / 2) + (size_t)ks * 32);
+            rs.c0 = __ldg(src);
+            rs.c1 = __ldg(src + 1);
+            const size_t blk = (size_t)n * blocks_per_row + ks;
+            rs.scale = p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos);
+        };
+        auto emit = [&](uint64_t cnt, const RowStage &rs) -> bool {
+            const uint32_t i = (uint32_t)(cnt / stages_per_tile), ks = (uint32_t)(cnt % stages_per_tile);
+            const uint32_t sa = (uint32_t)(cnt % kAStages), ph = (uint32_t)((cnt / kAStages) & 1u);
+            uint32_t out[32];
+            if (ks < k_stages) {
+                expand_row(tables, rs.c0, rs.c1, rs.scale, out);
+            } else {
+                // one 64-wide chunk of this row of LoRA B (bf16 pairs), zero beyond the rank
+                const uint32_t tile = blockIdx.x + i * gridDim.x;
+                const uint32_t n = (tile / p.m_tiles) * BM + row_in_tile;
+                const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
+                const uint32_t left = p.rank - chunk * 64;
+                const uint16_t *src = reinterpret_cast<const uint16_t *>(p.lora_b) +
+                                      (size_t)n * p.rank + chunk * 64;
+                #pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    uint32_t lo = 0, hi = 0;
+                    if (n < p.N) {
+                        if (2u * e < left) lo = __ldg(src + 2 * e);
+                        if (2u * e + 1 < left) hi = __ldg(src + 2 * e + 1);
+                    }
+                    out[e] = lo | (hi << 16);
+                }
+            }
+            if (!ptx::mbar_wait_bounded(bar(kBarAEmpty + sa), ph ^ 1u, kSpin)) return false;
+            ptx::tc_fence_after();
+            tmem_st32(tmem_a + ((q * 32) << 16) + sa * kAStageCols, out);
+            ptx::tmem_wait_st();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kBarAFull + sa));
+            return true;
+        };
+
+        // two-deep software pipeline over this group's stages (global stage counters
+        // group, group + 2, group + 4, ...)
+        RowStage r0, r1;
+        fetch(group, r0);
+        fetch(group + 2, r1);
+        for (uint64_t cnt = group; cnt < total && ok; cnt += 4) {
+            ok = emit(cnt, r0);
+            if (!ok) break;
+            fetch(cnt + 4, r0);
+            if (cnt + 2 < total) {
+                ok = emit(cnt + 2, r1);
+                if (!ok) break;
+                fetch(cnt + 6, r1);
+            }
+        }
+        if (!ok && lane == 0) atomicExch(&g_prefill_error, 4);
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- LoRA pre-pass: T = s * x A^T, written as bf16 hi / lo halves ----------------------
+// T[m][c] for c < 64*chunks holds bf16(T), T[m][64*chunks + c] holds bf16(T - bf16(T)); columns
+// beyond the rank are zero.  One CTA per 16 rows of x, eight warps splitting K, warp MMAs.
+constexpr int kTThreads = 256;
+
+__global__ void __launch_bounds__(kTThreads)
+lora_t_prefill_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
+                      uint32_t M, uint32_t K, uint32_t rank, uint32_t chunks, float scale,
+                      __nv_bfloat16 *__restrict__ t_out) {
+    __shared__ float red[16][64 + 1];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t m0 = blockIdx.x * 16;
+    const uint32_t ld_t = 2 * 64 * chunks;
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+        for (uint32_t i = threadIdx.x; i < 16 * 65; i += kTThreads) (&red[0][0])[i] = 0.0f;
+        __syncthreads();
+        float acc[8][4];
+        #pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
+        // k is walked in 32-wide pieces; inside a piece thread t owns k = 8t .. 8t+7 so that
+        // both operands are read with 16-byte loads (a consistent permutation of k on A and B)
+        for (uint32_t k0 = warp * 32; k0 < K; k0 += 8 * 32) {
+            uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
+            if (k0 + 8 * t + 8 <= K) {
+                if (m0 + g < M) xa = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + g) * K + k0 + 8 * t));
+                if (m0 + g + 8 < M) xb = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + g + 8) * K + k0 + 8 * t));
+            }
+            #pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t j = chunk * 64 + 8 * u + g;
+                uint4 bv = make_uint4(0, 0, 0, 0);
+                if (j < rank && k0 + 8 * t + 8 <= K)
+                    bv = __ldg(reinterpret_cast<const uint4 *>(a + (size_t)j * K + k0 + 8 * t));
+                ptx::mma_16816_bf16(acc[u], xa.x, xb.x, xa.y, xb.y, bv.x, bv.y);
+                ptx::mma_16816_bf16(acc[u], xa.z, xb.z, xa.w, xb.w, bv.z, bv.w);
+            }
+        }
+        #pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            atomicAdd(&red[g][8 * u + 2 * t], acc[u][0]);
+            atomicAdd(&red[g][8 * u + 2 * t + 1], acc[u][1]);
+            atomicAdd(&red[g + 8][8 * u + 2 * t], acc[u][2]);
+            atomicAdd(&red[g + 8][8 * u + 2 * t + 1], acc[u][3]);
+        }
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < 16 * 64; i += kTThreads) {
+            const uint32_t r = i >> 6, c = i & 63u;
+            if (m0 + r < M) {
+                const float v = red[r][c] * scale;
+                const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+                const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+                t_out[(size_t)(m0 + r) * ld_t + chunk * 64 + c] = hi;
+                t_out[(size_t)(m0 + r) * ld_t + 64 * chunks + chunk * 64 + c] = lo;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D row-major tensor [rows][cols] with row pitch `pitch_bytes`; box = [box_rows][box_cols].
+int32_t make_map(CUtensorMap *map, CUtensorMapDataType dt, uint32_t elem_bytes, const void *base,
+                 uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows,
+                 uint32_t box_cols, CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(NF4_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NF4_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return NF4_OK;
+}
+
+uint32_t lora_chunks_of(uint32_t rank) { return (rank + 63) / 64; }
+
+}  // namespace
+
+bool prefill_supported(const nf4_linear_args &a) {
+    if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
+    if (a.rows <= 16) return false;  // the decode kernel's territory
+    if (a.d_in % 64 != 0 || a.d_in >= (1ull << 31) || a.d_out >= (1ull << 31) || a.rows >= (1ull << 31))
+        return false;
+    const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
+    const uint64_t ybytes = a.y_f32 ? 4 : 2;
+    if ((ldy * ybytes) % 16 != 0 || !aligned16(a.y) || !aligned16(a.x) || !aligned16(a.packed))
+        return false;
+    if (a.lora_a) {
+        if (a.lora_rank > 256) return false;
+        if (a.d_in % 8 != 0 || !aligned16(a.lora_a)) return false;
+    }
+    return true;
+}
+
+uint64_t prefill_workspace_bytes(uint64_t rows, uint32_t lora_rank) {
+    if (rows <= 16 || lora_rank == 0) return 0;
+    return (rows * 2ull * 64 * lora_chunks_of(lora_rank) * 2 + 255) / 256 * 256;
+}
+
+int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
+    if (!prefill_supported(a)) return fail(NF4_ERR_UNSUPPORTED, "prefill_forward: unsupported shape");
+    PrefillParams p{};
+    p.codes = a.packed;
+    p.absmax = a.absmax;
+    p.scale_codes = a.scale_codes;
+    p.scale_of_scales = a.scale_of_scales;
+    p.bias = a.bias;
+    p.lora_b = static_cast<const __nv_bfloat16 *>(a.lora_b);
+    p.M = (uint32_t)a.rows;
+    p.N = (uint32_t)a.d_out;
+    p.K = (uint32_t)a.d_in;
+    p.rank = a.lora_a ? a.lora_rank : 0;
+    p.lora_chunks = lora_chunks_of(p.rank);
+    p.m_tiles = (p.M + BN - 1) / BN;
+    p.n_tiles = (p.N + BM - 1) / BM;
+    const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
+
+    CUtensorMap map_x, map_t, map_y;
+    NF4_TRY(make_map(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, p.M, p.K, (uint64_t)p.K * 2, BN,
+                     BK, CU_TENSOR_MAP_SWIZZLE_128B));
+    map_t = map_x;
+    if (p.rank) {
+        __nv_bfloat16 *t = static_cast<__nv_bfloat16 *>(a.workspace);
+        const uint32_t ld_t = 2 * 64 * p.lora_chunks;
+        lora_t_prefill_kernel<<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
+            static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(a.lora_a), p.M,
+            p.K, p.rank, p.lora_chunks, a.lora_scale, t);
+        count_launch();
+        NF4_CUDA_TRY(cudaGetLastError());
+        NF4_TRY(make_map(&map_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, p.M, ld_t, (uint64_t)ld_t * 2, BN,
+                         BK, CU_TENSOR_MAP_SWIZZLE_128B));
+    }
+    if (a.y_f32)
+        NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.y, p.M, p.N, ldy * 4, kEpiRows, BM,
+                         CU_TENSOR_MAP_SWIZZLE_NONE));
+    else
+        NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, p.M, p.N, ldy * 2, kEpiRows, BM,
+                         CU_TENSOR_MAP_SWIZZLE_NONE));
+
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    const uint32_t grid = total_tiles < (uint32_t)kNumSMs ? total_tiles : (uint32_t)kNumSMs;
+    const size_t smem = 1024 + kXStages * kXStageBytes + 2 * kEpiRows * BM * (a.y_f32 ? 4 : 2) +
+                        kNumBars * 8 + 64;
+    if (a.y_f32) {
+        static bool configured = false;
+        if (!configured) {
+            NF4_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured = true;
+        }
+        prefill_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_y, p);
+    } else {
+        static bool configured = false;
+        if (!configured) {
+            NF4_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<false>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured = true;
+        }
+        prefill_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_y, p);
+    }
+    count_launch();
+    return check_cuda(cudaGetLastError(), "prefill_kernel launch");
+}
+
+int32_t prefill_error_flag(int *host_value) {
+    return check_cuda(cudaMemcpyFromSymbol(host_value, g_prefill_error, sizeof(int)),
+                      "read prefill error flag");
+}
+
+}  // namespace nf4

@@ -39,13 +39,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: gives up after `limit` polls (each poll may itself sleep for a
-// hardware-defined slice), so a lost signal can never hang the GPU.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: gives up once about a second of wall time has passed (the third argument
+// is kept for call sites that pass a poll budget; the bound is on time, not on polls, because
+// one poll may itself sleep for a hardware-defined slice).  A lost signal can therefore
+// never hang the GPU: the caller records an error and leaves.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  uint32_t limit = (1u << 22)) {
-    for (uint32_t i = 0; i < limit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+                                                  uint32_t /*poll_budget*/ = 0) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        #pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > 1000000000ull) return false;
+    }
 }
 
 // ---- bulk async copy global -> shared (TMA, untiled) --------------------------
