@@ -234,10 +234,9 @@ int32_t nf4_quantize_dequantize_dev(const float *values, uint64_t len, int32_t d
 
 uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                     uint32_t lora_rank) {
-    (void)d_in;
     (void)d_out;
     uint64_t need = decode_workspace_bytes(rows, lora_rank);
-    const uint64_t b = prefill_workspace_bytes(rows, lora_rank);
+    const uint64_t b = prefill_workspace_bytes(rows, d_in, lora_rank);
     const uint64_t c = generic_workspace_bytes(rows, lora_rank);
     if (b > need) need = b;
     if (c > need) need = c;

@@ -3,7 +3,7 @@
 // bound, built on tcgen05.mma with the accumulator in tensor memory (TMEM).
 //
 // Roles inside one persistent CTA (one per SM, 448 threads):
-//   warp 0      TMA producer: x tiles [256 rows x 64 k] (bf16, 128B-swizzled, K-major) into a
+//   warp 0      TMA producer: x tiles [256 rows x 64 k] (f16, 128B-swizzled, K-major) into a
 //               5-deep shared-memory ring; after the K loop the same ring carries the LoRA
 //               intermediate T (bf16 hi / lo halves) so the adapter is just more k-steps.
 //   warp 1      owns TMEM (alloc/dealloc) and issues every tcgen05.mma from one thread.
@@ -17,9 +17,12 @@
 //               dequantised weight never touches shared memory.
 //
 // The MMA computes D[n, m] = sum_k W[n, k] x[m, k]: weight rows are the MMA's M (TMEM lanes),
-// activation rows its N (256 accumulator columns).  Operand types are f16 (weights) x bf16
-// (activations) with f32 accumulation; rounding the dequantised weight to bf16 instead would
-// cost ~1.6e-3 relative error, above the 1e-3 parity bar, while f16 costs ~3e-4.
+// activation rows its N (256 accumulator columns).  Both operands are f16 with f32 accumulation:
+// rounding the dequantised weight to bf16 instead would cost ~1.6e-3 relative error, above the
+// 1e-3 parity bar, while f16 costs ~3e-4.  The bf16 activations are converted to f16 by a
+// pre-pass (exact for every value inside f16's range; a row whose magnitude exceeds 32768 is
+// divided by a power of two that the epilogue multiplies back), which also produces the LoRA
+// intermediate.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -60,6 +63,7 @@ struct PrefillParams {
     const float *scale_of_scales;
     const float *bias;
     const __nv_bfloat16 *lora_b;  // [N][rank]
+    const float *row_scale;       // [M] power-of-two factor each activation row was divided by
     uint32_t M, N, K, rank;
     uint32_t lora_chunks;  // ceil(rank / 64); T is [M][2 * 64 * lora_chunks] (hi halves, then lo)
     uint32_t m_tiles, n_tiles;
@@ -264,7 +268,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     } else if (warp == 1) {
         // ============================= MMA issuer =============================
         if (lane == 0) {
-            constexpr uint32_t idesc_main = make_idesc(0, 1, BM, BN);  // f16 x bf16
+            constexpr uint32_t idesc_main = make_idesc(0, 0, BM, BN);  // f16 x f16
             constexpr uint32_t idesc_lora = make_idesc(1, 1, BM, BN);  // bf16 x bf16
             uint32_t cnt = 0;
             for (uint32_t i = 0; i < my_tiles && ok; ++i) {
@@ -334,7 +338,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 // staging layout: [kEpiRows activation rows][BM weight rows]
                 #pragma unroll
                 for (int r = 0; r < 32; ++r) {
-                    const float f = __uint_as_float(v[r]) + bias;
+                    const uint32_t m = m0 + c * kEpiRows + r;
+                    const float rs = m < p.M ? __ldg(p.row_scale + m) : 1.0f;
+                    const float f = fmaf(__uint_as_float(v[r]), rs, bias);
                     if (YF32)
                         reinterpret_cast<float *>(buf)[r * BM + row_in_tile] = f;
                     else
@@ -437,19 +443,76 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
 }
 
-// ---- LoRA pre-pass: T = s * x A^T, written as bf16 hi / lo halves ----------------------
-// T[m][c] for c < 64*chunks holds bf16(T), T[m][64*chunks + c] holds bf16(T - bf16(T)); columns
-// beyond the rank are zero.  One CTA per 16 rows of x, eight warps splitting K, warp MMAs.
+// ---- pre-pass: f16 activations, row scales and the LoRA intermediate ---------------------
+// One CTA per 16 rows of x.
+//   1. row_scale[m] = 1, or the power of two that brings a row whose magnitude exceeds 32768
+//      back under it; xh[m][k] = f16(x[m][k] / row_scale[m]) (exact inside f16's range).
+//   2. with an adapter: T = lora_scale * (x A^T) / row_scale, written as bf16 hi / lo halves:
+//      T[m][c] for c < 64*chunks holds bf16(T), T[m][64*chunks + c] holds bf16(T - bf16(T));
+//      columns beyond the rank are zero.  Eight warps split K and use warp MMAs.
 constexpr int kTThreads = 256;
 
 __global__ void __launch_bounds__(kTThreads)
-lora_t_prefill_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
-                      uint32_t M, uint32_t K, uint32_t rank, uint32_t chunks, float scale,
-                      __nv_bfloat16 *__restrict__ t_out) {
+prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
+                       uint32_t M, uint32_t K, uint32_t rank, uint32_t chunks, float scale,
+                       __half *__restrict__ xh, float *__restrict__ row_scale,
+                       __nv_bfloat16 *__restrict__ t_out) {
     __shared__ float red[16][64 + 1];
+    __shared__ uint32_t row_max_bits[16];
+    __shared__ float inv_scale[16];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t m0 = blockIdx.x * 16;
+    const uint32_t rows = min(16u, M - m0);
+
+    // ---- 1. row maxima -> scales -> f16 copy (K is a multiple of 8, rows are 16-byte aligned)
+    if (threadIdx.x < 16) row_max_bits[threadIdx.x] = 0;
+    __syncthreads();
+    const uint32_t vec_per_row = K / 8;
+    for (uint32_t i = threadIdx.x; i < rows * vec_per_row; i += kTThreads) {
+        const uint32_t r = i / vec_per_row, c = i % vec_per_row;
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + r) * K) + c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t mx = 0;
+        #pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            // |bf16| as the top half of an f32 pattern; NaNs are left out of the maximum
+            const uint32_t lo = (w[q] << 16) & 0x7fff0000u, hi = w[q] & 0x7fff0000u;
+            if (lo <= 0x7f800000u) mx = max(mx, lo);
+            if (hi <= 0x7f800000u) mx = max(mx, hi);
+        }
+        atomicMax(&row_max_bits[r], mx);
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        const float mx = __uint_as_float(row_max_bits[threadIdx.x]);
+        float sc = 1.0f;
+        if (mx > 32768.0f && mx < __int_as_float(0x7f800000)) {
+            int e;
+            frexpf(mx, &e);             // mx = f * 2^e with f in [0.5, 1)
+            sc = ldexpf(1.0f, e - 15);  // mx / sc lands in [16384, 32768)
+        }
+        inv_scale[threadIdx.x] = 1.0f / sc;  // exact: sc is a power of two
+        if (threadIdx.x < rows) row_scale[m0 + threadIdx.x] = sc;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < rows * vec_per_row; i += kTThreads) {
+        const uint32_t r = i / vec_per_row, c = i % vec_per_row;
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + r) * K) + c);
+        const float is = inv_scale[r];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+        #pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(w[q] << 16) * is,
+                                                __uint_as_float(w[q] & 0xffff0000u) * is);
+            o[q] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        reinterpret_cast<uint4 *>(xh + (size_t)(m0 + r) * K)[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    if (rank == 0) return;
+
+    // ---- 2. T = scale * x A^T / row_scale ----
     const uint32_t ld_t = 2 * 64 * chunks;
     for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
         for (uint32_t i = threadIdx.x; i < 16 * 65; i += kTThreads) (&red[0][0])[i] = 0.0f;
@@ -486,7 +549,7 @@ lora_t_prefill_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *
         for (uint32_t i = threadIdx.x; i < 16 * 64; i += kTThreads) {
             const uint32_t r = i >> 6, c = i & 63u;
             if (m0 + r < M) {
-                const float v = red[r][c] * scale;
+                const float v = red[r][c] * scale * inv_scale[r];
                 const __nv_bfloat16 hi = __float2bfloat16_rn(v);
                 const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
                 t_out[(size_t)(m0 + r) * ld_t + chunk * 64 + c] = hi;
@@ -554,9 +617,25 @@ bool prefill_supported(const nf4_linear_args &a) {
     return true;
 }
 
-uint64_t prefill_workspace_bytes(uint64_t rows, uint32_t lora_rank) {
-    if (rows <= 16 || lora_rank == 0) return 0;
-    return (rows * 2ull * 64 * lora_chunks_of(lora_rank) * 2 + 255) / 256 * 256;
+namespace {
+struct WorkspaceLayout {
+    uint64_t off_xh, off_scale, off_t, bytes;
+};
+// f16 copy of x | row scales | T (bf16 hi/lo); d_in is bounded so that rows * d_in * 2 fits
+WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint32_t lora_rank) {
+    auto up = [](uint64_t v) { return (v + 255) / 256 * 256; };
+    WorkspaceLayout w;
+    w.off_xh = 0;
+    w.off_scale = up(rows * d_in * 2);
+    w.off_t = w.off_scale + up(rows * 4);
+    w.bytes = w.off_t + up(rows * 2ull * 64 * lora_chunks_of(lora_rank) * 2);
+    return w;
+}
+}  // namespace
+
+uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint32_t lora_rank) {
+    if (rows <= 16 || d_in % 64 != 0) return 0;
+    return workspace_layout(rows, d_in, lora_rank).bytes;
 }
 
 int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
@@ -577,18 +656,24 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.n_tiles = (p.N + BM - 1) / BM;
     const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
 
+    const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.rank);
+    uint8_t *ws = static_cast<uint8_t *>(a.workspace);
+    __half *xh = reinterpret_cast<__half *>(ws + wl.off_xh);
+    float *row_scale = reinterpret_cast<float *>(ws + wl.off_scale);
+    __nv_bfloat16 *t = reinterpret_cast<__nv_bfloat16 *>(ws + wl.off_t);
+    p.row_scale = row_scale;
+    prefill_prepass_kernel<<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(a.lora_a), p.M, p.K,
+        p.rank, p.lora_chunks, a.lora_scale, xh, row_scale, t);
+    count_launch();
+    NF4_CUDA_TRY(cudaGetLastError());
+
     CUtensorMap map_x, map_t, map_y;
-    NF4_TRY(make_map(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, p.M, p.K, (uint64_t)p.K * 2, BN,
-                     BK, CU_TENSOR_MAP_SWIZZLE_128B));
+    NF4_TRY(make_map(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, p.M, p.K, (uint64_t)p.K * 2, BN, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B));
     map_t = map_x;
     if (p.rank) {
-        __nv_bfloat16 *t = static_cast<__nv_bfloat16 *>(a.workspace);
         const uint32_t ld_t = 2 * 64 * p.lora_chunks;
-        lora_t_prefill_kernel<<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
-            static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(a.lora_a), p.M,
-            p.K, p.rank, p.lora_chunks, a.lora_scale, t);
-        count_launch();
-        NF4_CUDA_TRY(cudaGetLastError());
         NF4_TRY(make_map(&map_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, p.M, ld_t, (uint64_t)ld_t * 2, BN,
                          BK, CU_TENSOR_MAP_SWIZZLE_128B));
     }
