@@ -16,8 +16,9 @@
 // keeps its slice of x as f16 B-fragments in registers for the whole kernel.  A block's
 // four MMAs accumulate into a scratch accumulator that is then scaled by the block's
 // f32 absmax (or its double-quantized decode) -- the scale never touches the f16 path.
-// Partial sums meet in shared memory (red.add), and the producer warp finishes each
-// tile: + bias, + LoRA (T = x A^T comes from a small pre-pass), convert to bf16, store.
+// Each warp parks its partial sums in its own slice of a shared-memory slot and the
+// producer warp finishes each tile: sum the slices in warp order (so results do not
+// depend on timing), + bias, + LoRA (T = x A^T comes from a small pre-pass), convert, store.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -73,20 +74,61 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
+// Producer warp: request one 16-row tile (packed bytes, block scales, LoRA-B rows) into its ring
+// slot.  Lane r copies row r; lane 31 issues the copies that cover the whole tile.
+template <bool DQ>
+__device__ __forceinline__ void issue_tile(const DecodeParams &p, uint32_t tile, uint32_t n0,
+                                           uint32_t n1, uint32_t S, uint8_t *stage_base,
+                                           uint32_t bar_full, uint32_t lane) {
+    const uint32_t s = tile % S;
+    const uint32_t row0 = n0 + tile * kTileRows;
+    const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
+    const uint32_t code_row_bytes = p.K / 2;
+    uint8_t *st = stage_base + (size_t)s * p.stage_bytes;
+    const uint32_t bar = bar_full + 8 * s;
+    const uint32_t lora_bytes = p.rank ? rows * p.rank * 2u : 0u;
+    if (lane == 0)
+        ptx::mbar_arrive_expect_tx(bar, rows * (code_row_bytes + p.scale_row_bytes) + lora_bytes);
+    __syncwarp();
+    if (lane < rows) {
+        const uint32_t r = row0 + lane;
+        ptx::bulk_g2s(ptx::smem_addr(st + lane * p.code_stride),
+                      p.codes + (size_t)r * code_row_bytes, code_row_bytes, bar);
+        if (p.scale_per_row) {
+            const uint8_t *src = DQ ? p.scale_codes + (size_t)r * p.scale_row_bytes
+                                    : reinterpret_cast<const uint8_t *>(p.absmax) +
+                                          (size_t)r * p.scale_row_bytes;
+            ptx::bulk_g2s(ptx::smem_addr(st + p.off_scales + lane * p.scale_stride), src,
+                          p.scale_row_bytes, bar);
+        }
+    }
+    if (lane == 31) {
+        if (!p.scale_per_row) {
+            const uint8_t *src = DQ ? p.scale_codes + (size_t)row0 * p.scale_row_bytes
+                                    : reinterpret_cast<const uint8_t *>(p.absmax) +
+                                          (size_t)row0 * p.scale_row_bytes;
+            ptx::bulk_g2s(ptx::smem_addr(st + p.off_scales), src, rows * p.scale_row_bytes, bar);
+        }
+        if (lora_bytes)
+            ptx::bulk_g2s(ptx::smem_addr(st + p.off_lora), p.lora_b + (size_t)row0 * p.rank,
+                          lora_bytes, bar);
+    }
+}
+
 template <int NT, bool DQ>
 __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
 decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kLutBytes);  // full[8], done[8]
-    float *t_s = reinterpret_cast<float *>(smem + kLutBytes + 128);    // [M][rank]
-    float *red = reinterpret_cast<float *>(smem + p.off_red);          // [stages][16][MP]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kLutBytes);  // full[8], done[8], red_free[2]
+    float *t_s = reinterpret_cast<float *>(smem + kLutBytes + 256);    // [M][rank]
+    float *red = reinterpret_cast<float *>(smem + p.off_red);          // [2][warps][16][MP]
     uint8_t *stage_base = smem + p.off_stages;
     constexpr int MP = 8 * NT;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t nthreads = blockDim.x;
     const uint32_t S = p.stages;
+    const uint32_t red_slot_floats = p.consumer_warps * kTileRows * MP;
 
     // rows owned by this CTA: units of `gran` rows, split evenly over the grid
     const uint64_t units = p.N / p.gran;
@@ -94,78 +136,62 @@ decode_kernel(const DecodeParams p) {
     const uint32_t n1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * units / gridDim.x) * p.gran;
     const uint32_t ntiles = (n1 - n0 + kTileRows - 1) / kTileRows;
 
-    // ---- set-up: lookup table, LoRA T, zeroed reduction slots, barriers ----
-    for (uint32_t i = tid; i < 256 * 32; i += nthreads) {
-        const uint32_t byte = i >> 5;
-        lut[i] = pack_f16x2(__uint_as_float(c_level_bits[byte & 15u]),
-                            __uint_as_float(c_level_bits[byte >> 4]));
-    }
-    if (p.t)
-        for (uint32_t i = tid; i < p.M * p.rank; i += nthreads) t_s[i] = __ldg(p.t + i);
-    for (uint32_t i = tid; i < S * kTileRows * MP; i += nthreads) red[i] = 0.0f;
     const uint32_t bar_full = ptx::smem_addr(bars), bar_done = ptx::smem_addr(bars + kMaxStages);
-    if (tid == 0) {
-        for (uint32_t s = 0; s < S; ++s) {
-            ptx::mbar_init(bar_full + 8 * s, 1);
-            ptx::mbar_init(bar_done + 8 * s, p.consumer_warps);
+    const uint32_t bar_red_free = ptx::smem_addr(bars + 2 * kMaxStages);
+    if (warp == p.consumer_warps) {
+        // =================== producer + epilogue warp ===================
+        // The barriers are this warp's to set up, so the first loads leave before the other
+        // warps have finished building the lookup table.
+        if (lane == 0) {
+            for (uint32_t s = 0; s < S; ++s) {
+                ptx::mbar_init(bar_full + 8 * s, 1);
+                ptx::mbar_init(bar_done + 8 * s, p.consumer_warps);
+            }
+            ptx::mbar_init(bar_red_free, 1);
+            ptx::mbar_init(bar_red_free + 8, 1);
+            ptx::fence_mbar_init();
+            ptx::fence_proxy_async();
         }
-        ptx::fence_mbar_init();
-        ptx::fence_proxy_async();
+        __syncwarp();
+        const uint32_t first = ntiles < S ? ntiles : S;
+        for (uint32_t tile = 0; tile < first; ++tile)
+            issue_tile<DQ>(p, tile, n0, n1, S, stage_base, bar_full, lane);
+    } else {
+        // ---- consumers build the lookup table while the first tiles are in flight ----
+        const uint32_t nthreads = p.consumer_warps * 32;
+        for (uint32_t i = tid; i < 256 * 32; i += nthreads) {
+            const uint32_t byte = i >> 5;
+            lut[i] = pack_f16x2(__uint_as_float(c_level_bits[byte & 15u]),
+                                __uint_as_float(c_level_bits[byte >> 4]));
+        }
     }
     __syncthreads();
 
-    const uint32_t code_row_bytes = p.K / 2;
-
     if (warp == p.consumer_warps) {
-        // =================== producer + epilogue warp ===================
-        auto issue = [&](uint32_t tile) {
+        // T = x A^T comes from the pre-pass that ran before this kernel
+        if (p.rank)
+            for (uint32_t i = lane; i < p.M * p.rank; i += 32) t_s[i] = __ldg(p.t + i);
+        __syncwarp();
+        // Finish tiles in order: sum the warps' partials in a fixed order (so the result does
+        // not depend on timing), add bias and the adapter term, convert, store; then hand the
+        // reduction slot back and refill the tile's ring slot.
+        bool ok = true;
+        for (uint32_t tile = 0; tile < ntiles && ok; ++tile) {
             const uint32_t s = tile % S;
+            ok = ptx::mbar_wait_bounded(bar_done + 8 * s, (tile / S) & 1u);
+            if (!ok) break;
             const uint32_t row0 = n0 + tile * kTileRows;
             const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
-            uint8_t *st = stage_base + (size_t)s * p.stage_bytes;
-            const uint32_t bar = bar_full + 8 * s;
-            const uint32_t lora_bytes = p.t ? rows * p.rank * 2u : 0u;
-            if (lane == 0)
-                ptx::mbar_arrive_expect_tx(
-                    bar, rows * (code_row_bytes + p.scale_row_bytes) + lora_bytes);
-            __syncwarp();
-            if (lane < rows) {
-                const uint32_t r = row0 + lane;
-                ptx::bulk_g2s(ptx::smem_addr(st + lane * p.code_stride),
-                              p.codes + (size_t)r * code_row_bytes, code_row_bytes, bar);
-                if (p.scale_per_row) {
-                    const uint8_t *src = DQ ? p.scale_codes + (size_t)r * p.scale_row_bytes
-                                            : reinterpret_cast<const uint8_t *>(p.absmax) +
-                                                  (size_t)r * p.scale_row_bytes;
-                    ptx::bulk_g2s(ptx::smem_addr(st + p.off_scales + lane * p.scale_stride), src,
-                                  p.scale_row_bytes, bar);
-                }
-            }
-            if (lane == 31) {
-                if (!p.scale_per_row) {
-                    const uint8_t *src = DQ ? p.scale_codes + (size_t)row0 * p.scale_row_bytes
-                                            : reinterpret_cast<const uint8_t *>(p.absmax) +
-                                                  (size_t)row0 * p.scale_row_bytes;
-                    ptx::bulk_g2s(ptx::smem_addr(st + p.off_scales), src,
-                                  rows * p.scale_row_bytes, bar);
-                }
-                if (lora_bytes)
-                    ptx::bulk_g2s(ptx::smem_addr(st + p.off_lora),
-                                  p.lora_b + (size_t)row0 * p.rank, lora_bytes, bar);
-            }
-        };
-        auto epilogue = [&](uint32_t tile) {
-            const uint32_t s = tile % S;
-            const uint32_t row0 = n0 + tile * kTileRows;
-            const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
-            float *rs = red + s * kTileRows * MP;
+            const float *rs = red + (tile & 1u) * red_slot_floats;
             const __nv_bfloat16 *lb = reinterpret_cast<const __nv_bfloat16 *>(
                 stage_base + (size_t)s * p.stage_bytes + p.off_lora);
             for (uint32_t idx = lane; idx < (uint32_t)kTileRows * MP; idx += 32) {
                 const uint32_t row = idx & 15u, m = idx >> 4;
                 if (m < p.M && row < rows) {
-                    float v = rs[row * MP + m];
-                    if (p.t) {
+                    float v = 0.0f;
+                    for (uint32_t w = 0; w < p.consumer_warps; ++w)
+                        v += rs[(w * kTileRows + row) * MP + m];
+                    if (p.rank) {
                         float dot = 0.0f;
                         for (uint32_t j = 0; j < p.rank; ++j)
                             dot = fmaf(t_s[m * p.rank + j], __bfloat162float(lb[row * p.rank + j]),
@@ -177,24 +203,13 @@ decode_kernel(const DecodeParams p) {
                     if (p.y_f32) static_cast<float *>(p.y)[o] = v;
                     else static_cast<__nv_bfloat16 *>(p.y)[o] = __float2bfloat16_rn(v);
                 }
-                rs[row * MP + m] = 0.0f;
             }
             __syncwarp();
-        };
-        bool ok = true;
-        for (uint32_t tile = 0; tile < ntiles && ok; ++tile) {
-            if (tile >= S) {
-                // the slot's previous tile must be fully reduced before it is finished/reused
-                ok = ptx::mbar_wait_bounded(bar_done + 8 * (tile % S), ((tile / S) - 1) & 1u);
-                if (!ok) break;
-                epilogue(tile - S);
+            if (lane == 0) ptx::mbar_arrive(bar_red_free + 8 * (tile & 1u));
+            if (tile + S < ntiles) {
                 ptx::fence_proxy_async();
+                issue_tile<DQ>(p, tile + S, n0, n1, S, stage_base, bar_full, lane);
             }
-            issue(tile);
-        }
-        for (uint32_t tile = (ntiles > S ? ntiles - S : 0); tile < ntiles && ok; ++tile) {
-            ok = ptx::mbar_wait_bounded(bar_done + 8 * (tile % S), (tile / S) & 1u);
-            if (ok) epilogue(tile);
         }
         if (!ok && lane == 0) atomicExch(&g_decode_error, 1);
     } else if (warp < p.consumer_warps) {
@@ -290,13 +305,19 @@ decode_kernel(const DecodeParams p) {
                     }
                 }
             }
-            float *rs = red + s * kTileRows * MP;
+            // this warp's partial sums go to its own slice of the tile's reduction slot; the
+            // slot is free once the epilogue has summed the tile two before this one
+            if (tile >= 2) {
+                ok = ptx::mbar_wait_bounded(bar_red_free + 8 * (tile & 1u), ((tile >> 1) - 1) & 1u);
+                if (!ok) break;
+            }
+            float *rs = red + (tile & 1u) * red_slot_floats + warp * kTileRows * MP;
             #pragma unroll
             for (int u = 0; u < NT; ++u) {
-                atomicAdd(rs + g * MP + 8 * u + 2 * t, acc[u][0]);
-                atomicAdd(rs + g * MP + 8 * u + 2 * t + 1, acc[u][1]);
-                atomicAdd(rs + (g + 8) * MP + 8 * u + 2 * t, acc[u][2]);
-                atomicAdd(rs + (g + 8) * MP + 8 * u + 2 * t + 1, acc[u][3]);
+                *reinterpret_cast<float2 *>(rs + g * MP + 8 * u + 2 * t) =
+                    make_float2(acc[u][0], acc[u][1]);
+                *reinterpret_cast<float2 *>(rs + (g + 8) * MP + 8 * u + 2 * t) =
+                    make_float2(acc[u][2], acc[u][3]);
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_done + 8 * s);
@@ -382,11 +403,12 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     const uint32_t max_rows = (uint32_t)(((units + grid - 1) / grid) * gran);
     const uint32_t max_tiles = (max_rows + kTileRows - 1) / kTileRows;
     const uint32_t mp = a.rows > 8 ? 16u : 8u;
-    const uint32_t fixed = kLutBytes + 128 + 16 * kMaxRank * 4;  // lut, barriers, T
+    const uint32_t fixed = kLutBytes + 256 + 16 * kMaxRank * 4;  // lut, barriers, T
+    const uint32_t red_bytes = 2u * p.consumer_warps * kTileRows * mp * 4u;  // two reduction slots
     uint32_t stages = max_tiles < (uint32_t)kMaxStages ? max_tiles : (uint32_t)kMaxStages;
     while (stages >= 1) {
         p.off_red = fixed;
-        p.off_stages = round_up(p.off_red + stages * kTileRows * mp * 4u, 128);
+        p.off_stages = round_up(p.off_red + red_bytes, 128);
         smem_bytes = p.off_stages + stages * p.stage_bytes;
         if (smem_bytes <= (uint32_t)kSmemLimit) break;
         --stages;
