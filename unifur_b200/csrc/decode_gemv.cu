@@ -22,12 +22,22 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "kernels.cuh"
 #include "ptx.cuh"
 
 namespace nf4 {
 
 __device__ int g_decode_error = 0;  // set when a bounded wait gives up
+
+#ifdef NF4_DECODE_TIMING
+// Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
+__device__ long long g_decode_ts[64];
+#define NF4_TS(i) do { if (blockIdx.x == 0 && lane == 0) g_decode_ts[(i)] = clock64(); } while (0)
+#else
+#define NF4_TS(i) do { } while (0)
+#endif
 
 namespace {
 
@@ -138,6 +148,32 @@ decode_kernel(const DecodeParams p) {
 
     const uint32_t bar_full = ptx::smem_addr(bars), bar_done = ptx::smem_addr(bars + kMaxStages);
     const uint32_t bar_red_free = ptx::smem_addr(bars + 2 * kMaxStages);
+    if (warp == 0) NF4_TS(0);
+
+    // Consumers ask for their slice of x before anything else: once the producer's bulk copies
+    // saturate the memory system, a late request would queue behind ~150 KB per SM.
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t nchunks = p.K / kChunk;
+    const uint32_t chunk0 = warp * p.chunks_per_warp;
+    uint4 xraw[NT][kMaxChunksPerWarp][2];
+    if (warp < p.consumer_warps) {
+        #pragma unroll
+        for (int u = 0; u < NT; ++u) {
+            const uint32_t m = 8 * u + g;
+            #pragma unroll
+            for (int c = 0; c < kMaxChunksPerWarp; ++c) {
+                const uint32_t kc = chunk0 + c;
+                xraw[u][c][0] = xraw[u][c][1] = make_uint4(0, 0, 0, 0);
+                if (m < p.M && c < (int)p.chunks_per_warp && kc < nchunks) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(
+                        p.x + (size_t)m * p.K + kc * kChunk + 16 * t);
+                    xraw[u][c][0] = __ldg(src);
+                    xraw[u][c][1] = __ldg(src + 1);
+                }
+            }
+        }
+    }
+
     if (warp == p.consumer_warps) {
         // =================== producer + epilogue warp ===================
         // The barriers are this warp's to set up, so the first loads leave before the other
@@ -166,6 +202,7 @@ decode_kernel(const DecodeParams p) {
         }
     }
     __syncthreads();
+    if (warp == 0) NF4_TS(1);
 
     if (warp == p.consumer_warps) {
         // T = x A^T comes from the pre-pass that ran before this kernel
@@ -205,35 +242,26 @@ decode_kernel(const DecodeParams p) {
                 }
             }
             __syncwarp();
+            if (tile < 8) NF4_TS(6 + 3 * tile);
             if (lane == 0) ptx::mbar_arrive(bar_red_free + 8 * (tile & 1u));
             if (tile + S < ntiles) {
                 ptx::fence_proxy_async();
                 issue_tile<DQ>(p, tile + S, n0, n1, S, stage_base, bar_full, lane);
             }
         }
+        NF4_TS(3);
         if (!ok && lane == 0) atomicExch(&g_decode_error, 1);
     } else if (warp < p.consumer_warps) {
         // ========================= consumer warps =========================
-        const uint32_t g = lane >> 2, t = lane & 3u;
-        const uint32_t nchunks = p.K / kChunk;
-        const uint32_t chunk0 = warp * p.chunks_per_warp;
         const float sos = DQ ? __ldg(p.scale_of_scales) : 0.0f;
 
         // x slice of this warp as f16 B-fragments: xf[u][c][j] = {b0, b1}
         uint32_t xf[NT][kMaxChunksPerWarp][4][2];
         #pragma unroll
         for (int u = 0; u < NT; ++u) {
-            const uint32_t m = 8 * u + g;
             #pragma unroll
             for (int c = 0; c < kMaxChunksPerWarp; ++c) {
-                const uint32_t kc = chunk0 + c;
-                uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
-                if (m < p.M && c < (int)p.chunks_per_warp && kc < nchunks) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(
-                        p.x + (size_t)m * p.K + kc * kChunk + 16 * t);
-                    q0 = __ldg(src);
-                    q1 = __ldg(src + 1);
-                }
+                const uint4 q0 = xraw[u][c][0], q1 = xraw[u][c][1];
                 const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
                 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -247,6 +275,7 @@ decode_kernel(const DecodeParams p) {
             }
         }
 
+        if (warp == 0) NF4_TS(2);
         const uint32_t *lut_lane = lut + lane;
         auto lut_at = [&](uint32_t word, int byte) -> uint32_t {
             return lut_lane[((word >> (8 * byte)) & 0xffu) << 5];
@@ -257,6 +286,7 @@ decode_kernel(const DecodeParams p) {
             const uint32_t s = tile % S;
             ok = ptx::mbar_wait_bounded(bar_full + 8 * s, (tile / S) & 1u);
             if (!ok) break;
+            if (warp == 0 && tile < 8) NF4_TS(4 + 3 * tile);
             const uint8_t *st = stage_base + (size_t)s * p.stage_bytes;
             const uint8_t *codes_lo = st + g * p.code_stride + t * 8;
             const uint8_t *codes_hi = codes_lo + 8 * p.code_stride;
@@ -305,6 +335,7 @@ decode_kernel(const DecodeParams p) {
                     }
                 }
             }
+            if (warp == 0 && tile < 8) NF4_TS(5 + 3 * tile);
             // this warp's partial sums go to its own slice of the tile's reduction slot; the
             // slot is free once the epilogue has summed the tile two before this one
             if (tile >= 2) {
@@ -481,6 +512,12 @@ int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
     if (p.M <= 8) return dq ? launch<1, true>(p, grid, smem, stream) : launch<1, false>(p, grid, smem, stream);
     return dq ? launch<2, true>(p, grid, smem, stream) : launch<2, false>(p, grid, smem, stream);
 }
+
+#ifdef NF4_DECODE_TIMING
+extern "C" __attribute__((visibility("default"))) int nf4_debug_decode_timestamps(long long *out64) {
+    return (int)cudaMemcpyFromSymbol(out64, g_decode_ts, sizeof(long long) * 64);
+}
+#endif
 
 int32_t decode_error_flag(int *host_value) {
     return check_cuda(cudaMemcpyFromSymbol(host_value, g_decode_error, sizeof(int)),
