@@ -167,6 +167,29 @@ NF4_API uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64
 
 NF4_API int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream);
 
+/* Decode-sized forward for callers that cannot allocate or own device memory.
+ * No counterpart in the reference (its forward allocates a fresh f32 weight on every call).
+ *
+ * Some hosts of this library only ever receive device pointers: a plug-in running inside
+ * another runtime's memory pool, a serving loop in a latency-critical section where cudaMalloc
+ * would synchronise the whole device, or an FFI shim with no allocator of its own.  Such a
+ * caller cannot supply the workspace nf4_linear_forward_dev asks for.  This entry point takes
+ * the same arguments (args->workspace / workspace_bytes are ignored) and keeps its scratch --
+ * the adapter intermediate x*A^T -- in a fixed array inside the library's device image,
+ * nf4_linear_noalloc_scratch_bytes() = 4096 bytes, which every GPU that loads the library
+ * holds until the process exits.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Limits: the decode shapes only (rows <= 16, bf16 x/y, NF4_LAYOUT_OUT_IN, d_in a multiple of 64
+ * and <= 4096) with rows * lora_rank * 4 <= 4096 bytes (e.g. 16 rows at rank 64); anything
+ * larger is refused with NF4_ERR_INVALID_ARG / NF4_ERR_UNSUPPORTED and a message.
+ * The first call on each device looks up the array's device address (with that device
+ * current); make that first call outside any stream capture.
+ * All calls on a device share the one array, which keeps whatever the last call left in it
+ * (nothing in it has to start at zero: each call rewrites what it reads).  Two calls whose
+ * kernels overlap on the GPU -- different streams, no dependency -- race on it; order them. */
+NF4_API uint64_t nf4_linear_noalloc_scratch_bytes(void);
+NF4_API int32_t nf4_linear_forward_noalloc_dev(const nf4_linear_args *args, void *stream);
+
 /* ------------------------------------------------ resident weight handles -- */
 
 /* An NF4 weight resident in device memory (what Nf4Linear holds in `packed`,

@@ -85,7 +85,7 @@ struct Carver {
 
 inline size_t dtype_bytes(int32_t dt) { return dt == NF4_DTYPE_F32 ? 4 : 2; }
 
-int32_t validate_linear(const nf4_linear_args *a) {
+int32_t validate_linear(const nf4_linear_args *a, bool needs_workspace = true) {
     if (!a) return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: null args");
     if (a->struct_bytes != sizeof(nf4_linear_args))
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: struct_bytes %u != %zu",
@@ -113,6 +113,7 @@ int32_t validate_linear(const nf4_linear_args *a) {
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: ldy < d_out");
     const uint64_t need = nf4_linear_workspace_bytes(a->rows, a->d_in, a->d_out,
                                                      a->lora_a ? a->lora_rank : 0);
+    if (!needs_workspace) return NF4_OK;
     if (need && (!a->workspace || a->workspace_bytes < need))
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward: workspace %llu < %llu bytes",
                     (unsigned long long)a->workspace_bytes, (unsigned long long)need);
@@ -250,6 +251,14 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     if (decode_supported(*args)) return decode_forward(*args, s);
     if (prefill_supported(*args)) return prefill_forward(*args, s);
     return generic_forward(*args, s);
+}
+
+uint64_t nf4_linear_noalloc_scratch_bytes(void) { return decode_static_scratch_bytes(); }
+
+int32_t nf4_linear_forward_noalloc_dev(const nf4_linear_args *args, void *stream) {
+    NF4_TRY(validate_linear(args, /*needs_workspace=*/false));
+    if (args->rows == 0) return NF4_OK;
+    return decode_forward_static_scratch(*args, static_cast<cudaStream_t>(stream));
 }
 
 // ---- host-pointer entry points ------------------------------------------------

@@ -519,6 +519,53 @@ extern "C" __attribute__((visibility("default"))) int nf4_debug_decode_timestamp
 }
 #endif
 
+// ---- decode forward whose scratch is a fixed device array (no allocation anywhere) ----
+// The adapter intermediate T = x A^T ([rows][rank] f32) is the only scratch the decode
+// path needs.  Here it lives in a file-scope device array instead of a caller buffer.
+constexpr uint32_t kStaticScratchBytes = 16 * kMaxRank * sizeof(float);  // 16 rows x rank 64
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+uint64_t decode_static_scratch_bytes() { return kStaticScratchBytes; }
+
+int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t stream) {
+    DecodeParams p;
+    uint32_t grid, smem;
+    if (!plan(a, p, grid, smem))
+        return fail(NF4_ERR_UNSUPPORTED,
+                    "nf4_linear_forward_noalloc_dev: only the decode shapes are served (rows <= 16, "
+                    "bf16, W [d_out, d_in], d_in %% 64 == 0 and <= 4096, rank <= 64)");
+    const uint64_t need = (uint64_t)p.M * p.rank * sizeof(float);
+    if (need > kStaticScratchBytes)
+        return fail(NF4_ERR_INVALID_ARG,
+                    "nf4_linear_forward_noalloc_dev: rows * rank * 4 = %llu bytes exceeds the fixed "
+                    "scratch of %u bytes", (unsigned long long)need, kStaticScratchBytes);
+    // In host code the array's name is only a handle: the device address has to be asked for,
+    // once per device, with that device current.
+    static std::mutex mu;
+    static void *scratch_of_device[64] = {};
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NF4_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!scratch_of_device[dev]) {
+            void *ptr = nullptr;
+            NF4_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+            scratch_of_device[dev] = ptr;
+        }
+        scratch = scratch_of_device[dev];
+    }
+    if (p.rank) {
+        float *t = static_cast<float *>(scratch);  // fully rewritten by the pre-pass: no clearing needed
+        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream));
+        p.t = t;
+    }
+    const bool dq = a.scale_codes != nullptr;
+    if (p.M <= 8) return dq ? launch<1, true>(p, grid, smem, stream) : launch<1, false>(p, grid, smem, stream);
+    return dq ? launch<2, true>(p, grid, smem, stream) : launch<2, false>(p, grid, smem, stream);
+}
+
 int32_t decode_error_flag(int *host_value) {
     return check_cuda(cudaMemcpyFromSymbol(host_value, g_decode_error, sizeof(int)),
                       "read decode error flag");

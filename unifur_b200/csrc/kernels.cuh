@@ -26,6 +26,8 @@ uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank);
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);
 
 int32_t decode_error_flag(int *host_value);
+uint64_t decode_static_scratch_bytes();
+int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t stream);
 
 // generic_linear.cu: any layout / dtype / shape on CUDA cores (exact f32 weights).
 uint64_t generic_workspace_bytes(uint64_t rows, uint32_t lora_rank);
