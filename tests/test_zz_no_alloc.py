@@ -53,8 +53,13 @@ def test_noalloc_entry_point_matches_the_workspace_entry_point(oracle):
         _lib.check(L.nf4_linear_forward_noalloc_dev(
             ctypes.byref(build_args(x, packed, absmax, la, lb, y_new, None, rank, 2.0, rows, k, n)), None))
         torch.cuda.synchronize()
-        # same kernels, same fixed-order reduction: identical bits
-        assert torch.equal(y_ref, y_new)
+        # The two entry points may run different decode kernels (the workspace one can use
+        # the split-K tensor-memory kernel, which needs more scratch than the fixed array
+        # holds), so they agree to the forward's tolerance rather than bit for bit: each is
+        # within rel. L2 1e-3 of the exact result before its single bf16 rounding.
+        a32, b32 = y_ref.float(), y_new.float()
+        assert ((a32 - b32).norm() / a32.norm()).item() <= 2 * (1e-3 + 2.0 ** -9)
+        assert bool(((a32 - b32).abs() <= 2.0 ** -6 * a32.abs() + 1e-3 * a32.abs().max()).all())
         # and both agree with the oracle within the forward's tolerance (bf16 output rounding added)
         ref = oracle.qlora_forward_bnb(x.float().cpu().numpy(), packed_np, absmax_np, n, k,
                                        la.float().cpu().numpy() if rank else None,

@@ -235,10 +235,12 @@ int32_t nf4_quantize_dequantize_dev(const float *values, uint64_t len, int32_t d
 
 uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                     uint32_t lora_rank) {
-    (void)d_out;
+
     uint64_t need = decode_workspace_bytes(rows, lora_rank);
     const uint64_t b = prefill_workspace_bytes(rows, d_in, lora_rank);
     const uint64_t c = generic_workspace_bytes(rows, lora_rank);
+    const uint64_t d = decode2_workspace_bytes(rows, d_in, d_out, lora_rank);
+    if (d > need) need = d;
     if (b > need) need = b;
     if (c > need) need = c;
     return need;
@@ -248,6 +250,7 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     NF4_TRY(validate_linear(args));
     if (args->rows == 0) return NF4_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (decode2_supported(*args)) return decode2_forward(*args, s);
     if (decode_supported(*args)) return decode_forward(*args, s);
     if (prefill_supported(*args)) return prefill_forward(*args, s);
     return generic_forward(*args, s);

@@ -29,6 +29,11 @@ int32_t decode_error_flag(int *host_value);
 uint64_t decode_static_scratch_bytes();
 int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t stream);
 
+// decode_umma.cu: rows <= 16 through tcgen05 (the fast decode path when its shape rules hold).
+bool decode2_supported(const nf4_linear_args &a);
+uint64_t decode2_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
+int32_t decode2_forward(const nf4_linear_args &a, cudaStream_t stream);
+
 // generic_linear.cu: any layout / dtype / shape on CUDA cores (exact f32 weights).
 uint64_t generic_workspace_bytes(uint64_t rows, uint32_t lora_rank);
 int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream);
