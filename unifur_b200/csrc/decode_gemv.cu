@@ -205,9 +205,12 @@ decode_kernel(const DecodeParams p) {
     if (warp == 0) NF4_TS(1);
 
     if (warp == p.consumer_warps) {
-        // T = x A^T comes from the pre-pass that ran before this kernel
-        if (p.rank)
-            for (uint32_t i = lane; i < p.M * p.rank; i += 32) t_s[i] = __ldg(p.t + i);
+        // T = x A^T comes from the pre-pass, which may still be running: wait for it here,
+        // after this kernel's own loads have long been issued
+        if (p.rank) {
+            ptx::pdl_wait();
+            for (uint32_t i = lane; i < p.M * p.rank; i += 32) t_s[i] = __ldcg(p.t + i);
+        }
         __syncwarp();
         // Finish tiles in order: sum the warps' partials in a fixed order (so the result does
         // not depend on timing), add bias and the adapter term, convert, store; then hand the
@@ -361,6 +364,7 @@ decode_kernel(const DecodeParams p) {
 __global__ void __launch_bounds__(128)
 lora_t_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a, uint32_t K,
               uint32_t rank, float *__restrict__ t_out) {
+    ptx::pdl_launch_dependents();  // the GEMV may start streaming weights right away
     const uint32_t j = blockIdx.x, m = blockIdx.y;
     const __nv_bfloat16 *xr = x + (size_t)m * K, *ar = a + (size_t)j * K;
     float acc = 0.0f;
@@ -472,9 +476,9 @@ int32_t launch(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaSt
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
         configured = true;
     }
-    decode_kernel<NT, DQ><<<grid, (p.consumer_warps + 1) * 32, smem_bytes, stream>>>(p);
     count_launch();
-    return check_cuda(cudaGetLastError(), "decode_kernel launch");
+    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3((p.consumer_warps + 1) * 32),
+                                   smem_bytes, stream, p.rank != 0 && pdl_enabled(), p);
 }
 
 }  // namespace

@@ -40,6 +40,14 @@ namespace nf4 {
 
 __device__ int g_decode2_error = 0;  // set when a bounded wait gives up
 
+#ifdef NF4_DECODE_TIMING
+// Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
+__device__ long long g_decode2_ts[64];
+#define NF4_TS2(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31u) == 0) g_decode2_ts[(i)] = clock64(); } while (0)
+#else
+#define NF4_TS2(i) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kRowsPerTile = 128;
@@ -49,11 +57,16 @@ constexpr int kScaleStageBytes = kRowsPerTile * 16;
 constexpr int kStageBytes = kCodeStageBytes + kScaleStageBytes;
 constexpr int kMaxCodeStages = 6;
 constexpr int kASlots = 8;                  // TMEM ring of dequantised blocks (32 columns each)
-constexpr int kMaxSegments = 8;             // accumulators of 16 columns each
-constexpr int kAccCols = 16;
+constexpr int kMaxSegments = 2;             // row-tiles one run may touch
+constexpr int kAccCols = 16;                // one accumulator: 128 rows x 16 activation rows
+constexpr int kAccPerSeg = 8;               // independent accumulators a segment's MMAs rotate over
 constexpr int kTmemCols = 512;
 constexpr int kExpanderWarps = 16;
-constexpr int kThreads = (kExpanderWarps + 2) * 32;  // + TMA warp + MMA warp
+constexpr int kIssuerWarps = 4;             // one MMA-issuing thread per expander group
+constexpr int kWarpTma = kExpanderWarps;
+constexpr int kWarpIssuer0 = kExpanderWarps + 1;
+constexpr int kWarpFinish0 = kWarpIssuer0 + kIssuerWarps;   // 21: warps 21..24 = lane quarters 1,2,3,0
+constexpr int kThreads = (kWarpFinish0 + 4) * 32;
 constexpr int kLutBytes = 256 * 32 * 4;
 constexpr int kXBlockBytes = 16 * 128;      // 16 rows x 64 f16
 constexpr int kMaxXBlocks = 56;
@@ -159,7 +172,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // barrier slots
 constexpr int kBarCodeFull = 0, kBarCodeEmpty = kBarCodeFull + kMaxCodeStages,
               kBarAFull = kBarCodeEmpty + kMaxCodeStages, kBarAEmpty = kBarAFull + kASlots,
-              kBarAccDone = kBarAEmpty + kASlots, kNumBars = kBarAccDone + 1;
+              kBarSegDone = kBarAEmpty + kASlots, kBarLut = kBarSegDone + kMaxSegments,
+              kNumBars = kBarLut + 1;
+
+// The lookup table in its shared-memory form -- entry (byte, lane) = half2 {level[byte & 15],
+// level[byte >> 4]}, one copy per lane so no two lanes ever share a bank -- built at compile
+// time and brought in with a single bulk copy.
+struct LutImage {
+    uint32_t v[256 * 32];
+};
+constexpr LutImage make_lut_image() {
+    constexpr uint32_t h[16] = {NF4_LEVEL_F16_BITS_LIST};
+    LutImage t{};
+    for (int byte = 0; byte < 256; ++byte)
+        for (int lane = 0; lane < 32; ++lane)
+            t.v[byte * 32 + lane] = h[byte & 15] | (h[byte >> 4] << 16);
+    return t;
+}
+__device__ __align__(128) const LutImage g_lut_image = make_lut_image();
 
 template <bool DQ>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -178,6 +208,7 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t grid = gridDim.x, cta = blockIdx.x;
+    if (warp == 0) NF4_TS2(0);
     const uint32_t u0 = run_start(cta, p.total_units, grid);
     const uint32_t u1 = run_start(cta + 1, p.total_units, grid);
     const uint32_t S = p.code_stages;
@@ -188,9 +219,21 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
     Segment seg0;
     segment_of(p, u0, u1, 0, seg0);
     const uint32_t x_base = (p.x_blocks == p.kb) ? 0u : seg0.kb0;
-    auto x_slot = [&](uint32_t kb) { return kb >= x_base ? kb - x_base : kb + p.kb - x_base; };
 
-    if (warp == kExpanderWarps) {
+    auto issue_stage = [&](uint32_t st, uint32_t rt, uint32_t g4) {
+        const uint32_t s = st % S;
+        uint8_t *dst = ring + s * kStageBytes;
+        ptx::mbar_arrive_expect_tx(bar(kBarCodeFull + s), kStageBytes);
+        ptx::tma_load_2d(ptx::smem_addr(dst), &tmap_codes, (int32_t)(g4 * 128),
+                         (int32_t)(rt * kRowsPerTile), bar(kBarCodeFull + s));
+        // scales: f32 -> the tile's 4 blocks; u8 -> the 16-block group holding them
+        const int32_t sx = DQ ? (int32_t)((g4 * 4) & ~15u) : (int32_t)(g4 * 4);
+        ptx::tma_load_2d(ptx::smem_addr(dst + kCodeStageBytes), &tmap_scales, sx,
+                         (int32_t)(rt * kRowsPerTile), bar(kBarCodeFull + s));
+    };
+
+    // ------------------------------- set-up -------------------------------
+    if (warp == kWarpTma) {
         if (lane == 0) {
             for (uint32_t s = 0; s < S; ++s) {
                 ptx::mbar_init(bar(kBarCodeFull + s), 1);
@@ -200,109 +243,138 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                 ptx::mbar_init(bar(kBarAFull + s), 4);
                 ptx::mbar_init(bar(kBarAEmpty + s), 1);
             }
-            ptx::mbar_init(bar(kBarAccDone), 1);
+            for (int s = 0; s < kMaxSegments; ++s) ptx::mbar_init(bar(kBarSegDone + s), kIssuerWarps);
+            ptx::mbar_init(bar(kBarLut), 1);
             ptx::fence_mbar_init();
             ptx::fence_proxy_async();
-            ptx::prefetch_tmap(&tmap_codes);
-            ptx::prefetch_tmap(&tmap_scales);
         }
-    } else if (warp == kExpanderWarps + 1) {
+        // let the expanders' few requests for x leave first: once ~100 KB of bulk copies are
+        // queued per SM, a late request waits microseconds behind them
+        asm volatile("bar.sync 3, %0;" ::"n"((kExpanderWarps + 1) * 32) : "memory");
+        if (lane == 0) {
+            // nothing else touches the ring or the table before the set-up barrier below, so
+            // the first requests leave right away
+            ptx::mbar_arrive_expect_tx(bar(kBarLut), kLutBytes);
+            ptx::bulk_g2s(ptx::smem_addr(lut), &g_lut_image, kLutBytes, bar(kBarLut));
+            uint32_t st = 0;
+            Segment sg;
+            for (uint32_t i = 0; st < S && segment_of(p, u0, u1, i, sg); ++i)
+                for (uint32_t g4 = sg.kb0 / 4; g4 * 4 < sg.kb1 && st < S; ++g4, ++st)
+                    issue_stage(st, sg.rt, g4);
+        }
+    } else if (warp == kWarpIssuer0) {
         ptx::tmem_alloc(ptx::smem_addr(tmem_slot), kTmemCols);
         ptx::tmem_relinquish();
-    } else {
+    } else if (warp < kExpanderWarps) {
         // ---- x's k-range -> f16, canonical K-major 128B-swizzled rows (16 rows per block) ----
-        // one 16-byte chunk (8 values) per thread-iteration; rows >= M are zero
+        // one 16-byte chunk (8 values) per thread and step, four loads in flight; rows >= M are zero
         const uint32_t chunks = p.x_blocks * 16 * 8;
-        const uint32_t nthreads = kExpanderWarps * 32;
-        for (uint32_t i = tid; i < chunks; i += nthreads) {
-            const uint32_t slot = i >> 7, row = (i >> 3) & 15u, c = i & 7u;
-            uint32_t kb = slot + x_base;
-            if (kb >= p.kb) kb -= p.kb;
-            uint4 o = make_uint4(0, 0, 0, 0);
-            if (row < p.M) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(
-                    p.x + (size_t)row * p.K + (size_t)kb * 64 + c * 8));
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        constexpr uint32_t nthreads = kExpanderWarps * 32;
+        bool released = false;
+        for (uint32_t base = tid; base < chunks; base += 4 * nthreads) {
+            uint4 v[4];
+            #pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = base + u * nthreads;
+                const uint32_t slot = i >> 7, row = (i >> 3) & 15u, c = i & 7u;
+                uint32_t kb = slot + x_base;
+                if (kb >= p.kb) kb -= p.kb;
+                v[u] = make_uint4(0, 0, 0, 0);
+                if (i < chunks && row < p.M)
+                    v[u] = __ldg(reinterpret_cast<const uint4 *>(
+                        p.x + (size_t)row * p.K + (size_t)kb * 64 + c * 8));
+            }
+            if (!released) {  // first batch of loads is out: release the producer
+                asm volatile("bar.arrive 3, %0;" ::"n"((kExpanderWarps + 1) * 32) : "memory");
+                released = true;
+            }
+            #pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = base + u * nthreads;
+                if (i >= chunks) break;
+                const uint32_t slot = i >> 7, row = (i >> 3) & 15u, c = i & 7u;
+                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
                 uint32_t h[4];
                 #pragma unroll
                 for (int q = 0; q < 4; ++q)
                     h[q] = pack_h2(__uint_as_float(w[q] << 16), __uint_as_float(w[q] & 0xffff0000u));
-                o = make_uint4(h[0], h[1], h[2], h[3]);
+                uint8_t *dst = x_s + slot * kXBlockBytes + (row >> 3) * 1024 + (row & 7u) * 128 +
+                               ((c ^ (row & 7u)) << 4);
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
             }
-            uint8_t *dst = x_s + slot * kXBlockBytes + (row >> 3) * 1024 + (row & 7u) * 128 +
-                           ((c ^ (row & 7u)) << 4);
-            *reinterpret_cast<uint4 *>(dst) = o;
         }
-        // ---- lookup table: byte -> half2 {level[lo nibble], level[hi nibble]}, one copy per lane
-        for (uint32_t i = tid; i < 256 * 32; i += nthreads) {
-            const uint32_t byte = i >> 5;
-            lut[i] = pack_h2(__uint_as_float(c_level_bits[byte & 15u]),
-                             __uint_as_float(c_level_bits[byte >> 4]));
-        }
-        if (p.rank)
-            for (uint32_t i = tid; i < p.M * p.rank; i += nthreads) t_s[i] = __ldg(p.t + i);
+        if (!released) asm volatile("bar.arrive 3, %0;" ::"n"((kExpanderWarps + 1) * 32) : "memory");
         ptx::fence_proxy_async();  // x_s is read by the tensor core through the async proxy
+        if (warp == 0) NF4_TS2(6);
     }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_a = tmem_base + kMaxSegments * kAccCols;
+    const uint32_t tmem_a = tmem_base + kMaxSegments * kAccPerSeg * kAccCols;
+    if (warp == 0) NF4_TS2(1);
 
     bool ok = true;
 
-    if (warp == kExpanderWarps) {
+    if (warp == kWarpTma) {
         // ============================== TMA producer ==============================
         if (lane == 0) {
             uint32_t st = 0;
             Segment sg;
             for (uint32_t i = 0; ok && segment_of(p, u0, u1, i, sg); ++i) {
                 for (uint32_t g4 = sg.kb0 / 4; g4 * 4 < sg.kb1; ++g4, ++st) {
+                    if (st < S) continue;  // requested before the set-up barrier
                     const uint32_t s = st % S, ph = (st / S) & 1u;
                     if (!ptx::mbar_wait_bounded(bar(kBarCodeEmpty + s), ph ^ 1u)) {
                         ok = false;
                         break;
                     }
-                    uint8_t *dst = ring + s * kStageBytes;
-                    ptx::mbar_arrive_expect_tx(bar(kBarCodeFull + s), kStageBytes);
-                    ptx::tma_load_2d(ptx::smem_addr(dst), &tmap_codes, (int32_t)(g4 * 128),
-                                     (int32_t)(sg.rt * kRowsPerTile), bar(kBarCodeFull + s));
-                    // scales: f32 -> the tile's 4 blocks; u8 -> the 16-block group holding them
-                    const int32_t sx = DQ ? (int32_t)((g4 * 4) & ~15u) : (int32_t)(g4 * 4);
-                    ptx::tma_load_2d(ptx::smem_addr(dst + kCodeStageBytes), &tmap_scales, sx,
-                                     (int32_t)(sg.rt * kRowsPerTile), bar(kBarCodeFull + s));
+                    issue_stage(st, sg.rt, g4);
                 }
             }
             if (!ok) atomicExch(&g_decode2_error, 1);
         }
-    } else if (warp == kExpanderWarps + 1) {
-        // =============================== MMA issuer ===============================
+    } else if (warp >= kWarpIssuer0 && warp < kWarpIssuer0 + kIssuerWarps) {
+        // ============================== MMA issuers ==============================
+        // Issuing a tcgen05.mma costs its thread ~100 cycles, far more than a 128 x 16 x 16
+        // MMA takes to run, so four threads issue side by side: issuer g takes the blocks
+        // kb % 4 == g (the ones expander group g writes) and owns two accumulators per segment.
         if (lane == 0) {
+            const uint32_t g = warp - kWarpIssuer0;
             // f16 x f16 -> f32, M = 128, N = 16, both K-major
             constexpr uint32_t idesc = (1u << 4) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-            uint32_t bc = 0;
+            const uint32_t xs_addr = ptx::smem_addr(x_s);
+            uint32_t bc_base = 0;
             Segment sg;
             for (uint32_t i = 0; ok && segment_of(p, u0, u1, i, sg); ++i) {
-                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++bc) {
+                uint32_t lb = 0;
+                for (uint32_t kb = (sg.kb0 & ~3u) + g; kb < sg.kb1; kb += 4) {
+                    if (kb < sg.kb0) continue;
+                    const uint32_t bc = bc_base + (kb - sg.kb0);
                     const uint32_t slot = bc % kASlots, ph = (bc / kASlots) & 1u;
                     if (!ptx::mbar_wait_bounded(bar(kBarAFull + slot), ph)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint64_t bdesc =
-                        make_kmajor_sw128_desc(ptx::smem_addr(x_s + x_slot(kb) * kXBlockBytes));
-                    #pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j)
-                        ptx::mma_ts_f16(tmem_base + i * kAccCols, tmem_a + slot * 32 + j * 8,
-                                        bdesc + 2 * j, idesc, (kb != sg.kb0 || j != 0) ? 1u : 0u);
+                    const uint32_t xslot = kb >= x_base ? kb - x_base : kb + p.kb - x_base;
+                    const uint64_t bdesc = make_kmajor_sw128_desc(xs_addr + xslot * kXBlockBytes);
+                    const uint32_t acc = tmem_base + (i * kAccPerSeg + g * 2 + (lb & 1u)) * kAccCols;
+                    const uint32_t a = tmem_a + slot * 32;
+                    const uint32_t first = lb >= 2 ? 1u : 0u;
+                    ptx::mma_ts_f16(acc, a, bdesc, idesc, first);
+                    ptx::mma_ts_f16(acc, a + 8, bdesc + 2, idesc, 1u);
+                    ptx::mma_ts_f16(acc, a + 16, bdesc + 4, idesc, 1u);
+                    ptx::mma_ts_f16(acc, a + 24, bdesc + 6, idesc, 1u);
                     ptx::tc_commit(bar(kBarAEmpty + slot));
+                    ++lb;
                 }
+                if (ok) ptx::tc_commit(bar(kBarSegDone + i));
+                bc_base += sg.kb1 - sg.kb0;
             }
-            if (ok) ptx::tc_commit(bar(kBarAccDone));
             if (!ok) atomicExch(&g_decode2_error, 2);
         }
-    } else {
+    } else if (warp < kExpanderWarps) {
         // ================================ expanders ================================
         const uint32_t q = warp & 3u, grp = warp >> 2;   // TMEM lane quarter, block within a tile
         const uint32_t row = q * 32 + lane;              // row inside the 128-row tile = TMEM lane
@@ -310,6 +382,7 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
         const uint32_t *lut_lane = lut + lane;
         const uint32_t swz = row & 7u;
         uint32_t st = 0, bc_base = 0;
+        ok = ptx::mbar_wait_bounded(bar(kBarLut), 0);
         Segment sg;
         for (uint32_t i = 0; ok && segment_of(p, u0, u1, i, sg); ++i) {
             for (uint32_t g4 = sg.kb0 / 4; g4 * 4 < sg.kb1; ++g4, ++st) {
@@ -318,6 +391,7 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                     ok = false;
                     break;
                 }
+                if (warp == 0 && st < 12) NF4_TS2(8 + 2 * st);
                 const uint32_t kb = g4 * 4 + grp;
                 if (kb >= sg.kb0 && kb < sg.kb1) {
                     const uint8_t *stage = ring + s * kStageBytes;
@@ -352,87 +426,154 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                     if (lane == 0) ptx::mbar_arrive(bar(kBarAFull + slot));
                 }
                 __syncwarp();
+                if (warp == 0 && st < 12) NF4_TS2(9 + 2 * st);
                 if (lane == 0) ptx::mbar_arrive(bar(kBarCodeEmpty + s));
             }
             bc_base += sg.kb1 - sg.kb0;
         }
+        if (warp == 0) NF4_TS2(2);
         if (!ok && lane == 0) atomicExch(&g_decode2_error, 3);
-    }
-
-    // ================================== finish ==================================
-    // warps 0-3 (lane quarters 0-3) read the accumulators once every MMA has completed
-    if (warp < 4) {
-        if (ok) ok = ptx::mbar_wait_bounded(bar(kBarAccDone), 0);
-        ptx::tc_fence_after();
-    }
-    Segment sg;
-    for (uint32_t i = 0; segment_of(p, u0, u1, i, sg); ++i) {
-        const uint32_t n = sg.rt * kRowsPerTile + tid;  // meaningful for tid < 128 (warps 0-3)
-        const bool whole = sg.kb0 == 0 && sg.kb1 == p.kb;
-        float v[16];
-        if (warp < 4) {
-            uint32_t r[16];
-            tmem_ld16(tmem_base + ((warp * 32) << 16) + i * kAccCols, r);
-            ptx::tmem_wait_ld();
-            #pragma unroll
-            for (int m = 0; m < 16; ++m) v[m] = ok ? __uint_as_float(r[m]) : 0.0f;
-        }
-        bool finish = whole;
-        uint32_t c_first = cta, c_last = cta;
-        if (!whole) {
-            // park the partial, then see whether this CTA is the last one of the row-tile
-            c_first = cta_of_unit(sg.rt * p.units_per_tile, p.total_units, grid);
-            c_last = cta_of_unit((sg.rt + 1) * p.units_per_tile - 1, p.total_units, grid);
-            if (warp < 4) {
-                float *dst = p.partials + (size_t)(cta + sg.rt) * (16 * kRowsPerTile);
-                #pragma unroll
-                for (int m = 0; m < 16; ++m) dst[m * kRowsPerTile + tid] = v[m];
-                __threadfence();
-            }
-            __syncthreads();
-            if (tid == 0) {
-                const int old = atomicAdd(p.counters + sg.rt, 1);
-                *last_flag = (old == (int)(c_last - c_first));
-            }
-            __syncthreads();
-            finish = *last_flag != 0;
-            if (finish) __threadfence();
-        }
-        if (finish && warp < 4) {
-            if (!whole) {
-                #pragma unroll
-                for (int m = 0; m < 16; ++m) v[m] = 0.0f;
-                for (uint32_t c = c_first; c <= c_last; ++c) {
-                    const float *src = p.partials + (size_t)(c + sg.rt) * (16 * kRowsPerTile);
-                    #pragma unroll
-                    for (int m = 0; m < 16; ++m) v[m] += __ldcg(src + m * kRowsPerTile + tid);
+    } else if (warp >= kWarpFinish0) {
+        // ================================= finish =================================
+        // Four dedicated warps (one per TMEM lane quarter) finish a segment as soon as its MMAs
+        // are done, so only the last segment's finish is exposed at the end of the kernel.
+        const uint32_t q = warp & 3u;
+        const uint32_t row = q * 32 + lane;  // TMEM lane = row inside the 128-row tile
+        const uint32_t ftid = (warp - kWarpFinish0) * 32 + lane;
+        Segment sg;
+        // this thread's LoRA-B rows (one per segment) are fetched now, long before they are needed
+        uint4 lbq[kMaxSegments][2];
+        const bool lb_in_regs = p.rank == 16;
+        #pragma unroll
+        for (int i = 0; i < kMaxSegments; ++i) {
+            lbq[i][0] = lbq[i][1] = make_uint4(0, 0, 0, 0);
+            if (lb_in_regs && segment_of(p, u0, u1, i, sg)) {
+                const uint32_t n = sg.rt * kRowsPerTile + row;
+                if (n < p.N) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(p.lora_b + (size_t)n * 16);
+                    lbq[i][0] = __ldg(src);
+                    lbq[i][1] = __ldg(src + 1);
                 }
             }
-            if (n < p.N) {
+        }
+        // T = x A^T comes from the pre-pass, which may still be running (programmatic dependent
+        // launch): wait for it here, with this kernel's streaming already under way
+        if (p.rank) {
+            ptx::pdl_wait();
+            for (uint32_t i = ftid; i < p.M * p.rank; i += 128) t_s[i] = __ldcg(p.t + i);
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+        }
+        #pragma unroll
+        for (uint32_t i = 0; i < (uint32_t)kMaxSegments; ++i) {
+            if (!segment_of(p, u0, u1, i, sg)) break;
+            if (ok) ok = ptx::mbar_wait_bounded(bar(kBarSegDone + i), 0);
+            ptx::tc_fence_after();
+            if (i == 0 && ftid == 0) NF4_TS2(3);
+            float v[16];
+            #pragma unroll
+            for (int m = 0; m < 16; ++m) v[m] = 0.0f;
+            // issuer g wrote accumulator 2g (and 2g+1 when it had a second block in the segment)
+            #pragma unroll
+            for (uint32_t g = 0; g < 4; ++g) {
+                const uint32_t first_kb = (sg.kb0 & ~3u) + g + ((((sg.kb0 & ~3u) + g) < sg.kb0) ? 4u : 0u);
+                const uint32_t cnt = first_kb < sg.kb1 ? (sg.kb1 - first_kb + 3) / 4 : 0u;
+                for (uint32_t a = 0; a < (cnt < 2u ? cnt : 2u); ++a) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + ((q * 32) << 16) + (i * kAccPerSeg + g * 2 + a) * kAccCols, r);
+                    ptx::tmem_wait_ld();
+                    #pragma unroll
+                    for (int m = 0; m < 16; ++m) v[m] += ok ? __uint_as_float(r[m]) : 0.0f;
+                }
+            }
+            const bool whole = sg.kb0 == 0 && sg.kb1 == p.kb;
+            bool finish = whole;
+            uint32_t c_first = cta, c_last = cta;
+            bool own_in_memory = false;
+            if (!whole) {
+                c_first = cta_of_unit(sg.rt * p.units_per_tile, p.total_units, grid);
+                c_last = cta_of_unit((sg.rt + 1) * p.units_per_tile - 1, p.total_units, grid);
+                const int others = (int)(c_last - c_first);
+                // everyone else already in?  then this CTA finishes the tile straight from its
+                // registers and never writes its own partial
+                if (ftid == 0) *last_flag = (atomicAdd(p.counters + sg.rt, 0) == others) ? 1 : 0;
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                finish = *last_flag != 0;
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (!finish) {
+                    float *dst = p.partials + (size_t)(cta + sg.rt) * (16 * kRowsPerTile);
+                    #pragma unroll
+                    for (int m = 0; m < 16; ++m) dst[m * kRowsPerTile + row] = v[m];
+                    __threadfence();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (ftid == 0) *last_flag = (atomicAdd(p.counters + sg.rt, 1) == others) ? 1 : 0;
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    finish = *last_flag != 0;
+                    own_in_memory = true;
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                }
+                if (finish) {
+                    __threadfence();
+                    float own[16];
+                    #pragma unroll
+                    for (int m = 0; m < 16; ++m) {
+                        own[m] = v[m];
+                        v[m] = 0.0f;
+                    }
+                    // fixed order c_first .. c_last, whoever happens to be last
+                    for (uint32_t c = c_first; c <= c_last; ++c) {
+                        if (c == cta && !own_in_memory) {
+                            #pragma unroll
+                            for (int m = 0; m < 16; ++m) v[m] += own[m];
+                        } else {
+                            const float *src = p.partials + (size_t)(c + sg.rt) * (16 * kRowsPerTile);
+                            #pragma unroll
+                            for (int m = 0; m < 16; ++m) v[m] += __ldcg(src + m * kRowsPerTile + row);
+                        }
+                    }
+                }
+            }
+            const uint32_t n = sg.rt * kRowsPerTile + row;
+            if (finish && n < p.N) {
                 const float b = p.bias ? __ldg(p.bias + n) : 0.0f;
+                float dot[16];
+                #pragma unroll
+                for (int m = 0; m < 16; ++m) dot[m] = 0.0f;
+                if (lb_in_regs) {
+                    const uint32_t w[8] = {lbq[i][0].x, lbq[i][0].y, lbq[i][0].z, lbq[i][0].w,
+                                           lbq[i][1].x, lbq[i][1].y, lbq[i][1].z, lbq[i][1].w};
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j) {
+                        const float bj = __uint_as_float((j & 1u) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
+                        #pragma unroll
+                        for (uint32_t m = 0; m < 16; ++m)
+                            if (m < p.M) dot[m] = fmaf(t_s[m * 16 + j], bj, dot[m]);
+                    }
+                } else {
+                    for (uint32_t j = 0; j < p.rank; ++j) {
+                        const float bj = __bfloat162float(p.lora_b[(size_t)n * p.rank + j]);
+                        #pragma unroll
+                        for (uint32_t m = 0; m < 16; ++m)
+                            if (m < p.M) dot[m] = fmaf(t_s[m * p.rank + j], bj, dot[m]);
+                    }
+                }
                 #pragma unroll
                 for (uint32_t m = 0; m < 16; ++m) {
                     if (m >= p.M) break;
-                    float o = v[m];
-                    if (p.rank) {
-                        float dot = 0.0f;
-                        for (uint32_t j = 0; j < p.rank; ++j)
-                            dot = fmaf(t_s[m * p.rank + j],
-                                       __bfloat162float(p.lora_b[(size_t)n * p.rank + j]), dot);
-                        o = fmaf(dot, p.lora_scale, o);  // scale applied last
-                    }
-                    o += b;
+                    const float o = fmaf(dot[m], p.lora_scale, v[m]) + b;  // scale applied last
                     const size_t idx = (size_t)m * p.ldy + n;
                     if (p.y_f32) static_cast<float *>(p.y)[idx] = o;
                     else static_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(o);
                 }
             }
         }
+        if (ftid == 0) NF4_TS2(4);
+        if (!ok && lane == 0) atomicExch(&g_decode2_error, 4);
     }
 
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == kExpanderWarps + 1) {
+    if (warp == 0) NF4_TS2(5);
+    if (warp == kWarpIssuer0) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -510,7 +651,8 @@ bool make_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, bool dq, uint32_t r
     for (;;) {
         const uint32_t run = (p.total_units + grid - 1) / grid;           // units
         const uint32_t blocks = run * 2 < p.kb ? run * 2 : p.kb;
-        const uint32_t segs = (run + p.units_per_tile - 1) / p.units_per_tile + 1;
+        const uint32_t segs = run >= p.units_per_tile
+                                  ? (run + p.units_per_tile - 1) / p.units_per_tile + 1 : 2;
         if (blocks <= (uint32_t)kMaxXBlocks && segs <= (uint32_t)kMaxSegments) {
             p.x_blocks = blocks;
             break;
@@ -555,12 +697,18 @@ int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cud
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
         configured = true;
     }
-    decode2_kernel<DQ><<<pl.grid, kThreads, pl.smem_bytes, stream>>>(mc, ms, pl.p);
     count_launch();
-    return check_cuda(cudaGetLastError(), "decode2_kernel launch");
+    return launch_maybe_overlapped(decode2_kernel<DQ>, dim3(pl.grid), dim3(kThreads), pl.smem_bytes,
+                                   stream, pl.p.rank != 0 && pdl_enabled(), mc, ms, pl.p);
 }
 
 }  // namespace
+
+#ifdef NF4_DECODE_TIMING
+extern "C" __attribute__((visibility("default"))) int nf4_debug_decode2_timestamps(long long *out64) {
+    return (int)cudaMemcpyFromSymbol(out64, g_decode2_ts, sizeof(long long) * 64);
+}
+#endif
 
 // lora_t_small lives in decode_gemv.cu
 int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, uint32_t rank,

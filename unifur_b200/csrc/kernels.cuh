@@ -4,6 +4,26 @@
 
 namespace nf4 {
 
+// Launch `kernel` so that it may start while its predecessor in `stream` is still running
+// (programmatic dependent launch); the kernel must call ptx::pdl_wait() before it touches
+// anything the predecessor writes.  Falls back to an ordinary launch when `overlap` is false.
+template <class... KArgs, class... Args>
+int32_t launch_maybe_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, bool overlap, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...), "kernel launch");
+}
+bool pdl_enabled();  // api.cu: NF4_PDL=0 in the environment turns the overlap off
+
 // quantize.cu
 int32_t quantize_packed(const float *values, uint64_t len, uint8_t *packed, float *absmax,
                         cudaStream_t stream);

@@ -172,6 +172,13 @@ __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// Programmatic dependent launch: the pre-pass lets its dependent start early; the dependent
+// blocks here (per thread) until the pre-pass has finished and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t elect_one() {
     uint32_t pred;
     asm volatile(

@@ -1,0 +1,127 @@
+"""Output-column sharding of an NF4 / QLoRA linear across the GPUs of one node.
+
+Each output column depends on one weight row (``W [d_out, d_in]``), its block scales and one row
+of LoRA ``B``; ``x`` and LoRA ``A`` are replicated.  Rank ``r`` of ``g`` owns a contiguous range
+of columns, computes ``y[:, range]`` with the single-GPU kernels, and the ranks exchange their
+slabs with one all-gather (NCCL over NVLink on GPUs; any ``torch.distributed`` backend works,
+which is how the host logic is tested on CPU with gloo).  The reference has no distributed
+runtime; this partition is the one its path admits without touching the numerics: no
+quantization block is split because blocks run along ``d_in``.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ._lib import LAYOUT_OUT_IN
+
+BLOCK_SIZE = 64
+
+
+def column_shards(d_out: int, world: int, granule: int = 1) -> List[Tuple[int, int]]:
+    """Contiguous column ranges ``[start, end)`` for ``world`` ranks, sizes differing by at most
+    one ``granule`` (trailing ranks may be empty when ``d_out < world * granule``)."""
+    if world < 1 or d_out < 0 or granule < 1:
+        raise ValueError("column_shards: world, granule >= 1 and d_out >= 0 required")
+    units = (d_out + granule - 1) // granule
+    out = []
+    for r in range(world):
+        a = min((units * r) // world * granule, d_out)
+        b = min((units * (r + 1)) // world * granule, d_out)
+        out.append((a, b))
+    return out
+
+
+def shard_packed_rows(codes: torch.Tensor, scales: torch.Tensor, d_in: int,
+                      rows: Tuple[int, int]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Slice rows ``[start, end)`` out of a packed ``W [d_out, d_in]`` weight (``d_in % 64 == 0``).
+
+    ``codes`` holds ``d_in / 2`` bytes per row and ``scales`` (f32 absmax or u8 scale codes)
+    ``d_in / 64`` entries per row, so a row range is a contiguous byte range of both."""
+    if d_in % BLOCK_SIZE != 0:
+        raise ValueError("row sharding of a packed weight needs d_in % 64 == 0 "
+                         "(otherwise a quantization block straddles two rows)")
+    a, b = rows
+    return (codes[a * (d_in // 2): b * (d_in // 2)].contiguous(),
+            scales[a * (d_in // BLOCK_SIZE): b * (d_in // BLOCK_SIZE)].contiguous())
+
+
+def gather_columns(y_local: torch.Tensor, shards: Sequence[Tuple[int, int]],
+                   group: Optional[dist.ProcessGroup] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All-gather the ranks' column slabs ``y_local [rows, end - start]`` into ``y [rows, d_out]``.
+
+    Equal slabs go through one ``all_gather_into_tensor`` (``[world, rows, width]``) followed by a
+    permuting copy; unequal slabs are padded to the widest one first."""
+    world = dist.get_world_size(group)
+    if len(shards) != world:
+        raise ValueError("gather_columns: one shard per rank expected")
+    rows = y_local.shape[0]
+    d_out = shards[-1][1]
+    widths = [b - a for a, b in shards]
+    wmax = max(widths)
+    mine = widths[dist.get_rank(group)]
+    if y_local.shape[1] != mine:
+        raise ValueError(f"gather_columns: local slab has {y_local.shape[1]} columns, shard says {mine}")
+    send = y_local.contiguous()
+    if mine != wmax:
+        send = torch.zeros(rows, wmax, dtype=y_local.dtype, device=y_local.device)
+        send[:, :mine] = y_local
+    flat = torch.empty(world * rows, wmax, dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(flat, send, group=group)  # slabs concatenated along dim 0
+    stacked = flat.view(world, rows, wmax)
+    y = out if out is not None else torch.empty(rows, d_out, dtype=y_local.dtype,
+                                                device=y_local.device)
+    if all(w == wmax for w in widths):
+        y.view(rows, world, wmax).copy_(stacked.permute(1, 0, 2))
+    else:
+        for r, (a, b) in enumerate(shards):
+            y[:, a:b] = stacked[r, :, : b - a]
+    return y
+
+
+class ShardedNf4Linear:
+    """One rank's column shard of a QLoRA linear (``W [d_out, d_in]``, blocks along ``d_in``)."""
+
+    def __init__(self, packed, d_in: int, d_out: int, shards: Sequence[Tuple[int, int]], rank: int,
+                 bias: Optional[torch.Tensor] = None, lora_a: Optional[torch.Tensor] = None,
+                 lora_b: Optional[torch.Tensor] = None, lora_scale: float = 0.0,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.packed = packed          # PackedNf4Tensor of the local rows only
+        self.d_in, self.d_out = d_in, d_out
+        self.shards, self.rank, self.group = list(shards), rank, group
+        self.bias, self.lora_a, self.lora_b, self.lora_scale = bias, lora_a, lora_b, lora_scale
+
+    @staticmethod
+    def from_full(packed_full, d_in: int, d_out: int, world: int, rank: int,
+                  bias=None, lora_a=None, lora_b=None, lora_scale: float = 0.0, group=None,
+                  granule: int = 1) -> "ShardedNf4Linear":
+        """Cut rank ``rank``'s rows out of a full packed weight that every rank can see."""
+        from .quantize import PackedNf4Tensor
+
+        shards = column_shards(d_out, world, granule)
+        a, b = shards[rank]
+        dq = packed_full.is_double_quantized()
+        scales = packed_full.scale_codes if dq else packed_full.absmax
+        codes, sc = shard_packed_rows(packed_full.codes, scales, d_in, (a, b))
+        local = PackedNf4Tensor(codes, (b - a) * d_in, None if dq else sc, sc if dq else None,
+                                packed_full.scale_of_scales)
+        return ShardedNf4Linear(local, d_in, d_out, shards, rank,
+                                bias[a:b].contiguous() if bias is not None else None, lora_a,
+                                lora_b[a:b].contiguous() if lora_b is not None else None,
+                                lora_scale, group)
+
+    def forward_local(self, x: torch.Tensor) -> torch.Tensor:
+        from .quantize import linear_forward
+
+        a, b = self.shards[self.rank]
+        return linear_forward(x, self.packed, self.d_in, b - a, LAYOUT_OUT_IN, bias=self.bias,
+                              lora_a=self.lora_a, lora_b=self.lora_b, lora_scale=self.lora_scale)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y_local = self.forward_local(x)
+        lead = y_local.shape[:-1]
+        y = gather_columns(y_local.reshape(-1, y_local.shape[-1]), self.shards, self.group)
+        return y.view(*lead, self.d_out)
