@@ -480,12 +480,12 @@ def aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind):
     return out
 
 
-def prefill_section(torch, lib, _lib, dev):
+def prefill_section(torch, lib, _lib, dev, pn: int = 14336, iters: int = 20):
     """QLoRA prefill GEMM of configuration 3: x bf16 [2048, 4096], W NF4 [14336, 4096], rank 64,
     scale 2.0 (the configuration names none; the decode configuration's value is used)."""
     from unifur_b200.quantize import PackedNf4Tensor
 
-    pm, pk, pn, pr = 2048, 4096, 14336, 64
+    pm, pk, pr = 2048, 4096, 64
     _hbm, tf_peak, peak_kind = measured_peaks()
     g = torch.Generator(device=dev).manual_seed(5)
     w = torch.randn(pn * pk, device=dev, generator=g) * 0.02
@@ -514,12 +514,12 @@ def prefill_section(torch, lib, _lib, dev):
         flush.fill_(i & 1)  # write more than the 126 MB L2 between timed launches
         _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), stream()))
 
-    ms_with_flush = time_loop(torch, run, 20)
-    ms_flush = time_loop(torch, lambda i: flush.fill_(i & 1), 20)
+    ms_with_flush = time_loop(torch, run, iters, warm=3)
+    ms_flush = time_loop(torch, lambda i: flush.fill_(i & 1), iters, warm=3)
     ms = ms_with_flush - ms_flush
     flops = 2.0 * pm * pn * pk + 2.0 * pm * pr * (pk + pn)
     tflops = flops / (ms * 1e-3) / 1e12
-    return {"workload": "QLoRA prefill GEMM: x bf16 [2048, 4096], W NF4 [14336, 4096] block 64, "
+    return {"workload": f"QLoRA prefill GEMM: x bf16 [2048, 4096], W NF4 [{pn}, 4096] block 64, "
                         "LoRA rank 64 fused, f32 accumulate, bf16 out (pre-pass + GEMM kernel)",
             "ms": ms, "TFLOP/s": tflops, "flops": flops,
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": tf_peak, "unit": "TFLOP/s",
@@ -534,9 +534,18 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--prefill-only", type=int, default=0, metavar="N",
+                    help="run only the prefill GEMM section with d_out = N (used under the profiler)")
     ap.add_argument("--device-only", action="store_true",
                     help="time only the device-resident decode region (used under the profiler)")
     args = ap.parse_args()
+    if args.prefill_only:
+        import torch
+        from unifur_b200 import _lib
+        torch.cuda.set_device(0)
+        print(json.dumps(prefill_section(torch, _lib.load(), _lib, torch.device("cuda", 0),
+                                         pn=args.prefill_only, iters=max(args.steps, 1))))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -126,7 +126,7 @@ __device__ __forceinline__ void issue_tile(const DecodeParams &p, uint32_t tile,
 }
 
 template <int NT, bool DQ>
-__global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
+__global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
 decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem);
@@ -148,6 +148,7 @@ decode_kernel(const DecodeParams p) {
 
     const uint32_t bar_full = ptx::smem_addr(bars), bar_done = ptx::smem_addr(bars + kMaxStages);
     const uint32_t bar_red_free = ptx::smem_addr(bars + 2 * kMaxStages);
+    const uint32_t bar_epi_done = ptx::smem_addr(bars + 2 * kMaxStages + 2);
     if (warp == 0) NF4_TS(0);
 
     // Consumers ask for their slice of x before anything else: once the producer's bulk copies
@@ -174,14 +175,41 @@ decode_kernel(const DecodeParams p) {
         }
     }
 
+    // x slice of this warp as f16 B-fragments, converted as soon as it arrives
+    uint32_t xf[NT][kMaxChunksPerWarp][4][2];
+    if (warp < p.consumer_warps) {
+        // x slice of this warp as f16 B-fragments: xf[u][c][j] = {b0, b1}
+        #pragma unroll
+        for (int u = 0; u < NT; ++u) {
+            #pragma unroll
+            for (int c = 0; c < kMaxChunksPerWarp; ++c) {
+                const uint4 q0 = xraw[u][c][0], q1 = xraw[u][c][1];
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    #pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t pair = w[2 * j + h];  // two bf16: k, k+1
+                        xf[u][c][j][h] = pack_f16x2(bf16_bits_to_float(pair & 0xffffu),
+                                                    bf16_bits_to_float(pair >> 16));
+                    }
+                }
+            }
+        }
+
+        if (warp == 0) NF4_TS(7);
+        asm volatile("bar.arrive 3, %0;" ::"r"((p.consumer_warps + 1) * 32) : "memory");
+    }
+
     if (warp == p.consumer_warps) {
-        // =================== producer + epilogue warp ===================
+        // ========================= producer warp =========================
         // The barriers are this warp's to set up, so the first loads leave before the other
         // warps have finished building the lookup table.
         if (lane == 0) {
             for (uint32_t s = 0; s < S; ++s) {
                 ptx::mbar_init(bar_full + 8 * s, 1);
                 ptx::mbar_init(bar_done + 8 * s, p.consumer_warps);
+                ptx::mbar_init(bar_epi_done + 8 * s, 1);
             }
             ptx::mbar_init(bar_red_free, 1);
             ptx::mbar_init(bar_red_free + 8, 1);
@@ -189,10 +217,14 @@ decode_kernel(const DecodeParams p) {
             ptx::fence_proxy_async();
         }
         __syncwarp();
-        const uint32_t first = ntiles < S ? ntiles : S;
-        for (uint32_t tile = 0; tile < first; ++tile)
-            issue_tile<DQ>(p, tile, n0, n1, S, stage_base, bar_full, lane);
-    } else {
+        // hold the bulk copies back until the consumers HAVE their x: requests issued behind
+        // ~150 KB of queued weight traffic per SM were seen to take ~4 us to come back
+        asm volatile("bar.sync 3, %0;" ::"r"((p.consumer_warps + 1) * 32) : "memory");
+        // Only the first tile is requested now.  Asking for everything at once makes every tile,
+        // the first included, arrive together after the whole ~150 KB burst (~4 us); with one to
+        // two tiles in flight the first is there after ~1 us and the rest keep ahead of the math.
+        issue_tile<DQ>(p, 0, n0, n1, S, stage_base, bar_full, lane);
+    } else if (warp < p.consumer_warps) {
         // ---- consumers build the lookup table while the first tiles are in flight ----
         const uint32_t nthreads = p.consumer_warps * 32;
         for (uint32_t i = tid; i < 256 * 32; i += nthreads) {
@@ -205,6 +237,23 @@ decode_kernel(const DecodeParams p) {
     if (warp == 0) NF4_TS(1);
 
     if (warp == p.consumer_warps) {
+        // Producer: keep `ahead + 1` tiles in flight, in order.  A tile is requested once the
+        // tile `ahead + 1` before it has landed and its ring slot's previous tile is finished.
+        const uint32_t ahead = S >= 4 ? 3u : S - 1u;
+        bool ok = true;
+        for (uint32_t n = 1; n < ntiles && ok; ++n) {
+            if (n > ahead) {
+                const uint32_t w = n - ahead - 1;
+                ok = ptx::mbar_wait_bounded(bar_full + 8 * (w % S), (w / S) & 1u);
+            }
+            if (ok && n >= S) ok = ptx::mbar_wait_bounded(bar_epi_done + 8 * (n % S), ((n / S) - 1) & 1u);
+            if (!ok) break;
+            ptx::fence_proxy_async();
+            issue_tile<DQ>(p, n, n0, n1, S, stage_base, bar_full, lane);
+        }
+        if (!ok && lane == 0) atomicExch(&g_decode_error, 3);
+    } else if (warp == p.consumer_warps + 1) {
+        // ========================= epilogue warp =========================
         // T = x A^T comes from the pre-pass, which may still be running: wait for it here,
         // after this kernel's own loads have long been issued
         if (p.rank) {
@@ -246,10 +295,9 @@ decode_kernel(const DecodeParams p) {
             }
             __syncwarp();
             if (tile < 8) NF4_TS(6 + 3 * tile);
-            if (lane == 0) ptx::mbar_arrive(bar_red_free + 8 * (tile & 1u));
-            if (tile + S < ntiles) {
-                ptx::fence_proxy_async();
-                issue_tile<DQ>(p, tile + S, n0, n1, S, stage_base, bar_full, lane);
+            if (lane == 0) {
+                ptx::mbar_arrive(bar_red_free + 8 * (tile & 1u));
+                ptx::mbar_arrive(bar_epi_done + 8 * s);
             }
         }
         NF4_TS(3);
@@ -257,26 +305,6 @@ decode_kernel(const DecodeParams p) {
     } else if (warp < p.consumer_warps) {
         // ========================= consumer warps =========================
         const float sos = DQ ? __ldg(p.scale_of_scales) : 0.0f;
-
-        // x slice of this warp as f16 B-fragments: xf[u][c][j] = {b0, b1}
-        uint32_t xf[NT][kMaxChunksPerWarp][4][2];
-        #pragma unroll
-        for (int u = 0; u < NT; ++u) {
-            #pragma unroll
-            for (int c = 0; c < kMaxChunksPerWarp; ++c) {
-                const uint4 q0 = xraw[u][c][0], q1 = xraw[u][c][1];
-                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t pair = w[2 * j + h];  // two bf16: k, k+1
-                        xf[u][c][j][h] = pack_f16x2(bf16_bits_to_float(pair & 0xffffu),
-                                                    bf16_bits_to_float(pair >> 16));
-                    }
-                }
-            }
-        }
 
         if (warp == 0) NF4_TS(2);
         const uint32_t *lut_lane = lut + lane;
@@ -477,7 +505,7 @@ int32_t launch(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaSt
         configured = true;
     }
     count_launch();
-    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3((p.consumer_warps + 1) * 32),
+    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3((p.consumer_warps + 2) * 32),
                                    smem_bytes, stream, p.rank != 0 && pdl_enabled(), p);
 }
 
