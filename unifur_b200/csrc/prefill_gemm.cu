@@ -36,25 +36,34 @@ namespace nf4 {
 
 __device__ int g_prefill_error = 0;  // set when a bounded wait gives up
 
+#ifdef NF4_PREFILL_TIMING
+// Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
+__device__ long long g_prefill_ts[128];
+#define NF4_PTS(i) do { if (blockIdx.x == 0) g_prefill_ts[(i)] = clock64(); } while (0)
+#else
+#define NF4_PTS(i) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int BM = 128;        // weight rows per tile (MMA M, TMEM lanes)
 constexpr int BN = 256;        // activation rows per tile (MMA N, accumulator columns)
 constexpr int BK = 64;         // k per stage = one quantization block = one 128B swizzle row
-constexpr int kXStages = 5;    // shared-memory ring for the B operand
-constexpr int kAStages = 4;    // TMEM ring for the A operand
-constexpr int kAStageCols = BK / 2;  // 32 columns: two f16 per 32-bit cell
-constexpr int kAccCols = BN;
+constexpr int kWStages = 3;    // shared-memory ring of dequantised weight tiles
+constexpr int kMaxXStages = 5; // shared-memory ring of activation tiles (5 with bf16 out, 4 with f32)
+constexpr int kAccCols = BN;   // one accumulator; two of them fill the 512 TMEM columns
 constexpr int kTmemCols = 512;
-constexpr int kXStageBytes = BN * BK * 2;  // 32 KB
+constexpr int kXTileBytes = BN * BK * 2;   // 32 KB: activations, written by TMA
+constexpr int kWTileBytes = BM * BK * 2;   // 16 KB: dequantised weights, written by the expanders
+
 constexpr int kEpiRows = 32;               // activation rows per epilogue chunk
 constexpr int kThreads = 14 * 32;
 constexpr uint32_t kSpin = 1u << 22;
 
 // barrier slots
-constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kXStages, kBarAFull = kBarXEmpty + kXStages,
-              kBarAEmpty = kBarAFull + kAStages, kBarAccFull = kBarAEmpty + kAStages,
-              kBarAccEmpty = kBarAccFull + 1, kNumBars = kBarAccEmpty + 1;
+constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kMaxXStages, kBarWFull = kBarXEmpty + kMaxXStages,
+              kBarWEmpty = kBarWFull + kWStages, kBarAccFull = kBarWEmpty + kWStages,
+              kBarAccEmpty = kBarAccFull + 2, kNumBars = kBarAccEmpty + 2;
 
 struct PrefillParams {
     const uint8_t *codes;
@@ -194,8 +203,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // 1024-byte alignment for the swizzled operand tiles
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *x_ring = smem;                                   // kXStages * 32 KB
-    uint8_t *epi = smem + kXStages * kXStageBytes;            // 2 staging buffers
+    constexpr int kXStages = YF32 ? 4 : 5;
+    uint8_t *x_ring = smem;                                   // kXStages activation tiles
+    uint8_t *w_ring = smem + kXStages * kXTileBytes;          // kWStages weight tiles
+    uint8_t *epi = w_ring + kWStages * kWTileBytes;           // 2 staging buffers
     constexpr int kEpiBufBytes = kEpiRows * BM * (YF32 ? 4 : 2);
     uint64_t *bars = reinterpret_cast<uint64_t *>(epi + 2 * kEpiBufBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
@@ -215,12 +226,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ptx::mbar_init(bar(kBarXFull + s), 1);
             ptx::mbar_init(bar(kBarXEmpty + s), 1);
         }
-        for (int s = 0; s < kAStages; ++s) {
-            ptx::mbar_init(bar(kBarAFull + s), 4);
-            ptx::mbar_init(bar(kBarAEmpty + s), 1);
+        for (int s = 0; s < kWStages; ++s) {
+            ptx::mbar_init(bar(kBarWFull + s), 4);  // the four warps writing the tile
+            ptx::mbar_init(bar(kBarWEmpty + s), 1);
         }
-        ptx::mbar_init(bar(kBarAccFull), 1);
-        ptx::mbar_init(bar(kBarAccEmpty), 4);
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(bar(kBarAccFull + b), 1);
+            ptx::mbar_init(bar(kBarAccEmpty + b), 4);
+        }
         ptx::fence_mbar_init();
         ptx::fence_proxy_async();
         ptx::prefetch_tmap(&tmap_x);
@@ -234,9 +247,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_acc = tmem_base;                 // columns [0, 256)
-    const uint32_t tmem_a = tmem_base + kAccCols;        // kAStages x 32 columns
+    const uint32_t tmem_base = *tmem_slot;  // two accumulators: columns [0,256) and [256,512)
 
     bool ok = true;
 
@@ -253,8 +264,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                         ok = false;
                         break;
                     }
-                    ptx::mbar_arrive_expect_tx(bar(kBarXFull + s), kXStageBytes);
-                    const uint32_t dst = ptx::smem_addr(x_ring + s * kXStageBytes);
+                    if (cnt >= 20 && cnt < 28) NF4_PTS(cnt - 20);
+                    ptx::mbar_arrive_expect_tx(bar(kBarXFull + s), kXTileBytes);
+                    const uint32_t dst = ptx::smem_addr(x_ring + s * kXTileBytes);
                     if (ks < k_stages)
                         ptx::tma_load_2d(dst, &tmap_x, (int32_t)(ks * BK), (int32_t)m0,
                                          bar(kBarXFull + s));
@@ -270,41 +282,52 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         if (lane == 0) {
             constexpr uint32_t idesc_main = make_idesc(0, 0, BM, BN);  // f16 x f16
             constexpr uint32_t idesc_lora = make_idesc(1, 1, BM, BN);  // bf16 x bf16
+            const uint32_t x_addr = ptx::smem_addr(x_ring), w_addr = ptx::smem_addr(w_ring);
             uint32_t cnt = 0;
             for (uint32_t i = 0; i < my_tiles && ok; ++i) {
-                // the epilogue must have drained the previous tile's accumulator
-                if (!ptx::mbar_wait_bounded(bar(kBarAccEmpty), (i & 1u) ^ 1u, kSpin)) {
+                const uint32_t buf = i & 1u, use = i >> 1;
+                // the epilogue must have drained this accumulator's previous tile
+                if (!ptx::mbar_wait_bounded(bar(kBarAccEmpty + buf), (use & 1u) ^ 1u, kSpin)) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
+                const uint32_t acc = tmem_base + buf * kAccCols;
                 for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
                     const uint32_t sx = cnt % kXStages, phx = (cnt / kXStages) & 1u;
-                    const uint32_t sa = cnt % kAStages, pha = (cnt / kAStages) & 1u;
-                    if (!ptx::mbar_wait_bounded(bar(kBarXFull + sx), phx, kSpin) ||
-                        !ptx::mbar_wait_bounded(bar(kBarAFull + sa), pha, kSpin)) {
+                    const uint32_t sw = cnt % kWStages, phw = (cnt / kWStages) & 1u;
+                    if (cnt >= 20 && cnt < 28) NF4_PTS(16 + 4 * (cnt - 20));
+                    if (!ptx::mbar_wait_bounded(bar(kBarXFull + sx), phx, kSpin)) {
                         ok = false;
                         break;
                     }
+                    if (cnt >= 20 && cnt < 28) NF4_PTS(17 + 4 * (cnt - 20));
+                    if (!ptx::mbar_wait_bounded(bar(kBarWFull + sw), phw, kSpin)) {
+                        ok = false;
+                        break;
+                    }
+                    if (cnt >= 20 && cnt < 28) NF4_PTS(18 + 4 * (cnt - 20));
                     ptx::tc_fence_after();
-                    const uint64_t bdesc =
-                        make_kmajor_sw128_desc(ptx::smem_addr(x_ring + sx * kXStageBytes));
-                    const bool lora = ks >= k_stages;
-                    uint32_t nk16 = BK / 16;
-                    if (lora) {
+                    const uint64_t bdesc = make_kmajor_sw128_desc(x_addr + sx * kXTileBytes);
+                    const uint64_t adesc = make_kmajor_sw128_desc(w_addr + sw * kWTileBytes);
+                    if (ks < k_stages) {
+                        // +32 bytes of K inside the swizzled row = +2 in the encoded address
+                        ptx::mma_ss_f16(acc, adesc, bdesc, idesc_main, ks != 0 ? 1u : 0u);
+                        ptx::mma_ss_f16(acc, adesc + 2, bdesc + 2, idesc_main, 1u);
+                        ptx::mma_ss_f16(acc, adesc + 4, bdesc + 4, idesc_main, 1u);
+                        ptx::mma_ss_f16(acc, adesc + 6, bdesc + 6, idesc_main, 1u);
+                    } else {
                         const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
                         const uint32_t left = p.rank - chunk * 64;
-                        nk16 = ((left < 64 ? left : 64) + 15) / 16;
-                    }
-                    for (uint32_t j = 0; j < nk16; ++j) {
-                        // +32 bytes of K inside the swizzled row = +2 in the encoded address
-                        ptx::mma_ts_f16(tmem_acc, tmem_a + sa * kAStageCols + j * 8, bdesc + 2 * j,
-                                        lora ? idesc_lora : idesc_main, (ks | j) != 0 ? 1u : 0u);
+                        const uint32_t nk16 = ((left < 64 ? left : 64) + 15) / 16;
+                        for (uint32_t j = 0; j < nk16; ++j)
+                            ptx::mma_ss_f16(acc, adesc + 2 * j, bdesc + 2 * j, idesc_lora, 1u);
                     }
                     ptx::tc_commit(bar(kBarXEmpty + sx));
-                    ptx::tc_commit(bar(kBarAEmpty + sa));
+                    ptx::tc_commit(bar(kBarWEmpty + sw));
+                    if (cnt >= 20 && cnt < 28) NF4_PTS(19 + 4 * (cnt - 20));
                 }
-                if (ok) ptx::tc_commit(bar(kBarAccFull));
+                if (ok) ptx::tc_commit(bar(kBarAccFull + buf));
             }
             if (!ok) atomicExch(&g_prefill_error, 2);
         }
@@ -317,23 +340,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             const uint32_t tile = blockIdx.x + i * gridDim.x;
             const uint32_t n0 = (tile / p.m_tiles) * BM, m0 = (tile % p.m_tiles) * BN;
             const uint32_t n = n0 + row_in_tile;
+            const uint32_t buf = i & 1u, use = i >> 1;
             const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
-            ok = ptx::mbar_wait_bounded(bar(kBarAccFull), i & 1u, kSpin);
+            ok = ptx::mbar_wait_bounded(bar(kBarAccFull + buf), use & 1u, kSpin);
             if (!ok) break;
             ptx::tc_fence_after();
+            const uint32_t acc = tmem_base + buf * kAccCols;
             for (uint32_t c = 0; c < BN / kEpiRows; ++c) {
-                uint8_t *buf = epi + (c & 1u) * kEpiBufBytes;
+                uint8_t *ebuf = epi + (c & 1u) * kEpiBufBytes;
                 // the TMA store that last read this buffer must be done with it
                 if (epi_leader) ptx::tma_store_wait_read<1>();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 uint32_t v[32];
-                tmem_ld32(tmem_acc + ((q * 32) << 16) + c * kEpiRows, v);
+                tmem_ld32(acc + ((q * 32) << 16) + c * kEpiRows, v);
                 ptx::tmem_wait_ld();
                 if (c == BN / kEpiRows - 1) {
                     // accumulator fully read: hand it back to the MMA warp
                     ptx::tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty));
+                    if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty + buf));
                 }
                 // staging layout: [kEpiRows activation rows][BM weight rows]
                 #pragma unroll
@@ -342,15 +367,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     const float rs = m < p.M ? __ldg(p.row_scale + m) : 1.0f;
                     const float f = fmaf(__uint_as_float(v[r]), rs, bias);
                     if (YF32)
-                        reinterpret_cast<float *>(buf)[r * BM + row_in_tile] = f;
+                        reinterpret_cast<float *>(ebuf)[r * BM + row_in_tile] = f;
                     else
-                        reinterpret_cast<__nv_bfloat16 *>(buf)[r * BM + row_in_tile] =
+                        reinterpret_cast<__nv_bfloat16 *>(ebuf)[r * BM + row_in_tile] =
                             __float2bfloat16_rn(f);
                 }
                 ptx::fence_proxy_async();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (epi_leader) {
-                    ptx::tma_store_2d(&tmap_y, ptx::smem_addr(buf), (int32_t)n0,
+                    ptx::tma_store_2d(&tmap_y, ptx::smem_addr(ebuf), (int32_t)n0,
                                       (int32_t)(m0 + c * kEpiRows));
                     ptx::tma_store_commit();
                 }
@@ -360,13 +385,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         if (!ok && lane == 0) atomicExch(&g_prefill_error, 3);
     } else {
         // ============================ dequantisers ============================
+        // Two groups of 128 threads take alternate stages.  A thread owns one weight row of the
+        // tile: 32 packed bytes + one scale in, 64 f16 values out, written as eight 16-byte
+        // chunks at the 128B-swizzled positions the MMA's shared-memory descriptor expects.
         const uint32_t group = (warp - 6) >> 2;           // 0 or 1: takes stages of that parity
-        const uint32_t q = warp & 3u;                      // TMEM lane quarter
-        const uint32_t row_in_tile = q * 32 + lane;
+        const uint32_t row_in_tile = ((warp - 6) & 3u) * 32 + lane;
         const LevelTables tables = make_level_tables();
         const float sos = p.scale_codes ? __ldg(p.scale_of_scales) : 0.0f;
         const uint32_t blocks_per_row = p.K / 64;
         const uint64_t total = (uint64_t)my_tiles * stages_per_tile;
+        const uint32_t row_off = (row_in_tile >> 3) * 1024 + (row_in_tile & 7u) * 128;
+        const uint32_t swz = row_in_tile & 7u;
 
         auto fetch = [&](uint64_t cnt, RowStage &rs) {
             rs.c0 = rs.c1 = make_uint4(0, 0, 0, 0);
@@ -385,7 +414,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         };
         auto emit = [&](uint64_t cnt, const RowStage &rs) -> bool {
             const uint32_t i = (uint32_t)(cnt / stages_per_tile), ks = (uint32_t)(cnt % stages_per_tile);
-            const uint32_t sa = (uint32_t)(cnt % kAStages), ph = (uint32_t)((cnt / kAStages) & 1u);
+            const uint32_t s = (uint32_t)(cnt % kWStages), ph = (uint32_t)((cnt / kWStages) & 1u);
             uint32_t out[32];
             if (ks < k_stages) {
                 expand_row(tables, rs.c0, rs.c1, rs.scale, out);
@@ -407,13 +436,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     out[e] = lo | (hi << 16);
                 }
             }
-            if (!ptx::mbar_wait_bounded(bar(kBarAEmpty + sa), ph ^ 1u, kSpin)) return false;
-            ptx::tc_fence_after();
-            tmem_st32(tmem_a + ((q * 32) << 16) + sa * kAStageCols, out);
-            ptx::tmem_wait_st();
-            ptx::tc_fence_before();
+            if ((warp == 6 || warp == 10) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(64 + 4 * (cnt - 20));
+            if (!ptx::mbar_wait_bounded(bar(kBarWEmpty + s), ph ^ 1u, kSpin)) return false;
+            if ((warp == 6 || warp == 10) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(65 + 4 * (cnt - 20));
+            uint8_t *wrow = w_ring + s * kWTileBytes + row_off;
+            #pragma unroll
+            for (uint32_t c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4 *>(wrow + ((c ^ swz) << 4)) =
+                    make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+            ptx::fence_proxy_async();  // the tensor core reads this tile through the async proxy
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar(kBarAFull + sa));
+            if (lane == 0) ptx::mbar_arrive(bar(kBarWFull + s));
+            if ((warp == 6 || warp == 10) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(66 + 4 * (cnt - 20));
             return true;
         };
 
@@ -686,7 +720,8 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
 
     const uint32_t total_tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = total_tiles < (uint32_t)kNumSMs ? total_tiles : (uint32_t)kNumSMs;
-    const size_t smem = 1024 + kXStages * kXStageBytes + 2 * kEpiRows * BM * (a.y_f32 ? 4 : 2) +
+    const size_t smem = 1024 + (a.y_f32 ? 4 : 5) * kXTileBytes + kWStages * kWTileBytes +
+                        2 * kEpiRows * BM * (a.y_f32 ? 4 : 2) +
                         kNumBars * 8 + 64;
     if (a.y_f32) {
         static bool configured = false;
@@ -708,6 +743,12 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     count_launch();
     return check_cuda(cudaGetLastError(), "prefill_kernel launch");
 }
+
+#ifdef NF4_PREFILL_TIMING
+extern "C" __attribute__((visibility("default"))) int nf4_debug_prefill_timestamps(long long *out128) {
+    return (int)cudaMemcpyFromSymbol(out128, g_prefill_ts, sizeof(long long) * 128);
+}
+#endif
 
 int32_t prefill_error_flag(int *host_value) {
     return check_cuda(cudaMemcpyFromSymbol(host_value, g_prefill_error, sizeof(int)),
