@@ -220,7 +220,18 @@ def run_reference(args) -> None:
 
 
 # ----------------------------------------------------------------------------------- own arm
+def log(msg: str) -> None:
+    """Progress line on stderr (rank-tagged) so a stuck multi-GPU run shows where it stopped."""
+    sys.stderr.write(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - _T0:.1f}s] {msg}\n")
+    sys.stderr.flush()
+
+
+_T0 = time.perf_counter()
+
+
 def run_own(args) -> None:
+    import datetime
+
     import torch
     import torch.distributed as dist
 
@@ -235,7 +246,9 @@ def run_own(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        log("init_process_group(nccl)")
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+        log("process group up")
     lib = _lib.load()
     hbm_peak, _tf_peak, peak_kind = measured_peaks()
 
@@ -275,6 +288,7 @@ def run_own(args) -> None:
         return a
 
     call_args = {(c, m): make_args(c, m) for c in range(N_COPIES) for m in MS}
+    log("weights quantized, arguments built")
 
     def step(i: int) -> None:
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -296,6 +310,7 @@ def run_own(args) -> None:
         for i in range(max(args.warmup, 3)):
             step(i)
     barrier()
+    log("warm-up done")
     launches0 = _lib.launch_count()
     launch_mode = "cuda-graph"
     graph = None
@@ -309,6 +324,15 @@ def run_own(args) -> None:
         launch_mode = f"eager ({type(e).__name__})"
         torch.cuda.synchronize()
     gpu_launches = _lib.launch_count() - launches0
+    if world > 1:
+        # every rank must take the same path: one rank replaying a graph while another launches
+        # eagerly would leave the collectives mismatched
+        flag = torch.tensor([1 if graph is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0 and graph is not None:
+            graph = None
+            launch_mode = "eager (capture failed on another rank)"
+    log(f"launch mode: {launch_mode}")
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if graph is not None:
@@ -329,6 +353,7 @@ def run_own(args) -> None:
             e1.record()
         gpu_launches = _lib.launch_count() - launches0
     barrier()
+    log("timed region done")
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -393,6 +418,7 @@ def run_own(args) -> None:
         }
         for h in handles:
             lib.nf4_weight_free(h)
+        log("end-to-end region done")
 
     # ---- other kernels of the path (not part of `value`) -----------------------------------
     if rank == 0 and not args.device_only:
@@ -435,9 +461,16 @@ def run_own(args) -> None:
         }
         line.update(extras)
         print(json.dumps(line))
+        sys.stdout.flush()
     if world > 1:
+        # Leave without tearing NCCL down: destroying a process group whose collectives were
+        # captured in a CUDA graph was seen to block for minutes.  Every rank has finished its
+        # work once the barrier returns.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        log("done")
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def time_loop(torch, fn, iters: int, warm: int = 5) -> float:
