@@ -423,6 +423,10 @@ def run_own(args) -> None:
     # ---- other kernels of the path (not part of `value`) -----------------------------------
     if rank == 0 and not args.device_only:
         extras = aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind)
+        if world == 1:  # the other named configurations, measured on the one GPU
+            log("side sections: block, sweep")
+            extras["qwen2_7b_block"] = block_section(torch, lib, _lib, dev)
+            extras["quantize_sweep"] = sweep_section(torch, lib, _lib, dev)
 
     # ---- CPU baseline beside it (rank 0, one GPU only) -----------------------------------------
     if rank == 0 and world == 1 and not args.device_only:
@@ -561,6 +565,104 @@ def prefill_section(torch, lib, _lib, dev, pn: int = 14336, iters: int = 20):
             "cache": "160 MB flush write between launches (its time subtracted)"}
 
 
+def build_linear(torch, lib, _lib, dev, m: int, k: int, n: int, r: int, seed: int):
+    """One NF4 linear with an adapter, resident on the device: argument block + what it points to."""
+    from unifur_b200.quantize import PackedNf4Tensor
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w = torch.randn(n * k, device=dev, generator=g) * 0.02
+    wq = PackedNf4Tensor.quantize(w)
+    del w
+    la = (torch.randn(r, k, device=dev, generator=g) * 0.01).bfloat16()
+    lb = (torch.randn(n, r, device=dev, generator=g) * 0.01).bfloat16()
+    x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    y = torch.zeros(m, n, device=dev, dtype=torch.bfloat16)
+    ws = torch.zeros(max(int(lib.nf4_linear_workspace_bytes(m, k, n, r)), 256), dtype=torch.uint8,
+                     device=dev)
+    a = _lib.LinearArgs()
+    a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+    a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16
+    a.rows, a.d_in, a.d_out = m, k, n
+    a.x, a.packed, a.absmax = x.data_ptr(), wq.codes.data_ptr(), wq.absmax.data_ptr()
+    a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb.data_ptr(), r, SCALE
+    a.y, a.ldy = y.data_ptr(), n
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    return a, (wq, la, lb, x, y, ws)
+
+
+QWEN2_7B_BLOCK = (("q", 3584, 3584), ("k", 3584, 512), ("v", 3584, 512), ("o", 3584, 3584),
+                  ("gate", 3584, 18944), ("up", 3584, 18944), ("down", 18944, 3584))
+
+
+def block_section(torch, lib, _lib, dev, iters: int = 20):
+    """Configuration 5 on one GPU: the seven NF4 projections of a Qwen2-7B-shaped decoder block,
+    rank-16 adapters, run back to back (decode batch 8, then prefill of 4096 tokens).  The glue
+    between projections is not on the measured path; each projection reads its own synthetic
+    input of the right shape."""
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    ms_flush = time_loop(torch, lambda i: flush.fill_(i & 1), iters, warm=3)
+    out = {}
+    for label, m in (("decode_batch_8", 8), ("prefill_4096", 4096)):
+        lins = [build_linear(torch, lib, _lib, dev, m, k, n, 16, 200 + i)
+                for i, (_nm, k, n) in enumerate(QWEN2_7B_BLOCK)]
+
+        def run(i):
+            flush.fill_(i & 1)
+            for a, _keep in lins:
+                _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), stream()))
+
+        ms = time_loop(torch, run, iters, warm=3) - ms_flush
+        elems = sum(k * n for _nm, k, n in QWEN2_7B_BLOCK)
+        if m == 8:
+            by = sum(k * n // 2 + k * n // 64 * 4 + 16 * (k + n) * 2 + m * (k + n) * 2
+                     for _nm, k, n in QWEN2_7B_BLOCK)
+            gbs = by / (ms * 1e-3) / 1e9
+            out[label] = {"us": ms * 1e3, "GB/s": gbs, "algorithmic_bytes": by,
+                          "frac": gbs / hbm_peak, "peak_kind": f"of {peak_kind}"}
+        else:
+            fl = sum(2.0 * m * k * n + 2.0 * m * 16 * (k + n) for _nm, k, n in QWEN2_7B_BLOCK)
+            tf = fl / (ms * 1e-3) / 1e12
+            out[label] = {"ms": ms, "TFLOP/s": tf, "flops": fl, "frac": tf / tf_peak,
+                          "peak_kind": f"of {peak_kind} (burst)"}
+        del lins
+    out["workload"] = ("Qwen2-7B-shaped block, 7 NF4 linears (233,046,016 weights), block 64, rank 16; "
+                       "160 MB flush write before each pass (its time subtracted)")
+    return out
+
+
+def sweep_section(torch, lib, _lib, dev):
+    """Configuration 4: 32 f32 matrices (8 each of 4096x4096, 4096x14336, 14336x4096, 1024x4096),
+    Student-t(4) * 0.02, quantized to packed NF4 with one call per matrix."""
+    hbm_peak, _tf, peak_kind = measured_peaks()
+    shapes = [(4096, 4096), (4096, 14336), (14336, 4096), (1024, 4096)]
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    g = torch.Generator(device=dev).manual_seed(100)
+    mats = []
+    for rep in range(8):
+        for r, c in shapes:
+            n = r * c
+            z = torch.randn(n, device=dev, generator=g)
+            chi = torch.randn(4, n, device=dev, generator=g).square_().sum(0).div_(4.0).sqrt_()
+            mats.append((z.div_(chi).mul_(0.02), torch.empty(n // 2, dtype=torch.uint8, device=dev),
+                         torch.empty(n // 64, dtype=torch.float32, device=dev)))
+            del chi
+
+    def run(_i):
+        for v, c, am in mats:
+            _lib.check(lib.nf4_quantize_dev(p(v), v.numel(), p(c), p(am), stream()))
+
+    ms = time_loop(torch, run, 5, warm=2)
+    elems = sum(v.numel() for v, _c, _a in mats)
+    by = elems * 4.5625
+    gbs = by / (ms * 1e-3) / 1e9
+    return {"workload": "32 f32 matrices, Student-t(4) * 0.02, one quantize call per matrix",
+            "elements": elems, "ms": ms, "GB/s": gbs, "algorithmic_bytes": int(by),
+            "frac": gbs / hbm_peak, "peak_kind": f"of {peak_kind}"}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -569,6 +671,10 @@ def main() -> None:
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--prefill-only", type=int, default=0, metavar="N",
                     help="run only the prefill GEMM section with d_out = N (used under the profiler)")
+    ap.add_argument("--sections", default="",
+                    help="comma list of side sections to run alone on one GPU: block (the seven "
+                         "projections of a Qwen2-7B-shaped block), sweep (32-matrix quantization "
+                         "sweep), aux (quantize / dequantize / prefill)")
     ap.add_argument("--device-only", action="store_true",
                     help="time only the device-resident decode region (used under the profiler)")
     args = ap.parse_args()
@@ -578,6 +684,24 @@ def main() -> None:
         torch.cuda.set_device(0)
         print(json.dumps(prefill_section(torch, _lib.load(), _lib, torch.device("cuda", 0),
                                          pn=args.prefill_only, iters=max(args.steps, 1))))
+        return
+    if args.sections:
+        import torch
+        from unifur_b200 import _lib
+        torch.cuda.set_device(0)
+        dev, lib = torch.device("cuda", 0), _lib.load()
+        res = {}
+        for name in args.sections.split(","):
+            if name == "block":
+                res["qwen2_7b_block"] = block_section(torch, lib, _lib, dev)
+            elif name == "sweep":
+                res["quantize_sweep"] = sweep_section(torch, lib, _lib, dev)
+            elif name == "aux":
+                hbm, _tf, kind = measured_peaks()
+                res.update(aux_sections(torch, lib, _lib, dev, hbm, kind))
+            else:
+                raise SystemExit(f"unknown section {name!r} (block, sweep, aux)")
+        print(json.dumps(res))
         return
     if args.impl == "reference":
         run_reference(args)

@@ -72,6 +72,13 @@ NF4_API uint64_t nf4_kernel_launch_count(void);
  * never exceeds 1) and returns how many disagree. */
 NF4_API int32_t nf4_selfcheck_code_selection(uint64_t first_bits, uint64_t count, uint64_t *mismatches);
 
+/* Diagnostic: for one block scale `absmax`, runs the quantizer's division-free fast path and
+ * the exact reference arithmetic (IEEE x / absmax, then the sixteen-way scan) on `count`
+ * consecutive f32 bit patterns of x starting at `first_bits` (only |x| <= absmax and NaNs are
+ * compared: nothing else can occur in a block with that absmax) and returns how many disagree. */
+NF4_API int32_t nf4_selfcheck_quantize_fast_path(uint64_t first_bits, uint64_t count, float absmax,
+                                         uint64_t *mismatches);
+
 /* The sixteen NF4 levels, src/quantize.rs:49-66. */
 NF4_API void nf4_levels(float out16[16]);
 

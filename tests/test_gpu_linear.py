@@ -246,6 +246,37 @@ def test_python_mirror_reads_like_the_reference(oracle):
     assert p1.resident_bytes() == 64 * 8 // 2 + 8 * 4
 
 
+QWEN2_7B_BLOCK = [  # name, d_in, d_out  (configuration 5: all seven projections NF4, rank 16)
+    ("q", 3584, 3584), ("k", 3584, 512), ("v", 3584, 512), ("o", 3584, 3584),
+    ("gate", 3584, 18944), ("up", 3584, 18944), ("down", 18944, 3584),
+]
+
+
+@pytest.mark.parametrize("dq", [False, True])
+def test_qwen2_7b_block_decode_batch_8(oracle, dq):
+    # The seven projections at full size, decode batch 8, chained the way a decoder block feeds
+    # them.  The reference has no Qwen2 block, so the glue between the projections is a cheap
+    # stand-in (attention replaced by v broadcast over the query groups, SiLU(gate) * up for the
+    # MLP); every projection is checked on its own input against the oracle.
+    M, r, scale = 8, 16, 2.0
+    rng = np.random.default_rng(200)
+    x = bf16_round(oracle, rng.standard_normal((M, 3584)))
+    outs = {}
+    for i, (name, K, N) in enumerate(QWEN2_7B_BLOCK):
+        if name in ("q", "k", "v", "gate", "up"):
+            inp = x
+        elif name == "o":
+            inp = bf16_round(oracle, np.tile(outs["v"], (1, 7)))
+        else:
+            g = outs["gate"].astype(np.float64)
+            inp = bf16_round(oracle, g / (1.0 + np.exp(-g)) * outs["up"])
+        c = make_case(oracle, 200 + i, M, K, N, r, dq=dq)
+        c["x"] = inp
+        outs[name], _ = check_out_in(oracle, c, M, K, N, scale)
+        if name == "o":
+            x = bf16_round(oracle, x + outs["o"])  # residual; feeds gate/up
+
+
 # ------------------------------------------------------------------ prefill (tcgen05) path
 @pytest.mark.parametrize("M,K,N,r,dq,bias", [
     (256, 256, 128, 0, False, False),     # one tile, four k-stages

@@ -129,6 +129,15 @@ def test_code_selection_matches_the_literal_scan_for_all_f32():
     assert bad.value == 0
 
 
+@pytest.mark.parametrize("absmax", [1.0, 0.75, 3.1415927, 0.0517, 1e-3, 6.1e-5, 1e-38, 3e38,
+                                    1.0000001, 0.99999994, 1e-31, 1e31, 0.0, float("inf")])
+def test_division_free_fast_path_equals_exact_division_for_all_x(absmax):
+    # every f32 x with |x| <= absmax (2^32 bit patterns walked), per block scale
+    bad = ctypes.c_uint64(99)
+    _lib.check(lib().nf4_selfcheck_quantize_fast_path(0, 1 << 32, absmax, ctypes.byref(bad)))
+    assert bad.value == 0
+
+
 def test_quantization_is_deterministic(oracle):
     # qwennet.rs:3041-3047: resume re-quantizes and expects identical bytes
     v = (np.random.default_rng(9).standard_normal(1 << 20) * 0.02).astype(np.float32)

@@ -62,6 +62,7 @@ SIGNATURES = {
     "nf4_last_error": (C.c_char_p, []),
     "nf4_kernel_launch_count": (_u64, []),
     "nf4_selfcheck_code_selection": (_i32, [_u64, _u64, C.POINTER(_u64)]),
+    "nf4_selfcheck_quantize_fast_path": (_i32, [_u64, _u64, _f32, C.POINTER(_u64)]),
     "nf4_levels": (None, [_vp]),
     "nf4_estimated_resident_bytes": (_u64, [_u64, _i32]),
     "nf4_num_blocks": (_u64, [_u64]),

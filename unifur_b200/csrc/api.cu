@@ -174,6 +174,19 @@ int32_t nf4_selfcheck_code_selection(uint64_t first_bits, uint64_t count, uint64
     return NF4_OK;
 }
 
+int32_t nf4_selfcheck_quantize_fast_path(uint64_t first_bits, uint64_t count, float absmax,
+                                         uint64_t *mismatches) {
+    if (!mismatches) return fail(NF4_ERR_INVALID_ARG, "nf4_selfcheck_quantize_fast_path: null pointer");
+    NF4_TRY(t_arena.reserve(256));
+    unsigned long long *d = static_cast<unsigned long long *>(t_arena.ptr);
+    NF4_CUDA_TRY(cudaMemsetAsync(d, 0, 8, 0));
+    NF4_TRY(selfcheck_fast(first_bits, count, absmax, d, 0));
+    unsigned long long h = 0;
+    NF4_CUDA_TRY(cudaMemcpy(&h, d, 8, cudaMemcpyDeviceToHost));
+    *mismatches = h;
+    return NF4_OK;
+}
+
 uint64_t nf4_num_blocks(uint64_t len) { return (len + kBlock - 1) / kBlock; }
 
 uint64_t nf4_packed_bytes(uint64_t len) { return (len + 1) / 2; }

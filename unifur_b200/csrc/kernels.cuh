@@ -37,6 +37,8 @@ int32_t dequantize_unpacked(const uint8_t *codes, uint64_t len, const float *abs
                             cudaStream_t stream);
 int32_t double_quantize(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
                         float *scale_of_scales, cudaStream_t stream);
+int32_t selfcheck_fast(uint64_t first_bits, uint64_t count, float absmax,
+                       unsigned long long *mismatches_dev, cudaStream_t stream);
 int32_t selfcheck_codes(uint64_t first_bits, uint64_t count, unsigned long long *mismatches_dev,
                         cudaStream_t stream);
 

@@ -87,6 +87,36 @@ __device__ __forceinline__ uint32_t code_of(float x, float absmax) {
     return code_of_normalized(__fdiv_rn(x, absmax));
 }
 
+// ---- fast code selection ------------------------------------------------------------------
+// Thirty-two uniform cells over [-1, 1); a cell holds at most one decision threshold.
+struct CellEntry {
+    uint32_t threshold_bits;  // the threshold inside the cell, or +inf
+    uint32_t below;           // number of thresholds below the cell
+};
+static __device__ __constant__ const CellEntry c_cell_table[32] = {NF4_CELL_TABLE_LIST};
+
+// Code of x / absmax without the division, when that is provably safe.
+//   q = x * rcp with rcp = fl(1 / absmax) lies within 1.8e-7 of the correctly rounded quotient
+//   (|x| <= absmax, both roundings <= 2^-24 relative).  The cell of q names the only threshold
+//   that can matter; when q is more than 1e-6 away from it, the exact quotient is on the same
+//   side and the code is `below + (q >= threshold)`.  Otherwise -- next to a threshold, NaN,
+//   or a scale outside [1e-30, 1e30] where rcp is not trustworthy -- the exact path decides.
+// `cells` is the table in shared memory.  Cell rounding can put q in a neighbouring cell only
+// within 2e-6 of a cell edge, and no threshold is that close to an edge, so the count is
+// unaffected.
+__device__ __forceinline__ uint32_t code_of_fast(float x, float absmax, float rcp, bool rcp_ok,
+                                                 const uint2 *cells) {
+    if (rcp_ok) {
+        const float q = __fmul_rn(x, rcp);
+        int c = __float2int_rz(fmaf(q, 16.0f, 16.0f));  // NaN -> 0
+        c = min(max(c, 0), 31);
+        const uint2 e = cells[c];
+        const float d = q - __uint_as_float(e.x);
+        if (fabsf(d) > 1e-6f) return e.y + (d >= 0.0f ? 1u : 0u);
+    }
+    return code_of(x, absmax);
+}
+
 // Scale of a double-quantized block: divide first, then multiply (src/quantize.rs:348).
 __device__ __forceinline__ float dq_scale(uint32_t code, float scale_of_scales) {
     return __fmul_rn(__fdiv_rn((float)code, 255.0f), scale_of_scales);

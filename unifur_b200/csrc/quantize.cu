@@ -29,6 +29,11 @@ template <bool PACKED>
 __global__ void __launch_bounds__(kThreads)
 quantize_full_kernel(const float4 *__restrict__ values, uint64_t nfull,
                      uint8_t *__restrict__ codes, float *__restrict__ absmax) {
+    __shared__ uint2 s_cells[32];
+    if (threadIdx.x < 32)
+        s_cells[threadIdx.x] = make_uint2(c_cell_table[threadIdx.x].threshold_bits,
+                                          c_cell_table[threadIdx.x].below);
+    __syncthreads();
     const uint32_t lane = threadIdx.x & 31u;
     const uint64_t warp = (uint64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     const uint64_t nwarps = (uint64_t)gridDim.x * kWarpsPerCta;
@@ -48,9 +53,18 @@ quantize_full_kernel(const float4 *__restrict__ values, uint64_t nfull,
         m = fmaxf(0.0f, m);
         m = group8_max(m);
         if (!live) continue;
-        const uint32_t c0 = code_of(a.x, m), c1 = code_of(a.y, m), c2 = code_of(a.z, m),
-                       c3 = code_of(a.w, m), c4 = code_of(b.x, m), c5 = code_of(b.y, m),
-                       c6 = code_of(b.z, m), c7 = code_of(b.w, m);
+        // one exact reciprocal per thread; each value is then decided from x * rcp unless it
+        // lands next to a decision threshold (see code_of_fast)
+        const bool rcp_ok = m >= 1e-30f && m <= 1e30f;
+        const float rcp = __fdiv_rn(1.0f, m);
+        const uint32_t c0 = code_of_fast(a.x, m, rcp, rcp_ok, s_cells),
+                       c1 = code_of_fast(a.y, m, rcp, rcp_ok, s_cells),
+                       c2 = code_of_fast(a.z, m, rcp, rcp_ok, s_cells),
+                       c3 = code_of_fast(a.w, m, rcp, rcp_ok, s_cells),
+                       c4 = code_of_fast(b.x, m, rcp, rcp_ok, s_cells),
+                       c5 = code_of_fast(b.y, m, rcp, rcp_ok, s_cells),
+                       c6 = code_of_fast(b.z, m, rcp, rcp_ok, s_cells),
+                       c7 = code_of_fast(b.w, m, rcp, rcp_ok, s_cells);
         if (PACKED) {
             const uint32_t word = c0 | (c1 << 4) | (c2 << 8) | (c3 << 12) | (c4 << 16) |
                                   (c5 << 20) | (c6 << 24) | (c7 << 28);
@@ -314,6 +328,37 @@ selfcheck_codes_kernel(uint64_t first_bits, uint64_t count, unsigned long long *
         bad += code_of_normalized(v) != code_by_scan(v);
     }
     if (bad) atomicAdd(mismatches, bad);
+}
+
+// Same walk for the division-free fast path: every f32 x with |x| <= absmax (and NaNs), one
+// given absmax, compared with the exact division + literal scan.
+__global__ void __launch_bounds__(kThreads)
+selfcheck_fast_kernel(uint64_t first_bits, uint64_t count, float absmax,
+                      unsigned long long *mismatches) {
+    __shared__ uint2 s_cells[32];
+    if (threadIdx.x < 32)
+        s_cells[threadIdx.x] = make_uint2(c_cell_table[threadIdx.x].threshold_bits,
+                                          c_cell_table[threadIdx.x].below);
+    __syncthreads();
+    const bool rcp_ok = absmax >= 1e-30f && absmax <= 1e30f;
+    const float rcp = __fdiv_rn(1.0f, absmax);
+    unsigned long long bad = 0;
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < count; i += stride) {
+        const float x = __uint_as_float((uint32_t)(first_bits + i));
+        if (fabsf(x) > absmax) continue;  // cannot occur inside a block whose absmax this is
+        const uint32_t exact = absmax == 0.0f ? 7u : code_by_scan(__fdiv_rn(x, absmax));
+        bad += code_of_fast(x, absmax, rcp, rcp_ok, s_cells) != exact;
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
+int32_t selfcheck_fast(uint64_t first_bits, uint64_t count, float absmax,
+                       unsigned long long *mismatches_dev, cudaStream_t stream) {
+    selfcheck_fast_kernel<<<kNumSMs * 8, kThreads, 0, stream>>>(first_bits, count, absmax,
+                                                               mismatches_dev);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "selfcheck launch");
 }
 
 int32_t selfcheck_codes(uint64_t first_bits, uint64_t count, unsigned long long *mismatches_dev,
