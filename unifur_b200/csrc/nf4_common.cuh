@@ -88,33 +88,39 @@ __device__ __forceinline__ uint32_t code_of(float x, float absmax) {
 }
 
 // ---- fast code selection ------------------------------------------------------------------
-// Thirty-two uniform cells over [-1, 1); a cell holds at most one decision threshold.
-struct CellEntry {
-    uint32_t threshold_bits;  // the threshold inside the cell, or +inf
-    uint32_t below;           // number of thresholds below the cell
-};
-static __device__ __constant__ const CellEntry c_cell_table[32] = {NF4_CELL_TABLE_LIST};
+// Thirty-two uniform cells over [-1, 1); a cell holds at most one decision threshold.  One word
+// per cell: the f32 threshold inside the cell with its low four mantissa bits replaced by the
+// number of thresholds below the cell (the threshold moves by < 9e-7), or 1.7e38 | count for a
+// cell that holds none.
+static __device__ __constant__ const uint32_t c_cell_table[32] = {NF4_CELL_TABLE_LIST};
 
 // Code of x / absmax without the division, when that is provably safe.
 //   q = x * rcp with rcp = fl(1 / absmax) lies within 1.8e-7 of the correctly rounded quotient
 //   (|x| <= absmax, both roundings <= 2^-24 relative).  The cell of q names the only threshold
-//   that can matter; when q is more than 1e-6 away from it, the exact quotient is on the same
-//   side and the code is `below + (q >= threshold)`.  Otherwise -- next to a threshold, NaN,
-//   or a scale outside [1e-30, 1e30] where rcp is not trustworthy -- the exact path decides.
-// `cells` is the table in shared memory.  Cell rounding can put q in a neighbouring cell only
-// within 2e-6 of a cell edge, and no threshold is that close to an edge, so the count is
-// unaffected.
-__device__ __forceinline__ uint32_t code_of_fast(float x, float absmax, float rcp, bool rcp_ok,
-                                                 const uint2 *cells) {
-    if (rcp_ok) {
-        const float q = __fmul_rn(x, rcp);
-        int c = __float2int_rz(fmaf(q, 16.0f, 16.0f));  // NaN -> 0
-        c = min(max(c, 0), 31);
-        const uint2 e = cells[c];
-        const float d = q - __uint_as_float(e.x);
-        if (fabsf(d) > 1e-6f) return e.y + (d >= 0.0f ? 1u : 0u);
-    }
-    return code_of(x, absmax);
+//   that can matter; when q is more than 3e-6 away from the table's (slightly moved) copy of
+//   it, q and the exact quotient are on the same side of the true threshold and the code is
+//   `count + (q >= threshold)`.  Otherwise -- next to a threshold, NaN, or a scale outside
+//   [1e-30, 1e30] where rcp is not trustworthy (the caller starts `unsure` as true for those)
+//   -- the exact path decides.
+// `cells` is the table in shared memory (32 words, one bank each: no conflicts).  Cell rounding
+// can put q in a neighbouring cell only within 2e-6 of a cell edge, and no threshold is within
+// 1e-4 of an edge, so the count is unaffected.
+// Out of line on purpose: taken for a few values in a million, and inlining sixteen copies of
+// the division and the bisection doubles the quantize kernel's register count.
+static __device__ __noinline__ uint32_t code_of_exact(float x, float absmax) { return code_of(x, absmax); }
+
+// `unsure` is set (never cleared) when the value sits next to a threshold or is NaN; the caller
+// then redoes its values with code_of_exact.  Keeping the decision out of this function leaves
+// the common path branch-free.
+__device__ __forceinline__ uint32_t code_of_fast(float x, float rcp, const uint32_t *cells,
+                                                 bool &unsure) {
+    const float q = __fmul_rn(x, rcp);
+    int c = __float2int_rz(fmaf(q, 16.0f, 16.0f));  // NaN -> 0
+    c = min(max(c, 0), 31);
+    const uint32_t e = cells[c];
+    const float d = q - __uint_as_float(e);
+    unsure |= !(fabsf(d) > 3e-6f);
+    return (e & 15u) + (d >= 0.0f ? 1u : 0u);
 }
 
 // Scale of a double-quantized block: divide first, then multiply (src/quantize.rs:348).

@@ -26,13 +26,11 @@ __device__ __forceinline__ float group8_max(float m) {
 // Full 64-blocks only: `nfull` blocks starting at values[0].  PACKED selects nibble
 // packing (two codes per byte) versus one code per byte.
 template <bool PACKED>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 8)
 quantize_full_kernel(const float4 *__restrict__ values, uint64_t nfull,
                      uint8_t *__restrict__ codes, float *__restrict__ absmax) {
-    __shared__ uint2 s_cells[32];
-    if (threadIdx.x < 32)
-        s_cells[threadIdx.x] = make_uint2(c_cell_table[threadIdx.x].threshold_bits,
-                                          c_cell_table[threadIdx.x].below);
+    __shared__ uint32_t s_cells[32];
+    if (threadIdx.x < 32) s_cells[threadIdx.x] = c_cell_table[threadIdx.x];
     __syncthreads();
     const uint32_t lane = threadIdx.x & 31u;
     const uint64_t warp = (uint64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
@@ -53,18 +51,24 @@ quantize_full_kernel(const float4 *__restrict__ values, uint64_t nfull,
         m = fmaxf(0.0f, m);
         m = group8_max(m);
         if (!live) continue;
-        // one exact reciprocal per thread; each value is then decided from x * rcp unless it
-        // lands next to a decision threshold (see code_of_fast)
-        const bool rcp_ok = m >= 1e-30f && m <= 1e30f;
+        // one exact reciprocal per thread; each value is then decided from x * rcp, and the
+        // whole group is redone exactly if any of its values lands next to a decision threshold
+        bool unsure = !(m >= 1e-30f && m <= 1e30f);
         const float rcp = __fdiv_rn(1.0f, m);
-        const uint32_t c0 = code_of_fast(a.x, m, rcp, rcp_ok, s_cells),
-                       c1 = code_of_fast(a.y, m, rcp, rcp_ok, s_cells),
-                       c2 = code_of_fast(a.z, m, rcp, rcp_ok, s_cells),
-                       c3 = code_of_fast(a.w, m, rcp, rcp_ok, s_cells),
-                       c4 = code_of_fast(b.x, m, rcp, rcp_ok, s_cells),
-                       c5 = code_of_fast(b.y, m, rcp, rcp_ok, s_cells),
-                       c6 = code_of_fast(b.z, m, rcp, rcp_ok, s_cells),
-                       c7 = code_of_fast(b.w, m, rcp, rcp_ok, s_cells);
+        uint32_t c0 = code_of_fast(a.x, rcp, s_cells, unsure),
+                 c1 = code_of_fast(a.y, rcp, s_cells, unsure),
+                 c2 = code_of_fast(a.z, rcp, s_cells, unsure),
+                 c3 = code_of_fast(a.w, rcp, s_cells, unsure),
+                 c4 = code_of_fast(b.x, rcp, s_cells, unsure),
+                 c5 = code_of_fast(b.y, rcp, s_cells, unsure),
+                 c6 = code_of_fast(b.z, rcp, s_cells, unsure),
+                 c7 = code_of_fast(b.w, rcp, s_cells, unsure);
+        if (unsure) {
+            c0 = code_of_exact(a.x, m); c1 = code_of_exact(a.y, m);
+            c2 = code_of_exact(a.z, m); c3 = code_of_exact(a.w, m);
+            c4 = code_of_exact(b.x, m); c5 = code_of_exact(b.y, m);
+            c6 = code_of_exact(b.z, m); c7 = code_of_exact(b.w, m);
+        }
         if (PACKED) {
             const uint32_t word = c0 | (c1 << 4) | (c2 << 8) | (c3 << 12) | (c4 << 16) |
                                   (c5 << 20) | (c6 << 24) | (c7 << 28);
@@ -118,43 +122,67 @@ __device__ __forceinline__ float block_scale(const float *__restrict__ absmax,
     return absmax ? __ldg(absmax + blk) : dq_scale(__ldg(scale_codes + blk), sos);
 }
 
+// Full 64-blocks, 16-byte aligned buffers.  A lane reads the codes of eight consecutive values;
+// neighbouring lanes then swap halves so that the pair's two 128-bit stores each fill whole
+// 32-byte sectors (lane 2j writes values 16j..16j+3 and 16j+8..16j+11, lane 2j+1 the other two
+// quads).  Four such groups are in flight per thread to cover the load latency.
 template <bool PACKED>
 __global__ void __launch_bounds__(kThreads)
 dequantize_full_kernel(const uint8_t *__restrict__ codes, uint64_t nfull,
                        const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
                        const float *__restrict__ scale_of_scales, float4 *__restrict__ out) {
+    constexpr int kInFlight = 4;
     __shared__ float s_levels[16];
     if (threadIdx.x < 16) s_levels[threadIdx.x] = __uint_as_float(c_level_bits[threadIdx.x]);
     __syncthreads();
     const float sos = scale_of_scales ? __ldg(scale_of_scales) : 0.0f;
-    const uint64_t ngroups = nfull * 8;  // 8 values per group
+    const uint64_t ngroups = nfull * 8;  // 8 values per group; a multiple of 8, so lane pairs stay whole
     const uint64_t stride = (uint64_t)gridDim.x * kThreads;
-    for (uint64_t g = (uint64_t)blockIdx.x * kThreads + threadIdx.x; g < ngroups; g += stride) {
-        uint32_t c[8];
-        if (PACKED) {
-            const uint32_t w = __ldcs(reinterpret_cast<const uint32_t *>(codes) + g);
-            #pragma unroll
-            for (int i = 0; i < 8; ++i) c[i] = (w >> (4 * i)) & 15u;
-        } else {
-            const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(codes) + g);
-            #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                c[i] = (w.x >> (8 * i)) & 15u;
-                c[4 + i] = (w.y >> (8 * i)) & 15u;
+    const uint32_t lane = threadIdx.x & 31u;
+    const bool odd = lane & 1u;
+    const uint64_t first = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
+    for (uint64_t g0 = first; g0 - lane < ngroups; g0 += stride * kInFlight) {
+        uint32_t lo[kInFlight], hi[kInFlight];  // codes of the first / second quad this lane stores
+        float s[kInFlight];
+        #pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const uint64_t g = g0 + u * stride;
+            const bool live = g < ngroups;
+            uint32_t a = 0, b = 0;  // codes of values 0..3 and 4..7 of the group
+            if (PACKED) {
+                const uint32_t w = live ? __ldcs(reinterpret_cast<const uint32_t *>(codes) + g) : 0u;
+                a = w & 0xffffu;
+                b = w >> 16;
+            } else {
+                const uint2 w = live ? __ldcs(reinterpret_cast<const uint2 *>(codes) + g)
+                                     : make_uint2(0u, 0u);
+                a = w.x;
+                b = w.y;
             }
+            s[u] = live ? block_scale(absmax, scale_codes, sos, g >> 3) : 0.0f;
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+            lo[u] = odd ? got : a;  // even: own first quad;   odd: partner's second quad
+            hi[u] = odd ? b : got;  // even: partner's first quad; odd: own second quad
         }
-        const float s = block_scale(absmax, scale_codes, sos, g >> 3);
-        float4 a, b;
-        a.x = __fmul_rn(s_levels[c[0]], s);
-        a.y = __fmul_rn(s_levels[c[1]], s);
-        a.z = __fmul_rn(s_levels[c[2]], s);
-        a.w = __fmul_rn(s_levels[c[3]], s);
-        b.x = __fmul_rn(s_levels[c[4]], s);
-        b.y = __fmul_rn(s_levels[c[5]], s);
-        b.z = __fmul_rn(s_levels[c[6]], s);
-        b.w = __fmul_rn(s_levels[c[7]], s);
-        __stcs(out + 2 * g, a);
-        __stcs(out + 2 * g + 1, b);
+        #pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const uint64_t g = g0 + u * stride;
+            if (g >= ngroups) continue;
+            constexpr int kBits = PACKED ? 4 : 8;
+            float4 q0, q1;
+            q0.x = __fmul_rn(s_levels[(lo[u] >> (0 * kBits)) & 15u], s[u]);
+            q0.y = __fmul_rn(s_levels[(lo[u] >> (1 * kBits)) & 15u], s[u]);
+            q0.z = __fmul_rn(s_levels[(lo[u] >> (2 * kBits)) & 15u], s[u]);
+            q0.w = __fmul_rn(s_levels[(lo[u] >> (3 * kBits)) & 15u], s[u]);
+            q1.x = __fmul_rn(s_levels[(hi[u] >> (0 * kBits)) & 15u], s[u]);
+            q1.y = __fmul_rn(s_levels[(hi[u] >> (1 * kBits)) & 15u], s[u]);
+            q1.z = __fmul_rn(s_levels[(hi[u] >> (2 * kBits)) & 15u], s[u]);
+            q1.w = __fmul_rn(s_levels[(hi[u] >> (3 * kBits)) & 15u], s[u]);
+            // pair base = float4 index 2 * (g & ~1); even lane stores quads 0 and 2, odd 1 and 3
+            float4 *dst = out + 2 * (g & ~(uint64_t)1) + (odd ? 1 : 0);
+            __stcs(dst, q0);
+            __stcs(dst + 2, q1);
+        }
     }
 }
 
@@ -335,10 +363,8 @@ selfcheck_codes_kernel(uint64_t first_bits, uint64_t count, unsigned long long *
 __global__ void __launch_bounds__(kThreads)
 selfcheck_fast_kernel(uint64_t first_bits, uint64_t count, float absmax,
                       unsigned long long *mismatches) {
-    __shared__ uint2 s_cells[32];
-    if (threadIdx.x < 32)
-        s_cells[threadIdx.x] = make_uint2(c_cell_table[threadIdx.x].threshold_bits,
-                                          c_cell_table[threadIdx.x].below);
+    __shared__ uint32_t s_cells[32];
+    if (threadIdx.x < 32) s_cells[threadIdx.x] = c_cell_table[threadIdx.x];
     __syncthreads();
     const bool rcp_ok = absmax >= 1e-30f && absmax <= 1e30f;
     const float rcp = __fdiv_rn(1.0f, absmax);
@@ -348,7 +374,10 @@ selfcheck_fast_kernel(uint64_t first_bits, uint64_t count, float absmax,
         const float x = __uint_as_float((uint32_t)(first_bits + i));
         if (fabsf(x) > absmax) continue;  // cannot occur inside a block whose absmax this is
         const uint32_t exact = absmax == 0.0f ? 7u : code_by_scan(__fdiv_rn(x, absmax));
-        bad += code_of_fast(x, absmax, rcp, rcp_ok, s_cells) != exact;
+        bool unsure = !rcp_ok;
+        uint32_t got = code_of_fast(x, rcp, s_cells, unsure);
+        if (unsure) got = code_of_exact(x, absmax);
+        bad += got != exact;
     }
     if (bad) atomicAdd(mismatches, bad);
 }
