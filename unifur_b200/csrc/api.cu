@@ -272,20 +272,17 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     NF4_TRY(validate_linear(args));
     if (args->rows == 0) return NF4_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Two decode kernels: warp-MMA (tile per 16 rows) and tcgen05 (128-row blocks, split K).
-    // Measured on B200 the first wins up to 8 rows, the second from 9 to 16; NF4_DECODE_KERNEL=1
-    // or 2 in the environment pins one of them (for measurements).
+    // Two decode kernels: warp-MMA (16-row tiles, d_in <= 4096) and tcgen05 (128-row blocks,
+    // split K, any d_in).  Measured on B200 the first wins wherever it applies;
+    // NF4_DECODE_KERNEL=1 or 2 in the environment pins one of them (for measurements).
     static const int pin = [] {
         const char *e = std::getenv("NF4_DECODE_KERNEL");
         return e ? std::atoi(e) : 0;
     }();
-    const bool v1 = pin != 2 && decode_supported(*args);
-    const bool v2 = pin != 1 && decode2_supported(*args);
-    if (v1 && v2) return args->rows <= 8 ? decode_forward(*args, s) : decode2_forward(*args, s);
-    if (v2) return decode2_forward(*args, s);
-    if (v1) return decode_forward(*args, s);
-    if (pin && decode2_supported(*args)) return decode2_forward(*args, s);
-    if (pin && decode_supported(*args)) return decode_forward(*args, s);
+    if (pin != 2 && decode_supported(*args)) return decode_forward(*args, s);
+    if (pin != 1 && decode2_supported(*args)) return decode2_forward(*args, s);
+    if (pin == 2 && decode_supported(*args)) return decode_forward(*args, s);
+    if (pin == 1 && decode2_supported(*args)) return decode2_forward(*args, s);
     if (prefill_supported(*args)) return prefill_forward(*args, s);
     return generic_forward(*args, s);
 }

@@ -2,26 +2,36 @@
 // packed NF4 [N, K] with 64-blocks along K.  HBM-bound: the kernel exists to stream
 // nibbles + scales once at full bandwidth.
 //
-// Data movement.  One CTA per SM owns a contiguous range of W rows.  A producer warp
-// streams 16-row tiles (packed bytes, block scales, LoRA-B rows) global -> shared with
-// untiled TMA bulk copies that complete on an mbarrier; every row lands on a padded
-// stride so the consumers' shared-memory reads are bank-conflict free.  Whole tiles
-// are requested as soon as a ring slot is free, which keeps ~150 KB per SM in flight.
+// Data movement.  One CTA per SM owns a contiguous range of W rows; its sixteen warps split K
+// (up to four 64-blocks each).  Every warp streams its own slice -- 16 rows x 128 bytes of
+// nibbles plus the 16 x 4 block scales per tile -- global -> shared with per-thread 16-byte
+// asynchronous copies (cp.async, L2 only) into a private ring of a few tiles, rows on a padded
+// stride so that the reads are bank-conflict free.  The warps therefore share no barrier while
+// the weights stream.  (A first version moved whole tiles with TMA bulk copies; measured on
+// B200 that path delivered ~13-20 bytes per clock per SM from DRAM however many tiles were
+// requested ahead, about half of what the copy engines of all SMs need to saturate HBM, so the
+// stream now goes through the load/store path, which keeps far more requests in flight.)
 //
 // Math.  Dequantisation is a shared-memory table lookup: one packed byte (two codes)
 // indexes a 256-entry table of half2 {level[lo], level[hi]}, replicated once per
-// lane so that no two lanes share a bank.  The looked-up register IS the A operand of
+// lane so that no two lanes share a bank; entries sit 256 bytes apart so that one byte
+// permute (code byte into bits 8..15, lane offset below) forms the address.  The looked-up
+// register IS the A operand of
 // a warp MMA (m16n8k16, f16 in / f32 accumulate), with W rows on the MMA's M side and
-// the <=16 activation rows on its N side.  The sixteen consumer warps split K; each
-// keeps its slice of x as f16 B-fragments in registers for the whole kernel.  A block's
-// four MMAs accumulate into a scratch accumulator that is then scaled by the block's
-// f32 absmax (or its double-quantized decode) -- the scale never touches the f16 path.
-// Each warp parks its partial sums in its own slice of a shared-memory slot and the
-// producer warp finishes each tile: sum the slices in warp order (so results do not
-// depend on timing), + bias, + LoRA (T = x A^T comes from a small pre-pass), convert, store.
+// the <=16 activation rows on its N side.  Each warp keeps its slice of x as f16 B-fragments
+// in registers for the whole kernel.  A block's four MMAs form two short chains, are
+// summed and scaled by the block's f32 absmax (or its double-quantized decode) -- the scale
+// never touches the f16 path.  The lookups bound the kernel: one shared-memory wavefront
+// serves 64 weights.
+//
+// Reduction.  A warp keeps the partial sums of several tiles in registers.  At the end of such
+// a pass every warp parks them in its own shared-memory slot and all threads sum the sixteen
+// slots in warp order (so results do not depend on timing), add bias and the LoRA term
+// (T = x A^T comes from a small pre-pass), convert and store.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -29,7 +39,7 @@
 
 namespace nf4 {
 
-__device__ int g_decode_error = 0;  // set when a bounded wait gives up
+__device__ int g_decode_error = 0;  // kept for the error-flag entry point; this kernel has no waits that can give up
 
 #ifdef NF4_DECODE_TIMING
 // Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
@@ -41,14 +51,20 @@ __device__ long long g_decode_ts[64];
 
 namespace {
 
-constexpr int kMaxConsumerWarps = 16;
+constexpr int kWarps = 16;           // all of them split K
+constexpr int kDecodeThreads = kWarps * 32;
 constexpr int kTileRows = 16;
 constexpr int kChunk = 64;           // one quantization block of K
 constexpr int kMaxChunksPerWarp = 4; // x fragments live in registers: K <= 16*4*64
-constexpr int kMaxStages = 8;
-constexpr int kLutBytes = 256 * 32 * 4;
+constexpr int kMaxRing = 6;          // tiles per warp ring (one being read, the rest in flight)
+constexpr int kLutStride = 256;      // bytes between table entries (128 used)
+constexpr int kLutBytes = 256 * kLutStride;
 constexpr int kMaxRank = 64;
 constexpr int kSmemLimit = 227 * 1024;
+constexpr int kSlots = kWarps;       // one reduction slot per warp
+
+// tiles whose partial sums a warp keeps in registers between two reductions
+template <int NT> struct PassTiles { static constexpr int value = NT == 1 ? 8 : 3; };
 
 struct DecodeParams {
     const __nv_bfloat16 *x;
@@ -65,16 +81,16 @@ struct DecodeParams {
     uint32_t M, K, N, rank;
     float lora_scale;
     uint32_t gran;            // CTA row ranges start on multiples of this
-    uint32_t consumer_warps;  // warps that split K
     uint32_t chunks_per_warp;
-    uint32_t stages;
-    uint32_t code_stride;   // bytes between rows of packed codes in shared memory
-    uint32_t scale_stride;  // bytes between rows of scales in shared memory
-    uint32_t scale_row_bytes;
-    uint32_t scale_per_row;  // 1: one bulk copy per row (padded); 0: one copy per tile
-    uint32_t stage_bytes;
-    uint32_t off_scales, off_lora;  // offsets inside a stage
-    uint32_t off_red, off_stages;   // offsets inside dynamic shared memory
+    uint32_t ring;            // tiles per warp ring
+    uint32_t pass_tiles;      // tiles per reduction pass (<= PassTiles<NT>)
+    uint32_t code_stride;     // bytes between rows of a warp's nibbles in shared memory
+    uint32_t slot_bytes;      // one tile of one warp: nibbles, then scales
+    uint32_t off_scales;      // offset of the scales inside a slot
+    uint32_t vec_scales;      // scales travel with the tile (else they are read from global)
+    uint32_t lora_bytes_max;  // room for the CTA's LoRA-B rows
+    uint32_t off_lora, off_rings;  // offsets inside dynamic shared memory (reduction slots alias the table)
+    uint32_t red_slot_bytes;
 };
 
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
@@ -84,267 +100,237 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
-// Producer warp: request one 16-row tile (packed bytes, block scales, LoRA-B rows) into its ring
-// slot.  Lane r copies row r; lane 31 issues the copies that cover the whole tile.
-template <bool DQ>
-__device__ __forceinline__ void issue_tile(const DecodeParams &p, uint32_t tile, uint32_t n0,
-                                           uint32_t n1, uint32_t S, uint8_t *stage_base,
-                                           uint32_t bar_full, uint32_t lane) {
-    const uint32_t s = tile % S;
-    const uint32_t row0 = n0 + tile * kTileRows;
-    const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
-    const uint32_t code_row_bytes = p.K / 2;
-    uint8_t *st = stage_base + (size_t)s * p.stage_bytes;
-    const uint32_t bar = bar_full + 8 * s;
-    const uint32_t lora_bytes = p.rank ? rows * p.rank * 2u : 0u;
-    if (lane == 0)
-        ptx::mbar_arrive_expect_tx(bar, rows * (code_row_bytes + p.scale_row_bytes) + lora_bytes);
-    __syncwarp();
-    if (lane < rows) {
-        const uint32_t r = row0 + lane;
-        ptx::bulk_g2s(ptx::smem_addr(st + lane * p.code_stride),
-                      p.codes + (size_t)r * code_row_bytes, code_row_bytes, bar);
-        if (p.scale_per_row) {
-            const uint8_t *src = DQ ? p.scale_codes + (size_t)r * p.scale_row_bytes
-                                    : reinterpret_cast<const uint8_t *>(p.absmax) +
-                                          (size_t)r * p.scale_row_bytes;
-            ptx::bulk_g2s(ptx::smem_addr(st + p.off_scales + lane * p.scale_stride), src,
-                          p.scale_row_bytes, bar);
+// sixteen bf16 (two 128-bit words) -> this lane's f16 B-fragments of one 64-chunk
+__device__ __forceinline__ void convert_x(const uint4 &q0, const uint4 &q1, uint32_t (&xf)[4][2]) {
+    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        #pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t pair = w[2 * j + h];  // two bf16: k, k+1
+            xf[j][h] = pack_f16x2(bf16_bits_to_float(pair & 0xffffu), bf16_bits_to_float(pair >> 16));
         }
     }
-    if (lane == 31) {
-        if (!p.scale_per_row) {
-            const uint8_t *src = DQ ? p.scale_codes + (size_t)row0 * p.scale_row_bytes
-                                    : reinterpret_cast<const uint8_t *>(p.absmax) +
-                                          (size_t)row0 * p.scale_row_bytes;
-            ptx::bulk_g2s(ptx::smem_addr(st + p.off_scales), src, rows * p.scale_row_bytes, bar);
-        }
-        if (lora_bytes)
-            ptx::bulk_g2s(ptx::smem_addr(st + p.off_lora), p.lora_b + (size_t)row0 * p.rank,
-                          lora_bytes, bar);
+}
+
+// Blocks until at most `n` of this thread's copy groups are in flight (n is small).
+__device__ __forceinline__ void wait_groups(uint32_t n) {
+    switch (n) {
+        case 0: ptx::cp_async_wait<0>(); break;
+        case 1: ptx::cp_async_wait<1>(); break;
+        case 2: ptx::cp_async_wait<2>(); break;
+        case 3: ptx::cp_async_wait<3>(); break;
+        case 4: ptx::cp_async_wait<4>(); break;
+        default: ptx::cp_async_wait<5>(); break;
     }
 }
 
 template <int NT, bool DQ>
-__global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
+__global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint32_t *lut = reinterpret_cast<uint32_t *>(smem);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kLutBytes);  // full[8], done[8], red_free[2]
-    float *t_s = reinterpret_cast<float *>(smem + kLutBytes + 256);    // [M][rank]
-    float *red = reinterpret_cast<float *>(smem + p.off_red);          // [2][warps][16][MP]
-    uint8_t *stage_base = smem + p.off_stages;
-    constexpr int MP = 8 * NT;
+    float *t_s = reinterpret_cast<float *>(smem + kLutBytes);  // [M][rank]
+    uint8_t *lora_raw = smem + p.off_lora;
+    const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(lora_raw);
+    float *red = reinterpret_cast<float *>(smem);  // the reduction slots take the lookup table's place
+    constexpr int PT = PassTiles<NT>::value;
+    constexpr int kAccs = 2;  // a block's four MMAs run as two chains of two
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t S = p.stages;
-    const uint32_t red_slot_floats = p.consumer_warps * kTileRows * MP;
+    uint8_t *ring = smem + p.off_rings + (size_t)warp * p.ring * p.slot_bytes;
+    const uint32_t ring_addr = ptx::smem_addr(ring);
+    const uint32_t R = p.ring, D = R - 1;  // D tiles in flight while one is read
 
     // rows owned by this CTA: units of `gran` rows, split evenly over the grid
     const uint64_t units = p.N / p.gran;
     const uint32_t n0 = (uint32_t)((uint64_t)blockIdx.x * units / gridDim.x) * p.gran;
     const uint32_t n1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * units / gridDim.x) * p.gran;
     const uint32_t ntiles = (n1 - n0 + kTileRows - 1) / kTileRows;
-
-    const uint32_t bar_full = ptx::smem_addr(bars), bar_done = ptx::smem_addr(bars + kMaxStages);
-    const uint32_t bar_red_free = ptx::smem_addr(bars + 2 * kMaxStages);
-    const uint32_t bar_epi_done = ptx::smem_addr(bars + 2 * kMaxStages + 2);
     if (warp == 0) NF4_TS(0);
 
-    // Consumers ask for their slice of x before anything else: once the producer's bulk copies
-    // saturate the memory system, a late request would queue behind ~150 KB per SM.
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t nchunks = p.K / kChunk;
     const uint32_t chunk0 = warp * p.chunks_per_warp;
-    uint4 xraw[NT][kMaxChunksPerWarp][2];
-    if (warp < p.consumer_warps) {
+    const bool active = chunk0 < nchunks;  // short K leaves the last warps without a slice
+    const uint32_t my_chunks = active ? min(p.chunks_per_warp, nchunks - chunk0) : 0u;
+    const uint32_t code_row_bytes = p.K / 2;
+
+    // Ask for one tile of this warp's slice: 16 rows x (32 bytes per chunk) of nibbles in
+    // 16-byte pieces, then the rows' scales.  Rows past the CTA's range are left as they are:
+    // their products land in accumulator rows that are never stored.
+    auto request_tile = [&](uint32_t tile) {
+        const uint32_t row0 = n0 + tile * kTileRows;
+        const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
+        const uint32_t slot = ring_addr + (tile % R) * p.slot_bytes;
+        const uint32_t pieces_per_row = my_chunks * 2u;
+        const uint8_t *src0 = p.codes + (size_t)row0 * code_row_bytes + chunk0 * 32u;
+        for (uint32_t q = lane; q < rows * pieces_per_row; q += 32) {
+            const uint32_t row = q / pieces_per_row, piece = q - row * pieces_per_row;
+            ptx::cp_async_16(slot + row * p.code_stride + piece * 16u,
+                             src0 + (size_t)row * code_row_bytes + piece * 16u);
+        }
+        if (p.vec_scales && lane < rows) {
+            if (DQ)
+                ptx::cp_async_4(slot + p.off_scales + lane * 4u,
+                                p.scale_codes + (size_t)(row0 + lane) * nchunks + chunk0);
+            else
+                ptx::cp_async_16(slot + p.off_scales + lane * 16u,
+                                 p.absmax + (size_t)(row0 + lane) * nchunks + chunk0);
+        }
+    };
+
+    // ---- x first (plain loads: nothing of this kernel's own is queued ahead of them).  The
+    // pre-pass that this kernel may overlap is an ordinary launch: x was complete before it
+    // started, so x is complete now. ----
+    uint32_t xf[NT][kMaxChunksPerWarp][4][2];  // this warp's slice of x as f16 B-fragments
+    {
+        uint4 xraw[NT][kMaxChunksPerWarp][2];
         #pragma unroll
         for (int u = 0; u < NT; ++u) {
             const uint32_t m = 8 * u + g;
             #pragma unroll
             for (int c = 0; c < kMaxChunksPerWarp; ++c) {
-                const uint32_t kc = chunk0 + c;
                 xraw[u][c][0] = xraw[u][c][1] = make_uint4(0, 0, 0, 0);
-                if (m < p.M && c < (int)p.chunks_per_warp && kc < nchunks) {
+                if (m < p.M && c < (int)my_chunks) {
                     const uint4 *src = reinterpret_cast<const uint4 *>(
-                        p.x + (size_t)m * p.K + kc * kChunk + 16 * t);
+                        p.x + (size_t)m * p.K + (chunk0 + c) * kChunk + 16 * t);
                     xraw[u][c][0] = __ldg(src);
                     xraw[u][c][1] = __ldg(src + 1);
                 }
             }
         }
-    }
 
-    // x slice of this warp as f16 B-fragments, converted as soon as it arrives
-    uint32_t xf[NT][kMaxChunksPerWarp][4][2];
-    if (warp < p.consumer_warps) {
-        // x slice of this warp as f16 B-fragments: xf[u][c][j] = {b0, b1}
+        // ---- the CTA's LoRA-B rows and the first tiles of the stream ----
+        if (p.rank) {
+            const uint32_t pieces = (n1 - n0) * p.rank * 2u / 16u;
+            const uint8_t *src = reinterpret_cast<const uint8_t *>(p.lora_b + (size_t)n0 * p.rank);
+            for (uint32_t q = tid; q < pieces; q += kDecodeThreads)
+                ptx::cp_async_16(ptx::smem_addr(lora_raw) + q * 16u, src + (size_t)q * 16u);
+        }
+        ptx::cp_async_commit();
+        for (uint32_t d = 0; d < D; ++d) {
+            if (active && d < ntiles) request_tile(d);
+            ptx::cp_async_commit();
+        }
+
+        if (warp == 0) NF4_TS(2);
         #pragma unroll
         for (int u = 0; u < NT; ++u) {
             #pragma unroll
-            for (int c = 0; c < kMaxChunksPerWarp; ++c) {
-                const uint4 q0 = xraw[u][c][0], q1 = xraw[u][c][1];
-                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t pair = w[2 * j + h];  // two bf16: k, k+1
-                        xf[u][c][j][h] = pack_f16x2(bf16_bits_to_float(pair & 0xffffu),
-                                                    bf16_bits_to_float(pair >> 16));
-                    }
-                }
-            }
+            for (int c = 0; c < kMaxChunksPerWarp; ++c) convert_x(xraw[u][c][0], xraw[u][c][1], xf[u][c]);
         }
-
-        if (warp == 0) NF4_TS(7);
-        asm volatile("bar.arrive 3, %0;" ::"r"((p.consumer_warps + 1) * 32) : "memory");
+#ifdef NF4_DECODE_TIMING
+        if (xf[0][0][0][0] == 0x12345678u) NF4_TS(63);  // forces the conversion before the next stamp
+#endif
+        if (warp == 0) NF4_TS(3);
     }
 
-    if (warp == p.consumer_warps) {
-        // ========================= producer warp =========================
-        // The barriers are this warp's to set up, so the first loads leave before the other
-        // warps have finished building the lookup table.
-        if (lane == 0) {
-            for (uint32_t s = 0; s < S; ++s) {
-                ptx::mbar_init(bar_full + 8 * s, 1);
-                ptx::mbar_init(bar_done + 8 * s, p.consumer_warps);
-                ptx::mbar_init(bar_epi_done + 8 * s, 1);
-            }
-            ptx::mbar_init(bar_red_free, 1);
-            ptx::mbar_init(bar_red_free + 8, 1);
-            ptx::fence_mbar_init();
-            ptx::fence_proxy_async();
-        }
-        __syncwarp();
-        // hold the bulk copies back until the consumers HAVE their x: requests issued behind
-        // ~150 KB of queued weight traffic per SM were seen to take ~4 us to come back
-        asm volatile("bar.sync 3, %0;" ::"r"((p.consumer_warps + 1) * 32) : "memory");
-        // Only the first tile is requested now.  Asking for everything at once makes every tile,
-        // the first included, arrive together after the whole ~150 KB burst (~4 us); with one to
-        // two tiles in flight the first is there after ~1 us and the rest keep ahead of the math.
-        issue_tile<DQ>(p, 0, n0, n1, S, stage_base, bar_full, lane);
-    } else if (warp < p.consumer_warps) {
-        // ---- consumers build the lookup table while the first tiles are in flight ----
-        const uint32_t nthreads = p.consumer_warps * 32;
-        for (uint32_t i = tid; i < 256 * 32; i += nthreads) {
-            const uint32_t byte = i >> 5;
-            lut[i] = pack_f16x2(__uint_as_float(c_level_bits[byte & 15u]),
-                                __uint_as_float(c_level_bits[byte >> 4]));
-        }
-    }
+    // ---- the lookup table: thread (byte, half) writes sixteen lanes' copies of its entry ----
+    auto build_table = [&]() {
+        const uint32_t byte = tid >> 1, half = tid & 1u;
+        const uint32_t entry = c_level_f16_bits[byte & 15u] | (c_level_f16_bits[byte >> 4] << 16);
+        const uint4 v = make_uint4(entry, entry, entry, entry);
+        #pragma unroll
+        for (int i = 0; i < 4; ++i)  // rotated by the byte so that a warp's stores spread over the banks
+            *reinterpret_cast<uint4 *>(smem + byte * kLutStride + half * 64u + ((i + byte) & 3u) * 16u) = v;
+    };
+    build_table();
+    if (warp == 0) NF4_TS(50);
     __syncthreads();
     if (warp == 0) NF4_TS(1);
 
-    if (warp == p.consumer_warps) {
-        // Producer: keep `ahead + 1` tiles in flight, in order.  A tile is requested once the
-        // tile `ahead + 1` before it has landed and its ring slot's previous tile is finished.
-        const uint32_t ahead = S >= 4 ? 3u : S - 1u;
-        bool ok = true;
-        for (uint32_t n = 1; n < ntiles && ok; ++n) {
-            if (n > ahead) {
-                const uint32_t w = n - ahead - 1;
-                ok = ptx::mbar_wait_bounded(bar_full + 8 * (w % S), (w / S) & 1u);
-            }
-            if (ok && n >= S) ok = ptx::mbar_wait_bounded(bar_epi_done + 8 * (n % S), ((n / S) - 1) & 1u);
-            if (!ok) break;
-            ptx::fence_proxy_async();
-            issue_tile<DQ>(p, n, n0, n1, S, stage_base, bar_full, lane);
-        }
-        if (!ok && lane == 0) atomicExch(&g_decode_error, 3);
-    } else if (warp == p.consumer_warps + 1) {
-        // ========================= epilogue warp =========================
-        // T = x A^T comes from the pre-pass, which may still be running: wait for it here,
-        // after this kernel's own loads have long been issued
-        if (p.rank) {
-            ptx::pdl_wait();
-            for (uint32_t i = lane; i < p.M * p.rank; i += 32) t_s[i] = __ldcg(p.t + i);
-        }
-        __syncwarp();
-        // Finish tiles in order: sum the warps' partials in a fixed order (so the result does
-        // not depend on timing), add bias and the adapter term, convert, store; then hand the
-        // reduction slot back and refill the tile's ring slot.
-        bool ok = true;
-        for (uint32_t tile = 0; tile < ntiles && ok; ++tile) {
-            const uint32_t s = tile % S;
-            ok = ptx::mbar_wait_bounded(bar_done + 8 * s, (tile / S) & 1u);
-            if (!ok) break;
-            const uint32_t row0 = n0 + tile * kTileRows;
-            const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
-            const float *rs = red + (tile & 1u) * red_slot_floats;
-            const __nv_bfloat16 *lb = reinterpret_cast<const __nv_bfloat16 *>(
-                stage_base + (size_t)s * p.stage_bytes + p.off_lora);
-            for (uint32_t idx = lane; idx < (uint32_t)kTileRows * MP; idx += 32) {
-                const uint32_t row = idx & 15u, m = idx >> 4;
-                if (m < p.M && row < rows) {
-                    float v = 0.0f;
-                    for (uint32_t w = 0; w < p.consumer_warps; ++w)
-                        v += rs[(w * kTileRows + row) * MP + m];
-                    if (p.rank) {
-                        float dot = 0.0f;
-                        for (uint32_t j = 0; j < p.rank; ++j)
-                            dot = fmaf(t_s[m * p.rank + j], __bfloat162float(lb[row * p.rank + j]),
-                                       dot);
-                        v = fmaf(dot, p.lora_scale, v);  // scale applied last
-                    }
-                    if (p.bias) v += __ldg(p.bias + row0 + row);
-                    const size_t o = (size_t)m * p.ldy + row0 + row;
-                    if (p.y_f32) static_cast<float *>(p.y)[o] = v;
-                    else static_cast<__nv_bfloat16 *>(p.y)[o] = __float2bfloat16_rn(v);
+    const float sos = DQ ? __ldg(p.scale_of_scales) : 0.0f;
+    // address of a table entry = table base (uniform) + {code byte in bits 8..15, lane * 4}
+    const uint32_t lane_off = lane * 4u;
+    auto lut_at = [&](uint32_t word, int byte) -> uint32_t {
+        const uint32_t off = __byte_perm(word, lane_off, 0x6604u | ((uint32_t)byte << 4));
+        return *reinterpret_cast<const uint32_t *>(smem + off);
+    };
+    const uint32_t slot_floats = p.red_slot_bytes / 4;
+    const uint32_t first_pass_last = min(ntiles, p.pass_tiles) - 1;
+
+    float acc[PT][NT][4];
+    #pragma unroll
+    for (int q = 0; q < PT; ++q) {
+        #pragma unroll
+        for (int u = 0; u < NT; ++u) acc[q][u][0] = acc[q][u][1] = acc[q][u][2] = acc[q][u][3] = 0.0f;
+    }
+    uint32_t pass_tile0 = 0;
+
+    // One copy of the tile code; the accumulators work as a shift register: the tile being
+    // multiplied is acc[0], older tiles of the pass move up.  The stream runs ahead across
+    // pass boundaries.
+    #pragma unroll 1
+    for (uint32_t tile = 0; tile < ntiles; ++tile) {
+        if (active) {
+            #pragma unroll
+            for (int q = PT - 1; q > 0; --q) {
+                #pragma unroll
+                for (int u = 0; u < NT; ++u) {
+                    #pragma unroll
+                    for (int r = 0; r < 4; ++r) acc[q][u][r] = acc[q - 1][u][r];
                 }
             }
-            __syncwarp();
-            if (tile < 8) NF4_TS(6 + 3 * tile);
-            if (lane == 0) {
-                ptx::mbar_arrive(bar_red_free + 8 * (tile & 1u));
-                ptx::mbar_arrive(bar_epi_done + 8 * s);
+            #pragma unroll
+            for (int u = 0; u < NT; ++u) acc[0][u][0] = acc[0][u][1] = acc[0][u][2] = acc[0][u][3] = 0.0f;
+
+            // The adapter intermediate comes from the pre-pass, which has had most of the
+            // stream to finish: warp 0 asks for it one tile before it is needed.
+            if (warp == 0 && p.rank && tile == first_pass_last) {
+                ptx::pdl_wait();
+                for (uint32_t i = lane; i < p.M * p.rank; i += 32)
+                    ptx::cp_async_4(ptx::smem_addr(t_s + i), p.t + i);
+                ptx::cp_async_commit();
             }
-        }
-        NF4_TS(3);
-        if (!ok && lane == 0) atomicExch(&g_decode_error, 1);
-    } else if (warp < p.consumer_warps) {
-        // ========================= consumer warps =========================
-        const float sos = DQ ? __ldg(p.scale_of_scales) : 0.0f;
-
-        if (warp == 0) NF4_TS(2);
-        const uint32_t *lut_lane = lut + lane;
-        auto lut_at = [&](uint32_t word, int byte) -> uint32_t {
-            return lut_lane[((word >> (8 * byte)) & 0xffu) << 5];
-        };
-
-        bool ok = true;
-        for (uint32_t tile = 0; tile < ntiles; ++tile) {
-            const uint32_t s = tile % S;
-            ok = ptx::mbar_wait_bounded(bar_full + 8 * s, (tile / S) & 1u);
-            if (!ok) break;
+            // keep D tiles in flight, then wait for this one (groups retire in order)
+            __syncwarp();  // every lane is done reading the slot about to be refilled
+            if (tile + D < ntiles) request_tile(tile + D);
+            ptx::cp_async_commit();
+            wait_groups(D);
+            __syncwarp();  // the other lanes' pieces are visible too
             if (warp == 0 && tile < 8) NF4_TS(4 + 3 * tile);
-            const uint8_t *st = stage_base + (size_t)s * p.stage_bytes;
+            const uint8_t *st = ring + (size_t)(tile % R) * p.slot_bytes;
             const uint8_t *codes_lo = st + g * p.code_stride + t * 8;
             const uint8_t *codes_hi = codes_lo + 8 * p.code_stride;
-            const uint8_t *sc_lo = st + p.off_scales + g * p.scale_stride;
-            const uint8_t *sc_hi = sc_lo + 8 * p.scale_stride;
 
-            float acc[NT][4];
-            #pragma unroll
-            for (int u = 0; u < NT; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
+            float s_lo[kMaxChunksPerWarp], s_hi[kMaxChunksPerWarp];
+            if (p.vec_scales) {
+                if (DQ) {
+                    const uint32_t a = *reinterpret_cast<const uint32_t *>(st + p.off_scales + g * 4);
+                    const uint32_t b = *reinterpret_cast<const uint32_t *>(st + p.off_scales + (g + 8) * 4);
+                    #pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        s_lo[c] = dq_scale((a >> (8 * c)) & 0xffu, sos);
+                        s_hi[c] = dq_scale((b >> (8 * c)) & 0xffu, sos);
+                    }
+                } else {
+                    const float4 a = *reinterpret_cast<const float4 *>(st + p.off_scales + g * 16);
+                    const float4 b = *reinterpret_cast<const float4 *>(st + p.off_scales + (g + 8) * 16);
+                    s_lo[0] = a.x; s_lo[1] = a.y; s_lo[2] = a.z; s_lo[3] = a.w;
+                    s_hi[0] = b.x; s_hi[1] = b.y; s_hi[2] = b.z; s_hi[3] = b.w;
+                }
+            } else {
+                // odd slice widths: the scales come straight from global memory
+                const uint32_t r_lo = min(n0 + tile * kTileRows + g, n1 - 1);
+                const uint32_t r_hi = min(n0 + tile * kTileRows + g + 8, n1 - 1);
+                #pragma unroll
+                for (int c = 0; c < kMaxChunksPerWarp; ++c) {
+                    s_lo[c] = s_hi[c] = 0.0f;
+                    if (c < (int)my_chunks) {
+                        const size_t i_lo = (size_t)r_lo * nchunks + chunk0 + c;
+                        const size_t i_hi = (size_t)r_hi * nchunks + chunk0 + c;
+                        s_lo[c] = DQ ? dq_scale(__ldg(p.scale_codes + i_lo), sos) : __ldg(p.absmax + i_lo);
+                        s_hi[c] = DQ ? dq_scale(__ldg(p.scale_codes + i_hi), sos) : __ldg(p.absmax + i_hi);
+                    }
+                }
+            }
 
             #pragma unroll
             for (int c = 0; c < kMaxChunksPerWarp; ++c) {
-                const uint32_t kc = chunk0 + c;
-                if (c < (int)p.chunks_per_warp && kc < nchunks) {
-                    const uint2 w0 = *reinterpret_cast<const uint2 *>(codes_lo + kc * 32);
-                    const uint2 w1 = *reinterpret_cast<const uint2 *>(codes_hi + kc * 32);
-                    float s_lo, s_hi;
-                    if (DQ) {
-                        s_lo = dq_scale(sc_lo[kc], sos);
-                        s_hi = dq_scale(sc_hi[kc], sos);
-                    } else {
-                        s_lo = reinterpret_cast<const float *>(sc_lo)[kc];
-                        s_hi = reinterpret_cast<const float *>(sc_hi)[kc];
-                    }
-                    float blk[NT][4];
-                    #pragma unroll
-                    for (int u = 0; u < NT; ++u) blk[u][0] = blk[u][1] = blk[u][2] = blk[u][3] = 0.0f;
+                if (c < (int)my_chunks) {
+                    const uint2 w0 = *reinterpret_cast<const uint2 *>(codes_lo + c * 32);
+                    const uint2 w1 = *reinterpret_cast<const uint2 *>(codes_hi + c * 32);
+                    float blk[kAccs][NT][4];
                     #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint32_t x0 = (j < 2) ? w0.x : w0.y;
@@ -353,39 +339,115 @@ decode_kernel(const DecodeParams p) {
                         const uint32_t a0 = lut_at(x0, b), a1 = lut_at(x1, b);
                         const uint32_t a2 = lut_at(x0, b + 1), a3 = lut_at(x1, b + 1);
                         #pragma unroll
-                        for (int u = 0; u < NT; ++u)
-                            ptx::mma_16816_f16(blk[u], a0, a1, a2, a3, xf[u][c][j][0],
-                                               xf[u][c][j][1]);
+                        for (int u = 0; u < NT; ++u) {
+                            if (j < kAccs)
+                                ptx::mma_16816_f16_zero(blk[j][u], a0, a1, a2, a3, xf[u][c][j][0],
+                                                        xf[u][c][j][1]);
+                            else
+                                ptx::mma_16816_f16(blk[j % kAccs][u], a0, a1, a2, a3, xf[u][c][j][0],
+                                                   xf[u][c][j][1]);
+                        }
                     }
                     #pragma unroll
                     for (int u = 0; u < NT; ++u) {
-                        acc[u][0] = fmaf(blk[u][0], s_lo, acc[u][0]);
-                        acc[u][1] = fmaf(blk[u][1], s_lo, acc[u][1]);
-                        acc[u][2] = fmaf(blk[u][2], s_hi, acc[u][2]);
-                        acc[u][3] = fmaf(blk[u][3], s_hi, acc[u][3]);
+                        #pragma unroll
+                        for (int r = 0; r < 4; ++r)
+                            acc[0][u][r] = fmaf(blk[0][u][r] + blk[1][u][r], r < 2 ? s_lo[c] : s_hi[c],
+                                                acc[0][u][r]);
                     }
                 }
             }
             if (warp == 0 && tile < 8) NF4_TS(5 + 3 * tile);
-            // this warp's partial sums go to its own slice of the tile's reduction slot; the
-            // slot is free once the epilogue has summed the tile two before this one
-            if (tile >= 2) {
-                ok = ptx::mbar_wait_bounded(bar_red_free + 8 * (tile & 1u), ((tile >> 1) - 1) & 1u);
-                if (!ok) break;
-            }
-            float *rs = red + (tile & 1u) * red_slot_floats + warp * kTileRows * MP;
-            #pragma unroll
-            for (int u = 0; u < NT; ++u) {
-                *reinterpret_cast<float2 *>(rs + g * MP + 8 * u + 2 * t) =
-                    make_float2(acc[u][0], acc[u][1]);
-                *reinterpret_cast<float2 *>(rs + (g + 8) * MP + 8 * u + 2 * t) =
-                    make_float2(acc[u][2], acc[u][3]);
-            }
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar_done + 8 * s);
         }
-        if (!ok && lane == 0) atomicExch(&g_decode_error, 2);
+
+        const uint32_t tiles_in_pass = tile + 1 - pass_tile0;
+        if (tiles_in_pass < p.pass_tiles && tile + 1 < ntiles) continue;
+
+        // ================= end of a pass: reduce, finish and store its rows =================
+        // The reduction slots take the place of the lookup table, which is rebuilt afterwards
+        // if more tiles follow; the rings keep filling meanwhile.
+        if (warp == 0) NF4_TS(40);
+        __syncthreads();  // nobody reads the table any more
+        {
+            // acc[q] holds the pass's tile number (tiles_in_pass - 1 - q)
+            float *slot = red + warp * slot_floats;
+            #pragma unroll
+            for (int q = 0; q < PT; ++q) {
+                if (q < (int)tiles_in_pass) {
+                    const int ti = (int)tiles_in_pass - 1 - q;
+                    #pragma unroll
+                    for (int u = 0; u < NT; ++u) {
+                        #pragma unroll
+                        for (int r = 0; r < 4; ++r)
+                            slot[((ti * NT + u) * 4 + r) * 32 + lane] = acc[q][u][r];
+                    }
+                }
+            }
+        }
+        if (pass_tile0 == 0) {
+            // first pass only: the LoRA-B rows and T must have landed; at most one copy group
+            // (a tile's) is newer than T's
+            if (tile + 1 == ntiles) ptx::cp_async_wait<0>();
+            else ptx::cp_async_wait<1>();
+        }
+        __syncthreads();
+
+        // ---- everyone: sum the sixteen slots in order, + adapter, + bias, convert, store ----
+        // Thread o takes slot element o (conflict-free reads) and works out which output that
+        // is: element = ((tile * NT + u) * 4 + r) * 32 + source lane.
+        const uint32_t pass_row0 = n0 + pass_tile0 * kTileRows;
+        const uint32_t pass_rows = min(n1 - pass_row0, tiles_in_pass * (uint32_t)kTileRows);
+        for (uint32_t o = tid; o < tiles_in_pass * NT * 128u; o += kDecodeThreads) {
+            const uint32_t src_lane = o & 31u, r = (o >> 5) & 3u, tu = o >> 7;
+            const uint32_t ti = tu / NT, u = tu - ti * NT;
+            const uint32_t rr = ti * kTileRows + (r >> 1) * 8u + (src_lane >> 2);
+            const uint32_t m = u * 8u + (src_lane & 3u) * 2u + (r & 1u);
+            if (rr >= pass_rows || m >= p.M) continue;
+            float v = red[o];
+            #pragma unroll
+            for (int w = 1; w < kSlots; ++w) v += red[w * slot_floats + o];
+            if (p.rank) {
+                const __nv_bfloat16 *lb = lora_s + (size_t)(pass_row0 - n0 + rr) * p.rank;
+                const float *tm = t_s + m * p.rank;
+                float dot = 0.0f;
+                if ((p.rank & 7u) == 0) {
+                    for (uint32_t j = 0; j < p.rank; j += 8) {
+                        const uint4 bq = *reinterpret_cast<const uint4 *>(lb + j);
+                        const float4 t0 = *reinterpret_cast<const float4 *>(tm + j);
+                        const float4 t1 = *reinterpret_cast<const float4 *>(tm + j + 4);
+                        dot = fmaf(t0.x, bf16_bits_to_float(bq.x & 0xffffu), dot);
+                        dot = fmaf(t0.y, bf16_bits_to_float(bq.x >> 16), dot);
+                        dot = fmaf(t0.z, bf16_bits_to_float(bq.y & 0xffffu), dot);
+                        dot = fmaf(t0.w, bf16_bits_to_float(bq.y >> 16), dot);
+                        dot = fmaf(t1.x, bf16_bits_to_float(bq.z & 0xffffu), dot);
+                        dot = fmaf(t1.y, bf16_bits_to_float(bq.z >> 16), dot);
+                        dot = fmaf(t1.z, bf16_bits_to_float(bq.w & 0xffffu), dot);
+                        dot = fmaf(t1.w, bf16_bits_to_float(bq.w >> 16), dot);
+                    }
+                } else {
+                    for (uint32_t j = 0; j < p.rank; ++j) dot = fmaf(tm[j], __bfloat162float(lb[j]), dot);
+                }
+                v = fmaf(dot, p.lora_scale, v);  // scale applied last
+            }
+            if (p.bias) v += __ldg(p.bias + pass_row0 + rr);
+            const size_t at = (size_t)m * p.ldy + pass_row0 + rr;
+            if (p.y_f32) static_cast<float *>(p.y)[at] = v;
+            else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(v);
+        }
+        if (warp == 0) NF4_TS(41);
+        pass_tile0 = tile + 1;
+        if (pass_tile0 < ntiles) {
+            __syncthreads();  // the slots have been read
+            build_table();
+            __syncthreads();
+            #pragma unroll
+            for (int q = 0; q < PT; ++q) {
+                #pragma unroll
+                for (int u = 0; u < NT; ++u) acc[q][u][0] = acc[q][u][1] = acc[q][u][2] = acc[q][u][3] = 0.0f;
+            }
+        }
     }
+    ptx::cp_async_wait<0>();
 }
 
 // T[m][j] = sum_k x[m][k] * A[j][k]  (x, A bf16; f32 accumulate).  One CTA per (j, m).
@@ -433,8 +495,7 @@ uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &smem_bytes) {
     if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
     if (a.rows == 0 || a.rows > 16) return false;
-    if (a.d_in % kChunk != 0 || a.d_in > (uint64_t)kMaxConsumerWarps * kMaxChunksPerWarp * kChunk)
-        return false;
+    if (a.d_in % kChunk != 0 || a.d_in > (uint64_t)kWarps * kMaxChunksPerWarp * kChunk) return false;
     if (a.d_out >= (1ull << 31)) return false;
     const bool dq = a.scale_codes != nullptr;
     const uint32_t rank = a.lora_a ? a.lora_rank : 0;
@@ -444,40 +505,45 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     if (rank && !aligned16(a.lora_b)) return false;
     if (reinterpret_cast<uintptr_t>(a.y) & (a.y_f32 ? 3u : 1u)) return false;
 
-    const uint32_t K = (uint32_t)a.d_in, N = (uint32_t)a.d_out;
+    const uint32_t K = (uint32_t)a.d_in, N = (uint32_t)a.d_out, M = (uint32_t)a.rows;
     const uint32_t nchunks = K / kChunk;
+    const uint32_t nt = M > 8 ? 2u : 1u;
     p = DecodeParams{};
-    p.scale_row_bytes = nchunks * (dq ? 1u : 4u);
-    uint32_t gran = 16u / gcd_u32(16u, p.scale_row_bytes);
-    if (rank) gran = lcm_u32(gran, 16u / gcd_u32(16u, rank * 2u));
+    // CTA row ranges start where the CTA's LoRA-B rows are 16-byte aligned
+    const uint32_t gran = rank ? 16u / gcd_u32(16u, rank * 2u) : 1u;
     if (N % gran != 0) return false;
     p.gran = gran;
-    p.chunks_per_warp = (nchunks + kMaxConsumerWarps - 1) / kMaxConsumerWarps;
-    p.consumer_warps = (nchunks + p.chunks_per_warp - 1) / p.chunks_per_warp;
-    p.code_stride = round_up(K / 2, 128) + 32;
-    p.scale_per_row = (p.scale_row_bytes % 16u == 0) ? 1u : 0u;
-    p.scale_stride = p.scale_per_row ? round_up(p.scale_row_bytes, 128) + 16 : p.scale_row_bytes;
+    p.chunks_per_warp = (nchunks + kWarps - 1) / kWarps;
+    p.vec_scales = (p.chunks_per_warp == 4 && nchunks % 4 == 0) ? 1u : 0u;
+    p.code_stride = p.chunks_per_warp * 32u + 32u;  // 160 for four chunks: conflict-free 64-bit reads
     p.off_scales = kTileRows * p.code_stride;
-    p.off_lora = round_up(p.off_scales + kTileRows * p.scale_stride, 128);
-    p.stage_bytes = round_up(p.off_lora + kTileRows * rank * 2u, 128);
+    p.slot_bytes = p.off_scales + kTileRows * 16u;
 
     const uint64_t units = N / gran;
     grid = (uint32_t)(units < (uint64_t)kNumSMs ? units : (uint64_t)kNumSMs);
     const uint32_t max_rows = (uint32_t)(((units + grid - 1) / grid) * gran);
     const uint32_t max_tiles = (max_rows + kTileRows - 1) / kTileRows;
-    const uint32_t mp = a.rows > 8 ? 16u : 8u;
-    const uint32_t fixed = kLutBytes + 256 + 16 * kMaxRank * 4;  // lut, barriers, T
-    const uint32_t red_bytes = 2u * p.consumer_warps * kTileRows * mp * 4u;  // two reduction slots
-    uint32_t stages = max_tiles < (uint32_t)kMaxStages ? max_tiles : (uint32_t)kMaxStages;
-    while (stages >= 1) {
-        p.off_red = fixed;
-        p.off_stages = round_up(p.off_red + red_bytes, 128);
-        smem_bytes = p.off_stages + stages * p.stage_bytes;
-        if (smem_bytes <= (uint32_t)kSmemLimit) break;
-        --stages;
-    }
-    if (stages == 0) return false;
-    p.stages = stages;
+    const uint32_t pt_max = nt == 1 ? (uint32_t)PassTiles<1>::value : (uint32_t)PassTiles<2>::value;
+    p.pass_tiles = max_tiles < pt_max ? max_tiles : pt_max;
+    p.red_slot_bytes = p.pass_tiles * nt * 512u;
+    p.lora_bytes_max = round_up(max_rows * rank * 2u, 128);
+    p.off_lora = kLutBytes + 16 * kMaxRank * 4;  // after the lookup table and T
+    p.off_rings = round_up(p.off_lora + p.lora_bytes_max, 128);
+    const uint32_t ring_unit = kWarps * p.slot_bytes;  // one tile of every warp
+    if (p.off_rings + 2 * ring_unit > (uint32_t)kSmemLimit) return false;
+    uint32_t ring = ((uint32_t)kSmemLimit - p.off_rings) / ring_unit;
+    if (ring > (uint32_t)kMaxRing) ring = kMaxRing;
+    if (ring > max_tiles + 1) ring = max_tiles + 1;  // no use for more
+    static const int ring_env = [] {
+        const char *e = std::getenv("NF4_DECODE_RING");  // experiment knob: tiles per warp ring
+        return e ? std::atoi(e) : 0;
+    }();
+    if (ring_env >= 2 && (uint32_t)ring_env < ring) ring = (uint32_t)ring_env;
+    if (ring < 2) ring = 2;
+    p.ring = ring;
+    if (kSlots * p.red_slot_bytes > (uint32_t)kLutBytes) return false;  // the slots reuse the table's room
+    smem_bytes = p.off_rings + ring * ring_unit;
+    if (smem_bytes > (uint32_t)kSmemLimit) return false;
     p.x = static_cast<const __nv_bfloat16 *>(a.x);
     p.codes = a.packed;
     p.absmax = a.absmax;
@@ -488,7 +554,7 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     p.y = a.y;
     p.y_f32 = (uint32_t)a.y_f32;
     p.ldy = a.ldy ? a.ldy : a.d_out;
-    p.M = (uint32_t)a.rows;
+    p.M = M;
     p.K = K;
     p.N = N;
     p.rank = rank;
@@ -505,7 +571,7 @@ int32_t launch(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaSt
         configured = true;
     }
     count_launch();
-    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3((p.consumer_warps + 2) * 32),
+    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3(kDecodeThreads),
                                    smem_bytes, stream, p.rank != 0 && pdl_enabled(), p);
 }
 
@@ -522,13 +588,14 @@ uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank) {
     return (rows * lora_rank * 4 + 255) / 256 * 256;
 }
 
+// `chained` launches the pre-pass as a programmatic dependent of the kernel ahead of it; the
+// kernel does not wait by itself, so callers pass false unless that kernel never writes x.
 int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, uint32_t rank,
-                     float *t_out, cudaStream_t stream) {
-    lora_t_kernel<<<dim3(rank, rows), 128, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x),
-                                                         static_cast<const __nv_bfloat16 *>(a), K,
-                                                         rank, t_out);
+                     float *t_out, cudaStream_t stream, bool chained) {
     count_launch();
-    return check_cuda(cudaGetLastError(), "lora_t_kernel launch");
+    return launch_maybe_overlapped(lora_t_kernel, dim3(rank, rows), dim3(128), 0, stream, chained,
+                                   static_cast<const __nv_bfloat16 *>(x),
+                                   static_cast<const __nv_bfloat16 *>(a), K, rank, t_out);
 }
 
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
@@ -537,7 +604,7 @@ int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
     if (!plan(a, p, grid, smem)) return fail(NF4_ERR_UNSUPPORTED, "decode_forward: unsupported shape");
     if (p.rank) {
         float *t = static_cast<float *>(a.workspace);
-        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream));
+        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream, false));
         p.t = t;
     }
     const bool dq = a.scale_codes != nullptr;
@@ -590,7 +657,7 @@ int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t str
     }
     if (p.rank) {
         float *t = static_cast<float *>(scratch);  // fully rewritten by the pre-pass: no clearing needed
-        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream));
+        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream, false));
         p.t = t;
     }
     const bool dq = a.scale_codes != nullptr;

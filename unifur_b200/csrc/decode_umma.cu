@@ -712,7 +712,7 @@ extern "C" __attribute__((visibility("default"))) int nf4_debug_decode2_timestam
 
 // lora_t_small lives in decode_gemv.cu
 int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, uint32_t rank,
-                     float *t_out, cudaStream_t stream);
+                     float *t_out, cudaStream_t stream, bool chained);
 
 bool decode2_supported(const nf4_linear_args &a) {
     if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
@@ -753,7 +753,7 @@ int32_t decode2_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.scale_of_scales = a.scale_of_scales;
     NF4_CUDA_TRY(cudaMemsetAsync(p.counters, 0, (size_t)p.row_tiles * 4, stream));
     if (p.rank) {
-        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream));
+        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream, false));
         p.t = t;
     }
     CUtensorMap mc, ms;

@@ -31,6 +31,8 @@ void count_launch(uint64_t n = 1);
 
 // ---- tables -----------------------------------------------------------------
 static __device__ __constant__ const uint32_t c_level_bits[16] = {NF4_LEVEL_BITS_LIST};
+// the same levels rounded to f16 (bit patterns)
+static __device__ __constant__ const uint32_t c_level_f16_bits[16] = {NF4_LEVEL_F16_BITS_LIST};
 static const uint32_t h_level_bits[16] = {NF4_LEVEL_BITS_LIST};
 static const uint32_t h_threshold_bits[15] = {NF4_THRESHOLD_BITS_LIST};
 

@@ -71,6 +71,30 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
         : "memory");
 }
 
+// ---- per-thread async copies global -> shared (LSU path, not TMA) -------------------
+// 16 bytes, L2 only (streaming data); both addresses 16-byte aligned.
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+// 4 bytes; both addresses 4-byte aligned.
+__device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// Blocks until at most N of this thread's committed groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Ask the L2 to fetch `bytes` (multiple of 16) from a 16-byte aligned global address; nothing
+// comes back to the SM.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // ---- tiled TMA ------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void *tmap, int32_t x,
                                             int32_t y, uint32_t bar) {
@@ -110,6 +134,16 @@ __device__ __forceinline__ void mma_16816_f16(float (&d)[4], uint32_t a0, uint32
         "{%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D = A * B (no accumulator input)
+__device__ __forceinline__ void mma_16816_f16_zero(float (&d)[4], uint32_t a0, uint32_t a1,
+                                                   uint32_t a2, uint32_t a3, uint32_t b0,
+                                                   uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 __device__ __forceinline__ void mma_16816_bf16(float (&d)[4], uint32_t a0, uint32_t a1,
                                                uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
