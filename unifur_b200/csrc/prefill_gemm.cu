@@ -1,20 +1,34 @@
 // Prefill path: y[M, N] = x * dequant(W)^T (+bias) (+ s * (x A^T) B^T) for many rows of x,
 // W stored as packed NF4 [N, K] with 64-blocks along K.  A dense contraction: tensor-core
-// bound, built on tcgen05.mma with the accumulator in tensor memory (TMEM).
+// bound, built on tcgen05.mma with both operands in shared memory and the accumulators in
+// tensor memory (TMEM).
 //
-// Roles inside one persistent CTA (one per SM, 448 threads):
+// Roles inside one persistent CTA (one per SM, 768 threads):
 //   warp 0      TMA producer: x tiles [256 rows x 64 k] (f16, 128B-swizzled, K-major) into a
-//               5-deep shared-memory ring; after the K loop the same ring carries the LoRA
+//               3-deep shared-memory ring; after the K loop the same ring carries the LoRA
 //               intermediate T (bf16 hi / lo halves) so the adapter is just more k-steps.
-//   warp 1      owns TMEM (alloc/dealloc) and issues every tcgen05.mma from one thread.
-//   warps 2-5   epilogue: TMEM -> registers -> (+bias) -> bf16/f32 -> shared -> TMA store.
-//   warps 6-13  dequantisers, two groups of 128 threads taking alternate k-stages.  A thread
-//               owns one weight row: it reads that row's 32 packed bytes and block scale
-//               straight from global memory (L2), expands the nibbles with byte-permute
-//               lookups held in registers, multiplies by the scale in f16x2 and writes the 64
-//               f16 values into its TMEM lane with tcgen05.st.  The MMA takes A (the weight
-//               tile, 128 rows) from TMEM and B (the activations) from shared memory, so the
-//               dequantised weight never touches shared memory.
+//   warp 1      owns TMEM (alloc/dealloc); one of its threads issues the tcgen05.mma of the even
+//               k-stages, one thread of warp 7 those of the odd ones.  Issuing a stage's MMAs
+//               holds the thread for about as long as they run, and ~400 cycles of waits,
+//               fences and commits separate two batches; with two threads the second has done
+//               its waiting while the first issues, and only a short hand-over is left.
+//   warp 6      idle.
+//   warps 2-5   epilogue: TMEM -> registers -> (* row scale, + bias) -> bf16/f32 -> shared ->
+//               TMA store.
+//   warps 8-23  dequantisers, two groups of 256 threads.  Two threads share one weight row of
+//               a stage: each reads 16 packed bytes and the block scale straight from global
+//               memory (L2), expands the nibbles with byte-permute lookups held in registers,
+//               multiplies by the scale in f16x2 and writes its 32 f16 values into the row's
+//               128B-swizzled place in the weight tile in shared memory.  (The expansion is a
+//               dependent chain of ~120 instructions per thread: it is the number of warps that
+//               hides its latency, so the work is cut fine.)
+//
+// Tile shapes.  A tile is one 128-row weight half against a 256-row activation tile, with the
+// accumulator double-buffered in TMEM so that the epilogue overlaps the next tile; the two
+// dequantiser groups take alternate k-stages.  A second shape (two halves per tile, one TMEM
+// accumulator and one dequantiser group each, eight MMAs per k-stage reading the activation
+// tile twice) is kept behind an environment switch for measurements: it halves the activation
+// bytes per flop but is slower, because the k-stage is bound by shared-memory traffic.
 //
 // The MMA computes D[n, m] = sum_k W[n, k] x[m, k]: weight rows are the MMA's M (TMEM lanes),
 // activation rows its N (256 accumulator columns).  Both operands are f16 with f32 accumulation:
@@ -27,6 +41,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -49,21 +64,25 @@ namespace {
 constexpr int BM = 128;        // weight rows per tile (MMA M, TMEM lanes)
 constexpr int BN = 256;        // activation rows per tile (MMA N, accumulator columns)
 constexpr int BK = 64;         // k per stage = one quantization block = one 128B swizzle row
-constexpr int kWStages = 3;    // shared-memory ring of dequantised weight tiles
-constexpr int kMaxXStages = 5; // shared-memory ring of activation tiles (5 with bf16 out, 4 with f32)
+constexpr int kHalves = 2;     // 128-row weight halves per tile on large problems
+constexpr int kWStages = 3;    // shared-memory ring of dequantised weight stages (kHalves tiles each)
+constexpr int kMaxXStages = 3; // shared-memory ring of activation tiles
 constexpr int kAccCols = BN;   // one accumulator; two of them fill the 512 TMEM columns
 constexpr int kTmemCols = 512;
 constexpr int kXTileBytes = BN * BK * 2;   // 32 KB: activations, written by TMA
 constexpr int kWTileBytes = BM * BK * 2;   // 16 KB: dequantised weights, written by the expanders
+constexpr int kWStageBytes = kHalves * kWTileBytes;
 
 constexpr int kEpiRows = 32;               // activation rows per epilogue chunk
-constexpr int kThreads = 14 * 32;
+constexpr int kThreads = 24 * 32;
+constexpr int kFirstExpanderWarp = 8;
+constexpr int kExpanderWarpsPerGroup = 8;
 constexpr uint32_t kSpin = 1u << 22;
 
 // barrier slots
 constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kMaxXStages, kBarWFull = kBarXEmpty + kMaxXStages,
               kBarWEmpty = kBarWFull + kWStages, kBarAccFull = kBarWEmpty + kWStages,
-              kBarAccEmpty = kBarAccFull + 2, kNumBars = kBarAccEmpty + 2;
+              kBarAccEmpty = kBarAccFull + 2, kBarIssued = kBarAccEmpty + 2, kNumBars = kBarIssued + 2;
 
 struct PrefillParams {
     const uint8_t *codes;
@@ -75,7 +94,8 @@ struct PrefillParams {
     const float *row_scale;       // [M] power-of-two factor each activation row was divided by
     uint32_t M, N, K, rank;
     uint32_t lora_chunks;  // ceil(rank / 64); T is [M][2 * 64 * lora_chunks] (hi halves, then lo)
-    uint32_t m_tiles, n_tiles;
+    uint32_t m_tiles, n_tiles;  // n_tiles counts groups of `halves` * 128 weight rows
+    uint32_t halves;            // 2: two 128-row halves per tile; 1: one, accumulator double-buffered
 };
 
 // ---- descriptors -----------------------------------------------------------------
@@ -172,26 +192,31 @@ __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
     return d;
 }
 
-// One stage of one weight row: 32 packed bytes + scale -> 32 registers of f16x2.
-__device__ __forceinline__ void expand_row(const LevelTables &t, const uint4 &c0, const uint4 &c1,
-                                           float scale, uint32_t (&out)[32]) {
+// Half a stage of one weight row: 16 packed bytes + scale -> 16 registers of f16x2.
+__device__ __forceinline__ void expand_half(const LevelTables &t, const uint4 &c, float scale,
+                                            uint32_t (&out)[16]) {
     const __half2 s2 = __float2half2_rn(scale);
     const uint32_t s = *reinterpret_cast<const uint32_t *>(&s2);
-    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+#ifdef NF4_PREFILL_FAKE_EXPAND  // measurement aid: what the stage costs without the expansion
     #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        uint32_t a, b, c, d;
+    for (int i = 0; i < 16; ++i) out[i] = w[i & 3] ^ s;
+    return;
+#endif
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t a, b, c2, d;
         expand4(t, w[i], a, b);
-        expand4(t, w[i] >> 16, c, d);
+        expand4(t, w[i] >> 16, c2, d);
         out[4 * i + 0] = hmul2(a, s);
         out[4 * i + 1] = hmul2(b, s);
-        out[4 * i + 2] = hmul2(c, s);
+        out[4 * i + 2] = hmul2(c2, s);
         out[4 * i + 3] = hmul2(d, s);
     }
 }
 
 struct RowStage {
-    uint4 c0, c1;  // the row's 64 packed codes of one k-stage
+    uint4 c;  // this thread's 32 packed codes of one k-stage
     float scale;
 };
 
@@ -203,10 +228,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     // 1024-byte alignment for the swizzled operand tiles
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int kXStages = YF32 ? 4 : 5;
+    constexpr int kXStages = kMaxXStages;
     uint8_t *x_ring = smem;                                   // kXStages activation tiles
-    uint8_t *w_ring = smem + kXStages * kXTileBytes;          // kWStages weight tiles
-    uint8_t *epi = w_ring + kWStages * kWTileBytes;           // 2 staging buffers
+    uint8_t *w_ring = smem + kXStages * kXTileBytes;          // kWStages weight stages
+    uint8_t *epi = w_ring + kWStages * kWStageBytes;          // 2 staging buffers
     constexpr int kEpiBufBytes = kEpiRows * BM * (YF32 ? 4 : 2);
     uint64_t *bars = reinterpret_cast<uint64_t *>(epi + 2 * kEpiBufBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
@@ -227,12 +252,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ptx::mbar_init(bar(kBarXEmpty + s), 1);
         }
         for (int s = 0; s < kWStages; ++s) {
-            ptx::mbar_init(bar(kBarWFull + s), 4);  // the four warps writing the tile
+            ptx::mbar_init(bar(kBarWFull + s), kExpanderWarpsPerGroup * p.halves);  // the warps writing the stage
             ptx::mbar_init(bar(kBarWEmpty + s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(bar(kBarAccFull + b), 1);
             ptx::mbar_init(bar(kBarAccEmpty + b), 4);
+            ptx::mbar_init(bar(kBarIssued + b), 1);
         }
         ptx::fence_mbar_init();
         ptx::fence_proxy_async();
@@ -277,26 +303,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             }
             if (!ok) atomicExch(&g_prefill_error, 1);
         }
-    } else if (warp == 1) {
-        // ============================= MMA issuer =============================
+    } else if (warp == 1 || warp == 7) {
+        // ============================= MMA issuers =============================
+        // Thread `me` (0: warp 1, 1: warp 7) issues the stages whose global counter has its
+        // parity.  Stage c may only be issued after stage c - 1 has been (hand-over barrier
+        // kBarIssued + parity of c - 1), which keeps the MMAs of an accumulator in order.
         if (lane == 0) {
+            const uint32_t me = warp == 1 ? 0u : 1u;
             constexpr uint32_t idesc_main = make_idesc(0, 0, BM, BN);  // f16 x f16
             constexpr uint32_t idesc_lora = make_idesc(1, 1, BM, BN);  // bf16 x bf16
             const uint32_t x_addr = ptx::smem_addr(x_ring), w_addr = ptx::smem_addr(w_ring);
             uint32_t cnt = 0;
             for (uint32_t i = 0; i < my_tiles && ok; ++i) {
-                const uint32_t buf = i & 1u, use = i >> 1;
-                // the epilogue must have drained this accumulator's previous tile
-                if (!ptx::mbar_wait_bounded(bar(kBarAccEmpty + buf), (use & 1u) ^ 1u, kSpin)) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after();
-                const uint32_t acc = tmem_base + buf * kAccCols;
+                // two halves: both accumulators belong to this tile; one half: they alternate
+                const uint32_t buf = p.halves == 2 ? 0u : (i & 1u), use = p.halves == 2 ? i : (i >> 1);
+                const uint32_t tile = blockIdx.x + i * gridDim.x;
+                const uint32_t n0 = (tile / p.m_tiles) * BM * p.halves;
+                const uint32_t halves_here = (p.halves == 2 && n0 + BM < p.N) ? 2u : 1u;
                 for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
+                    if ((cnt & 1u) != me) continue;
                     const uint32_t sx = cnt % kXStages, phx = (cnt / kXStages) & 1u;
                     const uint32_t sw = cnt % kWStages, phw = (cnt / kWStages) & 1u;
                     if (cnt >= 20 && cnt < 28) NF4_PTS(16 + 4 * (cnt - 20));
+                    // the epilogue must have drained this accumulator's previous tile
+                    if (ks == 0 &&
+                        !ptx::mbar_wait_bounded(bar(kBarAccEmpty + buf), (use & 1u) ^ 1u, kSpin)) {
+                        ok = false;
+                        break;
+                    }
                     if (!ptx::mbar_wait_bounded(bar(kBarXFull + sx), phx, kSpin)) {
                         ok = false;
                         break;
@@ -306,28 +340,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                         ok = false;
                         break;
                     }
+                    // hand-over: the other thread has issued stage cnt - 1 (its (cnt-1)/2-th)
+                    if (cnt > 0 &&
+                        !ptx::mbar_wait_bounded(bar(kBarIssued + (me ^ 1u)), ((cnt - 1) >> 1) & 1u, kSpin)) {
+                        ok = false;
+                        break;
+                    }
                     if (cnt >= 20 && cnt < 28) NF4_PTS(18 + 4 * (cnt - 20));
                     ptx::tc_fence_after();
                     const uint64_t bdesc = make_kmajor_sw128_desc(x_addr + sx * kXTileBytes);
-                    const uint64_t adesc = make_kmajor_sw128_desc(w_addr + sw * kWTileBytes);
-                    if (ks < k_stages) {
-                        // +32 bytes of K inside the swizzled row = +2 in the encoded address
-                        ptx::mma_ss_f16(acc, adesc, bdesc, idesc_main, ks != 0 ? 1u : 0u);
-                        ptx::mma_ss_f16(acc, adesc + 2, bdesc + 2, idesc_main, 1u);
-                        ptx::mma_ss_f16(acc, adesc + 4, bdesc + 4, idesc_main, 1u);
-                        ptx::mma_ss_f16(acc, adesc + 6, bdesc + 6, idesc_main, 1u);
-                    } else {
-                        const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
-                        const uint32_t left = p.rank - chunk * 64;
-                        const uint32_t nk16 = ((left < 64 ? left : 64) + 15) / 16;
-                        for (uint32_t j = 0; j < nk16; ++j)
-                            ptx::mma_ss_f16(acc, adesc + 2 * j, bdesc + 2 * j, idesc_lora, 1u);
+                    for (uint32_t h = 0; h < halves_here; ++h) {
+                        const uint32_t acc = tmem_base + (p.halves == 2 ? h : buf) * kAccCols;
+                        const uint64_t adesc =
+                            make_kmajor_sw128_desc(w_addr + sw * kWStageBytes + h * kWTileBytes);
+                        if (ks < k_stages) {
+                            // +32 bytes of K inside the swizzled row = +2 in the encoded address
+                            ptx::mma_ss_f16(acc, adesc, bdesc, idesc_main, ks != 0 ? 1u : 0u);
+                            ptx::mma_ss_f16(acc, adesc + 2, bdesc + 2, idesc_main, 1u);
+                            ptx::mma_ss_f16(acc, adesc + 4, bdesc + 4, idesc_main, 1u);
+                            ptx::mma_ss_f16(acc, adesc + 6, bdesc + 6, idesc_main, 1u);
+                        } else {
+                            const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
+                            const uint32_t left = p.rank - chunk * 64;
+                            const uint32_t nk16 = ((left < 64 ? left : 64) + 15) / 16;
+                            for (uint32_t j = 0; j < nk16; ++j)
+                                ptx::mma_ss_f16(acc, adesc + 2 * j, bdesc + 2 * j, idesc_lora, 1u);
+                        }
                     }
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(bar(kBarIssued + me));
                     ptx::tc_commit(bar(kBarXEmpty + sx));
                     ptx::tc_commit(bar(kBarWEmpty + sw));
+                    if (ks + 1 == stages_per_tile) ptx::tc_commit(bar(kBarAccFull + buf));
                     if (cnt >= 20 && cnt < 28) NF4_PTS(19 + 4 * (cnt - 20));
                 }
-                if (ok) ptx::tc_commit(bar(kBarAccFull + buf));
             }
             if (!ok) atomicExch(&g_prefill_error, 2);
         }
@@ -338,132 +384,181 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         const uint32_t epi_leader = (warp == 2 && lane == 0);
         for (uint32_t i = 0; i < my_tiles && ok; ++i) {
             const uint32_t tile = blockIdx.x + i * gridDim.x;
-            const uint32_t n0 = (tile / p.m_tiles) * BM, m0 = (tile % p.m_tiles) * BN;
-            const uint32_t n = n0 + row_in_tile;
-            const uint32_t buf = i & 1u, use = i >> 1;
-            const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+            const uint32_t n00 = (tile / p.m_tiles) * BM * p.halves, m0 = (tile % p.m_tiles) * BN;
+            const uint32_t buf = p.halves == 2 ? 0u : (i & 1u), use = p.halves == 2 ? i : (i >> 1);
+            const uint32_t halves_here = (p.halves == 2 && n00 + BM < p.N) ? 2u : 1u;
             ok = ptx::mbar_wait_bounded(bar(kBarAccFull + buf), use & 1u, kSpin);
             if (!ok) break;
             ptx::tc_fence_after();
-            const uint32_t acc = tmem_base + buf * kAccCols;
-            for (uint32_t c = 0; c < BN / kEpiRows; ++c) {
-                uint8_t *ebuf = epi + (c & 1u) * kEpiBufBytes;
-                // the TMA store that last read this buffer must be done with it
-                if (epi_leader) ptx::tma_store_wait_read<1>();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                uint32_t v[32];
-                tmem_ld32(acc + ((q * 32) << 16) + c * kEpiRows, v);
-                ptx::tmem_wait_ld();
-                if (c == BN / kEpiRows - 1) {
-                    // accumulator fully read: hand it back to the MMA warp
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty + buf));
-                }
-                // staging layout: [kEpiRows activation rows][BM weight rows]
-                #pragma unroll
-                for (int r = 0; r < 32; ++r) {
-                    const uint32_t m = m0 + c * kEpiRows + r;
-                    const float rs = m < p.M ? __ldg(p.row_scale + m) : 1.0f;
-                    const float f = fmaf(__uint_as_float(v[r]), rs, bias);
-                    if (YF32)
-                        reinterpret_cast<float *>(ebuf)[r * BM + row_in_tile] = f;
-                    else
-                        reinterpret_cast<__nv_bfloat16 *>(ebuf)[r * BM + row_in_tile] =
-                            __float2bfloat16_rn(f);
-                }
-                ptx::fence_proxy_async();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (epi_leader) {
-                    ptx::tma_store_2d(&tmap_y, ptx::smem_addr(ebuf), (int32_t)n0,
-                                      (int32_t)(m0 + c * kEpiRows));
-                    ptx::tma_store_commit();
+            for (uint32_t h = 0; h < halves_here; ++h) {
+                const uint32_t n0 = n00 + h * BM;
+                const uint32_t n = n0 + row_in_tile;
+                const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+                const uint32_t acc = tmem_base + (p.halves == 2 ? h : buf) * kAccCols;
+                for (uint32_t c = 0; c < BN / kEpiRows; ++c) {
+                    uint8_t *ebuf = epi + (c & 1u) * kEpiBufBytes;
+                    // the TMA store that last read this buffer must be done with it
+                    if (epi_leader) ptx::tma_store_wait_read<1>();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    uint32_t v[32];
+                    tmem_ld32(acc + ((q * 32) << 16) + c * kEpiRows, v);
+                    ptx::tmem_wait_ld();
+                    if (c == BN / kEpiRows - 1 && h + 1 == halves_here) {
+                        // accumulators fully read: hand them back to the MMA warp
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty + buf));
+                    }
+                    // staging layout: [kEpiRows activation rows][BM weight rows]
+                    #pragma unroll
+                    for (int r = 0; r < 32; ++r) {
+                        const uint32_t m = m0 + c * kEpiRows + r;
+                        const float rs = m < p.M ? __ldg(p.row_scale + m) : 1.0f;
+                        const float f = fmaf(__uint_as_float(v[r]), rs, bias);
+                        if (YF32)
+                            reinterpret_cast<float *>(ebuf)[r * BM + row_in_tile] = f;
+                        else
+                            reinterpret_cast<__nv_bfloat16 *>(ebuf)[r * BM + row_in_tile] =
+                                __float2bfloat16_rn(f);
+                    }
+                    ptx::fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (epi_leader) {
+                        ptx::tma_store_2d(&tmap_y, ptx::smem_addr(ebuf), (int32_t)n0,
+                                          (int32_t)(m0 + c * kEpiRows));
+                        ptx::tma_store_commit();
+                    }
                 }
             }
         }
         if (epi_leader) ptx::tma_store_wait<0>();
         if (!ok && lane == 0) atomicExch(&g_prefill_error, 3);
-    } else {
+    } else if (warp >= kFirstExpanderWarp) {
         // ============================ dequantisers ============================
-        // Two groups of 128 threads take alternate stages.  A thread owns one weight row of the
-        // tile: 32 packed bytes + one scale in, 64 f16 values out, written as eight 16-byte
-        // chunks at the 128B-swizzled positions the MMA's shared-memory descriptor expects.
-        const uint32_t group = (warp - 6) >> 2;           // 0 or 1: takes stages of that parity
-        const uint32_t row_in_tile = ((warp - 6) & 3u) * 32 + lane;
+        // Two groups of 256 threads: with two halves per tile each group owns a half and takes
+        // every stage; with one half they take alternate stages.  Two threads share a weight
+        // row: 16 packed bytes + the scale in, 32 f16 values out, written as four 16-byte chunks
+        // at the 128B-swizzled positions the MMA's shared-memory descriptor expects.
+        const uint32_t group = (warp - kFirstExpanderWarp) / kExpanderWarpsPerGroup;  // 0 or 1
+        const uint32_t half = p.halves == 2 ? group : 0u;
+        const uint32_t row_in_tile = ((warp - kFirstExpanderWarp) % kExpanderWarpsPerGroup) * 16 + (lane >> 1);
+        const uint32_t side = lane & 1u;  // which 32 of the row's 64 weights
         const LevelTables tables = make_level_tables();
         const float sos = p.scale_codes ? __ldg(p.scale_of_scales) : 0.0f;
         const uint32_t blocks_per_row = p.K / 64;
-        const uint64_t total = (uint64_t)my_tiles * stages_per_tile;
+        const uint32_t total = my_tiles * stages_per_tile;
         const uint32_t row_off = (row_in_tile >> 3) * 1024 + (row_in_tile & 7u) * 128;
         const uint32_t swz = row_in_tile & 7u;
 
-        auto fetch = [&](uint64_t cnt, RowStage &rs) {
-            rs.c0 = rs.c1 = make_uint4(0, 0, 0, 0);
-            rs.scale = 0.0f;
-            if (cnt >= total) return;
-            const uint32_t i = (uint32_t)(cnt / stages_per_tile), ks = (uint32_t)(cnt % stages_per_tile);
+        // Stage positions are walked, not divided out: a 64-bit division per stage costs more
+        // than the expansion itself.
+        struct Pos {
+            uint32_t cnt, i, ks, n;  // global stage counter, tile number, stage in tile, weight row
+        };
+        const uint32_t step = p.halves == 2 ? 1u : 2u;
+        auto row_of_tile = [&](uint32_t i) {
             const uint32_t tile = blockIdx.x + i * gridDim.x;
-            const uint32_t n = (tile / p.m_tiles) * BM + row_in_tile;
+            return (tile / p.m_tiles) * BM * p.halves + half * BM + row_in_tile;
+        };
+        auto advance = [&](Pos &q) {
+            q.cnt += step;
+            q.ks += step;
+            while (q.ks >= stages_per_tile) {
+                q.ks -= stages_per_tile;
+                ++q.i;
+                q.n = row_of_tile(q.i);
+            }
+        };
+        auto fetch = [&](const Pos &q, RowStage &rs) {
+            rs.c = make_uint4(0, 0, 0, 0);
+            rs.scale = 0.0f;
+            if (q.cnt >= total) return;
+            const uint32_t ks = q.ks, n = q.n;
             if (n >= p.N || ks >= k_stages) return;  // adapter stages are read when emitted
-            const uint4 *src = reinterpret_cast<const uint4 *>(
-                p.codes + (size_t)n * (p.K / 2) + (size_t)ks * 32);
-            rs.c0 = __ldg(src);
-            rs.c1 = __ldg(src + 1);
+#ifdef NF4_PREFILL_FAKE_FETCH  // measurement aid: what the stage costs without the global loads
+            rs.c = make_uint4(n, ks, n ^ ks, 7u);
+            rs.scale = 1.0f;
+            return;
+#endif
+            rs.c = __ldg(reinterpret_cast<const uint4 *>(
+                p.codes + (size_t)n * (p.K / 2) + (size_t)ks * 32 + side * 16));
             const size_t blk = (size_t)n * blocks_per_row + ks;
             rs.scale = p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos);
         };
-        auto emit = [&](uint64_t cnt, const RowStage &rs) -> bool {
-            const uint32_t i = (uint32_t)(cnt / stages_per_tile), ks = (uint32_t)(cnt % stages_per_tile);
-            const uint32_t s = (uint32_t)(cnt % kWStages), ph = (uint32_t)((cnt / kWStages) & 1u);
-            uint32_t out[32];
+        auto emit = [&](const Pos &q, const RowStage &rs) -> bool {
+            const uint32_t cnt = q.cnt, ks = q.ks;
+            const uint32_t s = cnt % kWStages, ph = (cnt / kWStages) & 1u;
+            uint32_t out[16];
             if (ks < k_stages) {
-                expand_row(tables, rs.c0, rs.c1, rs.scale, out);
+                expand_half(tables, rs.c, rs.scale, out);
             } else {
-                // one 64-wide chunk of this row of LoRA B (bf16 pairs), zero beyond the rank
-                const uint32_t tile = blockIdx.x + i * gridDim.x;
-                const uint32_t n = (tile / p.m_tiles) * BM + row_in_tile;
+                // this thread's half of one 64-wide chunk of this row of LoRA B (bf16 pairs),
+                // zero beyond the rank
+                const uint32_t n = q.n;
                 const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
                 const uint32_t left = p.rank - chunk * 64;
                 const uint16_t *src = reinterpret_cast<const uint16_t *>(p.lora_b) +
                                       (size_t)n * p.rank + chunk * 64;
                 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
+                for (int e = 0; e < 16; ++e) {
+                    const uint32_t col = side * 32 + 2 * e;
                     uint32_t lo = 0, hi = 0;
                     if (n < p.N) {
-                        if (2u * e < left) lo = __ldg(src + 2 * e);
-                        if (2u * e + 1 < left) hi = __ldg(src + 2 * e + 1);
+                        if (col < left) lo = __ldg(src + col);
+                        if (col + 1 < left) hi = __ldg(src + col + 1);
                     }
                     out[e] = lo | (hi << 16);
                 }
             }
-            if ((warp == 6 || warp == 10) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(64 + 4 * (cnt - 20));
+            if ((warp == 8 || warp == 16) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(64 + 4 * (cnt - 20));
             if (!ptx::mbar_wait_bounded(bar(kBarWEmpty + s), ph ^ 1u, kSpin)) return false;
-            if ((warp == 6 || warp == 10) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(65 + 4 * (cnt - 20));
-            uint8_t *wrow = w_ring + s * kWTileBytes + row_off;
+            if ((warp == 8 || warp == 16) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(65 + 4 * (cnt - 20));
+            uint8_t *wrow = w_ring + s * kWStageBytes + half * kWTileBytes + row_off;
             #pragma unroll
-            for (uint32_t c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4 *>(wrow + ((c ^ swz) << 4)) =
+            for (uint32_t c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4 *>(wrow + (((side * 4 + c) ^ swz) << 4)) =
                     make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
             ptx::fence_proxy_async();  // the tensor core reads this tile through the async proxy
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(kBarWFull + s));
-            if ((warp == 6 || warp == 10) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(66 + 4 * (cnt - 20));
+            if ((warp == 8 || warp == 16) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(66 + 4 * (cnt - 20));
             return true;
         };
 
-        // two-deep software pipeline over this group's stages (global stage counters
-        // group, group + 2, group + 4, ...)
-        RowStage r0, r1;
-        fetch(group, r0);
-        fetch(group + 2, r1);
-        for (uint64_t cnt = group; cnt < total && ok; cnt += 4) {
-            ok = emit(cnt, r0);
-            if (!ok) break;
-            fetch(cnt + 4, r0);
-            if (cnt + 2 < total) {
-                ok = emit(cnt + 2, r1);
-                if (!ok) break;
-                fetch(cnt + 6, r1);
+        // four-deep software pipeline over this group's stages (the loads of a stage are in
+        // flight for three emits): every stage with two halves, stages group, group + 2,
+        // group + 4, ... with one
+        constexpr int kDepth = 4;
+        Pos pe{0, 0, 0, row_of_tile(0)};
+        if (p.halves != 2 && group) {  // the second group starts one stage in
+            pe.cnt = 1;
+            pe.ks = 1;
+            while (pe.ks >= stages_per_tile) {
+                pe.ks -= stages_per_tile;
+                ++pe.i;
+                pe.n = row_of_tile(pe.i);
+            }
+        }
+        Pos pf = pe;
+        RowStage rs[kDepth];
+        #pragma unroll
+        for (int d = 0; d < kDepth; ++d) {
+            fetch(pf, rs[d]);
+            advance(pf);
+        }
+        while (pe.cnt < total && ok) {
+            #pragma unroll
+            for (int d = 0; d < kDepth; ++d) {
+                if (ok && pe.cnt < total) {
+                    ok = emit(pe, rs[d]);
+                    advance(pe);
+                    fetch(pf, rs[d]);
+                    advance(pf);
+#ifdef NF4_PREFILL_TIMING
+                    if ((warp == 8 || warp == 16) && lane == 0 && pe.cnt - step >= 20 && pe.cnt - step < 28)
+                        NF4_PTS(67 + 4 * (pe.cnt - step - 20));
+#endif
+                }
             }
         }
         if (!ok && lane == 0) atomicExch(&g_prefill_error, 4);
@@ -687,7 +782,16 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.rank = a.lora_a ? a.lora_rank : 0;
     p.lora_chunks = lora_chunks_of(p.rank);
     p.m_tiles = (p.M + BN - 1) / BN;
-    p.n_tiles = (p.N + BM - 1) / BM;
+    // One 128-row half per tile by default.  Two halves per tile (NF4_PREFILL_HALVES=2) halve the
+    // activation bytes per flop, but on B200 the k-stage is bound by shared-memory traffic (MMA
+    // operand reads + TMA writes + dequantiser stores), not by the activation stream: measured
+    // 547 against 601 TFLOP/s on the 2048 x 14336 x 4096 shape.
+    static const int halves_env = [] {
+        const char *e = std::getenv("NF4_PREFILL_HALVES");  // measurement knob: 1 or 2
+        return e ? std::atoi(e) : 0;
+    }();
+    p.halves = halves_env == 2 ? 2u : 1u;
+    p.n_tiles = (p.N + BM * p.halves - 1) / (BM * p.halves);
     const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
 
     const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.rank);
@@ -720,7 +824,7 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
 
     const uint32_t total_tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = total_tiles < (uint32_t)kNumSMs ? total_tiles : (uint32_t)kNumSMs;
-    const size_t smem = 1024 + (a.y_f32 ? 4 : 5) * kXTileBytes + kWStages * kWTileBytes +
+    const size_t smem = 1024 + kMaxXStages * kXTileBytes + kWStages * kWStageBytes +
                         2 * kEpiRows * BM * (a.y_f32 ? 4 : 2) +
                         kNumBars * 8 + 64;
     if (a.y_f32) {
