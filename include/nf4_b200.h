@@ -168,7 +168,9 @@ typedef struct nf4_linear_args {
     uint64_t workspace_bytes;
 } nf4_linear_args;
 
-/* Scratch the forward needs for these sizes (the LoRA intermediate x*A^T). */
+/* Scratch the forward needs for these sizes: the LoRA intermediate x*A^T, and for more than 16
+ * rows the f16 copy of x with its per-row power-of-two scales that the tensor-core kernel reads;
+ * for at most 16 rows also split-K partial sums when d_in exceeds 4096. */
 NF4_API uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                     uint32_t lora_rank);
 

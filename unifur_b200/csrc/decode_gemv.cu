@@ -4,9 +4,11 @@
 //
 // Data movement.  One CTA per SM owns a contiguous range of W rows; its sixteen warps split K
 // (up to four 64-blocks each).  Every warp streams its own slice -- 16 rows x 128 bytes of
-// nibbles plus the 16 x 4 block scales per tile -- global -> shared with per-thread 16-byte
-// asynchronous copies (cp.async, L2 only) into a private ring of a few tiles, rows on a padded
-// stride so that the reads are bank-conflict free.  The warps therefore share no barrier while
+// nibbles per tile -- global -> shared with per-thread 16-byte asynchronous copies (cp.async,
+// L2 only) into a private ring of a few tiles, rows on a padded stride so that the reads are
+// bank-conflict free.  The block scales of all the CTA's rows are fetched once, whole lines at
+// a time, at kernel start (fetched per warp and tile they cost one load/store-unit tag per
+// 16 bytes, as many as the nibbles themselves, and that unit is the busiest in the kernel).  The warps therefore share no barrier while
 // the weights stream.  (A first version moved whole tiles with TMA bulk copies; measured on
 // B200 that path delivered ~13-20 bytes per clock per SM from DRAM however many tiles were
 // requested ahead, about half of what the copy engines of all SMs need to saturate HBM, so the
@@ -14,9 +16,10 @@
 //
 // Math.  Dequantisation is a shared-memory table lookup: one packed byte (two codes)
 // indexes a 256-entry table of half2 {level[lo], level[hi]}, replicated once per
-// lane so that no two lanes share a bank; entries sit 256 bytes apart so that one byte
-// permute (code byte into bits 8..15, lane offset below) forms the address.  The looked-up
-// register IS the A operand of
+// lane so that no two lanes share a bank; entries sit 256 bytes apart and the table starts at
+// shared-window address 0x10000, so that one byte permute (code byte into bits 8..15, lane
+// offset below, the constant 0x0001 above) forms the whole address: two instructions per pair
+// of weights.  The looked-up register IS the A operand of
 // a warp MMA (m16n8k16, f16 in / f32 accumulate), with W rows on the MMA's M side and
 // the <=16 activation rows on its N side.  Each warp keeps its slice of x as f16 B-fragments
 // in registers for the whole kernel.  A block's four MMAs form two short chains, are
@@ -57,6 +60,7 @@ constexpr int kTileRows = 16;
 constexpr int kChunk = 64;           // one quantization block of K
 constexpr int kMaxChunksPerWarp = 4; // x fragments live in registers: K <= 16*4*64
 constexpr int kMaxRing = 6;          // tiles per warp ring (one being read, the rest in flight)
+constexpr uint32_t kLutWindow = 0x10000;  // shared-window address of the lookup table
 constexpr int kLutStride = 256;      // bytes between table entries (128 used)
 constexpr int kLutBytes = 256 * kLutStride;
 constexpr int kMaxRank = 64;
@@ -85,11 +89,12 @@ struct DecodeParams {
     uint32_t ring;            // tiles per warp ring
     uint32_t pass_tiles;      // tiles per reduction pass (<= PassTiles<NT>)
     uint32_t code_stride;     // bytes between rows of a warp's nibbles in shared memory
-    uint32_t slot_bytes;      // one tile of one warp: nibbles, then scales
-    uint32_t off_scales;      // offset of the scales inside a slot
-    uint32_t vec_scales;      // scales travel with the tile (else they are read from global)
+    uint32_t slot_bytes;      // one tile of one warp: its nibbles
+    uint32_t vec_scales;      // the CTA's scales are staged in shared memory (else read from global)
+    uint32_t scale_stride;    // bytes between rows of staged scales (padded)
+    uint32_t scale_bytes_max; // room for them
     uint32_t lora_bytes_max;  // room for the CTA's LoRA-B rows
-    uint32_t off_lora, off_rings;  // offsets inside dynamic shared memory (reduction slots alias the table)
+    uint32_t smem_bytes;      // dynamic shared memory of the launch (the kernel lays it out itself)
     uint32_t red_slot_bytes;
 };
 
@@ -128,17 +133,36 @@ __device__ __forceinline__ void wait_groups(uint32_t n) {
 template <int NT, bool DQ>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_kernel(const DecodeParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    float *t_s = reinterpret_cast<float *>(smem + kLutBytes);  // [M][rank]
-    uint8_t *lora_raw = smem + p.off_lora;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // Layout by shared-window address: [start, 0x10000) rings of the first warps |
+    // [0x10000, 0x20000) lookup table | [0x20000, ...) T, LoRA-B rows, rings of the other warps.
+    const uint32_t win0 = ptx::smem_addr(smem_raw);
+    uint8_t *smem = smem_raw + (kLutWindow - win0);  // generic pointer to the table
+    uint8_t *high = smem + kLutBytes;
+    float *t_s = reinterpret_cast<float *>(high);  // [M][rank]
+    uint64_t *scale_bar = reinterpret_cast<uint64_t *>(high + 16 * kMaxRank * 4);  // scales have landed
+    uint8_t *lora_raw = high + 16 * kMaxRank * 4 + 128;
     const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(lora_raw);
     float *red = reinterpret_cast<float *>(smem);  // the reduction slots take the lookup table's place
     constexpr int PT = PassTiles<NT>::value;
     constexpr int kAccs = 2;  // a block's four MMAs run as two chains of two
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    uint8_t *ring = smem + p.off_rings + (size_t)warp * p.ring * p.slot_bytes;
+    const uint32_t ring_bytes = p.ring * p.slot_bytes;
+    const uint32_t low_room = win0 < kLutWindow ? ((kLutWindow - win0) & ~127u) : 0u;
+    const uint32_t low_warps = min((uint32_t)kWarps, low_room / ring_bytes);
+    const uint32_t high_used = 16 * kMaxRank * 4 + 128 + p.lora_bytes_max + p.scale_bytes_max +
+                               (kWarps - low_warps) * ring_bytes;
+    if (win0 > kLutWindow || kLutWindow + kLutBytes + high_used > win0 + p.smem_bytes) {
+        if (threadIdx.x == 0) atomicExch(&g_decode_error, 4);  // the launch gave too little room
+        return;
+    }
+    uint8_t *ring = warp < low_warps
+                        ? smem - low_room + (size_t)warp * ring_bytes
+                        : lora_raw + p.lora_bytes_max + p.scale_bytes_max +
+                              (size_t)(warp - low_warps) * ring_bytes;
     const uint32_t ring_addr = ptx::smem_addr(ring);
+    uint8_t *scale_raw = lora_raw + p.lora_bytes_max;  // [rows of the CTA][scale_stride]
     const uint32_t R = p.ring, D = R - 1;  // D tiles in flight while one is read
 
     // rows owned by this CTA: units of `gran` rows, split evenly over the grid
@@ -158,24 +182,29 @@ decode_kernel(const DecodeParams p) {
     // Ask for one tile of this warp's slice: 16 rows x (32 bytes per chunk) of nibbles in
     // 16-byte pieces, then the rows' scales.  Rows past the CTA's range are left as they are:
     // their products land in accumulator rows that are never stored.
+    // four-chunk slices: lane l copies piece (l & 7) of rows (l >> 3) + 4 i, i = 0..3
+    const uint32_t lane_dst = (lane >> 3) * p.code_stride + (lane & 7u) * 16u;
+    const uint8_t *lane_src = p.codes + (size_t)(n0 + (lane >> 3)) * code_row_bytes + chunk0 * 32u +
+                              (lane & 7u) * 16u;
     auto request_tile = [&](uint32_t tile) {
         const uint32_t row0 = n0 + tile * kTileRows;
         const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
         const uint32_t slot = ring_addr + (tile % R) * p.slot_bytes;
+        if (p.vec_scales) {
+            const uint8_t *src = lane_src + (size_t)tile * (kTileRows * code_row_bytes);
+            #pragma unroll
+            for (uint32_t i = 0; i < 4; ++i)
+                if ((lane >> 3) + 4 * i < rows)
+                    ptx::cp_async_16(slot + lane_dst + i * 4u * p.code_stride,
+                                     src + (size_t)i * 4u * code_row_bytes);
+            return;
+        }
         const uint32_t pieces_per_row = my_chunks * 2u;
         const uint8_t *src0 = p.codes + (size_t)row0 * code_row_bytes + chunk0 * 32u;
         for (uint32_t q = lane; q < rows * pieces_per_row; q += 32) {
             const uint32_t row = q / pieces_per_row, piece = q - row * pieces_per_row;
             ptx::cp_async_16(slot + row * p.code_stride + piece * 16u,
                              src0 + (size_t)row * code_row_bytes + piece * 16u);
-        }
-        if (p.vec_scales && lane < rows) {
-            if (DQ)
-                ptx::cp_async_4(slot + p.off_scales + lane * 4u,
-                                p.scale_codes + (size_t)(row0 + lane) * nchunks + chunk0);
-            else
-                ptx::cp_async_16(slot + p.off_scales + lane * 16u,
-                                 p.absmax + (size_t)(row0 + lane) * nchunks + chunk0);
         }
     };
 
@@ -200,7 +229,29 @@ decode_kernel(const DecodeParams p) {
             }
         }
 
-        // ---- the CTA's LoRA-B rows and the first tiles of the stream ----
+        // ---- the CTA's block scales (whole rows), its LoRA-B rows and the first tiles ----
+        if (tid == 0) {
+            ptx::mbar_init(ptx::smem_addr(scale_bar), kDecodeThreads);
+            ptx::fence_mbar_init();
+        }
+        if (p.vec_scales) {
+            const uint32_t rows_cta = n1 - n0;
+            if (DQ) {
+                const uint32_t ppr = nchunks / 4;  // 4-byte pieces per row
+                for (uint32_t q = tid; q < rows_cta * ppr; q += kDecodeThreads) {
+                    const uint32_t row = q / ppr, pc = q - row * ppr;
+                    ptx::cp_async_4(ptx::smem_addr(scale_raw) + row * p.scale_stride + pc * 4u,
+                                    p.scale_codes + (size_t)(n0 + row) * nchunks + pc * 4u);
+                }
+            } else {
+                const uint32_t ppr = nchunks / 4;  // 16-byte pieces per row
+                for (uint32_t q = tid; q < rows_cta * ppr; q += kDecodeThreads) {
+                    const uint32_t row = q / ppr, pc = q - row * ppr;
+                    ptx::cp_async_16(ptx::smem_addr(scale_raw) + row * p.scale_stride + pc * 16u,
+                                     p.absmax + (size_t)(n0 + row) * nchunks + pc * 4u);
+                }
+            }
+        }
         if (p.rank) {
             const uint32_t pieces = (n1 - n0) * p.rank * 2u / 16u;
             const uint8_t *src = reinterpret_cast<const uint8_t *>(p.lora_b + (size_t)n0 * p.rank);
@@ -237,14 +288,18 @@ decode_kernel(const DecodeParams p) {
     build_table();
     if (warp == 0) NF4_TS(50);
     __syncthreads();
+    // every thread's scale pieces report to one barrier when they land (no wait here)
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(ptx::smem_addr(scale_bar)) : "memory");
     if (warp == 0) NF4_TS(1);
 
     const float sos = DQ ? __ldg(p.scale_of_scales) : 0.0f;
-    // address of a table entry = table base (uniform) + {code byte in bits 8..15, lane * 4}
-    const uint32_t lane_off = lane * 4u;
+    // shared-window address of a table entry = {0x0001, code byte, lane * 4}
+    const uint32_t lane_word = kLutWindow | (lane * 4u);
     auto lut_at = [&](uint32_t word, int byte) -> uint32_t {
-        const uint32_t off = __byte_perm(word, lane_off, 0x6604u | ((uint32_t)byte << 4));
-        return *reinterpret_cast<const uint32_t *>(smem + off);
+        const uint32_t addr = __byte_perm(word, lane_word, 0x7604u | ((uint32_t)byte << 4));
+        uint32_t v;
+        asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+        return v;
     };
     const uint32_t slot_floats = p.red_slot_bytes / 4;
     const uint32_t first_pass_last = min(ntiles, p.pass_tiles) - 1;
@@ -286,6 +341,7 @@ decode_kernel(const DecodeParams p) {
             __syncwarp();  // every lane is done reading the slot about to be refilled
             if (tile + D < ntiles) request_tile(tile + D);
             ptx::cp_async_commit();
+            if (warp == 0 && tile < 8) NF4_TS(42 + tile);
             wait_groups(D);
             __syncwarp();  // the other lanes' pieces are visible too
             if (warp == 0 && tile < 8) NF4_TS(4 + 3 * tile);
@@ -295,17 +351,21 @@ decode_kernel(const DecodeParams p) {
 
             float s_lo[kMaxChunksPerWarp], s_hi[kMaxChunksPerWarp];
             if (p.vec_scales) {
+                if (tile == 0 && !ptx::mbar_wait_bounded(ptx::smem_addr(scale_bar), 0)) {
+                    if (lane == 0) atomicExch(&g_decode_error, 5);
+                }
+                const uint8_t *sc = scale_raw + (size_t)(tile * kTileRows + g) * p.scale_stride;
                 if (DQ) {
-                    const uint32_t a = *reinterpret_cast<const uint32_t *>(st + p.off_scales + g * 4);
-                    const uint32_t b = *reinterpret_cast<const uint32_t *>(st + p.off_scales + (g + 8) * 4);
+                    const uint32_t a = *reinterpret_cast<const uint32_t *>(sc + chunk0);
+                    const uint32_t b = *reinterpret_cast<const uint32_t *>(sc + 8 * p.scale_stride + chunk0);
                     #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         s_lo[c] = dq_scale((a >> (8 * c)) & 0xffu, sos);
                         s_hi[c] = dq_scale((b >> (8 * c)) & 0xffu, sos);
                     }
                 } else {
-                    const float4 a = *reinterpret_cast<const float4 *>(st + p.off_scales + g * 16);
-                    const float4 b = *reinterpret_cast<const float4 *>(st + p.off_scales + (g + 8) * 16);
+                    const float4 a = *reinterpret_cast<const float4 *>(sc + chunk0 * 4);
+                    const float4 b = *reinterpret_cast<const float4 *>(sc + 8 * p.scale_stride + chunk0 * 4);
                     s_lo[0] = a.x; s_lo[1] = a.y; s_lo[2] = a.z; s_lo[3] = a.w;
                     s_hi[0] = b.x; s_hi[1] = b.y; s_hi[2] = b.z; s_hi[3] = b.w;
                 }
@@ -516,8 +576,7 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     p.chunks_per_warp = (nchunks + kWarps - 1) / kWarps;
     p.vec_scales = (p.chunks_per_warp == 4 && nchunks % 4 == 0) ? 1u : 0u;
     p.code_stride = p.chunks_per_warp * 32u + 32u;  // 160 for four chunks: conflict-free 64-bit reads
-    p.off_scales = kTileRows * p.code_stride;
-    p.slot_bytes = p.off_scales + kTileRows * 16u;
+    p.slot_bytes = kTileRows * p.code_stride;
 
     const uint64_t units = N / gran;
     grid = (uint32_t)(units < (uint64_t)kNumSMs ? units : (uint64_t)kNumSMs);
@@ -527,23 +586,37 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     p.pass_tiles = max_tiles < pt_max ? max_tiles : pt_max;
     p.red_slot_bytes = p.pass_tiles * nt * 512u;
     p.lora_bytes_max = round_up(max_rows * rank * 2u, 128);
-    p.off_lora = kLutBytes + 16 * kMaxRank * 4;  // after the lookup table and T
-    p.off_rings = round_up(p.off_lora + p.lora_bytes_max, 128);
-    const uint32_t ring_unit = kWarps * p.slot_bytes;  // one tile of every warp
-    if (p.off_rings + 2 * ring_unit > (uint32_t)kSmemLimit) return false;
-    uint32_t ring = ((uint32_t)kSmemLimit - p.off_rings) / ring_unit;
-    if (ring > (uint32_t)kMaxRing) ring = kMaxRing;
-    if (ring > max_tiles + 1) ring = max_tiles + 1;  // no use for more
+    // The kernel puts the table at shared-window address 0x10000 and the rings around it; with
+    // the usual 1 KB reserved at the start of the window that leaves 63 KB below and
+    // (227 - 127) KB above the table.
+    const uint32_t low_room = (kLutWindow - 1024u) & ~127u;
+    const uint32_t high_room = (uint32_t)kSmemLimit + 1024u - (kLutWindow + (uint32_t)kLutBytes);
+    p.scale_stride = nchunks * (dq ? 1u : 4u) + 16u;
+    p.scale_bytes_max = p.vec_scales ? round_up(max_tiles * kTileRows * p.scale_stride, 128) : 0u;
+    const uint32_t high_fixed = 16 * kMaxRank * 4 + 128 + p.lora_bytes_max + p.scale_bytes_max;
     static const int ring_env = [] {
         const char *e = std::getenv("NF4_DECODE_RING");  // experiment knob: tiles per warp ring
         return e ? std::atoi(e) : 0;
     }();
-    if (ring_env >= 2 && (uint32_t)ring_env < ring) ring = (uint32_t)ring_env;
-    if (ring < 2) ring = 2;
+    uint32_t ring = 0;
+    for (uint32_t r = 2; r <= (uint32_t)kMaxRing && r <= max_tiles + 1; ++r) {
+        const uint32_t ring_bytes = r * p.slot_bytes;
+        const uint32_t low_warps = low_room / ring_bytes < (uint32_t)kWarps ? low_room / ring_bytes : (uint32_t)kWarps;
+        if (high_fixed + (kWarps - low_warps) * ring_bytes > high_room) break;
+        if (ring_env >= 2 && r > (uint32_t)ring_env) break;
+        ring = r;
+    }
+    if (ring < 2) {
+        // a short matrix still needs two slots
+        const uint32_t ring_bytes = 2 * p.slot_bytes;
+        const uint32_t low_warps = low_room / ring_bytes < (uint32_t)kWarps ? low_room / ring_bytes : (uint32_t)kWarps;
+        if (high_fixed + (kWarps - low_warps) * ring_bytes > high_room) return false;
+        ring = 2;
+    }
     p.ring = ring;
     if (kSlots * p.red_slot_bytes > (uint32_t)kLutBytes) return false;  // the slots reuse the table's room
-    smem_bytes = p.off_rings + ring * ring_unit;
-    if (smem_bytes > (uint32_t)kSmemLimit) return false;
+    smem_bytes = kSmemLimit;
+    p.smem_bytes = smem_bytes;
     p.x = static_cast<const __nv_bfloat16 *>(a.x);
     p.codes = a.packed;
     p.absmax = a.absmax;

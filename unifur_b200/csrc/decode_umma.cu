@@ -1,10 +1,10 @@
 // Decode path, tcgen05 version: y[M<=16, N] = x * dequant(W)^T (+bias) (+ s * (x A^T) B^T) with
 // W packed NF4 [N, K], 64-blocks along K.  HBM-bound; every byte of W is read once.
 //
-// Why tcgen05 here: the legacy warp MMA (mma.sync) runs at about 1/16 of the tensor rate on
-// this part and bounded the first decode kernel at ~3 us per 16-row tile.  A 128 x 16 x 16
-// tcgen05.mma costs a handful of cycles, so the tensor work disappears and the kernel is left
-// with what it must do: stream nibbles and expand them.
+// Where it is used: shapes the warp-MMA decode kernel does not take (d_in above 4096, e.g. an
+// 18944-wide down projection).  Measured on B200, a tcgen05.mma whose A operand sits in TMEM
+// costs ~130-150 cycles whatever N is, so one MMA per 2048 weights bounds this kernel near
+// 10 us for the 11008 x 4096 layer; the warp-MMA kernel is faster wherever both apply.
 //
 // Work split.  The weight is cut into units of 128 rows x 128 k (two quantization blocks); the
 // units, in row-tile-major order, are dealt out in equal contiguous runs, one run per SM (a run
@@ -20,10 +20,11 @@
 // tile, block w / 4.  A thread owns one weight row: it reads the row's 32 packed bytes, looks
 // byte pairs up in a 256-entry half2 table replicated per lane (no bank conflicts), multiplies
 // by the block scale in f16x2 and writes the 64 f16 values into its TMEM lane (tcgen05.st).
-// One thread issues the MMAs: A = weight block from TMEM (128 rows), B = x from shared memory
-// (16 columns, rows >= M are zero), D = f32 accumulator in TMEM.
+// Four threads (one per block of a tile) issue the MMAs: A = weight block from TMEM (128 rows),
+// B = x from shared memory (16 columns, rows >= M are zero), D = f32 accumulators in TMEM (two
+// per issuer and segment, so consecutive MMAs of an issuer do not chain).
 //
-// Finish.  A segment that spans the whole K is finished in place (+bias, +LoRA, convert, store).
+// Finish (four warps).  A segment that spans the whole K is finished in place (+bias, +LoRA, convert, store).
 // Otherwise its 128 x 16 partial goes to a scratch slot; the last CTA to arrive for a row-tile
 // (one counter per row-tile) adds the slots in a fixed order and finishes the tile, so results
 // do not depend on timing.
