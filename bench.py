@@ -369,7 +369,10 @@ def run_own(args) -> None:
         "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
         "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
         "algorithmic_bytes_per_launch": STEP_BYTES // len(MS),
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum of decode_kernel from the committed ncu
+        # capture (profiles/decode_cfg2.md), mean of the M = 1, 4, 16 launches: the weights are
+        # read once, y stays in L2
+        "traffic": 25813248,
     }
 
     # ---- end to end through the host-pointer C ABI ------------------------------------------

@@ -126,6 +126,17 @@ NF4_API int32_t nf4_dequantize_unpacked_dev(const uint8_t *codes, uint64_t len, 
                                     const uint8_t *scale_codes, const float *scale_of_scales,
                                     float *out, void *stream);
 
+/* Rows of a packed [n_embedding, d_model] table selected by `ids` (int64, device memory),
+ * dequantized: out[t][j] = level[code] * block scale of element ids[t] * d_model + j, bit-exact
+ * with dequantizing the whole table and gathering.  Replaces the body of Nf4Embedding::forward,
+ * src/qwennet.rs:285-291, which rebuilds the whole f32 table on every call.  `out` is
+ * [n_ids, d_model] of out_dtype (NF4_DTYPE_F32, or NF4_DTYPE_BF16 = the f32 value rounded once).
+ * An id outside [0, n_embedding) gives a row of NaNs. */
+NF4_API int32_t nf4_embedding_gather_dev(const uint8_t *packed, const float *absmax,
+                                 const uint8_t *scale_codes, const float *scale_of_scales,
+                                 uint64_t n_embedding, uint64_t d_model, const int64_t *ids,
+                                 uint64_t n_ids, void *out, int32_t out_dtype, void *stream);
+
 /* Quantize then reconstruct in place of a weight: the error a frozen NF4 weight carries.
  * Replaces quantize_dequantize_tensor, src/quantize.rs:404-416 (and the body of
  * Nf4Quantizer::map_float, :469-493).  `workspace` must hold

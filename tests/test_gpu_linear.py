@@ -329,3 +329,47 @@ def test_prefill_linearity_at_full_config3_size(oracle):
     ref = x1[rows].double() @ deq.t() + 2.0 * (x1[rows].double() @ a.double().t()) @ b[:256].double().t()
     got = y1[rows, :256].double()
     assert ((got - ref).norm() / ref.norm()).item() < 1e-3 + 2.0 ** -9
+
+
+@pytest.mark.parametrize("layout_name,M,K,N,r", [("out_in", 8, 256, 192, 16), ("out_in", 40, 512, 320, 8),
+                                                 ("in_out", 6, 128, 96, 4)])
+def test_qlora_backward_matches_f64_reference(oracle, layout_name, M, K, N, r):
+    # Gradients with the NF4 base frozen (what the reference's autodiff sees through the detached
+    # weight, src/qwennet.rs:226-241): grad_x runs through the NF4 kernels on the same packed
+    # bytes in the other orientation, grad_a / grad_b are dense.  f32 activations: 1e-5.
+    from unifur_b200.quantize import PackedNf4Tensor
+    from unifur_b200.qwennet import Nf4Linear, QloraLinear
+
+    rng = np.random.default_rng(900 + M + K + N)
+    out_in = layout_name == "out_in"
+    w = (rng.standard_normal((N, K) if out_in else (K, N)) * 0.02).astype(np.float32)
+    packed, absmax = oracle.quantize_packed(w)
+    wd = oracle.dequantize_packed(packed, w.size, absmax).reshape(w.shape).astype(np.float64)
+    a = (rng.standard_normal((r, K) if out_in else (K, r)) * 0.1).astype(np.float32)
+    b = (rng.standard_normal((N, r) if out_in else (r, N)) * 0.1).astype(np.float32)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    gy = rng.standard_normal((M, N)).astype(np.float32)
+    s = 1.5
+    X, GY, A, B = (t.astype(np.float64) for t in (x, gy, a, b))
+    if out_in:
+        gx_ref = GY @ wd + s * (GY @ B) @ A
+        ga_ref = s * (GY @ B).T @ X
+        gb_ref = s * GY.T @ (X @ A.T)
+    else:
+        gx_ref = GY @ wd.T + s * (GY @ B.T) @ A.T
+        ga_ref = s * X.T @ (GY @ B.T)
+        gb_ref = s * (X @ A).T @ GY
+    lay = _lib.LAYOUT_OUT_IN if out_in else _lib.LAYOUT_IN_OUT
+    base = Nf4Linear(PackedNf4Tensor.quantize(torch.from_numpy(w.reshape(-1)).to(DEV)), K, N, None, lay)
+    q = QloraLinear(base, torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV), s)
+    gx, ga, gb = q.backward(torch.from_numpy(x).to(DEV), torch.from_numpy(gy).to(DEV))
+    assert rel_l2(gx.cpu().numpy(), gx_ref) <= REL_L2_F32
+    assert rel_l2(ga.cpu().numpy(), ga_ref) <= REL_L2_F32
+    assert rel_l2(gb.cpu().numpy(), gb_ref) <= REL_L2_F32
+    # and the forward it differentiates: finite differences along one direction
+    dx = rng.standard_normal((M, K)).astype(np.float32) * 1e-2
+    y0 = q.forward(torch.from_numpy(x).to(DEV)).double().cpu().numpy()
+    y1 = q.forward(torch.from_numpy(x + dx).to(DEV)).double().cpu().numpy()
+    lhs = float(np.sum((y1 - y0) * gy))
+    rhs = float(np.sum(gx.double().cpu().numpy() * dx))
+    assert abs(lhs - rhs) <= 1e-3 * max(abs(lhs), abs(rhs), 1e-6)

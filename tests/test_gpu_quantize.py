@@ -231,3 +231,36 @@ def test_encode_erase_nothing_decode_is_idempotent(oracle):
     gap = (lv[1:] - lv[:-1]).max()
     err = (d1 - w).view(nb, 64).abs()
     assert bool((err <= 0.5 * gap * a1[:, None] + 1e-6).all())
+
+
+@pytest.mark.parametrize("n_embedding,d_model,dq", [(1000, 64, True), (257, 136, True), (97, 100, False),
+                                                    (5000, 1024, True), (33, 7, False)])
+def test_embedding_gather_equals_dequantize_then_gather(oracle, n_embedding, d_model, dq):
+    # src/qwennet.rs:285-291 dequantizes the whole table and gathers; the kernel gathers and
+    # dequantizes only the selected rows.  Same values, bit for bit (blocks straddle rows when
+    # d_model is not a multiple of 64).
+    from unifur_b200.qwennet import Nf4Embedding
+    from unifur_b200.quantize import PackedNf4Tensor
+
+    rng = np.random.default_rng(n_embedding + d_model)
+    table = (rng.standard_normal(n_embedding * d_model) * 0.02).astype(np.float32)
+    packed, absmax = oracle.quantize_packed(table)
+    if dq:
+        sc, sos = oracle.double_quantize(absmax)
+        ref_table = oracle.dequantize_packed(packed, table.size, None, sc, sos)
+    else:
+        ref_table = oracle.dequantize_packed(packed, table.size, absmax)
+    ref_table = ref_table.reshape(n_embedding, d_model)
+    ids = rng.integers(0, n_embedding, size=(3, 41))
+    ids[0, 0], ids[2, 40] = 0, n_embedding - 1
+    pt = PackedNf4Tensor.quantize(torch.from_numpy(table).to(DEV))
+    if dq:
+        pt = pt.with_double_quantization()
+    emb = Nf4Embedding(pt, n_embedding, d_model)
+    got = emb.forward(torch.from_numpy(ids)).cpu().numpy()
+    assert got.shape == (3, 41, d_model)
+    assert bits_equal(got, ref_table[ids])
+    got16 = emb.forward(torch.from_numpy(ids), dtype=torch.bfloat16).float().cpu().numpy()
+    assert bits_equal(got16, oracle.round_bf16(ref_table[ids].astype(np.float32)))
+    bad = emb.forward(torch.tensor([[-1, n_embedding]]))
+    assert torch.isnan(bad).all()

@@ -221,6 +221,16 @@ int32_t nf4_dequantize_dev(const uint8_t *packed, uint64_t len, const float *abs
                              static_cast<cudaStream_t>(stream));
 }
 
+int32_t nf4_embedding_gather_dev(const uint8_t *packed, const float *absmax,
+                                 const uint8_t *scale_codes, const float *scale_of_scales,
+                                 uint64_t n_embedding, uint64_t d_model, const int64_t *ids,
+                                 uint64_t n_ids, void *out, int32_t out_dtype, void *stream) {
+    if (out_dtype != NF4_DTYPE_F32 && out_dtype != NF4_DTYPE_BF16)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_embedding_gather_dev: out_dtype must be NF4_DTYPE_F32 or NF4_DTYPE_BF16");
+    return embedding_gather(packed, absmax, scale_codes, scale_of_scales, n_embedding, d_model, ids,
+                            n_ids, out, out_dtype == NF4_DTYPE_BF16, static_cast<cudaStream_t>(stream));
+}
+
 int32_t nf4_dequantize_unpacked_dev(const uint8_t *codes, uint64_t len, const float *absmax,
                                     const uint8_t *scale_codes, const float *scale_of_scales,
                                     float *out, void *stream) {

@@ -35,6 +35,10 @@ int32_t dequantize_packed(const uint8_t *packed, uint64_t len, const float *absm
 int32_t dequantize_unpacked(const uint8_t *codes, uint64_t len, const float *absmax,
                             const uint8_t *scale_codes, const float *scale_of_scales, float *out,
                             cudaStream_t stream);
+int32_t embedding_gather(const uint8_t *packed, const float *absmax, const uint8_t *scale_codes,
+                         const float *scale_of_scales, uint64_t n_embedding, uint64_t d_model,
+                         const int64_t *ids, uint64_t n_ids, void *out, bool out_bf16,
+                         cudaStream_t stream);
 int32_t double_quantize(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
                         float *scale_of_scales, cudaStream_t stream);
 int32_t selfcheck_fast(uint64_t first_bits, uint64_t count, float absmax,

@@ -5,6 +5,8 @@
 // Layout: values and outputs are flat arrays; a thread owns 8 consecutive values
 // (one 32-byte sector of f32, one 32-bit word of nibbles), 8 lanes own one
 // 64-value block, a warp owns 4 blocks, and warps stride over the array.
+#include <cuda_bf16.h>
+
 #include "nf4_common.cuh"
 
 namespace nf4 {
@@ -207,6 +209,75 @@ dequantize_generic_kernel(const uint8_t *__restrict__ codes, uint64_t len, uint6
     }
 }
 
+// ---- embedding: gather rows of a packed table and dequantize them ---------------------
+// out[t][j] = level[code(ids[t] * d_model + j)] * scale(block of that element): the rows a batch
+// of token ids selects, without materialising the table.  Blocks run over the flat table, so
+// with d_model % 8 == 0 a group of eight consecutive elements of a row shares one 32-bit code
+// word and one block scale; other widths take the element-wise path.  An id outside
+// [0, n_embedding) yields a row of NaNs (the reference's gather would panic; a device kernel
+// must not trap).
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads)
+embedding_gather_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ absmax,
+                        const uint8_t *__restrict__ scale_codes,
+                        const float *__restrict__ scale_of_scales, uint64_t n_embedding,
+                        uint64_t d_model, const int64_t *__restrict__ ids, uint64_t n_ids,
+                        void *__restrict__ out) {
+    __shared__ float s_levels[16];
+    if (threadIdx.x < 16) s_levels[threadIdx.x] = __uint_as_float(c_level_bits[threadIdx.x]);
+    __syncthreads();
+    const float sos = scale_of_scales ? __ldg(scale_of_scales) : 0.0f;
+    const float nan = __uint_as_float(0x7fc00000u);
+    const uint64_t stride = (uint64_t)gridDim.x * kThreads;
+    const uint64_t first = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
+    if ((d_model & 7u) == 0) {
+        const uint64_t groups_per_row = d_model / 8, total = n_ids * groups_per_row;
+        for (uint64_t i = first; i < total; i += stride) {
+            const uint64_t t = i / groups_per_row, gi = i - t * groups_per_row;
+            const int64_t id = __ldg(ids + t);
+            float v[8];
+            if (id < 0 || (uint64_t)id >= n_embedding) {
+                #pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = nan;
+            } else {
+                const uint64_t e = (uint64_t)id * d_model + gi * 8;  // a multiple of 8
+                const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(codes) + e / 8);
+                const float sc = block_scale(absmax, scale_codes, sos, e / kBlock);
+                #pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = __fmul_rn(s_levels[(w >> (4 * k)) & 15u], sc);
+            }
+            if (BF16) {
+                uint32_t o[4];
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+                    o[k] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+            } else {
+                float4 *dst = reinterpret_cast<float4 *>(out) + 2 * i;
+                __stcs(dst, make_float4(v[0], v[1], v[2], v[3]));
+                __stcs(dst + 1, make_float4(v[4], v[5], v[6], v[7]));
+            }
+        }
+    } else {
+        const uint64_t total = n_ids * d_model;
+        for (uint64_t i = first; i < total; i += stride) {
+            const uint64_t t = i / d_model, j = i - t * d_model;
+            const int64_t id = __ldg(ids + t);
+            float v = nan;
+            if (id >= 0 && (uint64_t)id < n_embedding) {
+                const uint64_t e = (uint64_t)id * d_model + j;
+                const uint32_t byte = __ldg(codes + (e >> 1));
+                const uint32_t c = (e & 1u) ? (byte >> 4) : (byte & 15u);
+                v = __fmul_rn(__uint_as_float(c_level_bits[c]), block_scale(absmax, scale_codes, sos, e / kBlock));
+            }
+            if (BF16) reinterpret_cast<__nv_bfloat16 *>(out)[i] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float *>(out)[i] = v;
+        }
+    }
+}
+
 // ---- double quantization ------------------------------------------------------
 
 // Pass 1: max over the (non-negative, never-NaN) block scales.  Their f32 bit patterns
@@ -323,6 +394,29 @@ int32_t dequantize_unpacked(const uint8_t *codes, uint64_t len, const float *abs
                             const uint8_t *scale_codes, const float *scale_of_scales, float *out,
                             cudaStream_t stream) {
     return dequantize_impl<false>(codes, len, absmax, scale_codes, scale_of_scales, out, stream);
+}
+
+int32_t embedding_gather(const uint8_t *packed, const float *absmax, const uint8_t *scale_codes,
+                         const float *scale_of_scales, uint64_t n_embedding, uint64_t d_model,
+                         const int64_t *ids, uint64_t n_ids, void *out, bool out_bf16,
+                         cudaStream_t stream) {
+    if (n_ids == 0 || d_model == 0) return NF4_OK;
+    if (!packed || !ids || !out || (!absmax && !scale_codes))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_embedding_gather: null pointer");
+    if (scale_codes && !scale_of_scales)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_embedding_gather: scale_codes without scale_of_scales");
+    if ((d_model & 7u) == 0 && (!aligned16(out) || (reinterpret_cast<uintptr_t>(packed) & 3u)))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_embedding_gather: out must be 16-byte and packed 4-byte aligned");
+    const uint64_t work = (d_model & 7u) == 0 ? n_ids * (d_model / 8) : n_ids * d_model;
+    const int grid = grid_for(work, kThreads, 16);
+    if (out_bf16)
+        embedding_gather_kernel<true><<<grid, kThreads, 0, stream>>>(
+            packed, absmax, scale_codes, scale_of_scales, n_embedding, d_model, ids, n_ids, out);
+    else
+        embedding_gather_kernel<false><<<grid, kThreads, 0, stream>>>(
+            packed, absmax, scale_codes, scale_of_scales, n_embedding, d_model, ids, n_ids, out);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "nf4_embedding_gather launch");
 }
 
 int32_t double_quantize(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,

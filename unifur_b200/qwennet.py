@@ -1,7 +1,9 @@
 """Host-side mirror of the NF4-resident modules of the reference's ``src/qwennet.rs``
-(``Nf4Linear`` :168-242, ``QloraLinear`` :318-345, ``QwenLinear`` :305-435) over the C ABI."""
+(``Nf4Linear`` :168-242, ``Nf4Embedding`` :253-291, ``QloraLinear`` :318-345, ``QwenLinear``
+:305-435) over the C ABI."""
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -86,6 +88,33 @@ class QloraLinear:
                               self.base.layout, bias=self.base.bias, lora_a=self.lora_a,
                               lora_b=self.lora_b, lora_scale=self.scaling)
 
+    def backward(self, x: torch.Tensor, grad_y: torch.Tensor):
+        """Gradients of ``forward`` with the base weight frozen, as the reference's autodiff sees
+        the detached NF4 weight (src/qwennet.rs:226-241, used by src/qwentrain.rs:421-470):
+        returns ``(grad_x, grad_a, grad_b)`` with the shapes of ``x``, ``lora_a``, ``lora_b``.
+
+        ``grad_x = grad_y . W + s (grad_y . B) . A`` is one more NF4 linear over the SAME packed
+        bytes read in the other orientation (a ``[d_out, d_in]`` weight is a ``[d_in', d_out']``
+        weight with ``d_in' = d_out``), with the adapter factors swapping roles; the two adapter
+        gradients are small dense products."""
+        d_in, d_out, s = self.base.d_input(), self.base.d_output(), self.scaling
+        x2 = x.reshape(-1, d_in)
+        g2 = grad_y.reshape(-1, d_out)
+        if self.base.layout == LAYOUT_OUT_IN:
+            # forward: y = x W^T + s (x A^T) B^T with W [d_out, d_in], A [r, d_in], B [d_out, r]
+            gx = linear_forward(g2, self.base.packed(), d_out, d_in, LAYOUT_IN_OUT,
+                                lora_a=self.lora_b, lora_b=self.lora_a, lora_scale=s)
+            gb_t = g2.float().t() @ (x2.float() @ self.lora_a.float().t())   # [d_out, r]
+            ga_t = (g2.float() @ self.lora_b.float()).t() @ x2.float()       # [r, d_in]
+            ga, gb = s * ga_t, s * gb_t
+        else:
+            # forward: y = x W + s (x A) B with W [d_in, d_out], A [d_in, r], B [r, d_out]
+            gx = linear_forward(g2, self.base.packed(), d_out, d_in, LAYOUT_OUT_IN,
+                                lora_a=self.lora_b, lora_b=self.lora_a, lora_scale=s)
+            ga = s * (x2.float().t() @ (g2.float() @ self.lora_b.float().t()))   # [d_in, r]
+            gb = s * ((x2.float() @ self.lora_a.float()).t() @ g2.float())       # [r, d_out]
+        return gx.reshape(x.shape), ga.to(self.lora_a.dtype), gb.to(self.lora_b.dtype)
+
     def resident_bytes(self) -> int:
         """src/qwennet.rs:362-366."""
         r = self.lora_a.shape[0] if self.base.layout == LAYOUT_OUT_IN else self.lora_a.shape[1]
@@ -102,3 +131,43 @@ def with_lora(base: Nf4Linear, rank: int, alpha: float, generator=None) -> Qlora
     cfg = LoraConfig.new(base.d_input(), base.d_output(), rank).with_alpha(alpha)
     return QloraLinear.with_adapter(base, LoraAdapter.new(cfg, base.packed().codes.device,
                                                          generator=generator))
+
+
+class Nf4Embedding:
+    """A frozen NF4-resident embedding table ``[n_embedding, d_model]`` (src/qwennet.rs:253-291).
+
+    ``forward`` gathers and dequantizes only the rows the ids select; the reference rebuilds the
+    whole f32 table on every call and then gathers.  The values are bit-identical."""
+
+    def __init__(self, packed: PackedNf4Tensor, n_embedding: int, d_model: int):
+        if packed.len() != n_embedding * d_model:
+            raise ValueError(f"table of shape [{n_embedding}, {d_model}] carries {packed.len()} values")
+        self._packed, self._n_embedding, self._d_model = packed, n_embedding, d_model
+
+    @staticmethod
+    def from_values(values: torch.Tensor, n_embedding: int, d_model: int) -> "Nf4Embedding":
+        """Quantize a row-major table with double quantization (src/qwennet.rs:265-271)."""
+        return Nf4Embedding(PackedNf4Tensor.quantize(values).with_double_quantization(),
+                            n_embedding, d_model)
+
+    def resident_bytes(self) -> int:
+        return self._packed.resident_bytes()
+
+    def dequantized_weight(self) -> torch.Tensor:
+        return self._packed.dequantize().view(self._n_embedding, self._d_model)
+
+    def forward(self, ids: torch.Tensor, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """``ids`` of any shape (integer) -> ``[*ids.shape, d_model]``."""
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("dtype must be float32 or bfloat16")
+        p = self._packed
+        dev = p.codes.device
+        flat = ids.to(device=dev, dtype=torch.int64).contiguous().view(-1)
+        out = torch.empty(flat.numel(), self._d_model, dtype=dtype, device=dev)
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+        _lib.check(_lib.load().nf4_embedding_gather_dev(
+            ptr(p.codes), ptr(p.absmax), ptr(p.scale_codes), ptr(p.scale_of_scales),
+            self._n_embedding, self._d_model, ptr(flat), flat.numel(), ptr(out),
+            _lib.DTYPE_BF16 if dtype == torch.bfloat16 else _lib.DTYPE_F32,
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+        return out.view(*ids.shape, self._d_model)
