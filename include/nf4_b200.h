@@ -126,6 +126,18 @@ NF4_API int32_t nf4_dequantize_unpacked_dev(const uint8_t *codes, uint64_t len, 
                                     const uint8_t *scale_codes, const float *scale_of_scales,
                                     float *out, void *stream);
 
+/* Load path: packed NF4 of the TRANSPOSE of a checkpoint matrix, without materialising it.
+ * `src` is [rows, cols] row-major in device memory (a PyTorch linear weight [out, in]; f32, or
+ * bf16 as the reference's importer reads it, src/import.rs:9-12); the outputs are what
+ * PackedNf4Tensor::quantize returns for the transposed buffer [cols, rows] flattened row-major --
+ * the reference's transpose2d + quantize, src/qwennet.rs:1375-1390 and :1709-1711 -- bit for bit
+ * (follow with nf4_double_quantize_dev as the reference does).  rows % 64 == 0 and cols % 4 == 0
+ * run fused; other shapes go through `workspace` (nf4_quantize_transposed_workspace_bytes). */
+NF4_API uint64_t nf4_quantize_transposed_workspace_bytes(uint64_t rows, uint64_t cols);
+NF4_API int32_t nf4_quantize_transposed_dev(const void *src, int32_t src_dtype, uint64_t rows, uint64_t cols,
+                                    uint8_t *packed, float *absmax, void *workspace,
+                                    uint64_t workspace_bytes, void *stream);
+
 /* Rows of a packed [n_embedding, d_model] table selected by `ids` (int64, device memory),
  * dequantized: out[t][j] = level[code] * block scale of element ids[t] * d_model + j, bit-exact
  * with dequantizing the whole table and gathering.  Replaces the body of Nf4Embedding::forward,

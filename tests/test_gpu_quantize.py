@@ -264,3 +264,32 @@ def test_embedding_gather_equals_dequantize_then_gather(oracle, n_embedding, d_m
     assert bits_equal(got16, oracle.round_bf16(ref_table[ids].astype(np.float32)))
     bad = emb.forward(torch.tensor([[-1, n_embedding]]))
     assert torch.isnan(bad).all()
+
+
+@pytest.mark.parametrize("rows,cols,bf16", [(64, 64, False), (128, 200, True), (256, 1024, True),
+                                            (192, 36, False), (100, 72, True), (65, 7, False)])
+def test_load_path_quantize_of_the_transpose(oracle, rows, cols, bf16):
+    # src/qwennet.rs:1709-1711: transpose2d([out, in]) then PackedNf4Tensor::quantize (+ double
+    # quantization).  The fused kernel (rows % 64 == 0) and the workspace route must both give
+    # the oracle's bytes for the transposed buffer.
+    from unifur_b200.quantize import PackedNf4Tensor
+    from unifur_b200.qwennet import Nf4Linear
+
+    rng = np.random.default_rng(rows * 1000 + cols)
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    w[0, 0], w[rows - 1, cols - 1] = 0.5, -0.75  # outliers in the first and last block
+    if bf16:
+        w = oracle.round_bf16(w)
+    wt = np.ascontiguousarray(w.T).reshape(-1)
+    o_packed, o_absmax = oracle.quantize_packed(wt)
+    src = torch.from_numpy(w).to(DEV)
+    if bf16:
+        src = src.bfloat16()
+    p = PackedNf4Tensor.quantize_transposed(src)
+    assert np.array_equal(p.codes.cpu().numpy(), o_packed)
+    assert bits_equal(p.absmax.cpu().numpy(), o_absmax)
+    lin = Nf4Linear.from_checkpoint(src)
+    assert (lin.d_input(), lin.d_output()) == (cols, rows)
+    o_sc, o_sos = oracle.double_quantize(o_absmax)
+    assert np.array_equal(lin.packed().scale_codes.cpu().numpy(), o_sc)
+    assert bits_equal(lin.packed().scale_of_scales.cpu().numpy(), np.asarray([o_sos], np.float32))

@@ -63,6 +63,8 @@ SIGNATURES = {
     "nf4_kernel_launch_count": (_u64, []),
     "nf4_selfcheck_code_selection": (_i32, [_u64, _u64, C.POINTER(_u64)]),
     "nf4_selfcheck_quantize_fast_path": (_i32, [_u64, _u64, _f32, C.POINTER(_u64)]),
+    "nf4_quantize_transposed_workspace_bytes": (_u64, [_u64, _u64]),
+    "nf4_quantize_transposed_dev": (_i32, [_vp, _i32, _u64, _u64, _vp, _vp, _vp, _u64, _vp]),
     "nf4_embedding_gather_dev": (_i32, [_vp, _vp, _vp, _vp, _u64, _u64, _vp, _u64, _vp, _i32, _vp]),
     "nf4_levels": (None, [_vp]),
     "nf4_estimated_resident_bytes": (_u64, [_u64, _i32]),

@@ -221,6 +221,19 @@ int32_t nf4_dequantize_dev(const uint8_t *packed, uint64_t len, const float *abs
                              static_cast<cudaStream_t>(stream));
 }
 
+uint64_t nf4_quantize_transposed_workspace_bytes(uint64_t rows, uint64_t cols) {
+    return (rows % 64 == 0 && cols % 4 == 0) ? 0 : rows * cols * sizeof(float);
+}
+
+int32_t nf4_quantize_transposed_dev(const void *src, int32_t src_dtype, uint64_t rows, uint64_t cols,
+                                    uint8_t *packed, float *absmax, void *workspace,
+                                    uint64_t workspace_bytes, void *stream) {
+    if (src_dtype != NF4_DTYPE_F32 && src_dtype != NF4_DTYPE_BF16)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_quantize_transposed_dev: src_dtype must be NF4_DTYPE_F32 or NF4_DTYPE_BF16");
+    return quantize_transposed(src, src_dtype == NF4_DTYPE_BF16, rows, cols, packed, absmax, workspace,
+                               workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 int32_t nf4_embedding_gather_dev(const uint8_t *packed, const float *absmax,
                                  const uint8_t *scale_codes, const float *scale_of_scales,
                                  uint64_t n_embedding, uint64_t d_model, const int64_t *ids,

@@ -549,7 +549,6 @@ uint32_t gcd_u32(uint32_t a, uint32_t b) {
     }
     return a;
 }
-uint32_t lcm_u32(uint32_t a, uint32_t b) { return a / gcd_u32(a, b) * b; }
 uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &smem_bytes) {

@@ -52,7 +52,7 @@ __device__ long long g_decode2_ts[64];
 namespace {
 
 constexpr int kRowsPerTile = 128;
-constexpr int kBlocksPerStage = 4;          // one TMA tile = 4 quantization blocks = 128 bytes/row
+// one TMA tile = 4 quantization blocks = 128 bytes per row
 constexpr int kCodeStageBytes = kRowsPerTile * 128;
 constexpr int kScaleStageBytes = kRowsPerTile * 16;
 constexpr int kStageBytes = kCodeStageBytes + kScaleStageBytes;
@@ -173,8 +173,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // barrier slots
 constexpr int kBarCodeFull = 0, kBarCodeEmpty = kBarCodeFull + kMaxCodeStages,
               kBarAFull = kBarCodeEmpty + kMaxCodeStages, kBarAEmpty = kBarAFull + kASlots,
-              kBarSegDone = kBarAEmpty + kASlots, kBarLut = kBarSegDone + kMaxSegments,
-              kNumBars = kBarLut + 1;
+              kBarSegDone = kBarAEmpty + kASlots, kBarLut = kBarSegDone + kMaxSegments;  // one more after it
 
 // The lookup table in its shared-memory form -- entry (byte, lane) = half2 {level[byte & 15],
 // level[byte >> 4]}, one copy per lane so no two lanes ever share a bank -- built at compile

@@ -35,6 +35,9 @@ int32_t dequantize_packed(const uint8_t *packed, uint64_t len, const float *absm
 int32_t dequantize_unpacked(const uint8_t *codes, uint64_t len, const float *absmax,
                             const uint8_t *scale_codes, const float *scale_of_scales, float *out,
                             cudaStream_t stream);
+int32_t quantize_transposed(const void *src, bool src_bf16, uint64_t rows, uint64_t cols,
+                            uint8_t *packed, float *absmax, void *workspace, uint64_t workspace_bytes,
+                            cudaStream_t stream);
 int32_t embedding_gather(const uint8_t *packed, const float *absmax, const uint8_t *scale_codes,
                          const float *scale_of_scales, uint64_t n_embedding, uint64_t d_model,
                          const int64_t *ids, uint64_t n_ids, void *out, bool out_bf16,

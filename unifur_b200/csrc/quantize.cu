@@ -15,8 +15,6 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarpsPerCta = kThreads / 32;
-constexpr int kValsPerLane = 8;
-constexpr int kValsPerWarp = 32 * kValsPerLane;  // 256 values = 4 blocks
 
 __device__ __forceinline__ float group8_max(float m) {
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
@@ -209,6 +207,111 @@ dequantize_generic_kernel(const uint8_t *__restrict__ codes, uint64_t len, uint6
     }
 }
 
+// ---- load path: quantize the transpose of a checkpoint matrix without materialising it ----
+// src is [rows, cols] row-major (a PyTorch linear weight [out, in], bf16 or f32); the result is
+// the packed NF4 of its transpose [cols, rows] flattened row-major, i.e. element (c, r) at flat
+// index c * rows + r.  With rows % 64 == 0 a 64-block of the result is 64 consecutive r for one
+// c: a column segment of src.  One CTA takes a 64 x 64 tile of src through shared memory
+// (coalesced reads along c, conflict-free reads along r) and its eight warps quantize the tile's
+// 64 blocks with the same arithmetic as quantize_full_kernel.
+constexpr int kTTile = 64;
+constexpr int kTStride = kTTile + 1;  // floats between the tile's transposed rows (odd: spreads the banks)
+
+template <bool SRC_BF16>
+__global__ void __launch_bounds__(kThreads)
+quantize_transposed_kernel(const void *__restrict__ src, uint64_t rows, uint64_t cols,
+                           uint8_t *__restrict__ codes, float *__restrict__ absmax) {
+    __shared__ float s_t[kTTile * kTStride];  // s_t[c][r]
+    __shared__ uint32_t s_cells[32];
+    if (threadIdx.x < 32) s_cells[threadIdx.x] = c_cell_table[threadIdx.x];
+    const uint64_t tiles_c = (cols + kTTile - 1) / kTTile;
+    const uint64_t r0 = (blockIdx.x / tiles_c) * kTTile, c0 = (blockIdx.x % tiles_c) * kTTile;
+    // 256 threads: thread t reads row (t >> 4) + 16 i, columns 4 (t & 15) .. + 3
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint64_t r = r0 + (threadIdx.x >> 4) + 16 * i;
+        const uint64_t c = c0 + 4 * (threadIdx.x & 15u);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (c + 3 < cols) {
+            if (SRC_BF16) {
+                const uint2 w = __ldcs(reinterpret_cast<const uint2 *>(
+                    static_cast<const __nv_bfloat16 *>(src) + r * cols + c));
+                v[0] = __uint_as_float(w.x << 16);
+                v[1] = __uint_as_float(w.x & 0xffff0000u);
+                v[2] = __uint_as_float(w.y << 16);
+                v[3] = __uint_as_float(w.y & 0xffff0000u);
+            } else {
+                const float4 w = __ldcs(reinterpret_cast<const float4 *>(
+                    static_cast<const float *>(src) + r * cols + c));
+                v[0] = w.x; v[1] = w.y; v[2] = w.z; v[3] = w.w;
+            }
+        } else {
+            for (int k = 0; k < 4; ++k)
+                if (c + k < cols)
+                    v[k] = SRC_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16 *>(src)[r * cols + c + k])
+                                    : static_cast<const float *>(src)[r * cols + c + k];
+        }
+        const uint32_t rl = (threadIdx.x >> 4) + 16 * i, cl = 4 * (threadIdx.x & 15u);
+        #pragma unroll
+        for (int k = 0; k < 4; ++k) s_t[(cl + k) * kTStride + rl] = v[k];
+    }
+    __syncthreads();
+    // warp w quantizes the blocks of columns c0 + 8 w .. + 7, four at a time: lane l owns values
+    // 8 (l & 7) .. + 7 of block (l >> 3)
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    #pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const uint32_t cl = 8 * warp + 4 * half + (lane >> 3);
+        const uint64_t c = c0 + cl;
+        const float *sp = &s_t[cl * kTStride + 8 * (lane & 7u)];
+        const float4 a = make_float4(sp[0], sp[1], sp[2], sp[3]);
+        const float4 b = make_float4(sp[4], sp[5], sp[6], sp[7]);
+        float m = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))),
+                        fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+        m = group8_max(fmaxf(0.0f, m));
+        if (c >= cols) continue;
+        bool unsure = !(m >= 1e-30f && m <= 1e30f);
+        const float rcp = __fdiv_rn(1.0f, m);
+        uint32_t q0 = code_of_fast(a.x, rcp, s_cells, unsure), q1 = code_of_fast(a.y, rcp, s_cells, unsure),
+                 q2 = code_of_fast(a.z, rcp, s_cells, unsure), q3 = code_of_fast(a.w, rcp, s_cells, unsure),
+                 q4 = code_of_fast(b.x, rcp, s_cells, unsure), q5 = code_of_fast(b.y, rcp, s_cells, unsure),
+                 q6 = code_of_fast(b.z, rcp, s_cells, unsure), q7 = code_of_fast(b.w, rcp, s_cells, unsure);
+        if (unsure) {
+            q0 = code_of_exact(a.x, m); q1 = code_of_exact(a.y, m); q2 = code_of_exact(a.z, m);
+            q3 = code_of_exact(a.w, m); q4 = code_of_exact(b.x, m); q5 = code_of_exact(b.y, m);
+            q6 = code_of_exact(b.z, m); q7 = code_of_exact(b.w, m);
+        }
+        const uint64_t e = c * rows + r0 + 8 * (lane & 7u);  // flat index of this lane's first value
+        reinterpret_cast<uint32_t *>(codes)[e / 8] = q0 | (q1 << 4) | (q2 << 8) | (q3 << 12) | (q4 << 16) |
+                                                     (q5 << 20) | (q6 << 24) | (q7 << 28);
+        if ((lane & 7u) == 0) absmax[e / kBlock] = m;
+    }
+}
+
+// Any shape: the transpose written out as f32 (then quantized by the flat kernels).
+template <bool SRC_BF16>
+__global__ void __launch_bounds__(kThreads)
+transpose_to_f32_kernel(const void *__restrict__ src, uint64_t rows, uint64_t cols,
+                        float *__restrict__ out) {
+    __shared__ float s_t[32][33];
+    const uint64_t tiles_c = (cols + 31) / 32;
+    const uint64_t r0 = (blockIdx.x / tiles_c) * 32, c0 = (blockIdx.x % tiles_c) * 32;
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8
+    for (uint32_t i = ty; i < 32; i += 8) {
+        const uint64_t r = r0 + i, c = c0 + tx;
+        float v = 0.0f;
+        if (r < rows && c < cols)
+            v = SRC_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16 *>(src)[r * cols + c])
+                         : static_cast<const float *>(src)[r * cols + c];
+        s_t[i][tx] = v;
+    }
+    __syncthreads();
+    for (uint32_t i = ty; i < 32; i += 8) {
+        const uint64_t c = c0 + i, r = r0 + tx;
+        if (r < rows && c < cols) out[c * rows + r] = s_t[tx][i];
+    }
+}
+
 // ---- embedding: gather rows of a packed table and dequantize them ---------------------
 // out[t][j] = level[code(ids[t] * d_model + j)] * scale(block of that element): the rows a batch
 // of token ids selects, without materialising the table.  Blocks run over the flat table, so
@@ -394,6 +497,41 @@ int32_t dequantize_unpacked(const uint8_t *codes, uint64_t len, const float *abs
                             const uint8_t *scale_codes, const float *scale_of_scales, float *out,
                             cudaStream_t stream) {
     return dequantize_impl<false>(codes, len, absmax, scale_codes, scale_of_scales, out, stream);
+}
+
+int32_t quantize_transposed(const void *src, bool src_bf16, uint64_t rows, uint64_t cols,
+                            uint8_t *packed, float *absmax, void *workspace, uint64_t workspace_bytes,
+                            cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return NF4_OK;
+    if (!src || !packed || !absmax) return fail(NF4_ERR_INVALID_ARG, "nf4_quantize_transposed: null pointer");
+    const bool fused = rows % kTTile == 0 && cols % 4 == 0 && aligned16(src) &&
+                       (reinterpret_cast<uintptr_t>(packed) & 3u) == 0;
+    if (fused) {
+        const uint64_t tiles = (rows / kTTile) * ((cols + kTTile - 1) / kTTile);
+        if (tiles >= (1ull << 31)) return fail(NF4_ERR_UNSUPPORTED, "nf4_quantize_transposed: matrix too large");
+        if (src_bf16)
+            quantize_transposed_kernel<true><<<(unsigned)tiles, kThreads, 0, stream>>>(src, rows, cols, packed, absmax);
+        else
+            quantize_transposed_kernel<false><<<(unsigned)tiles, kThreads, 0, stream>>>(src, rows, cols, packed, absmax);
+        count_launch();
+        return check_cuda(cudaGetLastError(), "nf4_quantize_transposed launch");
+    }
+    // other shapes: transpose into the caller's workspace, then the flat quantizer
+    const uint64_t need = rows * cols * sizeof(float);
+    if (!workspace || workspace_bytes < need)
+        return fail(NF4_ERR_INVALID_ARG,
+                    "nf4_quantize_transposed: this shape needs a workspace of %llu bytes (rows %% 64 != 0)",
+                    (unsigned long long)need);
+    const uint64_t tiles = ((rows + 31) / 32) * ((cols + 31) / 32);
+    if (tiles >= (1ull << 31)) return fail(NF4_ERR_UNSUPPORTED, "nf4_quantize_transposed: matrix too large");
+    float *t = static_cast<float *>(workspace);
+    if (src_bf16)
+        transpose_to_f32_kernel<true><<<(unsigned)tiles, kThreads, 0, stream>>>(src, rows, cols, t);
+    else
+        transpose_to_f32_kernel<false><<<(unsigned)tiles, kThreads, 0, stream>>>(src, rows, cols, t);
+    count_launch();
+    NF4_CUDA_TRY(cudaGetLastError());
+    return quantize_impl<true>(t, rows * cols, packed, absmax, stream);
 }
 
 int32_t embedding_gather(const uint8_t *packed, const float *absmax, const uint8_t *scale_codes,

@@ -78,6 +78,29 @@ class PackedNf4Tensor:
                                                     _stream(dev)))
         return PackedNf4Tensor(codes, n, absmax)
 
+    @staticmethod
+    def quantize_transposed(weight: torch.Tensor) -> "PackedNf4Tensor":
+        """Packed NF4 of ``weight.t()`` flattened row-major, for a 2-D f32 or bf16 ``weight`` on
+        the GPU, without materialising the transpose: the reference's checkpoint load path
+        (``transpose2d`` + ``PackedNf4Tensor::quantize``, src/qwennet.rs:1375-1390, 1709-1711)."""
+        _require_cuda(weight, "weight")
+        if weight.dim() != 2 or weight.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("weight must be a 2-D float32 or bfloat16 tensor")
+        w = weight.contiguous()
+        rows, cols = w.shape
+        n = rows * cols
+        dev = w.device
+        codes = torch.empty((n + 1) // 2, dtype=torch.uint8, device=dev)
+        absmax = torch.empty((n + BLOCK_SIZE - 1) // BLOCK_SIZE, dtype=torch.float32, device=dev)
+        lib = _lib.load()
+        ws_bytes = int(lib.nf4_quantize_transposed_workspace_bytes(rows, cols))
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.nf4_quantize_transposed_dev(
+                _ptr(w), _lib.DTYPE_BF16 if w.dtype == torch.bfloat16 else _lib.DTYPE_F32, rows, cols,
+                _ptr(codes), _ptr(absmax), _ptr(ws), ws.numel(), _stream(dev)))
+        return PackedNf4Tensor(codes, n, absmax)
+
     def with_double_quantization(self) -> "PackedNf4Tensor":
         """src/quantize.rs:284-309; idempotent."""
         if self.is_double_quantized():

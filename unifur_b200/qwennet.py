@@ -44,6 +44,15 @@ class Nf4Linear:
             packed = packed.with_double_quantization()
         return Nf4Linear(packed, d_input, d_output, None, layout)
 
+    @staticmethod
+    def from_checkpoint(weight: torch.Tensor) -> "Nf4Linear":
+        """A PyTorch-style ``[out, in]`` weight (f32 or bf16, on the GPU) -> the reference's
+        ``[in, out]`` NF4 linear with double quantization, as its loader builds it
+        (src/qwennet.rs:1687-1726): transpose and quantize fused on the device."""
+        rows, cols = weight.shape
+        packed = PackedNf4Tensor.quantize_transposed(weight).with_double_quantization()
+        return Nf4Linear(packed, cols, rows, None, LAYOUT_IN_OUT)
+
     def d_input(self) -> int:
         return self._d_input
 
