@@ -22,8 +22,8 @@
 // of weights.  The looked-up register IS the A operand of
 // a warp MMA (m16n8k16, f16 in / f32 accumulate), with W rows on the MMA's M side and
 // the <=16 activation rows on its N side.  Each warp keeps its slice of x as f16 B-fragments
-// in registers for the whole kernel.  A block's four MMAs form two short chains, are
-// summed and scaled by the block's f32 absmax (or its double-quantized decode) -- the scale
+// in registers for the whole kernel.  A block's four MMAs accumulate in one chain (the four
+// blocks of a tile interleave) and the result is scaled by the block's f32 absmax (or its double-quantized decode) -- the scale
 // never touches the f16 path.  The lookups bound the kernel: one shared-memory wavefront
 // serves 64 weights.
 //
@@ -95,6 +95,7 @@ struct DecodeParams {
     uint32_t scale_bytes_max; // room for them
     uint32_t lora_bytes_max;  // room for the CTA's LoRA-B rows
     uint32_t smem_bytes;      // dynamic shared memory of the launch (the kernel lays it out itself)
+    uint32_t debug_no_request;  // timing build only: stream nothing after the first tiles
     uint32_t red_slot_bytes;
 };
 
@@ -130,7 +131,9 @@ __device__ __forceinline__ void wait_groups(uint32_t n) {
     }
 }
 
-template <int NT, bool DQ>
+// FULL: d_in is exactly 4096, so every warp owns four 64-blocks and no per-chunk guard is needed.
+// PT: tiles whose partial sums stay in registers between two reductions (>= p.pass_tiles).
+template <int NT, bool DQ, bool FULL, int PT>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -144,8 +147,7 @@ decode_kernel(const DecodeParams p) {
     uint8_t *lora_raw = high + 16 * kMaxRank * 4 + 128;
     const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(lora_raw);
     float *red = reinterpret_cast<float *>(smem);  // the reduction slots take the lookup table's place
-    constexpr int PT = PassTiles<NT>::value;
-    constexpr int kAccs = 2;  // a block's four MMAs run as two chains of two
+    constexpr int kAccs = 1;  // a block's four MMAs run as one chain (the four blocks of a tile interleave)
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t ring_bytes = p.ring * p.slot_bytes;
@@ -175,8 +177,9 @@ decode_kernel(const DecodeParams p) {
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t nchunks = p.K / kChunk;
     const uint32_t chunk0 = warp * p.chunks_per_warp;
-    const bool active = chunk0 < nchunks;  // short K leaves the last warps without a slice
-    const uint32_t my_chunks = active ? min(p.chunks_per_warp, nchunks - chunk0) : 0u;
+    const bool active = FULL || chunk0 < nchunks;  // short K leaves the last warps without a slice
+    const uint32_t my_chunks = FULL ? 4u : (active ? min(p.chunks_per_warp, nchunks - chunk0) : 0u);
+    const bool vec_scales = FULL || p.vec_scales;
     const uint32_t code_row_bytes = p.K / 2;
 
     // Ask for one tile of this warp's slice: 16 rows x (32 bytes per chunk) of nibbles in
@@ -186,11 +189,13 @@ decode_kernel(const DecodeParams p) {
     const uint32_t lane_dst = (lane >> 3) * p.code_stride + (lane & 7u) * 16u;
     const uint8_t *lane_src = p.codes + (size_t)(n0 + (lane >> 3)) * code_row_bytes + chunk0 * 32u +
                               (lane & 7u) * 16u;
+    uint32_t req_slot = 0, use_slot = 0;  // ring positions of the next request and the next tile read
     auto request_tile = [&](uint32_t tile) {
         const uint32_t row0 = n0 + tile * kTileRows;
         const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
-        const uint32_t slot = ring_addr + (tile % R) * p.slot_bytes;
-        if (p.vec_scales) {
+        const uint32_t slot = ring_addr + req_slot * p.slot_bytes;
+        req_slot = req_slot + 1 == R ? 0u : req_slot + 1;
+        if (vec_scales) {
             const uint8_t *src = lane_src + (size_t)tile * (kTileRows * code_row_bytes);
             #pragma unroll
             for (uint32_t i = 0; i < 4; ++i)
@@ -234,7 +239,7 @@ decode_kernel(const DecodeParams p) {
             ptx::mbar_init(ptx::smem_addr(scale_bar), kDecodeThreads);
             ptx::fence_mbar_init();
         }
-        if (p.vec_scales) {
+        if (vec_scales) {
             const uint32_t rows_cta = n1 - n0;
             if (DQ) {
                 const uint32_t ppr = nchunks / 4;  // 4-byte pieces per row
@@ -339,18 +344,22 @@ decode_kernel(const DecodeParams p) {
             }
             // keep D tiles in flight, then wait for this one (groups retire in order)
             __syncwarp();  // every lane is done reading the slot about to be refilled
+#ifdef NF4_DECODE_TIMING
+            if (!p.debug_no_request)
+#endif
             if (tile + D < ntiles) request_tile(tile + D);
             ptx::cp_async_commit();
             if (warp == 0 && tile < 8) NF4_TS(42 + tile);
             wait_groups(D);
             __syncwarp();  // the other lanes' pieces are visible too
             if (warp == 0 && tile < 8) NF4_TS(4 + 3 * tile);
-            const uint8_t *st = ring + (size_t)(tile % R) * p.slot_bytes;
+            const uint8_t *st = ring + (size_t)use_slot * p.slot_bytes;
+            use_slot = use_slot + 1 == R ? 0u : use_slot + 1;
             const uint8_t *codes_lo = st + g * p.code_stride + t * 8;
             const uint8_t *codes_hi = codes_lo + 8 * p.code_stride;
 
             float s_lo[kMaxChunksPerWarp], s_hi[kMaxChunksPerWarp];
-            if (p.vec_scales) {
+            if (vec_scales) {
                 if (tile == 0 && !ptx::mbar_wait_bounded(ptx::smem_addr(scale_bar), 0)) {
                     if (lane == 0) atomicExch(&g_decode_error, 5);
                 }
@@ -400,11 +409,11 @@ decode_kernel(const DecodeParams p) {
                         const uint32_t a2 = lut_at(x0, b + 1), a3 = lut_at(x1, b + 1);
                         #pragma unroll
                         for (int u = 0; u < NT; ++u) {
-                            if (j < kAccs)
-                                ptx::mma_16816_f16_zero(blk[j][u], a0, a1, a2, a3, xf[u][c][j][0],
+                            if (j == 0)
+                                ptx::mma_16816_f16_zero(blk[0][u], a0, a1, a2, a3, xf[u][c][j][0],
                                                         xf[u][c][j][1]);
                             else
-                                ptx::mma_16816_f16(blk[j % kAccs][u], a0, a1, a2, a3, xf[u][c][j][0],
+                                ptx::mma_16816_f16(blk[0][u], a0, a1, a2, a3, xf[u][c][j][0],
                                                    xf[u][c][j][1]);
                         }
                     }
@@ -412,8 +421,7 @@ decode_kernel(const DecodeParams p) {
                     for (int u = 0; u < NT; ++u) {
                         #pragma unroll
                         for (int r = 0; r < 4; ++r)
-                            acc[0][u][r] = fmaf(blk[0][u][r] + blk[1][u][r], r < 2 ? s_lo[c] : s_hi[c],
-                                                acc[0][u][r]);
+                            acc[0][u][r] = fmaf(blk[0][u][r], r < 2 ? s_lo[c] : s_hi[c], acc[0][u][r]);
                     }
                 }
             }
@@ -616,6 +624,11 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     if (kSlots * p.red_slot_bytes > (uint32_t)kLutBytes) return false;  // the slots reuse the table's room
     smem_bytes = kSmemLimit;
     p.smem_bytes = smem_bytes;
+    static const bool no_request = [] {
+        const char *e = std::getenv("NF4_DEBUG_NO_REQUEST");  // read by the timing build only
+        return e && e[0] == '1';
+    }();
+    p.debug_no_request = no_request ? 1u : 0u;
     p.x = static_cast<const __nv_bfloat16 *>(a.x);
     p.codes = a.packed;
     p.absmax = a.absmax;
@@ -634,17 +647,37 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     return true;
 }
 
-template <int NT, bool DQ>
-int32_t launch(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
+template <int NT, bool DQ, bool FULL, int PT>
+int32_t launch_pt(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
     static bool configured = false;  // benign race: the attribute is idempotent
     if (!configured) {
-        NF4_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<NT, DQ>,
+        NF4_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<NT, DQ, FULL, PT>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
         configured = true;
     }
     count_launch();
-    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3(kDecodeThreads),
+    return launch_maybe_overlapped(decode_kernel<NT, DQ, FULL, PT>, dim3(grid), dim3(kDecodeThreads),
                                    smem_bytes, stream, p.rank != 0 && pdl_enabled(), p);
+}
+
+// the register budget holds 8 tiles of 8 activation rows or 3 tiles of 16; shorter passes get a
+// kernel whose accumulator shift register is as short as they need
+template <int NT, bool DQ, bool FULL>
+int32_t launch_full(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
+    if constexpr (NT == 2) {
+        return launch_pt<NT, DQ, FULL, PassTiles<2>::value>(p, grid, smem_bytes, stream);
+    } else {
+        if (p.pass_tiles <= 2) return launch_pt<NT, DQ, FULL, 2>(p, grid, smem_bytes, stream);
+        if (p.pass_tiles <= 5) return launch_pt<NT, DQ, FULL, 5>(p, grid, smem_bytes, stream);
+        return launch_pt<NT, DQ, FULL, PassTiles<1>::value>(p, grid, smem_bytes, stream);
+    }
+}
+
+template <int NT, bool DQ>
+int32_t launch(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
+    return p.K == (uint32_t)(kWarps * kMaxChunksPerWarp * kChunk)
+               ? launch_full<NT, DQ, true>(p, grid, smem_bytes, stream)
+               : launch_full<NT, DQ, false>(p, grid, smem_bytes, stream);
 }
 
 }  // namespace
