@@ -6,30 +6,30 @@
 // (up to four 64-blocks each).  Every warp streams its own slice -- 16 rows x 128 bytes of
 // nibbles per tile -- global -> shared with per-thread 16-byte asynchronous copies (cp.async,
 // L2 only) into a private ring of a few tiles, rows on a padded stride so that the reads are
-// bank-conflict free.  The block scales of all the CTA's rows are fetched once, whole lines at
-// a time, at kernel start (fetched per warp and tile they cost one load/store-unit tag per
-// 16 bytes, as many as the nibbles themselves, and that unit is the busiest in the kernel).  The warps therefore share no barrier while
-// the weights stream.  (A first version moved whole tiles with TMA bulk copies; measured on
-// B200 that path delivered ~13-20 bytes per clock per SM from DRAM however many tiles were
-// requested ahead, about half of what the copy engines of all SMs need to saturate HBM, so the
-// stream now goes through the load/store path, which keeps far more requests in flight.)
+// bank-conflict free; the warps therefore share no barrier while the weights stream.  The block
+// scales of all the CTA's rows are fetched once, whole lines at a time, at kernel start
+// (fetched per warp and tile they cost one load/store-unit tag per 16 bytes, as many as the
+// nibbles themselves).  A first version moved whole tiles with TMA bulk copies issued by a
+// producer warp and met per tile on barriers; it was slower (18 us against 15 us per launch
+// under the profiler), mostly for its per-tile rendezvous and reduction.
 //
 // Math.  Dequantisation is a shared-memory table lookup: one packed byte (two codes)
 // indexes a 256-entry table of half2 {level[lo], level[hi]}, replicated once per
 // lane so that no two lanes share a bank; entries sit 256 bytes apart and the table starts at
 // shared-window address 0x10000, so that one byte permute (code byte into bits 8..15, lane
 // offset below, the constant 0x0001 above) forms the whole address: two instructions per pair
-// of weights.  The looked-up register IS the A operand of
-// a warp MMA (m16n8k16, f16 in / f32 accumulate), with W rows on the MMA's M side and
-// the <=16 activation rows on its N side.  Each warp keeps its slice of x as f16 B-fragments
-// in registers for the whole kernel.  A block's four MMAs accumulate in one chain (the four
-// blocks of a tile interleave) and the result is scaled by the block's f32 absmax (or its double-quantized decode) -- the scale
-// never touches the f16 path.  The lookups bound the kernel: one shared-memory wavefront
-// serves 64 weights.
+// of weights.  The looked-up register IS the A operand of a warp MMA (m16n8k16, f16 in / f32
+// accumulate), with W rows on the MMA's M side and the <=16 activation rows on its N side.
+// Each warp keeps its slice of x as f16 B-fragments in registers for the whole kernel.  A
+// block's four MMAs accumulate in one chain (the four blocks of a tile interleave) and the
+// result is scaled by the block's f32 absmax (or its double-quantized decode) -- the scale
+// never touches the f16 path.  What bounds the kernel is instruction issue at four warps per
+// scheduler (one 512-thread CTA with ~120 registers per thread fills the register file).
 //
-// Reduction.  A warp keeps the partial sums of several tiles in registers.  At the end of such
-// a pass every warp parks them in its own shared-memory slot and all threads sum the sixteen
-// slots in warp order (so results do not depend on timing), add bias and the LoRA term
+// Reduction.  A warp keeps the partial sums of a pass of tiles in registers (a shift register:
+// the tile being multiplied is slot 0).  At the end of a pass every warp parks them in its own
+// shared-memory slot (the slots take the lookup table's place) and all threads sum the
+// sixteen slots in warp order (so results do not depend on timing), add bias and the LoRA term
 // (T = x A^T comes from a small pre-pass), convert and store.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -42,7 +42,7 @@
 
 namespace nf4 {
 
-__device__ int g_decode_error = 0;  // kept for the error-flag entry point; this kernel has no waits that can give up
+__device__ int g_decode_error = 0;  // set when the launch gave too little shared memory or the one bounded wait gives up
 
 #ifdef NF4_DECODE_TIMING
 // Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
