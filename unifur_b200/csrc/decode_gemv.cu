@@ -65,6 +65,7 @@ constexpr int kLutStride = 256;      // bytes between table entries (128 used)
 constexpr int kLutBytes = 256 * kLutStride;
 constexpr int kMaxRank = 64;
 constexpr int kSmemLimit = 227 * 1024;
+constexpr int kSmemLeftForPrepass = 3 * 1024;  // so that a CTA of the pre-pass can share the SM
 constexpr int kSlots = kWarps;       // one reduction slot per warp
 
 // tiles whose partial sums a warp keeps in registers between two reductions
@@ -133,8 +134,10 @@ __device__ __forceinline__ void wait_groups(uint32_t n) {
 
 // FULL: d_in is exactly 4096, so every warp owns four 64-blocks and no per-chunk guard is needed.
 // PT: tiles whose partial sums stay in registers between two reductions (>= p.pass_tiles).
+// 120 registers x 512 threads and 3 KB short of all the shared memory: the pre-pass's small CTA
+// fits on the SM beside this one.
 template <int NT, bool DQ, bool FULL, int PT>
-__global__ void __launch_bounds__(kDecodeThreads, 1)
+__global__ void __maxnreg__(120)
 decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Layout by shared-window address: [start, 0x10000) rings of the first warps |
@@ -518,8 +521,10 @@ decode_kernel(const DecodeParams p) {
     ptx::cp_async_wait<0>();
 }
 
-// T[m][j] = sum_k x[m][k] * A[j][k]  (x, A bf16; f32 accumulate).  One CTA per (j, m).
-__global__ void __launch_bounds__(128)
+// T[m][j] = sum_k x[m][k] * A[j][k]  (x, A bf16; f32 accumulate).  One 128-thread CTA per (j, m):
+// many short CTAs with at most 32 registers, so that one of them fits on an SM beside a GEMV CTA
+// and the GEMV it overlaps with is not kept off the SMs the pre-pass occupies.
+__global__ void __launch_bounds__(128, 16)
 lora_t_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a, uint32_t K,
               uint32_t rank, float *__restrict__ t_out) {
     ptx::pdl_launch_dependents();  // the GEMV may start streaming weights right away
@@ -597,7 +602,7 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     // the usual 1 KB reserved at the start of the window that leaves 63 KB below and
     // (227 - 127) KB above the table.
     const uint32_t low_room = (kLutWindow - 1024u) & ~127u;
-    const uint32_t high_room = (uint32_t)kSmemLimit + 1024u - (kLutWindow + (uint32_t)kLutBytes);
+    const uint32_t high_room = (uint32_t)(kSmemLimit - kSmemLeftForPrepass) + 1024u - (kLutWindow + (uint32_t)kLutBytes);
     p.scale_stride = nchunks * (dq ? 1u : 4u) + 16u;
     p.scale_bytes_max = p.vec_scales ? round_up(max_tiles * kTileRows * p.scale_stride, 128) : 0u;
     const uint32_t high_fixed = 16 * kMaxRank * 4 + 128 + p.lora_bytes_max + p.scale_bytes_max;
@@ -622,7 +627,7 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     }
     p.ring = ring;
     if (kSlots * p.red_slot_bytes > (uint32_t)kLutBytes) return false;  // the slots reuse the table's room
-    smem_bytes = kSmemLimit;
+    smem_bytes = kSmemLimit - kSmemLeftForPrepass;
     p.smem_bytes = smem_bytes;
     static const bool no_request = [] {
         const char *e = std::getenv("NF4_DEBUG_NO_REQUEST");  // read by the timing build only
