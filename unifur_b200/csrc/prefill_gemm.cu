@@ -1,34 +1,35 @@
 // Prefill path: y[M, N] = x * dequant(W)^T (+bias) (+ s * (x A^T) B^T) for many rows of x,
 // W stored as packed NF4 [N, K] with 64-blocks along K.  A dense contraction: tensor-core
-// bound, built on tcgen05.mma with both operands in shared memory and the accumulators in
-// tensor memory (TMEM).
+// bound, built on tcgen05.mma with the dequantised weight operand and the accumulator in
+// tensor memory (TMEM) and the activations in shared memory.
 //
-// Roles inside one persistent CTA (one per SM, 768 threads):
+// Roles inside one persistent CTA (one per SM, 736 threads):
 //   warp 0      TMA producer: x tiles [256 rows x 64 k] (f16, 128B-swizzled, K-major) into a
-//               3-deep shared-memory ring; after the K loop the same ring carries the LoRA
-//               intermediate T (bf16 hi / lo halves) so the adapter is just more k-steps.
+//               4-deep shared-memory ring; after the K loop the same ring carries the LoRA
+//               intermediate T (bf16 hi / lo halves) and a second small ring the matching
+//               128 x 64 tiles of LoRA B, so the adapter is just more k-steps (with both
+//               operands in shared memory).
 //   warp 1      owns TMEM (alloc/dealloc); one of its threads issues the tcgen05.mma of the even
-//               k-stages, one thread of warp 7 those of the odd ones.  Issuing a stage's MMAs
-//               holds the thread for about as long as they run, and ~400 cycles of waits,
-//               fences and commits separate two batches; with two threads the second has done
-//               its waiting while the first issues, and only a short hand-over is left.
-//   warp 6      idle.
+//               k-stages, one thread of warp 6 those of the odd ones.  Issuing a stage's MMAs
+//               holds the thread for about as long as they run, and waits, fences and commits
+//               separate two batches; with two threads the second has done its waiting while
+//               the first issues, and only a short hand-over is left.
 //   warps 2-5   epilogue: TMEM -> registers -> (* row scale, + bias) -> bf16/f32 -> shared ->
 //               TMA store.
-//   warps 8-23  dequantisers, two groups of 256 threads.  Two threads share one weight row of
-//               a stage: each reads 16 packed bytes and the block scale straight from global
-//               memory (L2), expands the nibbles with byte-permute lookups held in registers,
-//               multiplies by the scale in f16x2 and writes its 32 f16 values into the row's
-//               128B-swizzled place in the weight tile in shared memory.  (The expansion is a
-//               dependent chain of ~120 instructions per thread: it is the number of warps that
-//               hides its latency, so the work is cut fine.)
+//   warps 7-22  dequantisers, four groups of 128 threads taking every fourth k-stage.  A thread
+//               owns one weight row (= one TMEM lane; a warp may only touch the lane quarter its
+//               number names): it reads the row's 32 packed bytes and the block scale straight
+//               from global memory (L2), expands the nibbles with byte-permute lookups held in
+//               registers, multiplies by the scale in f16x2 and writes the 64 f16 values into
+//               its lane of an eight-deep ring of TMEM columns with tcgen05.st.
 //
-// Tile shapes.  A tile is one 128-row weight half against a 256-row activation tile, with the
-// accumulator double-buffered in TMEM so that the epilogue overlaps the next tile; the two
-// dequantiser groups take alternate k-stages.  A second shape (two halves per tile, one TMEM
-// accumulator and one dequantiser group each, eight MMAs per k-stage reading the activation
-// tile twice) is kept behind an environment switch for measurements: it halves the activation
-// bytes per flop but is slower, because the k-stage is bound by shared-memory traffic.
+// Why the weight operand lives in TMEM.  An MMA of 128 x 256 x 16 with both operands in shared
+// memory reads 12 KB per 128 cycles, and the TMA and the dequantisers write as much again: more
+// than the 128 B/clk a shared memory delivers, so the k-stage was bound by shared-memory traffic.
+// With the 128-row operand in TMEM the shared memory carries only the activation tile (written
+// once, read once), and the dequantised weight never touches it.  The price: the accumulator
+// (256 columns) and the weight ring (8 x 32 columns) share the 512 TMEM columns, so there is one
+// accumulator and the MMAs of the next tile wait while the epilogue reads it out.
 //
 // The MMA computes D[n, m] = sum_k W[n, k] x[m, k]: weight rows are the MMA's M (TMEM lanes),
 // activation rows its N (256 accumulator columns).  Both operands are f16 with f32 accumulation:
@@ -41,7 +42,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -55,34 +55,40 @@ __device__ int g_prefill_error = 0;  // set when a bounded wait gives up
 // Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
 __device__ long long g_prefill_ts[128];
 #define NF4_PTS(i) do { if (blockIdx.x == 0) g_prefill_ts[(i)] = clock64(); } while (0)
+#ifndef NF4_PTS_FIRST
+#define NF4_PTS_FIRST 20
+#endif
 #else
+#define NF4_PTS_FIRST 20
 #define NF4_PTS(i) do { } while (0)
 #endif
 
 namespace {
 
+constexpr uint32_t kTsFirst = NF4_PTS_FIRST;  // first of the eight k-stages the timing build stamps
+
 constexpr int BM = 128;        // weight rows per tile (MMA M, TMEM lanes)
 constexpr int BN = 256;        // activation rows per tile (MMA N, accumulator columns)
 constexpr int BK = 64;         // k per stage = one quantization block = one 128B swizzle row
-constexpr int kHalves = 2;     // 128-row weight halves per tile on large problems
-constexpr int kWStages = 3;    // shared-memory ring of dequantised weight stages (kHalves tiles each)
-constexpr int kMaxXStages = 3; // shared-memory ring of activation tiles
-constexpr int kAccCols = BN;   // one accumulator; two of them fill the 512 TMEM columns
+constexpr int kXStages = 4;    // shared-memory ring of activation tiles
+constexpr int kLoraStages = 2; // shared-memory ring of LoRA B tiles (adapter k-stages)
+constexpr int kAStages = 8;    // TMEM ring of dequantised weight stages
+constexpr int kAStageCols = BK / 2;  // 32 columns: two f16 per 32-bit cell
+constexpr int kAccCols = BN;   // the accumulator: columns [0, 256); the weight ring follows
 constexpr int kTmemCols = 512;
 constexpr int kXTileBytes = BN * BK * 2;   // 32 KB: activations, written by TMA
-constexpr int kWTileBytes = BM * BK * 2;   // 16 KB: dequantised weights, written by the expanders
-constexpr int kWStageBytes = kHalves * kWTileBytes;
+constexpr int kLoraTileBytes = BM * BK * 2;  // 16 KB: 128 rows of LoRA B x 64 ranks, written by TMA
 
-constexpr int kEpiRows = 32;               // activation rows per epilogue chunk
-constexpr int kThreads = 24 * 32;
-constexpr int kFirstExpanderWarp = 8;
-constexpr int kExpanderWarpsPerGroup = 8;
-constexpr uint32_t kSpin = 1u << 22;
+constexpr int kEpiBytes = 64 * 1024;       // output staging: a whole tile of bf16, half a tile of f32
+constexpr int kThreads = 23 * 32;
+constexpr int kFirstExpanderWarp = 7;
+constexpr int kExpanderGroups = 4;         // of four warps (one per TMEM lane quarter) each
 
 // barrier slots
-constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kMaxXStages, kBarWFull = kBarXEmpty + kMaxXStages,
-              kBarWEmpty = kBarWFull + kWStages, kBarAccFull = kBarWEmpty + kWStages,
-              kBarAccEmpty = kBarAccFull + 2, kBarIssued = kBarAccEmpty + 2, kNumBars = kBarIssued + 2;
+constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kXStages, kBarAFull = kBarXEmpty + kXStages,
+              kBarAEmpty = kBarAFull + kAStages, kBarAccFull = kBarAEmpty + kAStages,
+              kBarAccEmpty = kBarAccFull + 1, kBarIssued = kBarAccEmpty + 1, kBarLEmpty = kBarIssued + 2,
+              kNumBars = kBarLEmpty + kLoraStages;
 
 struct PrefillParams {
     const uint8_t *codes;
@@ -90,12 +96,10 @@ struct PrefillParams {
     const uint8_t *scale_codes;
     const float *scale_of_scales;
     const float *bias;
-    const __nv_bfloat16 *lora_b;  // [N][rank]
     const float *row_scale;       // [M] power-of-two factor each activation row was divided by
     uint32_t M, N, K, rank;
     uint32_t lora_chunks;  // ceil(rank / 64); T is [M][2 * 64 * lora_chunks] (hi halves, then lo)
-    uint32_t m_tiles, n_tiles;  // n_tiles counts groups of `halves` * 128 weight rows
-    uint32_t halves;            // 2: two 128-row halves per tile; 1: one, accumulator double-buffered
+    uint32_t m_tiles, n_tiles;
 };
 
 // ---- descriptors -----------------------------------------------------------------
@@ -118,17 +122,26 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-// ---- TMEM load (32 lanes x 32-bit, 32 consecutive columns) ------------------------------
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+// ---- TMEM load (32 lanes x 32-bit, 16 consecutive columns) -------------------------------
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
-        "%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
+        "%15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
           "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
+        : "memory");
+}
+
+// ---- TMEM store (32 lanes x 32-bit, 16 consecutive columns) ------------------------------
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
+        "%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
         : "memory");
 }
 
@@ -205,32 +218,34 @@ __device__ __forceinline__ void expand_half(const LevelTables &t, const uint4 &c
 }
 
 struct RowStage {
-    uint4 c;  // this thread's 32 packed codes of one k-stage
+    uint4 c0, c1;  // the row's 64 packed codes of one k-stage
     float scale;
 };
 
 template <bool YF32>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t,
-               const __grid_constant__ CUtensorMap tmap_y, const PrefillParams p) {
+               const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_y,
+               const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled operand tiles
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int kXStages = kMaxXStages;
     uint8_t *x_ring = smem;                                   // kXStages activation tiles
-    uint8_t *w_ring = smem + kXStages * kXTileBytes;          // kWStages weight stages
-    uint8_t *epi = w_ring + kWStages * kWStageBytes;          // 2 staging buffers
-    constexpr int kEpiBufBytes = kEpiRows * BM * (YF32 ? 4 : 2);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(epi + 2 * kEpiBufBytes);
+    uint8_t *lora_ring = x_ring + kXStages * kXTileBytes;     // kLoraStages tiles of LoRA B
+    uint8_t *epi = lora_ring + kLoraStages * kLoraTileBytes;  // output staging, 64 KB
+    constexpr int kStageRows = kEpiBytes / (BM * (YF32 ? 4 : 2));  // activation rows per staging pass
+    uint64_t *bars = reinterpret_cast<uint64_t *>(epi + kEpiBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kNumBars);
+    float *row_scales = reinterpret_cast<float *>(bars + kNumBars + 2);  // BN factors of the tile's rows
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t bar0 = ptx::smem_addr(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
 
     const uint32_t k_stages = p.K / BK;
-    const uint32_t stages_per_tile = k_stages + 2 * p.lora_chunks;
+    const uint32_t lora_stages = 2 * p.lora_chunks;  // adapter k-stages per tile: hi and lo halves of T
+    const uint32_t stages_per_tile = k_stages + lora_stages;
     const uint32_t total_tiles = p.m_tiles * p.n_tiles;
     const uint32_t my_tiles = blockIdx.x < total_tiles
                                   ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -240,20 +255,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ptx::mbar_init(bar(kBarXFull + s), 1);
             ptx::mbar_init(bar(kBarXEmpty + s), 1);
         }
-        for (int s = 0; s < kWStages; ++s) {
-            ptx::mbar_init(bar(kBarWFull + s), kExpanderWarpsPerGroup * p.halves);  // the warps writing the stage
-            ptx::mbar_init(bar(kBarWEmpty + s), 1);
+        for (int s = 0; s < kAStages; ++s) {
+            ptx::mbar_init(bar(kBarAFull + s), 4);  // the four warps writing the stage
+            ptx::mbar_init(bar(kBarAEmpty + s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            ptx::mbar_init(bar(kBarAccFull + b), 1);
-            ptx::mbar_init(bar(kBarAccEmpty + b), 4);
-            ptx::mbar_init(bar(kBarIssued + b), 1);
-        }
+        ptx::mbar_init(bar(kBarAccFull), 1);
+        ptx::mbar_init(bar(kBarAccEmpty), 4);
+        ptx::mbar_init(bar(kBarIssued + 0), 1);
+        ptx::mbar_init(bar(kBarIssued + 1), 1);
+        for (int s = 0; s < kLoraStages; ++s) ptx::mbar_init(bar(kBarLEmpty + s), 1);
         ptx::fence_mbar_init();
         ptx::fence_proxy_async();
         ptx::prefetch_tmap(&tmap_x);
         ptx::prefetch_tmap(&tmap_y);
-        if (p.lora_chunks) ptx::prefetch_tmap(&tmap_t);
+        if (p.lora_chunks) {
+            ptx::prefetch_tmap(&tmap_t);
+            ptx::prefetch_tmap(&tmap_b);
+        }
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_addr(tmem_slot), kTmemCols);
@@ -262,7 +280,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;  // two accumulators: columns [0,256) and [256,512)
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_acc = tmem_base;             // columns [0, 256)
+    const uint32_t tmem_a = tmem_base + kAccCols;    // kAStages x 32 columns
 
     bool ok = true;
 
@@ -272,151 +292,204 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             uint32_t cnt = 0;
             for (uint32_t i = 0; i < my_tiles && ok; ++i) {
                 const uint32_t tile = blockIdx.x + i * gridDim.x;
-                const uint32_t m0 = (tile % p.m_tiles) * BN;
+                const uint32_t m0 = (tile % p.m_tiles) * BN, n0 = (tile / p.m_tiles) * BM;
                 for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
                     const uint32_t s = cnt % kXStages, ph = (cnt / kXStages) & 1u;
-                    if (!ptx::mbar_wait_bounded(bar(kBarXEmpty + s), ph ^ 1u, kSpin)) {
+                    if (!ptx::mbar_wait_suspended(bar(kBarXEmpty + s), ph ^ 1u)) {
                         ok = false;
                         break;
                     }
-                    if (cnt >= 20 && cnt < 28) NF4_PTS(cnt - 20);
-                    ptx::mbar_arrive_expect_tx(bar(kBarXFull + s), kXTileBytes);
+                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(cnt - kTsFirst);
+#ifdef NF4_PREFILL_FAKE_X  // measurement aid: what the stage costs without the activation stream
+                    ptx::mbar_arrive(bar(kBarXFull + s));
+                    continue;
+#endif
                     const uint32_t dst = ptx::smem_addr(x_ring + s * kXTileBytes);
-                    if (ks < k_stages)
+                    if (ks < k_stages) {
+                        ptx::mbar_arrive_expect_tx(bar(kBarXFull + s), kXTileBytes);
                         ptx::tma_load_2d(dst, &tmap_x, (int32_t)(ks * BK), (int32_t)m0,
                                          bar(kBarXFull + s));
-                    else
-                        ptx::tma_load_2d(dst, &tmap_t, (int32_t)((ks - k_stages) * BK), (int32_t)m0,
+                    } else {
+                        // adapter stage: a tile of T beside the activations' ring slot and the
+                        // matching 128 x 64 tile of LoRA B (ranks beyond the adapter's read as
+                        // zero) as the MMA's other shared-memory operand
+                        const uint32_t j = ks - k_stages, lcnt = i * lora_stages + j;
+                        const uint32_t ls = lcnt % kLoraStages, lph = (lcnt / kLoraStages) & 1u;
+                        if (!ptx::mbar_wait_suspended(bar(kBarLEmpty + ls), lph ^ 1u)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::mbar_arrive_expect_tx(bar(kBarXFull + s), kXTileBytes + kLoraTileBytes);
+                        ptx::tma_load_2d(dst, &tmap_t, (int32_t)(j * BK), (int32_t)m0, bar(kBarXFull + s));
+                        ptx::tma_load_2d(ptx::smem_addr(lora_ring + ls * kLoraTileBytes), &tmap_b,
+                                         (int32_t)((j % p.lora_chunks) * BK), (int32_t)n0,
                                          bar(kBarXFull + s));
+                    }
                 }
             }
             if (!ok) atomicExch(&g_prefill_error, 1);
         }
-    } else if (warp == 1 || warp == 7) {
+    } else if (warp == 1 || warp == 6) {
         // ============================= MMA issuers =============================
-        // Thread `me` (0: warp 1, 1: warp 7) issues the stages whose global counter has its
+        // Thread `me` (0: warp 1, 1: warp 6) issues the stages whose global counter has its
         // parity.  Stage c may only be issued after stage c - 1 has been (hand-over barrier
-        // kBarIssued + parity of c - 1), which keeps the MMAs of an accumulator in order.
+        // kBarIssued + parity of c - 1), which keeps the MMAs of the accumulator in order.
         if (lane == 0) {
             const uint32_t me = warp == 1 ? 0u : 1u;
             constexpr uint32_t idesc_main = make_idesc(0, 0, BM, BN);  // f16 x f16
             constexpr uint32_t idesc_lora = make_idesc(1, 1, BM, BN);  // bf16 x bf16
-            const uint32_t x_addr = ptx::smem_addr(x_ring), w_addr = ptx::smem_addr(w_ring);
+            const uint32_t x_addr = ptx::smem_addr(x_ring);
             uint32_t cnt = 0;
             for (uint32_t i = 0; i < my_tiles && ok; ++i) {
-                // two halves: both accumulators belong to this tile; one half: they alternate
-                const uint32_t buf = p.halves == 2 ? 0u : (i & 1u), use = p.halves == 2 ? i : (i >> 1);
-                const uint32_t tile = blockIdx.x + i * gridDim.x;
-                const uint32_t n0 = (tile / p.m_tiles) * BM * p.halves;
-                const uint32_t halves_here = (p.halves == 2 && n0 + BM < p.N) ? 2u : 1u;
                 for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
                     if ((cnt & 1u) != me) continue;
                     const uint32_t sx = cnt % kXStages, phx = (cnt / kXStages) & 1u;
-                    const uint32_t sw = cnt % kWStages, phw = (cnt / kWStages) & 1u;
-                    if (cnt >= 20 && cnt < 28) NF4_PTS(16 + 4 * (cnt - 20));
-                    // the epilogue must have drained this accumulator's previous tile
-                    if (ks == 0 &&
-                        !ptx::mbar_wait_bounded(bar(kBarAccEmpty + buf), (use & 1u) ^ 1u, kSpin)) {
+                    // the weight ring counts main stages only, the LoRA ring adapter stages only
+                    const bool main_stage = ks < k_stages;
+                    const uint32_t acnt = i * k_stages + ks, lcnt = i * lora_stages + (ks - k_stages);
+                    const uint32_t sa = acnt % kAStages, pha = (acnt / kAStages) & 1u;
+                    const uint32_t ls = lcnt % kLoraStages;
+                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(16 + 4 * (cnt - kTsFirst));
+                    // the epilogue must have read the previous tile out of the accumulator
+                    if (ks == 0 && !ptx::mbar_wait_suspended(bar(kBarAccEmpty), (i & 1u) ^ 1u)) {
                         ok = false;
                         break;
                     }
-                    if (!ptx::mbar_wait_bounded(bar(kBarXFull + sx), phx, kSpin)) {
+                    if (!ptx::mbar_wait_suspended(bar(kBarXFull + sx), phx)) {
                         ok = false;
                         break;
                     }
-                    if (cnt >= 20 && cnt < 28) NF4_PTS(17 + 4 * (cnt - 20));
-                    if (!ptx::mbar_wait_bounded(bar(kBarWFull + sw), phw, kSpin)) {
+                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(17 + 4 * (cnt - kTsFirst));
+                    if (main_stage && !ptx::mbar_wait_suspended(bar(kBarAFull + sa), pha)) {
                         ok = false;
                         break;
                     }
                     // hand-over: the other thread has issued stage cnt - 1 (its (cnt-1)/2-th)
                     if (cnt > 0 &&
-                        !ptx::mbar_wait_bounded(bar(kBarIssued + (me ^ 1u)), ((cnt - 1) >> 1) & 1u, kSpin)) {
+                        !ptx::mbar_wait_suspended(bar(kBarIssued + (me ^ 1u)), ((cnt - 1) >> 1) & 1u)) {
                         ok = false;
                         break;
                     }
-                    if (cnt >= 20 && cnt < 28) NF4_PTS(18 + 4 * (cnt - 20));
+                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(18 + 4 * (cnt - kTsFirst));
                     ptx::tc_fence_after();
                     const uint64_t bdesc = make_kmajor_sw128_desc(x_addr + sx * kXTileBytes);
-                    for (uint32_t h = 0; h < halves_here; ++h) {
-                        const uint32_t acc = tmem_base + (p.halves == 2 ? h : buf) * kAccCols;
+                    const uint32_t a_cols = tmem_a + sa * kAStageCols;
+                    if (main_stage) {
+                        // 16 k = 8 TMEM columns of the weight stage = 32 bytes inside the
+                        // activation tile's swizzled row (+2 in the encoded address)
+                        ptx::mma_ts_f16(tmem_acc, a_cols, bdesc, idesc_main, ks != 0 ? 1u : 0u);
+                        ptx::mma_ts_f16(tmem_acc, a_cols + 8, bdesc + 2, idesc_main, 1u);
+                        ptx::mma_ts_f16(tmem_acc, a_cols + 16, bdesc + 4, idesc_main, 1u);
+                        ptx::mma_ts_f16(tmem_acc, a_cols + 24, bdesc + 6, idesc_main, 1u);
+                    } else {
+                        const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
+                        const uint32_t left = p.rank - chunk * 64;
+                        const uint32_t nk16 = ((left < 64 ? left : 64) + 15) / 16;
                         const uint64_t adesc =
-                            make_kmajor_sw128_desc(w_addr + sw * kWStageBytes + h * kWTileBytes);
-                        if (ks < k_stages) {
-                            // +32 bytes of K inside the swizzled row = +2 in the encoded address
-                            ptx::mma_ss_f16(acc, adesc, bdesc, idesc_main, ks != 0 ? 1u : 0u);
-                            ptx::mma_ss_f16(acc, adesc + 2, bdesc + 2, idesc_main, 1u);
-                            ptx::mma_ss_f16(acc, adesc + 4, bdesc + 4, idesc_main, 1u);
-                            ptx::mma_ss_f16(acc, adesc + 6, bdesc + 6, idesc_main, 1u);
-                        } else {
-                            const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
-                            const uint32_t left = p.rank - chunk * 64;
-                            const uint32_t nk16 = ((left < 64 ? left : 64) + 15) / 16;
-                            for (uint32_t j = 0; j < nk16; ++j)
-                                ptx::mma_ss_f16(acc, adesc + 2 * j, bdesc + 2 * j, idesc_lora, 1u);
-                        }
+                            make_kmajor_sw128_desc(ptx::smem_addr(lora_ring) + ls * kLoraTileBytes);
+                        for (uint32_t j = 0; j < nk16; ++j)
+                            ptx::mma_ss_f16(tmem_acc, adesc + 2 * j, bdesc + 2 * j, idesc_lora, 1u);
                     }
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(bar(kBarIssued + me));
                     ptx::tc_commit(bar(kBarXEmpty + sx));
-                    ptx::tc_commit(bar(kBarWEmpty + sw));
-                    if (ks + 1 == stages_per_tile) ptx::tc_commit(bar(kBarAccFull + buf));
-                    if (cnt >= 20 && cnt < 28) NF4_PTS(19 + 4 * (cnt - 20));
+                    ptx::tc_commit(main_stage ? bar(kBarAEmpty + sa) : bar(kBarLEmpty + ls));
+                    if (ks + 1 == stages_per_tile) ptx::tc_commit(bar(kBarAccFull));
+                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(19 + 4 * (cnt - kTsFirst));
                 }
             }
             if (!ok) atomicExch(&g_prefill_error, 2);
         }
     } else if (warp < 6) {
         // ============================== epilogue ==============================
+        // The MMAs of the next tile wait for the accumulator, so it is read out as fast as four
+        // warps can: the whole tile (bf16) or half of it (f32) goes through one 64 KB staging
+        // buffer, two TMEM loads in flight, and the accumulator is handed back before the last
+        // values are converted; the TMA store of the tile then overlaps the next tile's MMAs.
         const uint32_t q = warp & 3u;  // TMEM lane quarter this warp may touch
         const uint32_t row_in_tile = q * 32 + lane;
         const uint32_t epi_leader = (warp == 2 && lane == 0);
+        const uint32_t acc_lane = tmem_acc + ((q * 32) << 16);
+        constexpr uint32_t kChunks = kStageRows / 16;  // 16-column TMEM loads per staging pass
         for (uint32_t i = 0; i < my_tiles && ok; ++i) {
             const uint32_t tile = blockIdx.x + i * gridDim.x;
-            const uint32_t n00 = (tile / p.m_tiles) * BM * p.halves, m0 = (tile % p.m_tiles) * BN;
-            const uint32_t buf = p.halves == 2 ? 0u : (i & 1u), use = p.halves == 2 ? i : (i >> 1);
-            const uint32_t halves_here = (p.halves == 2 && n00 + BM < p.N) ? 2u : 1u;
-            ok = ptx::mbar_wait_bounded(bar(kBarAccFull + buf), use & 1u, kSpin);
+            const uint32_t n0 = (tile / p.m_tiles) * BM, m0 = (tile % p.m_tiles) * BN;
+            const uint32_t n = n0 + row_in_tile;
+            const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+            // the rows' factors go to shared memory while the MMAs still run: a global load per
+            // value inside the read-out would wait for L2 every time (the L1 left beside 227 KB
+            // of shared memory is small and the dequantisers stream through it)
+            #pragma unroll
+            for (uint32_t h = 0; h < BN / 128; ++h) {
+                const uint32_t r = h * 128 + (warp - 2) * 32 + lane;
+                row_scales[r] = m0 + r < p.M ? __ldg(p.row_scale + m0 + r) : 1.0f;
+            }
+            ok = ptx::mbar_wait_suspended(bar(kBarAccFull), i & 1u);
             if (!ok) break;
+            if (warp == 2 && lane == 0) NF4_PTS(100 + 2 * (i & 3u));
+            if (warp == 2 && lane == 0 && i == 0) NF4_PTS(121);
             ptx::tc_fence_after();
-            for (uint32_t h = 0; h < halves_here; ++h) {
-                const uint32_t n0 = n00 + h * BM;
-                const uint32_t n = n0 + row_in_tile;
-                const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
-                const uint32_t acc = tmem_base + (p.halves == 2 ? h : buf) * kAccCols;
-                for (uint32_t c = 0; c < BN / kEpiRows; ++c) {
-                    uint8_t *ebuf = epi + (c & 1u) * kEpiBufBytes;
-                    // the TMA store that last read this buffer must be done with it
-                    if (epi_leader) ptx::tma_store_wait_read<1>();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    uint32_t v[32];
-                    tmem_ld32(acc + ((q * 32) << 16) + c * kEpiRows, v);
+            uint32_t va[16], vb[16];
+            tmem_ld16(acc_lane, va);
+            // staging layout: [kStageRows activation rows][BM weight rows]
+            auto stage_chunk = [&](const uint32_t (&v)[16], uint32_t col) {
+                const uint32_t r0 = col % kStageRows;
+                // the factors first, as vectors: a load per value between the stores could not be
+                // moved ahead of them (both are shared memory) and each would wait out its latency
+                float rs[16];
+                #pragma unroll
+                for (int r4 = 0; r4 < 4; ++r4) {
+                    const float4 f4 = reinterpret_cast<const float4 *>(row_scales + col)[r4];
+                    rs[4 * r4 + 0] = f4.x;
+                    rs[4 * r4 + 1] = f4.y;
+                    rs[4 * r4 + 2] = f4.z;
+                    rs[4 * r4 + 3] = f4.w;
+                }
+                #pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const float f = fmaf(__uint_as_float(v[r]), rs[r], bias);
+                    if (YF32)
+                        reinterpret_cast<float *>(epi)[(r0 + r) * BM + row_in_tile] = f;
+                    else
+                        reinterpret_cast<__nv_bfloat16 *>(epi)[(r0 + r) * BM + row_in_tile] =
+                            __float2bfloat16_rn(f);
+                }
+            };
+            for (uint32_t pass = 0; pass < BN / kStageRows; ++pass) {
+                // the TMA store that last read the staging buffer must be done with it
+                if (epi_leader) ptx::tma_store_wait_read<0>();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (uint32_t c = 0; c < kChunks; c += 2) {
+                    const uint32_t col = pass * kStageRows + c * 16;
+                    if (warp == 2 && lane == 0 && i == 2) NF4_PTS(108 + (c >> 1));
+                    const bool fine = warp == 2 && lane == 0 && i == 2 && c == 4;
                     ptx::tmem_wait_ld();
-                    if (c == BN / kEpiRows - 1 && h + 1 == halves_here) {
-                        // accumulators fully read: hand them back to the MMA warp
+                    if (fine) NF4_PTS(116);
+                    tmem_ld16(acc_lane + col + 16, vb);
+                    if (fine) NF4_PTS(117);
+                    stage_chunk(va, col);
+                    if (fine) NF4_PTS(118);
+                    ptx::tmem_wait_ld();
+                    if (fine) NF4_PTS(119);
+                    if (col + 32 < BN) {
+                        tmem_ld16(acc_lane + col + 32, va);
+                    } else {
+                        // accumulator fully read: hand it back to the MMA threads
                         ptx::tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty + buf));
+                        if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty));
+                        if (warp == 2 && lane == 0) NF4_PTS(101 + 2 * (i & 3u));
+                        if (warp == 2 && lane == 0 && i == 0) NF4_PTS(122);
                     }
-                    // staging layout: [kEpiRows activation rows][BM weight rows]
-                    #pragma unroll
-                    for (int r = 0; r < 32; ++r) {
-                        const uint32_t m = m0 + c * kEpiRows + r;
-                        const float rs = m < p.M ? __ldg(p.row_scale + m) : 1.0f;
-                        const float f = fmaf(__uint_as_float(v[r]), rs, bias);
-                        if (YF32)
-                            reinterpret_cast<float *>(ebuf)[r * BM + row_in_tile] = f;
-                        else
-                            reinterpret_cast<__nv_bfloat16 *>(ebuf)[r * BM + row_in_tile] =
-                                __float2bfloat16_rn(f);
-                    }
-                    ptx::fence_proxy_async();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (epi_leader) {
-                        ptx::tma_store_2d(&tmap_y, ptx::smem_addr(ebuf), (int32_t)n0,
-                                          (int32_t)(m0 + c * kEpiRows));
-                        ptx::tma_store_commit();
-                    }
+                    stage_chunk(vb, col + 16);
+                    if (fine) NF4_PTS(120);
+                }
+                ptx::fence_proxy_async();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (epi_leader) {
+                    ptx::tma_store_2d(&tmap_y, ptx::smem_addr(epi), (int32_t)n0,
+                                      (int32_t)(m0 + pass * kStageRows));
+                    ptx::tma_store_commit();
                 }
             }
         }
@@ -424,110 +497,93 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         if (!ok && lane == 0) atomicExch(&g_prefill_error, 3);
     } else if (warp >= kFirstExpanderWarp) {
         // ============================ dequantisers ============================
-        // Two groups of 256 threads: with two halves per tile each group owns a half and takes
-        // every stage; with one half they take alternate stages.  Two threads share a weight
-        // row: 16 packed bytes + the scale in, 32 f16 values out, written as four 16-byte chunks
-        // at the 128B-swizzled positions the MMA's shared-memory descriptor expects.
-        const uint32_t group = (warp - kFirstExpanderWarp) / kExpanderWarpsPerGroup;  // 0 or 1
-        const uint32_t half = p.halves == 2 ? group : 0u;
-        const uint32_t row_in_tile = ((warp - kFirstExpanderWarp) % kExpanderWarpsPerGroup) * 16 + (lane >> 1);
-        const uint32_t side = lane & 1u;  // which 32 of the row's 64 weights
+        // Four groups of four warps; group g takes the main stages (adapter stages need no
+        // dequantiser) whose running number over this CTA's tiles is g modulo 4.
+        // Within a group the warp's number modulo 4 names the TMEM lane quarter it may write, and
+        // the lane the weight row: 32 packed bytes + the scale in, 64 f16 values out, stored as
+        // 32 TMEM columns (two f16 per cell, even k in the low half) of the stage's ring slot.
+        const uint32_t group = (warp - kFirstExpanderWarp) >> 2;
+        const uint32_t q = warp & 3u;
+        const uint32_t row_in_tile = q * 32 + lane;
         const LevelTables tables = make_level_tables();
         const float sos = p.scale_codes ? __ldg(p.scale_of_scales) : 0.0f;
         const uint32_t blocks_per_row = p.K / 64;
-        const uint32_t total = my_tiles * stages_per_tile;
-        const uint32_t row_off = (row_in_tile >> 3) * 1024 + (row_in_tile & 7u) * 128;
-        const uint32_t swz = row_in_tile & 7u;
+        const uint32_t total = my_tiles * k_stages;
+        const uint32_t lane_base = tmem_a + ((q * 32) << 16);
 
         // Stage positions are walked, not divided out: a 64-bit division per stage costs more
         // than the expansion itself.
         struct Pos {
-            uint32_t cnt, i, ks, n;  // global stage counter, tile number, stage in tile, weight row
+            uint32_t cnt, i, ks, n;  // running main-stage number, tile number, stage in tile, weight row
         };
-        const uint32_t step = p.halves == 2 ? 1u : 2u;
         auto row_of_tile = [&](uint32_t i) {
             const uint32_t tile = blockIdx.x + i * gridDim.x;
-            return (tile / p.m_tiles) * BM * p.halves + half * BM + row_in_tile;
+            return (tile / p.m_tiles) * BM + row_in_tile;
         };
-        auto advance = [&](Pos &q) {
-            q.cnt += step;
-            q.ks += step;
-            while (q.ks >= stages_per_tile) {
-                q.ks -= stages_per_tile;
-                ++q.i;
-                q.n = row_of_tile(q.i);
+        auto settle = [&](Pos &pos) {
+            while (pos.ks >= k_stages) {
+                pos.ks -= k_stages;
+                ++pos.i;
+                pos.n = row_of_tile(pos.i);
             }
         };
-        auto fetch = [&](const Pos &q, RowStage &rs) {
-            rs.c = make_uint4(0, 0, 0, 0);
+        auto advance = [&](Pos &pos) {
+            pos.cnt += kExpanderGroups;
+            pos.ks += kExpanderGroups;
+            settle(pos);
+        };
+        auto fetch = [&](const Pos &pos, RowStage &rs) {
+            rs.c0 = rs.c1 = make_uint4(0, 0, 0, 0);
             rs.scale = 0.0f;
-            if (q.cnt >= total) return;
-            const uint32_t ks = q.ks, n = q.n;
-            if (n >= p.N || ks >= k_stages) return;  // adapter stages are read when emitted
+            if (pos.cnt >= total) return;
+            const uint32_t ks = pos.ks, n = pos.n;
+            if (n >= p.N) return;
 #ifdef NF4_PREFILL_FAKE_FETCH  // measurement aid: what the stage costs without the global loads
-            rs.c = make_uint4(n, ks, n ^ ks, 7u);
+            rs.c0 = make_uint4(n, ks, n ^ ks, 7u);
+            rs.c1 = rs.c0;
             rs.scale = 1.0f;
             return;
 #endif
-            rs.c = __ldg(reinterpret_cast<const uint4 *>(
-                p.codes + (size_t)n * (p.K / 2) + (size_t)ks * 32 + side * 16));
+            const uint4 *src = reinterpret_cast<const uint4 *>(
+                p.codes + (size_t)n * (p.K / 2) + (size_t)ks * 32);
+            rs.c0 = __ldg(src);
+            rs.c1 = __ldg(src + 1);
             const size_t blk = (size_t)n * blocks_per_row + ks;
             rs.scale = p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos);
         };
-        auto emit = [&](const Pos &q, const RowStage &rs) -> bool {
-            const uint32_t cnt = q.cnt, ks = q.ks;
-            const uint32_t s = cnt % kWStages, ph = (cnt / kWStages) & 1u;
+        auto emit = [&](const Pos &pos, const RowStage &rs) -> bool {
+            const uint32_t cnt = pos.cnt;
+            const uint32_t s = cnt % kAStages, ph = (cnt / kAStages) & 1u;
+            const uint32_t dst = lane_base + s * kAStageCols;
+            const bool stamp = q == 0 && lane == 0 && cnt >= kTsFirst && cnt < kTsFirst + 8;
             uint32_t out[16];
-            if (ks < k_stages) {
-                expand_half(tables, rs.c, rs.scale, out);
-            } else {
-                // this thread's half of one 64-wide chunk of this row of LoRA B (bf16 pairs),
-                // zero beyond the rank
-                const uint32_t n = q.n;
-                const uint32_t chunk = (ks - k_stages) % p.lora_chunks;
-                const uint32_t left = p.rank - chunk * 64;
-                const uint16_t *src = reinterpret_cast<const uint16_t *>(p.lora_b) +
-                                      (size_t)n * p.rank + chunk * 64;
-                #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const uint32_t col = side * 32 + 2 * e;
-                    uint32_t lo = 0, hi = 0;
-                    if (n < p.N) {
-                        if (col < left) lo = __ldg(src + col);
-                        if (col + 1 < left) hi = __ldg(src + col + 1);
-                    }
-                    out[e] = lo | (hi << 16);
-                }
-            }
-            if ((warp == 8 || warp == 16) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(64 + 4 * (cnt - 20));
-            if (!ptx::mbar_wait_bounded(bar(kBarWEmpty + s), ph ^ 1u, kSpin)) return false;
-            if ((warp == 8 || warp == 16) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(65 + 4 * (cnt - 20));
-            uint8_t *wrow = w_ring + s * kWStageBytes + half * kWTileBytes + row_off;
-            #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4 *>(wrow + (((side * 4 + c) ^ swz) << 4)) =
-                    make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
-            ptx::fence_proxy_async();  // the tensor core reads this tile through the async proxy
+            expand_half(tables, rs.c0, rs.scale, out);
+            if (stamp) NF4_PTS(64 + 4 * (cnt - kTsFirst));
+            if (!ptx::mbar_wait_suspended(bar(kBarAEmpty + s), ph ^ 1u)) return false;
+            if (stamp) NF4_PTS(65 + 4 * (cnt - kTsFirst));
+            ptx::tc_fence_after();
+#ifndef NF4_PREFILL_FAKE_STORE  // measurement aid: what the stage costs without the TMEM stores
+            tmem_st16(dst, out);
+#endif
+            expand_half(tables, rs.c1, rs.scale, out);
+#ifndef NF4_PREFILL_FAKE_STORE
+            tmem_st16(dst + 16, out);
+            ptx::tmem_wait_st();
+#else
+            if (out[3] == 0x12345678u) NF4_PTS(127);  // keeps the expansion alive
+#endif
+            ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar(kBarWFull + s));
-            if ((warp == 8 || warp == 16) && lane == 0 && cnt >= 20 && cnt < 28) NF4_PTS(66 + 4 * (cnt - 20));
+            if (lane == 0) ptx::mbar_arrive(bar(kBarAFull + s));
+            if (stamp) NF4_PTS(66 + 4 * (cnt - kTsFirst));
             return true;
         };
 
-        // four-deep software pipeline over this group's stages (the loads of a stage are in
-        // flight for three emits): every stage with two halves, stages group, group + 2,
-        // group + 4, ... with one
-        constexpr int kDepth = 4;
-        Pos pe{0, 0, 0, row_of_tile(0)};
-        if (p.halves != 2 && group) {  // the second group starts one stage in
-            pe.cnt = 1;
-            pe.ks = 1;
-            while (pe.ks >= stages_per_tile) {
-                pe.ks -= stages_per_tile;
-                ++pe.i;
-                pe.n = row_of_tile(pe.i);
-            }
-        }
+        // software pipeline over this group's stages (group, group + 4, group + 8, ...): the
+        // loads of a stage are in flight while the stages before it are expanded
+        constexpr int kDepth = 2;
+        Pos pe{group, 0, group, row_of_tile(0)};
+        settle(pe);
         Pos pf = pe;
         RowStage rs[kDepth];
         #pragma unroll
@@ -543,10 +599,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     advance(pe);
                     fetch(pf, rs[d]);
                     advance(pf);
-#ifdef NF4_PREFILL_TIMING
-                    if ((warp == 8 || warp == 16) && lane == 0 && pe.cnt - step >= 20 && pe.cnt - step < 28)
-                        NF4_PTS(67 + 4 * (pe.cnt - step - 20));
-#endif
                 }
             }
         }
@@ -729,7 +781,8 @@ bool prefill_supported(const nf4_linear_args &a) {
     if ((ldy * ybytes) % 16 != 0 || !aligned16(a.y) || !aligned16(a.x) || !aligned16(a.packed))
         return false;
     if (a.lora_a) {
-        if (a.lora_rank > 256) return false;
+        // LoRA B is read by TMA: rows (rank * 2 bytes) must be a multiple of 16 bytes
+        if (a.lora_rank > 256 || a.lora_rank % 8 != 0 || !aligned16(a.lora_b)) return false;
         if (a.d_in % 8 != 0 || !aligned16(a.lora_a)) return false;
     }
     return true;
@@ -764,23 +817,13 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.scale_codes = a.scale_codes;
     p.scale_of_scales = a.scale_of_scales;
     p.bias = a.bias;
-    p.lora_b = static_cast<const __nv_bfloat16 *>(a.lora_b);
     p.M = (uint32_t)a.rows;
     p.N = (uint32_t)a.d_out;
     p.K = (uint32_t)a.d_in;
     p.rank = a.lora_a ? a.lora_rank : 0;
     p.lora_chunks = lora_chunks_of(p.rank);
     p.m_tiles = (p.M + BN - 1) / BN;
-    // One 128-row half per tile by default.  Two halves per tile (NF4_PREFILL_HALVES=2) halve the
-    // activation bytes per flop, but on B200 the k-stage is bound by shared-memory traffic (MMA
-    // operand reads + TMA writes + dequantiser stores), not by the activation stream: measured
-    // 547 against 601 TFLOP/s on the 2048 x 14336 x 4096 shape.
-    static const int halves_env = [] {
-        const char *e = std::getenv("NF4_PREFILL_HALVES");  // measurement knob: 1 or 2
-        return e ? std::atoi(e) : 0;
-    }();
-    p.halves = halves_env == 2 ? 2u : 1u;
-    p.n_tiles = (p.N + BM * p.halves - 1) / (BM * p.halves);
+    p.n_tiles = (p.N + BM - 1) / BM;
     const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
 
     const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.rank);
@@ -795,27 +838,29 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     count_launch();
     NF4_CUDA_TRY(cudaGetLastError());
 
-    CUtensorMap map_x, map_t, map_y;
+    CUtensorMap map_x, map_t, map_b, map_y;
     NF4_TRY(make_map(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, p.M, p.K, (uint64_t)p.K * 2, BN, BK,
                      CU_TENSOR_MAP_SWIZZLE_128B));
-    map_t = map_x;
+    map_t = map_b = map_x;
     if (p.rank) {
         const uint32_t ld_t = 2 * 64 * p.lora_chunks;
         NF4_TRY(make_map(&map_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, p.M, ld_t, (uint64_t)ld_t * 2, BN,
                          BK, CU_TENSOR_MAP_SWIZZLE_128B));
+        // LoRA B [N][rank]: columns beyond the rank and rows beyond N read as zero
+        NF4_TRY(make_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b, p.N, p.rank,
+                         (uint64_t)p.rank * 2, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B));
     }
     if (a.y_f32)
-        NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.y, p.M, p.N, ldy * 4, kEpiRows, BM,
+        NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.y, p.M, p.N, ldy * 4, kEpiBytes / (BM * 4), BM,
                          CU_TENSOR_MAP_SWIZZLE_NONE));
     else
-        NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, p.M, p.N, ldy * 2, kEpiRows, BM,
+        NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, p.M, p.N, ldy * 2, kEpiBytes / (BM * 2), BM,
                          CU_TENSOR_MAP_SWIZZLE_NONE));
 
     const uint32_t total_tiles = p.m_tiles * p.n_tiles;
     const uint32_t grid = total_tiles < (uint32_t)kNumSMs ? total_tiles : (uint32_t)kNumSMs;
-    const size_t smem = 1024 + kMaxXStages * kXTileBytes + kWStages * kWStageBytes +
-                        2 * kEpiRows * BM * (a.y_f32 ? 4 : 2) +
-                        kNumBars * 8 + 64;
+    const size_t smem = 1024 + kXStages * kXTileBytes + kLoraStages * kLoraTileBytes + kEpiBytes +
+                        kNumBars * 8 + 16 + BN * 4 + 64;
     if (a.y_f32) {
         static bool configured = false;
         if (!configured) {
@@ -823,7 +868,7 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = true;
         }
-        prefill_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_y, p);
+        prefill_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_b, map_y, p);
     } else {
         static bool configured = false;
         if (!configured) {
@@ -831,7 +876,7 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = true;
         }
-        prefill_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_y, p);
+        prefill_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_b, map_y, p);
     }
     count_launch();
     return check_cuda(cudaGetLastError(), "prefill_kernel launch");

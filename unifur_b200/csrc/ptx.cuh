@@ -61,6 +61,27 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
+// The same bounded wait for threads that wait long and often beside warps that have work to do:
+// each poll lets the hardware suspend the thread until the phase completes or `suspend_ns` have
+// passed, so that a waiting warp takes no issue slots from the others (a plain try_wait comes
+// back at once when the phase is not complete and the loop around it competes for issue).
+__device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_t parity,
+                                                    uint32_t suspend_ns = 4000) {
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(suspend_ns)
+            : "memory");
+        if (ok) return true;
+        if (global_timer_ns() - t0 > 1000000000ull) return false;
+    }
+}
+
 // ---- bulk async copy global -> shared (TMA, untiled) --------------------------
 // dst, src 16-byte aligned; bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes,
