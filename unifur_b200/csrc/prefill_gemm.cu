@@ -3,7 +3,7 @@
 // bound, built on tcgen05.mma with the dequantised weight operand and the accumulator in
 // tensor memory (TMEM) and the activations in shared memory.
 //
-// Roles inside one persistent CTA (one per SM, 736 threads):
+// Roles inside one persistent CTA (one per SM, 864 threads):
 //   warp 0      TMA producer: x tiles [256 rows x 64 k] (f16, 128B-swizzled, K-major) into a
 //               4-deep shared-memory ring; after the K loop the same ring carries the LoRA
 //               intermediate T (bf16 hi / lo halves) and a second small ring the matching
@@ -14,8 +14,8 @@
 //               holds the thread for about as long as they run, and waits, fences and commits
 //               separate two batches; with two threads the second has done its waiting while
 //               the first issues, and only a short hand-over is left.
-//   warps 2-5   epilogue: TMEM -> registers -> (* row scale, + bias) -> bf16/f32 -> shared ->
-//               TMA store.
+//   warps 2-5, 23-26  epilogue: TMEM -> registers -> (* row scale, + bias) -> bf16/f32 ->
+//               shared -> TMA store.
 //   warps 7-22  dequantisers, four groups of 128 threads taking every fourth k-stage.  A thread
 //               owns one weight row (= one TMEM lane; a warp may only touch the lane quarter its
 //               number names): it reads the row's 32 packed bytes and the block scale straight
@@ -80,8 +80,9 @@ constexpr int kXTileBytes = BN * BK * 2;   // 32 KB: activations, written by TMA
 constexpr int kLoraTileBytes = BM * BK * 2;  // 16 KB: 128 rows of LoRA B x 64 ranks, written by TMA
 
 constexpr int kEpiBytes = 64 * 1024;       // output staging: a whole tile of bf16, half a tile of f32
-constexpr int kThreads = 23 * 32;
-constexpr int kFirstExpanderWarp = 7;
+constexpr int kThreads = 27 * 32;
+constexpr int kFirstExpanderWarp = 7;      // sixteen warps
+constexpr int kFirstEpilogueWarpB = 23;    // the second set of four epilogue warps
 constexpr int kExpanderGroups = 4;         // of four warps (one per TMEM lane quarter) each
 
 // barrier slots
@@ -134,14 +135,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 
-// ---- TMEM store (32 lanes x 32-bit, 16 consecutive columns) ------------------------------
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+// ---- TMEM store (32 lanes x 32-bit, 32 consecutive columns) ------------------------------
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&a)[16],
+                                          const uint32_t (&b)[16]) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
-        "%14,%15,%16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-        "r"(r[15])
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
+        "%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]),
+        "r"(a[7]), "r"(a[8]), "r"(a[9]), "r"(a[10]), "r"(a[11]), "r"(a[12]), "r"(a[13]), "r"(a[14]),
+        "r"(a[15]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]),
+        "r"(b[7]), "r"(b[8]), "r"(b[9]), "r"(b[10]), "r"(b[11]), "r"(b[12]), "r"(b[13]), "r"(b[14]),
+        "r"(b[15])
         : "memory");
 }
 
@@ -260,7 +264,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ptx::mbar_init(bar(kBarAEmpty + s), 1);
         }
         ptx::mbar_init(bar(kBarAccFull), 1);
-        ptx::mbar_init(bar(kBarAccEmpty), 4);
+        ptx::mbar_init(bar(kBarAccEmpty), 8);
         ptx::mbar_init(bar(kBarIssued + 0), 1);
         ptx::mbar_init(bar(kBarIssued + 1), 1);
         for (int s = 0; s < kLoraStages; ++s) ptx::mbar_init(bar(kBarLEmpty + s), 1);
@@ -400,17 +404,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             }
             if (!ok) atomicExch(&g_prefill_error, 2);
         }
-    } else if (warp < 6) {
+    } else if (warp < 6 || warp >= kFirstEpilogueWarpB) {
         // ============================== epilogue ==============================
-        // The MMAs of the next tile wait for the accumulator, so it is read out as fast as four
-        // warps can: the whole tile (bf16) or half of it (f32) goes through one 64 KB staging
-        // buffer, two TMEM loads in flight, and the accumulator is handed back before the last
-        // values are converted; the TMA store of the tile then overlaps the next tile's MMAs.
+        // The MMAs of the next tile wait for the accumulator, so it is read out as fast as eight
+        // warps can (two per TMEM lane quarter, each taking half of the columns): the whole tile
+        // (bf16) or half of it (f32) goes through one 64 KB staging buffer, two TMEM loads in
+        // flight per warp, and the accumulator is handed back before the last values are
+        // converted; the TMA store of the tile then overlaps the next tile's MMAs.
+        const uint32_t set = warp >= kFirstEpilogueWarpB ? 1u : 0u;
         const uint32_t q = warp & 3u;  // TMEM lane quarter this warp may touch
         const uint32_t row_in_tile = q * 32 + lane;
+        const uint32_t epi_thread = set * 128 + (warp - (set ? kFirstEpilogueWarpB : 2)) * 32 + lane;
         const uint32_t epi_leader = (warp == 2 && lane == 0);
         const uint32_t acc_lane = tmem_acc + ((q * 32) << 16);
-        constexpr uint32_t kChunks = kStageRows / 16;  // 16-column TMEM loads per staging pass
+        // this warp's eight 16-column TMEM loads of a tile: within every staging pass the first
+        // set takes the first half of the pass's activation rows, the second set the other half
+        constexpr uint32_t kHalfRows = kStageRows / 2, kPerPass = kHalfRows / 16;
+        constexpr uint32_t kLoads = BN / 2 / 16;
+        auto col_of = [&](uint32_t k) {
+            return (k / kPerPass) * kStageRows + set * kHalfRows + (k % kPerPass) * 16;
+        };
         for (uint32_t i = 0; i < my_tiles && ok; ++i) {
             const uint32_t tile = blockIdx.x + i * gridDim.x;
             const uint32_t n0 = (tile / p.m_tiles) * BM, m0 = (tile % p.m_tiles) * BN;
@@ -419,18 +432,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             // the rows' factors go to shared memory while the MMAs still run: a global load per
             // value inside the read-out would wait for L2 every time (the L1 left beside 227 KB
             // of shared memory is small and the dequantisers stream through it)
-            #pragma unroll
-            for (uint32_t h = 0; h < BN / 128; ++h) {
-                const uint32_t r = h * 128 + (warp - 2) * 32 + lane;
-                row_scales[r] = m0 + r < p.M ? __ldg(p.row_scale + m0 + r) : 1.0f;
-            }
+            row_scales[epi_thread] = m0 + epi_thread < p.M ? __ldg(p.row_scale + m0 + epi_thread) : 1.0f;
             ok = ptx::mbar_wait_suspended(bar(kBarAccFull), i & 1u);
             if (!ok) break;
             if (warp == 2 && lane == 0) NF4_PTS(100 + 2 * (i & 3u));
-            if (warp == 2 && lane == 0 && i == 0) NF4_PTS(121);
             ptx::tc_fence_after();
             uint32_t va[16], vb[16];
-            tmem_ld16(acc_lane, va);
+            tmem_ld16(acc_lane + col_of(0), va);
             // staging layout: [kStageRows activation rows][BM weight rows]
             auto stage_chunk = [&](const uint32_t (&v)[16], uint32_t col) {
                 const uint32_t r0 = col % kStageRows;
@@ -455,47 +463,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                             __float2bfloat16_rn(f);
                 }
             };
-            for (uint32_t pass = 0; pass < BN / kStageRows; ++pass) {
-                // the TMA store that last read the staging buffer must be done with it
-                if (epi_leader) ptx::tma_store_wait_read<0>();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                for (uint32_t c = 0; c < kChunks; c += 2) {
-                    const uint32_t col = pass * kStageRows + c * 16;
-                    if (warp == 2 && lane == 0 && i == 2) NF4_PTS(108 + (c >> 1));
-                    const bool fine = warp == 2 && lane == 0 && i == 2 && c == 4;
-                    ptx::tmem_wait_ld();
-                    if (fine) NF4_PTS(116);
-                    tmem_ld16(acc_lane + col + 16, vb);
-                    if (fine) NF4_PTS(117);
-                    stage_chunk(va, col);
-                    if (fine) NF4_PTS(118);
-                    ptx::tmem_wait_ld();
-                    if (fine) NF4_PTS(119);
-                    if (col + 32 < BN) {
-                        tmem_ld16(acc_lane + col + 32, va);
-                    } else {
-                        // accumulator fully read: hand it back to the MMA threads
-                        ptx::tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty));
-                        if (warp == 2 && lane == 0) NF4_PTS(101 + 2 * (i & 3u));
-                        if (warp == 2 && lane == 0 && i == 0) NF4_PTS(122);
-                    }
-                    stage_chunk(vb, col + 16);
-                    if (fine) NF4_PTS(120);
+            for (uint32_t k = 0; k < kLoads; k += 2) {
+                if (k % kPerPass == 0) {
+                    // the TMA store that last read the staging buffer must be done with it
+                    if (epi_leader) ptx::tma_store_wait_read<0>();
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
                 }
-                ptx::fence_proxy_async();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (epi_leader) {
-                    ptx::tma_store_2d(&tmap_y, ptx::smem_addr(epi), (int32_t)n0,
-                                      (int32_t)(m0 + pass * kStageRows));
-                    ptx::tma_store_commit();
+                ptx::tmem_wait_ld();
+                tmem_ld16(acc_lane + col_of(k + 1), vb);
+                stage_chunk(va, col_of(k));
+                ptx::tmem_wait_ld();
+                if (k + 2 < kLoads) {
+                    tmem_ld16(acc_lane + col_of(k + 2), va);
+                } else {
+                    // this warp's part of the accumulator is read: hand it back to the MMA threads
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty));
+                    if (warp == 2 && lane == 0) NF4_PTS(101 + 2 * (i & 3u));
+                }
+                stage_chunk(vb, col_of(k + 1));
+                if ((k + 2) % kPerPass == 0) {
+                    ptx::fence_proxy_async();
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (epi_leader) {
+                        ptx::tma_store_2d(&tmap_y, ptx::smem_addr(epi), (int32_t)n0,
+                                          (int32_t)(m0 + (k / kPerPass) * kStageRows));
+                        ptx::tma_store_commit();
+                    }
                 }
             }
         }
         if (epi_leader) ptx::tma_store_wait<0>();
         if (!ok && lane == 0) atomicExch(&g_prefill_error, 3);
-    } else if (warp >= kFirstExpanderWarp) {
+    } else if (warp >= kFirstExpanderWarp && warp < kFirstEpilogueWarpB) {
         // ============================ dequantisers ============================
         // Four groups of four warps; group g takes the main stages (adapter stages need no
         // dequantiser) whose running number over this CTA's tiles is g modulo 4.
@@ -556,21 +557,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             const uint32_t s = cnt % kAStages, ph = (cnt / kAStages) & 1u;
             const uint32_t dst = lane_base + s * kAStageCols;
             const bool stamp = q == 0 && lane == 0 && cnt >= kTsFirst && cnt < kTsFirst + 8;
-            uint32_t out[16];
-            expand_half(tables, rs.c0, rs.scale, out);
+            uint32_t lo[16], hi[16];
+            expand_half(tables, rs.c0, rs.scale, lo);
+            expand_half(tables, rs.c1, rs.scale, hi);
             if (stamp) NF4_PTS(64 + 4 * (cnt - kTsFirst));
             if (!ptx::mbar_wait_suspended(bar(kBarAEmpty + s), ph ^ 1u)) return false;
             if (stamp) NF4_PTS(65 + 4 * (cnt - kTsFirst));
             ptx::tc_fence_after();
 #ifndef NF4_PREFILL_FAKE_STORE  // measurement aid: what the stage costs without the TMEM stores
-            tmem_st16(dst, out);
-#endif
-            expand_half(tables, rs.c1, rs.scale, out);
-#ifndef NF4_PREFILL_FAKE_STORE
-            tmem_st16(dst + 16, out);
+            tmem_st32(dst, lo, hi);
             ptx::tmem_wait_st();
 #else
-            if (out[3] == 0x12345678u) NF4_PTS(127);  // keeps the expansion alive
+            if (lo[3] == 0x12345678u && hi[5] == 0x12345678u) NF4_PTS(127);  // keeps the expansion alive
 #endif
             ptx::tc_fence_before();
             __syncwarp();
