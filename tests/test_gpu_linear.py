@@ -285,6 +285,8 @@ def test_qwen2_7b_block_decode_batch_8(oracle, dq):
     (512, 1024, 384, 64, True, True),     # double-quantized scales, full-chunk adapter
     (257, 192, 136, 80, False, False),    # adapter wider than one 64-chunk
     (128, 3584, 512, 16, True, False),    # Qwen2-7B k/v projection
+    (40, 128, 72, 12, False, True),       # rank not a multiple of 8: LoRA B is not TMA-readable, general kernel
+    (520, 256, 304, 8, False, False),     # three activation tiles x three weight tiles, narrow adapter
 ])
 def test_prefill_shapes(oracle, M, K, N, r, dq, bias):
     c = make_case(oracle, 5000 + M + K + N, M, K, N, r, dq=dq, bias=bias)

@@ -612,13 +612,44 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 }
 
 // ---- pre-pass: f16 activations, row scales and the LoRA intermediate ---------------------
-// One CTA per 16 rows of x.
-//   1. row_scale[m] = 1, or the power of two that brings a row whose magnitude exceeds 32768
-//      back under it; xh[m][k] = f16(x[m][k] / row_scale[m]) (exact inside f16's range).
+// One CTA per 16 rows of x, sixteen warps splitting K.  x is read once:
+//   1. xh[m][k] = f16(x[m][k]) is written at once (exact inside f16's range) while the row
+//      maxima are collected; row_scale[m] = 1, or the power of two that brings a row whose
+//      magnitude exceeds 32768 back under it, in which case that row is converted again as
+//      f16(x / row_scale) at the end (rare).
 //   2. with an adapter: T = lora_scale * (x A^T) / row_scale, written as bf16 hi / lo halves:
 //      T[m][c] for c < 64*chunks holds bf16(T), T[m][64*chunks + c] holds bf16(T - bf16(T));
-//      columns beyond the rank are zero.  Eight warps split K and use warp MMAs.
-constexpr int kTThreads = 256;
+//      columns beyond the rank are zero.  The same registers of x feed warp MMAs against A.
+// k is walked in 32-wide pieces; inside a piece thread t owns k = 8t .. 8t+7 so that both
+// operands are read with 16-byte loads (a consistent permutation of k on A and B).  The loads
+// of the next piece are in flight while a piece is multiplied.
+constexpr int kTThreads = 512;
+constexpr int kTWarps = kTThreads / 32;
+
+struct PrepassPiece {
+    uint4 xa, xb;   // rows g and g + 8 of the slab
+    uint4 bv[8];    // rows 8u + g of this 64-rank chunk of A
+};
+
+__device__ __forceinline__ uint32_t bf16x2_absmax_bits(uint32_t w, uint32_t mx) {
+    // |bf16| as the top half of an f32 pattern; NaNs are left out of the maximum
+    const uint32_t lo = (w << 16) & 0x7fff0000u, hi = w & 0x7fff0000u;
+    if (lo <= 0x7f800000u) mx = max(mx, lo);
+    if (hi <= 0x7f800000u) mx = max(mx, hi);
+    return mx;
+}
+
+__device__ __forceinline__ uint4 bf16x8_to_f16x8(const uint4 &v, float is) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+    #pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const __half2 h = __floats2half2_rn(__uint_as_float(w[q] << 16) * is,
+                                            __uint_as_float(w[q] & 0xffff0000u) * is);
+        o[q] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
 
 __global__ void __launch_bounds__(kTThreads)
 prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
@@ -632,96 +663,115 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t m0 = blockIdx.x * 16;
     const uint32_t rows = min(16u, M - m0);
+    const bool row_a = g < rows, row_b = g + 8 < rows;
+    const uint32_t pieces = (K + 31) / 32, n_it = (pieces + kTWarps - 1) / kTWarps;
+    const size_t off_a = (size_t)(m0 + g) * K, off_b = (size_t)(m0 + g + 8) * K;
 
-    // ---- 1. row maxima -> scales -> f16 copy (K is a multiple of 8, rows are 16-byte aligned)
     if (threadIdx.x < 16) row_max_bits[threadIdx.x] = 0;
-    __syncthreads();
-    const uint32_t vec_per_row = K / 8;
-    for (uint32_t i = threadIdx.x; i < rows * vec_per_row; i += kTThreads) {
-        const uint32_t r = i / vec_per_row, c = i % vec_per_row;
-        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + r) * K) + c);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        uint32_t mx = 0;
-        #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            // |bf16| as the top half of an f32 pattern; NaNs are left out of the maximum
-            const uint32_t lo = (w[q] << 16) & 0x7fff0000u, hi = w[q] & 0x7fff0000u;
-            if (lo <= 0x7f800000u) mx = max(mx, lo);
-            if (hi <= 0x7f800000u) mx = max(mx, hi);
-        }
-        atomicMax(&row_max_bits[r], mx);
-    }
-    __syncthreads();
-    if (threadIdx.x < 16) {
-        const float mx = __uint_as_float(row_max_bits[threadIdx.x]);
-        float sc = 1.0f;
-        if (mx > 32768.0f && mx < __int_as_float(0x7f800000)) {
-            int e;
-            frexpf(mx, &e);             // mx = f * 2^e with f in [0.5, 1)
-            sc = ldexpf(1.0f, e - 15);  // mx / sc lands in [16384, 32768)
-        }
-        inv_scale[threadIdx.x] = 1.0f / sc;  // exact: sc is a power of two
-        if (threadIdx.x < rows) row_scale[m0 + threadIdx.x] = sc;
-    }
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < rows * vec_per_row; i += kTThreads) {
-        const uint32_t r = i / vec_per_row, c = i % vec_per_row;
-        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + r) * K) + c);
-        const float is = inv_scale[r];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        uint32_t o[4];
-        #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const __half2 h = __floats2half2_rn(__uint_as_float(w[q] << 16) * is,
-                                                __uint_as_float(w[q] & 0xffff0000u) * is);
-            o[q] = *reinterpret_cast<const uint32_t *>(&h);
-        }
-        reinterpret_cast<uint4 *>(xh + (size_t)(m0 + r) * K)[c] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-    if (rank == 0) return;
+    uint32_t mx_a = 0, mx_b = 0;
 
-    // ---- 2. T = scale * x A^T / row_scale ----
-    const uint32_t ld_t = 2 * 64 * chunks;
-    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+    const uint32_t passes = chunks ? chunks : 1u;
+    for (uint32_t chunk = 0; chunk < passes; ++chunk) {
         for (uint32_t i = threadIdx.x; i < 16 * 65; i += kTThreads) (&red[0][0])[i] = 0.0f;
         __syncthreads();
         float acc[8][4];
         #pragma unroll
         for (int u = 0; u < 8; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
-        // k is walked in 32-wide pieces; inside a piece thread t owns k = 8t .. 8t+7 so that
-        // both operands are read with 16-byte loads (a consistent permutation of k on A and B)
-        for (uint32_t k0 = warp * 32; k0 < K; k0 += 8 * 32) {
-            uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
-            if (k0 + 8 * t + 8 <= K) {
-                if (m0 + g < M) xa = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + g) * K + k0 + 8 * t));
-                if (m0 + g + 8 < M) xb = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + g + 8) * K + k0 + 8 * t));
-            }
+
+        // piece `it` of this warp starts at k = (warp + 16 it) * 32; this thread's 8 values at + 8t
+        auto k_of = [&](uint32_t it) { return (warp + kTWarps * it) * 32 + 8 * t; };
+        auto load = [&](PrepassPiece &pc, uint32_t it) {
+            const uint32_t k = k_of(it);
+            const bool in = it < n_it && k + 8 <= K;
+            pc.xa = pc.xb = make_uint4(0, 0, 0, 0);
+            if (in && row_a) pc.xa = __ldg(reinterpret_cast<const uint4 *>(x + off_a + k));
+            if (in && row_b) pc.xb = __ldg(reinterpret_cast<const uint4 *>(x + off_b + k));
             #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const uint32_t j = chunk * 64 + 8 * u + g;
-                uint4 bv = make_uint4(0, 0, 0, 0);
-                if (j < rank && k0 + 8 * t + 8 <= K)
-                    bv = __ldg(reinterpret_cast<const uint4 *>(a + (size_t)j * K + k0 + 8 * t));
-                ptx::mma_16816_bf16(acc[u], xa.x, xb.x, xa.y, xb.y, bv.x, bv.y);
-                ptx::mma_16816_bf16(acc[u], xa.z, xb.z, xa.w, xb.w, bv.z, bv.w);
+                pc.bv[u] = make_uint4(0, 0, 0, 0);
+                if (in && j < rank) pc.bv[u] = __ldg(reinterpret_cast<const uint4 *>(a + (size_t)j * K + k));
+            }
+        };
+        auto process = [&](const PrepassPiece &pc, uint32_t it) {
+            const uint32_t k = k_of(it);
+            if (chunk == 0 && it < n_it && k + 8 <= K) {
+                if (row_a) {
+                    mx_a = bf16x2_absmax_bits(pc.xa.x, bf16x2_absmax_bits(pc.xa.y, mx_a));
+                    mx_a = bf16x2_absmax_bits(pc.xa.z, bf16x2_absmax_bits(pc.xa.w, mx_a));
+                    *reinterpret_cast<uint4 *>(xh + off_a + k) = bf16x8_to_f16x8(pc.xa, 1.0f);
+                }
+                if (row_b) {
+                    mx_b = bf16x2_absmax_bits(pc.xb.x, bf16x2_absmax_bits(pc.xb.y, mx_b));
+                    mx_b = bf16x2_absmax_bits(pc.xb.z, bf16x2_absmax_bits(pc.xb.w, mx_b));
+                    *reinterpret_cast<uint4 *>(xh + off_b + k) = bf16x8_to_f16x8(pc.xb, 1.0f);
+                }
+            }
+            if (rank) {
+                #pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    ptx::mma_16816_bf16(acc[u], pc.xa.x, pc.xb.x, pc.xa.y, pc.xb.y, pc.bv[u].x, pc.bv[u].y);
+                    ptx::mma_16816_bf16(acc[u], pc.xa.z, pc.xb.z, pc.xa.w, pc.xb.w, pc.bv[u].z, pc.bv[u].w);
+                }
+            }
+        };
+        PrepassPiece p0, p1;
+        load(p0, 0);
+        for (uint32_t it = 0; it < n_it; it += 2) {
+            load(p1, it + 1);
+            process(p0, it);
+            load(p0, it + 2);
+            process(p1, it + 1);
+        }
+
+        if (chunk == 0) {
+            atomicMax(&row_max_bits[g], mx_a);
+            atomicMax(&row_max_bits[g + 8], mx_b);
+        }
+        if (rank) {
+            #pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                atomicAdd(&red[g][8 * u + 2 * t], acc[u][0]);
+                atomicAdd(&red[g][8 * u + 2 * t + 1], acc[u][1]);
+                atomicAdd(&red[g + 8][8 * u + 2 * t], acc[u][2]);
+                atomicAdd(&red[g + 8][8 * u + 2 * t + 1], acc[u][3]);
             }
         }
-        #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            atomicAdd(&red[g][8 * u + 2 * t], acc[u][0]);
-            atomicAdd(&red[g][8 * u + 2 * t + 1], acc[u][1]);
-            atomicAdd(&red[g + 8][8 * u + 2 * t], acc[u][2]);
-            atomicAdd(&red[g + 8][8 * u + 2 * t + 1], acc[u][3]);
-        }
         __syncthreads();
-        for (uint32_t i = threadIdx.x; i < 16 * 64; i += kTThreads) {
-            const uint32_t r = i >> 6, c = i & 63u;
-            if (m0 + r < M) {
-                const float v = red[r][c] * scale * inv_scale[r];
-                const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-                const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-                t_out[(size_t)(m0 + r) * ld_t + chunk * 64 + c] = hi;
-                t_out[(size_t)(m0 + r) * ld_t + 64 * chunks + chunk * 64 + c] = lo;
+        if (chunk == 0) {
+            if (threadIdx.x < 16) {
+                const float mx = __uint_as_float(row_max_bits[threadIdx.x]);
+                float sc = 1.0f;
+                if (mx > 32768.0f && mx < __int_as_float(0x7f800000)) {
+                    int e;
+                    frexpf(mx, &e);             // mx = f * 2^e with f in [0.5, 1)
+                    sc = ldexpf(1.0f, e - 15);  // mx / sc lands in [16384, 32768)
+                }
+                inv_scale[threadIdx.x] = 1.0f / sc;  // exact: sc is a power of two
+                if (threadIdx.x < rows) row_scale[m0 + threadIdx.x] = sc;
+            }
+            __syncthreads();
+            // rows beyond f16's range: convert again, scaled
+            for (uint32_t r = 0; r < rows; ++r) {
+                const float is = inv_scale[r];
+                if (is == 1.0f) continue;
+                for (uint32_t c = threadIdx.x; c < K / 8; c += kTThreads) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + r) * K) + c);
+                    reinterpret_cast<uint4 *>(xh + (size_t)(m0 + r) * K)[c] = bf16x8_to_f16x8(v, is);
+                }
+            }
+        }
+        if (rank) {
+            const uint32_t ld_t = 2 * 64 * chunks;
+            for (uint32_t i = threadIdx.x; i < 16 * 64; i += kTThreads) {
+                const uint32_t r = i >> 6, c = i & 63u;
+                if (m0 + r < M) {
+                    const float v = red[r][c] * scale * inv_scale[r];
+                    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+                    const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+                    t_out[(size_t)(m0 + r) * ld_t + chunk * 64 + c] = hi;
+                    t_out[(size_t)(m0 + r) * ld_t + 64 * chunks + chunk * 64 + c] = lo;
+                }
             }
         }
         __syncthreads();
