@@ -293,6 +293,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     if (warp == 0) {
         // ============================ TMA producer ============================
         if (lane == 0) {
+            // the f16 activations and T come from the pre-pass, which may still be running: this
+            // kernel is its programmatic dependent (the dequantisers start on the weights at once)
+            ptx::pdl_wait();
             uint32_t cnt = 0;
             for (uint32_t i = 0; i < my_tiles && ok; ++i) {
                 const uint32_t tile = blockIdx.x + i * gridDim.x;
@@ -424,6 +427,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         auto col_of = [&](uint32_t k) {
             return (k / kPerPass) * kStageRows + set * kHalfRows + (k % kPerPass) * 16;
         };
+        ptx::pdl_wait();  // the rows' factors come from the pre-pass
         for (uint32_t i = 0; i < my_tiles && ok; ++i) {
             const uint32_t tile = blockIdx.x + i * gridDim.x;
             const uint32_t n0 = (tile / p.m_tiles) * BM, m0 = (tile % p.m_tiles) * BN;
@@ -663,6 +667,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t m0 = blockIdx.x * 16;
     const uint32_t rows = min(16u, M - m0);
+    ptx::pdl_launch_dependents();  // the GEMM may set itself up and start on the weights
     const bool row_a = g < rows, row_b = g + 8 < rows;
     const uint32_t pieces = (K + 31) / 32, n_it = (pieces + kTWarps - 1) / kTWarps;
     const size_t off_a = (size_t)(m0 + g) * K, off_b = (size_t)(m0 + g + 8) * K;
@@ -916,7 +921,8 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = true;
         }
-        prefill_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_b, map_y, p);
+        NF4_TRY(launch_maybe_overlapped(prefill_kernel<true>, dim3(grid), dim3(kThreads), smem, stream,
+                                        pdl_enabled(), map_x, map_t, map_b, map_y, p));
     } else {
         static bool configured = false;
         if (!configured) {
@@ -924,7 +930,8 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = true;
         }
-        prefill_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_t, map_b, map_y, p);
+        NF4_TRY(launch_maybe_overlapped(prefill_kernel<false>, dim3(grid), dim3(kThreads), smem, stream,
+                                        pdl_enabled(), map_x, map_t, map_b, map_y, p));
     }
     count_launch();
     return check_cuda(cudaGetLastError(), "prefill_kernel launch");
