@@ -331,6 +331,12 @@ def test_prefill_linearity_at_full_config3_size(oracle):
     ref = x1[rows].double() @ deq.t() + 2.0 * (x1[rows].double() @ a.double().t()) @ b[:256].double().t()
     got = y1[rows, :256].double()
     assert ((got - ref).norm() / ref.norm()).item() < 1e-3 + 2.0 ** -9
+    # the last 128 weight rows belong to the tiles of the last, partly filled round
+    for rows in (slice(1000, 1016), slice(1080, 1096), slice(2040, 2048)):
+        deq = packed.dequantize().view(N, K)[N - 128:].double()
+        ref = x1[rows].double() @ deq.t() + 2.0 * (x1[rows].double() @ a.double().t()) @ b[N - 128:].double().t()
+        got = y1[rows, N - 128:].double()
+        assert ((got - ref).norm() / ref.norm()).item() < 1e-3 + 2.0 ** -9
 
 
 @pytest.mark.parametrize("layout_name,M,K,N,r", [("out_in", 8, 256, 192, 16), ("out_in", 40, 512, 320, 8),
