@@ -15,7 +15,8 @@ streams its weight from HBM.  `e2e` is the same metric through the host-pointer 
 (pinned host x in, host y out, copies inside the timed region).
 
 With N > 1 (torchrun) every rank owns one [11008, 4096] column shard of an N-times wider
-layer and the ranks all-gather y over NCCL (weak scaling).
+layer and the ranks all-gather the step's outputs over NCCL, one collective per step (weak
+scaling).
 
 `--impl reference` times the reference's CPU algorithm for the same step on the host cores:
 dequantize the packed weight to f32 (single-threaded scalar loop, as the reference's
@@ -268,8 +269,14 @@ def run_own(args) -> None:
     lora_b = (torch.randn(N, RANK, device=dev, generator=g) * 0.01).bfloat16()
     g = torch.Generator(device=dev).manual_seed(4)
     xs = {m: torch.randn(m, K, device=dev, generator=g).bfloat16() for m in MS}
-    ys = {m: torch.zeros(m, N, device=dev, dtype=torch.bfloat16) for m in MS}
-    ygs = {m: torch.zeros(world, m, N, device=dev, dtype=torch.bfloat16) for m in MS}
+    # the three passes write consecutive row ranges of one buffer, so that the sharded runs can
+    # gather a step's outputs with a single collective
+    y_all = torch.zeros(sum(MS), N, device=dev, dtype=torch.bfloat16)
+    ys, row0 = {}, 0
+    for m in MS:
+        ys[m] = y_all[row0:row0 + m]
+        row0 += m
+    y_gathered = torch.zeros(world, sum(MS), N, device=dev, dtype=torch.bfloat16)
     ws_bytes = max(int(lib.nf4_linear_workspace_bytes(m, K, N, RANK)) for m in MS)
     workspaces = {m: torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev) for m in MS}
 
@@ -295,8 +302,8 @@ def run_own(args) -> None:
         c = i % N_COPIES
         for m in MS:
             _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m)]), stream))
-            if world > 1:
-                dist.all_gather_into_tensor(ygs[m], ys[m])
+        if world > 1:
+            dist.all_gather_into_tensor(y_gathered, y_all)  # every rank's slab of the step's outputs
 
     def barrier():
         torch.cuda.synchronize()
@@ -461,7 +468,7 @@ def run_own(args) -> None:
                                 "per step",
                        "launch": launch_mode,
                        "sharding": "none" if world == 1 else
-                       f"{world} column shards of a [{world * N}, {K}] layer, NCCL all-gather of y"},
+                       f"{world} column shards of a [{world * N}, {K}] layer, one NCCL all-gather of y per step"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(gpu_launches), "clocks": clocks,
             "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
