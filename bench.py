@@ -15,8 +15,8 @@ streams its weight from HBM.  `e2e` is the same metric through the host-pointer 
 (pinned host x in, host y out, copies inside the timed region).
 
 With N > 1 (torchrun) every rank owns one [11008, 4096] column shard of an N-times wider
-layer and the ranks all-gather the step's outputs over NCCL, one collective per step (weak
-scaling).
+layer and the ranks all-gather the step's outputs over NCCL, one collective per step on its
+own stream beside the next step's passes (weak scaling).
 
 `--impl reference` times the reference's CPU algorithm for the same step on the host cores:
 dequantize the packed weight to f32 (single-threaded scalar loop, as the reference's
@@ -271,16 +271,19 @@ def run_own(args) -> None:
     xs = {m: torch.randn(m, K, device=dev, generator=g).bfloat16() for m in MS}
     # the three passes write consecutive row ranges of one buffer, so that the sharded runs can
     # gather a step's outputs with a single collective
-    y_all = torch.zeros(sum(MS), N, device=dev, dtype=torch.bfloat16)
+    # (two such buffers, used by alternate steps: the gather of one step runs on its own stream
+    # beside the passes of the next)
+    y_all = [torch.zeros(sum(MS), N, device=dev, dtype=torch.bfloat16) for _ in range(2)]
     ys, row0 = {}, 0
     for m in MS:
-        ys[m] = y_all[row0:row0 + m]
+        for par in range(2):
+            ys[(m, par)] = y_all[par][row0:row0 + m]
         row0 += m
-    y_gathered = torch.zeros(world, sum(MS), N, device=dev, dtype=torch.bfloat16)
+    y_gathered = [torch.zeros(world, sum(MS), N, device=dev, dtype=torch.bfloat16) for _ in range(2)]
     ws_bytes = max(int(lib.nf4_linear_workspace_bytes(m, K, N, RANK)) for m in MS)
     workspaces = {m: torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev) for m in MS}
 
-    def make_args(c, m):
+    def make_args(c, m, par=0):
         a = _lib.LinearArgs()
         a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
         a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16
@@ -290,20 +293,40 @@ def run_own(args) -> None:
         a.absmax = weights[c].absmax.data_ptr()
         a.lora_a, a.lora_b = lora_a.data_ptr(), lora_b.data_ptr()
         a.lora_rank, a.lora_scale = RANK, SCALE
-        a.y, a.ldy = ys[m].data_ptr(), N
+        a.y, a.ldy = ys[(m, par)].data_ptr(), N
         a.workspace, a.workspace_bytes = workspaces[m].data_ptr(), workspaces[m].numel()
         return a
 
-    call_args = {(c, m): make_args(c, m) for c in range(N_COPIES) for m in MS}
+    call_args = {(c, m, par): make_args(c, m, par) for c in range(N_COPIES) for m in MS for par in range(2)}
     log("weights quantized, arguments built")
 
+    comm = torch.cuda.Stream() if world > 1 else None
+    gathered = [None, None]  # per buffer: the event after the gather that last read it
+
     def step(i: int) -> None:
-        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        c = i % N_COPIES
+        cur = torch.cuda.current_stream()
+        stream = ctypes.c_void_p(cur.cuda_stream)
+        c, par = i % N_COPIES, i & 1
+        if world > 1 and gathered[par] is not None:
+            cur.wait_event(gathered[par])  # the buffer is written again only after its gather
         for m in MS:
-            _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m)]), stream))
+            _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, par)]), stream))
         if world > 1:
-            dist.all_gather_into_tensor(y_gathered, y_all)  # every rank's slab of the step's outputs
+            # every rank's slab of the step's outputs, gathered beside the next step's passes
+            done = torch.cuda.Event()
+            done.record(cur)
+            comm.wait_event(done)
+            with torch.cuda.stream(comm):
+                dist.all_gather_into_tensor(y_gathered[par], y_all[par])
+                gathered[par] = torch.cuda.Event()
+                gathered[par].record(comm)
+
+    def drain() -> None:
+        """The launching stream waits for the gathers still in flight (and joins their stream)."""
+        for par in range(2):
+            if gathered[par] is not None:
+                torch.cuda.current_stream().wait_event(gathered[par])
+                gathered[par] = None
 
     def barrier():
         torch.cuda.synchronize()
@@ -316,6 +339,7 @@ def run_own(args) -> None:
     with torch.cuda.stream(side):
         for i in range(max(args.warmup, 3)):
             step(i)
+        drain()
     barrier()
     log("warm-up done")
     launches0 = _lib.launch_count()
@@ -326,9 +350,11 @@ def run_own(args) -> None:
         with torch.cuda.graph(graph, stream=side):
             for i in range(args.steps):
                 step(i)
+            drain()
     except Exception as e:  # capture refused (e.g. a collective that cannot be captured)
         graph = None
         launch_mode = f"eager ({type(e).__name__})"
+        gathered[0] = gathered[1] = None
         torch.cuda.synchronize()
     gpu_launches = _lib.launch_count() - launches0
     if world > 1:
@@ -357,6 +383,7 @@ def run_own(args) -> None:
             e0.record()
             for i in range(args.steps):
                 step(i)
+            drain()
             e1.record()
         gpu_launches = _lib.launch_count() - launches0
     barrier()
