@@ -66,6 +66,18 @@ NF4_API const char *nf4_last_error(void);
 /* Number of kernels this library has launched in this process (all threads). */
 NF4_API uint64_t nf4_kernel_launch_count(void);
 
+/* Failure report of the tensor-core kernels.  Every device-side wait in them (on a TMA copy, on
+ * another warp) is bounded: when one gives up, the kernel records a code in a per-device flag
+ * and returns instead of hanging or trapping, and its output is void.  This call copies the
+ * current device's three flags to the host (it synchronises with the device), clears them and
+ * returns NF4_OK when all are zero, NF4_ERR_TIMEOUT when a wait gave up, NF4_ERR_CUDA when a
+ * launch found its shared memory laid out differently from what it was built for.  The `*_host`
+ * entry points make this check themselves before they return; callers of the `*_dev` entry
+ * points make it where they synchronise.  Any pointer may be NULL.
+ * The reference has no counterpart: its forward cannot fail (src/qwennet.rs:238-241); the
+ * Rust shim maps a non-zero status to anyhow::Error (src/lib.rs:16-32). */
+NF4_API int32_t nf4_device_status(int32_t *decode, int32_t *decode_split_k, int32_t *prefill);
+
 /* Diagnostic: runs the kernels' threshold bisection and the reference's literal
  * sixteen-way scan (src/quantize.rs:208-219) on `count` consecutive f32 bit patterns
  * starting at `first_bits` (only NaNs and |v| <= 65536 are compared: a normalised value
@@ -187,13 +199,18 @@ typedef struct nf4_linear_args {
     float lora_scale;           /* (alpha / rank) as f32, applied last (src/quantize.rs:623) */
     void *y;                    /* [rows, ldy] */
     uint64_t ldy;               /* row stride of y in elements; 0 means d_out */
-    void *workspace;            /* nf4_linear_workspace_bytes() bytes, 256-byte aligned */
+    void *workspace;            /* nf4_linear_workspace_bytes() bytes, 256-byte aligned; its first 256
+                                   bytes must be zero at the first call that uses it (cudaMemset once
+                                   after allocating); every call leaves them zero */
     uint64_t workspace_bytes;
 } nf4_linear_args;
 
-/* Scratch the forward needs for these sizes: the LoRA intermediate x*A^T, and for more than 16
- * rows the f16 copy of x with its per-row power-of-two scales that the tensor-core kernel reads;
- * for at most 16 rows also split-K partial sums when d_in exceeds 4096. */
+/* Scratch the forward needs for these sizes: the LoRA intermediate x*A^T behind 256 bytes of flag
+ * words (the CTAs that compute x*A^T and the CTAs that read it meet on them; zero before the first
+ * use, zero after every call), and for more than 16 rows the f16 copy of x with its per-row
+ * power-of-two scales that the tensor-core kernel reads; for at most 16 rows also split-K partial
+ * sums when d_in exceeds 4096.  One workspace serves one stream: calls that may overlap on the
+ * GPU need a workspace each. */
 NF4_API uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                     uint32_t lora_rank);
 
@@ -207,17 +224,18 @@ NF4_API int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream
  * would synchronise the whole device, or an FFI shim with no allocator of its own.  Such a
  * caller cannot supply the workspace nf4_linear_forward_dev asks for.  This entry point takes
  * the same arguments (args->workspace / workspace_bytes are ignored) and keeps its scratch --
- * the adapter intermediate x*A^T -- in a fixed array inside the library's device image,
- * nf4_linear_noalloc_scratch_bytes() = 4096 bytes, which every GPU that loads the library
+ * the adapter intermediate x*A^T and two flag words -- in a fixed array inside the library's device
+ * image, nf4_linear_noalloc_scratch_bytes() = 4352 bytes, which every GPU that loads the library
  * holds until the process exits.  It calls no cudaMalloc, cudaFree or other allocating routine.
  *
- * Limits: the decode shapes only (rows <= 16, bf16 x/y, NF4_LAYOUT_OUT_IN, d_in a multiple of 64
+ * Limits: the decode shapes only (rows <= 16, bf16 x/y, NF4_LAYOUT_OUT_IN, d_in a multiple of 256
  * and <= 4096) with rows * lora_rank * 4 <= 4096 bytes (e.g. 16 rows at rank 64); anything
  * larger is refused with NF4_ERR_INVALID_ARG / NF4_ERR_UNSUPPORTED and a message.
  * The first call on each device looks up the array's device address (with that device
  * current); make that first call outside any stream capture.
  * All calls on a device share the one array, which keeps whatever the last call left in it
- * (nothing in it has to start at zero: each call rewrites what it reads).  Two calls whose
+ * (its flag words start at zero with the library's device image and every call puts them back
+ * to zero; the intermediate is rewritten by each call before it is read: callers clear nothing).  Two calls whose
  * kernels overlap on the GPU -- different streams, no dependency -- race on it; order them. */
 NF4_API uint64_t nf4_linear_noalloc_scratch_bytes(void);
 NF4_API int32_t nf4_linear_forward_noalloc_dev(const nf4_linear_args *args, void *stream);

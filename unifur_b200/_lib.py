@@ -61,6 +61,7 @@ SIGNATURES = {
     "nf4_version": (_i32, []),
     "nf4_last_error": (C.c_char_p, []),
     "nf4_kernel_launch_count": (_u64, []),
+    "nf4_device_status": (_i32, [C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32)]),
     "nf4_selfcheck_code_selection": (_i32, [_u64, _u64, C.POINTER(_u64)]),
     "nf4_selfcheck_quantize_fast_path": (_i32, [_u64, _u64, _f32, C.POINTER(_u64)]),
     "nf4_quantize_transposed_workspace_bytes": (_u64, [_u64, _u64]),

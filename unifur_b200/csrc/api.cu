@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 
@@ -76,6 +77,31 @@ struct Arena {
 };
 thread_local Arena t_arena;
 
+// A small zero-filled device buffer per host thread and device: the decode kernel's workspace
+// (flag words that must be zero at first use and are left zero, then the adapter intermediate).
+struct ZeroScratch {
+    static constexpr size_t kBytes = 8192;
+    void *ptr = nullptr;
+    int device = -1;
+    int32_t get(void **out) {
+        int dev = 0;
+        NF4_CUDA_TRY(cudaGetDevice(&dev));
+        if (!ptr || dev != device) {
+            if (ptr) cudaFree(ptr);
+            ptr = nullptr;
+            NF4_CUDA_TRY(cudaMalloc(&ptr, kBytes));
+            NF4_CUDA_TRY(cudaMemset(ptr, 0, kBytes));
+            device = dev;
+        }
+        *out = ptr;
+        return NF4_OK;
+    }
+    ~ZeroScratch() {
+        if (ptr) cudaFree(ptr);
+    }
+};
+thread_local ZeroScratch t_zero_scratch;
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Carves aligned sub-buffers out of the arena.
@@ -91,6 +117,72 @@ struct Carver {
         return p;
     }
 };
+
+// ---- device-side failure flags ----------------------------------------------------
+// Device addresses of the three kernels' flags, looked up once per device.
+int32_t flag_ptrs(int **out3) {
+    static std::mutex mu;
+    static int *cache[64][3] = {};
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NF4_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev][0]) {
+        int *p0 = nullptr, *p1 = nullptr, *p2 = nullptr;
+        NF4_TRY(decode_error_flag_ptr(&p0));
+        NF4_TRY(decode2_error_flag_ptr(&p1));
+        NF4_TRY(prefill_error_flag_ptr(&p2));
+        cache[dev][1] = p1;
+        cache[dev][2] = p2;
+        cache[dev][0] = p0;
+    }
+    for (int i = 0; i < 3; ++i) out3[i] = cache[dev][i];
+    return NF4_OK;
+}
+
+// Turns flag values already on the host into a status; flags that were set are cleared.
+int32_t report_flags(int *const *ptrs, const int *v) {
+    for (int i = 0; i < 3; ++i)
+        if (v[i]) NF4_CUDA_TRY(cudaMemset(ptrs[i], 0, sizeof(int)));
+    if (v[0] == 4)
+        return fail(NF4_ERR_CUDA, "decode kernel: dynamic shared memory does not start where the kernel "
+                                  "expects it; the launch produced no output");
+    if (v[0] || v[1] || v[2])
+        return fail(NF4_ERR_TIMEOUT, "a bounded device-side wait gave up (decode %d, decode split-K %d, "
+                                     "prefill %d): the outputs of the calls since the last check are void",
+                    v[0], v[1], v[2]);
+    return NF4_OK;
+}
+
+// Pinned host words the host-pointer entry points copy the flags into beside their results.
+struct FlagMirror {
+    int *host = nullptr;
+    int32_t get(int **out) {
+        if (!host) NF4_CUDA_TRY(cudaMallocHost(reinterpret_cast<void **>(&host), 3 * sizeof(int)));
+        *out = host;
+        return NF4_OK;
+    }
+    ~FlagMirror() {
+        if (host) cudaFreeHost(host);
+    }
+};
+thread_local FlagMirror t_flag_mirror;
+
+// Which kernel the last nf4_linear_forward_dev of this host thread launched: 0 decode,
+// 1 split-K decode, 2 prefill, -1 a kernel without device-side waits.
+thread_local int t_last_family = -1;
+
+// Enqueues, on `stream`, the copy of the flag of the kernel this thread launched last (ahead of
+// the caller's final synchronise, so that the check costs no synchronisation of its own).
+int32_t flags_enqueue(cudaStream_t stream, int **ptrs, int **mirror) {
+    NF4_TRY(flag_ptrs(ptrs));
+    NF4_TRY(t_flag_mirror.get(mirror));
+    (*mirror)[0] = (*mirror)[1] = (*mirror)[2] = 0;
+    const int f = t_last_family;
+    if (f >= 0)
+        NF4_CUDA_TRY(cudaMemcpyAsync(*mirror + f, ptrs[f], sizeof(int), cudaMemcpyDeviceToHost, stream));
+    return NF4_OK;
+}
 
 inline size_t dtype_bytes(int32_t dt) { return dt == NF4_DTYPE_F32 ? 4 : 2; }
 
@@ -185,6 +277,18 @@ int32_t nf4_selfcheck_quantize_fast_path(uint64_t first_bits, uint64_t count, fl
     NF4_CUDA_TRY(cudaMemcpy(&h, d, 8, cudaMemcpyDeviceToHost));
     *mismatches = h;
     return NF4_OK;
+}
+
+int32_t nf4_device_status(int32_t *decode, int32_t *decode_split_k, int32_t *prefill) {
+    int *ptrs[3];
+    NF4_TRY(flag_ptrs(ptrs));
+    int v[3] = {0, 0, 0};
+    for (int i = 0; i < 3; ++i)
+        NF4_CUDA_TRY(cudaMemcpy(&v[i], ptrs[i], sizeof(int), cudaMemcpyDeviceToHost));
+    if (decode) *decode = v[0];
+    if (decode_split_k) *decode_split_k = v[1];
+    if (prefill) *prefill = v[2];
+    return report_flags(ptrs, v);
 }
 
 uint64_t nf4_num_blocks(uint64_t len) { return (len + kBlock - 1) / kBlock; }
@@ -295,18 +399,21 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     NF4_TRY(validate_linear(args));
     if (args->rows == 0) return NF4_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Two decode kernels: warp-MMA (16-row tiles, d_in <= 4096) and tcgen05 (128-row blocks,
-    // split K, any d_in).  Measured on B200 the first wins wherever it applies;
-    // NF4_DECODE_KERNEL=1 or 2 in the environment pins one of them (for measurements).
-    static const int pin = [] {
-        const char *e = std::getenv("NF4_DECODE_KERNEL");
-        return e ? std::atoi(e) : 0;
-    }();
-    if (pin != 2 && decode_supported(*args)) return decode_forward(*args, s);
-    if (pin != 1 && decode2_supported(*args)) return decode2_forward(*args, s);
-    if (pin == 2 && decode_supported(*args)) return decode_forward(*args, s);
-    if (pin == 1 && decode2_supported(*args)) return decode2_forward(*args, s);
-    if (prefill_supported(*args)) return prefill_forward(*args, s);
+    // rows <= 16: the warp-MMA kernel (d_in <= 4096, whole 256-slices), else the tcgen05 split-K
+    // kernel; more rows: the tcgen05 GEMM; whatever none of them takes: the CUDA-core kernel.
+    if (decode_supported(*args)) {
+        t_last_family = 0;
+        return decode_forward(*args, s);
+    }
+    if (decode2_supported(*args)) {
+        t_last_family = 1;
+        return decode2_forward(*args, s);
+    }
+    if (prefill_supported(*args)) {
+        t_last_family = 2;
+        return prefill_forward(*args, s);
+    }
+    t_last_family = -1;
     return generic_forward(*args, s);
 }
 
@@ -615,9 +722,21 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
     a.ldy = w->d_out;
     a.workspace = ws ? d_ws : nullptr;
     a.workspace_bytes = ws;
+    if (ws && ws <= ZeroScratch::kBytes) {
+        // the decode workspace starts with flag words that must be zero: a buffer kept for it
+        void *zs = nullptr;
+        NF4_TRY(t_zero_scratch.get(&zs));
+        a.workspace = zs;
+    } else if (ws) {
+        NF4_CUDA_TRY(cudaMemsetAsync(d_ws, 0, 256, 0));
+    }
     NF4_TRY(nf4_linear_forward_dev(&a, nullptr));
     NF4_CUDA_TRY(cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, 0));
-    return check_cuda(cudaStreamSynchronize(0), "nf4_weight_linear_forward_host sync");
+    // ... and a wait that gave up in a kernel must not pass for a result
+    int *ptrs[3], *mirror = nullptr;
+    NF4_TRY(flags_enqueue(0, ptrs, &mirror));
+    NF4_TRY(check_cuda(cudaStreamSynchronize(0), "nf4_weight_linear_forward_host sync"));
+    return report_flags(ptrs, mirror);
 }
 
 }  // extern "C"

@@ -2,39 +2,46 @@
 // packed NF4 [N, K] with 64-blocks along K.  HBM-bound: the kernel exists to stream
 // nibbles + scales once at full bandwidth.
 //
-// Data movement.  One CTA per SM owns a contiguous range of W rows; its sixteen warps split K
-// (up to four 64-blocks each).  Every warp streams its own slice -- 16 rows x 128 bytes of
-// nibbles per tile -- global -> shared with per-thread 16-byte asynchronous copies (cp.async,
-// L2 only) into a private ring of a few tiles, rows on a padded stride so that the reads are
-// bank-conflict free; the warps therefore share no barrier while the weights stream.  The block
-// scales of all the CTA's rows are fetched once, whole lines at a time, at kernel start
-// (fetched per warp and tile they cost one load/store-unit tag per 16 bytes, as many as the
-// nibbles themselves).  A first version moved whole tiles with TMA bulk copies issued by a
-// producer warp and met per tile on barriers; it was slower (18 us against 15 us per launch
-// under the profiler), mostly for its per-tile rendezvous and reduction.
+// Data movement.  One CTA per SM owns a contiguous range of W rows.  Its sixteen warps split K
+// into slices of 256 (four 64-blocks); when K is short the warps left over take other 16-row
+// tiles.  Every warp streams its own slice with TMA: one lane asks for a 2-D box of
+// 16 rows x 128 bytes of nibbles (128-byte swizzle) and a box of 16 rows x 4 f32 block scales,
+// both into the warp's private ring of four tiles, and the box's arrival is counted on the
+// warp's own mbarrier.  No warp ever waits for another while the weights stream: there is no
+// producer warp and no CTA-wide barrier inside a pass.  The tensor maps cover this GPU's weight
+// only and the loads are not multicast.  The requests for the first tiles (and the loads of the
+// adapter's A factor) are made BEFORE the kernel waits for its predecessor in the stream
+// (programmatic dependent launch): weights are immutable, so they may be fetched while the
+// kernel that produces x is still running.
 //
-// Math.  Dequantisation is a shared-memory table lookup: one packed byte (two codes)
-// indexes a 256-entry table of half2 {level[lo], level[hi]}, replicated once per
-// lane so that no two lanes share a bank; entries sit 256 bytes apart and the table starts at
-// shared-window address 0x10000, so that one byte permute (code byte into bits 8..15, lane
-// offset below, the constant 0x0001 above) forms the whole address: two instructions per pair
-// of weights.  The looked-up register IS the A operand of a warp MMA (m16n8k16, f16 in / f32
-// accumulate), with W rows on the MMA's M side and the <=16 activation rows on its N side.
-// Each warp keeps its slice of x as f16 B-fragments in registers for the whole kernel.  A
-// block's four MMAs accumulate in one chain (the four blocks of a tile interleave) and the
-// result is scaled by the block's f32 absmax (or its double-quantized decode) -- the scale
-// never touches the f16 path.  What bounds the kernel is instruction issue at four warps per
-// scheduler (one 512-thread CTA with ~120 registers per thread fills the register file).
+// Math.  Dequantisation is a shared-memory table lookup: one packed byte (two codes) indexes a
+// 256-entry table of half2 {level[lo], level[hi]}, replicated once per lane so that no two lanes
+// share a bank; entries sit 256 bytes apart from the start of dynamic shared memory, so one byte
+// permute (code byte into bits 8..15 above the lane's offset) forms the address and the table's
+// base rides in the load's immediate: two instructions per pair of weights.  The looked-up
+// register IS the A operand of a warp MMA (m16n8k16, f16 in / f32 accumulate) with W rows on
+// the MMA's M side (MMA row g holds tile row 2g, row g+8 holds 2g+1: the rows a half-warp reads
+// then fall into different banks of the swizzled box) and the <=16 activation rows on its N
+// side.  Each warp keeps its slice of x as f16 B-fragments in registers for the whole kernel.
+// A block's four MMAs accumulate in one chain and the result is scaled by the block's f32
+// absmax (or its double-quantized decode) -- the scale never touches the f16 path.
 //
-// Reduction.  A warp keeps the partial sums of a pass of tiles in registers (a shift register:
-// the tile being multiplied is slot 0).  At the end of a pass every warp parks them in its own
-// shared-memory slot (the slots take the lookup table's place) and all threads sum the
-// sixteen slots in warp order (so results do not depend on timing), add bias and the LoRA term
-// (T = x A^T comes from a small pre-pass), convert and store.
+// Adapter.  T = x A^T ([M][rank] f32) is needed by every CTA but costs rank * K * 2 bytes of A to
+// compute, so it is computed once per launch: the first `rank` CTAs each take one row of A
+// (their warps hold the matching slices of x already), write their column of T to the workspace
+// and count themselves in on a flag word there.  A CTA picks T up before the last tile of its first pass -- by then
+// the producers have long finished -- with a bounded wait on the flag.  The last CTA to have read
+// T puts the flag words back to zero, which is the state the workspace must have at first use.
+//
+// Reduction.  A warp keeps the partial sums of a pass of tiles in registers.  At the end of a
+// pass every warp parks them -- in its own ring when no more tiles follow (the usual case: a
+// CTA's rows fit one pass), else in the unused upper halves of the table's 256-byte rows -- and
+// all threads sum the slices in a fixed order (so results do not depend on timing), add bias and
+// the LoRA term, convert and store.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -42,62 +49,69 @@
 
 namespace nf4 {
 
-__device__ int g_decode_error = 0;  // set when the launch gave too little shared memory or the one bounded wait gives up
+// Set when the launch's shared-memory window is not where the kernel expects it (4) or a
+// bounded wait gives up (5).  Read and cleared by nf4_device_status().
+__device__ int g_decode_error = 0;
 
-#ifdef NF4_DECODE_TIMING
-// Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
-__device__ long long g_decode_ts[64];
-#define NF4_TS(i) do { if (blockIdx.x == 0 && lane == 0) g_decode_ts[(i)] = clock64(); } while (0)
-#else
-#define NF4_TS(i) do { } while (0)
-#endif
+int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, uint32_t rank,
+                     float *t_out, cudaStream_t stream, bool chained);
 
 namespace {
 
-constexpr int kWarps = 16;           // all of them split K
+constexpr int kWarps = 16;
 constexpr int kDecodeThreads = kWarps * 32;
 constexpr int kTileRows = 16;
-constexpr int kChunk = 64;           // one quantization block of K
-constexpr int kMaxChunksPerWarp = 4; // x fragments live in registers: K <= 16*4*64
-constexpr int kMaxRing = 6;          // tiles per warp ring (one being read, the rest in flight)
-constexpr uint32_t kLutWindow = 0x10000;  // shared-window address of the lookup table
-constexpr int kLutStride = 256;      // bytes between table entries (128 used)
-constexpr int kLutBytes = 256 * kLutStride;
+constexpr int kChunk = 64;         // one quantization block of K
+constexpr int kSliceChunks = 4;    // blocks per warp slice: K <= 16 * 4 * 64
+constexpr int kSliceK = kSliceChunks * kChunk;
+constexpr int kRing = 4;           // tiles per warp ring
 constexpr int kMaxRank = 64;
-constexpr int kSmemLimit = 227 * 1024;
-constexpr int kSmemLeftForPrepass = 3 * 1024;  // so that a CTA of the pre-pass can share the SM
-constexpr int kSlots = kWarps;       // one reduction slot per warp
+constexpr uint32_t kFlagBytes = 256;  // workspace: [ready, done] words, then T
+constexpr uint32_t kWin0 = 1024;   // shared-window address of dynamic shared memory
+constexpr uint32_t kLutStride = 256;
+constexpr uint32_t kLutBytes = 256 * kLutStride;
+constexpr uint32_t kCodesSlot = kTileRows * 128;
+constexpr uint32_t kScaleSlot = kTileRows * 16;
+constexpr uint32_t kSlotIdx = 16;  // partial-sum registers a warp can park (one table row each)
+// byte offsets from the start of dynamic shared memory
+constexpr uint32_t kOffCodes = kLutBytes;
+constexpr uint32_t kOffScales = kOffCodes + kWarps * kRing * kCodesSlot;
+constexpr uint32_t kOffBars = kOffScales + kWarps * kRing * kScaleSlot;
+constexpr uint32_t kOffT = kOffBars + 512;
+constexpr uint32_t kOffDq = kOffT + 16 * kMaxRank * 4;
+constexpr uint32_t kOffLora = kOffDq + 1024;
+constexpr uint32_t kSmemBytes = 227 * 1024;
+constexpr uint32_t kLoraRoom = kSmemBytes - kOffLora;
+static_assert(kWarps * kRing * 8 <= 512, "barrier room");
+static_assert((kWin0 + kOffCodes) % 1024 == 0, "swizzled boxes need 1024-byte alignment");
 
-// tiles whose partial sums a warp keeps in registers between two reductions
-template <int NT> struct PassTiles { static constexpr int value = NT == 1 ? 8 : 3; };
+// tiles a warp may hold between two reductions: in the last pass of a CTA (partials parked in
+// the warp's ring) and in earlier passes (parked in the table's gaps)
+template <int NT> struct PassTiles {
+    static constexpr int last = NT == 1 ? 5 : 3;
+    static constexpr int early = kSlotIdx / (4 * NT);
+};
 
 struct DecodeParams {
     const __nv_bfloat16 *x;
-    const uint8_t *codes;
-    const float *absmax;
     const uint8_t *scale_codes;
     const float *scale_of_scales;
     const float *bias;
-    const float *t;  // [M][rank] f32 = x A^T, or null
+    float *t_global;       // [M][rank] f32 = x A^T, written by the producer CTAs (workspace)
+    uint32_t *flags;       // [0] producers that have published, [1] CTAs that have read T
+    uint32_t n_prod;       // CTAs that compute T (each takes the rows j = cta, cta + n_prod, ...)
+    const __nv_bfloat16 *lora_a;
     const __nv_bfloat16 *lora_b;
     void *y;
-    uint32_t y_f32;
     uint64_t ldy;
+    uint32_t y_f32;
     uint32_t M, K, N, rank;
     float lora_scale;
-    uint32_t gran;            // CTA row ranges start on multiples of this
-    uint32_t chunks_per_warp;
-    uint32_t ring;            // tiles per warp ring
-    uint32_t pass_tiles;      // tiles per reduction pass (<= PassTiles<NT>)
-    uint32_t code_stride;     // bytes between rows of a warp's nibbles in shared memory
-    uint32_t slot_bytes;      // one tile of one warp: its nibbles
-    uint32_t vec_scales;      // the CTA's scales are staged in shared memory (else read from global)
-    uint32_t scale_stride;    // bytes between rows of staged scales (padded)
-    uint32_t scale_bytes_max; // room for them
-    uint32_t lora_bytes_max;  // room for the CTA's LoRA-B rows
-    uint32_t smem_bytes;      // dynamic shared memory of the launch (the kernel lays it out itself)
-    uint32_t debug_no_request;  // timing build only: stream nothing after the first tiles
-    uint32_t red_slot_bytes;
+    uint32_t gran;        // CTA row ranges start on multiples of this
+    uint32_t kw, rw;      // warps along K, groups of warps along rows (kw * rw <= 16)
+    uint32_t pt_last, pt_early;  // tiles per warp in the last pass / in each earlier pass
+    uint32_t nchunks;
+    uint32_t wait_ns;     // bound of every wait
 };
 
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
@@ -107,378 +121,431 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
-// sixteen bf16 (two 128-bit words) -> this lane's f16 B-fragments of one 64-chunk
-__device__ __forceinline__ void convert_x(const uint4 &q0, const uint4 &q1, uint32_t (&xf)[4][2]) {
-    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t pair) {
+    return pack_f16x2(bf16_bits_to_float(pair & 0xffffu), __uint_as_float(pair & 0xffff0000u));
+}
+
+// Waits for a phase of an mbarrier, at most `limit_ns`; false when the time ran out.
+__device__ __forceinline__ bool wait_phase(uint32_t bar, uint32_t parity, uint32_t limit_ns) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::global_timer_ns();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(2000u)
+            : "memory");
+        if (ok) return true;
+        if (ptx::global_timer_ns() - t0 > (uint64_t)limit_ns) return false;
+    }
+}
+
+// the sixteen f16 levels as immediates (a table in constant memory would be read with a
+// different index per lane, which the constant cache serialises)
+__device__ __forceinline__ uint32_t level_f16(uint32_t code) {
+    constexpr uint32_t L[16] = {NF4_LEVEL_F16_BITS_LIST};
+    uint32_t v = L[0];
     #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t pair = w[2 * j + h];  // two bf16: k, k+1
-            xf[j][h] = pack_f16x2(bf16_bits_to_float(pair & 0xffffu), bf16_bits_to_float(pair >> 16));
-        }
-    }
+    for (int k = 1; k < 16; ++k) v = (code == (uint32_t)k) ? L[k] : v;
+    return v;
 }
 
-// Blocks until at most `n` of this thread's copy groups are in flight (n is small).
-__device__ __forceinline__ void wait_groups(uint32_t n) {
-    switch (n) {
-        case 0: ptx::cp_async_wait<0>(); break;
-        case 1: ptx::cp_async_wait<1>(); break;
-        case 2: ptx::cp_async_wait<2>(); break;
-        case 3: ptx::cp_async_wait<3>(); break;
-        case 4: ptx::cp_async_wait<4>(); break;
-        default: ptx::cp_async_wait<5>(); break;
-    }
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
-// FULL: d_in is exactly 4096, so every warp owns four 64-blocks and no per-chunk guard is needed.
-// PT: tiles whose partial sums stay in registers between two reductions (>= p.pass_tiles).
-// 120 registers x 512 threads and 3 KB short of all the shared memory: the pre-pass's small CTA
-// fits on the SM beside this one.
-template <int NT, bool DQ, bool FULL, int PT>
-__global__ void __maxnreg__(120)
-decode_kernel(const DecodeParams p) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // Layout by shared-window address: [start, 0x10000) rings of the first warps |
-    // [0x10000, 0x20000) lookup table | [0x20000, ...) T, LoRA-B rows, rings of the other warps.
-    const uint32_t win0 = ptx::smem_addr(smem_raw);
-    uint8_t *smem = smem_raw + (kLutWindow - win0);  // generic pointer to the table
-    uint8_t *high = smem + kLutBytes;
-    float *t_s = reinterpret_cast<float *>(high);  // [M][rank]
-    uint64_t *scale_bar = reinterpret_cast<uint64_t *>(high + 16 * kMaxRank * 4);  // scales have landed
-    uint8_t *lora_raw = high + 16 * kMaxRank * 4 + 128;
-    const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(lora_raw);
-    float *red = reinterpret_cast<float *>(smem);  // the reduction slots take the lookup table's place
-    constexpr int kAccs = 1;  // a block's four MMAs run as one chain (the four blocks of a tile interleave)
-
+template <int NT, bool DQ>
+__global__ void __launch_bounds__(kDecodeThreads, 1)
+decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
+              const __grid_constant__ CUtensorMap tm_scales, const DecodeParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr int PT = PassTiles<NT>::last;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t ring_bytes = p.ring * p.slot_bytes;
-    const uint32_t low_room = win0 < kLutWindow ? ((kLutWindow - win0) & ~127u) : 0u;
-    const uint32_t low_warps = min((uint32_t)kWarps, low_room / ring_bytes);
-    const uint32_t high_used = 16 * kMaxRank * 4 + 128 + p.lora_bytes_max + p.scale_bytes_max +
-                               (kWarps - low_warps) * ring_bytes;
-    if (win0 > kLutWindow || kLutWindow + kLutBytes + high_used > win0 + p.smem_bytes) {
-        if (threadIdx.x == 0) atomicExch(&g_decode_error, 4);  // the launch gave too little room
+    if (ptx::smem_addr(smem) != kWin0) {
+        // the table's base is an immediate of the lookups: nothing can run from another address
+        if (tid == 0) atomicExch(&g_decode_error, 4);
         return;
     }
-    uint8_t *ring = warp < low_warps
-                        ? smem - low_room + (size_t)warp * ring_bytes
-                        : lora_raw + p.lora_bytes_max + p.scale_bytes_max +
-                              (size_t)(warp - low_warps) * ring_bytes;
-    const uint32_t ring_addr = ptx::smem_addr(ring);
-    uint8_t *scale_raw = lora_raw + p.lora_bytes_max;  // [rows of the CTA][scale_stride]
-    const uint32_t R = p.ring, D = R - 1;  // D tiles in flight while one is read
+    if (tid == 0) {
+        ptx::prefetch_tmap(&tm_codes);
+        if (!DQ) ptx::prefetch_tmap(&tm_scales);
+    }
+    float *t_s = reinterpret_cast<float *>(smem + kOffT);     // [M][rank]
+    float *dq_s = reinterpret_cast<float *>(smem + kOffDq);   // code / 255 for the 256 codes
+    const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(smem + kOffLora);
+    // parking places of partial sums: element (warp, idx, lane)
+    float *gaps = reinterpret_cast<float *>(smem + 128);       // + (warp * 16 + idx) * 256 bytes
+    float *rings = reinterpret_cast<float *>(smem + kOffCodes);  // + warp * ring bytes + idx * 128 bytes
+    constexpr uint32_t kGapWarp = kSlotIdx * kLutStride / 4, kGapIdx = kLutStride / 4;
+    constexpr uint32_t kRingWarp = kRing * kCodesSlot / 4, kRingIdx = 32;
 
     // rows owned by this CTA: units of `gran` rows, split evenly over the grid
     const uint64_t units = p.N / p.gran;
     const uint32_t n0 = (uint32_t)((uint64_t)blockIdx.x * units / gridDim.x) * p.gran;
     const uint32_t n1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * units / gridDim.x) * p.gran;
     const uint32_t ntiles = (n1 - n0 + kTileRows - 1) / kTileRows;
-    if (warp == 0) NF4_TS(0);
 
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint32_t nchunks = p.K / kChunk;
-    const uint32_t chunk0 = warp * p.chunks_per_warp;
-    const bool active = FULL || chunk0 < nchunks;  // short K leaves the last warps without a slice
-    const uint32_t my_chunks = FULL ? 4u : (active ? min(p.chunks_per_warp, nchunks - chunk0) : 0u);
-    const bool vec_scales = FULL || p.vec_scales;
-    const uint32_t code_row_bytes = p.K / 2;
+    const bool active = warp < p.kw * p.rw;
+    const uint32_t rg = active ? warp / p.kw : 0u;   // which tiles: rg, rg + rw, ...
+    const uint32_t ks = active ? warp - rg * p.kw : 0u;  // which K-slice
+    const uint32_t my_tiles = (active && rg < ntiles) ? (ntiles - rg + p.rw - 1) / p.rw : 0u;
+    const uint32_t k0 = ks * kSliceK;
 
-    // Ask for one tile of this warp's slice: 16 rows x (32 bytes per chunk) of nibbles in
-    // 16-byte pieces, then the rows' scales.  Rows past the CTA's range are left as they are:
-    // their products land in accumulator rows that are never stored.
-    // four-chunk slices: lane l copies piece (l & 7) of rows (l >> 3) + 4 i, i = 0..3
-    const uint32_t lane_dst = (lane >> 3) * p.code_stride + (lane & 7u) * 16u;
-    const uint8_t *lane_src = p.codes + (size_t)(n0 + (lane >> 3)) * code_row_bytes + chunk0 * 32u +
-                              (lane & 7u) * 16u;
-    uint32_t req_slot = 0, use_slot = 0;  // ring positions of the next request and the next tile read
-    auto request_tile = [&](uint32_t tile) {
-        const uint32_t row0 = n0 + tile * kTileRows;
-        const uint32_t rows = min((uint32_t)kTileRows, n1 - row0);
-        const uint32_t slot = ring_addr + req_slot * p.slot_bytes;
-        req_slot = req_slot + 1 == R ? 0u : req_slot + 1;
-        if (vec_scales) {
-            const uint8_t *src = lane_src + (size_t)tile * (kTileRows * code_row_bytes);
-            #pragma unroll
-            for (uint32_t i = 0; i < 4; ++i)
-                if ((lane >> 3) + 4 * i < rows)
-                    ptx::cp_async_16(slot + lane_dst + i * 4u * p.code_stride,
-                                     src + (size_t)i * 4u * code_row_bytes);
-            return;
+    const uint32_t bar0 = kWin0 + kOffBars + warp * kRing * 8u;
+    const uint32_t codes0 = kWin0 + kOffCodes + warp * kRing * kCodesSlot;
+    const uint32_t scales0 = kWin0 + kOffScales + warp * kRing * kScaleSlot;
+    const uint8_t *codes_ring = smem + kOffCodes + warp * kRing * kCodesSlot;
+    const uint8_t *scales_ring = smem + kOffScales + warp * kRing * kScaleSlot;
+
+    // ---- this warp's barriers and its first tiles (nothing here depends on the predecessor):
+    // lane s sets up slot s and asks for tile s, so the four requests leave in one instruction ----
+    auto request_tile = [&](uint32_t j) {
+        // tile number j of this warp goes to slot j % kRing
+        const uint32_t slot = j & (kRing - 1);
+        const int32_t row0 = (int32_t)(n0 + (rg + j * p.rw) * kTileRows);
+        const uint32_t bar = bar0 + 8 * slot;
+        ptx::mbar_arrive_expect_tx(bar, DQ ? kCodesSlot : kCodesSlot + kScaleSlot);
+        ptx::tma_load_2d(codes0 + slot * kCodesSlot, &tm_codes, (int32_t)(ks * 128u), row0, bar);
+        if (!DQ) ptx::tma_load_2d(scales0 + slot * kScaleSlot, &tm_scales, (int32_t)(ks * 4u), row0, bar);
+    };
+    if (lane < (uint32_t)kRing) {
+        ptx::mbar_init(bar0 + 8 * lane, 1);
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+        if (lane < my_tiles) request_tile(lane);
+    }
+    uint32_t req_j = my_tiles < (uint32_t)kRing ? my_tiles : (uint32_t)kRing;  // tiles requested so far
+
+    // ---- the lookup table: thread (byte, half) writes sixteen lanes' copies of its entry ----
+    {
+        const uint32_t byte = tid >> 1, half = tid & 1u;
+        const uint32_t entry = level_f16(byte & 15u) | (level_f16(byte >> 4) << 16);
+        const uint4 v = make_uint4(entry, entry, entry, entry);
+        #pragma unroll
+        for (int i = 0; i < 4; ++i)  // rotated by the byte so that a warp's stores spread over the banks
+            *reinterpret_cast<uint4 *>(smem + byte * kLutStride + half * 64u + ((i + byte) & 3u) * 16u) = v;
+        if (DQ && tid < 256) dq_s[tid] = __fdiv_rn((float)tid, 255.0f);
+    }
+
+    // ---- pass plan (the same for every warp): early passes of pt_early tiles per warp, parked in
+    // the table's gaps, then one last pass of at most pt_last tiles, parked in the rings ----
+    const uint32_t max_tiles = (ntiles + p.rw - 1) / p.rw;  // tiles of the busiest warp
+    const uint32_t n_early = max_tiles > p.pt_last ? (max_tiles - p.pt_last + p.pt_early - 1) / p.pt_early : 0u;
+    const uint32_t npasses = n_early + 1;
+    auto pass_first = [&](uint32_t pass) { return pass * p.pt_early; };  // warp-local tile a pass starts at
+    auto pass_count = [&](uint32_t pass) { return pass < n_early ? p.pt_early : max_tiles - n_early * p.pt_early; };
+
+    // LoRA-B rows of one pass of tiles, staged by everyone with 16-byte asynchronous copies
+    auto stage_lora_b = [&](uint32_t pass) {
+        if (p.rank) {
+            const uint32_t r0 = n0 + pass_first(pass) * p.rw * kTileRows;
+            if (r0 < n1) {
+                const uint32_t rows = min(n1 - r0, pass_count(pass) * p.rw * kTileRows);
+                const uint32_t pieces = rows * p.rank * 2u / 16u;
+                const uint8_t *src = reinterpret_cast<const uint8_t *>(p.lora_b + (size_t)r0 * p.rank);
+                for (uint32_t q = tid; q < pieces; q += kDecodeThreads)
+                    ptx::cp_async_16(kWin0 + kOffLora + q * 16u, src + (size_t)q * 16u);
+            }
         }
-        const uint32_t pieces_per_row = my_chunks * 2u;
-        const uint8_t *src0 = p.codes + (size_t)row0 * code_row_bytes + chunk0 * 32u;
-        for (uint32_t q = lane; q < rows * pieces_per_row; q += 32) {
-            const uint32_t row = q / pieces_per_row, piece = q - row * pieces_per_row;
-            ptx::cp_async_16(slot + row * p.code_stride + piece * 16u,
-                             src0 + (size_t)row * code_row_bytes + piece * 16u);
+        ptx::cp_async_commit();
+    };
+    stage_lora_b(0);
+
+    // ---- a producer CTA's row of the adapter factor A, this warp's K-slice of it (raw bf16,
+    // the lane's sixteen consecutive k of each 64-block, the same k the lane holds of x) ----
+    const bool producer = p.rank != 0 && blockIdx.x < p.n_prod;
+    const bool t_warp = producer && active && rg == 0;
+    uint4 araw[kSliceChunks][2];
+    auto load_a = [&](uint32_t j) {
+        #pragma unroll
+        for (int c = 0; c < kSliceChunks; ++c) {
+            araw[c][0] = araw[c][1] = make_uint4(0, 0, 0, 0);
+            if (t_warp) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(p.lora_a + (size_t)j * p.K + k0 + c * kChunk + 16 * t);
+                araw[c][0] = __ldg(src);
+                araw[c][1] = __ldg(src + 1);
+            }
         }
     };
+    if (producer) load_a(blockIdx.x);
+    __syncthreads();  // the table is in place
 
-    // ---- x first (plain loads: nothing of this kernel's own is queued ahead of them).  The
-    // pre-pass that this kernel may overlap is an ordinary launch: x was complete before it
-    // started, so x is complete now. ----
-    uint32_t xf[NT][kMaxChunksPerWarp][4][2];  // this warp's slice of x as f16 B-fragments
+    // ---- from here on the kernel reads what its predecessor wrote ----
+    ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
+
+    uint32_t xf[NT][kSliceChunks][4][2];  // this warp's slice of x as f16 B-fragments
     {
-        uint4 xraw[NT][kMaxChunksPerWarp][2];
+        uint4 xraw[NT][kSliceChunks][2];
         #pragma unroll
         for (int u = 0; u < NT; ++u) {
             const uint32_t m = 8 * u + g;
             #pragma unroll
-            for (int c = 0; c < kMaxChunksPerWarp; ++c) {
+            for (int c = 0; c < kSliceChunks; ++c) {
                 xraw[u][c][0] = xraw[u][c][1] = make_uint4(0, 0, 0, 0);
-                if (m < p.M && c < (int)my_chunks) {
+                if (m < p.M && active) {
                     const uint4 *src = reinterpret_cast<const uint4 *>(
-                        p.x + (size_t)m * p.K + (chunk0 + c) * kChunk + 16 * t);
+                        p.x + (size_t)m * p.K + k0 + c * kChunk + 16 * t);
                     xraw[u][c][0] = __ldg(src);
                     xraw[u][c][1] = __ldg(src + 1);
                 }
             }
         }
 
-        // ---- the CTA's block scales (whole rows), its LoRA-B rows and the first tiles ----
-        if (tid == 0) {
-            ptx::mbar_init(ptx::smem_addr(scale_bar), kDecodeThreads);
-            ptx::fence_mbar_init();
-        }
-        if (vec_scales) {
-            const uint32_t rows_cta = n1 - n0;
-            if (DQ) {
-                const uint32_t ppr = nchunks / 4;  // 4-byte pieces per row
-                for (uint32_t q = tid; q < rows_cta * ppr; q += kDecodeThreads) {
-                    const uint32_t row = q / ppr, pc = q - row * ppr;
-                    ptx::cp_async_4(ptx::smem_addr(scale_raw) + row * p.scale_stride + pc * 4u,
-                                    p.scale_codes + (size_t)(n0 + row) * nchunks + pc * 4u);
+        if (producer) {
+            // column j of T: every warp's slice of sum_k x[m][k] A[j][k], f32; the slices meet in
+            // the table's gaps (unused until the first parking) and warp 0 adds them in order
+            for (uint32_t j = blockIdx.x; j < p.rank; j += p.n_prod) {
+                if (j != blockIdx.x) {
+                    __syncthreads();  // the gaps have been read
+                    load_a(j);
                 }
-            } else {
-                const uint32_t ppr = nchunks / 4;  // 16-byte pieces per row
-                for (uint32_t q = tid; q < rows_cta * ppr; q += kDecodeThreads) {
-                    const uint32_t row = q / ppr, pc = q - row * ppr;
-                    ptx::cp_async_16(ptx::smem_addr(scale_raw) + row * p.scale_stride + pc * 16u,
-                                     p.absmax + (size_t)(n0 + row) * nchunks + pc * 4u);
+                #pragma unroll
+                for (int u = 0; u < NT; ++u) {
+                    float part = 0.0f;
+                    #pragma unroll
+                    for (int c = 0; c < kSliceChunks; ++c) {
+                        const uint32_t aw[8] = {araw[c][0].x, araw[c][0].y, araw[c][0].z, araw[c][0].w,
+                                                araw[c][1].x, araw[c][1].y, araw[c][1].z, araw[c][1].w};
+                        const uint32_t xw[8] = {xraw[u][c][0].x, xraw[u][c][0].y, xraw[u][c][0].z, xraw[u][c][0].w,
+                                                xraw[u][c][1].x, xraw[u][c][1].y, xraw[u][c][1].z, xraw[u][c][1].w};
+                        #pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            part = fmaf(bf16_bits_to_float(xw[i] & 0xffffu), bf16_bits_to_float(aw[i] & 0xffffu), part);
+                            part = fmaf(__uint_as_float(xw[i] & 0xffff0000u), __uint_as_float(aw[i] & 0xffff0000u), part);
+                        }
+                    }
+                    part += __shfl_xor_sync(0xffffffffu, part, 1);
+                    part += __shfl_xor_sync(0xffffffffu, part, 2);
+                    if (t == 0) gaps[warp * kGapWarp + 8 * u + g] = t_warp ? part : 0.0f;
+                }
+                __syncthreads();
+                if (warp == 0 && lane < p.M) {
+                    float v = 0.0f;
+                    for (uint32_t w = 0; w < (uint32_t)kWarps; ++w) v += gaps[w * kGapWarp + lane];
+                    p.t_global[(size_t)lane * p.rank + j] = v;
                 }
             }
-        }
-        if (p.rank) {
-            const uint32_t pieces = (n1 - n0) * p.rank * 2u / 16u;
-            const uint8_t *src = reinterpret_cast<const uint8_t *>(p.lora_b + (size_t)n0 * p.rank);
-            for (uint32_t q = tid; q < pieces; q += kDecodeThreads)
-                ptx::cp_async_16(ptx::smem_addr(lora_raw) + q * 16u, src + (size_t)q * 16u);
-        }
-        ptx::cp_async_commit();
-        for (uint32_t d = 0; d < D; ++d) {
-            if (active && d < ntiles) request_tile(d);
-            ptx::cp_async_commit();
+            if (warp == 0) {
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(p.flags, 1u);
+            }
         }
 
-        if (warp == 0) NF4_TS(2);
         #pragma unroll
         for (int u = 0; u < NT; ++u) {
             #pragma unroll
-            for (int c = 0; c < kMaxChunksPerWarp; ++c) convert_x(xraw[u][c][0], xraw[u][c][1], xf[u][c]);
+            for (int c = 0; c < kSliceChunks; ++c) {
+                const uint32_t w[8] = {xraw[u][c][0].x, xraw[u][c][0].y, xraw[u][c][0].z, xraw[u][c][0].w,
+                                       xraw[u][c][1].x, xraw[u][c][1].y, xraw[u][c][1].z, xraw[u][c][1].w};
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    xf[u][c][j][0] = bf16x2_to_f16x2(w[2 * j]);
+                    xf[u][c][j][1] = bf16x2_to_f16x2(w[2 * j + 1]);
+                }
+            }
         }
-#ifdef NF4_DECODE_TIMING
-        if (xf[0][0][0][0] == 0x12345678u) NF4_TS(63);  // forces the conversion before the next stamp
-#endif
-        if (warp == 0) NF4_TS(3);
     }
+    if (producer) __syncthreads();  // the gaps are free again
 
-    // ---- the lookup table: thread (byte, half) writes sixteen lanes' copies of its entry ----
-    auto build_table = [&]() {
-        const uint32_t byte = tid >> 1, half = tid & 1u;
-        const uint32_t entry = c_level_f16_bits[byte & 15u] | (c_level_f16_bits[byte >> 4] << 16);
-        const uint4 v = make_uint4(entry, entry, entry, entry);
-        #pragma unroll
-        for (int i = 0; i < 4; ++i)  // rotated by the byte so that a warp's stores spread over the banks
-            *reinterpret_cast<uint4 *>(smem + byte * kLutStride + half * 64u + ((i + byte) & 3u) * 16u) = v;
+    // Warp 0 brings T into shared memory shortly before the first pass ends: a bounded wait for the
+    // producers' count, then asynchronous copies that the end-of-pass wait collects.
+    bool lost = false;   // a wait of this warp ran out: results are void, the flag is set
+    auto fetch_t = [&]() {
+        uint32_t ok = 1;
+        if (lane == 0 && ld_acquire_gpu(p.flags) != p.n_prod) {
+            const uint64_t t0 = ptx::global_timer_ns();
+            while (ld_acquire_gpu(p.flags) != p.n_prod) {
+                if (ptx::global_timer_ns() - t0 > (uint64_t)p.wait_ns) {
+                    ok = 0;
+                    atomicExch(&g_decode_error, 6);
+                    break;
+                }
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) lost = true;
+        const uint32_t n = p.M * p.rank;
+        if ((n & 3u) == 0) {
+            for (uint32_t i = lane * 4; i < n; i += 128) ptx::cp_async_16(kWin0 + kOffT + i * 4u, p.t_global + i);
+        } else {
+            for (uint32_t i = lane; i < n; i += 32) t_s[i] = __ldcg(p.t_global + i);
+        }
+        ptx::cp_async_commit();
     };
-    build_table();
-    if (warp == 0) NF4_TS(50);
-    __syncthreads();
-    // every thread's scale pieces report to one barrier when they land (no wait here)
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(ptx::smem_addr(scale_bar)) : "memory");
-    if (warp == 0) NF4_TS(1);
 
     const float sos = DQ ? __ldg(p.scale_of_scales) : 0.0f;
-    // shared-window address of a table entry = {0x0001, code byte, lane * 4}
-    const uint32_t lane_word = kLutWindow | (lane * 4u);
+    // table entry of a code byte, relative to the table: {0, 0, byte, lane * 4}
+    const uint32_t lane_word = lane * 4u;
     auto lut_at = [&](uint32_t word, int byte) -> uint32_t {
         const uint32_t addr = __byte_perm(word, lane_word, 0x7604u | ((uint32_t)byte << 4));
         uint32_t v;
-        asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+        asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(kWin0));
         return v;
     };
-    const uint32_t slot_floats = p.red_slot_bytes / 4;
-    const uint32_t first_pass_last = min(ntiles, p.pass_tiles) - 1;
+    // byte offsets of this lane's first 8 bytes in rows 2g and 2g + 1 of a swizzled tile; the
+    // 32-byte block c of the row is at (offset ^ (c << 5))
+    const uint32_t off_lo = (2 * g) * 128u + ((((t >> 1) ^ ((2 * g) & 7u))) << 4) + (t & 1u) * 8u;
+    const uint32_t off_hi = (2 * g + 1) * 128u + ((((t >> 1) ^ ((2 * g + 1) & 7u))) << 4) + (t & 1u) * 8u;
 
-    float acc[PT][NT][4];
-    #pragma unroll
-    for (int q = 0; q < PT; ++q) {
-        #pragma unroll
-        for (int u = 0; u < NT; ++u) acc[q][u][0] = acc[q][u][1] = acc[q][u][2] = acc[q][u][3] = 0.0f;
-    }
-    uint32_t pass_tile0 = 0;
+    // double-quantized scales come straight from global memory, one tile ahead
+    uint32_t dq_lo = 0, dq_hi = 0;
+    auto fetch_dq = [&](uint32_t j) {
+        if (DQ && j < my_tiles) {
+            const uint32_t row = n0 + (rg + j * p.rw) * kTileRows + 2 * g;
+            const uint32_t r_lo = min(row, p.N - 1), r_hi = min(row + 1, p.N - 1);
+            dq_lo = __ldg(reinterpret_cast<const uint32_t *>(p.scale_codes + (size_t)r_lo * p.nchunks + ks * 4u));
+            dq_hi = __ldg(reinterpret_cast<const uint32_t *>(p.scale_codes + (size_t)r_hi * p.nchunks + ks * 4u));
+        }
+    };
+    fetch_dq(0);
 
-    // One copy of the tile code; the accumulators work as a shift register: the tile being
-    // multiplied is acc[0], older tiles of the pass move up.  The stream runs ahead across
-    // pass boundaries.
+    uint32_t use_j = 0;  // tiles consumed so far
+
     #pragma unroll 1
-    for (uint32_t tile = 0; tile < ntiles; ++tile) {
-        if (active) {
+    for (uint32_t pass = 0; pass < npasses; ++pass) {
+        const bool last_pass = pass + 1 == npasses;
+        float acc[PT][NT][4];
+        #pragma unroll
+        for (int q = 0; q < PT; ++q) {
             #pragma unroll
-            for (int q = PT - 1; q > 0; --q) {
-                #pragma unroll
-                for (int u = 0; u < NT; ++u) {
-                    #pragma unroll
-                    for (int r = 0; r < 4; ++r) acc[q][u][r] = acc[q - 1][u][r];
-                }
-            }
-            #pragma unroll
-            for (int u = 0; u < NT; ++u) acc[0][u][0] = acc[0][u][1] = acc[0][u][2] = acc[0][u][3] = 0.0f;
+            for (int u = 0; u < NT; ++u) acc[q][u][0] = acc[q][u][1] = acc[q][u][2] = acc[q][u][3] = 0.0f;
+        }
+        const uint32_t left = my_tiles - use_j;
+        const uint32_t cnt = pass_count(pass);
+        const uint32_t mine = left < cnt ? left : cnt;  // tiles of this warp in this pass
+        if (pass == 0 && p.rank && warp == 0 && mine == 0) fetch_t();
 
-            // The adapter intermediate comes from the pre-pass, which has had most of the
-            // stream to finish: warp 0 asks for it one tile before it is needed.
-            if (warp == 0 && p.rank && tile == first_pass_last) {
-                ptx::pdl_wait();
-                for (uint32_t i = lane; i < p.M * p.rank; i += 32)
-                    ptx::cp_async_4(ptx::smem_addr(t_s + i), p.t + i);
-                ptx::cp_async_commit();
-            }
-            // keep D tiles in flight, then wait for this one (groups retire in order)
-            __syncwarp();  // every lane is done reading the slot about to be refilled
-#ifdef NF4_DECODE_TIMING
-            if (!p.debug_no_request)
-#endif
-            if (tile + D < ntiles) request_tile(tile + D);
-            ptx::cp_async_commit();
-            if (warp == 0 && tile < 8) NF4_TS(42 + tile);
-            wait_groups(D);
-            __syncwarp();  // the other lanes' pieces are visible too
-            if (warp == 0 && tile < 8) NF4_TS(4 + 3 * tile);
-            const uint8_t *st = ring + (size_t)use_slot * p.slot_bytes;
-            use_slot = use_slot + 1 == R ? 0u : use_slot + 1;
-            const uint8_t *codes_lo = st + g * p.code_stride + t * 8;
-            const uint8_t *codes_hi = codes_lo + 8 * p.code_stride;
-
-            float s_lo[kMaxChunksPerWarp], s_hi[kMaxChunksPerWarp];
-            if (vec_scales) {
-                if (tile == 0 && !ptx::mbar_wait_bounded(ptx::smem_addr(scale_bar), 0)) {
+        #pragma unroll
+        for (int q = 0; q < PT; ++q) {
+            if ((uint32_t)q < mine) {
+                if (pass == 0 && p.rank && warp == 0 && (uint32_t)q + 1 == mine) fetch_t();
+                const uint32_t slot = use_j & (kRing - 1);
+                if (!lost && !wait_phase(bar0 + 8 * slot, (use_j / kRing) & 1u, p.wait_ns)) {
+                    lost = true;
                     if (lane == 0) atomicExch(&g_decode_error, 5);
                 }
-                const uint8_t *sc = scale_raw + (size_t)(tile * kTileRows + g) * p.scale_stride;
+                const uint8_t *cs = codes_ring + slot * kCodesSlot;
+                uint2 w0[kSliceChunks], w1[kSliceChunks];
+                #pragma unroll
+                for (int c = 0; c < kSliceChunks; ++c) {
+                    w0[c] = *reinterpret_cast<const uint2 *>(cs + (off_lo ^ ((uint32_t)c << 5)));
+                    w1[c] = *reinterpret_cast<const uint2 *>(cs + (off_hi ^ ((uint32_t)c << 5)));
+                }
+                float s_lo[kSliceChunks], s_hi[kSliceChunks];
                 if (DQ) {
-                    const uint32_t a = *reinterpret_cast<const uint32_t *>(sc + chunk0);
-                    const uint32_t b = *reinterpret_cast<const uint32_t *>(sc + 8 * p.scale_stride + chunk0);
                     #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        s_lo[c] = dq_scale((a >> (8 * c)) & 0xffu, sos);
-                        s_hi[c] = dq_scale((b >> (8 * c)) & 0xffu, sos);
+                    for (int c = 0; c < kSliceChunks; ++c) {
+                        s_lo[c] = __fmul_rn(dq_s[(dq_lo >> (8 * c)) & 0xffu], sos);
+                        s_hi[c] = __fmul_rn(dq_s[(dq_hi >> (8 * c)) & 0xffu], sos);
                     }
                 } else {
-                    const float4 a = *reinterpret_cast<const float4 *>(sc + chunk0 * 4);
-                    const float4 b = *reinterpret_cast<const float4 *>(sc + 8 * p.scale_stride + chunk0 * 4);
+                    const float4 a = *reinterpret_cast<const float4 *>(scales_ring + slot * kScaleSlot + g * 32u);
+                    const float4 b = *reinterpret_cast<const float4 *>(scales_ring + slot * kScaleSlot + g * 32u + 16u);
                     s_lo[0] = a.x; s_lo[1] = a.y; s_lo[2] = a.z; s_lo[3] = a.w;
                     s_hi[0] = b.x; s_hi[1] = b.y; s_hi[2] = b.z; s_hi[3] = b.w;
                 }
-            } else {
-                // odd slice widths: the scales come straight from global memory
-                const uint32_t r_lo = min(n0 + tile * kTileRows + g, n1 - 1);
-                const uint32_t r_hi = min(n0 + tile * kTileRows + g + 8, n1 - 1);
-                #pragma unroll
-                for (int c = 0; c < kMaxChunksPerWarp; ++c) {
-                    s_lo[c] = s_hi[c] = 0.0f;
-                    if (c < (int)my_chunks) {
-                        const size_t i_lo = (size_t)r_lo * nchunks + chunk0 + c;
-                        const size_t i_hi = (size_t)r_hi * nchunks + chunk0 + c;
-                        s_lo[c] = DQ ? dq_scale(__ldg(p.scale_codes + i_lo), sos) : __ldg(p.absmax + i_lo);
-                        s_hi[c] = DQ ? dq_scale(__ldg(p.scale_codes + i_hi), sos) : __ldg(p.absmax + i_hi);
-                    }
+                ++use_j;
+                fetch_dq(use_j);
+                // every lane holds its part of the tile in registers: the slot can be refilled
+                __syncwarp();
+                if (req_j < my_tiles) {
+                    if (lane == 0) request_tile(req_j);
+                    ++req_j;
                 }
-            }
 
-            #pragma unroll
-            for (int c = 0; c < kMaxChunksPerWarp; ++c) {
-                if (c < (int)my_chunks) {
-                    const uint2 w0 = *reinterpret_cast<const uint2 *>(codes_lo + c * 32);
-                    const uint2 w1 = *reinterpret_cast<const uint2 *>(codes_hi + c * 32);
-                    float blk[kAccs][NT][4];
+                #pragma unroll
+                for (int c = 0; c < kSliceChunks; ++c) {
+                    float blk[NT][4];
                     #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint32_t x0 = (j < 2) ? w0.x : w0.y;
-                        const uint32_t x1 = (j < 2) ? w1.x : w1.y;
+                        const uint32_t x0 = (j < 2) ? w0[c].x : w0[c].y;
+                        const uint32_t x1 = (j < 2) ? w1[c].x : w1[c].y;
                         const int b = 2 * (j & 1);
                         const uint32_t a0 = lut_at(x0, b), a1 = lut_at(x1, b);
                         const uint32_t a2 = lut_at(x0, b + 1), a3 = lut_at(x1, b + 1);
                         #pragma unroll
                         for (int u = 0; u < NT; ++u) {
                             if (j == 0)
-                                ptx::mma_16816_f16_zero(blk[0][u], a0, a1, a2, a3, xf[u][c][j][0],
-                                                        xf[u][c][j][1]);
+                                ptx::mma_16816_f16_zero(blk[u], a0, a1, a2, a3, xf[u][c][j][0], xf[u][c][j][1]);
                             else
-                                ptx::mma_16816_f16(blk[0][u], a0, a1, a2, a3, xf[u][c][j][0],
-                                                   xf[u][c][j][1]);
+                                ptx::mma_16816_f16(blk[u], a0, a1, a2, a3, xf[u][c][j][0], xf[u][c][j][1]);
                         }
                     }
                     #pragma unroll
                     for (int u = 0; u < NT; ++u) {
                         #pragma unroll
                         for (int r = 0; r < 4; ++r)
-                            acc[0][u][r] = fmaf(blk[0][u][r], r < 2 ? s_lo[c] : s_hi[c], acc[0][u][r]);
+                            acc[q][u][r] = fmaf(blk[u][r], r < 2 ? s_lo[c] : s_hi[c], acc[q][u][r]);
                     }
                 }
             }
-            if (warp == 0 && tile < 8) NF4_TS(5 + 3 * tile);
         }
-
-        const uint32_t tiles_in_pass = tile + 1 - pass_tile0;
-        if (tiles_in_pass < p.pass_tiles && tile + 1 < ntiles) continue;
 
         // ================= end of a pass: reduce, finish and store its rows =================
-        // The reduction slots take the place of the lookup table, which is rebuilt afterwards
-        // if more tiles follow; the rings keep filling meanwhile.
-        if (warp == 0) NF4_TS(40);
-        __syncthreads();  // nobody reads the table any more
-        {
-            // acc[q] holds the pass's tile number (tiles_in_pass - 1 - q)
-            float *slot = red + warp * slot_floats;
-            #pragma unroll
-            for (int q = 0; q < PT; ++q) {
-                if (q < (int)tiles_in_pass) {
-                    const int ti = (int)tiles_in_pass - 1 - q;
+        // Partials of the last pass go to the warp's own ring (all its tiles have been read);
+        // earlier passes use the table's gaps, which the pass before them may still be reading.
+        float *park = last_pass ? rings + warp * kRingWarp : gaps + warp * kGapWarp;
+        const uint32_t park_idx = last_pass ? kRingIdx : kGapIdx;
+        const uint32_t park_warp = last_pass ? kRingWarp : kGapWarp;
+        if (!last_pass && pass > 0) __syncthreads();  // the gaps are free
+        #pragma unroll
+        for (int q = 0; q < PT; ++q) {
+            if ((uint32_t)q < mine) {
+                #pragma unroll
+                for (int u = 0; u < NT; ++u) {
                     #pragma unroll
-                    for (int u = 0; u < NT; ++u) {
-                        #pragma unroll
-                        for (int r = 0; r < 4; ++r)
-                            slot[((ti * NT + u) * 4 + r) * 32 + lane] = acc[q][u][r];
-                    }
+                    for (int r = 0; r < 4; ++r)
+                        park[((q * NT + u) * 4 + r) * park_idx + lane] = acc[q][u][r];
                 }
             }
         }
-        if (pass_tile0 == 0) {
-            // first pass only: the LoRA-B rows and T must have landed; at most one copy group
-            // (a tile's) is newer than T's
-            if (tile + 1 == ntiles) ptx::cp_async_wait<0>();
-            else ptx::cp_async_wait<1>();
-        }
+        ptx::cp_async_wait<0>();  // this thread's pieces of the pass's LoRA-B rows (and of T)
         __syncthreads();
+        if (pass == 0 && p.rank && tid == 0) {
+            // T is in shared memory: count this CTA out; the last one re-arms the flag words
+            const uint32_t old = atomicAdd(p.flags + 1, 1u);
+            if (old == gridDim.x - 1) {
+                p.flags[1] = 0;
+                __threadfence();
+                p.flags[0] = 0;
+            }
+        }
 
-        // ---- everyone: sum the sixteen slots in order, + adapter, + bias, convert, store ----
-        // Thread o takes slot element o (conflict-free reads) and works out which output that
-        // is: element = ((tile * NT + u) * 4 + r) * 32 + source lane.
+        // ---- everyone: sum the K-slices in order, + adapter, + bias, convert, store ----
+        // element o = (tile of the pass * NT * 4 + u * 4 + r) * 32 + source lane
+        const uint32_t pass_tile0 = pass_first(pass) * p.rw;
+        const uint32_t tiles_in_pass = min(ntiles - pass_tile0, cnt * p.rw);
         const uint32_t pass_row0 = n0 + pass_tile0 * kTileRows;
         const uint32_t pass_rows = min(n1 - pass_row0, tiles_in_pass * (uint32_t)kTileRows);
+        const float *park0 = last_pass ? rings : gaps;
         for (uint32_t o = tid; o < tiles_in_pass * NT * 128u; o += kDecodeThreads) {
             const uint32_t src_lane = o & 31u, r = (o >> 5) & 3u, tu = o >> 7;
             const uint32_t ti = tu / NT, u = tu - ti * NT;
-            const uint32_t rr = ti * kTileRows + (r >> 1) * 8u + (src_lane >> 2);
+            const uint32_t trg = ti % p.rw, q = ti / p.rw;  // the warps that hold this tile, and where
+            const uint32_t rr = ti * kTileRows + 2u * (src_lane >> 2) + (r >> 1);
             const uint32_t m = u * 8u + (src_lane & 3u) * 2u + (r & 1u);
             if (rr >= pass_rows || m >= p.M) continue;
-            float v = red[o];
+            const float *sl = park0 + (trg * p.kw) * park_warp + ((q * NT + u) * 4 + r) * park_idx + src_lane;
+            // the K-slices' partial sums, all loaded before the first add, summed in a fixed order
+            float part[kWarps];
             #pragma unroll
-            for (int w = 1; w < kSlots; ++w) v += red[w * slot_floats + o];
+            for (int w = 0; w < kWarps; ++w) part[w] = (uint32_t)w < p.kw ? sl[w * park_warp] : 0.0f;
+            #pragma unroll
+            for (int s2 = 1; s2 < kWarps; s2 <<= 1) {
+                #pragma unroll
+                for (int w = 0; w < kWarps; w += 2 * s2) part[w] += part[w + s2];
+            }
+            float v = part[0];
             if (p.rank) {
-                const __nv_bfloat16 *lb = lora_s + (size_t)(pass_row0 - n0 + rr) * p.rank;
+                const __nv_bfloat16 *lb = lora_s + (size_t)rr * p.rank;
                 const float *tm = t_s + m * p.rank;
                 float dot = 0.0f;
                 if ((p.rank & 7u) == 0) {
@@ -505,33 +572,23 @@ decode_kernel(const DecodeParams p) {
             if (p.y_f32) static_cast<float *>(p.y)[at] = v;
             else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(v);
         }
-        if (warp == 0) NF4_TS(41);
-        pass_tile0 = tile + 1;
-        if (pass_tile0 < ntiles) {
-            __syncthreads();  // the slots have been read
-            build_table();
-            __syncthreads();
-            #pragma unroll
-            for (int q = 0; q < PT; ++q) {
-                #pragma unroll
-                for (int u = 0; u < NT; ++u) acc[q][u][0] = acc[q][u][1] = acc[q][u][2] = acc[q][u][3] = 0.0f;
-            }
+        if (!last_pass) {
+            __syncthreads();  // the pass's LoRA-B rows have been read
+            stage_lora_b(pass + 1);
         }
     }
     ptx::cp_async_wait<0>();
 }
 
-// T[m][j] = sum_k x[m][k] * A[j][k]  (x, A bf16; f32 accumulate).  One 128-thread CTA per (j, m):
-// many short CTAs with at most 32 registers, so that one of them fits on an SM beside a GEMV CTA
-// and the GEMV it overlaps with is not kept off the SMs the pre-pass occupies.
+// T[m][j] = sum_k x[m][k] * A[j][k]  (x, A bf16; f32 accumulate).  One 128-thread CTA per (j, m).
+// Used for adapter ranks the decode kernel does not multiply itself.
 __global__ void __launch_bounds__(128, 16)
 lora_t_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a, uint32_t K,
               uint32_t rank, float *__restrict__ t_out) {
-    ptx::pdl_launch_dependents();  // the GEMV may start streaming weights right away
     const uint32_t j = blockIdx.x, m = blockIdx.y;
     const __nv_bfloat16 *xr = x + (size_t)m * K, *ar = a + (size_t)j * K;
     float acc = 0.0f;
-    if ((K & 7u) == 0) {
+    if ((K & 7u) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a)) & 15u) == 0) {
         const uint4 *x4 = reinterpret_cast<const uint4 *>(xr), *a4 = reinterpret_cast<const uint4 *>(ar);
         for (uint32_t i = threadIdx.x; i < K / 8; i += 128) {
             const uint4 xv = __ldg(x4 + i), av = __ldg(a4 + i);
@@ -562,84 +619,86 @@ uint32_t gcd_u32(uint32_t a, uint32_t b) {
     }
     return a;
 }
-uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
-bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &smem_bytes) {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+int32_t make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t rows,
+                 uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                 CUtensorMapSwizzle swz) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(NF4_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NF4_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return NF4_OK;
+}
+
+bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid) {
     if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
     if (a.rows == 0 || a.rows > 16) return false;
-    if (a.d_in % kChunk != 0 || a.d_in > (uint64_t)kWarps * kMaxChunksPerWarp * kChunk) return false;
+    // whole slices of four blocks: the scale rows then have a 16-byte pitch, which TMA needs
+    if (a.d_in % kSliceK != 0 || a.d_in > (uint64_t)kWarps * kSliceK) return false;
     if (a.d_out >= (1ull << 31)) return false;
     const bool dq = a.scale_codes != nullptr;
     const uint32_t rank = a.lora_a ? a.lora_rank : 0;
     if (rank > kMaxRank) return false;
     const void *scales = dq ? (const void *)a.scale_codes : (const void *)a.absmax;
     if (!aligned16(a.x) || !aligned16(a.packed) || !aligned16(scales)) return false;
-    if (rank && !aligned16(a.lora_b)) return false;
+    if (rank && (!aligned16(a.lora_a) || !aligned16(a.lora_b))) return false;
     if (reinterpret_cast<uintptr_t>(a.y) & (a.y_f32 ? 3u : 1u)) return false;
 
     const uint32_t K = (uint32_t)a.d_in, N = (uint32_t)a.d_out, M = (uint32_t)a.rows;
-    const uint32_t nchunks = K / kChunk;
     const uint32_t nt = M > 8 ? 2u : 1u;
     p = DecodeParams{};
     // CTA row ranges start where the CTA's LoRA-B rows are 16-byte aligned
     const uint32_t gran = rank ? 16u / gcd_u32(16u, rank * 2u) : 1u;
     if (N % gran != 0) return false;
     p.gran = gran;
-    p.chunks_per_warp = (nchunks + kWarps - 1) / kWarps;
-    p.vec_scales = (p.chunks_per_warp == 4 && nchunks % 4 == 0) ? 1u : 0u;
-    p.code_stride = p.chunks_per_warp * 32u + 32u;  // 160 for four chunks: conflict-free 64-bit reads
-    p.slot_bytes = kTileRows * p.code_stride;
+    p.nchunks = K / kChunk;
+    p.kw = K / kSliceK;
+    p.rw = kWarps / p.kw;
 
     const uint64_t units = N / gran;
-    grid = (uint32_t)(units < (uint64_t)kNumSMs ? units : (uint64_t)kNumSMs);
-    const uint32_t max_rows = (uint32_t)(((units + grid - 1) / grid) * gran);
-    const uint32_t max_tiles = (max_rows + kTileRows - 1) / kTileRows;
-    const uint32_t pt_max = nt == 1 ? (uint32_t)PassTiles<1>::value : (uint32_t)PassTiles<2>::value;
-    p.pass_tiles = max_tiles < pt_max ? max_tiles : pt_max;
-    p.red_slot_bytes = p.pass_tiles * nt * 512u;
-    p.lora_bytes_max = round_up(max_rows * rank * 2u, 128);
-    // The kernel puts the table at shared-window address 0x10000 and the rings around it; with
-    // the usual 1 KB reserved at the start of the window that leaves 63 KB below and
-    // (227 - 127) KB above the table.
-    const uint32_t low_room = (kLutWindow - 1024u) & ~127u;
-    const uint32_t high_room = (uint32_t)(kSmemLimit - kSmemLeftForPrepass) + 1024u - (kLutWindow + (uint32_t)kLutBytes);
-    p.scale_stride = nchunks * (dq ? 1u : 4u) + 16u;
-    p.scale_bytes_max = p.vec_scales ? round_up(max_tiles * kTileRows * p.scale_stride, 128) : 0u;
-    const uint32_t high_fixed = 16 * kMaxRank * 4 + 128 + p.lora_bytes_max + p.scale_bytes_max;
-    static const int ring_env = [] {
-        const char *e = std::getenv("NF4_DECODE_RING");  // experiment knob: tiles per warp ring
-        return e ? std::atoi(e) : 0;
-    }();
-    uint32_t ring = 0;
-    for (uint32_t r = 2; r <= (uint32_t)kMaxRing && r <= max_tiles + 1; ++r) {
-        const uint32_t ring_bytes = r * p.slot_bytes;
-        const uint32_t low_warps = low_room / ring_bytes < (uint32_t)kWarps ? low_room / ring_bytes : (uint32_t)kWarps;
-        if (high_fixed + (kWarps - low_warps) * ring_bytes > high_room) break;
-        if (ring_env >= 2 && r > (uint32_t)ring_env) break;
-        ring = r;
-    }
-    if (ring < 2) {
-        // a short matrix still needs two slots
-        const uint32_t ring_bytes = 2 * p.slot_bytes;
-        const uint32_t low_warps = low_room / ring_bytes < (uint32_t)kWarps ? low_room / ring_bytes : (uint32_t)kWarps;
-        if (high_fixed + (kWarps - low_warps) * ring_bytes > high_room) return false;
-        ring = 2;
-    }
-    p.ring = ring;
-    if (kSlots * p.red_slot_bytes > (uint32_t)kLutBytes) return false;  // the slots reuse the table's room
-    smem_bytes = kSmemLimit - kSmemLeftForPrepass;
-    p.smem_bytes = smem_bytes;
-    static const bool no_request = [] {
-        const char *e = std::getenv("NF4_DEBUG_NO_REQUEST");  // read by the timing build only
-        return e && e[0] == '1';
-    }();
-    p.debug_no_request = no_request ? 1u : 0u;
+    const uint64_t tiles = ((uint64_t)N + kTileRows - 1) / kTileRows;
+    uint64_t ctas = tiles < (uint64_t)kNumSMs ? tiles : (uint64_t)kNumSMs;
+    if (ctas > units) ctas = units;
+    grid = (uint32_t)ctas;
+    // a pass's LoRA-B rows must fit their staging room
+    uint32_t pt_last = nt == 1 ? (uint32_t)PassTiles<1>::last : (uint32_t)PassTiles<2>::last;
+    uint32_t pt_early = nt == 1 ? (uint32_t)PassTiles<1>::early : (uint32_t)PassTiles<2>::early;
+    while (pt_last > 1 && rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > kLoraRoom) --pt_last;
+    if (rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > kLoraRoom) return false;
+    if (pt_early > pt_last) pt_early = pt_last;
+    p.pt_last = pt_last;
+    p.pt_early = pt_early;
+    p.n_prod = rank < grid ? rank : grid;
+    p.wait_ns = 1000000000u;
     p.x = static_cast<const __nv_bfloat16 *>(a.x);
-    p.codes = a.packed;
-    p.absmax = a.absmax;
     p.scale_codes = a.scale_codes;
     p.scale_of_scales = a.scale_of_scales;
     p.bias = a.bias;
+    p.lora_a = static_cast<const __nv_bfloat16 *>(a.lora_a);
     p.lora_b = static_cast<const __nv_bfloat16 *>(a.lora_b);
     p.y = a.y;
     p.y_f32 = (uint32_t)a.y_f32;
@@ -652,50 +711,58 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid, uint32_t &s
     return true;
 }
 
-template <int NT, bool DQ, bool FULL, int PT>
-int32_t launch_pt(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
-    static bool configured = false;  // benign race: the attribute is idempotent
-    if (!configured) {
-        NF4_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<NT, DQ, FULL, PT>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-        configured = true;
+template <int NT, bool DQ>
+int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const DecodeParams &p, uint32_t grid,
+               cudaStream_t stream) {
+    // the shared-memory attribute belongs to the device: set it once per device
+    static std::mutex mu;
+    static bool configured[64] = {};
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NF4_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[dev]) {
+            NF4_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<NT, DQ>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+            configured[dev] = true;
+        }
     }
     count_launch();
-    return launch_maybe_overlapped(decode_kernel<NT, DQ, FULL, PT>, dim3(grid), dim3(kDecodeThreads),
-                                   smem_bytes, stream, p.rank != 0 && pdl_enabled(), p);
+    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3(kDecodeThreads), kSmemBytes,
+                                   stream, pdl_enabled(), mc, ms, p);
 }
 
-// the register budget holds 8 tiles of 8 activation rows or 3 tiles of 16; shorter passes get a
-// kernel whose accumulator shift register is as short as they need
-template <int NT, bool DQ, bool FULL>
-int32_t launch_full(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
-    if constexpr (NT == 2) {
-        return launch_pt<NT, DQ, FULL, PassTiles<2>::value>(p, grid, smem_bytes, stream);
-    } else {
-        if (p.pass_tiles <= 2) return launch_pt<NT, DQ, FULL, 2>(p, grid, smem_bytes, stream);
-        if (p.pass_tiles <= 5) return launch_pt<NT, DQ, FULL, 5>(p, grid, smem_bytes, stream);
-        return launch_pt<NT, DQ, FULL, PassTiles<1>::value>(p, grid, smem_bytes, stream);
+// `scratch`: kFlagBytes of flag words (zero at first use, left zero) followed by room for T
+int32_t run(const nf4_linear_args &a, DecodeParams &p, uint32_t grid, void *scratch, cudaStream_t stream) {
+    const bool dq = a.scale_codes != nullptr;
+    if (p.rank) {
+        if (!scratch) return fail(NF4_ERR_INVALID_ARG, "decode_forward: an adapter needs the workspace");
+        p.flags = static_cast<uint32_t *>(scratch);
+        p.t_global = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + kFlagBytes);
     }
-}
-
-template <int NT, bool DQ>
-int32_t launch(const DecodeParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
-    return p.K == (uint32_t)(kWarps * kMaxChunksPerWarp * kChunk)
-               ? launch_full<NT, DQ, true>(p, grid, smem_bytes, stream)
-               : launch_full<NT, DQ, false>(p, grid, smem_bytes, stream);
+    CUtensorMap mc, ms;
+    NF4_TRY(make_map(&mc, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.packed, p.N, p.K / 2, p.K / 2, kTileRows, 128,
+                     CU_TENSOR_MAP_SWIZZLE_128B));
+    if (dq) ms = mc;  // not used by the kernel
+    else
+        NF4_TRY(make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.absmax, p.N, p.nchunks,
+                         (uint64_t)p.nchunks * 4, kTileRows, 4, CU_TENSOR_MAP_SWIZZLE_NONE));
+    if (p.M <= 8) return dq ? launch<1, true>(mc, ms, p, grid, stream) : launch<1, false>(mc, ms, p, grid, stream);
+    return dq ? launch<2, true>(mc, ms, p, grid, stream) : launch<2, false>(mc, ms, p, grid, stream);
 }
 
 }  // namespace
 
 bool decode_supported(const nf4_linear_args &a) {
     DecodeParams p;
-    uint32_t grid, smem;
-    return plan(a, p, grid, smem);
+    uint32_t grid;
+    return plan(a, p, grid);
 }
 
 uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank) {
     if (rows == 0 || rows > 16 || lora_rank == 0) return 0;
-    return (rows * lora_rank * 4 + 255) / 256 * 256;
+    return kFlagBytes + (rows * lora_rank * 4 + 255) / 256 * 256;
 }
 
 // `chained` launches the pre-pass as a programmatic dependent of the kernel ahead of it; the
@@ -710,44 +777,33 @@ int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, ui
 
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
     DecodeParams p;
-    uint32_t grid, smem;
-    if (!plan(a, p, grid, smem)) return fail(NF4_ERR_UNSUPPORTED, "decode_forward: unsupported shape");
-    if (p.rank) {
-        float *t = static_cast<float *>(a.workspace);
-        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream, false));
-        p.t = t;
-    }
-    const bool dq = a.scale_codes != nullptr;
-    if (p.M <= 8) return dq ? launch<1, true>(p, grid, smem, stream) : launch<1, false>(p, grid, smem, stream);
-    return dq ? launch<2, true>(p, grid, smem, stream) : launch<2, false>(p, grid, smem, stream);
+    uint32_t grid;
+    if (!plan(a, p, grid)) return fail(NF4_ERR_UNSUPPORTED, "decode_forward: unsupported shape");
+    return run(a, p, grid, a.workspace, stream);
 }
-
-#ifdef NF4_DECODE_TIMING
-extern "C" __attribute__((visibility("default"))) int nf4_debug_decode_timestamps(long long *out64) {
-    return (int)cudaMemcpyFromSymbol(out64, g_decode_ts, sizeof(long long) * 64);
-}
-#endif
 
 // ---- decode forward whose scratch is a fixed device array (no allocation anywhere) ----
-// The adapter intermediate T = x A^T ([rows][rank] f32) is the only scratch the decode
-// path needs.  Here it lives in a file-scope device array instead of a caller buffer.
-constexpr uint32_t kStaticScratchBytes = 16 * kMaxRank * sizeof(float);  // 16 rows x rank 64
+// The adapter intermediate T = x A^T ([rows][rank] f32) and the two flag words its producers
+// and readers meet on are the only scratch the decode path needs.  Here they live in a
+// file-scope device array instead of a caller buffer.
+constexpr uint32_t kStaticTBytes = 16 * kMaxRank * sizeof(float);  // 16 rows x rank 64
+constexpr uint32_t kStaticScratchBytes = kFlagBytes + kStaticTBytes;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 uint64_t decode_static_scratch_bytes() { return kStaticScratchBytes; }
 
 int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t stream) {
+    const uint64_t need = a.rows * (uint64_t)(a.lora_a ? a.lora_rank : 0) * sizeof(float);
+    if (need > kStaticTBytes)
+        return fail(NF4_ERR_INVALID_ARG,
+                    "nf4_linear_forward_noalloc_dev: rows * rank * 4 = %llu bytes exceeds the %u bytes "
+                    "the fixed scratch has for it", (unsigned long long)need, kStaticTBytes);
     DecodeParams p;
-    uint32_t grid, smem;
-    if (!plan(a, p, grid, smem))
+    uint32_t grid;
+    if (!plan(a, p, grid))
         return fail(NF4_ERR_UNSUPPORTED,
                     "nf4_linear_forward_noalloc_dev: only the decode shapes are served (rows <= 16, "
-                    "bf16, W [d_out, d_in], d_in %% 64 == 0 and <= 4096, rank <= 64)");
-    const uint64_t need = (uint64_t)p.M * p.rank * sizeof(float);
-    if (need > kStaticScratchBytes)
-        return fail(NF4_ERR_INVALID_ARG,
-                    "nf4_linear_forward_noalloc_dev: rows * rank * 4 = %llu bytes exceeds the fixed "
-                    "scratch of %u bytes", (unsigned long long)need, kStaticScratchBytes);
+                    "bf16, W [d_out, d_in], d_in %% 256 == 0 and <= 4096, rank <= 64)");
     // In host code the array's name is only a handle: the device address has to be asked for,
     // once per device, with that device current.
     static std::mutex mu;
@@ -765,19 +821,14 @@ int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t str
         }
         scratch = scratch_of_device[dev];
     }
-    if (p.rank) {
-        float *t = static_cast<float *>(scratch);  // fully rewritten by the pre-pass: no clearing needed
-        NF4_TRY(lora_t_small(a.x, a.lora_a, p.M, p.K, p.rank, t, stream, false));
-        p.t = t;
-    }
-    const bool dq = a.scale_codes != nullptr;
-    if (p.M <= 8) return dq ? launch<1, true>(p, grid, smem, stream) : launch<1, false>(p, grid, smem, stream);
-    return dq ? launch<2, true>(p, grid, smem, stream) : launch<2, false>(p, grid, smem, stream);
+    // The array starts zeroed (static storage) and every call leaves the flag words zero; T is
+    // rewritten by each call before it is read: nothing to clear here.
+    return run(a, p, grid, scratch, stream);
 }
 
-int32_t decode_error_flag(int *host_value) {
-    return check_cuda(cudaMemcpyFromSymbol(host_value, g_decode_error, sizeof(int)),
-                      "read decode error flag");
+int32_t decode_error_flag_ptr(int **dev_ptr) {
+    return check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(dev_ptr), g_decode_error),
+                      "address of the decode error flag");
 }
 
 }  // namespace nf4

@@ -768,4 +768,9 @@ int32_t decode2_forward(const nf4_linear_args &a, cudaStream_t stream) {
     return dq ? launch<true>(mc, ms, pl, stream) : launch<false>(mc, ms, pl, stream);
 }
 
+int32_t decode2_error_flag_ptr(int **dev_ptr) {
+    return check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(dev_ptr), g_decode2_error),
+                      "address of the split-K decode error flag");
+}
+
 }  // namespace nf4

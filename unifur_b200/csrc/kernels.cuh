@@ -54,7 +54,10 @@ bool decode_supported(const nf4_linear_args &a);
 uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank);
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);
 
-int32_t decode_error_flag(int *host_value);
+// device addresses (current device) of the kernels' failure flags
+int32_t decode_error_flag_ptr(int **dev_ptr);
+int32_t decode2_error_flag_ptr(int **dev_ptr);
+int32_t prefill_error_flag_ptr(int **dev_ptr);
 uint64_t decode_static_scratch_bytes();
 int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t stream);
 

@@ -943,9 +943,9 @@ extern "C" __attribute__((visibility("default"))) int nf4_debug_prefill_timestam
 }
 #endif
 
-int32_t prefill_error_flag(int *host_value) {
-    return check_cuda(cudaMemcpyFromSymbol(host_value, g_prefill_error, sizeof(int)),
-                      "read prefill error flag");
+int32_t prefill_error_flag_ptr(int **dev_ptr) {
+    return check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(dev_ptr), g_prefill_error),
+                      "address of the prefill error flag");
 }
 
 }  // namespace nf4

@@ -399,7 +399,9 @@ def linear_forward(x: torch.Tensor, packed: PackedNf4Tensor, d_in: int, d_out: i
         lora_b = lora_b.to(x2.dtype).contiguous()
     y = out if out is not None else torch.empty(rows, d_out, dtype=x2.dtype, device=dev)
     ws_bytes = int(lib.nf4_linear_workspace_bytes(rows, d_in, d_out, rank))
-    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    # zero-filled: the decode kernel's flag words at the start of the workspace must start at zero
+    ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    bias32 = bias.to(torch.float32).contiguous() if bias is not None else None  # alive until the launch
     a = LinearArgs()
     a.struct_bytes = ctypes.sizeof(LinearArgs)
     a.layout, a.io_dtype = layout, dt
@@ -409,7 +411,7 @@ def linear_forward(x: torch.Tensor, packed: PackedNf4Tensor, d_in: int, d_out: i
     a.absmax = packed.absmax.data_ptr() if not packed.is_double_quantized() else None
     a.scale_codes = packed.scale_codes.data_ptr() if packed.is_double_quantized() else None
     a.scale_of_scales = packed.scale_of_scales.data_ptr() if packed.is_double_quantized() else None
-    a.bias = bias.to(torch.float32).contiguous().data_ptr() if bias is not None else None
+    a.bias = bias32.data_ptr() if bias32 is not None else None
     a.lora_a = lora_a.data_ptr() if rank else None
     a.lora_b = lora_b.data_ptr() if rank else None
     a.lora_rank, a.lora_scale = rank, float(lora_scale)
