@@ -58,32 +58,46 @@ int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, ui
 
 namespace {
 
-constexpr int kWarps = 16;
-constexpr int kDecodeThreads = kWarps * 32;
 constexpr int kTileRows = 16;
 constexpr int kChunk = 64;         // one quantization block of K
-constexpr int kSliceChunks = 4;    // blocks per warp slice: K <= 16 * 4 * 64
+constexpr int kSliceChunks = 4;    // blocks per K-slice
 constexpr int kSliceK = kSliceChunks * kChunk;
-constexpr int kRing = 4;           // tiles per warp ring
+constexpr int kMaxSlices = 16;     // K <= 16 * 256
 constexpr int kMaxRank = 64;
 constexpr uint32_t kFlagBytes = 256;  // workspace: [ready, done] words, then T
 constexpr uint32_t kWin0 = 1024;   // shared-window address of dynamic shared memory
-constexpr uint32_t kLutStride = 256;
-constexpr uint32_t kLutBytes = 256 * kLutStride;
-constexpr uint32_t kCodesSlot = kTileRows * 128;
-constexpr uint32_t kScaleSlot = kTileRows * 16;
-constexpr uint32_t kSlotIdx = 16;  // partial-sum registers a warp can park (one table row each)
-// byte offsets from the start of dynamic shared memory
-constexpr uint32_t kOffCodes = kLutBytes;
-constexpr uint32_t kOffScales = kOffCodes + kWarps * kRing * kCodesSlot;
-constexpr uint32_t kOffBars = kOffScales + kWarps * kRing * kScaleSlot;
-constexpr uint32_t kOffT = kOffBars + 512;
-constexpr uint32_t kOffDq = kOffT + 16 * kMaxRank * 4;
-constexpr uint32_t kOffLora = kOffDq + 1024;
-constexpr uint32_t kSmemBytes = 227 * 1024;
-constexpr uint32_t kLoraRoom = kSmemBytes - kOffLora;
-static_assert(kWarps * kRing * 8 <= 512, "barrier room");
-static_assert((kWin0 + kOffCodes) % 1024 == 0, "swizzled boxes need 1024-byte alignment");
+constexpr uint32_t kCodesSlot = kTileRows * 128;  // one K-slice of one tile: nibbles
+constexpr uint32_t kScaleSlot = kTileRows * 16;   // ... and its block scales
+constexpr uint32_t kSlotIdx = 16;  // partial-sum registers a warp can park in the table's gaps
+
+// One CTA per SM: sixteen warps, one K-slice each.  Two tiles per warp ring: with 148 CTAs that is
+// ~70 KB per SM in flight, about what HBM bandwidth times latency needs; deeper rings only queue
+// requests up in the memory system and make every other load (x, the adapter) wait behind them
+// (four tiles per ring measured 13.8 us per forward against 10.1 us with two).
+struct Cfg {
+    static constexpr int kWarps = 16;
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr int kSlices = 1;  // K-slices per warp
+    static constexpr int kRing = 2;    // tiles per warp ring
+    static constexpr uint32_t kLutStride = 256;  // bytes between table entries (128 used)
+    static constexpr uint32_t kLutBytes = 256 * kLutStride;
+    static constexpr uint32_t kCodesTile = kSlices * kCodesSlot;
+    static constexpr uint32_t kScaleTile = kSlices * kScaleSlot;
+    // byte offsets from the start of dynamic shared memory
+    static constexpr uint32_t kOffCodes = kLutBytes;
+    static constexpr uint32_t kOffScales = kOffCodes + kWarps * kRing * kCodesTile;
+    static constexpr uint32_t kOffBars = kOffScales + kWarps * kRing * kScaleTile;
+    static constexpr uint32_t kOffRed = kOffBars + 512;              // [warps][16] f32: slices of a column of T
+    static constexpr uint32_t kOffT = kOffRed + 1024;
+    static constexpr uint32_t kTBytes = 16 * kMaxRank * 4;
+    static constexpr uint32_t kOffDq = kOffT + kTBytes;
+    static constexpr uint32_t kOffLora = kOffDq + 1024;
+    static constexpr uint32_t kLoraRoom = 24 * 1024;                 // LoRA-B rows of one pass
+    static constexpr uint32_t kSmemBytes = kOffLora + kLoraRoom;
+    static_assert(kWarps * kRing * 8 <= 512, "barrier room");
+    static_assert((kWin0 + kOffCodes) % 1024 == 0, "swizzled boxes need 1024-byte alignment");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory");
+};
 
 // tiles a warp may hold between two reductions: in the last pass of a CTA (partials parked in
 // the warp's ring) and in earlier passes (parked in the table's gaps)
@@ -97,9 +111,9 @@ struct DecodeParams {
     const uint8_t *scale_codes;
     const float *scale_of_scales;
     const float *bias;
-    float *t_global;       // [M][rank] f32 = x A^T, written by the producer CTAs (workspace)
+    float *t_global;       // [halves][M][rank] f32 = x A^T, written by the producer CTAs (workspace)
     uint32_t *flags;       // [0] producers that have published, [1] CTAs that have read T
-    uint32_t n_prod;       // CTAs that compute T (each takes the rows j = cta, cta + n_prod, ...)
+    uint32_t n_prod;       // CTAs that compute T (each takes the units cta, cta + n_prod, ...)
     const __nv_bfloat16 *lora_a;
     const __nv_bfloat16 *lora_b;
     void *y;
@@ -108,7 +122,8 @@ struct DecodeParams {
     uint32_t M, K, N, rank;
     float lora_scale;
     uint32_t gran;        // CTA row ranges start on multiples of this
-    uint32_t kw, rw;      // warps along K, groups of warps along rows (kw * rw <= 16)
+    uint32_t kw;          // K-slices of 256
+    uint32_t kwarps, rw;  // warps along K, groups of warps along rows (kwarps * rw <= warps)
     uint32_t pt_last, pt_early;  // tiles per warp in the last pass / in each earlier pass
     uint32_t nchunks;
     uint32_t wait_ns;     // bound of every wait
@@ -160,9 +175,12 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
 }
 
 template <int NT, bool DQ>
-__global__ void __launch_bounds__(kDecodeThreads, 1)
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
               const __grid_constant__ CUtensorMap tm_scales, const DecodeParams p) {
+    using C = Cfg;
+    constexpr int kWarps = C::kWarps, kThreads = C::kThreads, SL = C::kSlices, kRing = C::kRing;
+    constexpr int NC = SL * kSliceChunks;  // 64-blocks of K a warp owns
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int PT = PassTiles<NT>::last;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -175,14 +193,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         ptx::prefetch_tmap(&tm_codes);
         if (!DQ) ptx::prefetch_tmap(&tm_scales);
     }
-    float *t_s = reinterpret_cast<float *>(smem + kOffT);     // [M][rank]
-    float *dq_s = reinterpret_cast<float *>(smem + kOffDq);   // code / 255 for the 256 codes
-    const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(smem + kOffLora);
+    float *red_s = reinterpret_cast<float *>(smem + C::kOffRed);
+    float *t_s = reinterpret_cast<float *>(smem + C::kOffT);     // [SL][M][rank]
+    float *dq_s = reinterpret_cast<float *>(smem + C::kOffDq);   // code / 255 for the 256 codes
+    const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(smem + C::kOffLora);
     // parking places of partial sums: element (warp, idx, lane)
-    float *gaps = reinterpret_cast<float *>(smem + 128);       // + (warp * 16 + idx) * 256 bytes
-    float *rings = reinterpret_cast<float *>(smem + kOffCodes);  // + warp * ring bytes + idx * 128 bytes
-    constexpr uint32_t kGapWarp = kSlotIdx * kLutStride / 4, kGapIdx = kLutStride / 4;
-    constexpr uint32_t kRingWarp = kRing * kCodesSlot / 4, kRingIdx = 32;
+    float *gaps = reinterpret_cast<float *>(smem + 128);            // + (warp * 16 + idx) * 256 bytes
+    float *rings = reinterpret_cast<float *>(smem + C::kOffCodes);  // + warp * ring bytes + idx * 128 bytes
+    constexpr uint32_t kGapWarp = kSlotIdx * 256 / 4, kGapIdx = 256 / 4;
+    constexpr uint32_t kRingWarp = kRing * C::kCodesTile / 4, kRingIdx = 32;
+    static_assert(PT * NT * 4 * 128 <= kRing * C::kCodesTile, "a warp's ring holds its last pass");
 
     // rows owned by this CTA: units of `gran` rows, split evenly over the grid
     const uint64_t units = p.N / p.gran;
@@ -191,47 +211,59 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     const uint32_t ntiles = (n1 - n0 + kTileRows - 1) / kTileRows;
 
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const bool active = warp < p.kw * p.rw;
-    const uint32_t rg = active ? warp / p.kw : 0u;   // which tiles: rg, rg + rw, ...
-    const uint32_t ks = active ? warp - rg * p.kw : 0u;  // which K-slice
+    const bool active = warp < p.kwarps * p.rw;
+    const uint32_t rg = active ? warp / p.kwarps : 0u;      // which tiles: rg, rg + rw, ...
+    const uint32_t kpos = active ? warp - rg * p.kwarps : 0u;  // which K-slices: kpos * SL ...
+    const uint32_t slice0 = kpos * SL;
+    const uint32_t nsl = active ? min((uint32_t)SL, p.kw - slice0) : 0u;  // slices this warp owns
     const uint32_t my_tiles = (active && rg < ntiles) ? (ntiles - rg + p.rw - 1) / p.rw : 0u;
-    const uint32_t k0 = ks * kSliceK;
+    const uint32_t k0 = slice0 * kSliceK;
 
-    const uint32_t bar0 = kWin0 + kOffBars + warp * kRing * 8u;
-    const uint32_t codes0 = kWin0 + kOffCodes + warp * kRing * kCodesSlot;
-    const uint32_t scales0 = kWin0 + kOffScales + warp * kRing * kScaleSlot;
-    const uint8_t *codes_ring = smem + kOffCodes + warp * kRing * kCodesSlot;
-    const uint8_t *scales_ring = smem + kOffScales + warp * kRing * kScaleSlot;
+    const uint32_t bar0 = kWin0 + C::kOffBars + warp * kRing * 8u;
+    const uint32_t codes0 = kWin0 + C::kOffCodes + warp * kRing * C::kCodesTile;
+    const uint32_t scales0 = kWin0 + C::kOffScales + warp * kRing * C::kScaleTile;
+    const uint8_t *codes_ring = smem + C::kOffCodes + warp * kRing * C::kCodesTile;
+    const uint8_t *scales_ring = smem + C::kOffScales + warp * kRing * C::kScaleTile;
 
     // ---- this warp's barriers and its first tiles (nothing here depends on the predecessor):
-    // lane s sets up slot s and asks for tile s, so the four requests leave in one instruction ----
-    auto request_tile = [&](uint32_t j) {
-        // tile number j of this warp goes to slot j % kRing
+    // lane (slot, slice) asks for its box, so the requests of all slots leave in one instruction ----
+    auto request = [&](uint32_t j, uint32_t sl) {
+        // K-slice sl of this warp's tile number j goes to slot j % kRing
         const uint32_t slot = j & (kRing - 1);
         const int32_t row0 = (int32_t)(n0 + (rg + j * p.rw) * kTileRows);
         const uint32_t bar = bar0 + 8 * slot;
         ptx::mbar_arrive_expect_tx(bar, DQ ? kCodesSlot : kCodesSlot + kScaleSlot);
-        ptx::tma_load_2d(codes0 + slot * kCodesSlot, &tm_codes, (int32_t)(ks * 128u), row0, bar);
-        if (!DQ) ptx::tma_load_2d(scales0 + slot * kScaleSlot, &tm_scales, (int32_t)(ks * 4u), row0, bar);
+        ptx::tma_load_2d(codes0 + slot * C::kCodesTile + sl * kCodesSlot, &tm_codes,
+                         (int32_t)((slice0 + sl) * 128u), row0, bar);
+        if (!DQ)
+            ptx::tma_load_2d(scales0 + slot * C::kScaleTile + sl * kScaleSlot, &tm_scales,
+                             (int32_t)((slice0 + sl) * 4u), row0, bar);
     };
-    if (lane < (uint32_t)kRing) {
-        ptx::mbar_init(bar0 + 8 * lane, 1);
-        ptx::fence_mbar_init();
-        ptx::fence_proxy_async();
-        if (lane < my_tiles) request_tile(lane);
+    if (nsl) {
+        if (lane < (uint32_t)kRing) {
+            ptx::mbar_init(bar0 + 8 * lane, nsl);
+            ptx::fence_mbar_init();
+            ptx::fence_proxy_async();
+        }
+        __syncwarp();
+        if (lane < (uint32_t)(kRing * SL)) {
+            const uint32_t j = lane / SL, sl = lane % SL;
+            if (j < my_tiles && sl < nsl) request(j, sl);
+        }
     }
     uint32_t req_j = my_tiles < (uint32_t)kRing ? my_tiles : (uint32_t)kRing;  // tiles requested so far
 
-    // ---- the lookup table: thread (byte, half) writes sixteen lanes' copies of its entry ----
+    // ---- the lookup table: each byte value's entry, one copy per lane ----
     {
+        // thread (byte, half) writes sixteen lanes' copies
         const uint32_t byte = tid >> 1, half = tid & 1u;
         const uint32_t entry = level_f16(byte & 15u) | (level_f16(byte >> 4) << 16);
         const uint4 v = make_uint4(entry, entry, entry, entry);
         #pragma unroll
         for (int i = 0; i < 4; ++i)  // rotated by the byte so that a warp's stores spread over the banks
-            *reinterpret_cast<uint4 *>(smem + byte * kLutStride + half * 64u + ((i + byte) & 3u) * 16u) = v;
-        if (DQ && tid < 256) dq_s[tid] = __fdiv_rn((float)tid, 255.0f);
+            *reinterpret_cast<uint4 *>(smem + byte * 256u + half * 64u + ((i + byte) & 3u) * 16u) = v;
     }
+    if (DQ && tid < 256) dq_s[tid] = __fdiv_rn((float)tid, 255.0f);
 
     // ---- pass plan (the same for every warp): early passes of pt_early tiles per warp, parked in
     // the table's gaps, then one last pass of at most pt_last tiles, parked in the rings ----
@@ -249,25 +281,28 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                 const uint32_t rows = min(n1 - r0, pass_count(pass) * p.rw * kTileRows);
                 const uint32_t pieces = rows * p.rank * 2u / 16u;
                 const uint8_t *src = reinterpret_cast<const uint8_t *>(p.lora_b + (size_t)r0 * p.rank);
-                for (uint32_t q = tid; q < pieces; q += kDecodeThreads)
-                    ptx::cp_async_16(kWin0 + kOffLora + q * 16u, src + (size_t)q * 16u);
+                for (uint32_t q = tid; q < pieces; q += kThreads)
+                    ptx::cp_async_16(kWin0 + C::kOffLora + q * 16u, src + (size_t)q * 16u);
             }
         }
         ptx::cp_async_commit();
     };
     stage_lora_b(0);
 
-    // ---- a producer CTA's row of the adapter factor A, this warp's K-slice of it (raw bf16,
-    // the lane's sixteen consecutive k of each 64-block, the same k the lane holds of x) ----
+    // ---- a producer CTA's unit of T: row j of the adapter factor A against the warps' K-slice
+    // number h (unit = j * SL + h).  The lane loads its sixteen consecutive k of each 64-block,
+    // the same k it holds of x. ----
     const bool producer = p.rank != 0 && blockIdx.x < p.n_prod;
     const bool t_warp = producer && active && rg == 0;
     uint4 araw[kSliceChunks][2];
-    auto load_a = [&](uint32_t j) {
+    auto load_a = [&](uint32_t unit) {
+        const uint32_t j = unit / SL, h = unit % SL;
         #pragma unroll
         for (int c = 0; c < kSliceChunks; ++c) {
             araw[c][0] = araw[c][1] = make_uint4(0, 0, 0, 0);
-            if (t_warp) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(p.lora_a + (size_t)j * p.K + k0 + c * kChunk + 16 * t);
+            if (t_warp && h < nsl) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(
+                    p.lora_a + (size_t)j * p.K + k0 + (h * kSliceChunks + c) * kChunk + 16 * t);
                 araw[c][0] = __ldg(src);
                 araw[c][1] = __ldg(src + 1);
             }
@@ -280,83 +315,101 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
 
-    uint32_t xf[NT][kSliceChunks][4][2];  // this warp's slice of x as f16 B-fragments
-    {
-        uint4 xraw[NT][kSliceChunks][2];
+    // sum over this lane's 64 k of one K-slice: x[m][k] * A[j][k], both raw bf16, f32 products
+    auto dot_slice = [&](const uint4 (&xr)[4][2]) -> float {
+        float part = 0.0f;
         #pragma unroll
-        for (int u = 0; u < NT; ++u) {
-            const uint32_t m = 8 * u + g;
+        for (int c = 0; c < kSliceChunks; ++c) {
+            const uint32_t aw[8] = {araw[c][0].x, araw[c][0].y, araw[c][0].z, araw[c][0].w,
+                                    araw[c][1].x, araw[c][1].y, araw[c][1].z, araw[c][1].w};
+            const uint32_t xw[8] = {xr[c][0].x, xr[c][0].y, xr[c][0].z, xr[c][0].w,
+                                    xr[c][1].x, xr[c][1].y, xr[c][1].z, xr[c][1].w};
             #pragma unroll
-            for (int c = 0; c < kSliceChunks; ++c) {
-                xraw[u][c][0] = xraw[u][c][1] = make_uint4(0, 0, 0, 0);
-                if (m < p.M && active) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(
-                        p.x + (size_t)m * p.K + k0 + c * kChunk + 16 * t);
-                    xraw[u][c][0] = __ldg(src);
-                    xraw[u][c][1] = __ldg(src + 1);
-                }
+            for (int i = 0; i < 8; ++i) {
+                part = fmaf(bf16_bits_to_float(xw[i] & 0xffffu), bf16_bits_to_float(aw[i] & 0xffffu), part);
+                part = fmaf(__uint_as_float(xw[i] & 0xffff0000u), __uint_as_float(aw[i] & 0xffff0000u), part);
             }
         }
-
-        if (producer) {
-            // column j of T: every warp's slice of sum_k x[m][k] A[j][k], f32; the slices meet in
-            // the table's gaps (unused until the first parking) and warp 0 adds them in order
-            for (uint32_t j = blockIdx.x; j < p.rank; j += p.n_prod) {
-                if (j != blockIdx.x) {
-                    __syncthreads();  // the gaps have been read
-                    load_a(j);
-                }
-                #pragma unroll
-                for (int u = 0; u < NT; ++u) {
-                    float part = 0.0f;
-                    #pragma unroll
-                    for (int c = 0; c < kSliceChunks; ++c) {
-                        const uint32_t aw[8] = {araw[c][0].x, araw[c][0].y, araw[c][0].z, araw[c][0].w,
-                                                araw[c][1].x, araw[c][1].y, araw[c][1].z, araw[c][1].w};
-                        const uint32_t xw[8] = {xraw[u][c][0].x, xraw[u][c][0].y, xraw[u][c][0].z, xraw[u][c][0].w,
-                                                xraw[u][c][1].x, xraw[u][c][1].y, xraw[u][c][1].z, xraw[u][c][1].w};
-                        #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            part = fmaf(bf16_bits_to_float(xw[i] & 0xffffu), bf16_bits_to_float(aw[i] & 0xffffu), part);
-                            part = fmaf(__uint_as_float(xw[i] & 0xffff0000u), __uint_as_float(aw[i] & 0xffff0000u), part);
-                        }
-                    }
-                    part += __shfl_xor_sync(0xffffffffu, part, 1);
-                    part += __shfl_xor_sync(0xffffffffu, part, 2);
-                    if (t == 0) gaps[warp * kGapWarp + 8 * u + g] = t_warp ? part : 0.0f;
-                }
-                __syncthreads();
-                if (warp == 0 && lane < p.M) {
-                    float v = 0.0f;
-                    for (uint32_t w = 0; w < (uint32_t)kWarps; ++w) v += gaps[w * kGapWarp + lane];
-                    p.t_global[(size_t)lane * p.rank + j] = v;
-                }
-            }
-            if (warp == 0) {
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) atomicAdd(p.flags, 1u);
+        return part;
+    };
+    // this warp's K-slice `half` of x row m, raw: the lane's sixteen consecutive k of each 64-block
+    auto load_x = [&](uint4 (&xr)[4][2], uint32_t m, uint32_t half) {
+        #pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            xr[cc][0] = xr[cc][1] = make_uint4(0, 0, 0, 0);
+            if (m < p.M && half < nsl) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(
+                    p.x + (size_t)m * p.K + k0 + (half * 4 + cc) * kChunk + 16 * t);
+                xr[cc][0] = __ldg(src);
+                xr[cc][1] = __ldg(src + 1);
             }
         }
+    };
 
+    uint32_t xf[NT][NC][4][2];  // this warp's slices of x as f16 B-fragments
+    float tpart[NT];            // a producer's first unit of T: this lane's part
+    const uint32_t h_first = blockIdx.x % SL;
+    #pragma unroll
+    for (int u = 0; u < NT; ++u) {
+        tpart[u] = 0.0f;
         #pragma unroll
-        for (int u = 0; u < NT; ++u) {
+        for (int half = 0; half < SL; ++half) {
+            uint4 xraw[4][2];
+            load_x(xraw, 8 * u + g, half);
+            if (producer && (uint32_t)half == h_first) tpart[u] = dot_slice(xraw);
             #pragma unroll
-            for (int c = 0; c < kSliceChunks; ++c) {
-                const uint32_t w[8] = {xraw[u][c][0].x, xraw[u][c][0].y, xraw[u][c][0].z, xraw[u][c][0].w,
-                                       xraw[u][c][1].x, xraw[u][c][1].y, xraw[u][c][1].z, xraw[u][c][1].w};
+            for (int cc = 0; cc < 4; ++cc) {
+                const uint32_t w[8] = {xraw[cc][0].x, xraw[cc][0].y, xraw[cc][0].z, xraw[cc][0].w,
+                                       xraw[cc][1].x, xraw[cc][1].y, xraw[cc][1].z, xraw[cc][1].w};
                 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    xf[u][c][j][0] = bf16x2_to_f16x2(w[2 * j]);
-                    xf[u][c][j][1] = bf16x2_to_f16x2(w[2 * j + 1]);
+                    xf[u][half * 4 + cc][j][0] = bf16x2_to_f16x2(w[2 * j]);
+                    xf[u][half * 4 + cc][j][1] = bf16x2_to_f16x2(w[2 * j + 1]);
                 }
             }
         }
     }
-    if (producer) __syncthreads();  // the gaps are free again
 
-    // Warp 0 brings T into shared memory shortly before the first pass ends: a bounded wait for the
-    // producers' count, then asynchronous copies that the end-of-pass wait collects.
+    if (producer) {
+        // Unit (j, h) of T: every warp's K-slice h of sum_k x[m][k] A[j][k]; the slices meet in
+        // shared memory, warp 0 adds them in order and writes column j of half h.  The first
+        // unit was multiplied while x passed through the registers; a CTA that has more units
+        // (fewer CTAs than units: short matrices) reads x again for them.
+        for (uint32_t unit = blockIdx.x; unit < p.rank * SL; unit += p.n_prod) {
+            const uint32_t j = unit / SL, h = unit % SL;
+            if (unit != blockIdx.x) {
+                __syncthreads();  // the slices of the unit before have been read
+                load_a(unit);
+                #pragma unroll
+                for (int u = 0; u < NT; ++u) {
+                    uint4 xraw[4][2];
+                    load_x(xraw, 8 * u + g, h);
+                    tpart[u] = dot_slice(xraw);
+                }
+            }
+            #pragma unroll
+            for (int u = 0; u < NT; ++u) {
+                float part = tpart[u];
+                part += __shfl_xor_sync(0xffffffffu, part, 1);
+                part += __shfl_xor_sync(0xffffffffu, part, 2);
+                if (t == 0) red_s[warp * 16 + 8 * u + g] = t_warp ? part : 0.0f;
+            }
+            __syncthreads();
+            if (warp == 0 && lane < p.M) {
+                float v = 0.0f;
+                for (uint32_t w = 0; w < (uint32_t)kWarps; ++w) v += red_s[w * 16 + lane];
+                p.t_global[((size_t)h * p.M + lane) * p.rank + j] = v;
+            }
+        }
+        if (warp == 0) {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(p.flags, 1u);
+        }
+    }
+
+    // Warp 0 brings T into shared memory shortly before the first pass ends: a bounded wait for
+    // the producers' count, then asynchronous copies that the end-of-pass wait collects.
     bool lost = false;   // a wait of this warp ran out: results are void, the flag is set
     auto fetch_t = [&]() {
         uint32_t ok = 1;
@@ -372,9 +425,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) lost = true;
-        const uint32_t n = p.M * p.rank;
+        const uint32_t n = SL * p.M * p.rank;
         if ((n & 3u) == 0) {
-            for (uint32_t i = lane * 4; i < n; i += 128) ptx::cp_async_16(kWin0 + kOffT + i * 4u, p.t_global + i);
+            for (uint32_t i = lane * 4; i < n; i += 128) ptx::cp_async_16(kWin0 + C::kOffT + i * 4u, p.t_global + i);
         } else {
             for (uint32_t i = lane; i < n; i += 32) t_s[i] = __ldcg(p.t_global + i);
         }
@@ -390,19 +443,26 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(kWin0));
         return v;
     };
-    // byte offsets of this lane's first 8 bytes in rows 2g and 2g + 1 of a swizzled tile; the
+    // byte offsets of this lane's first 8 bytes in rows 2g and 2g + 1 of a swizzled box; the
     // 32-byte block c of the row is at (offset ^ (c << 5))
     const uint32_t off_lo = (2 * g) * 128u + ((((t >> 1) ^ ((2 * g) & 7u))) << 4) + (t & 1u) * 8u;
     const uint32_t off_hi = (2 * g + 1) * 128u + ((((t >> 1) ^ ((2 * g + 1) & 7u))) << 4) + (t & 1u) * 8u;
 
     // double-quantized scales come straight from global memory, one tile ahead
-    uint32_t dq_lo = 0, dq_hi = 0;
+    uint32_t dq_lo[SL], dq_hi[SL];
+    #pragma unroll
+    for (int sl = 0; sl < SL; ++sl) dq_lo[sl] = dq_hi[sl] = 0;
     auto fetch_dq = [&](uint32_t j) {
         if (DQ && j < my_tiles) {
             const uint32_t row = n0 + (rg + j * p.rw) * kTileRows + 2 * g;
             const uint32_t r_lo = min(row, p.N - 1), r_hi = min(row + 1, p.N - 1);
-            dq_lo = __ldg(reinterpret_cast<const uint32_t *>(p.scale_codes + (size_t)r_lo * p.nchunks + ks * 4u));
-            dq_hi = __ldg(reinterpret_cast<const uint32_t *>(p.scale_codes + (size_t)r_hi * p.nchunks + ks * 4u));
+            #pragma unroll
+            for (int sl = 0; sl < SL; ++sl) {
+                if ((uint32_t)sl < nsl) {
+                    dq_lo[sl] = __ldg(reinterpret_cast<const uint32_t *>(p.scale_codes + (size_t)r_lo * p.nchunks + (slice0 + sl) * 4u));
+                    dq_hi[sl] = __ldg(reinterpret_cast<const uint32_t *>(p.scale_codes + (size_t)r_hi * p.nchunks + (slice0 + sl) * 4u));
+                }
+            }
         }
     };
     fetch_dq(0);
@@ -432,58 +492,66 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                     lost = true;
                     if (lane == 0) atomicExch(&g_decode_error, 5);
                 }
-                const uint8_t *cs = codes_ring + slot * kCodesSlot;
-                uint2 w0[kSliceChunks], w1[kSliceChunks];
                 #pragma unroll
-                for (int c = 0; c < kSliceChunks; ++c) {
-                    w0[c] = *reinterpret_cast<const uint2 *>(cs + (off_lo ^ ((uint32_t)c << 5)));
-                    w1[c] = *reinterpret_cast<const uint2 *>(cs + (off_hi ^ ((uint32_t)c << 5)));
-                }
-                float s_lo[kSliceChunks], s_hi[kSliceChunks];
-                if (DQ) {
-                    #pragma unroll
-                    for (int c = 0; c < kSliceChunks; ++c) {
-                        s_lo[c] = __fmul_rn(dq_s[(dq_lo >> (8 * c)) & 0xffu], sos);
-                        s_hi[c] = __fmul_rn(dq_s[(dq_hi >> (8 * c)) & 0xffu], sos);
-                    }
-                } else {
-                    const float4 a = *reinterpret_cast<const float4 *>(scales_ring + slot * kScaleSlot + g * 32u);
-                    const float4 b = *reinterpret_cast<const float4 *>(scales_ring + slot * kScaleSlot + g * 32u + 16u);
-                    s_lo[0] = a.x; s_lo[1] = a.y; s_lo[2] = a.z; s_lo[3] = a.w;
-                    s_hi[0] = b.x; s_hi[1] = b.y; s_hi[2] = b.z; s_hi[3] = b.w;
-                }
-                ++use_j;
-                fetch_dq(use_j);
-                // every lane holds its part of the tile in registers: the slot can be refilled
-                __syncwarp();
-                if (req_j < my_tiles) {
-                    if (lane == 0) request_tile(req_j);
-                    ++req_j;
-                }
-
-                #pragma unroll
-                for (int c = 0; c < kSliceChunks; ++c) {
-                    float blk[NT][4];
-                    #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t x0 = (j < 2) ? w0[c].x : w0[c].y;
-                        const uint32_t x1 = (j < 2) ? w1[c].x : w1[c].y;
-                        const int b = 2 * (j & 1);
-                        const uint32_t a0 = lut_at(x0, b), a1 = lut_at(x1, b);
-                        const uint32_t a2 = lut_at(x0, b + 1), a3 = lut_at(x1, b + 1);
+                for (int sl = 0; sl < SL; ++sl) {
+                    if ((uint32_t)sl < nsl) {
+                        const uint8_t *cs = codes_ring + slot * C::kCodesTile + sl * kCodesSlot;
+                        uint2 w0[kSliceChunks], w1[kSliceChunks];
                         #pragma unroll
-                        for (int u = 0; u < NT; ++u) {
-                            if (j == 0)
-                                ptx::mma_16816_f16_zero(blk[u], a0, a1, a2, a3, xf[u][c][j][0], xf[u][c][j][1]);
-                            else
-                                ptx::mma_16816_f16(blk[u], a0, a1, a2, a3, xf[u][c][j][0], xf[u][c][j][1]);
+                        for (int c = 0; c < kSliceChunks; ++c) {
+                            w0[c] = *reinterpret_cast<const uint2 *>(cs + (off_lo ^ ((uint32_t)c << 5)));
+                            w1[c] = *reinterpret_cast<const uint2 *>(cs + (off_hi ^ ((uint32_t)c << 5)));
                         }
-                    }
-                    #pragma unroll
-                    for (int u = 0; u < NT; ++u) {
+                        float s_lo[kSliceChunks], s_hi[kSliceChunks];
+                        if (DQ) {
+                            #pragma unroll
+                            for (int c = 0; c < kSliceChunks; ++c) {
+                                s_lo[c] = __fmul_rn(dq_s[(dq_lo[sl] >> (8 * c)) & 0xffu], sos);
+                                s_hi[c] = __fmul_rn(dq_s[(dq_hi[sl] >> (8 * c)) & 0xffu], sos);
+                            }
+                        } else {
+                            const uint8_t *ss = scales_ring + slot * C::kScaleTile + sl * kScaleSlot + g * 32u;
+                            const float4 a = *reinterpret_cast<const float4 *>(ss);
+                            const float4 b = *reinterpret_cast<const float4 *>(ss + 16u);
+                            s_lo[0] = a.x; s_lo[1] = a.y; s_lo[2] = a.z; s_lo[3] = a.w;
+                            s_hi[0] = b.x; s_hi[1] = b.y; s_hi[2] = b.z; s_hi[3] = b.w;
+                        }
+                        if (sl + 1 == SL || (uint32_t)sl + 1 == nsl) {
+                            // every lane holds the last of the tile in registers: refill the slot
+                            ++use_j;
+                            fetch_dq(use_j);
+                            __syncwarp();
+                            if (req_j < my_tiles) {
+                                if (lane < nsl) request(req_j, lane);
+                                ++req_j;
+                            }
+                        }
+
                         #pragma unroll
-                        for (int r = 0; r < 4; ++r)
-                            acc[q][u][r] = fmaf(blk[u][r], r < 2 ? s_lo[c] : s_hi[c], acc[q][u][r]);
+                        for (int c = 0; c < kSliceChunks; ++c) {
+                            float blk[NT][4];
+                            #pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t x0 = (j < 2) ? w0[c].x : w0[c].y;
+                                const uint32_t x1 = (j < 2) ? w1[c].x : w1[c].y;
+                                const int b = 2 * (j & 1);
+                                const uint32_t a0 = lut_at(x0, b), a1 = lut_at(x1, b);
+                                const uint32_t a2 = lut_at(x0, b + 1), a3 = lut_at(x1, b + 1);
+                                #pragma unroll
+                                for (int u = 0; u < NT; ++u) {
+                                    const uint32_t b0 = xf[u][sl * kSliceChunks + c][j][0];
+                                    const uint32_t b1 = xf[u][sl * kSliceChunks + c][j][1];
+                                    if (j == 0) ptx::mma_16816_f16_zero(blk[u], a0, a1, a2, a3, b0, b1);
+                                    else ptx::mma_16816_f16(blk[u], a0, a1, a2, a3, b0, b1);
+                                }
+                            }
+                            #pragma unroll
+                            for (int u = 0; u < NT; ++u) {
+                                #pragma unroll
+                                for (int r = 0; r < 4; ++r)
+                                    acc[q][u][r] = fmaf(blk[u][r], r < 2 ? s_lo[c] : s_hi[c], acc[q][u][r]);
+                            }
+                        }
                     }
                 }
             }
@@ -495,7 +563,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         float *park = last_pass ? rings + warp * kRingWarp : gaps + warp * kGapWarp;
         const uint32_t park_idx = last_pass ? kRingIdx : kGapIdx;
         const uint32_t park_warp = last_pass ? kRingWarp : kGapWarp;
-        if (!last_pass && pass > 0) __syncthreads();  // the gaps are free
         #pragma unroll
         for (int q = 0; q < PT; ++q) {
             if ((uint32_t)q < mine) {
@@ -519,25 +586,25 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             }
         }
 
-        // ---- everyone: sum the K-slices in order, + adapter, + bias, convert, store ----
+        // ---- everyone: sum the K-slices in a fixed order, + adapter, + bias, convert, store ----
         // element o = (tile of the pass * NT * 4 + u * 4 + r) * 32 + source lane
         const uint32_t pass_tile0 = pass_first(pass) * p.rw;
         const uint32_t tiles_in_pass = min(ntiles - pass_tile0, cnt * p.rw);
         const uint32_t pass_row0 = n0 + pass_tile0 * kTileRows;
         const uint32_t pass_rows = min(n1 - pass_row0, tiles_in_pass * (uint32_t)kTileRows);
         const float *park0 = last_pass ? rings : gaps;
-        for (uint32_t o = tid; o < tiles_in_pass * NT * 128u; o += kDecodeThreads) {
+        for (uint32_t o = tid; o < tiles_in_pass * NT * 128u; o += kThreads) {
             const uint32_t src_lane = o & 31u, r = (o >> 5) & 3u, tu = o >> 7;
             const uint32_t ti = tu / NT, u = tu - ti * NT;
             const uint32_t trg = ti % p.rw, q = ti / p.rw;  // the warps that hold this tile, and where
             const uint32_t rr = ti * kTileRows + 2u * (src_lane >> 2) + (r >> 1);
             const uint32_t m = u * 8u + (src_lane & 3u) * 2u + (r & 1u);
             if (rr >= pass_rows || m >= p.M) continue;
-            const float *sl = park0 + (trg * p.kw) * park_warp + ((q * NT + u) * 4 + r) * park_idx + src_lane;
-            // the K-slices' partial sums, all loaded before the first add, summed in a fixed order
+            const float *sl = park0 + (trg * p.kwarps) * park_warp + ((q * NT + u) * 4 + r) * park_idx + src_lane;
+            // the K-warps' partial sums, all loaded before the first add, summed in a fixed order
             float part[kWarps];
             #pragma unroll
-            for (int w = 0; w < kWarps; ++w) part[w] = (uint32_t)w < p.kw ? sl[w * park_warp] : 0.0f;
+            for (int w = 0; w < kWarps; ++w) part[w] = (uint32_t)w < p.kwarps ? sl[w * park_warp] : 0.0f;
             #pragma unroll
             for (int s2 = 1; s2 < kWarps; s2 <<= 1) {
                 #pragma unroll
@@ -547,12 +614,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             if (p.rank) {
                 const __nv_bfloat16 *lb = lora_s + (size_t)rr * p.rank;
                 const float *tm = t_s + m * p.rank;
+                const uint32_t t_half = p.M * p.rank;  // a second K-slice's T would follow the first
                 float dot = 0.0f;
                 if ((p.rank & 7u) == 0) {
                     for (uint32_t j = 0; j < p.rank; j += 8) {
                         const uint4 bq = *reinterpret_cast<const uint4 *>(lb + j);
-                        const float4 t0 = *reinterpret_cast<const float4 *>(tm + j);
-                        const float4 t1 = *reinterpret_cast<const float4 *>(tm + j + 4);
+                        float4 t0 = *reinterpret_cast<const float4 *>(tm + j);
+                        float4 t1 = *reinterpret_cast<const float4 *>(tm + j + 4);
+                        if (SL == 2) {
+                            const float4 t2 = *reinterpret_cast<const float4 *>(tm + t_half + j);
+                            const float4 t3 = *reinterpret_cast<const float4 *>(tm + t_half + j + 4);
+                            t0.x += t2.x; t0.y += t2.y; t0.z += t2.z; t0.w += t2.w;
+                            t1.x += t3.x; t1.y += t3.y; t1.z += t3.z; t1.w += t3.w;
+                        }
                         dot = fmaf(t0.x, bf16_bits_to_float(bq.x & 0xffffu), dot);
                         dot = fmaf(t0.y, bf16_bits_to_float(bq.x >> 16), dot);
                         dot = fmaf(t0.z, bf16_bits_to_float(bq.y & 0xffffu), dot);
@@ -563,7 +637,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                         dot = fmaf(t1.w, bf16_bits_to_float(bq.w >> 16), dot);
                     }
                 } else {
-                    for (uint32_t j = 0; j < p.rank; ++j) dot = fmaf(tm[j], __bfloat162float(lb[j]), dot);
+                    for (uint32_t j = 0; j < p.rank; ++j) {
+                        const float tv = SL == 2 ? tm[j] + tm[t_half + j] : tm[j];
+                        dot = fmaf(tv, __bfloat162float(lb[j]), dot);
+                    }
                 }
                 v = fmaf(dot, p.lora_scale, v);  // scale applied last
             }
@@ -573,7 +650,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(v);
         }
         if (!last_pass) {
-            __syncthreads();  // the pass's LoRA-B rows have been read
+            __syncthreads();  // the pass's LoRA-B rows and the gaps have been read
             stage_lora_b(pass + 1);
         }
     }
@@ -654,11 +731,42 @@ int32_t make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uin
     return NF4_OK;
 }
 
-bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid) {
+struct Plan {
+    DecodeParams p;
+    uint32_t grid;
+};
+
+// Fills the shape-dependent fields; false when the shape does not fit.
+bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran, Plan &pl) {
+    using C = Cfg;
+    DecodeParams &p = pl.p;
+    const uint32_t nt = M > 8 ? 2u : 1u;
+    p.kw = K / kSliceK;
+    p.kwarps = (p.kw + C::kSlices - 1) / C::kSlices;
+    p.rw = C::kWarps / p.kwarps;
+    const uint64_t units = N / gran;
+    const uint64_t tiles = ((uint64_t)N + kTileRows - 1) / kTileRows;
+    uint64_t ctas = tiles < (uint64_t)kNumSMs ? tiles : (uint64_t)kNumSMs;
+    if (ctas > units) ctas = units;
+    pl.grid = (uint32_t)ctas;
+    // a pass's LoRA-B rows must fit their staging room
+    uint32_t pt_last = nt == 1 ? (uint32_t)PassTiles<1>::last : (uint32_t)PassTiles<2>::last;
+    uint32_t pt_early = nt == 1 ? (uint32_t)PassTiles<1>::early : (uint32_t)PassTiles<2>::early;
+    while (pt_last > 1 && rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > C::kLoraRoom) --pt_last;
+    if (rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > C::kLoraRoom) return false;
+    if (pt_early > pt_last) pt_early = pt_last;
+    p.pt_last = pt_last;
+    p.pt_early = pt_early;
+    const uint32_t t_units = rank * C::kSlices;
+    p.n_prod = t_units < pl.grid ? t_units : pl.grid;
+    return true;
+}
+
+bool plan(const nf4_linear_args &a, Plan &pl) {
     if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
     if (a.rows == 0 || a.rows > 16) return false;
     // whole slices of four blocks: the scale rows then have a 16-byte pitch, which TMA needs
-    if (a.d_in % kSliceK != 0 || a.d_in > (uint64_t)kWarps * kSliceK) return false;
+    if (a.d_in % kSliceK != 0 || a.d_in > (uint64_t)kMaxSlices * kSliceK) return false;
     if (a.d_out >= (1ull << 31)) return false;
     const bool dq = a.scale_codes != nullptr;
     const uint32_t rank = a.lora_a ? a.lora_rank : 0;
@@ -669,30 +777,14 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid) {
     if (reinterpret_cast<uintptr_t>(a.y) & (a.y_f32 ? 3u : 1u)) return false;
 
     const uint32_t K = (uint32_t)a.d_in, N = (uint32_t)a.d_out, M = (uint32_t)a.rows;
-    const uint32_t nt = M > 8 ? 2u : 1u;
+    DecodeParams &p = pl.p;
     p = DecodeParams{};
     // CTA row ranges start where the CTA's LoRA-B rows are 16-byte aligned
     const uint32_t gran = rank ? 16u / gcd_u32(16u, rank * 2u) : 1u;
     if (N % gran != 0) return false;
     p.gran = gran;
     p.nchunks = K / kChunk;
-    p.kw = K / kSliceK;
-    p.rw = kWarps / p.kw;
-
-    const uint64_t units = N / gran;
-    const uint64_t tiles = ((uint64_t)N + kTileRows - 1) / kTileRows;
-    uint64_t ctas = tiles < (uint64_t)kNumSMs ? tiles : (uint64_t)kNumSMs;
-    if (ctas > units) ctas = units;
-    grid = (uint32_t)ctas;
-    // a pass's LoRA-B rows must fit their staging room
-    uint32_t pt_last = nt == 1 ? (uint32_t)PassTiles<1>::last : (uint32_t)PassTiles<2>::last;
-    uint32_t pt_early = nt == 1 ? (uint32_t)PassTiles<1>::early : (uint32_t)PassTiles<2>::early;
-    while (pt_last > 1 && rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > kLoraRoom) --pt_last;
-    if (rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > kLoraRoom) return false;
-    if (pt_early > pt_last) pt_early = pt_last;
-    p.pt_last = pt_last;
-    p.pt_early = pt_early;
-    p.n_prod = rank < grid ? rank : grid;
+    if (!plan_shape(M, K, N, rank, gran, pl)) return false;
     p.wait_ns = 1000000000u;
     p.x = static_cast<const __nv_bfloat16 *>(a.x);
     p.scale_codes = a.scale_codes;
@@ -712,8 +804,8 @@ bool plan(const nf4_linear_args &a, DecodeParams &p, uint32_t &grid) {
 }
 
 template <int NT, bool DQ>
-int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const DecodeParams &p, uint32_t grid,
-               cudaStream_t stream) {
+int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
+    using C = Cfg;
     // the shared-memory attribute belongs to the device: set it once per device
     static std::mutex mu;
     static bool configured[64] = {};
@@ -724,17 +816,18 @@ int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const DecodeParams 
         std::lock_guard<std::mutex> lock(mu);
         if (!configured[dev]) {
             NF4_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<NT, DQ>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
             configured[dev] = true;
         }
     }
     count_launch();
-    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(grid), dim3(kDecodeThreads), kSmemBytes,
-                                   stream, pdl_enabled(), mc, ms, p);
+    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(pl.grid), dim3(C::kThreads),
+                                   C::kSmemBytes, stream, pdl_enabled(), mc, ms, pl.p);
 }
 
 // `scratch`: kFlagBytes of flag words (zero at first use, left zero) followed by room for T
-int32_t run(const nf4_linear_args &a, DecodeParams &p, uint32_t grid, void *scratch, cudaStream_t stream) {
+int32_t run(const nf4_linear_args &a, Plan &pl, void *scratch, cudaStream_t stream) {
+    DecodeParams &p = pl.p;
     const bool dq = a.scale_codes != nullptr;
     if (p.rank) {
         if (!scratch) return fail(NF4_ERR_INVALID_ARG, "decode_forward: an adapter needs the workspace");
@@ -748,21 +841,20 @@ int32_t run(const nf4_linear_args &a, DecodeParams &p, uint32_t grid, void *scra
     else
         NF4_TRY(make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.absmax, p.N, p.nchunks,
                          (uint64_t)p.nchunks * 4, kTileRows, 4, CU_TENSOR_MAP_SWIZZLE_NONE));
-    if (p.M <= 8) return dq ? launch<1, true>(mc, ms, p, grid, stream) : launch<1, false>(mc, ms, p, grid, stream);
-    return dq ? launch<2, true>(mc, ms, p, grid, stream) : launch<2, false>(mc, ms, p, grid, stream);
+    if (p.M <= 8) return dq ? launch<1, true>(mc, ms, pl, stream) : launch<1, false>(mc, ms, pl, stream);
+    return dq ? launch<2, true>(mc, ms, pl, stream) : launch<2, false>(mc, ms, pl, stream);
 }
 
 }  // namespace
 
 bool decode_supported(const nf4_linear_args &a) {
-    DecodeParams p;
-    uint32_t grid;
-    return plan(a, p, grid);
+    Plan pl;
+    return plan(a, pl);
 }
 
 uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank) {
     if (rows == 0 || rows > 16 || lora_rank == 0) return 0;
-    return kFlagBytes + (rows * lora_rank * 4 + 255) / 256 * 256;
+    return kFlagBytes + (2 * rows * lora_rank * 4 + 255) / 256 * 256;  // T, in two K-halves at most
 }
 
 // `chained` launches the pre-pass as a programmatic dependent of the kernel ahead of it; the
@@ -776,10 +868,9 @@ int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, ui
 }
 
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
-    DecodeParams p;
-    uint32_t grid;
-    if (!plan(a, p, grid)) return fail(NF4_ERR_UNSUPPORTED, "decode_forward: unsupported shape");
-    return run(a, p, grid, a.workspace, stream);
+    Plan pl;
+    if (!plan(a, pl)) return fail(NF4_ERR_UNSUPPORTED, "decode_forward: unsupported shape");
+    return run(a, pl, a.workspace, stream);
 }
 
 // ---- decode forward whose scratch is a fixed device array (no allocation anywhere) ----
@@ -798,9 +889,8 @@ int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t str
         return fail(NF4_ERR_INVALID_ARG,
                     "nf4_linear_forward_noalloc_dev: rows * rank * 4 = %llu bytes exceeds the %u bytes "
                     "the fixed scratch has for it", (unsigned long long)need, kStaticTBytes);
-    DecodeParams p;
-    uint32_t grid;
-    if (!plan(a, p, grid))
+    Plan pl;
+    if (!plan(a, pl))
         return fail(NF4_ERR_UNSUPPORTED,
                     "nf4_linear_forward_noalloc_dev: only the decode shapes are served (rows <= 16, "
                     "bf16, W [d_out, d_in], d_in %% 256 == 0 and <= 4096, rank <= 64)");
@@ -823,7 +913,7 @@ int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t str
     }
     // The array starts zeroed (static storage) and every call leaves the flag words zero; T is
     // rewritten by each call before it is read: nothing to clear here.
-    return run(a, p, grid, scratch, stream);
+    return run(a, pl, scratch, stream);
 }
 
 int32_t decode_error_flag_ptr(int **dev_ptr) {
