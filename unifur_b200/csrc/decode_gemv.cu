@@ -33,11 +33,17 @@
 // the producers have long finished -- with a bounded wait on the flag.  The last CTA to have read
 // T puts the flag words back to zero, which is the state the workspace must have at first use.
 //
-// Reduction.  A warp keeps the partial sums of a pass of tiles in registers.  At the end of a
-// pass every warp parks them -- in its own ring when no more tiles follow (the usual case: a
-// CTA's rows fit one pass), else in the unused upper halves of the table's 256-byte rows -- and
-// all threads sum the slices in a fixed order (so results do not depend on timing), add bias and
-// the LoRA term, convert and store.
+// Reduction.  When a warp has multiplied a tile it parks the tile's partial sums (four f32 per
+// lane and eight activation rows) in its own row of a parking area in shared memory.  After a
+// pass of tiles (all of a CTA's rows in the usual case) every warp takes one (tile, eight
+// activation rows) job: it sums the K-warps' partials in a fixed order (so results do not depend
+// on timing), adds the LoRA term with one bf16 MMA pair per sixteen ranks (LoRA-B rows x T, T split
+// into bf16 high and low parts) and the bias, converts and stores.
+//
+// Code size.  The tile loop is rolled and nothing in it is replicated per tile: the kernel is
+// launched once per forward and runs for microseconds, so code that is executed once is fetched
+// from memory every time, and a 90 KB kernel (the tile body unrolled five times) spent most of
+// its time waiting for instructions.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -68,7 +74,8 @@ constexpr uint32_t kFlagBytes = 256;  // workspace: [ready, done] words, then T
 constexpr uint32_t kWin0 = 1024;   // shared-window address of dynamic shared memory
 constexpr uint32_t kCodesSlot = kTileRows * 128;  // one K-slice of one tile: nibbles
 constexpr uint32_t kScaleSlot = kTileRows * 16;   // ... and its block scales
-constexpr uint32_t kSlotIdx = 16;  // partial-sum registers a warp can park in the table's gaps
+constexpr uint32_t kParkSlots = 10; // (tile, eight activation rows) results a warp can park per pass
+constexpr uint32_t kGapRows = 256;  // LoRA-B rows the table's gaps hold (one row of up to 128 bytes each)
 
 // One CTA per SM: sixteen warps, one K-slice each.  Two tiles per warp ring: with 148 CTAs that is
 // ~70 KB per SM in flight, about what HBM bandwidth times latency needs; deeper rings only queue
@@ -91,19 +98,11 @@ struct Cfg {
     static constexpr uint32_t kOffT = kOffRed + 1024;
     static constexpr uint32_t kTBytes = 16 * kMaxRank * 4;
     static constexpr uint32_t kOffDq = kOffT + kTBytes;
-    static constexpr uint32_t kOffLora = kOffDq + 1024;
-    static constexpr uint32_t kLoraRoom = 24 * 1024;                 // LoRA-B rows of one pass
-    static constexpr uint32_t kSmemBytes = kOffLora + kLoraRoom;
+    static constexpr uint32_t kOffPark = kOffDq + 1024;              // [warps][kParkSlots][32 lanes] float4
+    static constexpr uint32_t kSmemBytes = kOffPark + kWarps * kParkSlots * 512;
     static_assert(kWarps * kRing * 8 <= 512, "barrier room");
     static_assert((kWin0 + kOffCodes) % 1024 == 0, "swizzled boxes need 1024-byte alignment");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory");
-};
-
-// tiles a warp may hold between two reductions: in the last pass of a CTA (partials parked in
-// the warp's ring) and in earlier passes (parked in the table's gaps)
-template <int NT> struct PassTiles {
-    static constexpr int last = NT == 1 ? 5 : 3;
-    static constexpr int early = kSlotIdx / (4 * NT);
 };
 
 struct DecodeParams {
@@ -124,7 +123,7 @@ struct DecodeParams {
     uint32_t gran;        // CTA row ranges start on multiples of this
     uint32_t kw;          // K-slices of 256
     uint32_t kwarps, rw;  // warps along K, groups of warps along rows (kwarps * rw <= warps)
-    uint32_t pt_last, pt_early;  // tiles per warp in the last pass / in each earlier pass
+    uint32_t pass_tiles;  // tiles per warp between two reductions
     uint32_t nchunks;
     uint32_t wait_ns;     // bound of every wait
 };
@@ -182,7 +181,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     constexpr int kWarps = C::kWarps, kThreads = C::kThreads, SL = C::kSlices, kRing = C::kRing;
     constexpr int NC = SL * kSliceChunks;  // 64-blocks of K a warp owns
     extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr int PT = PassTiles<NT>::last;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (ptx::smem_addr(smem) != kWin0) {
         // the table's base is an immediate of the lookups: nothing can run from another address
@@ -196,13 +194,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     float *red_s = reinterpret_cast<float *>(smem + C::kOffRed);
     float *t_s = reinterpret_cast<float *>(smem + C::kOffT);     // [SL][M][rank]
     float *dq_s = reinterpret_cast<float *>(smem + C::kOffDq);   // code / 255 for the 256 codes
-    const __nv_bfloat16 *lora_s = reinterpret_cast<const __nv_bfloat16 *>(smem + C::kOffLora);
-    // parking places of partial sums: element (warp, idx, lane)
-    float *gaps = reinterpret_cast<float *>(smem + 128);            // + (warp * 16 + idx) * 256 bytes
-    float *rings = reinterpret_cast<float *>(smem + C::kOffCodes);  // + warp * ring bytes + idx * 128 bytes
-    constexpr uint32_t kGapWarp = kSlotIdx * 256 / 4, kGapIdx = 256 / 4;
-    constexpr uint32_t kRingWarp = kRing * C::kCodesTile / 4, kRingIdx = 32;
-    static_assert(PT * NT * 4 * 128 <= kRing * C::kCodesTile, "a warp's ring holds its last pass");
+    // LoRA-B rows of a pass live in the table's gaps (the unused upper half of each 256-byte row)
+    const uint8_t *lora_s = smem + 128;                             // row i at + i * 256 bytes
+    // parking place of a tile's partial sums: element (warp, slot, lane) is one float4
+    float *park_s = reinterpret_cast<float *>(smem + C::kOffPark);
+    constexpr uint32_t kParkWarp = kParkSlots * 128;                // floats per warp
 
     // rows owned by this CTA: units of `gran` rows, split evenly over the grid
     const uint64_t units = p.N / p.gran;
@@ -265,24 +261,22 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     }
     if (DQ && tid < 256) dq_s[tid] = __fdiv_rn((float)tid, 255.0f);
 
-    // ---- pass plan (the same for every warp): early passes of pt_early tiles per warp, parked in
-    // the table's gaps, then one last pass of at most pt_last tiles, parked in the rings ----
+    // ---- pass plan (the same for every warp): pass_tiles tiles per warp, then a reduction ----
     const uint32_t max_tiles = (ntiles + p.rw - 1) / p.rw;  // tiles of the busiest warp
-    const uint32_t n_early = max_tiles > p.pt_last ? (max_tiles - p.pt_last + p.pt_early - 1) / p.pt_early : 0u;
-    const uint32_t npasses = n_early + 1;
-    auto pass_first = [&](uint32_t pass) { return pass * p.pt_early; };  // warp-local tile a pass starts at
-    auto pass_count = [&](uint32_t pass) { return pass < n_early ? p.pt_early : max_tiles - n_early * p.pt_early; };
+    const uint32_t npasses = (max_tiles + p.pass_tiles - 1) / p.pass_tiles;
 
     // LoRA-B rows of one pass of tiles, staged by everyone with 16-byte asynchronous copies
+    const uint32_t row_pieces = p.rank * 2u / 16u;  // 16-byte pieces per row (rank % 8 == 0 here)
     auto stage_lora_b = [&](uint32_t pass) {
         if (p.rank) {
-            const uint32_t r0 = n0 + pass_first(pass) * p.rw * kTileRows;
+            const uint32_t r0 = n0 + pass * p.pass_tiles * p.rw * kTileRows;
             if (r0 < n1) {
-                const uint32_t rows = min(n1 - r0, pass_count(pass) * p.rw * kTileRows);
-                const uint32_t pieces = rows * p.rank * 2u / 16u;
+                const uint32_t rows = min(n1 - r0, p.pass_tiles * p.rw * kTileRows);
                 const uint8_t *src = reinterpret_cast<const uint8_t *>(p.lora_b + (size_t)r0 * p.rank);
-                for (uint32_t q = tid; q < pieces; q += kThreads)
-                    ptx::cp_async_16(kWin0 + C::kOffLora + q * 16u, src + (size_t)q * 16u);
+                for (uint32_t q = tid; q < rows * row_pieces; q += kThreads) {
+                    const uint32_t row = q / row_pieces, piece = q - row * row_pieces;
+                    ptx::cp_async_16(kWin0 + 128u + row * 256u + piece * 16u, src + (size_t)q * 16u);
+                }
             }
         }
         ptx::cp_async_commit();
@@ -408,12 +402,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         }
     }
 
-    // Warp 0 brings T into shared memory shortly before the first pass ends: a bounded wait for
-    // the producers' count, then asynchronous copies that the end-of-pass wait collects.
+    // Warp 0 brings T into shared memory shortly before the first pass ends.  Its lane 0 reads
+    // the producers' count one tile early (the load is in flight while that tile is multiplied),
+    // waits -- bounded -- only if the count is not there yet, then the warp issues asynchronous
+    // copies that the end-of-pass wait collects.
     bool lost = false;   // a wait of this warp ran out: results are void, the flag is set
+    uint32_t seen = 0;   // lane 0 of warp 0: the producers' count as last read
+    uint32_t done_old = 0xffffffffu;  // lane 0 of warp 0: CTAs that had read T before this one
+    auto peek_t = [&]() {
+        if (lane == 0) seen = ld_acquire_gpu(p.flags);
+    };
     auto fetch_t = [&]() {
         uint32_t ok = 1;
-        if (lane == 0 && ld_acquire_gpu(p.flags) != p.n_prod) {
+        if (lane == 0 && seen != p.n_prod) {
             const uint64_t t0 = ptx::global_timer_ns();
             while (ld_acquire_gpu(p.flags) != p.n_prod) {
                 if (ptx::global_timer_ns() - t0 > (uint64_t)p.wait_ns) {
@@ -471,190 +472,178 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
 
     #pragma unroll 1
     for (uint32_t pass = 0; pass < npasses; ++pass) {
-        const bool last_pass = pass + 1 == npasses;
-        float acc[PT][NT][4];
-        #pragma unroll
-        for (int q = 0; q < PT; ++q) {
-            #pragma unroll
-            for (int u = 0; u < NT; ++u) acc[q][u][0] = acc[q][u][1] = acc[q][u][2] = acc[q][u][3] = 0.0f;
-        }
         const uint32_t left = my_tiles - use_j;
-        const uint32_t cnt = pass_count(pass);
-        const uint32_t mine = left < cnt ? left : cnt;  // tiles of this warp in this pass
-        if (pass == 0 && p.rank && warp == 0 && mine == 0) fetch_t();
+        const uint32_t mine = left < p.pass_tiles ? left : p.pass_tiles;  // tiles of this warp in this pass
+        const bool t_pass = pass == 0 && p.rank != 0 && warp == 0;  // this warp fetches T in this pass
+        if (t_pass && mine < 2) peek_t();
+        if (t_pass && mine == 0) fetch_t();
 
-        #pragma unroll
-        for (int q = 0; q < PT; ++q) {
-            if ((uint32_t)q < mine) {
-                if (pass == 0 && p.rank && warp == 0 && (uint32_t)q + 1 == mine) fetch_t();
-                const uint32_t slot = use_j & (kRing - 1);
-                if (!lost && !wait_phase(bar0 + 8 * slot, (use_j / kRing) & 1u, p.wait_ns)) {
-                    lost = true;
-                    if (lane == 0) atomicExch(&g_decode_error, 5);
-                }
-                #pragma unroll
-                for (int sl = 0; sl < SL; ++sl) {
-                    if ((uint32_t)sl < nsl) {
-                        const uint8_t *cs = codes_ring + slot * C::kCodesTile + sl * kCodesSlot;
-                        uint2 w0[kSliceChunks], w1[kSliceChunks];
+        #pragma unroll 1
+        for (uint32_t q = 0; q < mine; ++q) {
+            if (t_pass && q + 2 == mine) peek_t();
+            if (t_pass && q + 1 == mine) fetch_t();
+            const uint32_t slot = use_j & (kRing - 1);
+            if (!lost && !wait_phase(bar0 + 8 * slot, (use_j / kRing) & 1u, p.wait_ns)) {
+                lost = true;
+                if (lane == 0) atomicExch(&g_decode_error, 5);
+            }
+            float acc[NT][4];
+            #pragma unroll
+            for (int u = 0; u < NT; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
+            #pragma unroll
+            for (int sl = 0; sl < SL; ++sl) {
+                if ((uint32_t)sl < nsl) {
+                    const uint8_t *cs = codes_ring + slot * C::kCodesTile + sl * kCodesSlot;
+                    uint2 w0[kSliceChunks], w1[kSliceChunks];
+                    #pragma unroll
+                    for (int c = 0; c < kSliceChunks; ++c) {
+                        w0[c] = *reinterpret_cast<const uint2 *>(cs + (off_lo ^ ((uint32_t)c << 5)));
+                        w1[c] = *reinterpret_cast<const uint2 *>(cs + (off_hi ^ ((uint32_t)c << 5)));
+                    }
+                    float s_lo[kSliceChunks], s_hi[kSliceChunks];
+                    if (DQ) {
                         #pragma unroll
                         for (int c = 0; c < kSliceChunks; ++c) {
-                            w0[c] = *reinterpret_cast<const uint2 *>(cs + (off_lo ^ ((uint32_t)c << 5)));
-                            w1[c] = *reinterpret_cast<const uint2 *>(cs + (off_hi ^ ((uint32_t)c << 5)));
+                            s_lo[c] = __fmul_rn(dq_s[(dq_lo[sl] >> (8 * c)) & 0xffu], sos);
+                            s_hi[c] = __fmul_rn(dq_s[(dq_hi[sl] >> (8 * c)) & 0xffu], sos);
                         }
-                        float s_lo[kSliceChunks], s_hi[kSliceChunks];
-                        if (DQ) {
-                            #pragma unroll
-                            for (int c = 0; c < kSliceChunks; ++c) {
-                                s_lo[c] = __fmul_rn(dq_s[(dq_lo[sl] >> (8 * c)) & 0xffu], sos);
-                                s_hi[c] = __fmul_rn(dq_s[(dq_hi[sl] >> (8 * c)) & 0xffu], sos);
-                            }
-                        } else {
-                            const uint8_t *ss = scales_ring + slot * C::kScaleTile + sl * kScaleSlot + g * 32u;
-                            const float4 a = *reinterpret_cast<const float4 *>(ss);
-                            const float4 b = *reinterpret_cast<const float4 *>(ss + 16u);
-                            s_lo[0] = a.x; s_lo[1] = a.y; s_lo[2] = a.z; s_lo[3] = a.w;
-                            s_hi[0] = b.x; s_hi[1] = b.y; s_hi[2] = b.z; s_hi[3] = b.w;
+                    } else {
+                        const uint8_t *ss = scales_ring + slot * C::kScaleTile + sl * kScaleSlot + g * 32u;
+                        const float4 a = *reinterpret_cast<const float4 *>(ss);
+                        const float4 b = *reinterpret_cast<const float4 *>(ss + 16u);
+                        s_lo[0] = a.x; s_lo[1] = a.y; s_lo[2] = a.z; s_lo[3] = a.w;
+                        s_hi[0] = b.x; s_hi[1] = b.y; s_hi[2] = b.z; s_hi[3] = b.w;
+                    }
+                    if (sl + 1 == SL || (uint32_t)sl + 1 == nsl) {
+                        // every lane holds the last of the tile in registers: refill the slot
+                        ++use_j;
+                        fetch_dq(use_j);
+                        __syncwarp();
+                        if (req_j < my_tiles) {
+                            if (lane < nsl) request(req_j, lane);
+                            ++req_j;
                         }
-                        if (sl + 1 == SL || (uint32_t)sl + 1 == nsl) {
-                            // every lane holds the last of the tile in registers: refill the slot
-                            ++use_j;
-                            fetch_dq(use_j);
-                            __syncwarp();
-                            if (req_j < my_tiles) {
-                                if (lane < nsl) request(req_j, lane);
-                                ++req_j;
-                            }
-                        }
+                    }
 
+                    #pragma unroll
+                    for (int c = 0; c < kSliceChunks; ++c) {
+                        float blk[NT][4];
                         #pragma unroll
-                        for (int c = 0; c < kSliceChunks; ++c) {
-                            float blk[NT][4];
-                            #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t x0 = (j < 2) ? w0[c].x : w0[c].y;
-                                const uint32_t x1 = (j < 2) ? w1[c].x : w1[c].y;
-                                const int b = 2 * (j & 1);
-                                const uint32_t a0 = lut_at(x0, b), a1 = lut_at(x1, b);
-                                const uint32_t a2 = lut_at(x0, b + 1), a3 = lut_at(x1, b + 1);
-                                #pragma unroll
-                                for (int u = 0; u < NT; ++u) {
-                                    const uint32_t b0 = xf[u][sl * kSliceChunks + c][j][0];
-                                    const uint32_t b1 = xf[u][sl * kSliceChunks + c][j][1];
-                                    if (j == 0) ptx::mma_16816_f16_zero(blk[u], a0, a1, a2, a3, b0, b1);
-                                    else ptx::mma_16816_f16(blk[u], a0, a1, a2, a3, b0, b1);
-                                }
-                            }
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t x0 = (j < 2) ? w0[c].x : w0[c].y;
+                            const uint32_t x1 = (j < 2) ? w1[c].x : w1[c].y;
+                            const int b = 2 * (j & 1);
+                            const uint32_t a0 = lut_at(x0, b), a1 = lut_at(x1, b);
+                            const uint32_t a2 = lut_at(x0, b + 1), a3 = lut_at(x1, b + 1);
                             #pragma unroll
                             for (int u = 0; u < NT; ++u) {
-                                #pragma unroll
-                                for (int r = 0; r < 4; ++r)
-                                    acc[q][u][r] = fmaf(blk[u][r], r < 2 ? s_lo[c] : s_hi[c], acc[q][u][r]);
+                                const uint32_t b0 = xf[u][sl * kSliceChunks + c][j][0];
+                                const uint32_t b1 = xf[u][sl * kSliceChunks + c][j][1];
+                                if (j == 0) ptx::mma_16816_f16_zero(blk[u], a0, a1, a2, a3, b0, b1);
+                                else ptx::mma_16816_f16(blk[u], a0, a1, a2, a3, b0, b1);
                             }
+                        }
+                        #pragma unroll
+                        for (int u = 0; u < NT; ++u) {
+                            #pragma unroll
+                            for (int r = 0; r < 4; ++r)
+                                acc[u][r] = fmaf(blk[u][r], r < 2 ? s_lo[c] : s_hi[c], acc[u][r]);
                         }
                     }
                 }
             }
+            // park the tile's partial sums: slot q * NT + u of this warp, one float4 per lane
+            #pragma unroll
+            for (int u = 0; u < NT; ++u)
+                *reinterpret_cast<float4 *>(park_s + warp * kParkWarp + (q * NT + u) * 128u + lane * 4u) =
+                    make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
         }
 
         // ================= end of a pass: reduce, finish and store its rows =================
-        // Partials of the last pass go to the warp's own ring (all its tiles have been read);
-        // earlier passes use the table's gaps, which the pass before them may still be reading.
-        float *park = last_pass ? rings + warp * kRingWarp : gaps + warp * kGapWarp;
-        const uint32_t park_idx = last_pass ? kRingIdx : kGapIdx;
-        const uint32_t park_warp = last_pass ? kRingWarp : kGapWarp;
-        #pragma unroll
-        for (int q = 0; q < PT; ++q) {
-            if ((uint32_t)q < mine) {
-                #pragma unroll
-                for (int u = 0; u < NT; ++u) {
-                    #pragma unroll
-                    for (int r = 0; r < 4; ++r)
-                        park[((q * NT + u) * 4 + r) * park_idx + lane] = acc[q][u][r];
-                }
-            }
-        }
         ptx::cp_async_wait<0>();  // this thread's pieces of the pass's LoRA-B rows (and of T)
+        // T has left global memory: count this CTA out (the count comes back while the pass is
+        // finished; it is looked at when the kernel ends)
+        if (t_pass && lane == 0) done_old = atomicAdd(p.flags + 1, 1u);
         __syncthreads();
-        if (pass == 0 && p.rank && tid == 0) {
-            // T is in shared memory: count this CTA out; the last one re-arms the flag words
-            const uint32_t old = atomicAdd(p.flags + 1, 1u);
-            if (old == gridDim.x - 1) {
-                p.flags[1] = 0;
-                __threadfence();
-                p.flags[0] = 0;
-            }
-        }
 
-        // ---- everyone: sum the K-slices in a fixed order, + adapter, + bias, convert, store ----
-        // element o = (tile of the pass * NT * 4 + u * 4 + r) * 32 + source lane
-        const uint32_t pass_tile0 = pass_first(pass) * p.rw;
-        const uint32_t tiles_in_pass = min(ntiles - pass_tile0, cnt * p.rw);
+        // ---- a warp per (tile, eight activation rows): sum the K-warps' partials in a fixed
+        // order, add the adapter term (one bf16 MMA pair per sixteen ranks: B rows x T, T split
+        // into bf16 high and low parts so that its f32 value survives), bias, convert, store ----
+        const uint32_t pass_tile0 = pass * p.pass_tiles * p.rw;
+        const uint32_t tiles_in_pass = min(ntiles - pass_tile0, p.pass_tiles * p.rw);
         const uint32_t pass_row0 = n0 + pass_tile0 * kTileRows;
         const uint32_t pass_rows = min(n1 - pass_row0, tiles_in_pass * (uint32_t)kTileRows);
-        const float *park0 = last_pass ? rings : gaps;
-        for (uint32_t o = tid; o < tiles_in_pass * NT * 128u; o += kThreads) {
-            const uint32_t src_lane = o & 31u, r = (o >> 5) & 3u, tu = o >> 7;
-            const uint32_t ti = tu / NT, u = tu - ti * NT;
+        #pragma unroll 1
+        for (uint32_t job = warp; job < tiles_in_pass * NT; job += kWarps) {
+            const uint32_t ti = job / NT, u = job - ti * NT;
             const uint32_t trg = ti % p.rw, q = ti / p.rw;  // the warps that hold this tile, and where
-            const uint32_t rr = ti * kTileRows + 2u * (src_lane >> 2) + (r >> 1);
-            const uint32_t m = u * 8u + (src_lane & 3u) * 2u + (r & 1u);
-            if (rr >= pass_rows || m >= p.M) continue;
-            const float *sl = park0 + (trg * p.kwarps) * park_warp + ((q * NT + u) * 4 + r) * park_idx + src_lane;
-            // the K-warps' partial sums, all loaded before the first add, summed in a fixed order
-            float part[kWarps];
+            // four K-warps at a time (a fixed order of additions: results do not depend on timing)
+            const float *src = park_s + (trg * p.kwarps) * kParkWarp + (q * NT + u) * 128u + lane * 4u;
+            auto ld4 = [&](uint32_t w) -> float4 {
+                return w < p.kwarps ? *reinterpret_cast<const float4 *>(src + w * kParkWarp)
+                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            };
+            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             #pragma unroll
-            for (int w = 0; w < kWarps; ++w) part[w] = (uint32_t)w < p.kwarps ? sl[w * park_warp] : 0.0f;
-            #pragma unroll
-            for (int s2 = 1; s2 < kWarps; s2 <<= 1) {
-                #pragma unroll
-                for (int w = 0; w < kWarps; w += 2 * s2) part[w] += part[w + s2];
+            for (int w4 = 0; w4 < kWarps; w4 += 4) {
+                const float4 pa = ld4(w4), pb = ld4(w4 + 1), pc = ld4(w4 + 2), pd = ld4(w4 + 3);
+                v[0] += (pa.x + pb.x) + (pc.x + pd.x);
+                v[1] += (pa.y + pb.y) + (pc.y + pd.y);
+                v[2] += (pa.z + pb.z) + (pc.z + pd.z);
+                v[3] += (pa.w + pb.w) + (pc.w + pd.w);
             }
-            float v = part[0];
+            // this lane's outputs: rows 2g, 2g+1 of the tile, activation rows m0, m0 + 1
+            const uint32_t row_a = ti * kTileRows + 2u * g, m0 = u * 8u + 2u * t;
             if (p.rank) {
-                const __nv_bfloat16 *lb = lora_s + (size_t)rr * p.rank;
-                const float *tm = t_s + m * p.rank;
-                const uint32_t t_half = p.M * p.rank;  // a second K-slice's T would follow the first
-                float dot = 0.0f;
-                if ((p.rank & 7u) == 0) {
-                    for (uint32_t j = 0; j < p.rank; j += 8) {
-                        const uint4 bq = *reinterpret_cast<const uint4 *>(lb + j);
-                        float4 t0 = *reinterpret_cast<const float4 *>(tm + j);
-                        float4 t1 = *reinterpret_cast<const float4 *>(tm + j + 4);
-                        if (SL == 2) {
-                            const float4 t2 = *reinterpret_cast<const float4 *>(tm + t_half + j);
-                            const float4 t3 = *reinterpret_cast<const float4 *>(tm + t_half + j + 4);
-                            t0.x += t2.x; t0.y += t2.y; t0.z += t2.z; t0.w += t2.w;
-                            t1.x += t3.x; t1.y += t3.y; t1.z += t3.z; t1.w += t3.w;
-                        }
-                        dot = fmaf(t0.x, bf16_bits_to_float(bq.x & 0xffffu), dot);
-                        dot = fmaf(t0.y, bf16_bits_to_float(bq.x >> 16), dot);
-                        dot = fmaf(t0.z, bf16_bits_to_float(bq.y & 0xffffu), dot);
-                        dot = fmaf(t0.w, bf16_bits_to_float(bq.y >> 16), dot);
-                        dot = fmaf(t1.x, bf16_bits_to_float(bq.z & 0xffffu), dot);
-                        dot = fmaf(t1.y, bf16_bits_to_float(bq.z >> 16), dot);
-                        dot = fmaf(t1.z, bf16_bits_to_float(bq.w & 0xffffu), dot);
-                        dot = fmaf(t1.w, bf16_bits_to_float(bq.w >> 16), dot);
-                    }
-                } else {
-                    for (uint32_t j = 0; j < p.rank; ++j) {
-                        const float tv = SL == 2 ? tm[j] + tm[t_half + j] : tm[j];
-                        dot = fmaf(tv, __bfloat162float(lb[j]), dot);
-                    }
+                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const __nv_bfloat16 *lb0 = reinterpret_cast<const __nv_bfloat16 *>(lora_s + (size_t)row_a * 256u);
+                const __nv_bfloat16 *lb1 = reinterpret_cast<const __nv_bfloat16 *>(lora_s + (size_t)(row_a + 1) * 256u);
+                const float *tm = t_s + (u * 8u + g) * p.rank;  // B operand: column m = 8u + g of T^T
+                const bool m_ok = u * 8u + g < p.M;
+                #pragma unroll 1
+                for (uint32_t k16 = 0; k16 < p.rank; k16 += 16) {
+                    const uint32_t ka = k16 + 2u * t, kb = ka + 8u;
+                    const bool oka = ka < p.rank, okb = kb < p.rank;
+                    const uint32_t a0 = oka ? *reinterpret_cast<const uint32_t *>(lb0 + ka) : 0u;
+                    const uint32_t a1 = oka ? *reinterpret_cast<const uint32_t *>(lb1 + ka) : 0u;
+                    const uint32_t a2 = okb ? *reinterpret_cast<const uint32_t *>(lb0 + kb) : 0u;
+                    const uint32_t a3 = okb ? *reinterpret_cast<const uint32_t *>(lb1 + kb) : 0u;
+                    const float2 ta = (oka && m_ok) ? *reinterpret_cast<const float2 *>(tm + ka) : make_float2(0.0f, 0.0f);
+                    const float2 tb = (okb && m_ok) ? *reinterpret_cast<const float2 *>(tm + kb) : make_float2(0.0f, 0.0f);
+                    const __nv_bfloat162 ha = __floats2bfloat162_rn(ta.x, ta.y), hb = __floats2bfloat162_rn(tb.x, tb.y);
+                    const __nv_bfloat162 la = __floats2bfloat162_rn(ta.x - __low2float(ha), ta.y - __high2float(ha));
+                    const __nv_bfloat162 lb = __floats2bfloat162_rn(tb.x - __low2float(hb), tb.y - __high2float(hb));
+                    ptx::mma_16816_bf16(d, a0, a1, a2, a3, *reinterpret_cast<const uint32_t *>(&ha),
+                                        *reinterpret_cast<const uint32_t *>(&hb));
+                    ptx::mma_16816_bf16(d, a0, a1, a2, a3, *reinterpret_cast<const uint32_t *>(&la),
+                                        *reinterpret_cast<const uint32_t *>(&lb));
                 }
-                v = fmaf(dot, p.lora_scale, v);  // scale applied last
+                #pragma unroll
+                for (int r = 0; r < 4; ++r) v[r] = fmaf(d[r], p.lora_scale, v[r]);  // scale applied last
             }
-            if (p.bias) v += __ldg(p.bias + pass_row0 + rr);
-            const size_t at = (size_t)m * p.ldy + pass_row0 + rr;
-            if (p.y_f32) static_cast<float *>(p.y)[at] = v;
-            else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(v);
+            #pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const uint32_t rr = row_a + (r >> 1), m = m0 + (r & 1u);
+                if (rr >= pass_rows || m >= p.M) continue;
+                float o = v[r];
+                if (p.bias) o += __ldg(p.bias + pass_row0 + rr);
+                const size_t at = (size_t)m * p.ldy + pass_row0 + rr;
+                if (p.y_f32) static_cast<float *>(p.y)[at] = o;
+                else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(o);
+            }
         }
-        if (!last_pass) {
-            __syncthreads();  // the pass's LoRA-B rows and the gaps have been read
+        if (pass + 1 < npasses) {
+            __syncthreads();  // the pass's LoRA-B rows and parked sums have been read
             stage_lora_b(pass + 1);
         }
     }
     ptx::cp_async_wait<0>();
+    if (done_old == gridDim.x - 1) {
+        // the last CTA to have read T re-arms the flag words for the next launch
+        p.flags[1] = 0;
+        __threadfence();
+        p.flags[0] = 0;
+    }
 }
 
 // T[m][j] = sum_k x[m][k] * A[j][k]  (x, A bf16; f32 accumulate).  One 128-thread CTA per (j, m).
@@ -749,14 +738,15 @@ bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran
     uint64_t ctas = tiles < (uint64_t)kNumSMs ? tiles : (uint64_t)kNumSMs;
     if (ctas > units) ctas = units;
     pl.grid = (uint32_t)ctas;
-    // a pass's LoRA-B rows must fit their staging room
-    uint32_t pt_last = nt == 1 ? (uint32_t)PassTiles<1>::last : (uint32_t)PassTiles<2>::last;
-    uint32_t pt_early = nt == 1 ? (uint32_t)PassTiles<1>::early : (uint32_t)PassTiles<2>::early;
-    while (pt_last > 1 && rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > C::kLoraRoom) --pt_last;
-    if (rank && (uint64_t)pt_last * p.rw * kTileRows * rank * 2u > C::kLoraRoom) return false;
-    if (pt_early > pt_last) pt_early = pt_last;
-    p.pt_last = pt_last;
-    p.pt_early = pt_early;
+    // tiles per warp between two reductions: what the parking area and (with an adapter) the
+    // table's gaps hold
+    uint32_t pt = kParkSlots / nt;
+    if (rank) {
+        const uint32_t by_rows = kGapRows / (p.rw * kTileRows);
+        if (by_rows == 0) return false;
+        if (pt > by_rows) pt = by_rows;
+    }
+    p.pass_tiles = pt;
     const uint32_t t_units = rank * C::kSlices;
     p.n_prod = t_units < pl.grid ? t_units : pl.grid;
     return true;
@@ -770,7 +760,7 @@ bool plan(const nf4_linear_args &a, Plan &pl) {
     if (a.d_out >= (1ull << 31)) return false;
     const bool dq = a.scale_codes != nullptr;
     const uint32_t rank = a.lora_a ? a.lora_rank : 0;
-    if (rank > kMaxRank) return false;
+    if (rank > kMaxRank || rank % 8 != 0) return false;  // LoRA-B rows move in 16-byte pieces
     const void *scales = dq ? (const void *)a.scale_codes : (const void *)a.absmax;
     if (!aligned16(a.x) || !aligned16(a.packed) || !aligned16(scales)) return false;
     if (rank && (!aligned16(a.lora_a) || !aligned16(a.lora_b))) return false;
