@@ -120,10 +120,15 @@ struct DecodeParams {
     uint32_t y_f32;
     uint32_t M, K, N, rank;
     float lora_scale;
-    uint32_t gran;        // CTA row ranges start on multiples of this
+    // CTA c owns rows_base (+ gran if c < rows_extra) rows; ranges start on multiples of gran
+    uint32_t gran, rows_base, rows_extra;
     uint32_t kw;          // K-slices of 256
-    uint32_t kwarps, rw;  // warps along K, groups of warps along rows (kwarps * rw <= warps)
+    uint32_t kwarps;      // warps along K
+    uint32_t rw_shift;    // 1 << rw_shift groups of warps take different tiles (kwarps << rw_shift <= warps)
     uint32_t pass_tiles;  // tiles per warp between two reductions
+    uint32_t piece_shift; // a LoRA-B row is 1 << piece_shift pieces of 16 bytes
+    uint8_t warp_rg[16];  // per warp: its group along rows (0xff: the warp has no work)
+    uint8_t warp_kpos[16];  // per warp: its position along K
     uint32_t nchunks;
     uint32_t wait_ns;     // bound of every wait
 };
@@ -157,15 +162,10 @@ __device__ __forceinline__ bool wait_phase(uint32_t bar, uint32_t parity, uint32
     }
 }
 
-// the sixteen f16 levels as immediates (a table in constant memory would be read with a
-// different index per lane, which the constant cache serialises)
-__device__ __forceinline__ uint32_t level_f16(uint32_t code) {
-    constexpr uint32_t L[16] = {NF4_LEVEL_F16_BITS_LIST};
-    uint32_t v = L[0];
-    #pragma unroll
-    for (int k = 1; k < 16; ++k) v = (code == (uint32_t)k) ? L[k] : v;
-    return v;
-}
+// The sixteen f16 levels, read with plain loads when the table is built (a table in constant
+// memory would be read with a different index per lane, which the constant cache serialises; a
+// chain of selects on immediates costs sixty instructions that are fetched cold at every launch).
+__device__ const uint32_t g_level_f16[16] = {NF4_LEVEL_F16_BITS_LIST};
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
     uint32_t v;
@@ -187,7 +187,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         if (tid == 0) atomicExch(&g_decode_error, 4);
         return;
     }
-    if (tid == 0) {
+    if (lane == 0) {  // the descriptors are on their way while the table is built
         ptx::prefetch_tmap(&tm_codes);
         if (!DQ) ptx::prefetch_tmap(&tm_scales);
     }
@@ -200,19 +200,20 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     float *park_s = reinterpret_cast<float *>(smem + C::kOffPark);
     constexpr uint32_t kParkWarp = kParkSlots * 128;                // floats per warp
 
-    // rows owned by this CTA: units of `gran` rows, split evenly over the grid
-    const uint64_t units = p.N / p.gran;
-    const uint32_t n0 = (uint32_t)((uint64_t)blockIdx.x * units / gridDim.x) * p.gran;
-    const uint32_t n1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * units / gridDim.x) * p.gran;
+    // rows owned by this CTA
+    const uint32_t extra = min(blockIdx.x, p.rows_extra);
+    const uint32_t n0 = blockIdx.x * p.rows_base + extra * p.gran;
+    const uint32_t n1 = n0 + p.rows_base + (blockIdx.x < p.rows_extra ? p.gran : 0u);
     const uint32_t ntiles = (n1 - n0 + kTileRows - 1) / kTileRows;
 
     const uint32_t g = lane >> 2, t = lane & 3u;
-    const bool active = warp < p.kwarps * p.rw;
-    const uint32_t rg = active ? warp / p.kwarps : 0u;      // which tiles: rg, rg + rw, ...
-    const uint32_t kpos = active ? warp - rg * p.kwarps : 0u;  // which K-slices: kpos * SL ...
+    const uint32_t rw = 1u << p.rw_shift;
+    const uint32_t rg = p.warp_rg[warp];        // which tiles: rg, rg + rw, ...
+    const bool active = rg != 0xffu;
+    const uint32_t kpos = p.warp_kpos[warp];    // which K-slices: kpos * SL ...
     const uint32_t slice0 = kpos * SL;
     const uint32_t nsl = active ? min((uint32_t)SL, p.kw - slice0) : 0u;  // slices this warp owns
-    const uint32_t my_tiles = (active && rg < ntiles) ? (ntiles - rg + p.rw - 1) / p.rw : 0u;
+    const uint32_t my_tiles = (active && rg < ntiles) ? (ntiles - rg + rw - 1) >> p.rw_shift : 0u;
     const uint32_t k0 = slice0 * kSliceK;
 
     const uint32_t bar0 = kWin0 + C::kOffBars + warp * kRing * 8u;
@@ -226,7 +227,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     auto request = [&](uint32_t j, uint32_t sl) {
         // K-slice sl of this warp's tile number j goes to slot j % kRing
         const uint32_t slot = j & (kRing - 1);
-        const int32_t row0 = (int32_t)(n0 + (rg + j * p.rw) * kTileRows);
+        const int32_t row0 = (int32_t)(n0 + (rg + j * rw) * kTileRows);
         const uint32_t bar = bar0 + 8 * slot;
         ptx::mbar_arrive_expect_tx(bar, DQ ? kCodesSlot : kCodesSlot + kScaleSlot);
         ptx::tma_load_2d(codes0 + slot * C::kCodesTile + sl * kCodesSlot, &tm_codes,
@@ -235,25 +236,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             ptx::tma_load_2d(scales0 + slot * C::kScaleTile + sl * kScaleSlot, &tm_scales,
                              (int32_t)((slice0 + sl) * 4u), row0, bar);
     };
-    if (nsl) {
-        if (lane < (uint32_t)kRing) {
-            ptx::mbar_init(bar0 + 8 * lane, nsl);
-            ptx::fence_mbar_init();
-            ptx::fence_proxy_async();
-        }
-        __syncwarp();
-        if (lane < (uint32_t)(kRing * SL)) {
-            const uint32_t j = lane / SL, sl = lane % SL;
-            if (j < my_tiles && sl < nsl) request(j, sl);
-        }
-    }
-    uint32_t req_j = my_tiles < (uint32_t)kRing ? my_tiles : (uint32_t)kRing;  // tiles requested so far
-
     // ---- the lookup table: each byte value's entry, one copy per lane ----
     {
         // thread (byte, half) writes sixteen lanes' copies
         const uint32_t byte = tid >> 1, half = tid & 1u;
-        const uint32_t entry = level_f16(byte & 15u) | (level_f16(byte >> 4) << 16);
+        const uint32_t entry = __ldg(g_level_f16 + (byte & 15u)) | (__ldg(g_level_f16 + (byte >> 4)) << 16);
         const uint4 v = make_uint4(entry, entry, entry, entry);
         #pragma unroll
         for (int i = 0; i < 4; ++i)  // rotated by the byte so that a warp's stores spread over the banks
@@ -262,19 +249,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     if (DQ && tid < 256) dq_s[tid] = __fdiv_rn((float)tid, 255.0f);
 
     // ---- pass plan (the same for every warp): pass_tiles tiles per warp, then a reduction ----
-    const uint32_t max_tiles = (ntiles + p.rw - 1) / p.rw;  // tiles of the busiest warp
-    const uint32_t npasses = (max_tiles + p.pass_tiles - 1) / p.pass_tiles;
+    const uint32_t max_tiles = (ntiles + rw - 1) >> p.rw_shift;  // tiles of the busiest warp
 
     // LoRA-B rows of one pass of tiles, staged by everyone with 16-byte asynchronous copies
-    const uint32_t row_pieces = p.rank * 2u / 16u;  // 16-byte pieces per row (rank % 8 == 0 here)
-    auto stage_lora_b = [&](uint32_t pass) {
+    auto stage_lora_b = [&](uint32_t tile0) {  // tile0: warp-local number of the pass's first tile
         if (p.rank) {
-            const uint32_t r0 = n0 + pass * p.pass_tiles * p.rw * kTileRows;
+            const uint32_t r0 = n0 + ((tile0 * kTileRows) << p.rw_shift);
             if (r0 < n1) {
-                const uint32_t rows = min(n1 - r0, p.pass_tiles * p.rw * kTileRows);
+                const uint32_t rows = min(n1 - r0, (p.pass_tiles * kTileRows) << p.rw_shift);
                 const uint8_t *src = reinterpret_cast<const uint8_t *>(p.lora_b + (size_t)r0 * p.rank);
-                for (uint32_t q = tid; q < rows * row_pieces; q += kThreads) {
-                    const uint32_t row = q / row_pieces, piece = q - row * row_pieces;
+                for (uint32_t q = tid; q < rows << p.piece_shift; q += kThreads) {
+                    const uint32_t row = q >> p.piece_shift, piece = q - (row << p.piece_shift);
                     ptx::cp_async_16(kWin0 + 128u + row * 256u + piece * 16u, src + (size_t)q * 16u);
                 }
             }
@@ -282,6 +267,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         ptx::cp_async_commit();
     };
     stage_lora_b(0);
+
+    if (nsl) {
+        if (lane < (uint32_t)kRing) {
+            ptx::mbar_init(bar0 + 8 * lane, nsl);
+            ptx::fence_mbar_init();
+        }
+        __syncwarp();
+        if (lane < (uint32_t)(kRing * SL)) {
+            const uint32_t j = lane / SL, sl = lane % SL;
+            if (j < my_tiles && sl < nsl) request(j, sl);
+        }
+    }
+    uint32_t req_j = my_tiles < (uint32_t)kRing ? my_tiles : (uint32_t)kRing;  // tiles requested so far
 
     // ---- a producer CTA's unit of T: row j of the adapter factor A against the warps' K-slice
     // number h (unit = j * SL + h).  The lane loads its sixteen consecutive k of each 64-block,
@@ -455,7 +453,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     for (int sl = 0; sl < SL; ++sl) dq_lo[sl] = dq_hi[sl] = 0;
     auto fetch_dq = [&](uint32_t j) {
         if (DQ && j < my_tiles) {
-            const uint32_t row = n0 + (rg + j * p.rw) * kTileRows + 2 * g;
+            const uint32_t row = n0 + (rg + j * rw) * kTileRows + 2 * g;
             const uint32_t r_lo = min(row, p.N - 1), r_hi = min(row + 1, p.N - 1);
             #pragma unroll
             for (int sl = 0; sl < SL; ++sl) {
@@ -471,10 +469,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     uint32_t use_j = 0;  // tiles consumed so far
 
     #pragma unroll 1
-    for (uint32_t pass = 0; pass < npasses; ++pass) {
+    for (uint32_t tile0 = 0; tile0 < max_tiles; tile0 += p.pass_tiles) {  // a pass: tiles tile0 ... of every warp
         const uint32_t left = my_tiles - use_j;
         const uint32_t mine = left < p.pass_tiles ? left : p.pass_tiles;  // tiles of this warp in this pass
-        const bool t_pass = pass == 0 && p.rank != 0 && warp == 0;  // this warp fetches T in this pass
+        const bool t_pass = tile0 == 0 && p.rank != 0 && warp == 0;  // this warp fetches T in this pass
         if (t_pass && mine < 2) peek_t();
         if (t_pass && mine == 0) fetch_t();
 
@@ -569,14 +567,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         // ---- a warp per (tile, eight activation rows): sum the K-warps' partials in a fixed
         // order, add the adapter term (one bf16 MMA pair per sixteen ranks: B rows x T, T split
         // into bf16 high and low parts so that its f32 value survives), bias, convert, store ----
-        const uint32_t pass_tile0 = pass * p.pass_tiles * p.rw;
-        const uint32_t tiles_in_pass = min(ntiles - pass_tile0, p.pass_tiles * p.rw);
+        const uint32_t pass_tile0 = tile0 << p.rw_shift;
+        const uint32_t tiles_in_pass = min(ntiles - pass_tile0, p.pass_tiles << p.rw_shift);
         const uint32_t pass_row0 = n0 + pass_tile0 * kTileRows;
         const uint32_t pass_rows = min(n1 - pass_row0, tiles_in_pass * (uint32_t)kTileRows);
         #pragma unroll 1
         for (uint32_t job = warp; job < tiles_in_pass * NT; job += kWarps) {
             const uint32_t ti = job / NT, u = job - ti * NT;
-            const uint32_t trg = ti % p.rw, q = ti / p.rw;  // the warps that hold this tile, and where
+            const uint32_t trg = ti & (rw - 1), q = ti >> p.rw_shift;  // the warps that hold this tile, and where
             // four K-warps at a time (a fixed order of additions: results do not depend on timing)
             const float *src = park_s + (trg * p.kwarps) * kParkWarp + (q * NT + u) * 128u + lane * 4u;
             auto ld4 = [&](uint32_t w) -> float4 {
@@ -632,9 +630,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                 else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(o);
             }
         }
-        if (pass + 1 < npasses) {
+        if (tile0 + p.pass_tiles < max_tiles) {
             __syncthreads();  // the pass's LoRA-B rows and parked sums have been read
-            stage_lora_b(pass + 1);
+            stage_lora_b(tile0 + p.pass_tiles);
         }
     }
     ptx::cp_async_wait<0>();
@@ -732,19 +730,29 @@ bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran
     const uint32_t nt = M > 8 ? 2u : 1u;
     p.kw = K / kSliceK;
     p.kwarps = (p.kw + C::kSlices - 1) / C::kSlices;
-    p.rw = C::kWarps / p.kwarps;
+    p.rw_shift = 0;
+    while ((p.kwarps << (p.rw_shift + 1)) <= (uint32_t)C::kWarps) ++p.rw_shift;
+    const uint32_t rw = 1u << p.rw_shift;
+    for (uint32_t w = 0; w < (uint32_t)C::kWarps; ++w) {
+        const bool active = w < p.kwarps * rw;
+        p.warp_rg[w] = active ? (uint8_t)(w / p.kwarps) : 0xffu;
+        p.warp_kpos[w] = active ? (uint8_t)(w % p.kwarps) : 0u;
+    }
     const uint64_t units = N / gran;
     const uint64_t tiles = ((uint64_t)N + kTileRows - 1) / kTileRows;
     uint64_t ctas = tiles < (uint64_t)kNumSMs ? tiles : (uint64_t)kNumSMs;
     if (ctas > units) ctas = units;
     pl.grid = (uint32_t)ctas;
+    p.rows_base = (uint32_t)(units / ctas) * gran;
+    p.rows_extra = (uint32_t)(units % ctas);
     // tiles per warp between two reductions: what the parking area and (with an adapter) the
     // table's gaps hold
     uint32_t pt = kParkSlots / nt;
     if (rank) {
-        const uint32_t by_rows = kGapRows / (p.rw * kTileRows);
+        const uint32_t by_rows = kGapRows / (rw * kTileRows);
         if (by_rows == 0) return false;
         if (pt > by_rows) pt = by_rows;
+        p.piece_shift = rank == 8 ? 0u : rank == 16 ? 1u : rank == 32 ? 2u : 3u;
     }
     p.pass_tiles = pt;
     const uint32_t t_units = rank * C::kSlices;
@@ -760,7 +768,8 @@ bool plan(const nf4_linear_args &a, Plan &pl) {
     if (a.d_out >= (1ull << 31)) return false;
     const bool dq = a.scale_codes != nullptr;
     const uint32_t rank = a.lora_a ? a.lora_rank : 0;
-    if (rank > kMaxRank || rank % 8 != 0) return false;  // LoRA-B rows move in 16-byte pieces
+    // LoRA-B rows move in a power-of-two number of 16-byte pieces
+    if (rank != 0 && rank != 8 && rank != 16 && rank != 32 && rank != 64) return false;
     const void *scales = dq ? (const void *)a.scale_codes : (const void *)a.absmax;
     if (!aligned16(a.x) || !aligned16(a.packed) || !aligned16(scales)) return false;
     if (rank && (!aligned16(a.lora_a) || !aligned16(a.lora_b))) return false;
