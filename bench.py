@@ -10,13 +10,16 @@ One step = the three M passes.  Inputs are seeded synthetic data of those shapes
 
 `value` is the effective HBM bandwidth: algorithmic bytes of the three passes (packed
 nibbles + absmax + A + B + x + y) divided by device time, with everything resident in HBM;
-eight distinct weight copies (203 MB, larger than the 126 MB L2) are rotated so every pass
-streams its weight from HBM.  `e2e` is the same metric through the host-pointer C ABI
+eight distinct weight copies (207 MB, larger than the 126 MB L2) are rotated per PASS, so every
+pass streams its weight from HBM (a copy comes round again after seven other copies, 181 MB).  `e2e` is the same metric through the host-pointer C ABI
 (pinned host x in, host y out, copies inside the timed region).
 
 With N > 1 (torchrun) every rank owns one [11008, 4096] column shard of an N-times wider
 layer and the ranks all-gather the step's outputs over NCCL, one collective per step on its
-own stream beside the next step's passes (weak scaling).
+own stream beside the next step's passes (weak scaling).  The line then also carries the two
+configurations that are sharded by definition, driven through ShardedNf4Linear and checked
+against the unsharded forward on every rank: `prefill_sharded` (W [14336, 4096] split by output
+columns, all-gather of y) and `qwen2_7b_block_sharded` (the seven projections of the block).
 
 `--impl reference` times the reference's CPU algorithm for the same step on the host cores:
 dequantize the packed weight to f32 (single-threaded scalar loop, as the reference's
@@ -306,10 +309,11 @@ def run_own(args) -> None:
     def step(i: int) -> None:
         cur = torch.cuda.current_stream()
         stream = ctypes.c_void_p(cur.cuda_stream)
-        c, par = i % N_COPIES, i & 1
+        par = i & 1
         if world > 1 and gathered[par] is not None:
             cur.wait_event(gathered[par])  # the buffer is written again only after its gather
-        for m in MS:
+        for j, m in enumerate(MS):
+            c = (len(MS) * i + j) % N_COPIES  # a different weight copy for every pass
             _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, par)]), stream))
         if world > 1:
             # every rank's slab of the step's outputs, gathered beside the next step's passes
@@ -367,46 +371,53 @@ def run_own(args) -> None:
             launch_mode = "eager (capture failed on another rank)"
     log(f"launch mode: {launch_mode}")
 
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # K steps per measurement; the measurement is repeated and the median taken (the minimum is
+    # reported beside it), each repetition bracketed by a barrier and CUDA events on the stream
+    reps = 11
+    rep_ms = []
     if graph is not None:
         with torch.cuda.stream(side):
             graph.replay()  # one untimed replay: graph upload
-        barrier()
-        with torch.cuda.stream(side):
-            e0.record()
-            graph.replay()
-            e1.record()
     else:
         launches0 = _lib.launch_count()
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         with torch.cuda.stream(side):
             e0.record()
-            for i in range(args.steps):
-                step(i)
-            drain()
+            if graph is not None:
+                graph.replay()
+            else:
+                for i in range(args.steps):
+                    step(i)
+                drain()
             e1.record()
-        gpu_launches = _lib.launch_count() - launches0
-    barrier()
+        barrier()
+        rep_ms.append(e0.elapsed_time(e1))
+    if graph is None:
+        gpu_launches = (_lib.launch_count() - launches0) // reps
     log("timed region done")
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    ms = torch.tensor(rep_ms, device=dev)
     if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    total_ms = float(ms.item())
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)  # per repetition: the slowest rank
+    rep_ms = sorted(float(v) for v in ms.tolist())
+    total_ms = rep_ms[len(rep_ms) // 2]
+    min_ms = rep_ms[0]
     value = STEP_BYTES * args.steps * world / (total_ms * 1e-3) / 1e9
 
     # ---- roofline of the dominant kernel (decode GEMV incl. its LoRA pre-pass) ----------
     per_launch_ms = total_ms / (args.steps * len(MS))
     achieved = (STEP_BYTES / len(MS)) / (per_launch_ms * 1e-3) / 1e9
     roofline = {
-        "kernel": "decode_kernel (+ lora_t_kernel pre-pass), mean over M in {1,4,16}",
+        "kernel": "decode_kernel (one launch per forward), mean over M in {1,4,16}",
         "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
         "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
         "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
         "algorithmic_bytes_per_launch": STEP_BYTES // len(MS),
-        # dram__bytes_read.sum + dram__bytes_write.sum of decode_kernel from the committed ncu
-        # capture (profiles/decode_cfg2.md), mean of the M = 1, 4, 16 launches: the weights are
-        # read once, y stays in L2
-        "traffic": 25813248,
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch of decode_kernel, from an ncu
+        # capture of this kernel on this workload (not measured in this run): the weights are read
+        # once, y stays in L2
+        "traffic": 25902336, "traffic_source": "ncu capture (M = 1), not this run",
     }
 
     # ---- end to end through the host-pointer C ABI ------------------------------------------
@@ -430,12 +441,28 @@ def run_own(args) -> None:
         x_host = {m: xs[m].cpu().pin_memory() for m in MS}
         y_host = {m: torch.zeros(m, N, dtype=torch.bfloat16).pin_memory() for m in MS}
 
+        y_all_host = torch.zeros(world, sum(MS), N, dtype=torch.bfloat16).pin_memory()
+
         def host_step(i):
-            h = handles[i % N_COPIES]
-            for m in MS:
-                _lib.check(lib.nf4_weight_linear_forward_host(
-                    h, vp(x_host[m].data_ptr()), m, _lib.DTYPE_BF16, None, None, None, 0, 0.0,
-                    vp(y_host[m].data_ptr())))
+            if world == 1:
+                # the reference-facing call: host x in, host y out, one synchronous call per forward
+                for j, m in enumerate(MS):
+                    h = handles[(len(MS) * i + j) % N_COPIES]
+                    _lib.check(lib.nf4_weight_linear_forward_host(
+                        h, vp(x_host[m].data_ptr()), m, _lib.DTYPE_BF16, None, None, None, 0, 0.0,
+                        vp(y_host[m].data_ptr())))
+                return
+            # a sharded layer end to end: host x in, the shard's forwards, the all-gather of y,
+            # the whole gathered y out to the host
+            cur = torch.cuda.current_stream()
+            stream = ctypes.c_void_p(cur.cuda_stream)
+            for j, m in enumerate(MS):
+                xs[m].copy_(x_host[m], non_blocking=True)
+                c = (len(MS) * i + j) % N_COPIES
+                _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, 0)]), stream))
+            dist.all_gather_into_tensor(y_gathered[0], y_all[0])
+            y_all_host.copy_(y_gathered[0], non_blocking=True)
+            cur.synchronize()
 
         for i in range(max(args.warmup, 3)):
             host_step(i)
@@ -450,16 +477,24 @@ def run_own(args) -> None:
         e2e = {
             "value": STEP_BYTES * args.steps * world / float(dt.item()) / 1e9, "unit": UNIT,
             "h2d_bytes_per_step": sum(m * K * 2 for m in MS),
-            "d2h_bytes_per_step": sum(m * N * 2 for m in MS),
-            "api": "nf4_weight_linear_forward_host (pinned host x in, host y out, synchronous)",
+            "d2h_bytes_per_step": sum(m * N * 2 for m in MS) * world,
+            "api": "nf4_weight_linear_forward_host (pinned host x in, host y out, synchronous)"
+                   if world == 1 else
+                   "per rank: pinned host x in, nf4_linear_forward_dev on the shard, NCCL all-gather of y, "
+                   "gathered y out to the host, synchronous",
         }
         for h in handles:
             lib.nf4_weight_free(h)
         log("end-to-end region done")
 
+    # ---- the configurations that are sharded by definition (every rank takes part) -------------
+    if world > 1 and not args.device_only:
+        log("sharded sections")
+        extras.update(sharded_sections(torch, dist, lib, _lib, dev, rank, world))
+
     # ---- other kernels of the path (not part of `value`) -----------------------------------
     if rank == 0 and not args.device_only:
-        extras = aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind)
+        extras.update(aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind))
         if world == 1:  # the other named configurations, measured on the one GPU
             log("side sections: block, sweep")
             extras["qwen2_7b_block"] = block_section(torch, lib, _lib, dev)
@@ -469,15 +504,22 @@ def run_own(args) -> None:
     if rank == 0 and world == 1 and not args.device_only:
         st = cpu_reference_setup()
         cpu_reference_step(st)
-        reps = 2
+        cpu_reps = 2
         t0 = time.perf_counter()
-        for _ in range(reps):
+        for _ in range(cpu_reps):
             cpu_reference_step(st)
-        cdt = (time.perf_counter() - t0) / reps
+        cdt = (time.perf_counter() - t0) / cpu_reps
+        log("CPU baselines of the side sections")
+        side = cpu_side_baselines()
+        for name in ("quantize", "dequantize", "prefill", "quantize_sweep"):
+            if name in extras:
+                extras[name]["cpu_baseline"] = side[name]
+        if "qwen2_7b_block" in extras:
+            extras["qwen2_7b_block"]["cpu_baseline_decode"] = side["qwen2_7b_block_decode"]
         cpu_baseline = {
             "value": STEP_BYTES / cdt / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
             "kind": "port",
-            "sample": f"{reps} full steps after 1 warm-up: scalar single-thread dequantize + torch "
+            "sample": f"{cpu_reps} full steps after 1 warm-up: scalar single-thread dequantize + torch "
                       f"f32 matmul on {torch.get_num_threads()} threads, {cdt:.2f} s per step",
         }
 
@@ -486,13 +528,17 @@ def run_own(args) -> None:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "timing": {"repetitions": reps, "statistic": "median of the repetitions (each: the K steps, "
+                       "CUDA events on the stream, max over ranks)", "ms_median": total_ms, "ms_min": min_ms,
+                       "ms_max": rep_ms[-1],
+                       "value_at_min": STEP_BYTES * args.steps * world / (min_ms * 1e-3) / 1e9},
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 tensor-core MMA on bf16 activations, f32 accumulate, bf16 out",
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "cache": f"{N_COPIES} distinct weight copies "
                                 f"({N_COPIES * algorithmic_bytes(1) / 1e6:.0f} MB > 126 MB L2) rotated "
-                                "per step",
+                                "per pass",
                        "launch": launch_mode,
                        "sharding": "none" if world == 1 else
                        f"{world} column shards of a [{world * N}, {K}] layer, one NCCL all-gather of y per step"},
@@ -526,6 +572,24 @@ def time_loop(torch, fn, iters: int, warm: int = 5) -> float:
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters
+
+
+def time_flushed(torch, fn, flush, iters: int, warm: int = 3):
+    """Median and minimum milliseconds of fn(i), each call timed by its own pair of CUDA events
+    with a write of `flush` (larger than the L2) before it, outside the events."""
+    for i in range(warm):
+        fn(i)
+    times = []
+    for i in range(iters):
+        flush.fill_(i & 1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2], times[0]
 
 
 def aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind):
@@ -584,13 +648,10 @@ def prefill_section(torch, lib, _lib, dev, pn: int = 14336, iters: int = 20):
     stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
-    def run(i):
-        flush.fill_(i & 1)  # write more than the 126 MB L2 between timed launches
+    def run(_i):
         _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), stream()))
 
-    ms_with_flush = time_loop(torch, run, iters, warm=3)
-    ms_flush = time_loop(torch, lambda i: flush.fill_(i & 1), iters, warm=3)
-    ms = ms_with_flush - ms_flush
+    ms, ms_min = time_flushed(torch, run, flush, iters)
     flops = 2.0 * pm * pn * pk + 2.0 * pm * pr * (pk + pn)
     tflops = flops / (ms * 1e-3) / 1e12
     return {"workload": f"QLoRA prefill GEMM: x bf16 [2048, 4096], W NF4 [{pn}, 4096] block 64, "
@@ -599,7 +660,8 @@ def prefill_section(torch, lib, _lib, dev, pn: int = 14336, iters: int = 20):
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": tf_peak, "unit": "TFLOP/s",
                          "frac": tflops / tf_peak, "peak_kind": f"of {peak_kind} (burst)",
                          "frac_of_nominal_2250": tflops / 2250.0},
-            "cache": "160 MB flush write between launches (its time subtracted)"}
+            "ms_min": ms_min,
+            "cache": "160 MB flush write before every launch, outside the timed events (median of the launches)"}
 
 
 def build_linear(torch, lib, _lib, dev, m: int, k: int, n: int, r: int, seed: int):
@@ -639,18 +701,16 @@ def block_section(torch, lib, _lib, dev, iters: int = 20):
     hbm_peak, tf_peak, peak_kind = measured_peaks()
     stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    ms_flush = time_loop(torch, lambda i: flush.fill_(i & 1), iters, warm=3)
     out = {}
     for label, m in (("decode_batch_8", 8), ("prefill_4096", 4096)):
         lins = [build_linear(torch, lib, _lib, dev, m, k, n, 16, 200 + i)
                 for i, (_nm, k, n) in enumerate(QWEN2_7B_BLOCK)]
 
-        def run(i):
-            flush.fill_(i & 1)
+        def run(_i):
             for a, _keep in lins:
                 _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), stream()))
 
-        ms = time_loop(torch, run, iters, warm=3) - ms_flush
+        ms, _ms_min = time_flushed(torch, run, flush, iters)
         elems = sum(k * n for _nm, k, n in QWEN2_7B_BLOCK)
         if m == 8:
             by = sum(k * n // 2 + k * n // 64 * 4 + 16 * (k + n) * 2 + m * (k + n) * 2
@@ -665,7 +725,7 @@ def block_section(torch, lib, _lib, dev, iters: int = 20):
                           "peak_kind": f"of {peak_kind} (burst)"}
         del lins
     out["workload"] = ("Qwen2-7B-shaped block, 7 NF4 linears (233,046,016 weights), block 64, rank 16; "
-                       "160 MB flush write before each pass (its time subtracted)")
+                       "160 MB flush write before each pass over the block, outside the timed events")
     return out
 
 
@@ -698,6 +758,201 @@ def sweep_section(torch, lib, _lib, dev):
     return {"workload": "32 f32 matrices, Student-t(4) * 0.02, one quantize call per matrix",
             "elements": elems, "ms": ms, "GB/s": gbs, "algorithmic_bytes": int(by),
             "frac": gbs / hbm_peak, "peak_kind": f"of {peak_kind}"}
+
+
+def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: int = 10):
+    """The two configurations that are sharded by definition, on `world` GPUs, through
+    ShardedNf4Linear: every rank owns a contiguous range of output columns of each weight (its rows
+    of the packed weight, of the scales and of LoRA B), runs the single-GPU kernels on it, and the
+    ranks all-gather y.  Before timing, every rank compares the gathered y with its own unsharded
+    forward of the full weight (`gather_check`).  Times are CUDA events on the stream, max over ranks,
+    median of `iters`, with a write larger than the L2 before each timed call."""
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+    from unifur_b200.sharded import ShardedNf4Linear
+
+    _hbm, tf_peak, peak_kind = measured_peaks()
+    hbm_peak = _hbm
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def reduce_max(v: float) -> float:
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def check(y_sharded, y_full) -> str:
+        if torch.equal(y_sharded, y_full):
+            verdict = 0.0
+        else:
+            d = (y_sharded.float() - y_full.float()).abs()
+            tol = y_full.float().abs() * 2.0 ** -7 + 4e-6 * float(y_full.float().abs().max())
+            verdict = 1.0 if bool((d <= tol).all()) else 2.0
+        worst = reduce_max(verdict)
+        return {0.0: "ok", 1.0: "ok_within_one_bf16_ulp"}.get(worst, "MISMATCH")
+
+    def build(seed: int, m: int, k: int, n: int, r: int):
+        """Same seed on every rank: the same full weight everywhere; each rank keeps its rows."""
+        g = torch.Generator(device=dev).manual_seed(seed)
+        w = torch.randn(n * k, device=dev, generator=g) * 0.02
+        full = PackedNf4Tensor.quantize(w)
+        del w
+        la = (torch.randn(r, k, device=dev, generator=g) * 0.01).bfloat16()
+        lb = (torch.randn(n, r, device=dev, generator=g) * 0.01).bfloat16()
+        x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+        lin = ShardedNf4Linear.from_full(full, k, n, world, rank, lora_a=la, lora_b=lb, lora_scale=SCALE,
+                                         granule=64)
+        return full, la, lb, x, lin
+
+    def timed(fn):
+        times = []
+        for i in range(iters + 2):
+            flush.fill_(i & 1)
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                times.append(e0.elapsed_time(e1))
+        t = torch.tensor(times, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.median().item())
+
+    out = {}
+    # ---- configuration 3: x [2048, 4096], W [14336, 4096], rank 64 ----
+    pm, pk, pn, pr = 2048, 4096, 14336, 64
+    full, la, lb, x, lin = build(5, pm, pk, pn, pr)
+    plan = lin.plan(x)
+    y_sharded = plan.run().clone()
+    y_full = linear_forward(x, full, pk, pn, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=SCALE)
+    torch.cuda.synchronize()
+    verdict = check(y_sharded, y_full)
+    del y_full, y_sharded
+    ms_local = timed(plan.run_local)
+    ms_all = timed(plan.run)
+    flops = 2.0 * pm * pn * pk + 2.0 * pm * pr * (pk + pn)
+    out["prefill_sharded"] = {
+        "workload": f"QLoRA prefill GEMM x bf16 [2048, 4096], W NF4 [14336, 4096] in {world} column shards "
+                    f"of {pn // world}, rank 64; all-gather of y (58.7 MB in all) into [2048, 14336]",
+        "gather_check": verdict, "ms_local_forward": ms_local, "ms_with_gather": ms_all,
+        "TFLOP/s": flops / (ms_all * 1e-3) / 1e12,
+        "TFLOP/s_per_gpu_local": flops / world / (ms_local * 1e-3) / 1e12,
+        "frac_per_gpu_local": flops / world / (ms_local * 1e-3) / 1e12 / tf_peak,
+        "peak_kind": f"of {peak_kind} (burst)",
+        "gather_share": max(0.0, (ms_all - ms_local) / ms_all), "n_gpus": world,
+        "limiter": "the all-gather and the permuting copy of y follow the GEMM on the same stream",
+    }
+    del full, la, lb, x, lin, plan
+    torch.cuda.empty_cache()
+
+    # ---- configuration 5: the seven projections of the Qwen2-7B-shaped block ----
+    blk = {}
+    for label, m in (("decode_batch_8", 8), ("prefill_4096", 4096)):
+        plans, checks = [], {}
+        for i, (nm, k, n) in enumerate(QWEN2_7B_BLOCK):
+            full, la, lb, x, lin = build(200 + i, m, k, n, 16)
+            plan = lin.plan(x)
+            y_sharded = plan.run().clone()
+            y_full = linear_forward(x, full, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=SCALE)
+            torch.cuda.synchronize()
+            checks[nm] = check(y_sharded, y_full)
+            del y_full, y_sharded, full
+            plans.append(plan)
+        ms_local = timed(lambda: [pl.run_local() for pl in plans])
+        ms_all = timed(lambda: [pl.run() for pl in plans])
+        worst = "MISMATCH" if "MISMATCH" in checks.values() else (
+            "ok" if all(v == "ok" for v in checks.values()) else "ok_within_one_bf16_ulp")
+        if m == 8:
+            by = sum(k * n // 2 + k * n // 64 * 4 + 16 * (k + n) * 2 + m * (k + n) * 2
+                     for _nm, k, n in QWEN2_7B_BLOCK)
+            blk[label] = {"us_local": ms_local * 1e3, "us_with_gather": ms_all * 1e3,
+                          "GB/s": by / (ms_all * 1e-3) / 1e9,
+                          "GB/s_per_gpu_local": by / world / (ms_local * 1e-3) / 1e9,
+                          "frac_per_gpu_local": by / world / (ms_local * 1e-3) / 1e9 / hbm_peak,
+                          "gather_check": worst, "per_projection": checks}
+        else:
+            fl = sum(2.0 * m * k * n + 2.0 * m * 16 * (k + n) for _nm, k, n in QWEN2_7B_BLOCK)
+            blk[label] = {"ms_local": ms_local, "ms_with_gather": ms_all,
+                          "TFLOP/s": fl / (ms_all * 1e-3) / 1e12,
+                          "TFLOP/s_per_gpu_local": fl / world / (ms_local * 1e-3) / 1e12,
+                          "frac_per_gpu_local": fl / world / (ms_local * 1e-3) / 1e12 / tf_peak,
+                          "gather_check": worst, "per_projection": checks}
+        del plans
+        torch.cuda.empty_cache()
+    blk["workload"] = (f"Qwen2-7B-shaped block, 7 NF4 linears in {world} column shards each "
+                       f"(per-GPU widths {3584 // world}/{512 // world}/{18944 // world}), rank 16, "
+                       "one all-gather per projection")
+    blk["n_gpus"] = world
+    out["qwen2_7b_block_sharded"] = blk
+    return out
+
+
+def cpu_side_baselines():
+    """The reference's CPU algorithm beside the side sections, on bounded samples: the oracle's C
+    restatement (scalar, one thread, as the reference's loops are) for quantize / dequantize, and
+    dequantize + f32 matmul on all cores (torch standing in for burn-ndarray) for the forwards."""
+    import torch
+    from oracle import nf4_oracle as o
+
+    o.build()
+    cores = torch.get_num_threads()
+    out = {}
+    rng = np.random.default_rng(1)
+    n = 4096 * 4096
+    w = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    t0 = time.perf_counter()
+    packed, absmax = o.quantize_packed(w)
+    tq = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    o.dequantize_packed(packed, n, absmax)
+    td = time.perf_counter() - t0
+    b = n * 4.5625
+    out["quantize"] = {"value": b / tq / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                       "sample": "the whole 4096x4096 matrix, once"}
+    out["dequantize"] = {"value": b / td / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                         "sample": "the whole 4096x4096 matrix, once"}
+    # sweep: the smallest and the square shape, once each (2 of the 32 matrices)
+    t_sweep, elems = 0.0, 0
+    for r, c in ((4096, 4096), (1024, 4096)):
+        z = rng.standard_normal(r * c)
+        chi = np.sqrt((rng.standard_normal((4, r * c)) ** 2).sum(0) / 4.0)
+        v = (0.02 * z / chi).astype(np.float32)
+        del z, chi
+        t0 = time.perf_counter()
+        o.quantize_packed(v)
+        t_sweep += time.perf_counter() - t0
+        elems += r * c
+    out["quantize_sweep"] = {"value": elems * 4.5625 / t_sweep / 1e9, "unit": "GB/s", "cores": 1,
+                             "kind": "port", "sample": "one 4096x4096 and one 1024x4096 Student-t matrix (2 of the 32)"}
+    # prefill of configuration 3 on the first 2048 weight rows (a seventh of the 14336)
+    pm, pk, pn_s, pr = 2048, 4096, 2048, 64
+    wq = (rng.standard_normal(pn_s * pk) * 0.02).astype(np.float32)
+    pk_codes, pk_absmax = o.quantize_packed(wq)
+    x = torch.from_numpy(o.round_bf16(rng.standard_normal((pm, pk))))
+    a = torch.from_numpy(o.round_bf16(rng.standard_normal((pk, pr)) * 0.01))
+    bb = torch.from_numpy(o.round_bf16(rng.standard_normal((pr, pn_s)) * 0.01))
+    t0 = time.perf_counter()
+    wd = torch.from_numpy(o.dequantize_packed(pk_codes, pn_s * pk, pk_absmax)).view(pn_s, pk)
+    y = x @ wd.t() + ((x @ a) @ bb) * np.float32(SCALE)
+    tp = time.perf_counter() - t0
+    fl = 2.0 * pm * pn_s * pk + 2.0 * pm * pr * (pk + pn_s)
+    out["prefill"] = {"value": fl / tp / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                      "sample": f"the first {pn_s} of 14336 weight rows: scalar dequantize (1 thread) + "
+                                f"f32 matmul on {cores} threads", "sink": float(y[0, 0])}
+    # the block's decode pass: the down projection (a seventh of the block's linears, 29 % of its weights)
+    k, n_, m = 18944, 3584, 8
+    wq = (rng.standard_normal(n_ * k) * 0.02).astype(np.float32)
+    c2, a2 = o.quantize_packed(wq)
+    x = torch.from_numpy(o.round_bf16(rng.standard_normal((m, k))))
+    t0 = time.perf_counter()
+    wd = torch.from_numpy(o.dequantize_packed(c2, n_ * k, a2)).view(n_, k)
+    y = x @ wd.t()
+    tb = time.perf_counter() - t0
+    by = k * n_ // 2 + k * n_ // 64 * 4 + m * (k + n_) * 2
+    out["qwen2_7b_block_decode"] = {"value": by / tb / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": "the down projection only (67.9 M of the block's 233 M weights), "
+                                              "no adapter", "sink": float(y[0, 0])}
+    return out
 
 
 def main() -> None:

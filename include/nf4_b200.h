@@ -57,7 +57,7 @@ extern "C" {
 
 /* ---------------------------------------------------------------- misc -- */
 
-/* Library version (major*10000 + minor*100 + patch). */
+/* Library version (major*100 + minor). */
 NF4_API int32_t nf4_version(void);
 
 /* Message of the last failing call on this host thread ("" if none). */
@@ -77,6 +77,13 @@ NF4_API uint64_t nf4_kernel_launch_count(void);
  * The reference has no counterpart: its forward cannot fail (src/qwennet.rs:238-241); the
  * Rust shim maps a non-zero status to anyhow::Error (src/lib.rs:16-32). */
 NF4_API int32_t nf4_device_status(int32_t *decode, int32_t *decode_split_k, int32_t *prefill);
+
+/* Diagnostic: launches a one-thread kernel that waits on a barrier nobody signals, with the same
+ * bounded wait the decode kernel uses and `limit_ns` (at most one second) as its limit.  The kernel
+ * returns when the limit has passed and records the failure as the decode kernel would; the call
+ * then reports it like any other: NF4_ERR_TIMEOUT, flags cleared.  `waited_ns` (may be NULL) gets
+ * the time the wait took.  Nothing hangs, traps or faults; the device stays usable. */
+NF4_API int32_t nf4_selftest_bounded_wait(uint64_t limit_ns, uint64_t *waited_ns);
 
 /* Diagnostic: runs the kernels' threshold bisection and the reference's literal
  * sixteen-way scan (src/quantize.rs:208-219) on `count` consecutive f32 bit patterns
@@ -215,6 +222,62 @@ NF4_API uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64
                                     uint32_t lora_rank);
 
 NF4_API int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream);
+
+/* The adapter alone: y = ((x A) B) * lora_scale, the three operations in the reference's order,
+ * f32 accumulation.  Replaces LoraAdapter::forward, src/quantize.rs:620-624.  Factor orientation
+ * follows `layout` as in nf4_linear_args (NF4_LAYOUT_IN_OUT is the reference's A [d_in, r],
+ * B [r, d_out]); x, y and the factors have `io_dtype`.  `workspace` holds
+ * nf4_lora_workspace_bytes(rows, lora_rank) bytes (the intermediate x A in f32). */
+NF4_API uint64_t nf4_lora_workspace_bytes(uint64_t rows, uint32_t lora_rank);
+NF4_API int32_t nf4_lora_forward_dev(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out,
+                                     const void *lora_a, const void *lora_b, uint32_t lora_rank,
+                                     float lora_scale, int32_t layout, int32_t io_dtype, void *y, uint64_t ldy,
+                                     void *workspace, uint64_t workspace_bytes, void *stream);
+
+/* The dense update dW = (A B) * lora_scale as f32, stored in the weight's orientation
+ * ([d_in, d_out] for NF4_LAYOUT_IN_OUT as the reference returns it, [d_out, d_in] for
+ * NF4_LAYOUT_OUT_IN).  Replaces LoraAdapter::delta_weight, src/quantize.rs:629-634. */
+NF4_API int32_t nf4_lora_delta_weight_dev(const void *lora_a, const void *lora_b, uint64_t d_in, uint64_t d_out,
+                                          uint32_t lora_rank, float lora_scale, int32_t layout,
+                                          int32_t io_dtype, float *out, void *stream);
+
+/* The adapter folded into the quantized base weight: out = dequant(W) + (A B) * lora_scale, f32, in
+ * the weight's orientation.  Replaces QLoraLinear::merged, src/quantize.rs:717-726 (which adds the
+ * update to the dequantized base weight it holds).  Scales as in nf4_dequantize_dev. */
+NF4_API int32_t nf4_qlora_merge_dev(const uint8_t *packed, const float *absmax, const uint8_t *scale_codes,
+                                    const float *scale_of_scales, uint64_t d_in, uint64_t d_out, int32_t layout,
+                                    const void *lora_a, const void *lora_b, uint32_t lora_rank,
+                                    float lora_scale, int32_t io_dtype, float *out, void *stream);
+
+/* Backward of the QLoRA linear with the base weight frozen, as the reference's autodiff sees the
+ * detached NF4 weight (src/qwennet.rs:226-241; used by the training engine, src/qwentrain.rs:421-470).
+ * `fwd` is the argument block of the forward being differentiated (x, the packed weight, the
+ * adapter; y and bias are not read); `grad_y` is [rows, d_out].  Outputs, all of io_dtype:
+ *   grad_x [rows, d_in]  = grad_y W^T + s (grad_y B^T) A^T   (one more NF4 linear over the same packed
+ *                          bytes read in the other orientation),
+ *   grad_a, grad_b with the shapes of lora_a, lora_b: s x^T (grad_y B^T) and s (x A)^T grad_y.
+ * fwd->workspace must hold nf4_qlora_backward_workspace_bytes() bytes. */
+NF4_API uint64_t nf4_qlora_backward_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
+                                                    uint32_t lora_rank);
+NF4_API int32_t nf4_qlora_backward_dev(const nf4_linear_args *fwd, const void *grad_y, void *grad_x,
+                                       void *grad_a, void *grad_b, void *stream);
+
+/* One rank's part of a forward whose weight is sharded by output columns over `world` GPUs, and
+ * the exchange that completes it.  `shard` describes this rank's slice exactly as for
+ * nf4_linear_forward_dev: the rows of the packed weight, of the scales, of the bias and of LoRA B
+ * that belong to its columns (every rank the same number of columns, d_out of the shard), x and
+ * LoRA A whole, y = the rank's dense slab [rows, d_out].  After the local forward the slabs are
+ * all-gathered into `gather_buffer` (nf4_sharded_gather_bytes) with ncclAllGather on `nccl_comm`
+ * (an ncclComm_t; NCCL is looked up at run time in the host process, the library does not link it)
+ * and placed side by side in y_full [rows, ldy_full] (0 = world * d_out), rank r's columns at
+ * r * d_out.  Everything is enqueued on `stream`; every rank of the communicator must make the call.
+ * The reference has no multi-GPU path: this is the partition its forward admits without touching
+ * the arithmetic (src/qwennet.rs:238-241 computes each output column from one weight column). */
+NF4_API uint64_t nf4_sharded_gather_bytes(uint64_t rows, uint64_t d_out_shard, int32_t world, int32_t io_dtype,
+                                          int32_t y_f32);
+NF4_API int32_t nf4_sharded_linear_forward_dev(const nf4_linear_args *shard, void *nccl_comm, int32_t rank,
+                                               int32_t world, void *gather_buffer, uint64_t gather_bytes,
+                                               void *y_full, uint64_t ldy_full, void *stream);
 
 /* Decode-sized forward for callers that cannot allocate or own device memory.
  * No counterpart in the reference (its forward allocates a fresh f32 weight on every call).

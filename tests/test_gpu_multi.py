@@ -1,0 +1,125 @@
+"""The column-sharded forward on two GPUs: through ShardedNf4Linear (torch.distributed, NCCL) and
+through nf4_sharded_linear_forward_dev with a raw two-rank NCCL communicator.  Every rank compares
+the gathered output with its own unsharded forward of the full weight.  Skipped on a machine with
+fewer than two GPUs (the host logic is covered on CPU by tests/test_sharded_gloo.py)."""
+import ctypes
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class _NcclId(ctypes.Structure):
+    _fields_ = [("internal", ctypes.c_byte * 128)]
+
+
+def _worker(rank, world, port, results):
+    import torch.distributed as dist
+
+    from unifur_b200 import _lib
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+    from unifur_b200.sharded import ShardedNf4Linear
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    ok = True
+    try:
+        L = _lib.load()
+        for case, (m, k, n, r, gran) in enumerate(((8, 3584, 512, 16, 64), (300, 1024, 1536, 64, 64),
+                                                   (4, 512, 320, 8, 64))):
+            g = torch.Generator(device=dev).manual_seed(40 + case)  # the same weight on every rank
+            w = torch.randn(n * k, device=dev, generator=g) * 0.02
+            full = PackedNf4Tensor.quantize(w)
+            la = (torch.randn(r, k, device=dev, generator=g) * 0.01).bfloat16()
+            lb = (torch.randn(n, r, device=dev, generator=g) * 0.01).bfloat16()
+            x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+            y_full = linear_forward(x, full, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=2.0)
+            lin = ShardedNf4Linear.from_full(full, k, n, world, rank, lora_a=la, lora_b=lb, lora_scale=2.0,
+                                             granule=gran)
+            y1 = lin.forward(x)                      # allocating form
+            plan = lin.plan(x)
+            y2 = plan.run().clone()                  # preallocated form
+            torch.cuda.synchronize()
+            tol = y_full.float().abs() * 2.0 ** -7 + 4e-6 * float(y_full.float().abs().max())
+            ok &= bool(((y1.float() - y_full.float()).abs() <= tol).all())
+            ok &= torch.equal(y1, y2)
+        # the same exchange below the C ABI: raw NCCL communicator, equal shards
+        nccl = ctypes.CDLL(os.path.join(os.path.dirname(torch.__file__), "..", "nvidia", "nccl", "lib",
+                                        "libnccl.so.2"), mode=ctypes.RTLD_GLOBAL)
+        uid = _NcclId()
+        buf = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            assert nccl.ncclGetUniqueId(ctypes.byref(uid)) == 0
+            buf.copy_(torch.frombuffer(bytearray(bytes(uid.internal)), dtype=torch.uint8))
+        dist.broadcast(buf, 0)
+        ctypes.memmove(ctypes.byref(uid), bytes(buf.cpu().numpy().tobytes()), 128)
+        comm = ctypes.c_void_p()
+        nccl.ncclCommInitRank.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, _NcclId, ctypes.c_int]
+        assert nccl.ncclCommInitRank(ctypes.byref(comm), world, uid, rank) == 0
+        m, k, n, r = 16, 4096, 1024, 16
+        nl = n // world
+        g = torch.Generator(device=dev).manual_seed(99)
+        w = torch.randn(n * k, device=dev, generator=g) * 0.02
+        full = PackedNf4Tensor.quantize(w)
+        la = (torch.randn(r, k, device=dev, generator=g) * 0.01).bfloat16()
+        lb = (torch.randn(n, r, device=dev, generator=g) * 0.01).bfloat16()
+        x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+        y_ref = linear_forward(x, full, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=2.0)
+        codes = full.codes[rank * nl * (k // 2):(rank + 1) * nl * (k // 2)].contiguous()
+        absmax = full.absmax[rank * nl * (k // 64):(rank + 1) * nl * (k // 64)].contiguous()
+        lb_l = lb[rank * nl:(rank + 1) * nl].contiguous()
+        slab = torch.zeros(m, nl, dtype=torch.bfloat16, device=dev)
+        y_out = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+        gb = int(L.nf4_sharded_gather_bytes(m, nl, world, _lib.DTYPE_BF16, 0))
+        gbuf = torch.zeros(gb, dtype=torch.uint8, device=dev)
+        ws = torch.zeros(max(int(L.nf4_linear_workspace_bytes(m, k, nl, r)), 256), dtype=torch.uint8, device=dev)
+        a = _lib.LinearArgs()
+        a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+        a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16
+        a.rows, a.d_in, a.d_out = m, k, nl
+        a.x, a.packed, a.absmax = x.data_ptr(), codes.data_ptr(), absmax.data_ptr()
+        a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb_l.data_ptr(), r, 2.0
+        a.y, a.ldy = slab.data_ptr(), nl
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        vp = ctypes.c_void_p
+        _lib.check(L.nf4_sharded_linear_forward_dev(ctypes.byref(a), comm, rank, world, vp(gbuf.data_ptr()), gb,
+                                                    vp(y_out.data_ptr()), n, None))
+        torch.cuda.synchronize()
+        ok &= torch.equal(y_out, y_ref)   # the decode kernel's arithmetic per row does not depend on the shard
+        nccl.ncclCommDestroy(comm)
+    finally:
+        results[rank] = 1 if ok else 0
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_forward_on_two_gpus():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    results = ctx.Array("i", [0] * world)
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert list(results) == [1] * world

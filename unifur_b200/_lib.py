@@ -62,6 +62,7 @@ SIGNATURES = {
     "nf4_last_error": (C.c_char_p, []),
     "nf4_kernel_launch_count": (_u64, []),
     "nf4_device_status": (_i32, [C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32)]),
+    "nf4_selftest_bounded_wait": (_i32, [_u64, C.POINTER(_u64)]),
     "nf4_selfcheck_code_selection": (_i32, [_u64, _u64, C.POINTER(_u64)]),
     "nf4_selfcheck_quantize_fast_path": (_i32, [_u64, _u64, _f32, C.POINTER(_u64)]),
     "nf4_quantize_transposed_workspace_bytes": (_u64, [_u64, _u64]),
@@ -84,6 +85,15 @@ SIGNATURES = {
     "nf4_quantize_dequantize_host": (_i32, [_vp, _u64, _i32, _vp]),
     "nf4_linear_workspace_bytes": (_u64, [_u64, _u64, _u64, _u32]),
     "nf4_linear_forward_dev": (_i32, [C.POINTER(LinearArgs), _vp]),
+    "nf4_lora_workspace_bytes": (_u64, [_u64, _u32]),
+    "nf4_lora_forward_dev": (_i32, [_vp, _u64, _u64, _u64, _vp, _vp, _u32, _f32, _i32, _i32, _vp, _u64, _vp,
+                                    _u64, _vp]),
+    "nf4_lora_delta_weight_dev": (_i32, [_vp, _vp, _u64, _u64, _u32, _f32, _i32, _i32, _vp, _vp]),
+    "nf4_qlora_merge_dev": (_i32, [_vp, _vp, _vp, _vp, _u64, _u64, _i32, _vp, _vp, _u32, _f32, _i32, _vp, _vp]),
+    "nf4_qlora_backward_workspace_bytes": (_u64, [_u64, _u64, _u64, _u32]),
+    "nf4_qlora_backward_dev": (_i32, [C.POINTER(LinearArgs), _vp, _vp, _vp, _vp, _vp]),
+    "nf4_sharded_gather_bytes": (_u64, [_u64, _u64, _i32, _i32, _i32]),
+    "nf4_sharded_linear_forward_dev": (_i32, [C.POINTER(LinearArgs), _vp, _i32, _i32, _vp, _u64, _vp, _u64, _vp]),
     "nf4_linear_noalloc_scratch_bytes": (_u64, []),
     "nf4_linear_forward_noalloc_dev": (_i32, [C.POINTER(LinearArgs), _vp]),
     "nf4_weight_from_values_host": (_i32, [_vp, _u64, _u64, _i32, _i32, C.POINTER(_vp)]),

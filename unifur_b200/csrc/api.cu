@@ -37,12 +37,22 @@ int32_t check_cuda(cudaError_t e, const char *what) {
     return fail(code, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
 }
 
-bool pdl_enabled() {
-    static const bool on = [] {
-        const char *e = std::getenv("NF4_PDL");
-        return !(e && e[0] == '0');
-    }();
-    return on;
+int32_t ensure_dynamic_smem(const void *kernel, int bytes) {
+    struct Done {
+        const void *kernel;
+        int device;
+    };
+    static std::mutex mu;
+    static Done done[256];
+    static int n_done = 0;
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < n_done; ++i)
+        if (done[i].kernel == kernel && done[i].device == dev) return NF4_OK;
+    NF4_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (n_done < 256) done[n_done++] = Done{kernel, dev};
+    return NF4_OK;
 }
 
 void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -244,9 +254,20 @@ struct nf4_weight {
     int32_t lora_dtype = 0;
 };
 
+// A weight lives on the device that was current when it was created: its kernels must be
+// launched there.
+static int32_t check_weight_device(const nf4_weight *w, const char *who) {
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != w->device)
+        return fail(NF4_ERR_INVALID_ARG, "%s: the weight lives on device %d, the current device is %d", who,
+                    w->device, dev);
+    return NF4_OK;
+}
+
 extern "C" {
 
-int32_t nf4_version(void) { return 100; }
+int32_t nf4_version(void) { return 200; }
 
 const char *nf4_last_error(void) { return t_last_error.c_str(); }
 
@@ -289,6 +310,18 @@ int32_t nf4_device_status(int32_t *decode, int32_t *decode_split_k, int32_t *pre
     if (decode_split_k) *decode_split_k = v[1];
     if (prefill) *prefill = v[2];
     return report_flags(ptrs, v);
+}
+
+int32_t nf4_selftest_bounded_wait(uint64_t limit_ns, uint64_t *waited_ns) {
+    if (limit_ns == 0 || limit_ns > 1000000000ull)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_selftest_bounded_wait: limit must be 1 ns .. 1 s");
+    NF4_TRY(t_arena.reserve(256));
+    unsigned long long *d = static_cast<unsigned long long *>(t_arena.ptr);
+    NF4_TRY(decode_selftest_wait((uint32_t)limit_ns, d, 0));
+    unsigned long long h = 0;
+    NF4_CUDA_TRY(cudaMemcpy(&h, d, 8, cudaMemcpyDeviceToHost));
+    if (waited_ns) *waited_ns = h;
+    return nf4_device_status(nullptr, nullptr, nullptr);
 }
 
 uint64_t nf4_num_blocks(uint64_t len) { return (len + kBlock - 1) / kBlock; }
@@ -423,6 +456,129 @@ int32_t nf4_linear_forward_noalloc_dev(const nf4_linear_args *args, void *stream
     NF4_TRY(validate_linear(args, /*needs_workspace=*/false));
     if (args->rows == 0) return NF4_OK;
     return decode_forward_static_scratch(*args, static_cast<cudaStream_t>(stream));
+}
+
+// ---- the adapter alone, its dense update, the merge ----------------------------------------
+
+static int32_t check_lora(const void *a, const void *b, uint64_t d_in, uint64_t d_out, uint32_t rank,
+                          int32_t layout, int32_t io_dtype, const char *who) {
+    if (!a || !b) return fail(NF4_ERR_INVALID_ARG, "%s: null factors", who);
+    if (rank == 0 || d_in == 0 || d_out == 0) return fail(NF4_ERR_INVALID_ARG, "%s: zero rank or dimension", who);
+    if (layout != NF4_LAYOUT_OUT_IN && layout != NF4_LAYOUT_IN_OUT) return fail(NF4_ERR_INVALID_ARG, "%s: bad layout %d", who, layout);
+    if (io_dtype != NF4_DTYPE_BF16 && io_dtype != NF4_DTYPE_F32) return fail(NF4_ERR_INVALID_ARG, "%s: bad io_dtype %d", who, io_dtype);
+    return NF4_OK;
+}
+
+uint64_t nf4_lora_workspace_bytes(uint64_t rows, uint32_t lora_rank) { return lora_workspace_bytes(rows, lora_rank); }
+
+int32_t nf4_lora_forward_dev(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, const void *lora_a,
+                             const void *lora_b, uint32_t lora_rank, float lora_scale, int32_t layout,
+                             int32_t io_dtype, void *y, uint64_t ldy, void *workspace, uint64_t workspace_bytes,
+                             void *stream) {
+    NF4_TRY(check_lora(lora_a, lora_b, d_in, d_out, lora_rank, layout, io_dtype, "nf4_lora_forward_dev"));
+    if (rows == 0) return NF4_OK;
+    if (!x || !y) return fail(NF4_ERR_INVALID_ARG, "nf4_lora_forward_dev: null x/y");
+    if (ldy != 0 && ldy < d_out) return fail(NF4_ERR_INVALID_ARG, "nf4_lora_forward_dev: ldy < d_out");
+    if (!workspace || workspace_bytes < lora_workspace_bytes(rows, lora_rank))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_lora_forward_dev: workspace smaller than nf4_lora_workspace_bytes");
+    return lora_forward(x, rows, d_in, d_out, lora_a, lora_b, lora_rank, lora_scale, layout, io_dtype, y,
+                        ldy ? ldy : d_out, static_cast<float *>(workspace), static_cast<cudaStream_t>(stream));
+}
+
+int32_t nf4_lora_delta_weight_dev(const void *lora_a, const void *lora_b, uint64_t d_in, uint64_t d_out,
+                                  uint32_t lora_rank, float lora_scale, int32_t layout, int32_t io_dtype,
+                                  float *out, void *stream) {
+    NF4_TRY(check_lora(lora_a, lora_b, d_in, d_out, lora_rank, layout, io_dtype, "nf4_lora_delta_weight_dev"));
+    if (!out) return fail(NF4_ERR_INVALID_ARG, "nf4_lora_delta_weight_dev: null out");
+    return lora_delta(lora_a, lora_b, nullptr, nullptr, nullptr, nullptr, d_in, d_out, lora_rank, lora_scale,
+                      layout, io_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+int32_t nf4_qlora_merge_dev(const uint8_t *packed, const float *absmax, const uint8_t *scale_codes,
+                            const float *scale_of_scales, uint64_t d_in, uint64_t d_out, int32_t layout,
+                            const void *lora_a, const void *lora_b, uint32_t lora_rank, float lora_scale,
+                            int32_t io_dtype, float *out, void *stream) {
+    NF4_TRY(check_lora(lora_a, lora_b, d_in, d_out, lora_rank, layout, io_dtype, "nf4_qlora_merge_dev"));
+    if (!packed || !out) return fail(NF4_ERR_INVALID_ARG, "nf4_qlora_merge_dev: null packed/out");
+    if ((absmax != nullptr) == (scale_codes != nullptr) || (scale_codes && !scale_of_scales))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_qlora_merge_dev: give either absmax or scale_codes+scale_of_scales");
+    return lora_delta(lora_a, lora_b, packed, absmax, scale_codes, scale_of_scales, d_in, d_out, lora_rank,
+                      lora_scale, layout, io_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+// ---- backward of the QLoRA linear (base weight frozen) -----------------------------------------
+
+uint64_t nf4_qlora_backward_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
+    // grad_x is a forward with d_in and d_out exchanged; then two [rows][rank] f32 intermediates
+    return nf4_linear_workspace_bytes(rows, d_out, d_in, lora_rank) + 2 * lora_workspace_bytes(rows, lora_rank);
+}
+
+int32_t nf4_qlora_backward_dev(const nf4_linear_args *fwd, const void *grad_y, void *grad_x, void *grad_a,
+                               void *grad_b, void *stream) {
+    if (!fwd) return fail(NF4_ERR_INVALID_ARG, "nf4_qlora_backward_dev: null args");
+    if (fwd->struct_bytes != sizeof(nf4_linear_args))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_qlora_backward_dev: struct_bytes %u != %zu", fwd->struct_bytes,
+                    sizeof(nf4_linear_args));
+    const uint32_t r = fwd->lora_a ? fwd->lora_rank : 0;
+    if (fwd->rows == 0) return NF4_OK;
+    if (!grad_y || !grad_x || (r && (!grad_a || !grad_b)))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_qlora_backward_dev: null gradient buffer");
+    const uint64_t need = nf4_qlora_backward_workspace_bytes(fwd->rows, fwd->d_in, fwd->d_out, r);
+    if (need && (!fwd->workspace || fwd->workspace_bytes < need || (reinterpret_cast<uintptr_t>(fwd->workspace) & 255u)))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_qlora_backward_dev: workspace smaller than "
+                                         "nf4_qlora_backward_workspace_bytes or not 256-byte aligned");
+    // grad_x = grad_y W^T + s (grad_y B^T) A^T: one more NF4 linear over the same packed bytes read
+    // in the other orientation, the adapter factors exchanging roles
+    nf4_linear_args g = *fwd;
+    g.layout = fwd->layout == NF4_LAYOUT_OUT_IN ? NF4_LAYOUT_IN_OUT : NF4_LAYOUT_OUT_IN;
+    g.d_in = fwd->d_out;
+    g.d_out = fwd->d_in;
+    g.x = grad_y;
+    g.y = grad_x;
+    g.ldy = 0;
+    g.y_f32 = 0;
+    g.bias = nullptr;
+    g.lora_a = fwd->lora_b;
+    g.lora_b = fwd->lora_a;
+    const uint64_t fw = nf4_linear_workspace_bytes(fwd->rows, fwd->d_out, fwd->d_in, r);
+    g.workspace_bytes = fw;
+    NF4_TRY(nf4_linear_forward_dev(&g, stream));
+    if (!r) return NF4_OK;
+    uint8_t *ws = static_cast<uint8_t *>(fwd->workspace) + fw;
+    float *t = reinterpret_cast<float *>(ws);
+    float *u = reinterpret_cast<float *>(ws + lora_workspace_bytes(fwd->rows, r));
+    return lora_grads(fwd->x, grad_y, fwd->lora_a, fwd->lora_b, fwd->rows, fwd->d_in, fwd->d_out, r,
+                      fwd->lora_scale, fwd->layout, fwd->io_dtype, grad_a, grad_b, t, u,
+                      static_cast<cudaStream_t>(stream));
+}
+
+// ---- column-sharded forward ------------------------------------------------------------------
+
+uint64_t nf4_sharded_gather_bytes(uint64_t rows, uint64_t d_out_shard, int32_t world, int32_t io_dtype, int32_t y_f32) {
+    const uint64_t eb = (y_f32 || io_dtype == NF4_DTYPE_F32) ? 4 : 2;
+    return world > 0 ? (uint64_t)world * rows * d_out_shard * eb : 0;
+}
+
+int32_t nf4_sharded_linear_forward_dev(const nf4_linear_args *shard, void *nccl_comm, int32_t rank, int32_t world,
+                                       void *gather_buffer, uint64_t gather_bytes, void *y_full,
+                                       uint64_t ldy_full, void *stream) {
+    NF4_TRY(validate_linear(shard));
+    if (!nccl_comm || world < 1 || rank < 0 || rank >= world)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_sharded_linear_forward_dev: bad communicator, rank or world");
+    if (shard->rows == 0) return NF4_OK;
+    const uint64_t eb = (shard->y_f32 || shard->io_dtype == NF4_DTYPE_F32) ? 4 : 2;
+    const uint64_t ldy_local = shard->ldy ? shard->ldy : shard->d_out;
+    if (ldy_local != shard->d_out)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_sharded_linear_forward_dev: the local slab must be dense (ldy = d_out)");
+    if (ldy_full == 0) ldy_full = shard->d_out * (uint64_t)world;
+    if (ldy_full < shard->d_out * (uint64_t)world)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_sharded_linear_forward_dev: ldy_full < world * d_out of a shard");
+    if (!gather_buffer || !y_full ||
+        gather_bytes < nf4_sharded_gather_bytes(shard->rows, shard->d_out, world, shard->io_dtype, shard->y_f32))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_sharded_linear_forward_dev: gather buffer smaller than nf4_sharded_gather_bytes");
+    NF4_TRY(nf4_linear_forward_dev(shard, stream));
+    return gather_slabs(shard->y, gather_buffer, y_full, shard->rows, shard->d_out * eb, ldy_full * eb, nccl_comm,
+                        world, static_cast<cudaStream_t>(stream));
 }
 
 // ---- host-pointer entry points ------------------------------------------------
@@ -633,6 +789,7 @@ int32_t nf4_weight_download_host(const nf4_weight *w, uint8_t *packed, float *ab
 
 int32_t nf4_weight_dequantize_host(const nf4_weight *w, float *out) {
     if (!w || !out) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_dequantize_host: null pointer");
+    NF4_TRY(check_weight_device(w, "nf4_weight_dequantize_host"));
     NF4_TRY(t_arena.reserve(w->len * 4));
     float *d_o = static_cast<float *>(t_arena.ptr);
     NF4_TRY(dequantize_packed(w->packed, w->len, w->absmax, w->scale_codes, w->scale_of_scales, d_o, 0));
@@ -643,6 +800,7 @@ int32_t nf4_weight_dequantize_host(const nf4_weight *w, float *out) {
 int32_t nf4_weight_attach_lora_host(nf4_weight *w, const void *lora_a, const void *lora_b,
                                     uint32_t lora_rank, float lora_scale, int32_t io_dtype) {
     if (!w) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_attach_lora_host: null weight");
+    NF4_TRY(check_weight_device(w, "nf4_weight_attach_lora_host"));
     cudaFree(w->lora_a);
     cudaFree(w->lora_b);
     w->lora_a = w->lora_b = nullptr;
@@ -668,6 +826,7 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
                                        const void *lora_b, uint32_t lora_rank, float lora_scale,
                                        void *y) {
     if (!w) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_linear_forward_host: null weight");
+    NF4_TRY(check_weight_device(w, "nf4_weight_linear_forward_host"));
     if (rows == 0) return NF4_OK;
     if (!x || !y) return fail(NF4_ERR_INVALID_ARG, "nf4_weight_linear_forward_host: null x/y");
     if (io_dtype != NF4_DTYPE_BF16 && io_dtype != NF4_DTYPE_F32)

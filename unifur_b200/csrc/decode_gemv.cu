@@ -338,28 +338,70 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         }
     };
 
+    // x becomes f16 (the MMA's operand type).  A bf16 value is an f16 value exactly as long as
+    // its magnitude is inside f16's normal range, which activations usually are; a warp whose
+    // slice of an activation row has its largest magnitude at 2^16 or above, or below 2^-7, first
+    // divides that slice by the power of two that brings the largest magnitude to [2^14, 2^15)
+    // and multiplies the row's partial sums back when it parks them (both exact).
     uint32_t xf[NT][NC][4][2];  // this warp's slices of x as f16 B-fragments
     float tpart[NT];            // a producer's first unit of T: this lane's part
+    float col_scale[NT][2];     // factors of this lane's accumulator columns (activation rows 2t, 2t + 1)
+    bool rescaled = false;      // some row of this warp's slice was divided (warp-uniform)
     const uint32_t h_first = blockIdx.x % SL;
     #pragma unroll
     for (int u = 0; u < NT; ++u) {
         tpart[u] = 0.0f;
+        float row_scale = 1.0f;
         #pragma unroll
         for (int half = 0; half < SL; ++half) {
             uint4 xraw[4][2];
             load_x(xraw, 8 * u + g, half);
             if (producer && (uint32_t)half == h_first) tpart[u] = dot_slice(xraw);
+            // the row's largest magnitude in this slice, as bf16 pairs (NaNs are left out)
+            __nv_bfloat162 mx2 = __float2bfloat162_rn(0.0f);
+            #pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                const uint32_t w[8] = {xraw[cc][0].x, xraw[cc][0].y, xraw[cc][0].z, xraw[cc][0].w,
+                                       xraw[cc][1].x, xraw[cc][1].y, xraw[cc][1].z, xraw[cc][1].w};
+                #pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+            }
+            uint32_t mx = *reinterpret_cast<const uint32_t *>(&mx2);
+            mx = max(mx & 0xffffu, mx >> 16);  // non-negative bf16 values order like their bit patterns
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const int ex = (int)(mx >> 7);  // biased exponent: 127 is 2^0, 255 is infinity
+            const bool odd = mx != 0u && ex != 255 && (ex > 142 || ex < 120);
+            float down = 1.0f;
+            if (__any_sync(0xffffffffu, odd)) {
+                int k = odd ? ex - 141 : 0;  // the largest magnitude goes to [2^14, 2^15)
+                k = max(k, -100);
+                down = __int_as_float((127 - k) << 23);
+                row_scale = __int_as_float((127 + k) << 23);
+                rescaled = true;
+            }
             #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 const uint32_t w[8] = {xraw[cc][0].x, xraw[cc][0].y, xraw[cc][0].z, xraw[cc][0].w,
                                        xraw[cc][1].x, xraw[cc][1].y, xraw[cc][1].z, xraw[cc][1].w};
                 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    xf[u][half * 4 + cc][j][0] = bf16x2_to_f16x2(w[2 * j]);
-                    xf[u][half * 4 + cc][j][1] = bf16x2_to_f16x2(w[2 * j + 1]);
+                    if (down == 1.0f) {
+                        xf[u][half * 4 + cc][j][0] = bf16x2_to_f16x2(w[2 * j]);
+                        xf[u][half * 4 + cc][j][1] = bf16x2_to_f16x2(w[2 * j + 1]);
+                    } else {
+                        xf[u][half * 4 + cc][j][0] = pack_f16x2(bf16_bits_to_float(w[2 * j] & 0xffffu) * down,
+                                                                __uint_as_float(w[2 * j] & 0xffff0000u) * down);
+                        xf[u][half * 4 + cc][j][1] = pack_f16x2(bf16_bits_to_float(w[2 * j + 1] & 0xffffu) * down,
+                                                                __uint_as_float(w[2 * j + 1] & 0xffff0000u) * down);
+                    }
                 }
             }
         }
+        // the factor of activation row 8u + 2t + b sits in the lanes whose g is 2t + b
+        col_scale[u][0] = __shfl_sync(0xffffffffu, row_scale, (2u * t) * 4u);
+        col_scale[u][1] = __shfl_sync(0xffffffffu, row_scale, (2u * t + 1u) * 4u);
     }
 
     if (producer) {
@@ -548,6 +590,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                                 acc[u][r] = fmaf(blk[u][r], r < 2 ? s_lo[c] : s_hi[c], acc[u][r]);
                         }
                     }
+                }
+            }
+            if (rescaled) {
+                #pragma unroll
+                for (int u = 0; u < NT; ++u) {
+                    #pragma unroll
+                    for (int r = 0; r < 4; ++r) acc[u][r] *= col_scale[u][r & 1];
                 }
             }
             // park the tile's partial sums: slot q * NT + u of this warp, one float4 per lane
@@ -805,23 +854,10 @@ bool plan(const nf4_linear_args &a, Plan &pl) {
 template <int NT, bool DQ>
 int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
     using C = Cfg;
-    // the shared-memory attribute belongs to the device: set it once per device
-    static std::mutex mu;
-    static bool configured[64] = {};
-    int dev = 0;
-    NF4_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail(NF4_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!configured[dev]) {
-            NF4_CUDA_TRY(cudaFuncSetAttribute(decode_kernel<NT, DQ>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-            configured[dev] = true;
-        }
-    }
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(decode_kernel<NT, DQ>), (int)C::kSmemBytes));
     count_launch();
     return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(pl.grid), dim3(C::kThreads),
-                                   C::kSmemBytes, stream, pdl_enabled(), mc, ms, pl.p);
+                                   C::kSmemBytes, stream, true, mc, ms, pl.p);
 }
 
 // `scratch`: kFlagBytes of flag words (zero at first use, left zero) followed by room for T
@@ -913,6 +949,25 @@ int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t str
     // The array starts zeroed (static storage) and every call leaves the flag words zero; T is
     // rewritten by each call before it is read: nothing to clear here.
     return run(a, pl, scratch, stream);
+}
+
+// A wait that nothing satisfies, with the caller's limit: exercises the bounded wait and the
+// failure flag exactly as the decode kernel uses them, without hanging or trapping anything.
+__global__ void selftest_wait_kernel(uint32_t limit_ns, unsigned long long *waited_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    const uint32_t b = ptx::smem_addr(&bar);
+    ptx::mbar_init(b, 1);
+    ptx::fence_mbar_init();
+    const uint64_t t0 = ptx::global_timer_ns();
+    const bool ok = wait_phase(b, 0, limit_ns);  // phase 0 never completes: nobody arrives
+    *waited_ns = ptx::global_timer_ns() - t0;
+    if (!ok) atomicExch(&g_decode_error, 5);
+}
+
+int32_t decode_selftest_wait(uint32_t limit_ns, unsigned long long *waited_ns_dev, cudaStream_t stream) {
+    selftest_wait_kernel<<<1, 1, 0, stream>>>(limit_ns, waited_ns_dev);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "selftest_wait_kernel launch");
 }
 
 int32_t decode_error_flag_ptr(int **dev_ptr) {

@@ -41,13 +41,6 @@ namespace nf4 {
 
 __device__ int g_decode2_error = 0;  // set when a bounded wait gives up
 
-#ifdef NF4_DECODE_TIMING
-// Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
-__device__ long long g_decode2_ts[64];
-#define NF4_TS2(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31u) == 0) g_decode2_ts[(i)] = clock64(); } while (0)
-#else
-#define NF4_TS2(i) do { } while (0)
-#endif
 
 namespace {
 
@@ -208,7 +201,6 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t grid = gridDim.x, cta = blockIdx.x;
-    if (warp == 0) NF4_TS2(0);
     const uint32_t u0 = run_start(cta, p.total_units, grid);
     const uint32_t u1 = run_start(cta + 1, p.total_units, grid);
     const uint32_t S = p.code_stages;
@@ -305,14 +297,12 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
         }
         if (!released) asm volatile("bar.arrive 3, %0;" ::"n"((kExpanderWarps + 1) * 32) : "memory");
         ptx::fence_proxy_async();  // x_s is read by the tensor core through the async proxy
-        if (warp == 0) NF4_TS2(6);
     }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a = tmem_base + kMaxSegments * kAccPerSeg * kAccCols;
-    if (warp == 0) NF4_TS2(1);
 
     bool ok = true;
 
@@ -391,7 +381,6 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                     ok = false;
                     break;
                 }
-                if (warp == 0 && st < 12) NF4_TS2(8 + 2 * st);
                 const uint32_t kb = g4 * 4 + grp;
                 if (kb >= sg.kb0 && kb < sg.kb1) {
                     const uint8_t *stage = ring + s * kStageBytes;
@@ -426,12 +415,10 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                     if (lane == 0) ptx::mbar_arrive(bar(kBarAFull + slot));
                 }
                 __syncwarp();
-                if (warp == 0 && st < 12) NF4_TS2(9 + 2 * st);
                 if (lane == 0) ptx::mbar_arrive(bar(kBarCodeEmpty + s));
             }
             bc_base += sg.kb1 - sg.kb0;
         }
-        if (warp == 0) NF4_TS2(2);
         if (!ok && lane == 0) atomicExch(&g_decode2_error, 3);
     } else if (warp >= kWarpFinish0) {
         // ================================= finish =================================
@@ -468,7 +455,6 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
             if (!segment_of(p, u0, u1, i, sg)) break;
             if (ok) ok = ptx::mbar_wait_bounded(bar(kBarSegDone + i), 0);
             ptx::tc_fence_after();
-            if (i == 0 && ftid == 0) NF4_TS2(3);
             float v[16];
             #pragma unroll
             for (int m = 0; m < 16; ++m) v[m] = 0.0f;
@@ -566,13 +552,11 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                 }
             }
         }
-        if (ftid == 0) NF4_TS2(4);
         if (!ok && lane == 0) atomicExch(&g_decode2_error, 4);
     }
 
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 0) NF4_TS2(5);
     if (warp == kWarpIssuer0) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
@@ -691,24 +675,14 @@ bool make_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, bool dq, uint32_t r
 
 template <bool DQ>
 int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        NF4_CUDA_TRY(cudaFuncSetAttribute(decode2_kernel<DQ>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-        configured = true;
-    }
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(decode2_kernel<DQ>), kSmemLimit));
     count_launch();
     return launch_maybe_overlapped(decode2_kernel<DQ>, dim3(pl.grid), dim3(kThreads), pl.smem_bytes,
-                                   stream, pl.p.rank != 0 && pdl_enabled(), mc, ms, pl.p);
+                                   stream, pl.p.rank != 0, mc, ms, pl.p);
 }
 
 }  // namespace
 
-#ifdef NF4_DECODE_TIMING
-extern "C" __attribute__((visibility("default"))) int nf4_debug_decode2_timestamps(long long *out64) {
-    return (int)cudaMemcpyFromSymbol(out64, g_decode2_ts, sizeof(long long) * 64);
-}
-#endif
 
 // lora_t_small lives in decode_gemv.cu
 int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, uint32_t rank,

@@ -22,7 +22,23 @@ int32_t launch_maybe_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     cfg.numAttrs = overlap ? 1 : 0;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...), "kernel launch");
 }
-bool pdl_enabled();  // api.cu: NF4_PDL=0 in the environment turns the overlap off
+// api.cu: sets cudaFuncAttributeMaxDynamicSharedMemorySize for `kernel` on the current device,
+// once per (kernel, device): the attribute belongs to the device a kernel is loaded on.
+int32_t ensure_dynamic_smem(const void *kernel, int bytes);
+
+// lora.cu: the adapter alone, its dense update, the merge, and the gather of column slabs
+uint64_t lora_workspace_bytes(uint64_t rows, uint32_t rank);
+int32_t lora_forward(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, const void *a, const void *b,
+                     uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *y, uint64_t ldy,
+                     float *t, cudaStream_t s);
+int32_t lora_delta(const void *a, const void *b, const uint8_t *packed, const float *absmax,
+                   const uint8_t *scale_codes, const float *scale_of_scales, uint64_t d_in, uint64_t d_out,
+                   uint32_t rank, float scale, int32_t layout, int32_t io_dtype, float *out, cudaStream_t s);
+int32_t lora_grads(const void *x, const void *gy, const void *a, const void *b, uint64_t rows, uint64_t d_in,
+                   uint64_t d_out, uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *ga,
+                   void *gb, float *t, float *u, cudaStream_t s);
+int32_t gather_slabs(const void *slab, void *gathered, void *y, uint64_t rows, uint64_t width_bytes,
+                     uint64_t ldy_bytes, void *comm, int32_t world, cudaStream_t s);
 
 // quantize.cu
 int32_t quantize_packed(const float *values, uint64_t len, uint8_t *packed, float *absmax,
@@ -54,6 +70,7 @@ bool decode_supported(const nf4_linear_args &a);
 uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank);
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);
 
+int32_t decode_selftest_wait(uint32_t limit_ns, unsigned long long *waited_ns_dev, cudaStream_t stream);
 // device addresses (current device) of the kernels' failure flags
 int32_t decode_error_flag_ptr(int **dev_ptr);
 int32_t decode2_error_flag_ptr(int **dev_ptr);

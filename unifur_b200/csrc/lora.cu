@@ -1,0 +1,246 @@
+// The adapter by itself: LoraAdapter::forward, LoraAdapter::delta_weight and QLoraLinear::merged of
+// the reference (src/quantize.rs:620-624, 629-634, 717-726), and the gather step of the
+// column-sharded forward.  Small CUDA-core kernels: a rank-r product has r multiply-adds per
+// output, so these are bound by the bytes of x, A, B and the output they touch.
+//
+// Arithmetic follows the reference's order in f32: (x A) first, then (.) B, the scale last;
+// delta = (A B) * scale; merged = W + delta with W = level * block scale.
+#include <cuda_bf16.h>
+#include <dlfcn.h>
+
+#include <mutex>
+
+#include "kernels.cuh"
+
+namespace nf4 {
+namespace {
+
+template <class T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <class T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// A(k, j) and B(j, n) in either orientation:
+//   OUT_IN: A [r, d_in], B [d_out, r]      IN_OUT (the reference's): A [d_in, r], B [r, d_out]
+template <class T>
+__device__ __forceinline__ float a_at(const T *a, int32_t layout, uint64_t k, uint64_t j, uint64_t d_in, uint32_t rank) {
+    return to_f32<T>(layout == NF4_LAYOUT_OUT_IN ? a[j * d_in + k] : a[k * rank + j]);
+}
+template <class T>
+__device__ __forceinline__ float b_at(const T *b, int32_t layout, uint64_t j, uint64_t n, uint64_t d_out, uint32_t rank) {
+    return to_f32<T>(layout == NF4_LAYOUT_OUT_IN ? b[n * rank + j] : b[j * d_out + n]);
+}
+
+// T[m][j] = sum_k x[m][k] * A(k, j); one warp per (m, j), lanes stride over k.
+template <class T>
+__global__ void __launch_bounds__(256)
+lora_xa_kernel(const T *__restrict__ x, const T *__restrict__ a, float *__restrict__ t, uint64_t rows,
+               uint64_t d_in, uint32_t rank, int32_t layout) {
+    const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (warp >= rows * rank) return;
+    const uint64_t m = warp / rank, j = warp % rank;
+    float acc = 0.0f;
+    for (uint64_t k = lane; k < d_in; k += 32) acc = fmaf(to_f32<T>(x[m * d_in + k]), a_at<T>(a, layout, k, j, d_in, rank), acc);
+    #pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) t[m * rank + j] = acc;
+}
+
+// y[m][n] = (sum_j T[m][j] * B(j, n)) * scale; one thread per (m, n), n fastest.
+template <class T>
+__global__ void __launch_bounds__(256)
+lora_tb_kernel(const float *__restrict__ t, const T *__restrict__ b, T *__restrict__ y, uint64_t rows,
+               uint64_t d_out, uint64_t ldy, uint32_t rank, float scale, int32_t layout) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * d_out) return;
+    const uint64_t m = i / d_out, n = i % d_out;
+    float acc = 0.0f;
+    for (uint32_t j = 0; j < rank; ++j) acc = fmaf(t[m * rank + j], b_at<T>(b, layout, j, n, d_out, rank), acc);
+    y[m * ldy + n] = from_f32<T>(__fmul_rn(acc, scale));
+}
+
+// out(k, n) = [W(k, n) +] (sum_j A(k, j) * B(j, n)) * scale, stored in the weight's own orientation
+// (flat index = k * d_out + n for IN_OUT, n * d_in + k for OUT_IN); one thread per element.
+template <class T, bool MERGE>
+__global__ void __launch_bounds__(256)
+lora_delta_kernel(const T *__restrict__ a, const T *__restrict__ b, const uint8_t *__restrict__ packed,
+                  const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
+                  const float *__restrict__ scale_of_scales, float *__restrict__ out, uint64_t d_in,
+                  uint64_t d_out, uint32_t rank, float scale, int32_t layout) {
+    const uint64_t flat = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (flat >= d_in * d_out) return;
+    const uint64_t k = layout == NF4_LAYOUT_OUT_IN ? flat % d_in : flat / d_out;
+    const uint64_t n = layout == NF4_LAYOUT_OUT_IN ? flat / d_in : flat % d_out;
+    float acc = 0.0f;
+    for (uint32_t j = 0; j < rank; ++j)
+        acc = fmaf(a_at<T>(a, layout, k, j, d_in, rank), b_at<T>(b, layout, j, n, d_out, rank), acc);
+    float v = __fmul_rn(acc, scale);
+    if (MERGE) {
+        const uint32_t byte = __ldg(packed + (flat >> 1));
+        const uint32_t code = (flat & 1u) ? (byte >> 4) : (byte & 15u);
+        const uint64_t blk = flat / kBlock;
+        const float s = absmax ? __ldg(absmax + blk) : dq_scale(__ldg(scale_codes + blk), __ldg(scale_of_scales));
+        v = __fadd_rn(__fmul_rn(__uint_as_float(c_level_bits[code]), s), v);
+    }
+    out[flat] = v;
+}
+
+// out(p, j) = scale * sum_m X[m][p] * R[m][j]: the adapter gradients (X = x or grad_y in the io type,
+// R = the f32 intermediate of the other factor).  One thread per (p, j), p fastest in memory reads.
+// `p_major`: out is [P][rank] (else [rank][P]).
+template <class T>
+__global__ void __launch_bounds__(256)
+lora_xtr_kernel(const T *__restrict__ x, const float *__restrict__ r, T *__restrict__ out, uint64_t rows,
+                uint64_t P, uint32_t rank, float scale, int p_major) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P * rank) return;
+    const uint64_t j = i / P, pp = i % P;
+    float acc = 0.0f;
+    for (uint64_t m = 0; m < rows; ++m) acc = fmaf(to_f32<T>(x[m * P + pp]), r[m * rank + j], acc);
+    out[p_major ? pp * rank + j : j * P + pp] = from_f32<T>(__fmul_rn(acc, scale));
+}
+
+// y[r][rank * width + c] = gathered[rank][r][c]: the ranks' slabs side by side.  16-byte pieces.
+__global__ void __launch_bounds__(256)
+place_slabs_kernel(const uint4 *__restrict__ gathered, uint4 *__restrict__ y, uint64_t rows, uint64_t pieces_per_row,
+                   uint64_t ldy_pieces, uint32_t world) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t per_rank = rows * pieces_per_row;
+    if (i >= per_rank * world) return;
+    const uint64_t rk = i / per_rank, rem = i % per_rank, r = rem / pieces_per_row, c = rem % pieces_per_row;
+    y[r * ldy_pieces + rk * pieces_per_row + c] = gathered[i];
+}
+
+template <class T>
+int32_t forward_t(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, const void *a, const void *b,
+                  uint32_t rank, float scale, int32_t layout, void *y, uint64_t ldy, float *t, cudaStream_t s) {
+    const uint64_t warps = rows * rank;
+    lora_xa_kernel<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(
+        static_cast<const T *>(x), static_cast<const T *>(a), t, rows, d_in, rank, layout);
+    lora_tb_kernel<T><<<(unsigned)((rows * d_out + 255) / 256), 256, 0, s>>>(
+        t, static_cast<const T *>(b), static_cast<T *>(y), rows, d_out, ldy, rank, scale, layout);
+    count_launch(2);
+    return check_cuda(cudaGetLastError(), "lora forward launch");
+}
+
+template <class T>
+int32_t grads_t(const void *x, const void *gy, const void *a, const void *b, uint64_t rows, uint64_t d_in,
+                uint64_t d_out, uint32_t rank, float scale, int32_t layout, void *ga, void *gb, float *t,
+                float *u, cudaStream_t s) {
+    const T *xx = static_cast<const T *>(x), *gg = static_cast<const T *>(gy);
+    const unsigned wgrid = (unsigned)((rows * rank * 32 + 255) / 256);
+    // T = x A (as in the forward) and U = grad_y B^T (B read as an "A" of the other orientation)
+    lora_xa_kernel<T><<<wgrid, 256, 0, s>>>(xx, static_cast<const T *>(a), t, rows, d_in, rank, layout);
+    lora_xa_kernel<T><<<wgrid, 256, 0, s>>>(gg, static_cast<const T *>(b), u, rows, d_out, rank,
+                                          layout == NF4_LAYOUT_OUT_IN ? NF4_LAYOUT_IN_OUT : NF4_LAYOUT_OUT_IN);
+    // grad_A(k, j) = s sum_m x[m][k] U[m][j];  grad_B(j, n) = s sum_m T[m][j] grad_y[m][n]
+    lora_xtr_kernel<T><<<(unsigned)((d_in * rank + 255) / 256), 256, 0, s>>>(
+        xx, u, static_cast<T *>(ga), rows, d_in, rank, scale, layout == NF4_LAYOUT_IN_OUT);
+    lora_xtr_kernel<T><<<(unsigned)((d_out * rank + 255) / 256), 256, 0, s>>>(
+        gg, t, static_cast<T *>(gb), rows, d_out, rank, scale, layout == NF4_LAYOUT_OUT_IN);
+    count_launch(4);
+    return check_cuda(cudaGetLastError(), "lora gradient launch");
+}
+
+// ---- NCCL, looked up at run time: the library is not linked against it, so that hosts
+// without NCCL can load everything else ----
+typedef int (*AllGatherFn)(const void *, void *, size_t, int, void *, cudaStream_t);
+typedef const char *(*ErrStrFn)(int);
+
+AllGatherFn nccl_all_gather(ErrStrFn *err) {
+    static AllGatherFn fn = nullptr;
+    static ErrStrFn efn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = dlsym(RTLD_DEFAULT, "ncclAllGather");  // already loaded by the host (torch, a Rust binding)
+        void *esym = dlsym(RTLD_DEFAULT, "ncclGetErrorString");
+        if (!sym) {
+            void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+            if (h) {
+                sym = dlsym(h, "ncclAllGather");
+                esym = dlsym(h, "ncclGetErrorString");
+            }
+        }
+        fn = reinterpret_cast<AllGatherFn>(sym);
+        efn = reinterpret_cast<ErrStrFn>(esym);
+    });
+    *err = efn;
+    return fn;
+}
+
+}  // namespace
+
+uint64_t lora_workspace_bytes(uint64_t rows, uint32_t rank) { return (rows * rank * 4 + 255) / 256 * 256; }
+
+int32_t lora_forward(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, const void *a, const void *b,
+                     uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *y, uint64_t ldy,
+                     float *t, cudaStream_t s) {
+    if (rows * rank >= (1ull << 40) || rows * d_out >= (1ull << 40))
+        return fail(NF4_ERR_UNSUPPORTED, "nf4_lora_forward: shape too large");
+    return io_dtype == NF4_DTYPE_F32
+               ? forward_t<float>(x, rows, d_in, d_out, a, b, rank, scale, layout, y, ldy, t, s)
+               : forward_t<__nv_bfloat16>(x, rows, d_in, d_out, a, b, rank, scale, layout, y, ldy, t, s);
+}
+
+int32_t lora_delta(const void *a, const void *b, const uint8_t *packed, const float *absmax,
+                   const uint8_t *scale_codes, const float *scale_of_scales, uint64_t d_in, uint64_t d_out,
+                   uint32_t rank, float scale, int32_t layout, int32_t io_dtype, float *out, cudaStream_t s) {
+    const uint64_t n = d_in * d_out;
+    if (n >= (1ull << 40)) return fail(NF4_ERR_UNSUPPORTED, "lora delta: shape too large");
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    const bool merge = packed != nullptr;
+    if (io_dtype == NF4_DTYPE_F32) {
+        const float *fa = static_cast<const float *>(a), *fb = static_cast<const float *>(b);
+        if (merge) lora_delta_kernel<float, true><<<grid, 256, 0, s>>>(fa, fb, packed, absmax, scale_codes, scale_of_scales, out, d_in, d_out, rank, scale, layout);
+        else lora_delta_kernel<float, false><<<grid, 256, 0, s>>>(fa, fb, nullptr, nullptr, nullptr, nullptr, out, d_in, d_out, rank, scale, layout);
+    } else {
+        const __nv_bfloat16 *ha = static_cast<const __nv_bfloat16 *>(a), *hb = static_cast<const __nv_bfloat16 *>(b);
+        if (merge) lora_delta_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(ha, hb, packed, absmax, scale_codes, scale_of_scales, out, d_in, d_out, rank, scale, layout);
+        else lora_delta_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(ha, hb, nullptr, nullptr, nullptr, nullptr, out, d_in, d_out, rank, scale, layout);
+    }
+    count_launch();
+    return check_cuda(cudaGetLastError(), "lora delta launch");
+}
+
+// grad_A and grad_B of y = x W + s (x A) B with W frozen; t and u are [rows][rank] f32 scratch.
+int32_t lora_grads(const void *x, const void *gy, const void *a, const void *b, uint64_t rows, uint64_t d_in,
+                   uint64_t d_out, uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *ga,
+                   void *gb, float *t, float *u, cudaStream_t s) {
+    if (rows * rank >= (1ull << 40) || (d_in + d_out) * rank >= (1ull << 40))
+        return fail(NF4_ERR_UNSUPPORTED, "lora gradients: shape too large");
+    return io_dtype == NF4_DTYPE_F32
+               ? grads_t<float>(x, gy, a, b, rows, d_in, d_out, rank, scale, layout, ga, gb, t, u, s)
+               : grads_t<__nv_bfloat16>(x, gy, a, b, rows, d_in, d_out, rank, scale, layout, ga, gb, t, u, s);
+}
+
+// All-gather of the ranks' [rows, width_bytes] slabs into `gathered` ([world][rows][width_bytes]),
+// then the slabs side by side into y ([rows][ldy_bytes]).
+int32_t gather_slabs(const void *slab, void *gathered, void *y, uint64_t rows, uint64_t width_bytes,
+                     uint64_t ldy_bytes, void *comm, int32_t world, cudaStream_t s) {
+    if (width_bytes % 16 != 0 || ldy_bytes % 16 != 0 ||
+        ((reinterpret_cast<uintptr_t>(gathered) | reinterpret_cast<uintptr_t>(y)) & 15u))
+        return fail(NF4_ERR_INVALID_ARG, "sharded forward: slab widths and buffers must be multiples of 16 bytes");
+    ErrStrFn estr = nullptr;
+    AllGatherFn ag = nccl_all_gather(&estr);
+    if (!ag) return fail(NF4_ERR_UNSUPPORTED, "sharded forward: ncclAllGather not found (is NCCL loaded?)");
+    const int rc = ag(slab, gathered, (size_t)(rows * width_bytes), /*ncclUint8*/ 1, comm, s);
+    if (rc != 0) return fail(NF4_ERR_CUDA, "ncclAllGather failed: %s", estr ? estr(rc) : "unknown NCCL error");
+    const uint64_t pieces = rows * (width_bytes / 16) * (uint64_t)world;
+    place_slabs_kernel<<<(unsigned)((pieces + 255) / 256), 256, 0, s>>>(
+        static_cast<const uint4 *>(gathered), static_cast<uint4 *>(y), rows, width_bytes / 16, ldy_bytes / 16,
+        (uint32_t)world);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "slab placement launch");
+}
+
+}  // namespace nf4

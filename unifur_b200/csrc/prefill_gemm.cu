@@ -51,21 +51,8 @@ namespace nf4 {
 
 __device__ int g_prefill_error = 0;  // set when a bounded wait gives up
 
-#ifdef NF4_PREFILL_TIMING
-// Optional instrumentation (off in the shipped build): SM-clock timestamps of CTA 0.
-__device__ long long g_prefill_ts[128];
-#define NF4_PTS(i) do { if (blockIdx.x == 0) g_prefill_ts[(i)] = clock64(); } while (0)
-#ifndef NF4_PTS_FIRST
-#define NF4_PTS_FIRST 20
-#endif
-#else
-#define NF4_PTS_FIRST 20
-#define NF4_PTS(i) do { } while (0)
-#endif
 
 namespace {
-
-constexpr uint32_t kTsFirst = NF4_PTS_FIRST;  // first of the eight k-stages the timing build stamps
 
 constexpr int BM = 128;        // weight rows per tile (MMA M, TMEM lanes)
 constexpr int BN = 256;        // activation rows per tile (MMA N, accumulator columns)
@@ -204,11 +191,6 @@ __device__ __forceinline__ void expand_half(const LevelTables &t, const uint4 &c
     const __half2 s2 = __float2half2_rn(scale);
     const uint32_t s = *reinterpret_cast<const uint32_t *>(&s2);
     const uint32_t w[4] = {c.x, c.y, c.z, c.w};
-#ifdef NF4_PREFILL_FAKE_EXPAND  // measurement aid: what the stage costs without the expansion
-    #pragma unroll
-    for (int i = 0; i < 16; ++i) out[i] = w[i & 3] ^ s;
-    return;
-#endif
     #pragma unroll
     for (int i = 0; i < 4; ++i) {
         uint32_t a, b, c2, d;
@@ -225,6 +207,20 @@ struct RowStage {
     uint4 c0, c1;  // the row's 64 packed codes of one k-stage
     float scale;
 };
+
+// The tensor-core GEMM scales the expanded levels in f16, so block scales must sit inside f16's
+// normal range (6.1e-5 .. 65504).  Both kernels therefore work with scales divided by 2^e, e the
+// exponent of the weight's first block scale (the scales of one weight lie within a few powers of
+// two of each other), and the outputs are multiplied back by 2^e: the pre-pass folds 2^e into the
+// rows' factors and 2^-e into the adapter intermediate.  Powers of two: every step is exact.
+__device__ __forceinline__ int weight_exponent(const float *absmax, const uint8_t *scale_codes,
+                                               const float *scale_of_scales) {
+    const float s0 = absmax ? __ldg(absmax) : dq_scale(__ldg(scale_codes), __ldg(scale_of_scales));
+    if (!(s0 > 0.0f) || s0 >= __int_as_float(0x7f800000)) return 0;
+    int e;
+    frexpf(s0, &e);  // s0 = f * 2^e, f in [0.5, 1)
+    return min(max(e, -100), 100);
+}
 
 template <bool YF32>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -306,11 +302,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                         ok = false;
                         break;
                     }
-                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(cnt - kTsFirst);
-#ifdef NF4_PREFILL_FAKE_X  // measurement aid: what the stage costs without the activation stream
-                    ptx::mbar_arrive(bar(kBarXFull + s));
-                    continue;
-#endif
                     const uint32_t dst = ptx::smem_addr(x_ring + s * kXTileBytes);
                     if (ks < k_stages) {
                         ptx::mbar_arrive_expect_tx(bar(kBarXFull + s), kXTileBytes);
@@ -356,7 +347,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     const uint32_t acnt = i * k_stages + ks, lcnt = i * lora_stages + (ks - k_stages);
                     const uint32_t sa = acnt % kAStages, pha = (acnt / kAStages) & 1u;
                     const uint32_t ls = lcnt % kLoraStages;
-                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(16 + 4 * (cnt - kTsFirst));
                     // the epilogue must have read the previous tile out of the accumulator
                     if (ks == 0 && !ptx::mbar_wait_suspended(bar(kBarAccEmpty), (i & 1u) ^ 1u)) {
                         ok = false;
@@ -366,7 +356,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                         ok = false;
                         break;
                     }
-                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(17 + 4 * (cnt - kTsFirst));
                     if (main_stage && !ptx::mbar_wait_suspended(bar(kBarAFull + sa), pha)) {
                         ok = false;
                         break;
@@ -377,7 +366,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                         ok = false;
                         break;
                     }
-                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(18 + 4 * (cnt - kTsFirst));
                     ptx::tc_fence_after();
                     const uint64_t bdesc = make_kmajor_sw128_desc(x_addr + sx * kXTileBytes);
                     const uint32_t a_cols = tmem_a + sa * kAStageCols;
@@ -402,7 +390,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     ptx::tc_commit(bar(kBarXEmpty + sx));
                     ptx::tc_commit(main_stage ? bar(kBarAEmpty + sa) : bar(kBarLEmpty + ls));
                     if (ks + 1 == stages_per_tile) ptx::tc_commit(bar(kBarAccFull));
-                    if (cnt >= kTsFirst && cnt < kTsFirst + 8) NF4_PTS(19 + 4 * (cnt - kTsFirst));
                 }
             }
             if (!ok) atomicExch(&g_prefill_error, 2);
@@ -439,7 +426,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             row_scales[epi_thread] = m0 + epi_thread < p.M ? __ldg(p.row_scale + m0 + epi_thread) : 1.0f;
             ok = ptx::mbar_wait_suspended(bar(kBarAccFull), i & 1u);
             if (!ok) break;
-            if (warp == 2 && lane == 0) NF4_PTS(100 + 2 * (i & 3u));
             ptx::tc_fence_after();
             uint32_t va[16], vb[16];
             tmem_ld16(acc_lane + col_of(0), va);
@@ -484,7 +470,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty));
-                    if (warp == 2 && lane == 0) NF4_PTS(101 + 2 * (i & 3u));
                 }
                 stage_chunk(vb, col_of(k + 1));
                 if ((k + 2) % kPerPass == 0) {
@@ -512,6 +497,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         const uint32_t row_in_tile = q * 32 + lane;
         const LevelTables tables = make_level_tables();
         const float sos = p.scale_codes ? __ldg(p.scale_of_scales) : 0.0f;
+        // block scales are used divided by a power of two (see weight_exponent)
+        const float w_down = ldexpf(1.0f, -weight_exponent(p.absmax, p.scale_codes, p.scale_of_scales));
         const uint32_t blocks_per_row = p.K / 64;
         const uint32_t total = my_tiles * k_stages;
         const uint32_t lane_base = tmem_a + ((q * 32) << 16);
@@ -543,41 +530,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             if (pos.cnt >= total) return;
             const uint32_t ks = pos.ks, n = pos.n;
             if (n >= p.N) return;
-#ifdef NF4_PREFILL_FAKE_FETCH  // measurement aid: what the stage costs without the global loads
-            rs.c0 = make_uint4(n, ks, n ^ ks, 7u);
-            rs.c1 = rs.c0;
-            rs.scale = 1.0f;
-            return;
-#endif
             const uint4 *src = reinterpret_cast<const uint4 *>(
                 p.codes + (size_t)n * (p.K / 2) + (size_t)ks * 32);
             rs.c0 = __ldg(src);
             rs.c1 = __ldg(src + 1);
             const size_t blk = (size_t)n * blocks_per_row + ks;
-            rs.scale = p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos);
+            rs.scale = (p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos)) * w_down;
         };
         auto emit = [&](const Pos &pos, const RowStage &rs) -> bool {
             const uint32_t cnt = pos.cnt;
             const uint32_t s = cnt % kAStages, ph = (cnt / kAStages) & 1u;
             const uint32_t dst = lane_base + s * kAStageCols;
-            const bool stamp = q == 0 && lane == 0 && cnt >= kTsFirst && cnt < kTsFirst + 8;
             uint32_t lo[16], hi[16];
             expand_half(tables, rs.c0, rs.scale, lo);
             expand_half(tables, rs.c1, rs.scale, hi);
-            if (stamp) NF4_PTS(64 + 4 * (cnt - kTsFirst));
             if (!ptx::mbar_wait_suspended(bar(kBarAEmpty + s), ph ^ 1u)) return false;
-            if (stamp) NF4_PTS(65 + 4 * (cnt - kTsFirst));
             ptx::tc_fence_after();
-#ifndef NF4_PREFILL_FAKE_STORE  // measurement aid: what the stage costs without the TMEM stores
             tmem_st32(dst, lo, hi);
             ptx::tmem_wait_st();
-#else
-            if (lo[3] == 0x12345678u && hi[5] == 0x12345678u) NF4_PTS(127);  // keeps the expansion alive
-#endif
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(kBarAFull + s));
-            if (stamp) NF4_PTS(66 + 4 * (cnt - kTsFirst));
             return true;
         };
 
@@ -659,7 +632,8 @@ __global__ void __launch_bounds__(kTThreads)
 prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
                        uint32_t M, uint32_t K, uint32_t rank, uint32_t chunks, float scale,
                        __half *__restrict__ xh, float *__restrict__ row_scale,
-                       __nv_bfloat16 *__restrict__ t_out) {
+                       __nv_bfloat16 *__restrict__ t_out, const float *__restrict__ absmax,
+                       const uint8_t *__restrict__ scale_codes, const float *__restrict__ scale_of_scales) {
     __shared__ float red[16][64 + 1];
     __shared__ uint32_t row_max_bits[16];
     __shared__ float inv_scale[16];
@@ -668,6 +642,8 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
     const uint32_t m0 = blockIdx.x * 16;
     const uint32_t rows = min(16u, M - m0);
     ptx::pdl_launch_dependents();  // the GEMM may set itself up and start on the weights
+    const int w_exp = weight_exponent(absmax, scale_codes, scale_of_scales);
+    const float w_up = ldexpf(1.0f, w_exp), w_down = ldexpf(1.0f, -w_exp);
     const bool row_a = g < rows, row_b = g + 8 < rows;
     const uint32_t pieces = (K + 31) / 32, n_it = (pieces + kTWarps - 1) / kTWarps;
     const size_t off_a = (size_t)(m0 + g) * K, off_b = (size_t)(m0 + g + 8) * K;
@@ -753,7 +729,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
                     sc = ldexpf(1.0f, e - 15);  // mx / sc lands in [16384, 32768)
                 }
                 inv_scale[threadIdx.x] = 1.0f / sc;  // exact: sc is a power of two
-                if (threadIdx.x < rows) row_scale[m0 + threadIdx.x] = sc;
+                if (threadIdx.x < rows) row_scale[m0 + threadIdx.x] = sc * w_up;  // both factors of the outputs
             }
             __syncthreads();
             // rows beyond f16's range: convert again, scaled
@@ -771,7 +747,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             for (uint32_t i = threadIdx.x; i < 16 * 64; i += kTThreads) {
                 const uint32_t r = i >> 6, c = i & 63u;
                 if (m0 + r < M) {
-                    const float v = red[r][c] * scale * inv_scale[r];
+                    const float v = red[r][c] * scale * inv_scale[r] * w_down;
                     const __nv_bfloat16 hi = __float2bfloat16_rn(v);
                     const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
                     t_out[(size_t)(m0 + r) * ld_t + chunk * 64 + c] = hi;
@@ -887,7 +863,7 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.row_scale = row_scale;
     prefill_prepass_kernel<<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(a.lora_a), p.M, p.K,
-        p.rank, p.lora_chunks, a.lora_scale, xh, row_scale, t);
+        p.rank, p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales);
     count_launch();
     NF4_CUDA_TRY(cudaGetLastError());
 
@@ -915,33 +891,18 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     const size_t smem = 1024 + kXStages * kXTileBytes + kLoraStages * kLoraTileBytes + kEpiBytes +
                         kNumBars * 8 + 16 + BN * 4 + 64;
     if (a.y_f32) {
-        static bool configured = false;
-        if (!configured) {
-            NF4_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<true>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            configured = true;
-        }
+        NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_kernel<true>), (int)smem));
         NF4_TRY(launch_maybe_overlapped(prefill_kernel<true>, dim3(grid), dim3(kThreads), smem, stream,
-                                        pdl_enabled(), map_x, map_t, map_b, map_y, p));
+                                        true, map_x, map_t, map_b, map_y, p));
     } else {
-        static bool configured = false;
-        if (!configured) {
-            NF4_CUDA_TRY(cudaFuncSetAttribute(prefill_kernel<false>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            configured = true;
-        }
+        NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_kernel<false>), (int)smem));
         NF4_TRY(launch_maybe_overlapped(prefill_kernel<false>, dim3(grid), dim3(kThreads), smem, stream,
-                                        pdl_enabled(), map_x, map_t, map_b, map_y, p));
+                                        true, map_x, map_t, map_b, map_y, p));
     }
     count_launch();
     return check_cuda(cudaGetLastError(), "prefill_kernel launch");
 }
 
-#ifdef NF4_PREFILL_TIMING
-extern "C" __attribute__((visibility("default"))) int nf4_debug_prefill_timestamps(long long *out128) {
-    return (int)cudaMemcpyFromSymbol(out128, g_prefill_ts, sizeof(long long) * 128);
-}
-#endif
 
 int32_t prefill_error_flag_ptr(int **dev_ptr) {
     return check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(dev_ptr), g_prefill_error),

@@ -252,13 +252,15 @@ def quantize_module(module: torch.nn.Module, double_quantization: bool,
                     skip: Sequence[str] = ()) -> Tuple[torch.nn.Module, int]:
     """src/quantize.rs:426-511: put every weight-shaped parameter on the NF4 grid in place.
 
-    Parameters of rank < 2, with fewer than 64 values, or whose dotted path contains any
-    entry of ``skip`` are left untouched.  Returns the module and the number of values
-    quantized."""
+    Parameters of rank < 2, with fewer than 64 values, or with a path component (a module or
+    field name between the dots) that contains any entry of ``skip`` are left untouched, as
+    ``Nf4Quantizer::is_skipped`` decides it (src/quantize.rs:454-458).  Returns the module and
+    the number of values quantized."""
     count = 0
     with torch.no_grad():
         for name, param in module.named_parameters():
-            if param.dim() < 2 or param.numel() < BLOCK_SIZE or any(s in name for s in skip):
+            skipped = any(needle in part for needle in skip for part in name.split("."))
+            if param.dim() < 2 or param.numel() < BLOCK_SIZE or skipped:
                 continue
             param.copy_(quantize_dequantize_tensor(param.data, double_quantization))
             param.requires_grad_(False)
@@ -332,16 +334,13 @@ class LoraAdapter:
         return self._scaling
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x [rows, in] -> [rows, out].  Runs the library's forward with an all-zero-free
-        path: the adapter alone is a linear layer whose base weight is absent, so this is
-        expressed through :func:`linear_forward` with ``packed=None``."""
+        """``((x A) B) * scaling`` for ``x [rows, in]`` (src/quantize.rs:620-624)."""
         return lora_forward(x, self._a, self._b, self._scaling)
 
     def delta_weight(self) -> torch.Tensor:
-        """``(A B) * scaling`` as ``[in, out]`` (src/quantize.rs:629-634); merge/verification
-        only -- identity rows pushed through the adapter."""
-        eye = torch.eye(self.in_features(), device=self._a.device, dtype=self._a.dtype)
-        return lora_forward(eye, self._a, self._b, self._scaling)
+        """``(A B) * scaling`` as f32 ``[in, out]`` (src/quantize.rs:629-634); for merging and
+        verification, not for the forward path."""
+        return lora_delta_weight(self._a, self._b, self._scaling)
 
 
 def _io_dtype(t: torch.Tensor) -> int:
@@ -352,27 +351,60 @@ def _io_dtype(t: torch.Tensor) -> int:
     raise TypeError(f"activations must be bf16 or f32, got {t.dtype}")
 
 
-_ZERO_WEIGHTS = {}
-
-
-def _zero_weight(d_in: int, d_out: int, device) -> PackedNf4Tensor:
-    """An all-zero packed weight (code 7 everywhere, scale 0) used to run the adapter alone."""
-    key = (d_in, d_out, str(device))
-    if key not in _ZERO_WEIGHTS:
-        n = d_in * d_out
-        codes = torch.full(((n + 1) // 2,), 0x77, dtype=torch.uint8, device=device)
-        absmax = torch.zeros((n + BLOCK_SIZE - 1) // BLOCK_SIZE, dtype=torch.float32, device=device)
-        _ZERO_WEIGHTS[key] = PackedNf4Tensor(codes, n, absmax)
-    return _ZERO_WEIGHTS[key]
-
-
 def lora_forward(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, scaling: float) -> torch.Tensor:
     """``LoraAdapter::forward`` (src/quantize.rs:620-624) with the reference's factor shapes
-    ``A [in, rank]``, ``B [rank, out]``."""
+    ``A [in, rank]``, ``B [rank, out]``, through ``nf4_lora_forward_dev``."""
+    _require_cuda(x, "x")
+    lib = _lib.load()
     d_in, rank = a.shape
     d_out = b.shape[1]
-    return linear_forward(x, _zero_weight(d_in, d_out, x.device), d_in, d_out, LAYOUT_IN_OUT,
-                          lora_a=a, lora_b=b, lora_scale=scaling)
+    x2 = x.contiguous().view(-1, d_in)
+    rows, dev = x2.shape[0], x2.device
+    a2, b2 = a.to(x2.dtype).contiguous(), b.to(x2.dtype).contiguous()
+    y = torch.empty(rows, d_out, dtype=x2.dtype, device=dev)
+    ws = torch.empty(max(int(lib.nf4_lora_workspace_bytes(rows, rank)), 256), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.nf4_lora_forward_dev(_ptr(x2), rows, d_in, d_out, _ptr(a2), _ptr(b2), rank,
+                                            float(scaling), LAYOUT_IN_OUT, _io_dtype(x2), _ptr(y), d_out,
+                                            _ptr(ws), ws.numel(), _stream(dev)))
+    return y.view(*x.shape[:-1], d_out)
+
+
+def lora_delta_weight(a: torch.Tensor, b: torch.Tensor, scaling: float) -> torch.Tensor:
+    """``LoraAdapter::delta_weight`` (src/quantize.rs:629-634): f32 ``[in, out]``."""
+    _require_cuda(a, "a")
+    lib = _lib.load()
+    d_in, rank = a.shape
+    d_out = b.shape[1]
+    dev = a.device
+    a2 = a.contiguous()
+    b2 = b.to(a2.dtype).contiguous()
+    out = torch.empty(d_in, d_out, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.nf4_lora_delta_weight_dev(_ptr(a2), _ptr(b2), d_in, d_out, rank, float(scaling),
+                                                 LAYOUT_IN_OUT, _io_dtype(a2), _ptr(out), _stream(dev)))
+    return out
+
+
+def qlora_merge(packed: "PackedNf4Tensor", d_in: int, d_out: int, a: torch.Tensor, b: torch.Tensor,
+                scaling: float, layout: int = LAYOUT_IN_OUT) -> torch.Tensor:
+    """``dequant(W) + (A B) * scaling`` in f32, in the weight's orientation
+    (``QLoraLinear::merged``, src/quantize.rs:717-726)."""
+    lib = _lib.load()
+    dev = packed.codes.device
+    rank = a.shape[1] if layout == LAYOUT_IN_OUT else a.shape[0]
+    a2 = a.contiguous()
+    b2 = b.to(a2.dtype).contiguous()
+    shape = (d_in, d_out) if layout == LAYOUT_IN_OUT else (d_out, d_in)
+    out = torch.empty(shape, dtype=torch.float32, device=dev)
+    dq = packed.is_double_quantized()
+    with torch.cuda.device(dev):
+        _lib.check(lib.nf4_qlora_merge_dev(
+            _ptr(packed.codes), None if dq else _ptr(packed.absmax),
+            _ptr(packed.scale_codes) if dq else None, _ptr(packed.scale_of_scales) if dq else None,
+            d_in, d_out, layout, _ptr(a2), _ptr(b2), rank, float(scaling), _io_dtype(a2), _ptr(out),
+            _stream(dev)))
+    return out
 
 
 def linear_forward(x: torch.Tensor, packed: PackedNf4Tensor, d_in: int, d_out: int, layout: int,
@@ -433,6 +465,7 @@ class QLoraLinear:
         self._adapter = adapter
         self.quantized_values = quantized_values
         self.double_quantized = double_quantized
+        self._packed = None   # the packed form of `weight`, made once (the weight is frozen)
 
     @staticmethod
     def from_linear(weight: torch.Tensor, bias: Optional[torch.Tensor], config: LoraConfig,
@@ -442,18 +475,33 @@ class QLoraLinear:
         adapter = LoraAdapter.new(config, weight.device, generator=generator)
         return QLoraLinear(q, bias, adapter, weight.numel(), double_quantization)
 
+    @staticmethod
+    def new(in_features: int, out_features: int, config: LoraConfig, double_quantization: bool,
+            device, generator=None) -> "QLoraLinear":
+        """A fresh quantized and adapted layer with a bias (src/quantize.rs:678-690): the base is
+        initialised as Burn's ``LinearConfig`` does, uniform in ``+-1/sqrt(in_features)``."""
+        bound = 1.0 / math.sqrt(in_features)
+        w = (torch.rand(in_features, out_features, device=device, generator=generator) * 2 - 1) * bound
+        b = (torch.rand(out_features, device=device, generator=generator) * 2 - 1) * bound
+        return QLoraLinear.from_linear(w, b, config, double_quantization, generator=generator)
+
     def adapter(self) -> LoraAdapter:
         return self._adapter
 
+    def packed(self) -> PackedNf4Tensor:
+        """The frozen weight in packed form; quantizing a weight that is already on the NF4 grid
+        (with the scales it was dequantized with) gives back its codes, so this is exact."""
+        if self._packed is None:
+            self._packed = PackedNf4Tensor.quantize(self.weight)
+        return self._packed
+
     def base_forward(self, x: torch.Tensor) -> torch.Tensor:
-        packed = PackedNf4Tensor.quantize(self.weight)  # exact: the weight is on the grid
-        return linear_forward(x, packed, self.weight.shape[0], self.weight.shape[1], LAYOUT_IN_OUT,
+        return linear_forward(x, self.packed(), self.weight.shape[0], self.weight.shape[1], LAYOUT_IN_OUT,
                               bias=self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """``base(x) + adapter(x)`` (src/quantize.rs:692-694) in one fused call."""
-        packed = PackedNf4Tensor.quantize(self.weight)
-        return linear_forward(x, packed, self.weight.shape[0], self.weight.shape[1], LAYOUT_IN_OUT,
+        return linear_forward(x, self.packed(), self.weight.shape[0], self.weight.shape[1], LAYOUT_IN_OUT,
                               bias=self.bias, lora_a=self._adapter.a(), lora_b=self._adapter.b(),
                               lora_scale=self._adapter.scaling())
 
@@ -464,5 +512,7 @@ class QLoraLinear:
         return 4.0 * self.quantized_values + scale_bits, 32.0 * self.quantized_values
 
     def merged(self) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-        """``W + dW`` as a plain ``[in, out]`` weight and the bias (src/quantize.rs:717-726)."""
-        return self.weight + self._adapter.delta_weight().to(self.weight.dtype), self.bias
+        """``W + dW`` as a plain ``[in, out]`` f32 weight and the bias (src/quantize.rs:717-726)."""
+        w = qlora_merge(self.packed(), self.weight.shape[0], self.weight.shape[1], self._adapter.a(),
+                        self._adapter.b(), self._adapter.scaling(), LAYOUT_IN_OUT)
+        return w, self.bias

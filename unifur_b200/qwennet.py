@@ -105,23 +105,36 @@ class QloraLinear:
         ``grad_x = grad_y . W + s (grad_y . B) . A`` is one more NF4 linear over the SAME packed
         bytes read in the other orientation (a ``[d_out, d_in]`` weight is a ``[d_in', d_out']``
         weight with ``d_in' = d_out``), with the adapter factors swapping roles; the two adapter
-        gradients are small dense products."""
-        d_in, d_out, s = self.base.d_input(), self.base.d_output(), self.scaling
-        x2 = x.reshape(-1, d_in)
-        g2 = grad_y.reshape(-1, d_out)
-        if self.base.layout == LAYOUT_OUT_IN:
-            # forward: y = x W^T + s (x A^T) B^T with W [d_out, d_in], A [r, d_in], B [d_out, r]
-            gx = linear_forward(g2, self.base.packed(), d_out, d_in, LAYOUT_IN_OUT,
-                                lora_a=self.lora_b, lora_b=self.lora_a, lora_scale=s)
-            gb_t = g2.float().t() @ (x2.float() @ self.lora_a.float().t())   # [d_out, r]
-            ga_t = (g2.float() @ self.lora_b.float()).t() @ x2.float()       # [r, d_in]
-            ga, gb = s * ga_t, s * gb_t
-        else:
-            # forward: y = x W + s (x A) B with W [d_in, d_out], A [d_in, r], B [r, d_out]
-            gx = linear_forward(g2, self.base.packed(), d_out, d_in, LAYOUT_OUT_IN,
-                                lora_a=self.lora_b, lora_b=self.lora_a, lora_scale=s)
-            ga = s * (x2.float().t() @ (g2.float() @ self.lora_b.float().t()))   # [d_in, r]
-            gb = s * ((x2.float() @ self.lora_a.float()).t() @ g2.float())       # [r, d_out]
+        gradients are small dense products.  All of it runs in ``nf4_qlora_backward_dev``."""
+        lib = _lib.load()
+        d_in, d_out = self.base.d_input(), self.base.d_output()
+        x2 = x.reshape(-1, d_in).contiguous()
+        g2 = grad_y.reshape(-1, d_out).to(x2.dtype).contiguous()
+        rows, dev = x2.shape[0], x2.device
+        la, lb = self.lora_a.to(x2.dtype).contiguous(), self.lora_b.to(x2.dtype).contiguous()
+        rank = la.shape[0] if self.base.layout == LAYOUT_OUT_IN else la.shape[1]
+        gx = torch.empty(rows, d_in, dtype=x2.dtype, device=dev)
+        ga, gb = torch.empty_like(la), torch.empty_like(lb)
+        ws = torch.zeros(max(int(lib.nf4_qlora_backward_workspace_bytes(rows, d_in, d_out, rank)), 256),
+                         dtype=torch.uint8, device=dev)
+        pk = self.base.packed()
+        dq = pk.is_double_quantized()
+        a = _lib.LinearArgs()
+        a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+        a.layout = self.base.layout
+        a.io_dtype = _lib.DTYPE_BF16 if x2.dtype == torch.bfloat16 else _lib.DTYPE_F32
+        a.rows, a.d_in, a.d_out = rows, d_in, d_out
+        a.x, a.packed = x2.data_ptr(), pk.codes.data_ptr()
+        a.absmax = None if dq else pk.absmax.data_ptr()
+        a.scale_codes = pk.scale_codes.data_ptr() if dq else None
+        a.scale_of_scales = pk.scale_of_scales.data_ptr() if dq else None
+        a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb.data_ptr(), rank, self.scaling
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        vp = ctypes.c_void_p
+        with torch.cuda.device(dev):
+            _lib.check(lib.nf4_qlora_backward_dev(
+                ctypes.byref(a), vp(g2.data_ptr()), vp(gx.data_ptr()), vp(ga.data_ptr()), vp(gb.data_ptr()),
+                vp(torch.cuda.current_stream(dev).cuda_stream)))
         return gx.reshape(x.shape), ga.to(self.lora_a.dtype), gb.to(self.lora_b.dtype)
 
     def resident_bytes(self) -> int:
@@ -131,8 +144,8 @@ class QloraLinear:
 
 
 def with_lora(base: Nf4Linear, rank: int, alpha: float, generator=None) -> QloraLinear:
-    """``QwenLinear::with_lora`` (src/qwennet.rs:419-434): attach a fresh zero-B adapter.
-    Rank 0 and non-finite alpha are refused as ``QwenLoraConfig::validate`` does."""
+    """``QwenLinear::with_lora`` (src/qwennet.rs:419-434) on an NF4-resident base: attach a fresh
+    zero-B adapter.  Rank 0 and non-finite alpha are refused as ``QwenLoraConfig::validate`` does."""
     if rank < 1:
         raise ValueError("LoRA rank must be at least 1")
     if not (alpha == alpha and abs(alpha) != float("inf")):
@@ -140,6 +153,75 @@ def with_lora(base: Nf4Linear, rank: int, alpha: float, generator=None) -> Qlora
     cfg = LoraConfig.new(base.d_input(), base.d_output(), rank).with_alpha(alpha)
     return QloraLinear.with_adapter(base, LoraAdapter.new(cfg, base.packed().codes.device,
                                                          generator=generator))
+
+
+class QwenLinearError(RuntimeError):
+    """The ``anyhow`` errors of ``QwenLinear::to_nf4`` / ``with_lora`` (src/qwennet.rs:378-435)."""
+
+
+class QwenLinear:
+    """Residency switch of one projection (src/qwennet.rs:305-435): an f32 weight, an NF4-resident
+    weight, or an NF4-resident weight with an adapter.  ``forward`` gives the same function in all
+    three; only the memory differs."""
+
+    F32, NF4, QLORA = "F32", "Nf4", "Qlora"
+
+    def __init__(self, kind: str, inner, bias: Optional[torch.Tensor] = None):
+        self.kind, self.inner, self._f32_bias = kind, inner, bias
+
+    @staticmethod
+    def f32(weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> "QwenLinear":
+        """``weight [d_input, d_output]`` f32, as Burn's ``Linear`` stores it."""
+        return QwenLinear(QwenLinear.F32, weight, bias)
+
+    @staticmethod
+    def nf4(linear: Nf4Linear) -> "QwenLinear":
+        return QwenLinear(QwenLinear.NF4, linear)
+
+    @staticmethod
+    def qlora(linear: QloraLinear) -> "QwenLinear":
+        return QwenLinear(QwenLinear.QLORA, linear)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.kind == QwenLinear.F32:
+            # the f32 variant is Burn's own Linear, outside the NF4 path: plain framework matmul
+            y = x.to(self.inner.dtype) @ self.inner
+            return (y + self._f32_bias if self._f32_bias is not None else y).to(x.dtype)
+        return self.inner.forward(x)
+
+    def resident_bytes(self) -> int:
+        """src/qwennet.rs:356-368."""
+        if self.kind == QwenLinear.F32:
+            return 4 * self.inner.numel()
+        return self.inner.resident_bytes()
+
+    def to_nf4(self) -> "QwenLinear":
+        """Quantize an f32 weight into NF4 residency (src/qwennet.rs:378-413).  The in-memory
+        weight is already ``[d_input, d_output]`` and is NOT transposed; a bias keeps its
+        identity; an NF4 weight is returned as it is; a weight carrying an adapter is an error."""
+        if self.kind == QwenLinear.F32:
+            d_in, d_out = self.inner.shape
+            if self.inner.numel() != d_in * d_out:
+                raise QwenLinearError(f"weight of shape [{d_in}, {d_out}] carries {self.inner.numel()} values")
+            lin = Nf4Linear.from_values(self.inner.contiguous().view(-1).float(), d_in, d_out)
+            lin.bias = self._f32_bias  # the same tensor object: its identity is kept
+            return QwenLinear.nf4(lin)
+        if self.kind == QwenLinear.NF4:
+            return self
+        raise QwenLinearError("a weight carrying an adapter must be de-adapted before conversion")
+
+    def with_lora(self, rank: int, alpha: float, generator=None) -> "QwenLinear":
+        """Attach a fresh, exactly no-op adapter to an NF4-resident base (src/qwennet.rs:419-434);
+        attaching to an f32 weight or twice is an error."""
+        if rank < 1:
+            raise QwenLinearError("LoRA rank must be at least 1")
+        if not (alpha == alpha and abs(alpha) != float("inf")):
+            raise QwenLinearError("LoRA alpha must be finite")
+        if self.kind == QwenLinear.NF4:
+            return QwenLinear.qlora(with_lora(self.inner, rank, alpha, generator))
+        if self.kind == QwenLinear.F32:
+            raise QwenLinearError("LoRA adapters attach to NF4-resident weights only")
+        raise QwenLinearError("weight already carries a LoRA adapter")
 
 
 class Nf4Embedding:

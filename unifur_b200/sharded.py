@@ -125,3 +125,84 @@ class ShardedNf4Linear:
         lead = y_local.shape[:-1]
         y = gather_columns(y_local.reshape(-1, y_local.shape[-1]), self.shards, self.group)
         return y.view(*lead, self.d_out)
+
+    def plan(self, x: torch.Tensor) -> "ShardedForwardPlan":
+        """Buffers and the argument block for repeated forwards of ``x``'s shape and storage: the
+        serving loop's form of ``forward`` (nothing is allocated per call, so the calls can be
+        captured in a CUDA graph)."""
+        return ShardedForwardPlan(self, x)
+
+
+class ShardedForwardPlan:
+    """``ShardedNf4Linear.forward`` with everything allocated once: the local slab, the workspace,
+    the gather buffer and the full output.  ``run()`` enqueues the local forward on the current
+    stream, the all-gather of the slabs and the permuting copy into ``y [rows, d_out]``."""
+
+    def __init__(self, lin: ShardedNf4Linear, x: torch.Tensor):
+        import ctypes
+
+        from . import _lib
+
+        if x.dtype != torch.bfloat16 or not x.is_contiguous() or x.dim() != 2:
+            raise ValueError("ShardedForwardPlan: x must be a contiguous bf16 [rows, d_in] tensor")
+        self.lin, self.x = lin, x
+        self.lib = _lib.load()
+        self._check = _lib.check
+        rows, dev = x.shape[0], x.device
+        world = dist.get_world_size(lin.group)
+        a, b = lin.shards[lin.rank]
+        widths = [e - s for s, e in lin.shards]
+        self.wmax, self.world, self.rows = max(widths), world, rows
+        self.equal = all(w == self.wmax for w in widths)
+        # the local slab is written straight into a [rows, wmax] send buffer (ldy = wmax)
+        self.send = torch.zeros(rows, self.wmax, dtype=torch.bfloat16, device=dev)
+        self.flat = torch.empty(world * rows, self.wmax, dtype=torch.bfloat16, device=dev)
+        self.y = torch.empty(rows, lin.d_out, dtype=torch.bfloat16, device=dev)
+        rank = lin.lora_a.shape[0] if lin.lora_a is not None else 0
+        ws_bytes = int(self.lib.nf4_linear_workspace_bytes(rows, lin.d_in, b - a, rank))
+        self.ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        self.bias32 = lin.bias.to(torch.float32).contiguous() if lin.bias is not None else None
+        self.la = lin.lora_a.to(torch.bfloat16).contiguous() if rank else None
+        self.lb = lin.lora_b.to(torch.bfloat16).contiguous() if rank else None
+        pk = lin.packed
+        dq = pk.is_double_quantized()
+        args = _lib.LinearArgs()
+        args.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+        args.layout, args.io_dtype = LAYOUT_OUT_IN, _lib.DTYPE_BF16
+        args.rows, args.d_in, args.d_out = rows, lin.d_in, b - a
+        args.x, args.packed = x.data_ptr(), pk.codes.data_ptr()
+        args.absmax = None if dq else pk.absmax.data_ptr()
+        args.scale_codes = pk.scale_codes.data_ptr() if dq else None
+        args.scale_of_scales = pk.scale_of_scales.data_ptr() if dq else None
+        args.bias = self.bias32.data_ptr() if self.bias32 is not None else None
+        args.lora_a = self.la.data_ptr() if rank else None
+        args.lora_b = self.lb.data_ptr() if rank else None
+        args.lora_rank, args.lora_scale = rank, float(lin.lora_scale)
+        args.y, args.ldy = self.send.data_ptr(), self.wmax
+        args.workspace, args.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+        self.args = args
+        self._byref = ctypes.byref(args)
+        self._vp = ctypes.c_void_p
+        self.empty_local = b == a
+
+    def run_local(self) -> torch.Tensor:
+        """The local slab only (no exchange); returns the [rows, wmax] send buffer."""
+        if not self.empty_local:
+            stream = self._vp(torch.cuda.current_stream(self.x.device).cuda_stream)
+            self._check(self.lib.nf4_linear_forward_dev(self._byref, stream))
+        return self.send
+
+    def gather(self) -> torch.Tensor:
+        """All-gather of the slabs and the permuting copy into ``y [rows, d_out]``."""
+        dist.all_gather_into_tensor(self.flat, self.send, group=self.lin.group)
+        stacked = self.flat.view(self.world, self.rows, self.wmax)
+        if self.equal:
+            self.y.view(self.rows, self.world, self.wmax).copy_(stacked.permute(1, 0, 2))
+        else:
+            for r, (a, b) in enumerate(self.lin.shards):
+                self.y[:, a:b] = stacked[r, :, : b - a]
+        return self.y
+
+    def run(self) -> torch.Tensor:
+        self.run_local()
+        return self.gather()
