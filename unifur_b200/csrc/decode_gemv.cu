@@ -373,29 +373,28 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const int ex = (int)(mx >> 7);  // biased exponent: 127 is 2^0, 255 is infinity
             const bool odd = mx != 0u && ex != 255 && (ex > 142 || ex < 120);
-            float down = 1.0f;
-            if (__any_sync(0xffffffffu, odd)) {
+            if (__any_sync(0xffffffffu, odd)) {  // rare: the whole warp takes the scaling conversion
                 int k = odd ? ex - 141 : 0;  // the largest magnitude goes to [2^14, 2^15)
                 k = max(k, -100);
-                down = __int_as_float((127 - k) << 23);
+                const float down = __int_as_float((127 - k) << 23);
                 row_scale = __int_as_float((127 + k) << 23);
                 rescaled = true;
-            }
-            #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                const uint32_t w[8] = {xraw[cc][0].x, xraw[cc][0].y, xraw[cc][0].z, xraw[cc][0].w,
-                                       xraw[cc][1].x, xraw[cc][1].y, xraw[cc][1].z, xraw[cc][1].w};
                 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (down == 1.0f) {
-                        xf[u][half * 4 + cc][j][0] = bf16x2_to_f16x2(w[2 * j]);
-                        xf[u][half * 4 + cc][j][1] = bf16x2_to_f16x2(w[2 * j + 1]);
-                    } else {
-                        xf[u][half * 4 + cc][j][0] = pack_f16x2(bf16_bits_to_float(w[2 * j] & 0xffffu) * down,
-                                                                __uint_as_float(w[2 * j] & 0xffff0000u) * down);
-                        xf[u][half * 4 + cc][j][1] = pack_f16x2(bf16_bits_to_float(w[2 * j + 1] & 0xffffu) * down,
-                                                                __uint_as_float(w[2 * j + 1] & 0xffff0000u) * down);
-                    }
+                for (int cc = 0; cc < 4; ++cc) {
+                    const uint32_t w[8] = {xraw[cc][0].x, xraw[cc][0].y, xraw[cc][0].z, xraw[cc][0].w,
+                                           xraw[cc][1].x, xraw[cc][1].y, xraw[cc][1].z, xraw[cc][1].w};
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        xf[u][half * 4 + cc][i >> 1][i & 1] =
+                            pack_f16x2(bf16_bits_to_float(w[i] & 0xffffu) * down, __uint_as_float(w[i] & 0xffff0000u) * down);
+                }
+            } else {
+                #pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const uint32_t w[8] = {xraw[cc][0].x, xraw[cc][0].y, xraw[cc][0].z, xraw[cc][0].w,
+                                           xraw[cc][1].x, xraw[cc][1].y, xraw[cc][1].z, xraw[cc][1].w};
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) xf[u][half * 4 + cc][i >> 1][i & 1] = bf16x2_to_f16x2(w[i]);
                 }
             }
         }
