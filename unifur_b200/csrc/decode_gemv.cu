@@ -94,8 +94,10 @@ struct Cfg {
     static constexpr uint32_t kOffCodes = kLutBytes;
     static constexpr uint32_t kOffScales = kOffCodes + kWarps * kRing * kCodesTile;
     static constexpr uint32_t kOffBars = kOffScales + kWarps * kRing * kScaleTile;
-    static constexpr uint32_t kOffRed = kOffBars + 512;              // [warps][16] f32: slices of a column of T
-    static constexpr uint32_t kOffT = kOffRed + 1024;
+    // [warps][2][8][8] f32: a producer's slices of a unit of T (8 KB).  The upper half is where T
+    // itself arrives later, asked for by warp 0, which is among the readers of the slices.
+    static constexpr uint32_t kOffRed = kOffBars + 512;
+    static constexpr uint32_t kOffT = kOffRed + 4096;
     static constexpr uint32_t kTBytes = 16 * kMaxRank * 4;
     static constexpr uint32_t kOffDq = kOffT + kTBytes;
     static constexpr uint32_t kOffPark = kOffDq + 1024;              // [warps][kParkSlots][32 lanes] float4
@@ -112,16 +114,18 @@ struct DecodeParams {
     const float *bias;
     float *t_global;       // [halves][M][rank] f32 = x A^T, written by the producer CTAs (workspace)
     uint32_t *flags;       // [0] producers that have published, [1] CTAs that have read T
-    uint32_t n_prod;       // CTAs that compute T (each takes the units cta, cta + n_prod, ...)
+    uint32_t n_prod;       // CTAs that compute T (each takes the units cta, cta + n_prod, ...; a unit is 8 columns)
     const __nv_bfloat16 *lora_a;
     const __nv_bfloat16 *lora_b;
     void *y;
     uint64_t ldy;
     uint32_t y_f32;
+    uint32_t y_pair;       // bf16 y whose even columns are 4-byte aligned in every row
     uint32_t M, K, N, rank;
     float lora_scale;
-    // CTA c owns rows_base (+ gran if c < rows_extra) rows; ranges start on multiples of gran
-    uint32_t gran, rows_base, rows_extra;
+    // CTA c owns rows_base rows, and gran more if light_front <= c < light_front + rows_extra;
+    // ranges start on multiples of gran
+    uint32_t gran, rows_base, rows_extra, light_front;
     uint32_t kw;          // K-slices of 256
     uint32_t kwarps;      // warps along K
     uint32_t rw_shift;    // 1 << rw_shift groups of warps take different tiles (kwarps << rw_shift <= warps)
@@ -201,9 +205,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     constexpr uint32_t kParkWarp = kParkSlots * 128;                // floats per warp
 
     // rows owned by this CTA
-    const uint32_t extra = min(blockIdx.x, p.rows_extra);
-    const uint32_t n0 = blockIdx.x * p.rows_base + extra * p.gran;
-    const uint32_t n1 = n0 + p.rows_base + (blockIdx.x < p.rows_extra ? p.gran : 0u);
+    const uint32_t past = blockIdx.x > p.light_front ? blockIdx.x - p.light_front : 0u;
+    const uint32_t n0 = blockIdx.x * p.rows_base + min(past, p.rows_extra) * p.gran;
+    const uint32_t n1 = n0 + p.rows_base +
+                        (blockIdx.x >= p.light_front && past < p.rows_extra ? p.gran : 0u);
     const uint32_t ntiles = (n1 - n0 + kTileRows - 1) / kTileRows;
 
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -281,14 +286,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     }
     uint32_t req_j = my_tiles < (uint32_t)kRing ? my_tiles : (uint32_t)kRing;  // tiles requested so far
 
-    // ---- a producer CTA's unit of T: row j of the adapter factor A against the warps' K-slice
-    // number h (unit = j * SL + h).  The lane loads its sixteen consecutive k of each 64-block,
-    // the same k it holds of x. ----
+    // ---- a producer CTA's unit of T: eight rows of the adapter factor A (row 8 * j8 + g in the
+    // lanes of group g) against the warps' K-slice number h (unit = j8 * SL + h).  The lane loads
+    // its sixteen consecutive k of each 64-block, the same k it holds of x, so that A's rows and
+    // x's rows are the two operands of a bf16 MMA with the same order of k. ----
     const bool producer = p.rank != 0 && blockIdx.x < p.n_prod;
     const bool t_warp = producer && active && rg == 0;
     uint4 araw[kSliceChunks][2];
     auto load_a = [&](uint32_t unit) {
-        const uint32_t j = unit / SL, h = unit % SL;
+        const uint32_t j = (unit / SL) * 8u + g, h = unit % SL;
         #pragma unroll
         for (int c = 0; c < kSliceChunks; ++c) {
             araw[c][0] = araw[c][1] = make_uint4(0, 0, 0, 0);
@@ -307,9 +313,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
 
-    // sum over this lane's 64 k of one K-slice: x[m][k] * A[j][k], both raw bf16, f32 products
-    auto dot_slice = [&](const uint4 (&xr)[4][2]) -> float {
-        float part = 0.0f;
+    // One K-slice of T^T = A x^T for the unit's eight rows of A and eight rows of x (raw bf16,
+    // exact products, f32 sums): the lane gets T[m][j] for j = 8 * j8 + g, m = 8u + 2t and + 1.
+    auto dot_slice = [&](const uint4 (&xr)[4][2]) -> float2 {
+        float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         #pragma unroll
         for (int c = 0; c < kSliceChunks; ++c) {
             const uint32_t aw[8] = {araw[c][0].x, araw[c][0].y, araw[c][0].z, araw[c][0].w,
@@ -317,12 +324,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             const uint32_t xw[8] = {xr[c][0].x, xr[c][0].y, xr[c][0].z, xr[c][0].w,
                                     xr[c][1].x, xr[c][1].y, xr[c][1].z, xr[c][1].w};
             #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                part = fmaf(bf16_bits_to_float(xw[i] & 0xffffu), bf16_bits_to_float(aw[i] & 0xffffu), part);
-                part = fmaf(__uint_as_float(xw[i] & 0xffff0000u), __uint_as_float(aw[i] & 0xffff0000u), part);
-            }
+            for (int j = 0; j < 4; ++j)
+                ptx::mma_16816_bf16(d, aw[2 * j], 0u, aw[2 * j + 1], 0u, xw[2 * j], xw[2 * j + 1]);
         }
-        return part;
+        return make_float2(d[0], d[1]);
     };
     // this warp's K-slice `half` of x row m, raw: the lane's sixteen consecutive k of each 64-block
     auto load_x = [&](uint4 (&xr)[4][2], uint32_t m, uint32_t half) {
@@ -344,18 +349,23 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     // divides that slice by the power of two that brings the largest magnitude to [2^14, 2^15)
     // and multiplies the row's partial sums back when it parks them (both exact).
     uint32_t xf[NT][NC][4][2];  // this warp's slices of x as f16 B-fragments
-    float tpart[NT];            // a producer's first unit of T: this lane's part
+    float2 tpart[NT];           // a producer's first unit of T: this lane's part
     float col_scale[NT][2];     // factors of this lane's accumulator columns (activation rows 2t, 2t + 1)
     bool rescaled = false;      // some row of this warp's slice was divided (warp-uniform)
     const uint32_t h_first = blockIdx.x % SL;
+    uint4 xraw_all[NT][SL][4][2];  // every row's loads leave before the first is looked at
     #pragma unroll
     for (int u = 0; u < NT; ++u) {
-        tpart[u] = 0.0f;
+        #pragma unroll
+        for (int half = 0; half < SL; ++half) load_x(xraw_all[u][half], 8 * u + g, half);
+    }
+    #pragma unroll
+    for (int u = 0; u < NT; ++u) {
+        tpart[u] = make_float2(0.0f, 0.0f);
         float row_scale = 1.0f;
         #pragma unroll
         for (int half = 0; half < SL; ++half) {
-            uint4 xraw[4][2];
-            load_x(xraw, 8 * u + g, half);
+            const uint4 (&xraw)[4][2] = xraw_all[u][half];
             if (producer && (uint32_t)half == h_first) tpart[u] = dot_slice(xraw);
             // the row's largest magnitude in this slice, as bf16 pairs (NaNs are left out)
             __nv_bfloat162 mx2 = __float2bfloat162_rn(0.0f);
@@ -404,12 +414,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     }
 
     if (producer) {
-        // Unit (j, h) of T: every warp's K-slice h of sum_k x[m][k] A[j][k]; the slices meet in
-        // shared memory, warp 0 adds them in order and writes column j of half h.  The first
-        // unit was multiplied while x passed through the registers; a CTA that has more units
-        // (fewer CTAs than units: short matrices) reads x again for them.
-        for (uint32_t unit = blockIdx.x; unit < p.rank * SL; unit += p.n_prod) {
-            const uint32_t j = unit / SL, h = unit % SL;
+        // Unit (j8, h) of T: every warp's K-slice h of sum_k x[m][k] A[j][k] for eight j; the
+        // slices meet in shared memory, where the first warps add them in a fixed order (one
+        // output per thread) and write the unit's columns of half h.  The first unit was
+        // multiplied while x passed through the registers; a CTA that has more units (fewer CTAs
+        // than units: short matrices) reads x again for them.
+        constexpr uint32_t kOut = 64 * NT;  // (u, j, m) outputs of a unit
+        for (uint32_t unit = blockIdx.x; unit < (p.rank >> 3) * SL; unit += p.n_prod) {
+            const uint32_t j8 = unit / SL, h = unit % SL;
             if (unit != blockIdx.x) {
                 __syncthreads();  // the slices of the unit before have been read
                 load_a(unit);
@@ -421,23 +433,25 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                 }
             }
             #pragma unroll
-            for (int u = 0; u < NT; ++u) {
-                float part = tpart[u];
-                part += __shfl_xor_sync(0xffffffffu, part, 1);
-                part += __shfl_xor_sync(0xffffffffu, part, 2);
-                if (t == 0) red_s[warp * 16 + 8 * u + g] = t_warp ? part : 0.0f;
-            }
+            for (int u = 0; u < NT; ++u)
+                *reinterpret_cast<float2 *>(red_s + warp * kOut + (u * 8 + g) * 8 + 2 * t) =
+                    t_warp ? tpart[u] : make_float2(0.0f, 0.0f);
             __syncthreads();
-            if (warp == 0 && lane < p.M) {
+            if (tid < kOut) {
                 float v = 0.0f;
-                for (uint32_t w = 0; w < (uint32_t)kWarps; ++w) v += red_s[w * 16 + lane];
-                p.t_global[((size_t)h * p.M + lane) * p.rank + j] = v;
+                #pragma unroll
+                for (uint32_t w = 0; w < (uint32_t)kWarps; ++w) v += red_s[w * kOut + tid];
+                const uint32_t m = (tid >> 6) * 8u + (tid & 7u), j = j8 * 8u + ((tid >> 3) & 7u);
+                if (m < p.M) p.t_global[((size_t)h * p.M + m) * p.rank + j] = v;
             }
         }
-        if (warp == 0) {
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) atomicAdd(p.flags, 1u);
+        if (tid < kOut) {
+            // the writers meet (a barrier of their own), then one of them publishes
+            asm volatile("bar.sync 1, %0;" ::"n"(kOut) : "memory");
+            if (tid == 0) {
+                __threadfence();
+                atomicAdd(p.flags, 1u);
+            }
         }
     }
 
@@ -667,15 +681,28 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                 #pragma unroll
                 for (int r = 0; r < 4; ++r) v[r] = fmaf(d[r], p.lora_scale, v[r]);  // scale applied last
             }
+            // v[0], v[2]: rows 2g and 2g + 1 for activation row m0 (neighbours in y); v[1], v[3]: for m0 + 1
+            const uint32_t col = pass_row0 + row_a;
+            const bool two = row_a + 1 < pass_rows;
+            const bool pair = p.y_pair && two && (col & 1u) == 0;  // one 32-bit store for the two rows
             #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const uint32_t rr = row_a + (r >> 1), m = m0 + (r & 1u);
-                if (rr >= pass_rows || m >= p.M) continue;
-                float o = v[r];
-                if (p.bias) o += __ldg(p.bias + pass_row0 + rr);
-                const size_t at = (size_t)m * p.ldy + pass_row0 + rr;
-                if (p.y_f32) static_cast<float *>(p.y)[at] = o;
-                else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(o);
+            for (int b = 0; b < 2; ++b) {
+                if (row_a >= pass_rows || m0 + b >= p.M) continue;
+                float o0 = v[b], o1 = v[b + 2];
+                if (p.bias) {
+                    o0 += __ldg(p.bias + col);
+                    if (two) o1 += __ldg(p.bias + col + 1);
+                }
+                const size_t at = (size_t)(m0 + b) * p.ldy + col;
+                if (p.y_f32) {
+                    static_cast<float *>(p.y)[at] = o0;
+                    if (two) static_cast<float *>(p.y)[at + 1] = o1;
+                } else if (pair) {
+                    *reinterpret_cast<__nv_bfloat162 *>(static_cast<__nv_bfloat16 *>(p.y) + at) = __floats2bfloat162_rn(o0, o1);
+                } else {
+                    static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(o0);
+                    if (two) static_cast<__nv_bfloat16 *>(p.y)[at + 1] = __float2bfloat16_rn(o1);
+                }
             }
         }
         if (tile0 + p.pass_tiles < max_tiles) {
@@ -786,6 +813,11 @@ bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran
         p.warp_rg[w] = active ? (uint8_t)(w / p.kwarps) : 0xffu;
         p.warp_kpos[w] = active ? (uint8_t)(w % p.kwarps) : 0u;
     }
+    // Row ranges are whole tiles where the matrix allows it (a CTA multiplies a partial tile at
+    // the cost of a whole one).  The CTAs that get one unit less are the producers of T, which
+    // have that work on top, and then the last ones, which tend to start last.
+    if (N % kTileRows == 0 && kTileRows % gran == 0) gran = kTileRows;
+    p.gran = gran;
     const uint64_t units = N / gran;
     const uint64_t tiles = ((uint64_t)N + kTileRows - 1) / kTileRows;
     uint64_t ctas = tiles < (uint64_t)kNumSMs ? tiles : (uint64_t)kNumSMs;
@@ -803,8 +835,10 @@ bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran
         p.piece_shift = rank == 8 ? 0u : rank == 16 ? 1u : rank == 32 ? 2u : 3u;
     }
     p.pass_tiles = pt;
-    const uint32_t t_units = rank * C::kSlices;
+    const uint32_t t_units = (rank >> 3) * C::kSlices;
     p.n_prod = t_units < pl.grid ? t_units : pl.grid;
+    const uint32_t light = pl.grid - p.rows_extra;
+    p.light_front = rank ? (p.n_prod < light ? p.n_prod : light) : 0u;
     return true;
 }
 
@@ -829,7 +863,6 @@ bool plan(const nf4_linear_args &a, Plan &pl) {
     // CTA row ranges start where the CTA's LoRA-B rows are 16-byte aligned
     const uint32_t gran = rank ? 16u / gcd_u32(16u, rank * 2u) : 1u;
     if (N % gran != 0) return false;
-    p.gran = gran;
     p.nchunks = K / kChunk;
     if (!plan_shape(M, K, N, rank, gran, pl)) return false;
     p.wait_ns = 1000000000u;
@@ -842,6 +875,7 @@ bool plan(const nf4_linear_args &a, Plan &pl) {
     p.y = a.y;
     p.y_f32 = (uint32_t)a.y_f32;
     p.ldy = a.ldy ? a.ldy : a.d_out;
+    p.y_pair = (!a.y_f32 && (reinterpret_cast<uintptr_t>(a.y) & 3u) == 0 && (p.ldy & 1u) == 0) ? 1u : 0u;
     p.M = M;
     p.K = K;
     p.N = N;
