@@ -279,6 +279,16 @@ NF4_API int32_t nf4_sharded_linear_forward_dev(const nf4_linear_args *shard, voi
                                                int32_t world, void *gather_buffer, uint64_t gather_bytes,
                                                void *y_full, uint64_t ldy_full, void *stream);
 
+/* Several forwards of the same activations in one call: the projections a transformer block
+ * applies to one input (q, k, v; gate, up).  The reference calls them one after another
+ * (QwenLinear::forward per projection, src/qwennet.rs:372-383); the results are the same, bit for
+ * bit, as `count` calls of nf4_linear_forward_dev with args[0] ... args[count - 1].
+ * Where the arguments share x, rows, d_in and the form of the scales, rows <= 16 and every
+ * forward fits the decode kernel (d_in <= 4096), they run as ONE kernel launch whose CTAs are
+ * shared out in proportion to d_out; otherwise as `count` launches.  Every args[i] keeps its own
+ * y, weights, adapter and workspace (the workspaces must not overlap).  count <= 4. */
+NF4_API int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint32_t count, void *stream);
+
 /* Decode-sized forward for callers that cannot allocate or own device memory.
  * No counterpart in the reference (its forward allocates a fresh f32 weight on every call).
  *

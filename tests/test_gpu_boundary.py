@@ -275,3 +275,47 @@ def test_sharded_forward_through_the_c_abi_with_a_one_rank_communicator(oracle):
         assert L.nf4_sharded_linear_forward_dev(ctypes.byref(a), None, 0, 1, _vp(gbuf), gb, _vp(y_full), n, None) == -1
     finally:
         nccl.ncclCommDestroy(comm)
+
+
+@pytest.mark.parametrize("m,k,widths,ranks,dq", [
+    (8, 3584, (3584, 512, 512), (16, 16, 16), False),   # q | k | v of the Qwen2-7B-shaped block
+    (1, 3584, (18944, 18944), (16, 16), False),         # gate | up
+    (16, 4096, (1024, 160, 48, 2048), (64, 0, 8, 16), True),
+    (4, 2048, (320, 64), (16, 32), False),              # two groups of warps per CTA
+    (8, 18944, (512, 256), (16, 16), False),            # d_in above 4096: falls back to one launch each
+    (40, 1024, (256, 384), (8, 8), False),              # more than 16 rows: one launch each (tensor-core GEMM)
+])
+def test_grouped_forward_equals_one_call_per_projection(m, k, widths, ranks, dq):
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward, linear_forward_grouped
+
+    g = torch.Generator(device=DEV).manual_seed(500 + m + k)
+    x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
+    projections = []
+    for n, r in zip(widths, ranks):
+        w = torch.randn(n * k, device=DEV, generator=g) * 0.02
+        packed = PackedNf4Tensor.quantize(w)
+        pr = {"packed": packed.with_double_quantization() if dq else packed, "d_out": n,
+              "bias": torch.randn(n, device=DEV, generator=g) * 0.1 if n % 3 == 0 else None}
+        if r:
+            pr["lora_a"] = (torch.randn(r, k, device=DEV, generator=g) * 0.01).bfloat16()
+            pr["lora_b"] = (torch.randn(n, r, device=DEV, generator=g) * 0.01).bfloat16()
+            pr["lora_scale"] = 2.0
+        projections.append(pr)
+    lib = _lib.load()
+    before = _lib.launch_count()
+    ys = linear_forward_grouped(x, k, _lib.LAYOUT_OUT_IN, projections)
+    launches = _lib.launch_count() - before
+    torch.cuda.synchronize()
+    fits = m <= 16 and k <= 4096
+    assert launches == 1 if fits else launches >= len(widths)
+    for pr, y in zip(projections, ys):
+        one = linear_forward(x, pr["packed"], k, pr["d_out"], _lib.LAYOUT_OUT_IN, bias=pr.get("bias"),
+                             lora_a=pr.get("lora_a"), lora_b=pr.get("lora_b"), lora_scale=pr.get("lora_scale", 0.0))
+        torch.cuda.synchronize()
+        if m <= 16:
+            assert torch.equal(y, one)   # the decode kernels add in a fixed order
+        else:
+            tol = one.float().abs() * 2.0 ** -7 + 4e-6 * float(one.float().abs().max())
+            assert bool(((y.float() - one.float()).abs() <= tol).all())
+    d0, d1, d2 = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+    assert lib.nf4_device_status(ctypes.byref(d0), ctypes.byref(d1), ctypes.byref(d2)) == 0

@@ -27,7 +27,7 @@ def rel_l2(got, ref):
 
 
 def run_forward(layout, dtype, x, packed, absmax, d_in, d_out, bias=None, lora_a=None, lora_b=None,
-                scale=0.0, scale_codes=None, sos=None, y_f32=False):
+                scale=0.0, scale_codes=None, sos=None, y_f32=False, calls=1):
     L = lib()
     tdt = torch.bfloat16 if dtype == _lib.DTYPE_BF16 else torch.float32
     rows = x.shape[0]
@@ -59,7 +59,10 @@ def run_forward(layout, dtype, x, packed, absmax, d_in, d_out, bias=None, lora_a
     a.lora_rank, a.lora_scale = rank, scale
     a.y, a.ldy = y.data_ptr(), d_out
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-    _lib.check(L.nf4_linear_forward_dev(ctypes.byref(a), None))
+    for i in range(calls):  # the same arguments and workspace again: what a call leaves must serve the next
+        if i:
+            y.fill_(777.0)
+        _lib.check(L.nf4_linear_forward_dev(ctypes.byref(a), None))
     torch.cuda.synchronize()
     return y.float().cpu().numpy()
 
@@ -250,6 +253,24 @@ QWEN2_7B_BLOCK = [  # name, d_in, d_out  (configuration 5: all seven projections
     ("q", 3584, 3584), ("k", 3584, 512), ("v", 3584, 512), ("o", 3584, 3584),
     ("gate", 3584, 18944), ("up", 3584, 18944), ("down", 18944, 3584),
 ]
+
+
+@pytest.mark.parametrize("M,K,N,r,dq,bias", [
+    (1, 8192, 384, 16, False, False),     # two parts of sixteen slices
+    (8, 4352, 96, 8, True, True),         # seventeen slices: parts of nine and eight
+    (16, 18944, 512, 64, False, True),    # five parts, the last one slice shorter
+    (3, 12288, 1000, 0, False, True),     # no adapter, ragged N, three parts
+    (5, 32768, 48, 32, True, False),      # the longest K the kernel takes: eight parts
+])
+def test_decode_long_k_shared_out_between_ctas(oracle, M, K, N, r, dq, bias):
+    # d_in above 4096: groups of CTAs multiply parts of K and the last to arrive for a range of
+    # rows adds the parts' sums in a fixed order
+    c = make_case(oracle, 3000 + M + K + N, M, K, N, r, dq=dq, bias=bias)
+    y1, _ = check_out_in(oracle, c, M, K, N, 1.5)
+    # three calls on one workspace: the flag words and counters re-arm, the result is the same
+    y3 = run_forward(_lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16, c["x"], c["packed"], c["absmax"], K, N, bias=c["bias"],
+                     lora_a=c["la"], lora_b=c["lb"], scale=1.5, scale_codes=c["sc"], sos=c["sos"], calls=3)
+    assert np.array_equal(y1, y3)
 
 
 @pytest.mark.parametrize("dq", [False, True])

@@ -418,7 +418,7 @@ int32_t nf4_quantize_dequantize_dev(const float *values, uint64_t len, int32_t d
 uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                     uint32_t lora_rank) {
 
-    uint64_t need = decode_workspace_bytes(rows, lora_rank);
+    uint64_t need = decode_workspace_bytes(rows, d_in, d_out, lora_rank);
     const uint64_t b = prefill_workspace_bytes(rows, d_in, lora_rank);
     const uint64_t c = generic_workspace_bytes(rows, lora_rank);
     const uint64_t d = decode2_workspace_bytes(rows, d_in, d_out, lora_rank);
@@ -448,6 +448,29 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     }
     t_last_family = -1;
     return generic_forward(*args, s);
+}
+
+int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint32_t count, void *stream) {
+    if (!args || count == 0 || count > 4)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward_grouped_dev: count must be 1 ... 4");
+    bool together = true;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (args[i].struct_bytes != sizeof(nf4_linear_args))
+            return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward_grouped_dev: struct_bytes of element %u", i);
+        NF4_TRY(validate_linear(&args[i]));
+        together = together && decode_supported(args[i]);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (together && args[0].rows != 0) {
+        bool taken = false;
+        NF4_TRY(decode_forward_grouped(args, count, s, &taken));
+        if (taken) {
+            t_last_family = 0;
+            return NF4_OK;
+        }
+    }
+    for (uint32_t i = 0; i < count; ++i) NF4_TRY(nf4_linear_forward_dev(&args[i], stream));
+    return NF4_OK;
 }
 
 uint64_t nf4_linear_noalloc_scratch_bytes(void) { return decode_static_scratch_bytes(); }

@@ -68,7 +68,8 @@ constexpr int kTileRows = 16;
 constexpr int kChunk = 64;         // one quantization block of K
 constexpr int kSliceChunks = 4;    // blocks per K-slice
 constexpr int kSliceK = kSliceChunks * kChunk;
-constexpr int kMaxSlices = 16;     // K <= 16 * 256
+constexpr int kMaxSlices = 16;     // slices of K a CTA multiplies (its sixteen warps)
+constexpr int kMaxParts = 8;       // parts of K that CTAs share out: K <= 8 * 16 * 256
 constexpr int kMaxRank = 64;
 constexpr uint32_t kFlagBytes = 256;  // workspace: [ready, done] words, then T
 constexpr uint32_t kWin0 = 1024;   // shared-window address of dynamic shared memory
@@ -112,9 +113,17 @@ struct DecodeParams {
     const uint8_t *scale_codes;
     const float *scale_of_scales;
     const float *bias;
-    float *t_global;       // [halves][M][rank] f32 = x A^T, written by the producer CTAs (workspace)
-    uint32_t *flags;       // [0] producers that have published, [1] CTAs that have read T
-    uint32_t n_prod;       // CTAs that compute T (each takes the units cta, cta + n_prod, ...; a unit is 8 columns)
+    float *t_global;       // [part][M][rank] f32 = x A^T over the part's K, written by the producer CTAs (workspace)
+    uint32_t *flags;       // [0] producers that have published, [1] CTAs that have read T, [2...] arrival counters
+    uint32_t n_prod;       // CTAs of a K-part that compute T (each takes the units cta, cta + n_prod, ...; a unit is 8 columns)
+    uint32_t n_prod_all;   // ... of all K-parts: the count the readers of T wait for
+    // K longer than sixteen slices is split into kparts parts of part_slices slices; part i is
+    // multiplied by the CTAs i * cpp ... (i + 1) * cpp - 1, which share the rows like the CTAs of
+    // an unsplit launch do.  The parts' results meet in `partial` ([part][M][N] f32); the CTA
+    // that arrives last for a row range (a byte counter per range after the two flag words) adds
+    // them in the order of the parts and writes y.
+    uint32_t kparts, part_slices, cpp;
+    float *partial;
     const __nv_bfloat16 *lora_a;
     const __nv_bfloat16 *lora_b;
     void *y;
@@ -177,10 +186,12 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
     return v;
 }
 
-template <int NT, bool DQ>
-__global__ void __launch_bounds__(Cfg::kThreads, 1)
-decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
-              const __grid_constant__ CUtensorMap tm_scales, const DecodeParams p) {
+// One CTA's share of one forward.  `bid` of `nctas`: the CTA's number among the CTAs of this
+// forward (a launch can hold several forwards).  SPLIT: K is longer than a CTA's sixteen slices
+// and groups of CTAs multiply parts of it.  The descriptors and `p` are kernel parameters.
+template <int NT, bool DQ, bool SPLIT>
+__device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const CUtensorMap *tm_scales,
+                                            const DecodeParams &p, const uint32_t bid, const uint32_t nctas) {
     using C = Cfg;
     constexpr int kWarps = C::kWarps, kThreads = C::kThreads, SL = C::kSlices, kRing = C::kRing;
     constexpr int NC = SL * kSliceChunks;  // 64-blocks of K a warp owns
@@ -192,8 +203,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         return;
     }
     if (lane == 0) {  // the descriptors are on their way while the table is built
-        ptx::prefetch_tmap(&tm_codes);
-        if (!DQ) ptx::prefetch_tmap(&tm_scales);
+        ptx::prefetch_tmap(tm_codes);
+        if (!DQ) ptx::prefetch_tmap(tm_scales);
     }
     float *red_s = reinterpret_cast<float *>(smem + C::kOffRed);
     float *t_s = reinterpret_cast<float *>(smem + C::kOffT);     // [SL][M][rank]
@@ -204,11 +215,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     float *park_s = reinterpret_cast<float *>(smem + C::kOffPark);
     constexpr uint32_t kParkWarp = kParkSlots * 128;                // floats per warp
 
-    // rows owned by this CTA
-    const uint32_t past = blockIdx.x > p.light_front ? blockIdx.x - p.light_front : 0u;
-    const uint32_t n0 = blockIdx.x * p.rows_base + min(past, p.rows_extra) * p.gran;
-    const uint32_t n1 = n0 + p.rows_base +
-                        (blockIdx.x >= p.light_front && past < p.rows_extra ? p.gran : 0u);
+    // this CTA's part of K and, within the part's CTAs, its rows
+    const uint32_t part = SPLIT ? bid / p.cpp : 0u;
+    const uint32_t cta = bid - part * p.cpp;
+    const uint32_t part_s0 = SPLIT ? part * p.part_slices : 0u;
+    const uint32_t part_s1 = SPLIT ? min(p.kw, part_s0 + p.part_slices) : p.kw;
+    const uint32_t past = cta > p.light_front ? cta - p.light_front : 0u;
+    const uint32_t n0 = cta * p.rows_base + min(past, p.rows_extra) * p.gran;
+    const uint32_t n1 = n0 + p.rows_base + (cta >= p.light_front && past < p.rows_extra ? p.gran : 0u);
     const uint32_t ntiles = (n1 - n0 + kTileRows - 1) / kTileRows;
 
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -216,9 +230,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     const uint32_t rg = p.warp_rg[warp];        // which tiles: rg, rg + rw, ...
     const bool active = rg != 0xffu;
     const uint32_t kpos = p.warp_kpos[warp];    // which K-slices: kpos * SL ...
-    const uint32_t slice0 = kpos * SL;
-    const uint32_t nsl = active ? min((uint32_t)SL, p.kw - slice0) : 0u;  // slices this warp owns
-    const uint32_t my_tiles = (active && rg < ntiles) ? (ntiles - rg + rw - 1) >> p.rw_shift : 0u;
+    const uint32_t slice0 = part_s0 + kpos * SL;
+    const uint32_t nsl = (active && slice0 < part_s1) ? min((uint32_t)SL, part_s1 - slice0) : 0u;  // slices this warp owns
+    // (a K-warp without slices in this part -- the last part can be shorter -- has no tiles; its
+    // parking place is zeroed once, so that the sums over the K-warps need not know)
+    const uint32_t my_tiles = (nsl && rg < ntiles) ? (ntiles - rg + rw - 1) >> p.rw_shift : 0u;
     const uint32_t k0 = slice0 * kSliceK;
 
     const uint32_t bar0 = kWin0 + C::kOffBars + warp * kRing * 8u;
@@ -235,12 +251,17 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         const int32_t row0 = (int32_t)(n0 + (rg + j * rw) * kTileRows);
         const uint32_t bar = bar0 + 8 * slot;
         ptx::mbar_arrive_expect_tx(bar, DQ ? kCodesSlot : kCodesSlot + kScaleSlot);
-        ptx::tma_load_2d(codes0 + slot * C::kCodesTile + sl * kCodesSlot, &tm_codes,
+        ptx::tma_load_2d(codes0 + slot * C::kCodesTile + sl * kCodesSlot, tm_codes,
                          (int32_t)((slice0 + sl) * 128u), row0, bar);
         if (!DQ)
-            ptx::tma_load_2d(scales0 + slot * C::kScaleTile + sl * kScaleSlot, &tm_scales,
+            ptx::tma_load_2d(scales0 + slot * C::kScaleTile + sl * kScaleSlot, tm_scales,
                              (int32_t)((slice0 + sl) * 4u), row0, bar);
     };
+    if (active && nsl == 0) {
+        #pragma unroll 1
+        for (uint32_t i = lane; i < kParkSlots * 32u; i += 32)
+            reinterpret_cast<float4 *>(park_s + warp * kParkWarp)[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
     // ---- the lookup table: each byte value's entry, one copy per lane ----
     {
         // thread (byte, half) writes sixteen lanes' copies
@@ -290,7 +311,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     // lanes of group g) against the warps' K-slice number h (unit = j8 * SL + h).  The lane loads
     // its sixteen consecutive k of each 64-block, the same k it holds of x, so that A's rows and
     // x's rows are the two operands of a bf16 MMA with the same order of k. ----
-    const bool producer = p.rank != 0 && blockIdx.x < p.n_prod;
+    const bool producer = p.rank != 0 && cta < p.n_prod;
     const bool t_warp = producer && active && rg == 0;
     uint4 araw[kSliceChunks][2];
     auto load_a = [&](uint32_t unit) {
@@ -306,7 +327,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             }
         }
     };
-    if (producer) load_a(blockIdx.x);
+    if (producer) load_a(cta);
     __syncthreads();  // the table is in place
 
     // ---- from here on the kernel reads what its predecessor wrote ----
@@ -352,7 +373,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     float2 tpart[NT];           // a producer's first unit of T: this lane's part
     float col_scale[NT][2];     // factors of this lane's accumulator columns (activation rows 2t, 2t + 1)
     bool rescaled = false;      // some row of this warp's slice was divided (warp-uniform)
-    const uint32_t h_first = blockIdx.x % SL;
+    const uint32_t h_first = cta % SL;
     uint4 xraw_all[NT][SL][4][2];  // every row's loads leave before the first is looked at
     #pragma unroll
     for (int u = 0; u < NT; ++u) {
@@ -420,9 +441,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         // multiplied while x passed through the registers; a CTA that has more units (fewer CTAs
         // than units: short matrices) reads x again for them.
         constexpr uint32_t kOut = 64 * NT;  // (u, j, m) outputs of a unit
-        for (uint32_t unit = blockIdx.x; unit < (p.rank >> 3) * SL; unit += p.n_prod) {
+        for (uint32_t unit = cta; unit < (p.rank >> 3) * SL; unit += p.n_prod) {
             const uint32_t j8 = unit / SL, h = unit % SL;
-            if (unit != blockIdx.x) {
+            if (unit != cta) {
                 __syncthreads();  // the slices of the unit before have been read
                 load_a(unit);
                 #pragma unroll
@@ -442,7 +463,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
                 #pragma unroll
                 for (uint32_t w = 0; w < (uint32_t)kWarps; ++w) v += red_s[w * kOut + tid];
                 const uint32_t m = (tid >> 6) * 8u + (tid & 7u), j = j8 * 8u + ((tid >> 3) & 7u);
-                if (m < p.M) p.t_global[((size_t)h * p.M + m) * p.rank + j] = v;
+                if (m < p.M) p.t_global[((size_t)(part * SL + h) * p.M + m) * p.rank + j] = v;
             }
         }
         if (tid < kOut) {
@@ -467,9 +488,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
     };
     auto fetch_t = [&]() {
         uint32_t ok = 1;
-        if (lane == 0 && seen != p.n_prod) {
+        if (lane == 0 && seen != p.n_prod_all) {
             const uint64_t t0 = ptx::global_timer_ns();
-            while (ld_acquire_gpu(p.flags) != p.n_prod) {
+            while (ld_acquire_gpu(p.flags) != p.n_prod_all) {
                 if (ptx::global_timer_ns() - t0 > (uint64_t)p.wait_ns) {
                     ok = 0;
                     atomicExch(&g_decode_error, 6);
@@ -480,10 +501,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) lost = true;
         const uint32_t n = SL * p.M * p.rank;
+        const float *t_part = p.t_global + (size_t)part * n;  // this part's share of T
         if ((n & 3u) == 0) {
-            for (uint32_t i = lane * 4; i < n; i += 128) ptx::cp_async_16(kWin0 + C::kOffT + i * 4u, p.t_global + i);
+            for (uint32_t i = lane * 4; i < n; i += 128) ptx::cp_async_16(kWin0 + C::kOffT + i * 4u, t_part + i);
         } else {
-            for (uint32_t i = lane; i < n; i += 32) t_s[i] = __ldcg(p.t_global + i);
+            for (uint32_t i = lane; i < n; i += 32) t_s[i] = __ldcg(t_part + i);
         }
         ptx::cp_async_commit();
     };
@@ -689,6 +711,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
             for (int b = 0; b < 2; ++b) {
                 if (row_a >= pass_rows || m0 + b >= p.M) continue;
                 float o0 = v[b], o1 = v[b + 2];
+                if (SPLIT) {  // this part's share of the sums; bias and conversion come later
+                    float *dst = p.partial + ((size_t)part * p.M + m0 + b) * p.N + col;
+                    dst[0] = o0;
+                    if (two) dst[1] = o1;
+                    continue;
+                }
                 if (p.bias) {
                     o0 += __ldg(p.bias + col);
                     if (two) o1 += __ldg(p.bias + col + 1);
@@ -711,12 +739,69 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
         }
     }
     ptx::cp_async_wait<0>();
-    if (done_old == gridDim.x - 1) {
+    if (SPLIT) {
+        // The parts of K meet: the CTA that arrives last for these rows adds the parts' sums in
+        // the order of the parts (the result does not depend on who was last), adds the bias,
+        // converts and writes y, and leaves the counter at zero.
+        uint32_t *last_s = reinterpret_cast<uint32_t *>(red_s);
+        __syncthreads();  // every partial sum of this CTA has been stored
+        if (tid == 0) {
+            __threadfence();
+            const uint32_t sh = (cta & 3u) * 8u;
+            uint32_t *counter = p.flags + 2 + (cta >> 2);
+            const uint32_t old = (atomicAdd(counter, 1u << sh) >> sh) & 0xffu;
+            if (old == p.kparts - 1) atomicSub(counter, p.kparts << sh);
+            *last_s = old == p.kparts - 1 ? 1u : 0u;
+        }
+        __syncthreads();
+        if (*last_s) {
+            __threadfence();
+            const uint32_t rows = n1 - n0;
+            for (uint32_t e = tid; e < rows * p.M; e += kThreads) {
+                const uint32_t m = e / rows, col = n0 + (e - m * rows);
+                float o = 0.0f;
+                for (uint32_t q = 0; q < p.kparts; ++q) o += __ldcg(p.partial + ((size_t)q * p.M + m) * p.N + col);
+                if (p.bias) o += __ldg(p.bias + col);
+                const size_t at = (size_t)m * p.ldy + col;
+                if (p.y_f32) static_cast<float *>(p.y)[at] = o;
+                else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(o);
+            }
+        }
+    }
+    if (done_old == nctas - 1) {
         // the last CTA to have read T re-arms the flag words for the next launch
         p.flags[1] = 0;
         __threadfence();
         p.flags[0] = 0;
     }
+}
+
+template <int NT, bool DQ, bool SPLIT>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
+              const __grid_constant__ CUtensorMap tm_scales, const __grid_constant__ DecodeParams p) {
+    decode_body<NT, DQ, SPLIT>(&tm_codes, &tm_scales, p, blockIdx.x, gridDim.x);
+}
+
+// Several forwards of the same activations (projections that share their input) in one launch:
+// forward i is multiplied by the CTAs cta0[i] ... cta0[i + 1] - 1, exactly as a launch of its own
+// with that many CTAs would do it.
+constexpr int kMaxGroup = 4;
+struct GroupParams {
+    CUtensorMap tm_codes[kMaxGroup];
+    CUtensorMap tm_scales[kMaxGroup];
+    DecodeParams p[kMaxGroup];
+    uint32_t cta0[kMaxGroup + 1];
+    uint32_t count;
+};
+
+template <int NT, bool DQ>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+decode_group_kernel(const __grid_constant__ GroupParams gp) {
+    uint32_t i = 0;
+    while (i + 1 < gp.count && blockIdx.x >= gp.cta0[i + 1]) ++i;
+    decode_body<NT, DQ, false>(&gp.tm_codes[i], &gp.tm_scales[i], gp.p[i], blockIdx.x - gp.cta0[i],
+                               gp.cta0[i + 1] - gp.cta0[i]);
 }
 
 // T[m][j] = sum_k x[m][k] * A[j][k]  (x, A bf16; f32 accumulate).  One 128-thread CTA per (j, m).
@@ -799,12 +884,15 @@ struct Plan {
 };
 
 // Fills the shape-dependent fields; false when the shape does not fit.
-bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran, Plan &pl) {
+bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran, Plan &pl,
+                uint32_t max_ctas = kNumSMs) {
     using C = Cfg;
     DecodeParams &p = pl.p;
     const uint32_t nt = M > 8 ? 2u : 1u;
     p.kw = K / kSliceK;
-    p.kwarps = (p.kw + C::kSlices - 1) / C::kSlices;
+    p.kparts = (p.kw + kMaxSlices - 1) / kMaxSlices;
+    p.part_slices = (p.kw + p.kparts - 1) / p.kparts;
+    p.kwarps = (p.part_slices + C::kSlices - 1) / C::kSlices;
     p.rw_shift = 0;
     while ((p.kwarps << (p.rw_shift + 1)) <= (uint32_t)C::kWarps) ++p.rw_shift;
     const uint32_t rw = 1u << p.rw_shift;
@@ -820,9 +908,12 @@ bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran
     p.gran = gran;
     const uint64_t units = N / gran;
     const uint64_t tiles = ((uint64_t)N + kTileRows - 1) / kTileRows;
-    uint64_t ctas = tiles < (uint64_t)kNumSMs ? tiles : (uint64_t)kNumSMs;
+    const uint64_t per_part = (uint64_t)max_ctas / p.kparts;
+    if (per_part == 0) return false;
+    uint64_t ctas = tiles < per_part ? tiles : per_part;
     if (ctas > units) ctas = units;
-    pl.grid = (uint32_t)ctas;
+    p.cpp = (uint32_t)ctas;
+    pl.grid = (uint32_t)ctas * p.kparts;
     p.rows_base = (uint32_t)(units / ctas) * gran;
     p.rows_extra = (uint32_t)(units % ctas);
     // tiles per warp between two reductions: what the parking area and (with an adapter) the
@@ -836,17 +927,18 @@ bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran
     }
     p.pass_tiles = pt;
     const uint32_t t_units = (rank >> 3) * C::kSlices;
-    p.n_prod = t_units < pl.grid ? t_units : pl.grid;
-    const uint32_t light = pl.grid - p.rows_extra;
+    p.n_prod = t_units < p.cpp ? t_units : p.cpp;
+    p.n_prod_all = p.n_prod * p.kparts;
+    const uint32_t light = p.cpp - p.rows_extra;
     p.light_front = rank ? (p.n_prod < light ? p.n_prod : light) : 0u;
     return true;
 }
 
-bool plan(const nf4_linear_args &a, Plan &pl) {
+bool plan(const nf4_linear_args &a, Plan &pl, uint32_t max_ctas = kNumSMs) {
     if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
     if (a.rows == 0 || a.rows > 16) return false;
     // whole slices of four blocks: the scale rows then have a 16-byte pitch, which TMA needs
-    if (a.d_in % kSliceK != 0 || a.d_in > (uint64_t)kMaxSlices * kSliceK) return false;
+    if (a.d_in % kSliceK != 0 || a.d_in > (uint64_t)kMaxParts * kMaxSlices * kSliceK) return false;
     if (a.d_out >= (1ull << 31)) return false;
     const bool dq = a.scale_codes != nullptr;
     const uint32_t rank = a.lora_a ? a.lora_rank : 0;
@@ -864,7 +956,7 @@ bool plan(const nf4_linear_args &a, Plan &pl) {
     const uint32_t gran = rank ? 16u / gcd_u32(16u, rank * 2u) : 1u;
     if (N % gran != 0) return false;
     p.nchunks = K / kChunk;
-    if (!plan_shape(M, K, N, rank, gran, pl)) return false;
+    if (!plan_shape(M, K, N, rank, gran, pl, max_ctas)) return false;
     p.wait_ns = 1000000000u;
     p.x = static_cast<const __nv_bfloat16 *>(a.x);
     p.scale_codes = a.scale_codes;
@@ -884,31 +976,50 @@ bool plan(const nf4_linear_args &a, Plan &pl) {
     return true;
 }
 
-template <int NT, bool DQ>
-int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
+template <int NT, bool DQ, bool SPLIT>
+int32_t launch_as(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
     using C = Cfg;
-    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(decode_kernel<NT, DQ>), (int)C::kSmemBytes));
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(decode_kernel<NT, DQ, SPLIT>), (int)C::kSmemBytes));
     count_launch();
-    return launch_maybe_overlapped(decode_kernel<NT, DQ>, dim3(pl.grid), dim3(C::kThreads),
+    return launch_maybe_overlapped(decode_kernel<NT, DQ, SPLIT>, dim3(pl.grid), dim3(C::kThreads),
                                    C::kSmemBytes, stream, true, mc, ms, pl.p);
 }
 
-// `scratch`: kFlagBytes of flag words (zero at first use, left zero) followed by room for T
-int32_t run(const nf4_linear_args &a, Plan &pl, void *scratch, cudaStream_t stream) {
+template <int NT, bool DQ>
+int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
+    return pl.p.kparts > 1 ? launch_as<NT, DQ, true>(mc, ms, pl, stream) : launch_as<NT, DQ, false>(mc, ms, pl, stream);
+}
+
+// bytes of T in the workspace: a share per part of K (room for two where K is not split)
+uint64_t t_bytes(uint64_t rows, uint32_t rank, uint32_t kparts) {
+    return ((kparts > 2 ? kparts : 2u) * rows * rank * 4 + 255) / 256 * 256;
+}
+
+// `scratch`: kFlagBytes of flag words and counters (zero at first use, left zero), room for T,
+// and, where K is split, for the parts' sums
+int32_t prepare(const nf4_linear_args &a, Plan &pl, void *scratch, CUtensorMap &mc, CUtensorMap &ms) {
     DecodeParams &p = pl.p;
     const bool dq = a.scale_codes != nullptr;
-    if (p.rank) {
-        if (!scratch) return fail(NF4_ERR_INVALID_ARG, "decode_forward: an adapter needs the workspace");
+    if (p.rank || p.kparts > 1) {
+        if (!scratch) return fail(NF4_ERR_INVALID_ARG, "decode_forward: this shape needs the workspace");
         p.flags = static_cast<uint32_t *>(scratch);
         p.t_global = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + kFlagBytes);
+        p.partial = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + kFlagBytes + t_bytes(p.M, p.rank, p.kparts));
     }
-    CUtensorMap mc, ms;
     NF4_TRY(make_map(&mc, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.packed, p.N, p.K / 2, p.K / 2, kTileRows, 128,
                      CU_TENSOR_MAP_SWIZZLE_128B));
     if (dq) ms = mc;  // not used by the kernel
     else
         NF4_TRY(make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.absmax, p.N, p.nchunks,
                          (uint64_t)p.nchunks * 4, kTileRows, 4, CU_TENSOR_MAP_SWIZZLE_NONE));
+    return NF4_OK;
+}
+
+int32_t run(const nf4_linear_args &a, Plan &pl, void *scratch, cudaStream_t stream) {
+    CUtensorMap mc, ms;
+    NF4_TRY(prepare(a, pl, scratch, mc, ms));
+    const DecodeParams &p = pl.p;
+    const bool dq = a.scale_codes != nullptr;
     if (p.M <= 8) return dq ? launch<1, true>(mc, ms, pl, stream) : launch<1, false>(mc, ms, pl, stream);
     return dq ? launch<2, true>(mc, ms, pl, stream) : launch<2, false>(mc, ms, pl, stream);
 }
@@ -920,9 +1031,15 @@ bool decode_supported(const nf4_linear_args &a) {
     return plan(a, pl);
 }
 
-uint64_t decode_workspace_bytes(uint64_t rows, uint32_t lora_rank) {
-    if (rows == 0 || rows > 16 || lora_rank == 0) return 0;
-    return kFlagBytes + (2 * rows * lora_rank * 4 + 255) / 256 * 256;  // T, in two K-halves at most
+uint64_t decode_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
+    if (rows == 0 || rows > 16) return 0;
+    const uint64_t kw = d_in / kSliceK;
+    const uint32_t kparts = (uint32_t)((kw + kMaxSlices - 1) / kMaxSlices);
+    const bool split = d_in % kSliceK == 0 && kparts > 1 && kparts <= (uint32_t)kMaxParts;
+    if (lora_rank == 0 && !split) return 0;
+    uint64_t need = kFlagBytes + t_bytes(rows, lora_rank, split ? kparts : 1u);
+    if (split) need += (uint64_t)kparts * rows * d_out * 4;  // the parts' sums
+    return need;
 }
 
 // `chained` launches the pre-pass as a programmatic dependent of the kernel ahead of it; the
@@ -933,6 +1050,67 @@ int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, ui
     return launch_maybe_overlapped(lora_t_kernel, dim3(rank, rows), dim3(128), 0, stream, chained,
                                    static_cast<const __nv_bfloat16 *>(x),
                                    static_cast<const __nv_bfloat16 *>(a), K, rank, t_out);
+}
+
+template <int NT, bool DQ>
+int32_t launch_group(const GroupParams &gp, cudaStream_t stream) {
+    using C = Cfg;
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(decode_group_kernel<NT, DQ>), (int)C::kSmemBytes));
+    count_launch();
+    return launch_maybe_overlapped(decode_group_kernel<NT, DQ>, dim3(gp.cta0[gp.count]), dim3(C::kThreads),
+                                   C::kSmemBytes, stream, true, gp);
+}
+
+// Forwards that share x, rows, d_in and the scale form, as one launch; false (nothing launched,
+// no error) when they do not fit together and the caller should launch them one by one.
+int32_t decode_forward_grouped(const nf4_linear_args *a, uint32_t count, cudaStream_t stream, bool *taken) {
+    *taken = false;
+    if (count < 2 || count > (uint32_t)kMaxGroup) return NF4_OK;
+    uint64_t tiles[kMaxGroup], all = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (a[i].x != a[0].x || a[i].rows != a[0].rows || a[i].d_in != a[0].d_in ||
+            (a[i].scale_codes != nullptr) != (a[0].scale_codes != nullptr))
+            return NF4_OK;
+        if (a[i].d_in > (uint64_t)kMaxSlices * kSliceK) return NF4_OK;  // K shared out between CTAs: on its own
+        tiles[i] = (a[i].d_out + kTileRows - 1) / kTileRows;
+        all += tiles[i];
+    }
+    if (all == 0) return NF4_OK;
+    // CTAs in proportion to the tiles, one at least
+    uint32_t ctas[kMaxGroup], sum = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        ctas[i] = (uint32_t)(tiles[i] * kNumSMs / all);
+        if (ctas[i] == 0) ctas[i] = 1;
+        sum += ctas[i];
+    }
+    while (sum > (uint32_t)kNumSMs) {  // (only if several forwards were rounded up to one CTA)
+        uint32_t big = 0;
+        for (uint32_t i = 1; i < count; ++i) if (ctas[i] > ctas[big]) big = i;
+        --ctas[big];
+        --sum;
+    }
+    while (sum < (uint32_t)kNumSMs) {  // the CTAs left over go where a CTA has the most tiles
+        uint32_t worst = 0;
+        for (uint32_t j = 1; j < count; ++j)
+            if (tiles[j] * ctas[worst] > tiles[worst] * ctas[j]) worst = j;
+        if (ctas[worst] >= tiles[worst]) break;
+        ++ctas[worst];
+        ++sum;
+    }
+    static thread_local GroupParams gp;
+    gp.count = count;
+    gp.cta0[0] = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        Plan pl;
+        if (!plan(a[i], pl, ctas[i])) return NF4_OK;
+        NF4_TRY(prepare(a[i], pl, a[i].workspace, gp.tm_codes[i], gp.tm_scales[i]));
+        gp.p[i] = pl.p;
+        gp.cta0[i + 1] = gp.cta0[i] + pl.grid;
+    }
+    *taken = true;
+    const bool dq = a[0].scale_codes != nullptr;
+    if (a[0].rows <= 8) return dq ? launch_group<1, true>(gp, stream) : launch_group<1, false>(gp, stream);
+    return dq ? launch_group<2, true>(gp, stream) : launch_group<2, false>(gp, stream);
 }
 
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
@@ -958,7 +1136,7 @@ int32_t decode_forward_static_scratch(const nf4_linear_args &a, cudaStream_t str
                     "nf4_linear_forward_noalloc_dev: rows * rank * 4 = %llu bytes exceeds the %u bytes "
                     "the fixed scratch has for it", (unsigned long long)need, kStaticTBytes);
     Plan pl;
-    if (!plan(a, pl))
+    if (!plan(a, pl) || pl.p.kparts > 1)
         return fail(NF4_ERR_UNSUPPORTED,
                     "nf4_linear_forward_noalloc_dev: only the decode shapes are served (rows <= 16, "
                     "bf16, W [d_out, d_in], d_in %% 256 == 0 and <= 4096, rank <= 64)");

@@ -407,6 +407,39 @@ def qlora_merge(packed: "PackedNf4Tensor", d_in: int, d_out: int, a: torch.Tenso
     return out
 
 
+def _linear_args(lib, x2: torch.Tensor, packed: PackedNf4Tensor, d_in: int, d_out: int, layout: int, bias, lora_a,
+                 lora_b, lora_scale: float, out):
+    """The argument block of one forward, its output, and the tensors that must outlive the launch."""
+    dev = x2.device
+    rows = x2.shape[0]
+    rank = 0
+    if lora_a is not None:
+        rank = lora_a.shape[0] if layout == LAYOUT_OUT_IN else lora_a.shape[1]
+        lora_a = lora_a.to(x2.dtype).contiguous()
+        lora_b = lora_b.to(x2.dtype).contiguous()
+    y = out if out is not None else torch.empty(rows, d_out, dtype=x2.dtype, device=dev)
+    ws_bytes = int(lib.nf4_linear_workspace_bytes(rows, d_in, d_out, rank))
+    # zero-filled: the decode kernel's flag words at the start of the workspace must start at zero
+    ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
+    a = LinearArgs()
+    a.struct_bytes = ctypes.sizeof(LinearArgs)
+    a.layout, a.io_dtype = layout, _io_dtype(x2)
+    a.rows, a.d_in, a.d_out = rows, d_in, d_out
+    a.x = x2.data_ptr()
+    a.packed = packed.codes.data_ptr()
+    a.absmax = packed.absmax.data_ptr() if not packed.is_double_quantized() else None
+    a.scale_codes = packed.scale_codes.data_ptr() if packed.is_double_quantized() else None
+    a.scale_of_scales = packed.scale_of_scales.data_ptr() if packed.is_double_quantized() else None
+    a.bias = bias32.data_ptr() if bias32 is not None else None
+    a.lora_a = lora_a.data_ptr() if rank else None
+    a.lora_b = lora_b.data_ptr() if rank else None
+    a.lora_rank, a.lora_scale = rank, float(lora_scale)
+    a.y, a.ldy = y.data_ptr(), y.stride(0)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    return a, y, (ws, bias32, lora_a, lora_b, x2)
+
+
 def linear_forward(x: torch.Tensor, packed: PackedNf4Tensor, d_in: int, d_out: int, layout: int,
                    bias: Optional[torch.Tensor] = None, lora_a: Optional[torch.Tensor] = None,
                    lora_b: Optional[torch.Tensor] = None, lora_scale: float = 0.0,
@@ -422,36 +455,34 @@ def linear_forward(x: torch.Tensor, packed: PackedNf4Tensor, d_in: int, d_out: i
     dev = x.device
     lead = x.shape[:-1]
     x2 = x.contiguous().view(-1, d_in)
-    rows = x2.shape[0]
-    dt = _io_dtype(x2)
-    rank = 0
-    if lora_a is not None:
-        rank = lora_a.shape[0] if layout == LAYOUT_OUT_IN else lora_a.shape[1]
-        lora_a = lora_a.to(x2.dtype).contiguous()
-        lora_b = lora_b.to(x2.dtype).contiguous()
-    y = out if out is not None else torch.empty(rows, d_out, dtype=x2.dtype, device=dev)
-    ws_bytes = int(lib.nf4_linear_workspace_bytes(rows, d_in, d_out, rank))
-    # zero-filled: the decode kernel's flag words at the start of the workspace must start at zero
-    ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
-    bias32 = bias.to(torch.float32).contiguous() if bias is not None else None  # alive until the launch
-    a = LinearArgs()
-    a.struct_bytes = ctypes.sizeof(LinearArgs)
-    a.layout, a.io_dtype = layout, dt
-    a.rows, a.d_in, a.d_out = rows, d_in, d_out
-    a.x = x2.data_ptr()
-    a.packed = packed.codes.data_ptr()
-    a.absmax = packed.absmax.data_ptr() if not packed.is_double_quantized() else None
-    a.scale_codes = packed.scale_codes.data_ptr() if packed.is_double_quantized() else None
-    a.scale_of_scales = packed.scale_of_scales.data_ptr() if packed.is_double_quantized() else None
-    a.bias = bias32.data_ptr() if bias32 is not None else None
-    a.lora_a = lora_a.data_ptr() if rank else None
-    a.lora_b = lora_b.data_ptr() if rank else None
-    a.lora_rank, a.lora_scale = rank, float(lora_scale)
-    a.y, a.ldy = y.data_ptr(), y.stride(0)
-    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a, y, _alive = _linear_args(lib, x2, packed, d_in, d_out, layout, bias, lora_a, lora_b, lora_scale, out)
     with torch.cuda.device(dev):
         _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), _stream(dev)))
     return y.view(*lead, d_out) if out is None else y
+
+
+def linear_forward_grouped(x: torch.Tensor, d_in: int, layout: int, projections) -> list:
+    """Several projections of the same ``x`` through ``nf4_linear_forward_grouped_dev`` (one kernel
+    launch where the shapes allow it).  ``projections``: up to four dicts with ``packed`` and
+    ``d_out`` and optionally ``bias``, ``lora_a``, ``lora_b``, ``lora_scale``.  The outputs equal
+    those of one ``linear_forward`` per projection, which is what the reference does
+    (src/qwennet.rs:372-383 per projection)."""
+    _require_cuda(x, "x")
+    lib = _lib.load()
+    dev = x.device
+    lead = x.shape[:-1]
+    x2 = x.contiguous().view(-1, d_in)
+    block = (LinearArgs * len(projections))()
+    ys, alive = [], []
+    for i, pr in enumerate(projections):
+        a, y, keep = _linear_args(lib, x2, pr["packed"], d_in, pr["d_out"], layout, pr.get("bias"),
+                                  pr.get("lora_a"), pr.get("lora_b"), pr.get("lora_scale", 0.0), None)
+        block[i] = a
+        ys.append(y.view(*lead, pr["d_out"]))
+        alive.append(keep)
+    with torch.cuda.device(dev):
+        _lib.check(lib.nf4_linear_forward_grouped_dev(block, len(projections), _stream(dev)))
+    return ys
 
 
 class QLoraLinear:
