@@ -769,10 +769,10 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
         }
     }
     if (done_old == nctas - 1) {
-        // the last CTA to have read T re-arms the flag words for the next launch
-        p.flags[1] = 0;
-        __threadfence();
-        p.flags[0] = 0;
+        // The last CTA to have read T re-arms the two flag words for the next launch: every other
+        // CTA read the first before it counted itself in on the second, and the next launch
+        // looks at them only after this one has completed, so no order is needed between them.
+        *reinterpret_cast<uint2 *>(p.flags) = make_uint2(0u, 0u);
     }
 }
 
