@@ -88,6 +88,56 @@ struct PrefillParams {
     uint32_t M, N, K, rank;
     uint32_t lora_chunks;  // ceil(rank / 64); T is [M][2 * 64 * lora_chunks] (hi halves, then lo)
     uint32_t m_tiles, n_tiles;
+    // Work of a CTA: first its share of the `sk_tiles` tiles whose k-stages all CTAs divide
+    // evenly between them (a tile can be split between neighbouring CTAs), then `dp_rounds`
+    // whole tiles.  A CTA that multiplies the leading stages of a tile leaves its accumulator
+    // in `partial` ([CTA][BN][BM] f32) and raises its word of `sk_flags`; the CTA that multiplies
+    // the last stages adds those and finishes the tile.
+    uint32_t sk_tiles, dp_rounds;
+    float *partial;
+    uint32_t *sk_flags;
+    uint32_t wait_ns;  // bound of the wait for a neighbour's flag
+};
+
+// This CTA's list of segments (tile, main k-stages [b, e)), in the order they are worked on: the
+// shared tiles from the last to the first -- a piece without a tile's last stage comes first and
+// waits for nobody; the piece with the last stage of a tile that a neighbour began comes last of
+// them -- then the whole tiles.
+struct WorkList {
+    uint64_t u0, u1;   // this CTA's range of main stages of the shared tiles
+    uint32_t ks;       // main stages per tile
+    uint32_t t_first, t_last, n_shared, n_seg, sk_tiles, cta, ctas;
+
+    __device__ void init(const PrefillParams &p, uint32_t k_stages, uint32_t cta_, uint32_t ctas_) {
+        ks = k_stages;
+        cta = cta_;
+        ctas = ctas_;
+        sk_tiles = p.sk_tiles;
+        const uint64_t all = (uint64_t)p.sk_tiles * ks;
+        u0 = all * cta / ctas;
+        u1 = all * (cta + 1) / ctas;
+        n_shared = 0;
+        t_first = t_last = 0;
+        if (u1 > u0) {
+            t_first = (uint32_t)(u0 / ks);
+            t_last = (uint32_t)((u1 - 1) / ks);
+            n_shared = t_last - t_first + 1;
+        }
+        n_seg = n_shared + p.dp_rounds;
+    }
+    __device__ static uint64_t range_begin(uint64_t all, uint32_t c, uint32_t n) { return all * c / n; }
+    __device__ void get(uint32_t j, uint32_t &tile, uint32_t &b, uint32_t &e) const {
+        if (j < n_shared) {
+            tile = t_last - j;
+            const uint64_t t0 = (uint64_t)tile * ks;
+            b = (uint32_t)((u0 > t0 ? u0 : t0) - t0);
+            e = (uint32_t)((u1 < t0 + ks ? u1 : t0 + ks) - t0);
+        } else {
+            tile = sk_tiles + (j - n_shared) * ctas + cta;
+            b = 0;
+            e = ks;
+        }
+    }
 };
 
 // ---- descriptors -----------------------------------------------------------------
@@ -245,10 +295,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
     const uint32_t k_stages = p.K / BK;
     const uint32_t lora_stages = 2 * p.lora_chunks;  // adapter k-stages per tile: hi and lo halves of T
-    const uint32_t stages_per_tile = k_stages + lora_stages;
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
-    const uint32_t my_tiles = blockIdx.x < total_tiles
-                                  ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    WorkList wl;
+    wl.init(p, k_stages, blockIdx.x, gridDim.x);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kXStages; ++s) {
@@ -292,11 +340,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             // the f16 activations and T come from the pre-pass, which may still be running: this
             // kernel is its programmatic dependent (the dequantisers start on the weights at once)
             ptx::pdl_wait();
-            uint32_t cnt = 0;
-            for (uint32_t i = 0; i < my_tiles && ok; ++i) {
-                const uint32_t tile = blockIdx.x + i * gridDim.x;
+            uint32_t cnt = 0, lcnt = 0;
+            for (uint32_t seg = 0; seg < wl.n_seg && ok; ++seg) {
+                uint32_t tile, kb, ke;
+                wl.get(seg, tile, kb, ke);
                 const uint32_t m0 = (tile % p.m_tiles) * BN, n0 = (tile / p.m_tiles) * BM;
-                for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
+                // the adapter's stages follow a tile's last main stage
+                const uint32_t k_end = ke == k_stages ? k_stages + lora_stages : ke;
+                for (uint32_t ks = kb; ks < k_end; ++ks, ++cnt) {
                     const uint32_t s = cnt % kXStages, ph = (cnt / kXStages) & 1u;
                     if (!ptx::mbar_wait_suspended(bar(kBarXEmpty + s), ph ^ 1u)) {
                         ok = false;
@@ -311,8 +362,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                         // adapter stage: a tile of T beside the activations' ring slot and the
                         // matching 128 x 64 tile of LoRA B (ranks beyond the adapter's read as
                         // zero) as the MMA's other shared-memory operand
-                        const uint32_t j = ks - k_stages, lcnt = i * lora_stages + j;
+                        const uint32_t j = ks - k_stages;
                         const uint32_t ls = lcnt % kLoraStages, lph = (lcnt / kLoraStages) & 1u;
+                        ++lcnt;
                         if (!ptx::mbar_wait_suspended(bar(kBarLEmpty + ls), lph ^ 1u)) {
                             ok = false;
                             break;
@@ -337,18 +389,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             constexpr uint32_t idesc_main = make_idesc(0, 0, BM, BN);  // f16 x f16
             constexpr uint32_t idesc_lora = make_idesc(1, 1, BM, BN);  // bf16 x bf16
             const uint32_t x_addr = ptx::smem_addr(x_ring);
-            uint32_t cnt = 0;
-            for (uint32_t i = 0; i < my_tiles && ok; ++i) {
-                for (uint32_t ks = 0; ks < stages_per_tile; ++ks, ++cnt) {
-                    if ((cnt & 1u) != me) continue;
-                    const uint32_t sx = cnt % kXStages, phx = (cnt / kXStages) & 1u;
+            uint32_t cnt = 0, a_next = 0, l_next = 0;  // stages, main stages, adapter stages so far
+            for (uint32_t seg = 0; seg < wl.n_seg && ok; ++seg) {
+                uint32_t tile, kb, ke;
+                wl.get(seg, tile, kb, ke);
+                const uint32_t k_end = ke == k_stages ? k_stages + lora_stages : ke;
+                for (uint32_t ks = kb; ks < k_end; ++ks, ++cnt) {
                     // the weight ring counts main stages only, the LoRA ring adapter stages only
                     const bool main_stage = ks < k_stages;
-                    const uint32_t acnt = i * k_stages + ks, lcnt = i * lora_stages + (ks - k_stages);
+                    const uint32_t acnt = a_next, lcnt = l_next;
+                    if (main_stage) ++a_next;
+                    else ++l_next;
+                    if ((cnt & 1u) != me) continue;
+                    const uint32_t sx = cnt % kXStages, phx = (cnt / kXStages) & 1u;
                     const uint32_t sa = acnt % kAStages, pha = (acnt / kAStages) & 1u;
                     const uint32_t ls = lcnt % kLoraStages;
-                    // the epilogue must have read the previous tile out of the accumulator
-                    if (ks == 0 && !ptx::mbar_wait_suspended(bar(kBarAccEmpty), (i & 1u) ^ 1u)) {
+                    // the epilogue must have read the previous segment out of the accumulator
+                    if (ks == kb && !ptx::mbar_wait_suspended(bar(kBarAccEmpty), (seg & 1u) ^ 1u)) {
                         ok = false;
                         break;
                     }
@@ -372,7 +429,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     if (main_stage) {
                         // 16 k = 8 TMEM columns of the weight stage = 32 bytes inside the
                         // activation tile's swizzled row (+2 in the encoded address)
-                        ptx::mma_ts_f16(tmem_acc, a_cols, bdesc, idesc_main, ks != 0 ? 1u : 0u);
+                        ptx::mma_ts_f16(tmem_acc, a_cols, bdesc, idesc_main, ks != kb ? 1u : 0u);
                         ptx::mma_ts_f16(tmem_acc, a_cols + 8, bdesc + 2, idesc_main, 1u);
                         ptx::mma_ts_f16(tmem_acc, a_cols + 16, bdesc + 4, idesc_main, 1u);
                         ptx::mma_ts_f16(tmem_acc, a_cols + 24, bdesc + 6, idesc_main, 1u);
@@ -389,7 +446,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     ptx::mbar_arrive(bar(kBarIssued + me));
                     ptx::tc_commit(bar(kBarXEmpty + sx));
                     ptx::tc_commit(main_stage ? bar(kBarAEmpty + sa) : bar(kBarLEmpty + ls));
-                    if (ks + 1 == stages_per_tile) ptx::tc_commit(bar(kBarAccFull));
+                    if (ks + 1 == k_end) ptx::tc_commit(bar(kBarAccFull));
                 }
             }
             if (!ok) atomicExch(&g_prefill_error, 2);
@@ -414,11 +471,49 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         auto col_of = [&](uint32_t k) {
             return (k / kPerPass) * kStageRows + set * kHalfRows + (k % kPerPass) * 16;
         };
-        ptx::pdl_wait();  // the rows' factors come from the pre-pass
-        for (uint32_t i = 0; i < my_tiles && ok; ++i) {
-            const uint32_t tile = blockIdx.x + i * gridDim.x;
+        ptx::pdl_wait();  // the rows' factors come from the pre-pass, which also cleared the flags
+        float *own_partial = p.partial + (size_t)blockIdx.x * (BM * BN) + row_in_tile;
+        for (uint32_t seg = 0; seg < wl.n_seg && ok; ++seg) {
+            const uint32_t i = seg;  // the accumulator's barriers alternate per segment
+            uint32_t tile, kb, ke;
+            wl.get(seg, tile, kb, ke);
             const uint32_t n0 = (tile / p.m_tiles) * BM, m0 = (tile % p.m_tiles) * BN;
             const uint32_t n = n0 + row_in_tile;
+            if (ke != k_stages) {
+                // The leading stages of a tile that a neighbour finishes: the raw sums go to this
+                // CTA's place in global memory ([activation row][weight row]: a warp's stores are
+                // whole lines; a thread's values 64 bytes in a row were measured 15 % slower over
+                // the whole GEMM), then the flag goes up.
+                ok = ptx::mbar_wait_suspended(bar(kBarAccFull), i & 1u);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                uint32_t v[16];
+                for (uint32_t k = 0; k < kLoads; ++k) {
+                    tmem_ld16(acc_lane + col_of(k), v);
+                    ptx::tmem_wait_ld();
+                    float *dst = own_partial + (size_t)col_of(k) * BM;
+                    #pragma unroll
+                    for (int r = 0; r < 16; ++r) dst[r * BM] = __uint_as_float(v[r]);
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar(kBarAccEmpty));
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (epi_leader) {
+                    __threadfence();
+                    atomicExch(p.sk_flags + blockIdx.x, 1u);
+                }
+                continue;
+            }
+            // a tile whose leading stages other CTAs multiplied: the CTAs before this one, back to
+            // the one that began the tile
+            uint32_t first_helper = blockIdx.x;
+            if (kb != 0) {
+                const uint64_t all = (uint64_t)wl.sk_tiles * k_stages, t0 = (uint64_t)tile * k_stages;
+                do {
+                    --first_helper;
+                } while (first_helper > 0 && WorkList::range_begin(all, first_helper, gridDim.x) > t0);
+            }
             const float bias = (p.bias && n < p.N) ? __ldg(p.bias + n) : 0.0f;
             // the rows' factors go to shared memory while the MMAs still run: a global load per
             // value inside the read-out would wait for L2 every time (the L1 left beside 227 KB
@@ -453,6 +548,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                             __float2bfloat16_rn(f);
                 }
             };
+            // the helpers' sums for sixteen activation rows of this thread's weight row
+            auto add_helpers = [&](uint32_t (&v)[16], uint32_t col) {
+                for (uint32_t h = first_helper; h < blockIdx.x; ++h) {
+                    const float *src = p.partial + (size_t)h * (BM * BN) + (size_t)col * BM + row_in_tile;
+                    float part[16];
+                    #pragma unroll
+                    for (int r = 0; r < 16; ++r) part[r] = __ldcg(src + r * BM);
+                    #pragma unroll
+                    for (int r = 0; r < 16; ++r) v[r] = __float_as_uint(__uint_as_float(v[r]) + part[r]);
+                }
+            };
+            if (first_helper != blockIdx.x && epi_leader) {
+                // bounded wait for the helpers' flags (they dumped before anything else they did)
+                const uint64_t t_begin = ptx::global_timer_ns();
+                for (uint32_t h = first_helper; h < blockIdx.x && ok; ++h) {
+                    while (ptx::ld_acquire_gpu_u32(p.sk_flags + h) == 0u) {
+                        if (ptx::global_timer_ns() - t_begin > (uint64_t)p.wait_ns) {
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                }
+                if (!ok) atomicExch(&g_prefill_error, 5);  // the sums are wrong; the flag says so
+                ok = true;  // the read-out goes on (every role must finish its segments)
+            }
             for (uint32_t k = 0; k < kLoads; k += 2) {
                 if (k % kPerPass == 0) {
                     // the TMA store that last read the staging buffer must be done with it
@@ -461,8 +582,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 }
                 ptx::tmem_wait_ld();
                 tmem_ld16(acc_lane + col_of(k + 1), vb);
+                if (first_helper != blockIdx.x) add_helpers(va, col_of(k));
                 stage_chunk(va, col_of(k));
                 ptx::tmem_wait_ld();
+                if (first_helper != blockIdx.x) add_helpers(vb, col_of(k + 1));
                 if (k + 2 < kLoads) {
                     tmem_ld16(acc_lane + col_of(k + 2), va);
                 } else {
@@ -500,23 +623,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         // block scales are used divided by a power of two (see weight_exponent)
         const float w_down = ldexpf(1.0f, -weight_exponent(p.absmax, p.scale_codes, p.scale_of_scales));
         const uint32_t blocks_per_row = p.K / 64;
-        const uint32_t total = my_tiles * k_stages;
+        const uint32_t total = (uint32_t)(wl.u1 - wl.u0) + p.dp_rounds * k_stages;  // main stages of this CTA
         const uint32_t lane_base = tmem_a + ((q * 32) << 16);
 
         // Stage positions are walked, not divided out: a 64-bit division per stage costs more
         // than the expansion itself.
         struct Pos {
-            uint32_t cnt, i, ks, n;  // running main-stage number, tile number, stage in tile, weight row
+            uint32_t cnt, seg, ks, ke, n;  // running main-stage number, segment, stage in tile, the segment's end, weight row
         };
-        auto row_of_tile = [&](uint32_t i) {
-            const uint32_t tile = blockIdx.x + i * gridDim.x;
-            return (tile / p.m_tiles) * BM + row_in_tile;
+        auto enter = [&](Pos &pos, uint32_t over) {  // to segment pos.seg, `over` stages in
+            uint32_t tile, kb, ke;
+            wl.get(pos.seg, tile, kb, ke);
+            pos.ks = kb + over;
+            pos.ke = ke;
+            pos.n = (tile / p.m_tiles) * BM + row_in_tile;
         };
         auto settle = [&](Pos &pos) {
-            while (pos.ks >= k_stages) {
-                pos.ks -= k_stages;
-                ++pos.i;
-                pos.n = row_of_tile(pos.i);
+            while (pos.ks >= pos.ke) {
+                const uint32_t over = pos.ks - pos.ke;
+                if (++pos.seg >= wl.n_seg) {  // past the last segment
+                    pos.cnt = total;
+                    return;
+                }
+                enter(pos, over);
             }
         };
         auto advance = [&](Pos &pos) {
@@ -557,8 +686,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         // software pipeline over this group's stages (group, group + 4, group + 8, ...): the
         // loads of a stage are in flight while the stages before it are expanded
         constexpr int kDepth = 2;
-        Pos pe{group, 0, group, row_of_tile(0)};
-        settle(pe);
+        Pos pe{group, 0, 0, 0, 0};
+        if (wl.n_seg == 0) pe.cnt = total;
+        else {
+            enter(pe, group);
+            settle(pe);
+        }
         Pos pf = pe;
         RowStage rs[kDepth];
         #pragma unroll
@@ -633,7 +766,8 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
                        uint32_t M, uint32_t K, uint32_t rank, uint32_t chunks, float scale,
                        __half *__restrict__ xh, float *__restrict__ row_scale,
                        __nv_bfloat16 *__restrict__ t_out, const float *__restrict__ absmax,
-                       const uint8_t *__restrict__ scale_codes, const float *__restrict__ scale_of_scales) {
+                       const uint8_t *__restrict__ scale_codes, const float *__restrict__ scale_of_scales,
+                       uint32_t *__restrict__ sk_flags, uint32_t n_flags) {
     __shared__ float red[16][64 + 1];
     __shared__ uint32_t row_max_bits[16];
     __shared__ float inv_scale[16];
@@ -642,6 +776,9 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
     const uint32_t m0 = blockIdx.x * 16;
     const uint32_t rows = min(16u, M - m0);
     ptx::pdl_launch_dependents();  // the GEMM may set itself up and start on the weights
+    // the GEMM's CTAs raise these once this kernel has completed (their readers and writers wait for that)
+    if (blockIdx.x == 0)
+        for (uint32_t i = threadIdx.x; i < n_flags; i += kTThreads) sk_flags[i] = 0;
     const int w_exp = weight_exponent(absmax, scale_codes, scale_of_scales);
     const float w_up = ldexpf(1.0f, w_exp), w_down = ldexpf(1.0f, -w_exp);
     const bool row_a = g < rows, row_b = g + 8 < rows;
@@ -818,24 +955,57 @@ bool prefill_supported(const nf4_linear_args &a) {
 }
 
 namespace {
-struct WorkspaceLayout {
-    uint64_t off_xh, off_scale, off_t, bytes;
+// How the tiles are shared out: `grid` CTAs; the first `sk_tiles` tiles are divided by k-stages
+// (every CTA the same number of stages, a tile possibly split between neighbours), the other
+// grid * dp_rounds tiles go out whole.  With a tile count that is a multiple of the grid nothing
+// is split.  Otherwise the last round of whole tiles would leave most CTAs idle (896 tiles on 148
+// CTAs: seven rounds for 6.05 rounds of work), so the last full round and the remainder are
+// divided by stages instead.  Fewer tiles than SMs: divided as long as a CTA keeps 24 stages.
+struct Sharing {
+    uint32_t grid, sk_tiles, dp_rounds;
 };
-// f16 copy of x | row scales | T (bf16 hi/lo); d_in is bounded so that rows * d_in * 2 fits
-WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint32_t lora_rank) {
+Sharing share_tiles(uint64_t rows, uint64_t d_in, uint64_t d_out) {
+    const uint64_t tiles = ((rows + BN - 1) / BN) * ((d_out + BM - 1) / BM), ks = d_in / BK;
+    Sharing sh;
+    uint64_t grid = kNumSMs;
+    if (tiles < grid) {
+        const uint64_t by_stages = tiles * ks / 24;
+        grid = by_stages < grid ? by_stages : grid;
+        if (grid < tiles) grid = tiles;
+    }
+    sh.grid = (uint32_t)grid;
+    if (tiles % grid == 0) {
+        sh.sk_tiles = 0;
+        sh.dp_rounds = (uint32_t)(tiles / grid);
+    } else {
+        sh.dp_rounds = tiles / grid >= 1 ? (uint32_t)(tiles / grid - 1) : 0u;
+        sh.sk_tiles = (uint32_t)(tiles - (uint64_t)sh.dp_rounds * grid);
+    }
+    return sh;
+}
+
+struct WorkspaceLayout {
+    uint64_t off_xh, off_scale, off_t, off_flags, off_partial, bytes;
+};
+// f16 copy of x | row scales | T (bf16 hi/lo) | flags and partial sums of the split tiles; d_in is
+// bounded so that rows * d_in * 2 fits
+WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
     auto up = [](uint64_t v) { return (v + 255) / 256 * 256; };
     WorkspaceLayout w;
     w.off_xh = 0;
     w.off_scale = up(rows * d_in * 2);
     w.off_t = w.off_scale + up(rows * 4);
-    w.bytes = w.off_t + up(rows * 2ull * 64 * lora_chunks_of(lora_rank) * 2);
+    w.off_flags = w.off_t + up(rows * 2ull * 64 * lora_chunks_of(lora_rank) * 2);
+    const Sharing sh = share_tiles(rows, d_in, d_out);
+    w.off_partial = w.off_flags + up((uint64_t)sh.grid * 4);
+    w.bytes = w.off_partial + (sh.sk_tiles ? (uint64_t)sh.grid * BM * BN * 4 : 0);
     return w;
 }
 }  // namespace
 
-uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint32_t lora_rank) {
-    if (rows <= 16 || d_in % 64 != 0) return 0;
-    return workspace_layout(rows, d_in, lora_rank).bytes;
+uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
+    if (rows <= 16 || d_in % 64 != 0 || d_in == 0 || d_out == 0) return 0;
+    return workspace_layout(rows, d_in, d_out, lora_rank).bytes;
 }
 
 int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
@@ -855,15 +1025,22 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.n_tiles = (p.N + BM - 1) / BM;
     const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
 
-    const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.rank);
+    const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.N, p.rank);
+    const Sharing sh = share_tiles(p.M, p.K, p.N);
+    p.sk_tiles = sh.sk_tiles;
+    p.dp_rounds = sh.dp_rounds;
+    p.wait_ns = 1000000000u;
     uint8_t *ws = static_cast<uint8_t *>(a.workspace);
     __half *xh = reinterpret_cast<__half *>(ws + wl.off_xh);
     float *row_scale = reinterpret_cast<float *>(ws + wl.off_scale);
     __nv_bfloat16 *t = reinterpret_cast<__nv_bfloat16 *>(ws + wl.off_t);
     p.row_scale = row_scale;
+    p.sk_flags = reinterpret_cast<uint32_t *>(ws + wl.off_flags);
+    p.partial = reinterpret_cast<float *>(ws + wl.off_partial);
     prefill_prepass_kernel<<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(a.lora_a), p.M, p.K,
-        p.rank, p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales);
+        p.rank, p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales,
+        p.sk_flags, sh.grid);
     count_launch();
     NF4_CUDA_TRY(cudaGetLastError());
 
@@ -886,8 +1063,7 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
         NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, p.M, p.N, ldy * 2, kEpiBytes / (BM * 2), BM,
                          CU_TENSOR_MAP_SWIZZLE_NONE));
 
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
-    const uint32_t grid = total_tiles < (uint32_t)kNumSMs ? total_tiles : (uint32_t)kNumSMs;
+    const uint32_t grid = sh.grid;
     const size_t smem = 1024 + kXStages * kXTileBytes + kLoraStages * kLoraTileBytes + kEpiBytes +
                         kNumBars * 8 + 16 + BN * 4 + 64;
     if (a.y_f32) {

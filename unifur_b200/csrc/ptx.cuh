@@ -82,6 +82,12 @@ __device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_t parit
     }
 }
 
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // ---- bulk async copy global -> shared (TMA, untiled) --------------------------
 // dst, src 16-byte aligned; bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes,
