@@ -800,12 +800,14 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def check(y_sharded, y_full) -> str:
+    def check(y_sharded, y_full, k: int) -> str:
         if torch.equal(y_sharded, y_full):
             verdict = 0.0
         else:
+            # one bf16 ulp, plus what f32 sums of k terms added in another order (other tile splits
+            # on a shard than on the whole weight) can differ by where the terms cancel
             d = (y_sharded.float() - y_full.float()).abs()
-            tol = y_full.float().abs() * 2.0 ** -7 + 4e-6 * float(y_full.float().abs().max())
+            tol = y_full.float().abs() * 2.0 ** -7 + 5e-7 * (k / 64) ** 0.5 * float(y_full.float().abs().max())
             verdict = 1.0 if bool((d <= tol).all()) else 2.0
         worst = reduce_max(verdict)
         return {0.0: "ok", 1.0: "ok_within_one_bf16_ulp"}.get(worst, "MISMATCH")
@@ -847,7 +849,7 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
     y_sharded = plan.run().clone()
     y_full = linear_forward(x, full, pk, pn, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=SCALE)
     torch.cuda.synchronize()
-    verdict = check(y_sharded, y_full)
+    verdict = check(y_sharded, y_full, pk)
     del y_full, y_sharded
     ms_local = timed(plan.run_local)
     ms_all = timed(plan.run)
@@ -876,7 +878,7 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
             y_sharded = plan.run().clone()
             y_full = linear_forward(x, full, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=SCALE)
             torch.cuda.synchronize()
-            checks[nm] = check(y_sharded, y_full)
+            checks[nm] = check(y_sharded, y_full, k)
             del y_full, y_sharded, full
             plans.append(plan)
         ms_local = timed(lambda: [pl.run_local() for pl in plans])

@@ -308,6 +308,9 @@ def test_qwen2_7b_block_decode_batch_8(oracle, dq):
     (128, 3584, 512, 16, True, False),    # Qwen2-7B k/v projection
     (40, 128, 72, 12, False, True),       # rank not a multiple of 8: LoRA B is not TMA-readable, general kernel
     (520, 256, 304, 8, False, False),     # three activation tiles x three weight tiles, narrow adapter
+    (512, 4096, 256, 16, False, True),    # four tiles over ten CTAs: a tile's k-stages split three ways
+    (300, 3072, 200, 64, True, True),     # four ragged tiles over eight CTAs, adapter stages on the finishing CTA only
+    (768, 1536, 6400, 16, False, False),  # 150 tiles on 148 CTAs: every CTA takes a little more than one tile
 ])
 def test_prefill_shapes(oracle, M, K, N, r, dq, bias):
     c = make_case(oracle, 5000 + M + K + N, M, K, N, r, dq=dq, bias=bias)

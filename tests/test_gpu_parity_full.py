@@ -75,6 +75,16 @@ def test_config5_prefill_4096_tokens_every_projection(oracle, name, k, n):
     _check_slices(oracle, packed, a, b, x, y, k, n, cols, [slice(0, 8), slice(2048, 2056), slice(4088, 4096)])
 
 
+@pytest.mark.parametrize("k,n", [(18944, 1792), (3584, 9472), (3584, 256)])
+def test_config5_prefill_4096_tokens_two_gpu_shards(oracle, k, n):
+    # the column shards a GPU owns when the block is split over two GPUs (down, gate / up, k / v):
+    # other tile counts than the whole projections, so other splits of the tiles between the CTAs
+    m, r = 4096, 16
+    packed, a, b, x, y = _forward_full(m, k, n, r, seed=300 + n % 89)
+    cols = sorted({0, (n // 2) // 128 * 128, n - 128})
+    _check_slices(oracle, packed, a, b, x, y, k, n, cols, [slice(0, 8), slice(2048, 2056), slice(4088, 4096)])
+
+
 @pytest.mark.parametrize("rows,cols", [(4096, 14336), (14336, 4096)])
 def test_config4_the_two_long_matrices_bit_exact(oracle, rows, cols):
     # the 58.7 M-element members of the sweep, heavy-tailed values: codes and absmax bit-exact
