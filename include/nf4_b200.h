@@ -215,9 +215,11 @@ typedef struct nf4_linear_args {
 /* Scratch the forward needs for these sizes: the LoRA intermediate x*A^T behind 256 bytes of flag
  * words (the CTAs that compute x*A^T and the CTAs that read it meet on them; zero before the first
  * use, zero after every call), and for more than 16 rows the f16 copy of x with its per-row
- * power-of-two scales that the tensor-core kernel reads; for at most 16 rows also split-K partial
- * sums when d_in exceeds 4096.  One workspace serves one stream: calls that may overlap on the
- * GPU need a workspace each. */
+ * power-of-two scales that the tensor-core kernel reads (plus a 128 x 256 f32 accumulator per SM
+ * where it splits tiles between CTAs); for at most 16 rows also the partial sums of the parts of K
+ * when d_in exceeds 4096, or, in the reference's weight orientation, of the pieces of K its kernel
+ * works in.  One workspace serves one stream: calls that may overlap on the GPU need a workspace
+ * each. */
 NF4_API uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                     uint32_t lora_rank);
 
@@ -256,7 +258,8 @@ NF4_API int32_t nf4_qlora_merge_dev(const uint8_t *packed, const float *absmax, 
  *   grad_x [rows, d_in]  = grad_y W^T + s (grad_y B^T) A^T   (one more NF4 linear over the same packed
  *                          bytes read in the other orientation),
  *   grad_a, grad_b with the shapes of lora_a, lora_b: s x^T (grad_y B^T) and s (x A)^T grad_y.
- * fwd->workspace must hold nf4_qlora_backward_workspace_bytes() bytes. */
+ * fwd->workspace must hold nf4_qlora_backward_workspace_bytes() bytes, 256-byte aligned, its first 256
+ * bytes zero at the first use like any forward workspace (every call leaves them zero). */
 NF4_API uint64_t nf4_qlora_backward_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                                     uint32_t lora_rank);
 NF4_API int32_t nf4_qlora_backward_dev(const nf4_linear_args *fwd, const void *grad_y, void *grad_x,

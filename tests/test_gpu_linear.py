@@ -173,6 +173,46 @@ def test_general_kernel_in_out_layout_f32(oracle):
         assert rel_l2(got, ref) <= REL_L2_F32
 
 
+@pytest.mark.parametrize("rows,d_in,d_out,r,dq,f32", [
+    (1, 4096, 11008, 16, False, True),     # the decode configuration in the reference's orientation and types
+    (4, 4096, 11008, 16, True, False),     # bf16 activations, double-quantized scales
+    (16, 1024, 4096, 8, False, True),      # two launches of eight activation rows
+    (40, 512, 320, 4, True, True),         # five launches; strip narrower than 256 columns at the end
+    (3, 100, 64, 0, False, True),          # one strip, K shorter than two pieces
+    (8, 18944, 3584, 16, False, False),    # the block's down projection
+])
+def test_reference_orientation_at_decode_sizes(oracle, rows, d_in, d_out, r, dq, f32):
+    # W [d_in, d_out] with d_out a multiple of 64 and few activation rows: the strip kernel (f32
+    # dequantisation as the reference does it, f32 sums; pieces of K added in a fixed order)
+    rng = np.random.default_rng(700 + rows + d_in + d_out)
+    w = (rng.standard_normal((d_in, d_out)) * 0.02).astype(np.float32)
+    packed, absmax = oracle.quantize_packed(w)
+    sc = sos = None
+    if dq:
+        sc, sos = oracle.double_quantize(absmax)
+    x = rng.uniform(-1, 1, (rows, d_in)).astype(np.float32)
+    la = lb = None
+    if r:
+        la = (rng.standard_normal((d_in, r)) * 0.05).astype(np.float32)
+        lb = rng.uniform(-0.5, 0.5, (r, d_out)).astype(np.float32)
+    bias = rng.standard_normal(d_out).astype(np.float32)
+    if not f32:
+        x, bias = bf16_round(oracle, x), bias
+        if r:
+            la, lb = bf16_round(oracle, la), bf16_round(oracle, lb)
+    ref = oracle.qlora_forward_burn(x, packed, None if dq else absmax, d_in, d_out, la, lb, 2.0, bias, sc,
+                                    sos if dq else 0.0)
+    dt = _lib.DTYPE_F32 if f32 else _lib.DTYPE_BF16
+    kw = dict(bias=bias, lora_a=la, lora_b=lb, scale=2.0, scale_codes=sc, sos=sos)
+    got = run_forward(_lib.LAYOUT_IN_OUT, dt, x, packed, None if dq else absmax, d_in, d_out, y_f32=True, calls=2, **kw)
+    assert rel_l2(got, ref) <= REL_L2_F32   # f32 products and sums of exactly dequantized weights
+    again = run_forward(_lib.LAYOUT_IN_OUT, dt, x, packed, None if dq else absmax, d_in, d_out, y_f32=True, **kw)
+    assert np.array_equal(got, again)       # bit-reproducible
+    if not f32:
+        y16 = run_forward(_lib.LAYOUT_IN_OUT, dt, x, packed, None if dq else absmax, d_in, d_out, **kw)
+        assert np.array_equal(y16, torch.from_numpy(got).bfloat16().float().numpy())
+
+
 def test_layout_kat_minus_three(oracle):
     # qwennet.rs:2196-2211: y[o] = sum_i x[i] W[i][o] with W = [[1,2,3],[4,5,6]] (values on a
     # grid NF4 cannot hold exactly, so compare against the oracle's own dequantized weight)

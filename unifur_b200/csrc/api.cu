@@ -420,7 +420,7 @@ uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out
 
     uint64_t need = decode_workspace_bytes(rows, d_in, d_out, lora_rank);
     const uint64_t b = prefill_workspace_bytes(rows, d_in, d_out, lora_rank);
-    const uint64_t c = generic_workspace_bytes(rows, lora_rank);
+    const uint64_t c = generic_workspace_bytes(rows, d_in, d_out, lora_rank);
     const uint64_t d = decode2_workspace_bytes(rows, d_in, d_out, lora_rank);
     if (d > need) need = d;
     if (b > need) need = b;

@@ -85,7 +85,7 @@ uint64_t decode2_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, u
 int32_t decode2_forward(const nf4_linear_args &a, cudaStream_t stream);
 
 // generic_linear.cu: any layout / dtype / shape on CUDA cores (exact f32 weights).
-uint64_t generic_workspace_bytes(uint64_t rows, uint32_t lora_rank);
+uint64_t generic_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
 int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream);
 
 // prefill_gemm.cu: tcgen05 GEMM, NF4_LAYOUT_OUT_IN, bf16 activations.
