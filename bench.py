@@ -615,6 +615,46 @@ def aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind):
                      "algorithmic_bytes": int(b)}
     del vals, packed, absmax
     out["prefill"] = prefill_section(torch, lib, _lib, dev)
+    out["reference_orientation"] = reference_orientation_section(torch, lib, _lib, dev)
+    return out
+
+
+def reference_orientation_section(torch, lib, _lib, dev, iters: int = 20):
+    """The decode configuration's layer as the reference itself stores and calls it: x f32 [M, 4096],
+    W [4096, 11008] with the 64-blocks along d_out, adapter A [4096, 16], B [16, 11008] in f32
+    (Nf4Linear::forward / QloraLinear::forward, src/qwennet.rs:230-241, 325-344)."""
+    from unifur_b200.quantize import PackedNf4Tensor
+
+    hbm_peak, _tf, peak_kind = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(12)
+    w = torch.randn(K * N, device=dev, generator=g) * 0.02
+    wq = PackedNf4Tensor.quantize(w)
+    del w
+    la = torch.randn(K, RANK, device=dev, generator=g) * 0.01
+    lb = torch.randn(RANK, N, device=dev, generator=g) * 0.01
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    out = {"workload": "x f32 [M, 4096], W NF4 [4096, 11008] (blocks along d_out), LoRA rank 16 in f32; "
+                       "CUDA-core strip kernel, f32 dequantisation and sums; 160 MB flush write before every "
+                       "forward, outside the timed events"}
+    for m in MS:
+        x = torch.randn(m, K, device=dev, generator=g)
+        y = torch.zeros(m, N, device=dev)
+        ws = torch.zeros(max(int(lib.nf4_linear_workspace_bytes(m, K, N, RANK)), 256), dtype=torch.uint8, device=dev)
+        a = _lib.LinearArgs()
+        a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+        a.layout, a.io_dtype = _lib.LAYOUT_IN_OUT, _lib.DTYPE_F32
+        a.rows, a.d_in, a.d_out = m, K, N
+        a.x, a.packed, a.absmax = x.data_ptr(), wq.codes.data_ptr(), wq.absmax.data_ptr()
+        a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb.data_ptr(), RANK, SCALE
+        a.y, a.ldy = y.data_ptr(), N
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        ms, _ = time_flushed(torch, lambda _i: _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), stream())),
+                             flush, iters)
+        by = K * N // 2 + K * N // 64 * 4 + RANK * (K + N) * 4 + m * (K + N) * 4
+        gbs = by / (ms * 1e-3) / 1e9
+        out[f"M={m}"] = {"us": ms * 1e3, "GB/s": gbs, "algorithmic_bytes": by, "frac": gbs / hbm_peak,
+                         "peak_kind": f"of {peak_kind}"}
     return out
 
 
