@@ -255,7 +255,6 @@ def run_own(args) -> None:
         log("process group up")
     lib = _lib.load()
     hbm_peak, _tf_peak, peak_kind = measured_peaks()
-
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -541,7 +540,8 @@ def run_own(args) -> None:
                                 "per pass",
                        "launch": launch_mode,
                        "sharding": "none" if world == 1 else
-                       f"{world} column shards of a [{world * N}, {K}] layer, one NCCL all-gather of y per step"},
+                       f"{world} column shards of a [{world * N}, {K}] layer, one NCCL all-gather of y per step "
+                       "on its own stream"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(gpu_launches), "clocks": clocks,
             "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
@@ -847,7 +847,7 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
             # one bf16 ulp, plus what f32 sums of k terms added in another order (other tile splits
             # on a shard than on the whole weight) can differ by where the terms cancel
             d = (y_sharded.float() - y_full.float()).abs()
-            tol = y_full.float().abs() * 2.0 ** -7 + 5e-7 * (k / 64) ** 0.5 * float(y_full.float().abs().max())
+            tol = y_full.float().abs() * 2.0 ** -7 + 2e-6 * (k / 64) ** 0.5 * float(y_full.float().abs().max())
             verdict = 1.0 if bool((d <= tol).all()) else 2.0
         worst = reduce_max(verdict)
         return {0.0: "ok", 1.0: "ok_within_one_bf16_ulp"}.get(worst, "MISMATCH")

@@ -292,6 +292,13 @@ NF4_API int32_t nf4_sharded_linear_forward_dev(const nf4_linear_args *shard, voi
  * y, weights, adapter and workspace (the workspaces must not overlap).  count <= 4. */
 NF4_API int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint32_t count, void *stream);
 
+/* The decode kernel puts one CTA on every SM (it needs a whole SM's shared memory), so a kernel
+ * that runs beside it on another stream -- a collective gathering the previous step's outputs --
+ * holds back whole CTAs of it.  A host that overlaps such work tells the library to leave `count`
+ * SMs free (0 ... 74, default 0; process-wide, takes effect with the next call); the forward's
+ * results do not depend on it.  No counterpart in the reference (single device, no streams). */
+NF4_API int32_t nf4_reserve_sms(int32_t count);
+
 /* Decode-sized forward for callers that cannot allocate or own device memory.
  * No counterpart in the reference (its forward allocates a fresh f32 weight on every call).
  *

@@ -319,3 +319,26 @@ def test_grouped_forward_equals_one_call_per_projection(m, k, widths, ranks, dq)
             assert bool(((y.float() - one.float()).abs() <= tol).all())
     d0, d1, d2 = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
     assert lib.nf4_device_status(ctypes.byref(d0), ctypes.byref(d1), ctypes.byref(d2)) == 0
+
+
+def test_reserved_sms_do_not_change_results():
+    # nf4_reserve_sms shrinks the decode kernel's grid (fewer CTAs, other row ranges): same bits
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+
+    L = _lib.load()
+    g = torch.Generator(device=DEV).manual_seed(77)
+    m, k, n, r = 4, 4096, 11008, 16
+    w = torch.randn(n * k, device=DEV, generator=g) * 0.02
+    packed = PackedNf4Tensor.quantize(w)
+    la = (torch.randn(r, k, device=DEV, generator=g) * 0.01).bfloat16()
+    lb = (torch.randn(n, r, device=DEV, generator=g) * 0.01).bfloat16()
+    x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
+    base = linear_forward(x, packed, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=2.0)
+    try:
+        for count in (4, 20, 74):
+            _lib.check(L.nf4_reserve_sms(count))
+            y = linear_forward(x, packed, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=2.0)
+            assert torch.equal(y, base), count
+        assert L.nf4_reserve_sms(75) == -1 and L.nf4_reserve_sms(-1) == -1
+    finally:
+        _lib.check(L.nf4_reserve_sms(0))

@@ -75,9 +75,9 @@ def test_config5_prefill_4096_tokens_every_projection(oracle, name, k, n):
     _check_slices(oracle, packed, a, b, x, y, k, n, cols, [slice(0, 8), slice(2048, 2056), slice(4088, 4096)])
 
 
-@pytest.mark.parametrize("k,n", [(18944, 1792), (3584, 9472), (3584, 256)])
-def test_config5_prefill_4096_tokens_two_gpu_shards(oracle, k, n):
-    # the column shards a GPU owns when the block is split over two GPUs (down, gate / up, k / v):
+@pytest.mark.parametrize("k,n", [(18944, 1792), (3584, 9472), (3584, 256), (18944, 896), (18944, 448), (3584, 2368)])
+def test_config5_prefill_4096_tokens_shards(oracle, k, n):
+    # the column shards a GPU owns when the block is split over two, four or eight GPUs (down, gate / up, k / v):
     # other tile counts than the whole projections, so other splits of the tiles between the CTAs
     m, r = 4096, 16
     packed, a, b, x, y = _forward_full(m, k, n, r, seed=300 + n % 89)

@@ -96,6 +96,7 @@ SIGNATURES = {
     "nf4_sharded_linear_forward_dev": (_i32, [C.POINTER(LinearArgs), _vp, _i32, _i32, _vp, _u64, _vp, _u64, _vp]),
     "nf4_linear_noalloc_scratch_bytes": (_u64, []),
     "nf4_linear_forward_grouped_dev": (_i32, [C.POINTER(LinearArgs), _u32, _vp]),
+    "nf4_reserve_sms": (_i32, [_i32]),
     "nf4_linear_forward_noalloc_dev": (_i32, [C.POINTER(LinearArgs), _vp]),
     "nf4_weight_from_values_host": (_i32, [_vp, _u64, _u64, _i32, _i32, C.POINTER(_vp)]),
     "nf4_weight_from_packed_host": (_i32, [_vp, _vp, _vp, _f32, _u64, _u64, _i32,

@@ -450,6 +450,23 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     return generic_forward(*args, s);
 }
 
+// SMs the decode kernel leaves alone (see nf4_reserve_sms)
+static std::atomic<int> g_reserved_sms{0};
+
+}  // extern "C"
+uint32_t nf4::persistent_ctas() {
+    const int r = g_reserved_sms.load(std::memory_order_relaxed);
+    return (uint32_t)(kNumSMs - r);
+}
+extern "C" {
+
+int32_t nf4_reserve_sms(int32_t count) {
+    if (count < 0 || count > kNumSMs / 2)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_reserve_sms: count must be 0 ... %d", kNumSMs / 2);
+    g_reserved_sms.store(count, std::memory_order_relaxed);
+    return NF4_OK;
+}
+
 int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint32_t count, void *stream) {
     if (!args || count == 0 || count > 4)
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward_grouped_dev: count must be 1 ... 4");

@@ -885,7 +885,7 @@ struct Plan {
 
 // Fills the shape-dependent fields; false when the shape does not fit.
 bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran, Plan &pl,
-                uint32_t max_ctas = kNumSMs) {
+                uint32_t max_ctas) {
     using C = Cfg;
     DecodeParams &p = pl.p;
     const uint32_t nt = M > 8 ? 2u : 1u;
@@ -934,7 +934,8 @@ bool plan_shape(uint32_t M, uint32_t K, uint32_t N, uint32_t rank, uint32_t gran
     return true;
 }
 
-bool plan(const nf4_linear_args &a, Plan &pl, uint32_t max_ctas = kNumSMs) {
+bool plan(const nf4_linear_args &a, Plan &pl, uint32_t max_ctas = 0) {
+    if (max_ctas == 0) max_ctas = persistent_ctas();  // one CTA per SM, less what the host keeps free
     if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
     if (a.rows == 0 || a.rows > 16) return false;
     // whole slices of four blocks: the scale rows then have a 16-byte pitch, which TMA needs
@@ -1077,19 +1078,20 @@ int32_t decode_forward_grouped(const nf4_linear_args *a, uint32_t count, cudaStr
     }
     if (all == 0) return NF4_OK;
     // CTAs in proportion to the tiles, one at least
+    const uint32_t n_sms = persistent_ctas();
     uint32_t ctas[kMaxGroup], sum = 0;
     for (uint32_t i = 0; i < count; ++i) {
-        ctas[i] = (uint32_t)(tiles[i] * kNumSMs / all);
+        ctas[i] = (uint32_t)(tiles[i] * n_sms / all);
         if (ctas[i] == 0) ctas[i] = 1;
         sum += ctas[i];
     }
-    while (sum > (uint32_t)kNumSMs) {  // (only if several forwards were rounded up to one CTA)
+    while (sum > n_sms) {  // (only if several forwards were rounded up to one CTA)
         uint32_t big = 0;
         for (uint32_t i = 1; i < count; ++i) if (ctas[i] > ctas[big]) big = i;
         --ctas[big];
         --sum;
     }
-    while (sum < (uint32_t)kNumSMs) {  // the CTAs left over go where a CTA has the most tiles
+    while (sum < n_sms) {  // the CTAs left over go where a CTA has the most tiles
         uint32_t worst = 0;
         for (uint32_t j = 1; j < count; ++j)
             if (tiles[j] * ctas[worst] > tiles[worst] * ctas[j]) worst = j;

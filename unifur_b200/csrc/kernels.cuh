@@ -68,6 +68,8 @@ int32_t selfcheck_codes(uint64_t first_bits, uint64_t count, unsigned long long 
 // decode_gemv.cu: rows <= 16, NF4_LAYOUT_OUT_IN, bf16 activations.
 bool decode_supported(const nf4_linear_args &a);
 uint64_t decode_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
+// api.cu: CTAs a kernel that puts one CTA on every SM may use (the SM count less nf4_reserve_sms)
+uint32_t persistent_ctas();
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);
 int32_t decode_forward_grouped(const nf4_linear_args *a, uint32_t count, cudaStream_t stream, bool *taken);
 
