@@ -342,3 +342,26 @@ def test_reserved_sms_do_not_change_results():
         assert L.nf4_reserve_sms(75) == -1 and L.nf4_reserve_sms(-1) == -1
     finally:
         _lib.check(L.nf4_reserve_sms(0))
+
+
+@pytest.mark.parametrize("m,k,n", [(4, 4096, 512), (8, 4128, 256), (64, 1024, 256)])
+def test_adapter_views_at_odd_offsets_take_the_general_kernel(m, k, n):
+    # LoRA factors that are views two bytes into a buffer (an ordinary slice) cannot be read with
+    # the tuned kernels' 16-byte loads: the forward must neither fault nor differ
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+
+    g = torch.Generator(device=DEV).manual_seed(91 + k)
+    r = 16
+    w = torch.randn(n * k, device=DEV, generator=g) * 0.02
+    packed = PackedNf4Tensor.quantize(w)
+    x = torch.randn(m, k, device=DEV, generator=g).bfloat16()
+    la_buf = (torch.randn(r * k + 8, device=DEV, generator=g) * 0.01).bfloat16()
+    lb_buf = (torch.randn(n * r + 8, device=DEV, generator=g) * 0.01).bfloat16()
+    la_odd, lb_odd = la_buf[1:1 + r * k].view(r, k), lb_buf[1:1 + n * r].view(n, r)
+    assert la_odd.data_ptr() % 16 != 0 and lb_odd.data_ptr() % 16 != 0
+    y_odd = linear_forward(x, packed, k, n, _lib.LAYOUT_OUT_IN, lora_a=la_odd, lora_b=lb_odd, lora_scale=2.0)
+    y_ref = linear_forward(x, packed, k, n, _lib.LAYOUT_OUT_IN, lora_a=la_odd.clone(), lora_b=lb_odd.clone(),
+                           lora_scale=2.0)
+    torch.cuda.synchronize()
+    tol = y_ref.float().abs() * 2.0 ** -6 + 1e-5 * float(y_ref.float().abs().max())
+    assert bool(((y_odd.float() - y_ref.float()).abs() <= tol).all())

@@ -693,6 +693,8 @@ bool decode2_supported(const nf4_linear_args &a) {
     const bool dq = a.scale_codes != nullptr;
     const void *scales = dq ? (const void *)a.scale_codes : (const void *)a.absmax;
     if (!aligned16(a.x) || !aligned16(a.packed) || !aligned16(scales)) return false;
+    // the adapter factors are read with 16-byte loads: views at odd offsets go to the general kernel
+    if (a.lora_a && (!aligned16(a.lora_a) || !aligned16(a.lora_b))) return false;
     if (reinterpret_cast<uintptr_t>(a.y) & (a.y_f32 ? 3u : 1u)) return false;
     Plan pl;
     return make_plan(a.rows, a.d_in, a.d_out, dq, a.lora_a ? a.lora_rank : 0, pl);
