@@ -363,5 +363,7 @@ def test_adapter_views_at_odd_offsets_take_the_general_kernel(m, k, n):
     y_ref = linear_forward(x, packed, k, n, _lib.LAYOUT_OUT_IN, lora_a=la_odd.clone(), lora_b=lb_odd.clone(),
                            lora_scale=2.0)
     torch.cuda.synchronize()
-    tol = y_ref.float().abs() * 2.0 ** -6 + 1e-5 * float(y_ref.float().abs().max())
-    assert bool(((y_odd.float() - y_ref.float()).abs() <= tol).all())
+    # the general kernel multiplies exactly dequantized weights in f32, the tuned ones f16 operands:
+    # both are within 1e-3 of the exact product, and each output is rounded to bf16 once
+    err = (y_odd.float() - y_ref.float()).norm() / y_ref.float().norm()
+    assert float(err) <= 2e-3 + 2.0 ** -8

@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(256, MR >= 8 ? 2 : 3) in_out_rows_kernel(const
     __shared__ uint32_t last_s;
     // [256 byte values][32 lanes] pairs {level of the low nibble, level of the high nibble}
     float2 *lut = reinterpret_cast<float2 *>(dyn);
-    float *xs = dyn + 256 * 32 * 2;                   // [MR][k_chunk]
+    float *xs = dyn + 256 * 32 * 2;                   // [k_chunk][MR]
     float *red = xs + (size_t)MR * p.k_chunk;         // [MR][8][32]: column 8 * lane + i at [i][lane]
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t strip = blockIdx.x, part = blockIdx.y;
@@ -206,8 +206,8 @@ __global__ void __launch_bounds__(256, MR >= 8 ? 2 : 3) in_out_rows_kernel(const
     }
     const T *x = static_cast<const T *>(p.x);
     for (uint32_t i = tid; i < MR * p.k_chunk; i += 256) {
-        const uint32_t m = i / p.k_chunk, kk = i - m * p.k_chunk;
-        xs[i] = (m < p.rows && kk < kc) ? to_f32<T>(x[(uint64_t)m * p.d_in + k_begin + kk]) : 0.0f;
+        const uint32_t m = i / p.k_chunk, kk = i - m * p.k_chunk;  // consecutive threads read consecutive k
+        xs[kk * MR + m] = (m < p.rows && kk < kc) ? to_f32<T>(x[(uint64_t)m * p.d_in + k_begin + kk]) : 0.0f;
     }
     __syncthreads();
 
@@ -226,43 +226,45 @@ __global__ void __launch_bounds__(256, MR >= 8 ? 2 : 3) in_out_rows_kernel(const
         // warp's rows are eight apart.
         constexpr uint32_t D = MR <= 2 ? 12 : (MR == 4 ? 8 : 4);
         const uint32_t my_rows = kc > warp ? (kc - warp + kRowsWarps - 1) / kRowsWarps : 0u;
-        const uint64_t first = k_begin + warp;
-        const uint32_t *code_ptr = reinterpret_cast<const uint32_t *>(p.packed + (n >> 1) + first * (p.d_out >> 1));
-        const size_t code_step = (size_t)kRowsWarps * (p.d_out >> 3);          // in 32-bit words
-        const size_t scale_step = (size_t)kRowsWarps * blocks_per_row;
-        const float *abs_ptr = DQ ? nullptr : p.absmax + first * blocks_per_row + (n >> 6);
-        const uint8_t *sc_ptr = DQ ? p.scale_codes + first * blocks_per_row + (n >> 6) : nullptr;
-        const float *x_ptr = xs + warp;
+        // rows of W are addressed as base + row number * pitch (one wide multiply-add each); the
+        // table and the activations through 32-bit shared-memory addresses
+        const uint32_t *code_base = reinterpret_cast<const uint32_t *>(p.packed + (n >> 1) + (k_begin + warp) * (p.d_out >> 1));
+        const uint32_t code_pitch = (uint32_t)(kRowsWarps * (p.d_out >> 3));         // 32-bit words between this warp's rows
+        const uint32_t scale_pitch = (uint32_t)(kRowsWarps * blocks_per_row);
+        const float *abs_base = DQ ? nullptr : p.absmax + (k_begin + warp) * blocks_per_row + (n >> 6);
+        const uint8_t *sc_base = DQ ? p.scale_codes + (k_begin + warp) * blocks_per_row + (n >> 6) : nullptr;
+        uint32_t lut_lane;
+        asm("{ .reg .u64 t; cvta.to.shared.u64 t, %1; cvt.u32.u64 %0, t; }" : "=r"(lut_lane) : "l"(lut));
+        lut_lane += lane * 8u;
+        const float *x_ptr = xs + warp * MR;
         uint32_t codes[D];
         float scale[D];
         uint32_t fetched = 0;  // rows asked for so far
         auto fetch = [&](uint32_t slot) {
             const bool in = fetched < my_rows;
+            codes[slot] = in ? __ldg(code_base + (size_t)fetched * code_pitch) : 0u;
+            if (DQ) scale[slot] = in ? dq_scale(__ldg(sc_base + (size_t)fetched * scale_pitch), sos) : 0.0f;
+            else scale[slot] = in ? __ldg(abs_base + (size_t)fetched * scale_pitch) : 0.0f;
             ++fetched;
-            codes[slot] = in ? __ldg(code_ptr) : 0u;
-            if (DQ) scale[slot] = in ? dq_scale(__ldg(sc_ptr), sos) : 0.0f;
-            else scale[slot] = in ? __ldg(abs_ptr) : 0.0f;
-            code_ptr += code_step;
-            if (DQ) sc_ptr += scale_step;
-            else abs_ptr += scale_step;
         };
         auto multiply = [&](uint32_t slot) {
             float w[8];
             #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                // byte b of the codes to bits 8..15, this lane's offset below it: the entry's address
-                const uint32_t off = __byte_perm(codes[slot], lane * 8u, 0x7604u | ((uint32_t)b << 4));
-                const float2 lv = *reinterpret_cast<const float2 *>(reinterpret_cast<const uint8_t *>(lut) + off);
-                w[2 * b] = __fmul_rn(lv.x, scale[slot]);
-                w[2 * b + 1] = __fmul_rn(lv.y, scale[slot]);
+                // byte b of the codes times 256 plus this lane's place in the entry: the pair's address
+                const uint32_t at = __byte_perm(codes[slot], 0u, 0x4404u | ((uint32_t)b << 4)) + lut_lane;
+                float lo, hi;
+                asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(lo), "=f"(hi) : "r"(at));
+                w[2 * b] = __fmul_rn(lo, scale[slot]);
+                w[2 * b + 1] = __fmul_rn(hi, scale[slot]);
             }
             #pragma unroll
             for (int m = 0; m < MR; ++m) {
-                const float xv = x_ptr[m * p.k_chunk];
+                const float xv = x_ptr[m];
                 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[m][i] = fmaf(xv, w[i], acc[m][i]);
             }
-            x_ptr += kRowsWarps;
+            x_ptr += kRowsWarps * MR;
         };
         #pragma unroll
         for (uint32_t d = 0; d < D; ++d) fetch(d);
@@ -349,7 +351,10 @@ bool rows_plan(uint64_t d_in, uint64_t d_out, RowsPlan &rp) {
     if (d_out % kBlock != 0 || d_in == 0 || d_in >= (1ull << 31) || d_out >= (1ull << 31)) return false;
     rp.strips = (uint32_t)((d_out + kStripCols - 1) / kStripCols);
     if (rp.strips > 248) return false;  // a byte counter per strip in the workspace's 62 counter words
-    uint64_t parts = (3ull * kNumSMs + rp.strips - 1) / rp.strips;  // three CTAs per SM (64 KB of table each)
+    // three CTAs per SM (64 KB of table each), and no more CTAs than fit at once: a second,
+    // partly filled round would double the time
+    uint64_t parts = 3ull * kNumSMs / rp.strips;
+    if (parts == 0) parts = 1;
     const uint64_t most = d_in / 64 ? d_in / 64 : 1;  // a piece keeps 64 rows of W at least
     if (parts > most) parts = most;
     if (parts > 255) parts = 255;
