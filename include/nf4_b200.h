@@ -299,6 +299,36 @@ NF4_API int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint
  * results do not depend on it.  No counterpart in the reference (single device, no streams). */
 NF4_API int32_t nf4_reserve_sms(int32_t count);
 
+/* A column-sharded layer at decode sizes without a collective: every rank's kernel stores its
+ * columns straight into every rank's output over NVLink (plain peer stores from the epilogue; no
+ * gather buffer, no all-gather kernel, no copy).  The host maps each rank's output and arrival
+ * counter into every process (CUDA IPC or any other peer mapping) and passes them here:
+ *   y_full[r]   rank r's output [rows, ldy_full] (0 = world * d_out) as mapped into THIS process;
+ *               this rank's columns start at rank * d_out in each of them,
+ *   arrivals[r] rank r's 32-bit arrival counter, likewise (zero at first use).
+ * `shard` describes this rank's slice as for nf4_sharded_linear_forward_dev (its y is ignored);
+ * rows <= 16 and a shape the decode kernel takes, up to eight ranks (NF4_ERR_UNSUPPORTED otherwise).
+ * Every CTA of the kernel, when its stores are out, makes them visible system-wide and adds one
+ * to every rank's counter; *ctas_per_call (may be NULL) receives how many CTAs that is.
+ * nf4_peer_arrivals_wait_dev enqueues the other half: a one-thread kernel that waits (at most
+ * timeout_ns, then NF4_ERR_TIMEOUT shows in nf4_device_status) until `expected` arrivals -- the
+ * sum of ctas_per_call over the ranks and over the forwards since the last wait -- are on this
+ * rank's own counter and takes them off it; kernels behind it in the stream see all columns.
+ * A rank may run ahead of another by less than one wait: outputs that are still being read when
+ * the next forwards are issued need a second buffer (and its own counter).
+ * The reference has no multi-GPU path (see nf4_sharded_linear_forward_dev). */
+typedef struct nf4_peer_outputs {
+    uint32_t struct_bytes;      /* sizeof(nf4_peer_outputs) */
+    int32_t world, rank;
+    void *y_full[8];
+    uint64_t ldy_full;
+    uint32_t *arrivals[8];
+} nf4_peer_outputs;
+NF4_API int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_peer_outputs *peers,
+                                               uint32_t *ctas_per_call, void *stream);
+NF4_API int32_t nf4_peer_arrivals_wait_dev(uint32_t *own_arrivals, uint32_t expected, uint32_t timeout_ns,
+                                           void *stream);
+
 /* Decode-sized forward for callers that cannot allocate or own device memory.
  * No counterpart in the reference (its forward allocates a fresh f32 weight on every call).
  *

@@ -117,6 +117,119 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
+def _share(t):
+    """CUDA IPC handle of a tensor's storage (what torch.multiprocessing sends between processes)."""
+    return t.untyped_storage()._share_cuda_()
+
+
+def _open(handle, dtype, shape, device_index):
+    """Maps another process's allocation into THIS process's device `device_index` (the handle's
+    first element names the device to make current while it is opened: the importing GPU, whose
+    kernels will store into the memory, as NCCL's peer transport does; opened under the exporting
+    device instead, the mapping belongs to that device's context and kernels of this one fault)."""
+    st = torch.UntypedStorage._new_shared_cuda(device_index, *handle[1:])
+    return torch.empty(0, dtype=dtype, device=st.device).set_(st).view(*shape)
+
+
+def _scatter_worker(rank, world, port, results):
+    """Every rank's decode kernel stores its columns into every rank's output (peer stores through
+    IPC-mapped buffers, arrival counters, the bounded wait kernel); no collective on the data path."""
+    import torch.distributed as dist
+
+    from unifur_b200 import _lib
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    ok = True
+    peers_y = peers_c = None
+    try:
+        L = _lib.load()
+        k, n, r = 4096, 1024, 16
+        nl = n // world
+        rows_max = 16
+        y_mine = torch.zeros(rows_max, n, dtype=torch.bfloat16, device=dev)
+        cnt_mine = torch.zeros(64, dtype=torch.int32, device=dev)
+        handles = [None] * world
+        dist.all_gather_object(handles, (_share(y_mine), _share(cnt_mine)))
+        for i in range(world):
+            assert i == rank or torch.cuda.can_device_access_peer(rank, i)
+        peers_y = [y_mine if i == rank else _open(handles[i][0], torch.bfloat16, (rows_max, n), rank)
+                   for i in range(world)]
+        peers_c = [cnt_mine if i == rank else _open(handles[i][1], torch.int32, (64,), rank) for i in range(world)]
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.Generator(device=dev).manual_seed(123)     # the same layer on every rank
+        w = torch.randn(n * k, device=dev, generator=g) * 0.02
+        full = PackedNf4Tensor.quantize(w)
+        la = (torch.randn(r, k, device=dev, generator=g) * 0.01).bfloat16()
+        lb = (torch.randn(n, r, device=dev, generator=g) * 0.01).bfloat16()
+        codes = full.codes[rank * nl * (k // 2):(rank + 1) * nl * (k // 2)].contiguous()
+        absmax = full.absmax[rank * nl * (k // 64):(rank + 1) * nl * (k // 64)].contiguous()
+        lb_l = lb[rank * nl:(rank + 1) * nl].contiguous()
+        for m in (1, 8, 16):
+            x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+            y_ref = linear_forward(x, full, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=2.0)
+            ws = torch.zeros(max(int(L.nf4_linear_workspace_bytes(m, k, nl, r)), 256), dtype=torch.uint8, device=dev)
+            a = _lib.LinearArgs()
+            a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+            a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16
+            a.rows, a.d_in, a.d_out = m, k, nl
+            a.x, a.packed, a.absmax = x.data_ptr(), codes.data_ptr(), absmax.data_ptr()
+            a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb_l.data_ptr(), r, 2.0
+            a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            po = _lib.PeerOutputs()
+            po.struct_bytes = ctypes.sizeof(_lib.PeerOutputs)
+            po.world, po.rank, po.ldy_full = world, rank, n
+            for i in range(world):
+                po.y_full[i] = peers_y[i].data_ptr()
+                po.arrivals[i] = peers_c[i].data_ptr()
+            ctas = ctypes.c_uint32(0)
+            for _rep in range(3):  # the counters come back to zero after every wait
+                y_mine.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()      # nobody writes into an output that is still being cleared
+                _lib.check(L.nf4_linear_forward_scatter_dev(ctypes.byref(a), ctypes.byref(po), ctypes.byref(ctas), None))
+                _lib.check(L.nf4_peer_arrivals_wait_dev(ctypes.c_void_p(cnt_mine.data_ptr()), world * ctas.value,
+                                                        2_000_000_000, None))
+                torch.cuda.synchronize()
+                good = torch.equal(y_mine[:m], y_ref) and int(cnt_mine[0].item()) == 0
+                if not good:
+                    print(f"rank {rank} m {m}: scattered output differs or counter not back at zero "
+                          f"({int(cnt_mine[0].item())})", flush=True)
+                ok &= good
+                dist.barrier()      # everyone has compared before the next round overwrites
+        d0, d1, d2 = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+        ok &= L.nf4_device_status(ctypes.byref(d0), ctypes.byref(d1), ctypes.byref(d2)) == 0
+    finally:
+        results[rank] = 1 if ok else 0
+        torch.cuda.synchronize()
+        dist.barrier()
+        del peers_y, peers_c
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_scattered_decode_forward_on_two_gpus():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    results = ctx.Array("i", [0] * world)
+    port = _free_port()
+    procs = [ctx.Process(target=_scatter_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert list(results) == [1] * world
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_sharded_forward_on_two_gpus():
     import torch.multiprocessing as mp

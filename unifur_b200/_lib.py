@@ -26,6 +26,12 @@ class Nf4Error(RuntimeError):
         self.status = status
 
 
+class PeerOutputs(C.Structure):
+    """``nf4_peer_outputs`` (include/nf4_b200.h)."""
+    _fields_ = [("struct_bytes", C.c_uint32), ("world", C.c_int32), ("rank", C.c_int32),
+                ("y_full", C.c_void_p * 8), ("ldy_full", C.c_uint64), ("arrivals", C.c_void_p * 8)]
+
+
 class LinearArgs(C.Structure):
     """Mirror of ``nf4_linear_args`` (include/nf4_b200.h)."""
 
@@ -97,6 +103,8 @@ SIGNATURES = {
     "nf4_linear_noalloc_scratch_bytes": (_u64, []),
     "nf4_linear_forward_grouped_dev": (_i32, [C.POINTER(LinearArgs), _u32, _vp]),
     "nf4_reserve_sms": (_i32, [_i32]),
+    "nf4_linear_forward_scatter_dev": (_i32, [C.POINTER(LinearArgs), C.POINTER(PeerOutputs), C.POINTER(_u32), _vp]),
+    "nf4_peer_arrivals_wait_dev": (_i32, [_vp, _u32, _u32, _vp]),
     "nf4_linear_forward_noalloc_dev": (_i32, [C.POINTER(LinearArgs), _vp]),
     "nf4_weight_from_values_host": (_i32, [_vp, _u64, _u64, _i32, _i32, C.POINTER(_vp)]),
     "nf4_weight_from_packed_host": (_i32, [_vp, _vp, _vp, _f32, _u64, _u64, _i32,

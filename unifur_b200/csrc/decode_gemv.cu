@@ -130,6 +130,12 @@ struct DecodeParams {
     uint64_t ldy;
     uint32_t y_f32;
     uint32_t y_pair;       // bf16 y whose even columns are 4-byte aligned in every row
+    // Sharded layer whose ranks write their columns straight into every rank's output (PEERS):
+    // dest[d] is rank d's output as mapped into this process, already at this rank's first
+    // column, with row stride ldy; arrive[d] is rank d's arrival counter.
+    void *dest[8];
+    uint32_t *arrive[8];
+    uint32_t n_dest;
     uint32_t M, K, N, rank;
     float lora_scale;
     // CTA c owns rows_base rows, and gran more if light_front <= c < light_front + rows_extra;
@@ -189,7 +195,7 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
 // One CTA's share of one forward.  `bid` of `nctas`: the CTA's number among the CTAs of this
 // forward (a launch can hold several forwards).  SPLIT: K is longer than a CTA's sixteen slices
 // and groups of CTAs multiply parts of it.  The descriptors and `p` are kernel parameters.
-template <int NT, bool DQ, bool SPLIT>
+template <int NT, bool DQ, bool SPLIT, bool PEERS = false>
 __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const CUtensorMap *tm_scales,
                                             const DecodeParams &p, const uint32_t bid, const uint32_t nctas) {
     using C = Cfg;
@@ -722,14 +728,18 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
                     if (two) o1 += __ldg(p.bias + col + 1);
                 }
                 const size_t at = (size_t)(m0 + b) * p.ldy + col;
-                if (p.y_f32) {
-                    static_cast<float *>(p.y)[at] = o0;
-                    if (two) static_cast<float *>(p.y)[at + 1] = o1;
-                } else if (pair) {
-                    *reinterpret_cast<__nv_bfloat162 *>(static_cast<__nv_bfloat16 *>(p.y) + at) = __floats2bfloat162_rn(o0, o1);
-                } else {
-                    static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(o0);
-                    if (two) static_cast<__nv_bfloat16 *>(p.y)[at + 1] = __float2bfloat16_rn(o1);
+                const uint32_t n_dest = PEERS ? p.n_dest : 1u;
+                for (uint32_t d = 0; d < n_dest; ++d) {  // (the same values to every rank's output)
+                    void *yb = PEERS ? p.dest[d] : p.y;
+                    if (p.y_f32) {
+                        static_cast<float *>(yb)[at] = o0;
+                        if (two) static_cast<float *>(yb)[at + 1] = o1;
+                    } else if (pair) {
+                        *reinterpret_cast<__nv_bfloat162 *>(static_cast<__nv_bfloat16 *>(yb) + at) = __floats2bfloat162_rn(o0, o1);
+                    } else {
+                        static_cast<__nv_bfloat16 *>(yb)[at] = __float2bfloat16_rn(o0);
+                        if (two) static_cast<__nv_bfloat16 *>(yb)[at + 1] = __float2bfloat16_rn(o1);
+                    }
                 }
             }
         }
@@ -763,9 +773,22 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
                 for (uint32_t q = 0; q < p.kparts; ++q) o += __ldcg(p.partial + ((size_t)q * p.M + m) * p.N + col);
                 if (p.bias) o += __ldg(p.bias + col);
                 const size_t at = (size_t)m * p.ldy + col;
-                if (p.y_f32) static_cast<float *>(p.y)[at] = o;
-                else static_cast<__nv_bfloat16 *>(p.y)[at] = __float2bfloat16_rn(o);
+                const uint32_t n_dest = PEERS ? p.n_dest : 1u;
+                for (uint32_t d = 0; d < n_dest; ++d) {
+                    void *yb = PEERS ? p.dest[d] : p.y;
+                    if (p.y_f32) static_cast<float *>(yb)[at] = o;
+                    else static_cast<__nv_bfloat16 *>(yb)[at] = __float2bfloat16_rn(o);
+                }
             }
+        }
+    }
+    if (PEERS) {
+        // every store of this CTA has been issued: make them visible to the other GPUs, then
+        // count this CTA in on every rank's arrival counter
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            for (uint32_t d = 0; d < p.n_dest; ++d) atomicAdd_system(p.arrive[d], 1u);
         }
     }
     if (done_old == nctas - 1) {
@@ -776,11 +799,29 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
     }
 }
 
-template <int NT, bool DQ, bool SPLIT>
+template <int NT, bool DQ, bool SPLIT, bool PEERS>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_codes,
               const __grid_constant__ CUtensorMap tm_scales, const __grid_constant__ DecodeParams p) {
-    decode_body<NT, DQ, SPLIT>(&tm_codes, &tm_scales, p, blockIdx.x, gridDim.x);
+    decode_body<NT, DQ, SPLIT, PEERS>(&tm_codes, &tm_scales, p, blockIdx.x, gridDim.x);
+}
+
+// Waits (bounded) until `expected` CTAs of the ranks of a sharded layer have counted themselves in
+// on this rank's arrival counter, then takes them off the counter: the kernels behind it in the
+// stream find every rank's columns in this rank's output.
+__global__ void peer_wait_kernel(uint32_t *counter, uint32_t expected, uint32_t limit_ns) {
+    const uint64_t t0 = ptx::global_timer_ns();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= expected) break;
+        if (ptx::global_timer_ns() - t0 > (uint64_t)limit_ns) {
+            atomicExch(&g_decode_error, 7);
+            return;
+        }
+        __nanosleep(100);
+    }
+    atomicSub(counter, expected);
 }
 
 // Several forwards of the same activations (projections that share their input) in one launch:
@@ -977,18 +1018,22 @@ bool plan(const nf4_linear_args &a, Plan &pl, uint32_t max_ctas = 0) {
     return true;
 }
 
-template <int NT, bool DQ, bool SPLIT>
+template <int NT, bool DQ, bool SPLIT, bool PEERS>
 int32_t launch_as(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
     using C = Cfg;
-    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(decode_kernel<NT, DQ, SPLIT>), (int)C::kSmemBytes));
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(decode_kernel<NT, DQ, SPLIT, PEERS>), (int)C::kSmemBytes));
     count_launch();
-    return launch_maybe_overlapped(decode_kernel<NT, DQ, SPLIT>, dim3(pl.grid), dim3(C::kThreads),
+    return launch_maybe_overlapped(decode_kernel<NT, DQ, SPLIT, PEERS>, dim3(pl.grid), dim3(C::kThreads),
                                    C::kSmemBytes, stream, true, mc, ms, pl.p);
 }
 
 template <int NT, bool DQ>
 int32_t launch(const CUtensorMap &mc, const CUtensorMap &ms, const Plan &pl, cudaStream_t stream) {
-    return pl.p.kparts > 1 ? launch_as<NT, DQ, true>(mc, ms, pl, stream) : launch_as<NT, DQ, false>(mc, ms, pl, stream);
+    if (pl.p.n_dest)
+        return pl.p.kparts > 1 ? launch_as<NT, DQ, true, true>(mc, ms, pl, stream)
+                               : launch_as<NT, DQ, false, true>(mc, ms, pl, stream);
+    return pl.p.kparts > 1 ? launch_as<NT, DQ, true, false>(mc, ms, pl, stream)
+                           : launch_as<NT, DQ, false, false>(mc, ms, pl, stream);
 }
 
 // bytes of T in the workspace: a share per part of K (room for two where K is not split)
@@ -1113,6 +1158,35 @@ int32_t decode_forward_grouped(const nf4_linear_args *a, uint32_t count, cudaStr
     const bool dq = a[0].scale_codes != nullptr;
     if (a[0].rows <= 8) return dq ? launch_group<1, true>(gp, stream) : launch_group<1, false>(gp, stream);
     return dq ? launch_group<2, true>(gp, stream) : launch_group<2, false>(gp, stream);
+}
+
+// The forward of one rank's column shard, stored into every rank's output.  `dest`: the outputs
+// [rows, ldy] as mapped here, `arrive`: the ranks' arrival counters.  *ctas: CTAs that will count
+// themselves in (what the ranks' waits add up).
+int32_t decode_forward_scatter(const nf4_linear_args &a, void *const *dest, uint32_t *const *arrive, uint32_t world,
+                               uint32_t rank, uint64_t ldy, uint32_t *ctas, cudaStream_t stream) {
+    Plan pl;
+    if (world == 0 || world > 8 || rank >= world || !plan(a, pl))
+        return fail(NF4_ERR_UNSUPPORTED, "decode_forward_scatter: decode shapes and up to eight ranks only");
+    DecodeParams &p = pl.p;
+    const size_t eb = a.y_f32 ? 4 : 2;
+    p.ldy = ldy;
+    p.n_dest = world;
+    p.y_pair = (!a.y_f32 && (ldy & 1u) == 0 && ((rank * a.d_out) & 1u) == 0) ? 1u : 0u;
+    for (uint32_t d = 0; d < world; ++d) {
+        if (!dest[d] || !arrive[d]) return fail(NF4_ERR_INVALID_ARG, "decode_forward_scatter: null output or counter of rank %u", d);
+        p.dest[d] = static_cast<uint8_t *>(dest[d]) + (size_t)rank * a.d_out * eb;
+        p.arrive[d] = arrive[d];
+        if (reinterpret_cast<uintptr_t>(p.dest[d]) & 3u) p.y_pair = 0;
+    }
+    if (ctas) *ctas = pl.grid;
+    return run(a, pl, a.workspace, stream);
+}
+
+int32_t decode_peer_wait(uint32_t *counter, uint32_t expected, uint32_t limit_ns, cudaStream_t stream) {
+    peer_wait_kernel<<<1, 1, 0, stream>>>(counter, expected, limit_ns);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "peer_wait_kernel launch");
 }
 
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
