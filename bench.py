@@ -281,7 +281,18 @@ def run_own(args) -> None:
         for par in range(2):
             ys[(m, par)] = y_all[par][row0:row0 + m]
         row0 += m
-    y_gathered = [torch.zeros(world, sum(MS), N, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    # Sharded runs: every rank's kernel stores its columns straight into every rank's output
+    # [rows, world * N] (peer stores over NVLink through IPC-mapped buffers), and a step ends with a
+    # bounded wait for all ranks' CTAs on this rank's arrival counter: no collective, no copy.
+    # Two outputs and counters, used by alternate steps (a rank may be one step ahead of another).
+    y_full = arrivals = peer_y = peer_arr = None
+    if world > 1:
+        from unifur_b200.sharded import map_peer_tensors
+
+        y_full = [torch.zeros(sum(MS), world * N, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+        arrivals = torch.zeros(64, device=dev, dtype=torch.int32)
+        peer_y = [map_peer_tensors(y_full[par]) for par in range(2)]
+        peer_arr = map_peer_tensors(arrivals)
     ws_bytes = max(int(lib.nf4_linear_workspace_bytes(m, K, N, RANK)) for m in MS)
     workspaces = {m: torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev) for m in MS}
 
@@ -300,36 +311,49 @@ def run_own(args) -> None:
         return a
 
     call_args = {(c, m, par): make_args(c, m, par) for c in range(N_COPIES) for m in MS for par in range(2)}
+    # A step's last forward signals (one arrival per rank on every rank's counter of the step's
+    # output); the next step's first forward waits for them inside the kernel before it reads its
+    # input, as the next layer of a sharded model would; the first step of a sequence waits for
+    # nothing and a wait kernel closes the sequence.
+    peer_out = {}
+    if world > 1:
+        row0 = 0
+        for j, m in enumerate(MS):
+            for par in range(2):
+                for first in (False, True):
+                    po = _lib.PeerOutputs()
+                    po.struct_bytes = ctypes.sizeof(_lib.PeerOutputs)
+                    po.world, po.rank, po.ldy_full = world, rank, world * N
+                    for r in range(world):
+                        po.y_full[r] = peer_y[par][r][row0:].data_ptr()
+                        po.arrivals[r] = peer_arr[r][par:par + 1].data_ptr()
+                    po.signal = 1 if j == len(MS) - 1 else 0
+                    if j == 0 and not first:
+                        po.wait_arrivals = arrivals[(par ^ 1):(par ^ 1) + 1].data_ptr()
+                        po.wait_expected = world
+                    peer_out[(m, par, first)] = po
+            row0 += m
     log("weights quantized, arguments built")
 
-    comm = torch.cuda.Stream() if world > 1 else None
-    gathered = [None, None]  # per buffer: the event after the gather that last read it
-
-    def step(i: int) -> None:
+    def step(i: int, first: bool = False) -> None:
         cur = torch.cuda.current_stream()
         stream = ctypes.c_void_p(cur.cuda_stream)
         par = i & 1
-        if world > 1 and gathered[par] is not None:
-            cur.wait_event(gathered[par])  # the buffer is written again only after its gather
         for j, m in enumerate(MS):
             c = (len(MS) * i + j) % N_COPIES  # a different weight copy for every pass
-            _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, par)]), stream))
-        if world > 1:
-            # every rank's slab of the step's outputs, gathered beside the next step's passes
-            done = torch.cuda.Event()
-            done.record(cur)
-            comm.wait_event(done)
-            with torch.cuda.stream(comm):
-                dist.all_gather_into_tensor(y_gathered[par], y_all[par])
-                gathered[par] = torch.cuda.Event()
-                gathered[par].record(comm)
+            if world == 1:
+                _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, par)]), stream))
+            else:
+                _lib.check(lib.nf4_linear_forward_scatter_dev(ctypes.byref(call_args[(c, m, par)]),
+                                                              ctypes.byref(peer_out[(m, par, first)]), stream))
 
-    def drain() -> None:
-        """The launching stream waits for the gathers still in flight (and joins their stream)."""
-        for par in range(2):
-            if gathered[par] is not None:
-                torch.cuda.current_stream().wait_event(gathered[par])
-                gathered[par] = None
+    def drain(last: int) -> None:
+        """Closes a sequence of steps: the last step's outputs are whole on this rank once every
+        rank has signalled."""
+        if world > 1:
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _lib.check(lib.nf4_peer_arrivals_wait_dev(ctypes.c_void_p(arrivals[(last & 1):(last & 1) + 1].data_ptr()),
+                                                      world, 2_000_000_000, stream))
 
     def barrier():
         torch.cuda.synchronize()
@@ -341,9 +365,30 @@ def run_own(args) -> None:
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         for i in range(max(args.warmup, 3)):
-            step(i)
-        drain()
+            step(i, i == 0)
+        drain(max(args.warmup, 3) - 1)
     barrier()
+    scatter_check = "n/a"
+    if world > 1:
+        # the last warm-up step's output on this rank against every rank's own columns (computed
+        # with the plain forward into a local buffer and exchanged with NCCL, off the timed path)
+        last = max(args.warmup, 3) - 1
+        mine = torch.zeros(sum(MS), N, device=dev, dtype=torch.bfloat16)
+        with torch.cuda.stream(side):
+            r0 = 0
+            for j, m in enumerate(MS):
+                a = make_args((len(MS) * last + j) % N_COPIES, m, 0)
+                a.y = mine[r0:].data_ptr()
+                _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), ctypes.c_void_p(side.cuda_stream)))
+                r0 += m
+        torch.cuda.synchronize()
+        everyone = torch.zeros(world, sum(MS), N, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(everyone, mine)
+        got = y_full[last & 1].view(sum(MS), world, N).transpose(0, 1)
+        same = torch.tensor([1 if torch.equal(got, everyone) else 0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        scatter_check = "ok" if int(same.item()) else "MISMATCH"
+        barrier()
     log("warm-up done")
     launches0 = _lib.launch_count()
     launch_mode = "cuda-graph"
@@ -352,12 +397,11 @@ def run_own(args) -> None:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             for i in range(args.steps):
-                step(i)
-            drain()
-    except Exception as e:  # capture refused (e.g. a collective that cannot be captured)
+                step(i, i == 0)
+            drain(args.steps - 1)
+    except Exception as e:  # capture refused
         graph = None
         launch_mode = f"eager ({type(e).__name__})"
-        gathered[0] = gathered[1] = None
         torch.cuda.synchronize()
     gpu_launches = _lib.launch_count() - launches0
     if world > 1:
@@ -388,8 +432,8 @@ def run_own(args) -> None:
                 graph.replay()
             else:
                 for i in range(args.steps):
-                    step(i)
-                drain()
+                    step(i, i == 0)
+                drain(args.steps - 1)
             e1.record()
         barrier()
         rep_ms.append(e0.elapsed_time(e1))
@@ -440,7 +484,7 @@ def run_own(args) -> None:
         x_host = {m: xs[m].cpu().pin_memory() for m in MS}
         y_host = {m: torch.zeros(m, N, dtype=torch.bfloat16).pin_memory() for m in MS}
 
-        y_all_host = torch.zeros(world, sum(MS), N, dtype=torch.bfloat16).pin_memory()
+        y_all_host = torch.zeros(sum(MS), world * N, dtype=torch.bfloat16).pin_memory()
 
         def host_step(i):
             if world == 1:
@@ -451,16 +495,14 @@ def run_own(args) -> None:
                         h, vp(x_host[m].data_ptr()), m, _lib.DTYPE_BF16, None, None, None, 0, 0.0,
                         vp(y_host[m].data_ptr())))
                 return
-            # a sharded layer end to end: host x in, the shard's forwards, the all-gather of y,
-            # the whole gathered y out to the host
+            # a sharded layer end to end: host x in, the shard's forwards storing into every rank's
+            # output, the wait for all ranks' columns, the whole output out to the host
             cur = torch.cuda.current_stream()
-            stream = ctypes.c_void_p(cur.cuda_stream)
-            for j, m in enumerate(MS):
+            for m in MS:
                 xs[m].copy_(x_host[m], non_blocking=True)
-                c = (len(MS) * i + j) % N_COPIES
-                _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, 0)]), stream))
-            dist.all_gather_into_tensor(y_gathered[0], y_all[0])
-            y_all_host.copy_(y_gathered[0], non_blocking=True)
+            step(i, True)
+            drain(i)
+            y_all_host.copy_(y_full[i & 1], non_blocking=True)
             cur.synchronize()
 
         for i in range(max(args.warmup, 3)):
@@ -479,8 +521,9 @@ def run_own(args) -> None:
             "d2h_bytes_per_step": sum(m * N * 2 for m in MS) * world,
             "api": "nf4_weight_linear_forward_host (pinned host x in, host y out, synchronous)"
                    if world == 1 else
-                   "per rank: pinned host x in, nf4_linear_forward_dev on the shard, NCCL all-gather of y, "
-                   "gathered y out to the host, synchronous",
+                   "per rank: pinned host x in, nf4_linear_forward_scatter_dev on the shard (its columns go to every "
+                   "rank's output, the last forward signals), nf4_peer_arrivals_wait_dev, the whole [rows, world * N] "
+                   "output out to the host, synchronous",
         }
         for h in handles:
             lib.nf4_weight_free(h)
@@ -540,8 +583,9 @@ def run_own(args) -> None:
                                 "per pass",
                        "launch": launch_mode,
                        "sharding": "none" if world == 1 else
-                       f"{world} column shards of a [{world * N}, {K}] layer, one NCCL all-gather of y per step "
-                       "on its own stream"},
+                       f"{world} column shards of a [{world * N}, {K}] layer: every rank's kernel stores its columns "
+                       "into every rank's output over NVLink, a step's last forward signals and the next step's "
+                       f"first forward waits for all ranks inside the kernel (scatter_check: {scatter_check})"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(gpu_launches), "clocks": clocks,
             "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,

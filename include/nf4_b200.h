@@ -302,18 +302,25 @@ NF4_API int32_t nf4_reserve_sms(int32_t count);
 /* A column-sharded layer at decode sizes without a collective: every rank's kernel stores its
  * columns straight into every rank's output over NVLink (plain peer stores from the epilogue; no
  * gather buffer, no all-gather kernel, no copy).  The host maps each rank's output and arrival
- * counter into every process (CUDA IPC or any other peer mapping) and passes them here:
+ * counter into every process (CUDA IPC opened with the importing device current, or any other
+ * peer mapping) and passes them here:
  *   y_full[r]   rank r's output [rows, ldy_full] (0 = world * d_out) as mapped into THIS process;
  *               this rank's columns start at rank * d_out in each of them,
  *   arrivals[r] rank r's 32-bit arrival counter, likewise (zero at first use).
- * `shard` describes this rank's slice as for nf4_sharded_linear_forward_dev (its y is ignored);
- * rows <= 16 and a shape the decode kernel takes, up to eight ranks (NF4_ERR_UNSUPPORTED otherwise).
- * Every CTA of the kernel, when its stores are out, makes them visible system-wide and adds one
- * to every rank's counter; *ctas_per_call (may be NULL) receives how many CTAs that is.
- * nf4_peer_arrivals_wait_dev enqueues the other half: a one-thread kernel that waits (at most
- * timeout_ns, then NF4_ERR_TIMEOUT shows in nf4_device_status) until `expected` arrivals -- the
- * sum of ctas_per_call over the ranks and over the forwards since the last wait -- are on this
- * rank's own counter and takes them off it; kernels behind it in the stream see all columns.
+ * `shard` describes this rank's slice as for nf4_sharded_linear_forward_dev (its y is ignored; its
+ * workspace is needed, 256 bytes at least); rows <= 16 and a shape the decode kernel takes, up to
+ * eight ranks (NF4_ERR_UNSUPPORTED otherwise).
+ *   signal != 0: when the launch's last CTA is done it makes the stores of this launch -- and of
+ *               the launches before it in the stream -- visible system-wide and adds ONE to
+ *               every rank's counter.  A group of forwards into the same outputs signals with
+ *               its last member.
+ *   wait_arrivals / wait_expected: if non-NULL, this forward's x is the output of a sharded
+ *               layer: before reading x every CTA waits (bounded; NF4_ERR_TIMEOUT shows in
+ *               nf4_device_status) until wait_expected arrivals -- one per rank and signal --
+ *               are on this rank's own counter, and the launch takes them off it.
+ * nf4_peer_arrivals_wait_dev is the wait on its own, for consumers that are not this library's
+ * kernels: a one-thread kernel that waits (at most timeout_ns) until `expected` arrivals are on
+ * the counter and takes them off; kernels behind it in the stream see all columns.
  * A rank may run ahead of another by less than one wait: outputs that are still being read when
  * the next forwards are issued need a second buffer (and its own counter).
  * The reference has no multi-GPU path (see nf4_sharded_linear_forward_dev). */
@@ -323,9 +330,12 @@ typedef struct nf4_peer_outputs {
     void *y_full[8];
     uint64_t ldy_full;
     uint32_t *arrivals[8];
+    uint32_t signal;
+    uint32_t wait_expected;
+    uint32_t *wait_arrivals;
 } nf4_peer_outputs;
 NF4_API int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_peer_outputs *peers,
-                                               uint32_t *ctas_per_call, void *stream);
+                                               void *stream);
 NF4_API int32_t nf4_peer_arrivals_wait_dev(uint32_t *own_arrivals, uint32_t expected, uint32_t timeout_ns,
                                            void *stream);
 

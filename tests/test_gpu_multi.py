@@ -117,20 +117,6 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-def _share(t):
-    """CUDA IPC handle of a tensor's storage (what torch.multiprocessing sends between processes)."""
-    return t.untyped_storage()._share_cuda_()
-
-
-def _open(handle, dtype, shape, device_index):
-    """Maps another process's allocation into THIS process's device `device_index` (the handle's
-    first element names the device to make current while it is opened: the importing GPU, whose
-    kernels will store into the memory, as NCCL's peer transport does; opened under the exporting
-    device instead, the mapping belongs to that device's context and kernels of this one fault)."""
-    st = torch.UntypedStorage._new_shared_cuda(device_index, *handle[1:])
-    return torch.empty(0, dtype=dtype, device=st.device).set_(st).view(*shape)
-
-
 def _scatter_worker(rank, world, port, results):
     """Every rank's decode kernel stores its columns into every rank's output (peer stores through
     IPC-mapped buffers, arrival counters, the bounded wait kernel); no collective on the data path."""
@@ -138,6 +124,7 @@ def _scatter_worker(rank, world, port, results):
 
     from unifur_b200 import _lib
     from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+    from unifur_b200.sharded import map_peer_tensors
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -146,7 +133,7 @@ def _scatter_worker(rank, world, port, results):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     ok = True
-    peers_y = peers_c = None
+    peers_y = peers_c = peers_z = None
     try:
         L = _lib.load()
         k, n, r = 4096, 1024, 16
@@ -154,13 +141,8 @@ def _scatter_worker(rank, world, port, results):
         rows_max = 16
         y_mine = torch.zeros(rows_max, n, dtype=torch.bfloat16, device=dev)
         cnt_mine = torch.zeros(64, dtype=torch.int32, device=dev)
-        handles = [None] * world
-        dist.all_gather_object(handles, (_share(y_mine), _share(cnt_mine)))
-        for i in range(world):
-            assert i == rank or torch.cuda.can_device_access_peer(rank, i)
-        peers_y = [y_mine if i == rank else _open(handles[i][0], torch.bfloat16, (rows_max, n), rank)
-                   for i in range(world)]
-        peers_c = [cnt_mine if i == rank else _open(handles[i][1], torch.int32, (64,), rank) for i in range(world)]
+        peers_y = map_peer_tensors(y_mine)     # every rank's output and counters, mapped into this GPU
+        peers_c = map_peer_tensors(cnt_mine)
         torch.cuda.synchronize()
         dist.barrier()
         g = torch.Generator(device=dev).manual_seed(123)     # the same layer on every rank
@@ -171,36 +153,65 @@ def _scatter_worker(rank, world, port, results):
         codes = full.codes[rank * nl * (k // 2):(rank + 1) * nl * (k // 2)].contiguous()
         absmax = full.absmax[rank * nl * (k // 64):(rank + 1) * nl * (k // 64)].contiguous()
         lb_l = lb[rank * nl:(rank + 1) * nl].contiguous()
-        for m in (1, 8, 16):
-            x = torch.randn(m, k, device=dev, generator=g).bfloat16()
-            y_ref = linear_forward(x, full, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=2.0)
-            ws = torch.zeros(max(int(L.nf4_linear_workspace_bytes(m, k, nl, r)), 256), dtype=torch.uint8, device=dev)
+        # a second layer that reads the first one's gathered output: [n2, n], sharded the same way
+        n2 = 512
+        nl2 = n2 // world
+        w2 = torch.randn(n2 * n, device=dev, generator=g) * 0.02
+        full2 = PackedNf4Tensor.quantize(w2)
+        codes2 = full2.codes[rank * nl2 * (n // 2):(rank + 1) * nl2 * (n // 2)].contiguous()
+        absmax2 = full2.absmax[rank * nl2 * (n // 64):(rank + 1) * nl2 * (n // 64)].contiguous()
+        z_mine = torch.zeros(rows_max, n2, dtype=torch.bfloat16, device=dev)
+        peers_z = map_peer_tensors(z_mine)
+
+        def shard_args(m, x_t, d_in, d_out_l, codes_t, absmax_t, rank_r):
+            ws = torch.zeros(max(int(L.nf4_linear_workspace_bytes(m, d_in, d_out_l, rank_r)), 256), dtype=torch.uint8,
+                             device=dev)
             a = _lib.LinearArgs()
             a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
             a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16
-            a.rows, a.d_in, a.d_out = m, k, nl
-            a.x, a.packed, a.absmax = x.data_ptr(), codes.data_ptr(), absmax.data_ptr()
-            a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb_l.data_ptr(), r, 2.0
+            a.rows, a.d_in, a.d_out = m, d_in, d_out_l
+            a.x, a.packed, a.absmax = x_t.data_ptr(), codes_t.data_ptr(), absmax_t.data_ptr()
+            if rank_r:
+                a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb_l.data_ptr(), rank_r, 2.0
             a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            return a, ws
+
+        def outputs(peers, counter_index, ldy, signal, wait_index=None):
             po = _lib.PeerOutputs()
             po.struct_bytes = ctypes.sizeof(_lib.PeerOutputs)
-            po.world, po.rank, po.ldy_full = world, rank, n
+            po.world, po.rank, po.ldy_full = world, rank, ldy
             for i in range(world):
-                po.y_full[i] = peers_y[i].data_ptr()
-                po.arrivals[i] = peers_c[i].data_ptr()
-            ctas = ctypes.c_uint32(0)
-            for _rep in range(3):  # the counters come back to zero after every wait
+                po.y_full[i] = peers[i].data_ptr()
+                po.arrivals[i] = peers_c[i][counter_index:counter_index + 1].data_ptr()
+            po.signal = 1 if signal else 0
+            if wait_index is not None:
+                po.wait_arrivals = cnt_mine[wait_index:wait_index + 1].data_ptr()
+                po.wait_expected = world
+            return po
+
+        for m in (1, 8, 16):
+            x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+            y_ref = linear_forward(x, full, k, n, _lib.LAYOUT_OUT_IN, lora_a=la, lora_b=lb, lora_scale=2.0)
+            z_ref = linear_forward(y_ref, full2, n, n2, _lib.LAYOUT_OUT_IN)
+            a1, ws1 = shard_args(m, x, k, nl, codes, absmax, r)
+            a2, ws2 = shard_args(m, y_mine, n, nl2, codes2, absmax2, 0)   # x of layer 2 = this rank's gathered y
+            po1 = outputs(peers_y, 0, n, signal=True)
+            po2 = outputs(peers_z, 1, n2, signal=True, wait_index=0)       # waits for layer 1's arrivals in the kernel
+            for _rep in range(3):  # the counters come back to zero every time
                 y_mine.zero_()
+                z_mine.zero_()
                 torch.cuda.synchronize()
                 dist.barrier()      # nobody writes into an output that is still being cleared
-                _lib.check(L.nf4_linear_forward_scatter_dev(ctypes.byref(a), ctypes.byref(po), ctypes.byref(ctas), None))
-                _lib.check(L.nf4_peer_arrivals_wait_dev(ctypes.c_void_p(cnt_mine.data_ptr()), world * ctas.value,
+                _lib.check(L.nf4_linear_forward_scatter_dev(ctypes.byref(a1), ctypes.byref(po1), None))
+                _lib.check(L.nf4_linear_forward_scatter_dev(ctypes.byref(a2), ctypes.byref(po2), None))
+                _lib.check(L.nf4_peer_arrivals_wait_dev(ctypes.c_void_p(cnt_mine[1:2].data_ptr()), world,
                                                         2_000_000_000, None))
                 torch.cuda.synchronize()
-                good = torch.equal(y_mine[:m], y_ref) and int(cnt_mine[0].item()) == 0
+                good = (torch.equal(y_mine[:m], y_ref) and torch.equal(z_mine[:m], z_ref)
+                        and int(cnt_mine[0].item()) == 0 and int(cnt_mine[1].item()) == 0)
                 if not good:
-                    print(f"rank {rank} m {m}: scattered output differs or counter not back at zero "
-                          f"({int(cnt_mine[0].item())})", flush=True)
+                    print(f"rank {rank} m {m}: layer 1 equal {torch.equal(y_mine[:m], y_ref)}, layer 2 equal "
+                          f"{torch.equal(z_mine[:m], z_ref)}, counters {cnt_mine[:2].tolist()}", flush=True)
                 ok &= good
                 dist.barrier()      # everyone has compared before the next round overwrites
         d0, d1, d2 = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
@@ -209,7 +220,7 @@ def _scatter_worker(rank, world, port, results):
         results[rank] = 1 if ok else 0
         torch.cuda.synchronize()
         dist.barrier()
-        del peers_y, peers_c
+        del peers_y, peers_c, peers_z
         dist.destroy_process_group()
 
 

@@ -29,7 +29,8 @@ class Nf4Error(RuntimeError):
 class PeerOutputs(C.Structure):
     """``nf4_peer_outputs`` (include/nf4_b200.h)."""
     _fields_ = [("struct_bytes", C.c_uint32), ("world", C.c_int32), ("rank", C.c_int32),
-                ("y_full", C.c_void_p * 8), ("ldy_full", C.c_uint64), ("arrivals", C.c_void_p * 8)]
+                ("y_full", C.c_void_p * 8), ("ldy_full", C.c_uint64), ("arrivals", C.c_void_p * 8),
+                ("signal", C.c_uint32), ("wait_expected", C.c_uint32), ("wait_arrivals", C.c_void_p)]
 
 
 class LinearArgs(C.Structure):
@@ -103,7 +104,7 @@ SIGNATURES = {
     "nf4_linear_noalloc_scratch_bytes": (_u64, []),
     "nf4_linear_forward_grouped_dev": (_i32, [C.POINTER(LinearArgs), _u32, _vp]),
     "nf4_reserve_sms": (_i32, [_i32]),
-    "nf4_linear_forward_scatter_dev": (_i32, [C.POINTER(LinearArgs), C.POINTER(PeerOutputs), C.POINTER(_u32), _vp]),
+    "nf4_linear_forward_scatter_dev": (_i32, [C.POINTER(LinearArgs), C.POINTER(PeerOutputs), _vp]),
     "nf4_peer_arrivals_wait_dev": (_i32, [_vp, _u32, _u32, _vp]),
     "nf4_linear_forward_noalloc_dev": (_i32, [C.POINTER(LinearArgs), _vp]),
     "nf4_weight_from_values_host": (_i32, [_vp, _u64, _u64, _i32, _i32, C.POINTER(_vp)]),

@@ -490,8 +490,7 @@ int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint32_t cou
     return NF4_OK;
 }
 
-int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_peer_outputs *peers,
-                                       uint32_t *ctas_per_call, void *stream) {
+int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_peer_outputs *peers, void *stream) {
     if (!shard || !peers || peers->struct_bytes != sizeof(nf4_peer_outputs))
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward_scatter_dev: null arguments or struct_bytes");
     if (peers->world < 1 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world)
@@ -503,16 +502,16 @@ int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_p
     const uint64_t ldy = peers->ldy_full ? peers->ldy_full : (uint64_t)peers->world * a.d_out;
     if (ldy < (uint64_t)peers->world * a.d_out)
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward_scatter_dev: ldy_full < world * d_out");
-    if (a.rows == 0) {
-        if (ctas_per_call) *ctas_per_call = 0;
-        return NF4_OK;
-    }
+    if (a.rows == 0) return NF4_OK;
     if (!decode_supported(a))
         return fail(NF4_ERR_UNSUPPORTED, "nf4_linear_forward_scatter_dev: only shapes the decode kernel takes "
                                          "(rows <= 16, bf16, W [d_out, d_in], d_in a multiple of 256)");
+    if (!a.workspace || a.workspace_bytes < 256)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward_scatter_dev: the workspace must hold 256 bytes at least");
     t_last_family = 0;
     return decode_forward_scatter(a, peers->y_full, peers->arrivals, (uint32_t)peers->world, (uint32_t)peers->rank,
-                                  ldy, ctas_per_call, static_cast<cudaStream_t>(stream));
+                                  ldy, peers->signal != 0, peers->wait_arrivals, peers->wait_expected,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 int32_t nf4_peer_arrivals_wait_dev(uint32_t *own_arrivals, uint32_t expected, uint32_t timeout_ns, void *stream) {

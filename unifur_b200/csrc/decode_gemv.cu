@@ -133,9 +133,15 @@ struct DecodeParams {
     // Sharded layer whose ranks write their columns straight into every rank's output (PEERS):
     // dest[d] is rank d's output as mapped into this process, already at this rank's first
     // column, with row stride ldy; arrive[d] is rank d's arrival counter.
+    // signal: when the kernel's last CTA is done it makes the launch's stores visible system-wide
+    // and adds one to every rank's counter (word 63 of `flags` counts the CTAs that are done).
+    // wait_on: before it reads x, every CTA waits (bounded) until wait_expected arrivals are on
+    // this rank's counter -- x is the output of a sharded layer -- and the last CTA takes them off.
     void *dest[8];
     uint32_t *arrive[8];
-    uint32_t n_dest;
+    uint32_t n_dest, signal;
+    uint32_t *wait_on;
+    uint32_t wait_expected;
     uint32_t M, K, N, rank;
     float lora_scale;
     // CTA c owns rows_base rows, and gran more if light_front <= c < light_front + rows_extra;
@@ -339,6 +345,21 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
     // ---- from here on the kernel reads what its predecessor wrote ----
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
+    if (PEERS && p.wait_on) {
+        if (tid == 0) {
+            const uint64_t t0 = ptx::global_timer_ns();
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_on) : "memory");
+                if (v >= p.wait_expected) break;
+                if (ptx::global_timer_ns() - t0 > (uint64_t)p.wait_ns) {
+                    atomicExch(&g_decode_error, 7);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
 
     // One K-slice of T^T = A x^T for the unit's eight rows of A and eight rows of x (raw bf16,
     // exact products, f32 sums): the lane gets T[m][j] for j = 8 * j8 + g, m = 8u + 2t and + 1.
@@ -364,8 +385,9 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
             if (m < p.M && half < nsl) {
                 const uint4 *src = reinterpret_cast<const uint4 *>(
                     p.x + (size_t)m * p.K + k0 + (half * 4 + cc) * kChunk + 16 * t);
-                xr[cc][0] = __ldg(src);
-                xr[cc][1] = __ldg(src + 1);
+                // (x that other GPUs stored into while this kernel waited is read past the L1)
+                xr[cc][0] = PEERS ? __ldcg(src) : __ldg(src);
+                xr[cc][1] = PEERS ? __ldcg(src + 1) : __ldg(src + 1);
             }
         }
     };
@@ -782,13 +804,23 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
             }
         }
     }
-    if (PEERS) {
-        // every store of this CTA has been issued: make them visible to the other GPUs, then
-        // count this CTA in on every rank's arrival counter
+    if (PEERS && (p.signal || p.wait_on)) {
+        // Every store of this CTA has been issued.  The CTAs count themselves out on a word of the
+        // workspace; the last one takes the arrivals this launch waited for off this rank's
+        // counter and, if the launch signals, makes the launch's stores visible to the other GPUs
+        // (its fence follows the others' through the counter) and adds one to every rank's
+        // arrival counter.  Launches without a signal rely on a later launch of the stream for it.
         __syncthreads();
         if (tid == 0) {
-            __threadfence_system();
-            for (uint32_t d = 0; d < p.n_dest; ++d) atomicAdd_system(p.arrive[d], 1u);
+            __threadfence();
+            if (atomicAdd(p.flags + 63, 1u) == nctas - 1) {
+                p.flags[63] = 0;
+                if (p.wait_on) atomicSub(p.wait_on, p.wait_expected);
+                if (p.signal) {
+                    __threadfence_system();
+                    for (uint32_t d = 0; d < p.n_dest; ++d) atomicAdd_system(p.arrive[d], 1u);
+                }
+            }
         }
     }
     if (done_old == nctas - 1) {
@@ -1046,7 +1078,7 @@ uint64_t t_bytes(uint64_t rows, uint32_t rank, uint32_t kparts) {
 int32_t prepare(const nf4_linear_args &a, Plan &pl, void *scratch, CUtensorMap &mc, CUtensorMap &ms) {
     DecodeParams &p = pl.p;
     const bool dq = a.scale_codes != nullptr;
-    if (p.rank || p.kparts > 1) {
+    if (p.rank || p.kparts > 1 || p.signal || p.wait_on) {
         if (!scratch) return fail(NF4_ERR_INVALID_ARG, "decode_forward: this shape needs the workspace");
         p.flags = static_cast<uint32_t *>(scratch);
         p.t_global = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + kFlagBytes);
@@ -1161,10 +1193,10 @@ int32_t decode_forward_grouped(const nf4_linear_args *a, uint32_t count, cudaStr
 }
 
 // The forward of one rank's column shard, stored into every rank's output.  `dest`: the outputs
-// [rows, ldy] as mapped here, `arrive`: the ranks' arrival counters.  *ctas: CTAs that will count
-// themselves in (what the ranks' waits add up).
+// [rows, ldy] as mapped here, `arrive`: the ranks' arrival counters.
 int32_t decode_forward_scatter(const nf4_linear_args &a, void *const *dest, uint32_t *const *arrive, uint32_t world,
-                               uint32_t rank, uint64_t ldy, uint32_t *ctas, cudaStream_t stream) {
+                               uint32_t rank, uint64_t ldy, bool signal, uint32_t *wait_on, uint32_t wait_expected,
+                               cudaStream_t stream) {
     Plan pl;
     if (world == 0 || world > 8 || rank >= world || !plan(a, pl))
         return fail(NF4_ERR_UNSUPPORTED, "decode_forward_scatter: decode shapes and up to eight ranks only");
@@ -1179,7 +1211,11 @@ int32_t decode_forward_scatter(const nf4_linear_args &a, void *const *dest, uint
         p.arrive[d] = arrive[d];
         if (reinterpret_cast<uintptr_t>(p.dest[d]) & 3u) p.y_pair = 0;
     }
-    if (ctas) *ctas = pl.grid;
+    p.signal = signal ? 1u : 0u;
+    p.wait_on = wait_on;
+    p.wait_expected = wait_expected;
+    if ((signal || wait_on) && !a.workspace)
+        return fail(NF4_ERR_INVALID_ARG, "decode_forward_scatter: signalling and waiting need the workspace (256 bytes at least)");
     return run(a, pl, a.workspace, stream);
 }
 

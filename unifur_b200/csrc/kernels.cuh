@@ -72,7 +72,8 @@ uint64_t decode_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, ui
 uint32_t persistent_ctas();
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);
 int32_t decode_forward_scatter(const nf4_linear_args &a, void *const *dest, uint32_t *const *arrive, uint32_t world,
-                               uint32_t rank, uint64_t ldy, uint32_t *ctas, cudaStream_t stream);
+                               uint32_t rank, uint64_t ldy, bool signal, uint32_t *wait_on, uint32_t wait_expected,
+                               cudaStream_t stream);
 int32_t decode_peer_wait(uint32_t *counter, uint32_t expected, uint32_t limit_ns, cudaStream_t stream);
 int32_t decode_forward_grouped(const nf4_linear_args *a, uint32_t count, cudaStream_t stream, bool *taken);
 

@@ -206,3 +206,32 @@ class ShardedForwardPlan:
     def run(self) -> torch.Tensor:
         self.run_local()
         return self.gather()
+
+
+def map_peer_tensors(t: torch.Tensor, group=None) -> List[torch.Tensor]:
+    """Every rank's copy of ``t`` (same shape and dtype on every rank, each in its own GPU's
+    memory) as tensors of THIS process: element ``r`` is rank ``r``'s allocation mapped into this
+    rank's device through CUDA IPC, element ``rank`` is ``t`` itself.  Kernels of this rank can
+    store into them over NVLink (``nf4_linear_forward_scatter_dev``).
+
+    The handle is opened with the importing device current (as NCCL's peer transport does):
+    opened under the exporting device, the mapping belongs to that device's context and kernels
+    of this one fault.  Keep the returned tensors alive while kernels may touch them, and ``t``
+    alive on every rank while any peer still holds its mapping."""
+    if not t.is_cuda:
+        raise ValueError("map_peer_tensors needs a CUDA tensor")
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    dev = t.device
+    for r in range(world):
+        if r != rank and not torch.cuda.can_device_access_peer(dev.index, r):
+            raise RuntimeError(f"device {dev.index} cannot access device {r} as a peer")
+    handles = [None] * world
+    dist.all_gather_object(handles, t.untyped_storage()._share_cuda_(), group=group)
+    out = []
+    for r in range(world):
+        if r == rank:
+            out.append(t)
+            continue
+        st = torch.UntypedStorage._new_shared_cuda(dev.index, *handles[r][1:])
+        out.append(torch.empty(0, dtype=t.dtype, device=dev).set_(st).view(t.shape))
+    return out
