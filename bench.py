@@ -970,13 +970,41 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
         worst = "MISMATCH" if "MISMATCH" in checks.values() else (
             "ok" if all(v == "ok" for v in checks.values()) else "ok_within_one_bf16_ulp")
         if m == 8:
+            # the same seven sharded projections without a collective: every rank's kernels store
+            # their columns into every rank's outputs; the last projection signals for the block
+            # (kernel boundaries order the earlier launches' stores before it), one wait for the
+            # ranks' arrivals closes the block
+            pplans, pchecks, arr = [], {}, None
+            for i, pl in enumerate(plans):
+                pp = pl.lin.peer_store_plan(pl.x, signal=(i == len(plans) - 1), peer_arrivals=arr)
+                arr = pp.peer_arrivals
+                pplans.append(pp)
+
+            def run_peer():
+                for pp in pplans:
+                    pp.run()
+                pplans[0].wait(world)
+
+            run_peer()
+            torch.cuda.synchronize()
+            dist.barrier()
+            for (nm, k, n), pl, pp in zip(QWEN2_7B_BLOCK, plans, pplans):
+                pchecks[nm] = check(pp.y, pl.run().clone(), k)   # against the all-gathered output, checked above
+            torch.cuda.synchronize()
+            dist.barrier()
+            ms_peer = timed(run_peer)
+            peer_worst = "MISMATCH" if "MISMATCH" in pchecks.values() else (
+                "ok" if all(v == "ok" for v in pchecks.values()) else "ok_within_one_bf16_ulp")
             by = sum(k * n // 2 + k * n // 64 * 4 + 16 * (k + n) * 2 + m * (k + n) * 2
                      for _nm, k, n in QWEN2_7B_BLOCK)
             blk[label] = {"us_local": ms_local * 1e3, "us_with_gather": ms_all * 1e3,
-                          "GB/s": by / (ms_all * 1e-3) / 1e9,
+                          "us_with_peer_stores": ms_peer * 1e3, "peer_store_check": peer_worst,
+                          "GB/s": by / (ms_peer * 1e-3) / 1e9,
+                          "GB/s_with_gather": by / (ms_all * 1e-3) / 1e9,
                           "GB/s_per_gpu_local": by / world / (ms_local * 1e-3) / 1e9,
                           "frac_per_gpu_local": by / world / (ms_local * 1e-3) / 1e9 / hbm_peak,
                           "gather_check": worst, "per_projection": checks}
+            del pplans
         else:
             fl = sum(2.0 * m * k * n + 2.0 * m * 16 * (k + n) for _nm, k, n in QWEN2_7B_BLOCK)
             blk[label] = {"ms_local": ms_local, "ms_with_gather": ms_all,

@@ -126,11 +126,94 @@ class ShardedNf4Linear:
         y = gather_columns(y_local.reshape(-1, y_local.shape[-1]), self.shards, self.group)
         return y.view(*lead, self.d_out)
 
+    def peer_store_plan(self, x: torch.Tensor, **kw) -> "PeerStorePlan":
+        """The decode-sized forward whose kernel stores into every rank's output (no collective)."""
+        return PeerStorePlan(self, x, **kw)
+
     def plan(self, x: torch.Tensor) -> "ShardedForwardPlan":
         """Buffers and the argument block for repeated forwards of ``x``'s shape and storage: the
         serving loop's form of ``forward`` (nothing is allocated per call, so the calls can be
         captured in a CUDA graph)."""
         return ShardedForwardPlan(self, x)
+
+
+class PeerStorePlan:
+    """A decode-sized sharded forward without a collective: ``run()`` enqueues this rank's forward,
+    whose kernel stores its columns into every rank's ``y [rows, d_out]`` over NVLink and (with
+    ``signal``) adds one arrival to every rank's counter ``arrivals[counter_index]`` when it is
+    done; ``wait(n)`` enqueues the bounded wait for ``n`` arrivals on this rank's own counter
+    (one per rank and signalling forward).  Equal shards, rows <= 16, a shape the decode kernel
+    takes.  ``y`` and ``arrivals`` are allocated here, on every rank alike, and mapped into the
+    peers with :func:`map_peer_tensors` (``arrivals`` may be shared between plans: pass the list
+    a previous plan returned in ``peer_arrivals``)."""
+
+    def __init__(self, lin: "ShardedNf4Linear", x: torch.Tensor, signal: bool = True, counter_index: int = 0,
+                 peer_arrivals: Optional[List[torch.Tensor]] = None, wait_for: int = 0):
+        import ctypes
+
+        from . import _lib
+
+        if x.dtype != torch.bfloat16 or not x.is_contiguous() or x.dim() != 2:
+            raise ValueError("PeerStorePlan: x must be a contiguous bf16 [rows, d_in] tensor")
+        world = dist.get_world_size(lin.group)
+        widths = {e - s for s, e in lin.shards}
+        if len(widths) != 1:
+            raise ValueError("PeerStorePlan: the shards must be equal")
+        width = widths.pop()
+        self.lin, self.x, self.world = lin, x, world
+        self.lib, self._check, self._vp = _lib.load(), _lib.check, ctypes.c_void_p
+        rows, dev = x.shape[0], x.device
+        self.y = torch.zeros(rows, lin.d_out, dtype=torch.bfloat16, device=dev)
+        self.peer_y = map_peer_tensors(self.y, lin.group)
+        if peer_arrivals is None:
+            self.arrivals = torch.zeros(64, dtype=torch.int32, device=dev)
+            peer_arrivals = map_peer_tensors(self.arrivals, lin.group)
+        self.peer_arrivals = peer_arrivals
+        self.arrivals = peer_arrivals[lin.rank]
+        self.counter_index = counter_index
+        rank = lin.lora_a.shape[0] if lin.lora_a is not None else 0
+        ws_bytes = int(self.lib.nf4_linear_workspace_bytes(rows, lin.d_in, width, rank))
+        self.ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        self.bias32 = lin.bias.to(torch.float32).contiguous() if lin.bias is not None else None
+        self.la = lin.lora_a.to(torch.bfloat16).contiguous() if rank else None
+        self.lb = lin.lora_b.to(torch.bfloat16).contiguous() if rank else None
+        pk = lin.packed
+        dq = pk.is_double_quantized()
+        args = _lib.LinearArgs()
+        args.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+        args.layout, args.io_dtype = LAYOUT_OUT_IN, _lib.DTYPE_BF16
+        args.rows, args.d_in, args.d_out = rows, lin.d_in, width
+        args.x, args.packed = x.data_ptr(), pk.codes.data_ptr()
+        args.absmax = None if dq else pk.absmax.data_ptr()
+        args.scale_codes = pk.scale_codes.data_ptr() if dq else None
+        args.scale_of_scales = pk.scale_of_scales.data_ptr() if dq else None
+        args.bias = self.bias32.data_ptr() if self.bias32 is not None else None
+        args.lora_a = self.la.data_ptr() if rank else None
+        args.lora_b = self.lb.data_ptr() if rank else None
+        args.lora_rank, args.lora_scale = rank, float(lin.lora_scale)
+        args.workspace, args.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+        po = _lib.PeerOutputs()
+        po.struct_bytes = ctypes.sizeof(_lib.PeerOutputs)
+        po.world, po.rank, po.ldy_full = world, lin.rank, lin.d_out
+        for r in range(world):
+            po.y_full[r] = self.peer_y[r].data_ptr()
+            po.arrivals[r] = peer_arrivals[r][counter_index:counter_index + 1].data_ptr()
+        po.signal = 1 if signal else 0
+        if wait_for:
+            po.wait_arrivals = self.arrivals[counter_index:counter_index + 1].data_ptr()
+            po.wait_expected = wait_for
+        self.args, self.peers = args, po
+        self._a, self._p = ctypes.byref(args), ctypes.byref(po)
+
+    def run(self) -> torch.Tensor:
+        stream = self._vp(torch.cuda.current_stream(self.x.device).cuda_stream)
+        self._check(self.lib.nf4_linear_forward_scatter_dev(self._a, self._p, stream))
+        return self.y
+
+    def wait(self, arrivals: int, timeout_ns: int = 2_000_000_000) -> None:
+        stream = self._vp(torch.cuda.current_stream(self.x.device).cuda_stream)
+        ptr = self._vp(self.arrivals[self.counter_index:self.counter_index + 1].data_ptr())
+        self._check(self.lib.nf4_peer_arrivals_wait_dev(ptr, arrivals, timeout_ns, stream))
 
 
 class ShardedForwardPlan:
