@@ -6,10 +6,10 @@
 // into slices of 256 (four 64-blocks); when K is short the warps left over take other 16-row
 // tiles.  Every warp streams its own slice with TMA: one lane asks for a 2-D box of
 // 16 rows x 128 bytes of nibbles (128-byte swizzle) and a box of 16 rows x 4 f32 block scales,
-// both into the warp's private ring of four tiles, and the box's arrival is counted on the
+// both into the warp's private ring of two tiles, and the box's arrival is counted on the
 // warp's own mbarrier.  No warp ever waits for another while the weights stream: there is no
 // producer warp and no CTA-wide barrier inside a pass.  The tensor maps cover this GPU's weight
-// only and the loads are not multicast.  The requests for the first tiles (and the loads of the
+// only and every load goes to one CTA.  The requests for the first tiles (and the loads of the
 // adapter's A factor) are made BEFORE the kernel waits for its predecessor in the stream
 // (programmatic dependent launch): weights are immutable, so they may be fetched while the
 // kernel that produces x is still running.
@@ -27,11 +27,18 @@
 // absmax (or its double-quantized decode) -- the scale never touches the f16 path.
 //
 // Adapter.  T = x A^T ([M][rank] f32) is needed by every CTA but costs rank * K * 2 bytes of A to
-// compute, so it is computed once per launch: the first `rank` CTAs each take one row of A
-// (their warps hold the matching slices of x already), write their column of T to the workspace
-// and count themselves in on a flag word there.  A CTA picks T up before the last tile of its first pass -- by then
-// the producers have long finished -- with a bounded wait on the flag.  The last CTA to have read
-// T puts the flag words back to zero, which is the state the workspace must have at first use.
+// compute, so it is computed once per launch: the first rank / 8 CTAs each take eight rows of A
+// (their warps hold the matching slices of x already: sixteen bf16 MMAs per warp), write their
+// columns of T to the workspace and count themselves in on a flag word there.  A CTA picks T up
+// before the last tile of its first pass -- by then the producers have long finished -- with a
+// bounded wait on the flag.  The last CTA to have read T puts the flag words back to zero, which
+// is the state the workspace must have at first use.
+//
+// Longer K, several forwards, several GPUs.  d_in above 4096 is cut into parts that groups of
+// CTAs multiply (SPLIT: the parts' sums meet in the workspace, the last CTA of a row range adds
+// them in a fixed order).  Forwards that share x run as one launch whose CTAs are shared out
+// between them (decode_group_kernel).  A column-sharded layer's kernel can store its columns
+// into every rank's output over NVLink and signal the ranks (PEERS).
 //
 // Reduction.  When a warp has multiplied a tile it parks the tile's partial sums (four f32 per
 // lane and eight activation rows) in its own row of a parking area in shared memory.  After a
@@ -56,7 +63,8 @@
 namespace nf4 {
 
 // Set when the launch's shared-memory window is not where the kernel expects it (4) or a
-// bounded wait gives up (5).  Read and cleared by nf4_device_status().
+// bounded wait gives up (5: a tile, 6: the adapter intermediate, 7: the ranks' arrivals).  Read
+// and cleared by nf4_device_status().
 __device__ int g_decode_error = 0;
 
 int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, uint32_t rank,
