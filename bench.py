@@ -286,13 +286,23 @@ def run_own(args) -> None:
     # bounded wait for all ranks' CTAs on this rank's arrival counter: no collective, no copy.
     # Two outputs and counters, used by alternate steps (a rank may be one step ahead of another).
     y_full = arrivals = peer_y = peer_arr = None
+    peer_stores = world > 1
     if world > 1:
         from unifur_b200.sharded import map_peer_tensors
 
         y_full = [torch.zeros(sum(MS), world * N, device=dev, dtype=torch.bfloat16) for _ in range(2)]
         arrivals = torch.zeros(64, device=dev, dtype=torch.int32)
-        peer_y = [map_peer_tensors(y_full[par]) for par in range(2)]
-        peer_arr = map_peer_tensors(arrivals)
+        try:
+            peer_y = [map_peer_tensors(y_full[par]) for par in range(2)]
+            peer_arr = map_peer_tensors(arrivals)
+            mapped = 1
+        except Exception as e:  # no peer mapping on this machine (IPC closed, no peer access)
+            log(f"peer mapping failed ({type(e).__name__}: {e}); the ranks exchange with an all-gather instead")
+            mapped = 0
+        flag = torch.tensor([mapped], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # every rank takes the same path
+        peer_stores = bool(int(flag.item()))
+        gathered_flat = None if peer_stores else torch.zeros(world, sum(MS), N, device=dev, dtype=torch.bfloat16)
     ws_bytes = max(int(lib.nf4_linear_workspace_bytes(m, K, N, RANK)) for m in MS)
     workspaces = {m: torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev) for m in MS}
 
@@ -316,7 +326,7 @@ def run_own(args) -> None:
     # input, as the next layer of a sharded model would; the first step of a sequence waits for
     # nothing and a wait kernel closes the sequence.
     peer_out = {}
-    if world > 1:
+    if peer_stores:
         row0 = 0
         for j, m in enumerate(MS):
             for par in range(2):
@@ -341,16 +351,21 @@ def run_own(args) -> None:
         par = i & 1
         for j, m in enumerate(MS):
             c = (len(MS) * i + j) % N_COPIES  # a different weight copy for every pass
-            if world == 1:
-                _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, par)]), stream))
-            else:
+            if peer_stores:
                 _lib.check(lib.nf4_linear_forward_scatter_dev(ctypes.byref(call_args[(c, m, par)]),
                                                               ctypes.byref(peer_out[(m, par, first)]), stream))
+            else:
+                _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(call_args[(c, m, par)]), stream))
+        if world > 1 and not peer_stores:
+            # without peer mapping: the step's slabs are all-gathered behind it on the same stream
+            # and placed side by side
+            dist.all_gather_into_tensor(gathered_flat, y_all[par])
+            y_full[par].view(sum(MS), world, N).copy_(gathered_flat.permute(1, 0, 2))
 
     def drain(last: int) -> None:
         """Closes a sequence of steps: the last step's outputs are whole on this rank once every
         rank has signalled."""
-        if world > 1:
+        if peer_stores:
             stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
             _lib.check(lib.nf4_peer_arrivals_wait_dev(ctypes.c_void_p(arrivals[(last & 1):(last & 1) + 1].data_ptr()),
                                                       world, 2_000_000_000, stream))
@@ -532,7 +547,7 @@ def run_own(args) -> None:
     # ---- the configurations that are sharded by definition (every rank takes part) -------------
     if world > 1 and not args.device_only:
         log("sharded sections")
-        extras.update(sharded_sections(torch, dist, lib, _lib, dev, rank, world))
+        extras.update(sharded_sections(torch, dist, lib, _lib, dev, rank, world, peer_stores=peer_stores))
 
     # ---- other kernels of the path (not part of `value`) -----------------------------------
     if rank == 0 and not args.device_only:
@@ -583,9 +598,12 @@ def run_own(args) -> None:
                                 "per pass",
                        "launch": launch_mode,
                        "sharding": "none" if world == 1 else
-                       f"{world} column shards of a [{world * N}, {K}] layer: every rank's kernel stores its columns "
-                       "into every rank's output over NVLink, a step's last forward signals and the next step's "
-                       f"first forward waits for all ranks inside the kernel (scatter_check: {scatter_check})"},
+                       (f"{world} column shards of a [{world * N}, {K}] layer: every rank's kernel stores its columns "
+                        "into every rank's output over NVLink, a step's last forward signals and the next step's "
+                        f"first forward waits for all ranks inside the kernel (scatter_check: {scatter_check})"
+                        if peer_stores else
+                        f"{world} column shards of a [{world * N}, {K}] layer, one NCCL all-gather of y per step "
+                        f"(no peer mapping on this machine; scatter_check: {scatter_check})")},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(gpu_launches), "clocks": clocks,
             "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
@@ -865,7 +883,7 @@ def sweep_section(torch, lib, _lib, dev):
             "frac": gbs / hbm_peak, "peak_kind": f"of {peak_kind}"}
 
 
-def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: int = 10):
+def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: int = 10, peer_stores: bool = True):
     """The two configurations that are sharded by definition, on `world` GPUs, through
     ShardedNf4Linear: every rank owns a contiguous range of output columns of each weight (its rows
     of the packed weight, of the scales and of LoRA B), runs the single-GPU kernels on it, and the
@@ -969,7 +987,15 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
         ms_all = timed(lambda: [pl.run() for pl in plans])
         worst = "MISMATCH" if "MISMATCH" in checks.values() else (
             "ok" if all(v == "ok" for v in checks.values()) else "ok_within_one_bf16_ulp")
-        if m == 8:
+        if m == 8 and not peer_stores:
+            by = sum(k * n // 2 + k * n // 64 * 4 + 16 * (k + n) * 2 + m * (k + n) * 2
+                     for _nm, k, n in QWEN2_7B_BLOCK)
+            blk[label] = {"us_local": ms_local * 1e3, "us_with_gather": ms_all * 1e3,
+                          "GB/s": by / (ms_all * 1e-3) / 1e9,
+                          "GB/s_per_gpu_local": by / world / (ms_local * 1e-3) / 1e9,
+                          "frac_per_gpu_local": by / world / (ms_local * 1e-3) / 1e9 / hbm_peak,
+                          "gather_check": worst, "per_projection": checks}
+        elif m == 8:
             # the same seven sharded projections without a collective: every rank's kernels store
             # their columns into every rank's outputs; the last projection signals for the block
             # (kernel boundaries order the earlier launches' stores before it), one wait for the
