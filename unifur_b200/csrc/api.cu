@@ -164,33 +164,27 @@ int32_t report_flags(int *const *ptrs, const int *v) {
     return NF4_OK;
 }
 
-// Pinned host words the host-pointer entry points copy the flags into beside their results.
-struct FlagMirror {
-    int *host = nullptr;
-    int32_t get(int **out) {
-        if (!host) NF4_CUDA_TRY(cudaMallocHost(reinterpret_cast<void **>(&host), 3 * sizeof(int)));
-        *out = host;
-        return NF4_OK;
+// Three words of mapped host memory per device that the kernels' failure codes are written to
+// as well as to the device flags: the host-pointer entry points look at them after their final
+// synchronise, without a copy.  Set up at the first such call on a device.
+int32_t host_flag_words(volatile int **out) {
+    static std::mutex mu;
+    static int *words[64] = {};
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NF4_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!words[dev]) {
+        int *h = nullptr, *d = nullptr;
+        NF4_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void **>(&h), 3 * sizeof(int), cudaHostAllocMapped));
+        h[0] = h[1] = h[2] = 0;
+        NF4_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&d), h, 0));
+        NF4_TRY(decode_set_host_flag(d));
+        NF4_TRY(decode2_set_host_flag(d + 1));
+        NF4_TRY(prefill_set_host_flag(d + 2));
+        words[dev] = h;
     }
-    ~FlagMirror() {
-        if (host) cudaFreeHost(host);
-    }
-};
-thread_local FlagMirror t_flag_mirror;
-
-// Which kernel the last nf4_linear_forward_dev of this host thread launched: 0 decode,
-// 1 split-K decode, 2 prefill, -1 a kernel without device-side waits.
-thread_local int t_last_family = -1;
-
-// Enqueues, on `stream`, the copy of the flag of the kernel this thread launched last (ahead of
-// the caller's final synchronise, so that the check costs no synchronisation of its own).
-int32_t flags_enqueue(cudaStream_t stream, int **ptrs, int **mirror) {
-    NF4_TRY(flag_ptrs(ptrs));
-    NF4_TRY(t_flag_mirror.get(mirror));
-    (*mirror)[0] = (*mirror)[1] = (*mirror)[2] = 0;
-    const int f = t_last_family;
-    if (f >= 0)
-        NF4_CUDA_TRY(cudaMemcpyAsync(*mirror + f, ptrs[f], sizeof(int), cudaMemcpyDeviceToHost, stream));
+    *out = words[dev];
     return NF4_OK;
 }
 
@@ -435,18 +429,14 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     // rows <= 16: the warp-MMA kernel (d_in <= 4096, whole 256-slices), else the tcgen05 split-K
     // kernel; more rows: the tcgen05 GEMM; whatever none of them takes: the CUDA-core kernel.
     if (decode_supported(*args)) {
-        t_last_family = 0;
         return decode_forward(*args, s);
     }
     if (decode2_supported(*args)) {
-        t_last_family = 1;
         return decode2_forward(*args, s);
     }
     if (prefill_supported(*args)) {
-        t_last_family = 2;
         return prefill_forward(*args, s);
     }
-    t_last_family = -1;
     return generic_forward(*args, s);
 }
 
@@ -482,7 +472,6 @@ int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint32_t cou
         bool taken = false;
         NF4_TRY(decode_forward_grouped(args, count, s, &taken));
         if (taken) {
-            t_last_family = 0;
             return NF4_OK;
         }
     }
@@ -508,7 +497,6 @@ int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_p
                                          "(rows <= 16, bf16, W [d_out, d_in], d_in a multiple of 256)");
     if (!a.workspace || a.workspace_bytes < 256)
         return fail(NF4_ERR_INVALID_ARG, "nf4_linear_forward_scatter_dev: the workspace must hold 256 bytes at least");
-    t_last_family = 0;
     return decode_forward_scatter(a, peers->y_full, peers->arrivals, (uint32_t)peers->world, (uint32_t)peers->rank,
                                   ldy, peers->signal != 0, peers->wait_arrivals, peers->wait_expected,
                                   static_cast<cudaStream_t>(stream));
@@ -516,7 +504,6 @@ int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_p
 
 int32_t nf4_peer_arrivals_wait_dev(uint32_t *own_arrivals, uint32_t expected, uint32_t timeout_ns, void *stream) {
     if (!own_arrivals) return fail(NF4_ERR_INVALID_ARG, "nf4_peer_arrivals_wait_dev: null counter");
-    t_last_family = 0;
     return decode_peer_wait(own_arrivals, expected, timeout_ns, static_cast<cudaStream_t>(stream));
 }
 
@@ -959,13 +946,20 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
     } else if (ws) {
         NF4_CUDA_TRY(cudaMemsetAsync(d_ws, 0, 256, 0));
     }
+    volatile int *failed = nullptr;
+    NF4_TRY(host_flag_words(&failed));  // (before the launch: the kernels write their failure codes there too)
     NF4_TRY(nf4_linear_forward_dev(&a, nullptr));
     NF4_CUDA_TRY(cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, 0));
-    // ... and a wait that gave up in a kernel must not pass for a result
-    int *ptrs[3], *mirror = nullptr;
-    NF4_TRY(flags_enqueue(0, ptrs, &mirror));
     NF4_TRY(check_cuda(cudaStreamSynchronize(0), "nf4_weight_linear_forward_host sync"));
-    return report_flags(ptrs, mirror);
+    // ... and a wait that gave up in a kernel must not pass for a result
+    if (failed[0] | failed[1] | failed[2]) {
+        int *ptrs[3];
+        NF4_TRY(flag_ptrs(ptrs));
+        const int v[3] = {failed[0], failed[1], failed[2]};
+        failed[0] = failed[1] = failed[2] = 0;
+        return report_flags(ptrs, v);
+    }
+    return NF4_OK;
 }
 
 }  // extern "C"

@@ -66,6 +66,7 @@ namespace nf4 {
 // bounded wait gives up (5: a tile, 6: the adapter intermediate, 7: the ranks' arrivals).  Read
 // and cleared by nf4_device_status().
 __device__ int g_decode_error = 0;
+__device__ int *g_decode_error_host = nullptr;  // the same, in mapped host memory (set by the host-pointer entry points)
 
 int32_t lora_t_small(const void *x, const void *a, uint32_t rows, uint32_t K, uint32_t rank,
                      float *t_out, cudaStream_t stream, bool chained);
@@ -219,7 +220,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     if (ptx::smem_addr(smem) != kWin0) {
         // the table's base is an immediate of the lookups: nothing can run from another address
-        if (tid == 0) atomicExch(&g_decode_error, 4);
+        if (tid == 0) NF4_REPORT_FAILURE(g_decode_error, g_decode_error_host, 4);
         return;
     }
     if (lane == 0) {  // the descriptors are on their way while the table is built
@@ -361,7 +362,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_on) : "memory");
                 if (v >= p.wait_expected) break;
                 if (ptx::global_timer_ns() - t0 > (uint64_t)p.wait_ns) {
-                    atomicExch(&g_decode_error, 7);
+                    NF4_REPORT_FAILURE(g_decode_error, g_decode_error_host, 7);
                     break;
                 }
             }
@@ -529,7 +530,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
             while (ld_acquire_gpu(p.flags) != p.n_prod_all) {
                 if (ptx::global_timer_ns() - t0 > (uint64_t)p.wait_ns) {
                     ok = 0;
-                    atomicExch(&g_decode_error, 6);
+                    NF4_REPORT_FAILURE(g_decode_error, g_decode_error_host, 6);
                     break;
                 }
             }
@@ -596,7 +597,7 @@ __device__ __forceinline__ void decode_body(const CUtensorMap *tm_codes, const C
             const uint32_t slot = use_j & (kRing - 1);
             if (!lost && !wait_phase(bar0 + 8 * slot, (use_j / kRing) & 1u, p.wait_ns)) {
                 lost = true;
-                if (lane == 0) atomicExch(&g_decode_error, 5);
+                if (lane == 0) NF4_REPORT_FAILURE(g_decode_error, g_decode_error_host, 5);
             }
             float acc[NT][4];
             #pragma unroll
@@ -856,7 +857,7 @@ __global__ void peer_wait_kernel(uint32_t *counter, uint32_t expected, uint32_t 
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
         if (v >= expected) break;
         if (ptx::global_timer_ns() - t0 > (uint64_t)limit_ns) {
-            atomicExch(&g_decode_error, 7);
+            NF4_REPORT_FAILURE(g_decode_error, g_decode_error_host, 7);
             return;
         }
         __nanosleep(100);
@@ -1292,13 +1293,17 @@ __global__ void selftest_wait_kernel(uint32_t limit_ns, unsigned long long *wait
     const uint64_t t0 = ptx::global_timer_ns();
     const bool ok = wait_phase(b, 0, limit_ns);  // phase 0 never completes: nobody arrives
     *waited_ns = ptx::global_timer_ns() - t0;
-    if (!ok) atomicExch(&g_decode_error, 5);
+    if (!ok) NF4_REPORT_FAILURE(g_decode_error, g_decode_error_host, 5);
 }
 
 int32_t decode_selftest_wait(uint32_t limit_ns, unsigned long long *waited_ns_dev, cudaStream_t stream) {
     selftest_wait_kernel<<<1, 1, 0, stream>>>(limit_ns, waited_ns_dev);
     count_launch();
     return check_cuda(cudaGetLastError(), "selftest_wait_kernel launch");
+}
+
+int32_t decode_set_host_flag(int *mapped) {
+    return check_cuda(cudaMemcpyToSymbol(g_decode_error_host, &mapped, sizeof(mapped)), "setting the mapped failure word");
 }
 
 int32_t decode_error_flag_ptr(int **dev_ptr) {

@@ -40,6 +40,7 @@
 namespace nf4 {
 
 __device__ int g_decode2_error = 0;  // set when a bounded wait gives up
+__device__ int *g_decode2_error_host = nullptr;  // the same, in mapped host memory (set by the host-pointer entry points)
 
 
 namespace {
@@ -322,7 +323,7 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                     issue_stage(st, sg.rt, g4);
                 }
             }
-            if (!ok) atomicExch(&g_decode2_error, 1);
+            if (!ok) NF4_REPORT_FAILURE(g_decode2_error, g_decode2_error_host, 1);
         }
     } else if (warp >= kWarpIssuer0 && warp < kWarpIssuer0 + kIssuerWarps) {
         // ============================== MMA issuers ==============================
@@ -362,7 +363,7 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                 if (ok) ptx::tc_commit(bar(kBarSegDone + i));
                 bc_base += sg.kb1 - sg.kb0;
             }
-            if (!ok) atomicExch(&g_decode2_error, 2);
+            if (!ok) NF4_REPORT_FAILURE(g_decode2_error, g_decode2_error_host, 2);
         }
     } else if (warp < kExpanderWarps) {
         // ================================ expanders ================================
@@ -419,7 +420,7 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
             }
             bc_base += sg.kb1 - sg.kb0;
         }
-        if (!ok && lane == 0) atomicExch(&g_decode2_error, 3);
+        if (!ok && lane == 0) NF4_REPORT_FAILURE(g_decode2_error, g_decode2_error_host, 3);
     } else if (warp >= kWarpFinish0) {
         // ================================= finish =================================
         // Four dedicated warps (one per TMEM lane quarter) finish a segment as soon as its MMAs
@@ -552,7 +553,7 @@ decode2_kernel(const __grid_constant__ CUtensorMap tmap_codes,
                 }
             }
         }
-        if (!ok && lane == 0) atomicExch(&g_decode2_error, 4);
+        if (!ok && lane == 0) NF4_REPORT_FAILURE(g_decode2_error, g_decode2_error_host, 4);
     }
 
     ptx::tc_fence_before();
@@ -742,6 +743,10 @@ int32_t decode2_forward(const nf4_linear_args &a, cudaStream_t stream) {
         NF4_TRY(make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.absmax, p.N, p.kb, (uint64_t)p.kb * 4,
                          kRowsPerTile, 4, CU_TENSOR_MAP_SWIZZLE_NONE));
     return dq ? launch<true>(mc, ms, pl, stream) : launch<false>(mc, ms, pl, stream);
+}
+
+int32_t decode2_set_host_flag(int *mapped) {
+    return check_cuda(cudaMemcpyToSymbol(g_decode2_error_host, &mapped, sizeof(mapped)), "setting the mapped failure word");
 }
 
 int32_t decode2_error_flag_ptr(int **dev_ptr) {

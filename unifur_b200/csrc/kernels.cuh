@@ -68,6 +68,18 @@ int32_t selfcheck_codes(uint64_t first_bits, uint64_t count, unsigned long long 
 // decode_gemv.cu: rows <= 16, NF4_LAYOUT_OUT_IN, bf16 activations.
 bool decode_supported(const nf4_linear_args &a);
 uint64_t decode_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
+// A kernel's failure code goes to its device flag and, where the host has given the kernel's file
+// a word of mapped host memory (the host-pointer entry points do, so that they need no copy to
+// look at it), to that word as well.
+#define NF4_REPORT_FAILURE(flag, host_word, code)                          \
+    do {                                                                   \
+        atomicExch(&(flag), (code));                                       \
+        if (host_word) *reinterpret_cast<volatile int *>(host_word) = (code); \
+    } while (0)
+int32_t decode_set_host_flag(int *mapped);
+int32_t decode2_set_host_flag(int *mapped);
+int32_t prefill_set_host_flag(int *mapped);
+
 // api.cu: CTAs a kernel that puts one CTA on every SM may use (the SM count less nf4_reserve_sms)
 uint32_t persistent_ctas();
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream);

@@ -50,6 +50,7 @@
 namespace nf4 {
 
 __device__ int g_prefill_error = 0;  // set when a bounded wait gives up
+__device__ int *g_prefill_error_host = nullptr;  // the same, in mapped host memory (set by the host-pointer entry points)
 
 
 namespace {
@@ -377,7 +378,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     }
                 }
             }
-            if (!ok) atomicExch(&g_prefill_error, 1);
+            if (!ok) NF4_REPORT_FAILURE(g_prefill_error, g_prefill_error_host, 1);
         }
     } else if (warp == 1 || warp == 6) {
         // ============================= MMA issuers =============================
@@ -449,7 +450,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     if (ks + 1 == k_end) ptx::tc_commit(bar(kBarAccFull));
                 }
             }
-            if (!ok) atomicExch(&g_prefill_error, 2);
+            if (!ok) NF4_REPORT_FAILURE(g_prefill_error, g_prefill_error_host, 2);
         }
     } else if (warp < 6 || warp >= kFirstEpilogueWarpB) {
         // ============================== epilogue ==============================
@@ -571,7 +572,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                         __nanosleep(64);
                     }
                 }
-                if (!ok) atomicExch(&g_prefill_error, 5);  // the sums are wrong; the flag says so
+                if (!ok) NF4_REPORT_FAILURE(g_prefill_error, g_prefill_error_host, 5);  // the sums are wrong; the flag says so
                 ok = true;  // the read-out goes on (every role must finish its segments)
             }
             for (uint32_t k = 0; k < kLoads; k += 2) {
@@ -607,7 +608,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             }
         }
         if (epi_leader) ptx::tma_store_wait<0>();
-        if (!ok && lane == 0) atomicExch(&g_prefill_error, 3);
+        if (!ok && lane == 0) NF4_REPORT_FAILURE(g_prefill_error, g_prefill_error_host, 3);
     } else if (warp >= kFirstExpanderWarp && warp < kFirstEpilogueWarpB) {
         // ============================ dequantisers ============================
         // Four groups of four warps; group g takes the main stages (adapter stages need no
@@ -710,7 +711,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 }
             }
         }
-        if (!ok && lane == 0) atomicExch(&g_prefill_error, 4);
+        if (!ok && lane == 0) NF4_REPORT_FAILURE(g_prefill_error, g_prefill_error_host, 4);
     }
 
     ptx::tc_fence_before();
@@ -1079,6 +1080,10 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     return check_cuda(cudaGetLastError(), "prefill_kernel launch");
 }
 
+
+int32_t prefill_set_host_flag(int *mapped) {
+    return check_cuda(cudaMemcpyToSymbol(g_prefill_error_host, &mapped, sizeof(mapped)), "setting the mapped failure word");
+}
 
 int32_t prefill_error_flag_ptr(int **dev_ptr) {
     return check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(dev_ptr), g_prefill_error),
