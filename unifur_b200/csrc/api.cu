@@ -188,6 +188,10 @@ int32_t host_flag_words(volatile int **out) {
     return NF4_OK;
 }
 
+// The host-pointer entry points work on the calling thread's own stream, so that calls from
+// several host threads (each with its own staging arena) do not serialise on the default stream.
+#define kHostStream cudaStreamPerThread
+
 inline size_t dtype_bytes(int32_t dt) { return dt == NF4_DTYPE_F32 ? 4 : 2; }
 
 int32_t validate_linear(const nf4_linear_args *a, bool needs_workspace = true) {
@@ -650,11 +654,11 @@ int32_t nf4_quantize_host(const float *values, uint64_t len, uint8_t *packed, fl
     float *d_v = cv.take<float>(len);
     uint8_t *d_p = cv.take<uint8_t>(pb);
     float *d_a = cv.take<float>(nb);
-    NF4_CUDA_TRY(cudaMemcpyAsync(d_v, values, len * 4, cudaMemcpyHostToDevice, 0));
-    NF4_TRY(quantize_packed(d_v, len, d_p, d_a, 0));
-    NF4_CUDA_TRY(cudaMemcpyAsync(packed, d_p, pb, cudaMemcpyDeviceToHost, 0));
-    NF4_CUDA_TRY(cudaMemcpyAsync(absmax, d_a, nb * 4, cudaMemcpyDeviceToHost, 0));
-    return check_cuda(cudaStreamSynchronize(0), "nf4_quantize_host sync");
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_v, values, len * 4, cudaMemcpyHostToDevice, kHostStream));
+    NF4_TRY(quantize_packed(d_v, len, d_p, d_a, kHostStream));
+    NF4_CUDA_TRY(cudaMemcpyAsync(packed, d_p, pb, cudaMemcpyDeviceToHost, kHostStream));
+    NF4_CUDA_TRY(cudaMemcpyAsync(absmax, d_a, nb * 4, cudaMemcpyDeviceToHost, kHostStream));
+    return check_cuda(cudaStreamSynchronize(kHostStream), "nf4_quantize_host sync");
 }
 
 int32_t nf4_double_quantize_host(const float *absmax, uint64_t nblocks, uint8_t *scale_codes,
@@ -671,11 +675,11 @@ int32_t nf4_double_quantize_host(const float *absmax, uint64_t nblocks, uint8_t 
     float *d_a = cv.take<float>(nblocks);
     uint8_t *d_c = cv.take<uint8_t>(nblocks);
     float *d_s = cv.take<float>(1);
-    NF4_CUDA_TRY(cudaMemcpyAsync(d_a, absmax, nblocks * 4, cudaMemcpyHostToDevice, 0));
-    NF4_TRY(double_quantize(d_a, nblocks, d_c, d_s, 0));
-    NF4_CUDA_TRY(cudaMemcpyAsync(scale_codes, d_c, nblocks, cudaMemcpyDeviceToHost, 0));
-    NF4_CUDA_TRY(cudaMemcpyAsync(scale_of_scales, d_s, 4, cudaMemcpyDeviceToHost, 0));
-    return check_cuda(cudaStreamSynchronize(0), "nf4_double_quantize_host sync");
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_a, absmax, nblocks * 4, cudaMemcpyHostToDevice, kHostStream));
+    NF4_TRY(double_quantize(d_a, nblocks, d_c, d_s, kHostStream));
+    NF4_CUDA_TRY(cudaMemcpyAsync(scale_codes, d_c, nblocks, cudaMemcpyDeviceToHost, kHostStream));
+    NF4_CUDA_TRY(cudaMemcpyAsync(scale_of_scales, d_s, 4, cudaMemcpyDeviceToHost, kHostStream));
+    return check_cuda(cudaStreamSynchronize(kHostStream), "nf4_double_quantize_host sync");
 }
 
 int32_t nf4_dequantize_host(const uint8_t *packed, uint64_t len, const float *absmax,
@@ -692,17 +696,17 @@ int32_t nf4_dequantize_host(const uint8_t *packed, uint64_t len, const float *ab
     uint8_t *d_p = cv.take<uint8_t>(pb);
     float *d_a = cv.take<float>(nb);  // f32 scales, or the u8 codes in the same space
     float *d_s = cv.take<float>(1);
-    NF4_CUDA_TRY(cudaMemcpyAsync(d_p, packed, pb, cudaMemcpyHostToDevice, 0));
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_p, packed, pb, cudaMemcpyHostToDevice, kHostStream));
     if (absmax) {
-        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, absmax, nb * 4, cudaMemcpyHostToDevice, 0));
-        NF4_TRY(dequantize_packed(d_p, len, d_a, nullptr, nullptr, d_o, 0));
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, absmax, nb * 4, cudaMemcpyHostToDevice, kHostStream));
+        NF4_TRY(dequantize_packed(d_p, len, d_a, nullptr, nullptr, d_o, kHostStream));
     } else {
-        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, scale_codes, nb, cudaMemcpyHostToDevice, 0));
-        NF4_CUDA_TRY(cudaMemcpyAsync(d_s, scale_of_scales, 4, cudaMemcpyHostToDevice, 0));
-        NF4_TRY(dequantize_packed(d_p, len, nullptr, reinterpret_cast<uint8_t *>(d_a), d_s, d_o, 0));
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, scale_codes, nb, cudaMemcpyHostToDevice, kHostStream));
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_s, scale_of_scales, 4, cudaMemcpyHostToDevice, kHostStream));
+        NF4_TRY(dequantize_packed(d_p, len, nullptr, reinterpret_cast<uint8_t *>(d_a), d_s, d_o, kHostStream));
     }
-    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, len * 4, cudaMemcpyDeviceToHost, 0));
-    return check_cuda(cudaStreamSynchronize(0), "nf4_dequantize_host sync");
+    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, len * 4, cudaMemcpyDeviceToHost, kHostStream));
+    return check_cuda(cudaStreamSynchronize(kHostStream), "nf4_dequantize_host sync");
 }
 
 int32_t nf4_quantize_dequantize_host(const float *values, uint64_t len,
@@ -715,10 +719,10 @@ int32_t nf4_quantize_dequantize_host(const float *values, uint64_t len,
     float *d_v = cv.take<float>(len);
     float *d_o = cv.take<float>(len);
     uint8_t *d_w = cv.take<uint8_t>(ws);
-    NF4_CUDA_TRY(cudaMemcpyAsync(d_v, values, len * 4, cudaMemcpyHostToDevice, 0));
-    NF4_TRY(nf4_quantize_dequantize_dev(d_v, len, double_quantization, d_o, d_w, ws, nullptr));
-    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, len * 4, cudaMemcpyDeviceToHost, 0));
-    return check_cuda(cudaStreamSynchronize(0), "nf4_quantize_dequantize_host sync");
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_v, values, len * 4, cudaMemcpyHostToDevice, kHostStream));
+    NF4_TRY(nf4_quantize_dequantize_dev(d_v, len, double_quantization, d_o, d_w, ws, kHostStream));
+    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, len * 4, cudaMemcpyDeviceToHost, kHostStream));
+    return check_cuda(cudaStreamSynchronize(kHostStream), "nf4_quantize_dequantize_host sync");
 }
 
 // ---- resident weight handles -----------------------------------------------------
@@ -762,11 +766,11 @@ int32_t nf4_weight_from_values_host(const float *values, uint64_t d_in, uint64_t
     int32_t st = t_arena.reserve(w->len * 4);
     if (st == NF4_OK) {
         float *d_v = static_cast<float *>(t_arena.ptr);
-        st = check_cuda(cudaMemcpyAsync(d_v, values, w->len * 4, cudaMemcpyHostToDevice, 0), "H2D values");
-        if (st == NF4_OK) st = quantize_packed(d_v, w->len, w->packed, w->absmax, 0);
+        st = check_cuda(cudaMemcpyAsync(d_v, values, w->len * 4, cudaMemcpyHostToDevice, kHostStream), "H2D values");
+        if (st == NF4_OK) st = quantize_packed(d_v, w->len, w->packed, w->absmax, kHostStream);
         if (st == NF4_OK && w->double_quantized)
-            st = double_quantize(w->absmax, w->nblocks, w->scale_codes, w->scale_of_scales, 0);
-        if (st == NF4_OK) st = check_cuda(cudaStreamSynchronize(0), "nf4_weight_from_values_host sync");
+            st = double_quantize(w->absmax, w->nblocks, w->scale_codes, w->scale_of_scales, kHostStream);
+        if (st == NF4_OK) st = check_cuda(cudaStreamSynchronize(kHostStream), "nf4_weight_from_values_host sync");
     }
     if (st == NF4_OK && w->double_quantized) {
         // The f32 scales are not part of a double-quantized weight (src/quantize.rs:304-307).
@@ -849,9 +853,9 @@ int32_t nf4_weight_dequantize_host(const nf4_weight *w, float *out) {
     NF4_TRY(check_weight_device(w, "nf4_weight_dequantize_host"));
     NF4_TRY(t_arena.reserve(w->len * 4));
     float *d_o = static_cast<float *>(t_arena.ptr);
-    NF4_TRY(dequantize_packed(w->packed, w->len, w->absmax, w->scale_codes, w->scale_of_scales, d_o, 0));
-    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, w->len * 4, cudaMemcpyDeviceToHost, 0));
-    return check_cuda(cudaStreamSynchronize(0), "nf4_weight_dequantize_host sync");
+    NF4_TRY(dequantize_packed(w->packed, w->len, w->absmax, w->scale_codes, w->scale_of_scales, d_o, kHostStream));
+    NF4_CUDA_TRY(cudaMemcpyAsync(out, d_o, w->len * 4, cudaMemcpyDeviceToHost, kHostStream));
+    return check_cuda(cudaStreamSynchronize(kHostStream), "nf4_weight_dequantize_host sync");
 }
 
 int32_t nf4_weight_attach_lora_host(nf4_weight *w, const void *lora_a, const void *lora_b,
@@ -910,12 +914,12 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
     uint8_t *d_b = cv.take<uint8_t>(bb);
     float *d_bias = cv.take<float>(w->d_out);
     uint8_t *d_ws = cv.take<uint8_t>(ws);
-    NF4_CUDA_TRY(cudaMemcpyAsync(d_x, x, xb, cudaMemcpyHostToDevice, 0));
+    NF4_CUDA_TRY(cudaMemcpyAsync(d_x, x, xb, cudaMemcpyHostToDevice, kHostStream));
     if (r && !resident) {
-        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, lora_a, ab, cudaMemcpyHostToDevice, 0));
-        NF4_CUDA_TRY(cudaMemcpyAsync(d_b, lora_b, bb, cudaMemcpyHostToDevice, 0));
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_a, lora_a, ab, cudaMemcpyHostToDevice, kHostStream));
+        NF4_CUDA_TRY(cudaMemcpyAsync(d_b, lora_b, bb, cudaMemcpyHostToDevice, kHostStream));
     }
-    if (bias) NF4_CUDA_TRY(cudaMemcpyAsync(d_bias, bias, w->d_out * 4, cudaMemcpyHostToDevice, 0));
+    if (bias) NF4_CUDA_TRY(cudaMemcpyAsync(d_bias, bias, w->d_out * 4, cudaMemcpyHostToDevice, kHostStream));
     nf4_linear_args a;
     std::memset(&a, 0, sizeof(a));
     a.struct_bytes = sizeof(a);
@@ -944,13 +948,13 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
         NF4_TRY(t_zero_scratch.get(&zs));
         a.workspace = zs;
     } else if (ws) {
-        NF4_CUDA_TRY(cudaMemsetAsync(d_ws, 0, 256, 0));
+        NF4_CUDA_TRY(cudaMemsetAsync(d_ws, 0, 256, kHostStream));
     }
     volatile int *failed = nullptr;
     NF4_TRY(host_flag_words(&failed));  // (before the launch: the kernels write their failure codes there too)
-    NF4_TRY(nf4_linear_forward_dev(&a, nullptr));
-    NF4_CUDA_TRY(cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, 0));
-    NF4_TRY(check_cuda(cudaStreamSynchronize(0), "nf4_weight_linear_forward_host sync"));
+    NF4_TRY(nf4_linear_forward_dev(&a, kHostStream));
+    NF4_CUDA_TRY(cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, kHostStream));
+    NF4_TRY(check_cuda(cudaStreamSynchronize(kHostStream), "nf4_weight_linear_forward_host sync"));
     // ... and a wait that gave up in a kernel must not pass for a result
     if (failed[0] | failed[1] | failed[2]) {
         int *ptrs[3];
