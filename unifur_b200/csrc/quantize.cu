@@ -127,7 +127,7 @@ __device__ __forceinline__ float block_scale(const float *__restrict__ absmax,
 // 32-byte sectors (lane 2j writes values 16j..16j+3 and 16j+8..16j+11, lane 2j+1 the other two
 // quads).  Four such groups are in flight per thread to cover the load latency.
 template <bool PACKED>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 8)
 dequantize_full_kernel(const uint8_t *__restrict__ codes, uint64_t nfull,
                        const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
                        const float *__restrict__ scale_of_scales, float4 *__restrict__ out) {
