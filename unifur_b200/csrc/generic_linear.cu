@@ -186,7 +186,7 @@ constexpr int kStripCols = 256;
 constexpr int kRowsWarps = 8;
 
 template <class T, int MR, bool DQ>
-__global__ void __launch_bounds__(256, MR >= 8 ? 2 : 3) in_out_rows_kernel(const GenericParams p) {
+__global__ void __launch_bounds__(256, MR >= 4 ? 2 : 3) in_out_rows_kernel(const GenericParams p) {
     extern __shared__ __align__(16) float dyn[];
     __shared__ uint32_t last_s;
     // [256 byte values][32 lanes] pairs {level of the low nibble, level of the high nibble}
@@ -347,13 +347,15 @@ __global__ void __launch_bounds__(256, MR >= 8 ? 2 : 3) in_out_rows_kernel(const
 struct RowsPlan {
     uint32_t strips, k_parts, k_chunk;
 };
-bool rows_plan(uint64_t d_in, uint64_t d_out, RowsPlan &rp) {
+bool rows_plan(uint64_t d_in, uint64_t d_out, uint64_t rows, RowsPlan &rp) {
     if (d_out % kBlock != 0 || d_in == 0 || d_in >= (1ull << 31) || d_out >= (1ull << 31)) return false;
     rp.strips = (uint32_t)((d_out + kStripCols - 1) / kStripCols);
     if (rp.strips > 248) return false;  // a byte counter per strip in the workspace's 62 counter words
-    // three CTAs per SM (64 KB of table each), and no more CTAs than fit at once: a second,
-    // partly filled round would double the time
-    uint64_t parts = 3ull * kNumSMs / rp.strips;
+    // three CTAs per SM (64 KB of table each; two where a launch carries more than two activation
+    // rows: their slices of x and the registers of eight rows leave no room for a third), and no
+    // more CTAs than fit at once: a second, partly filled round would double the time
+    const uint64_t per_sm = rows >= 3 ? 2 : 3;
+    uint64_t parts = per_sm * kNumSMs / rp.strips;
     if (parts == 0) parts = 1;
     const uint64_t most = d_in / 64 ? d_in / 64 : 1;  // a piece keeps 64 rows of W at least
     if (parts > most) parts = most;
@@ -434,7 +436,7 @@ uint64_t t_bytes(uint64_t rows, uint32_t lora_rank) { return (rows * lora_rank *
 uint64_t generic_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
     uint64_t need = lora_rank ? kCounterBytes + t_bytes(rows, lora_rank) : 0;
     RowsPlan rp;
-    if (rows <= kRowsKernelMaxRows && rows_plan(d_in, d_out, rp) && rp.k_parts > 1)
+    if (rows <= kRowsKernelMaxRows && rows_plan(d_in, d_out, rows, rp) && rp.k_parts > 1)
         need = kCounterBytes + t_bytes(rows, lora_rank) + (uint64_t)rp.k_parts * (rows < 8 ? rows : 8) * d_out * 4;
     return need;
 }
@@ -465,7 +467,7 @@ int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.layout = a.layout;
     p.y_f32 = a.y_f32;
     RowsPlan rp;
-    if (a.layout == NF4_LAYOUT_IN_OUT && a.rows <= kRowsKernelMaxRows && rows_plan(a.d_in, a.d_out, rp) &&
+    if (a.layout == NF4_LAYOUT_IN_OUT && a.rows <= kRowsKernelMaxRows && rows_plan(a.d_in, a.d_out, a.rows, rp) &&
         (reinterpret_cast<uintptr_t>(a.packed) & 3u) == 0 && (rp.k_parts == 1 || a.workspace))
         return a.io_dtype == NF4_DTYPE_F32 ? run_rows<float>(p, rp, stream) : run_rows<__nv_bfloat16>(p, rp, stream);
     return a.io_dtype == NF4_DTYPE_F32 ? run<float>(p, stream) : run<__nv_bfloat16>(p, stream);
