@@ -292,6 +292,22 @@ NF4_API int32_t nf4_sharded_linear_forward_dev(const nf4_linear_args *shard, voi
  * y, weights, adapter and workspace (the workspaces must not overlap).  count <= 4. */
 NF4_API int32_t nf4_linear_forward_grouped_dev(const nf4_linear_args *args, uint32_t count, void *stream);
 
+/* How the decode kernel (at most 16 rows) shares a forward out between its CTAs, computed on the
+ * host: k0_k1_n0_n1 receives, for CTA `cta`, the range of k it multiplies and the rows of W it owns.
+ * Returns the number of CTAs, or a negative status.  For inspection and tests. */
+NF4_API int32_t nf4_decode_share_plan(uint32_t rows, uint32_t d_in, uint32_t d_out, uint32_t lora_rank, uint32_t cta,
+                                      uint32_t *k0_k1_n0_n1);
+
+/* How the tensor-core kernel (more than 16 rows) shares a forward's 128 x 256 tiles out between its
+ * CTAs, computed on the host (no GPU needed): *ctas receives the number of CTAs; segments
+ * receives, for CTA `cta`, up to `capacity` triples (tile, first main k-stage, one past the last)
+ * in the order the CTA works on them.  Returns the number of the CTA's segments, or a negative
+ * status.  Tiles that appear with a partial range of k-stages are split between neighbouring
+ * CTAs (the one with the last stages finishes the tile).  For inspection and tests; the
+ * reference has no counterpart. */
+NF4_API int32_t nf4_prefill_share_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t cta, uint32_t *ctas,
+                                       uint32_t *segments, uint32_t capacity);
+
 /* The decode kernel puts one CTA on every SM (it needs a whole SM's shared memory), so a kernel
  * that runs beside it on another stream -- a collective gathering the previous step's outputs --
  * holds back whole CTAs of it.  A host that overlaps such work tells the library to leave `count`

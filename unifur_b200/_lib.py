@@ -104,6 +104,8 @@ SIGNATURES = {
     "nf4_linear_noalloc_scratch_bytes": (_u64, []),
     "nf4_linear_forward_grouped_dev": (_i32, [C.POINTER(LinearArgs), _u32, _vp]),
     "nf4_reserve_sms": (_i32, [_i32]),
+    "nf4_decode_share_plan": (_i32, [_u32, _u32, _u32, _u32, _u32, C.POINTER(_u32)]),
+    "nf4_prefill_share_plan": (_i32, [_u64, _u64, _u64, _u32, C.POINTER(_u32), C.POINTER(_u32), _u32]),
     "nf4_linear_forward_scatter_dev": (_i32, [C.POINTER(LinearArgs), C.POINTER(PeerOutputs), _vp]),
     "nf4_peer_arrivals_wait_dev": (_i32, [_vp, _u32, _u32, _vp]),
     "nf4_linear_forward_noalloc_dev": (_i32, [C.POINTER(LinearArgs), _vp]),

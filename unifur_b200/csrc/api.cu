@@ -511,6 +511,22 @@ int32_t nf4_peer_arrivals_wait_dev(uint32_t *own_arrivals, uint32_t expected, ui
     return decode_peer_wait(own_arrivals, expected, timeout_ns, static_cast<cudaStream_t>(stream));
 }
 
+int32_t nf4_decode_share_plan(uint32_t rows, uint32_t d_in, uint32_t d_out, uint32_t lora_rank, uint32_t cta,
+                              uint32_t *k0_k1_n0_n1) {
+    if (!k0_k1_n0_n1) return fail(NF4_ERR_INVALID_ARG, "nf4_decode_share_plan: null output");
+    const int32_t n = decode_share_plan(rows, d_in, d_out, lora_rank, cta, k0_k1_n0_n1);
+    if (n < 0) return fail(NF4_ERR_INVALID_ARG, "nf4_decode_share_plan: not a shape of the decode kernel, or no such CTA");
+    return n;
+}
+
+int32_t nf4_prefill_share_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t cta, uint32_t *ctas,
+                               uint32_t *segments, uint32_t capacity) {
+    if (!segments && capacity) return fail(NF4_ERR_INVALID_ARG, "nf4_prefill_share_plan: null segments");
+    const int32_t n = prefill_share_plan(rows, d_in, d_out, cta, ctas, segments, capacity);
+    if (n < 0) return fail(NF4_ERR_INVALID_ARG, "nf4_prefill_share_plan: not a shape of the tensor-core kernel, or no such CTA");
+    return n;
+}
+
 uint64_t nf4_linear_noalloc_scratch_bytes(void) { return decode_static_scratch_bytes(); }
 
 int32_t nf4_linear_forward_noalloc_dev(const nf4_linear_args *args, void *stream) {

@@ -1234,6 +1234,29 @@ int32_t decode_peer_wait(uint32_t *counter, uint32_t expected, uint32_t limit_ns
     return check_cuda(cudaGetLastError(), "peer_wait_kernel launch");
 }
 
+// The row ranges and parts of K as the kernel will see them, for inspection on the host: for CTA
+// `cta`, the part of K it multiplies ([k0, k1)) and its rows ([n0, n1)), by the kernel's own
+// formulas.  Returns the number of CTAs, or -1 when the shape is not the kernel's.
+int32_t decode_share_plan(uint32_t rows, uint32_t d_in, uint32_t d_out, uint32_t rank, uint32_t cta, uint32_t *out4) {
+    if (rows == 0 || rows > 16 || d_in % kSliceK != 0 || d_in > (uint32_t)kMaxParts * kMaxSlices * kSliceK) return -1;
+    if (rank != 0 && rank != 8 && rank != 16 && rank != 32 && rank != 64) return -1;
+    Plan pl;
+    pl.p = DecodeParams{};
+    if (!plan_shape(rows, d_in, d_out, rank, 1, pl, persistent_ctas())) return -1;
+    const DecodeParams &p = pl.p;
+    if (cta >= pl.grid) return -1;
+    const uint32_t part = p.kparts > 1 ? cta / p.cpp : 0u, c = cta - part * p.cpp;
+    const uint32_t s0 = part * p.part_slices, s1 = p.kw < s0 + p.part_slices ? p.kw : s0 + p.part_slices;
+    const uint32_t past = c > p.light_front ? c - p.light_front : 0u;
+    const uint32_t n0 = c * p.rows_base + (past < p.rows_extra ? past : p.rows_extra) * p.gran;
+    const uint32_t n1 = n0 + p.rows_base + (c >= p.light_front && past < p.rows_extra ? p.gran : 0u);
+    out4[0] = s0 * kSliceK;
+    out4[1] = s1 * kSliceK;
+    out4[2] = n0;
+    out4[3] = n1;
+    return (int32_t)pl.grid;
+}
+
 int32_t decode_forward(const nf4_linear_args &a, cudaStream_t stream) {
     Plan pl;
     if (!plan(a, pl)) return fail(NF4_ERR_UNSUPPORTED, "decode_forward: unsupported shape");

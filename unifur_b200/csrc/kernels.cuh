@@ -87,6 +87,7 @@ int32_t decode_forward_scatter(const nf4_linear_args &a, void *const *dest, uint
                                uint32_t rank, uint64_t ldy, bool signal, uint32_t *wait_on, uint32_t wait_expected,
                                cudaStream_t stream);
 int32_t decode_peer_wait(uint32_t *counter, uint32_t expected, uint32_t limit_ns, cudaStream_t stream);
+int32_t decode_share_plan(uint32_t rows, uint32_t d_in, uint32_t d_out, uint32_t rank, uint32_t cta, uint32_t *out4);
 int32_t decode_forward_grouped(const nf4_linear_args *a, uint32_t count, cudaStream_t stream, bool *taken);
 
 int32_t decode_selftest_wait(uint32_t limit_ns, unsigned long long *waited_ns_dev, cudaStream_t stream);
@@ -109,6 +110,8 @@ int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream);
 // prefill_gemm.cu: tcgen05 GEMM, NF4_LAYOUT_OUT_IN, bf16 activations.
 bool prefill_supported(const nf4_linear_args &a);
 uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
+int32_t prefill_share_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t cta, uint32_t *ctas,
+                           uint32_t *segments, uint32_t cap);
 int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream);
 
 }  // namespace nf4

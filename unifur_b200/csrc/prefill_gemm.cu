@@ -109,7 +109,7 @@ struct WorkList {
     uint32_t ks;       // main stages per tile
     uint32_t t_first, t_last, n_shared, n_seg, sk_tiles, cta, ctas;
 
-    __device__ void init(const PrefillParams &p, uint32_t k_stages, uint32_t cta_, uint32_t ctas_) {
+    __host__ __device__ void init(const PrefillParams &p, uint32_t k_stages, uint32_t cta_, uint32_t ctas_) {
         ks = k_stages;
         cta = cta_;
         ctas = ctas_;
@@ -126,8 +126,8 @@ struct WorkList {
         }
         n_seg = n_shared + p.dp_rounds;
     }
-    __device__ static uint64_t range_begin(uint64_t all, uint32_t c, uint32_t n) { return all * c / n; }
-    __device__ void get(uint32_t j, uint32_t &tile, uint32_t &b, uint32_t &e) const {
+    __host__ __device__ static uint64_t range_begin(uint64_t all, uint32_t c, uint32_t n) { return all * c / n; }
+    __host__ __device__ void get(uint32_t j, uint32_t &tile, uint32_t &b, uint32_t &e) const {
         if (j < n_shared) {
             tile = t_last - j;
             const uint64_t t0 = (uint64_t)tile * ks;
@@ -1083,6 +1083,30 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
 
 int32_t prefill_set_host_flag(int *mapped) {
     return check_cuda(cudaMemcpyToSymbol(g_prefill_error_host, &mapped, sizeof(mapped)), "setting the mapped failure word");
+}
+
+// The sharing of the tiles as the kernel will see it, for inspection on the host: the number of
+// CTAs and, for CTA `cta`, its segments (tile, first main k-stage, one past the last) in the order
+// it works on them.  Returns the number of segments (at most `cap` are written), or -1.
+int32_t prefill_share_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t cta, uint32_t *ctas,
+                           uint32_t *segments, uint32_t cap) {
+    if (rows <= 16 || d_in % BK != 0 || d_in == 0 || d_out == 0) return -1;
+    const Sharing sh = share_tiles(rows, d_in, d_out);
+    if (ctas) *ctas = sh.grid;
+    if (cta >= sh.grid) return -1;
+    PrefillParams p{};
+    p.sk_tiles = sh.sk_tiles;
+    p.dp_rounds = sh.dp_rounds;
+    WorkList wl;
+    wl.init(p, (uint32_t)(d_in / BK), cta, sh.grid);
+    for (uint32_t j = 0; j < wl.n_seg && j < cap; ++j) {
+        uint32_t tile, b, e;
+        wl.get(j, tile, b, e);
+        segments[3 * j] = tile;
+        segments[3 * j + 1] = b;
+        segments[3 * j + 2] = e;
+    }
+    return (int32_t)wl.n_seg;
 }
 
 int32_t prefill_error_flag_ptr(int **dev_ptr) {
