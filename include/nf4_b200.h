@@ -352,6 +352,15 @@ typedef struct nf4_peer_outputs {
 } nf4_peer_outputs;
 NF4_API int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_peer_outputs *peers,
                                                void *stream);
+/* The same exchange for forwards of any size (the tensor-core kernel's included): the rank's forward
+ * writes its columns into its OWN output in place (y = y_full[rank] + rank * d_out, ldy = ldy_full
+ * in nf4_linear_forward_dev), then this call pushes those columns -- rows x d_out_shard elements of
+ * elem_bytes -- into the same place of every other rank's output with peer stores (one pass over
+ * the shard; no gather buffer, no placing copy) and, with peers->signal, adds one arrival to every
+ * rank's counter when all of it is out.  d_out_shard * elem_bytes and the pitch must be multiples of
+ * 16 bytes.  scratch_word: four bytes of device memory, zero at first use, left zero. */
+NF4_API int32_t nf4_peer_push_columns_dev(const nf4_peer_outputs *peers, uint64_t rows, uint64_t d_out_shard,
+                                          int32_t elem_bytes, uint32_t *scratch_word, void *stream);
 NF4_API int32_t nf4_peer_arrivals_wait_dev(uint32_t *own_arrivals, uint32_t expected, uint32_t timeout_ns,
                                            void *stream);
 

@@ -214,6 +214,38 @@ def _scatter_worker(rank, world, port, results):
                           f"{torch.equal(z_mine[:m], z_ref)}, counters {cnt_mine[:2].tolist()}", flush=True)
                 ok &= good
                 dist.barrier()      # everyone has compared before the next round overwrites
+        # the same through ShardedNf4Linear.peer_store_plan: a shape of the tensor-core kernel (the
+        # forward writes its columns in place, a second kernel pushes them to the peers) and a
+        # decode shape (the kernel's own epilogue stores into the peers)
+        from unifur_b200.sharded import ShardedNf4Linear
+
+        for case, (m3, k3, n3, r3) in enumerate(((300, 1024, 1536, 64), (8, 3584, 512, 16), (2048, 512, 256, 0))):
+            g3 = torch.Generator(device=dev).manual_seed(777 + case)
+            full3 = PackedNf4Tensor.quantize(torch.randn(n3 * k3, device=dev, generator=g3) * 0.02)
+            la3 = (torch.randn(r3, k3, device=dev, generator=g3) * 0.01).bfloat16() if r3 else None
+            lb3 = (torch.randn(n3, r3, device=dev, generator=g3) * 0.01).bfloat16() if r3 else None
+            x3 = torch.randn(m3, k3, device=dev, generator=g3).bfloat16()
+            ref3 = linear_forward(x3, full3, k3, n3, _lib.LAYOUT_OUT_IN, lora_a=la3, lora_b=lb3, lora_scale=2.0)
+            lin3 = ShardedNf4Linear.from_full(full3, k3, n3, world, rank, lora_a=la3, lora_b=lb3, lora_scale=2.0)
+            pp = lin3.peer_store_plan(x3, signal=True)
+            for _rep in range(2):
+                pp.y.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                pp.run()
+                pp.wait(world)
+                torch.cuda.synchronize()
+                if m3 <= 16:
+                    good = torch.equal(pp.y, ref3)
+                else:
+                    tol = ref3.float().abs() * 2.0 ** -7 + 4e-6 * float(ref3.float().abs().max())
+                    good = bool(((pp.y.float() - ref3.float()).abs() <= tol).all())
+                good = good and int(pp.arrivals[0].item()) == 0
+                if not good:
+                    print(f"rank {rank} peer_store_plan case {case}: output differs or counter not back at zero", flush=True)
+                ok &= good
+                dist.barrier()
+            del pp
         d0, d1, d2 = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
         ok &= L.nf4_device_status(ctypes.byref(d0), ctypes.byref(d1), ctypes.byref(d2)) == 0
     finally:

@@ -108,6 +108,7 @@ SIGNATURES = {
     "nf4_prefill_share_plan": (_i32, [_u64, _u64, _u64, _u32, C.POINTER(_u32), C.POINTER(_u32), _u32]),
     "nf4_linear_forward_scatter_dev": (_i32, [C.POINTER(LinearArgs), C.POINTER(PeerOutputs), _vp]),
     "nf4_peer_arrivals_wait_dev": (_i32, [_vp, _u32, _u32, _vp]),
+    "nf4_peer_push_columns_dev": (_i32, [C.POINTER(PeerOutputs), _u64, _u64, _i32, _vp, _vp]),
     "nf4_linear_forward_noalloc_dev": (_i32, [C.POINTER(LinearArgs), _vp]),
     "nf4_weight_from_values_host": (_i32, [_vp, _u64, _u64, _i32, _i32, C.POINTER(_vp)]),
     "nf4_weight_from_packed_host": (_i32, [_vp, _vp, _vp, _f32, _u64, _u64, _i32,

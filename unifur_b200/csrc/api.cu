@@ -506,6 +506,19 @@ int32_t nf4_linear_forward_scatter_dev(const nf4_linear_args *shard, const nf4_p
                                   static_cast<cudaStream_t>(stream));
 }
 
+int32_t nf4_peer_push_columns_dev(const nf4_peer_outputs *peers, uint64_t rows, uint64_t d_out_shard,
+                                  int32_t elem_bytes, uint32_t *scratch_word, void *stream) {
+    if (!peers || peers->struct_bytes != sizeof(nf4_peer_outputs))
+        return fail(NF4_ERR_INVALID_ARG, "nf4_peer_push_columns_dev: null arguments or struct_bytes");
+    if (peers->world < 1 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world)
+        return fail(NF4_ERR_INVALID_ARG, "nf4_peer_push_columns_dev: world 1 ... 8, rank inside it");
+    if (elem_bytes != 2 && elem_bytes != 4) return fail(NF4_ERR_INVALID_ARG, "nf4_peer_push_columns_dev: elem_bytes 2 or 4");
+    const uint64_t ldy = peers->ldy_full ? peers->ldy_full : (uint64_t)peers->world * d_out_shard;
+    return push_columns(peers->y_full, peers->arrivals, (uint32_t)peers->world, (uint32_t)peers->rank, rows,
+                        d_out_shard * elem_bytes, ldy * elem_bytes, peers->signal != 0, scratch_word,
+                        static_cast<cudaStream_t>(stream));
+}
+
 int32_t nf4_peer_arrivals_wait_dev(uint32_t *own_arrivals, uint32_t expected, uint32_t timeout_ns, void *stream) {
     if (!own_arrivals) return fail(NF4_ERR_INVALID_ARG, "nf4_peer_arrivals_wait_dev: null counter");
     return decode_peer_wait(own_arrivals, expected, timeout_ns, static_cast<cudaStream_t>(stream));

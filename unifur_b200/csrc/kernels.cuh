@@ -37,6 +37,8 @@ int32_t lora_delta(const void *a, const void *b, const uint8_t *packed, const fl
 int32_t lora_grads(const void *x, const void *gy, const void *a, const void *b, uint64_t rows, uint64_t d_in,
                    uint64_t d_out, uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *ga,
                    void *gb, float *t, float *u, cudaStream_t s);
+int32_t push_columns(void *const *y_full, uint32_t *const *arrive, uint32_t world, uint32_t rank, uint64_t rows,
+                     uint64_t width_bytes, uint64_t ldy_bytes, bool signal, uint32_t *done, cudaStream_t s);
 int32_t gather_slabs(const void *slab, void *gathered, void *y, uint64_t rows, uint64_t width_bytes,
                      uint64_t ldy_bytes, void *comm, int32_t world, cudaStream_t s);
 

@@ -121,6 +121,42 @@ place_slabs_kernel(const uint4 *__restrict__ gathered, uint4 *__restrict__ y, ui
     y[r * ldy_pieces + rk * pieces_per_row + c] = gathered[i];
 }
 
+// A rank's columns of its own output, pushed into the same columns of every other rank's output
+// over NVLink: 16-byte pieces, plain loads from this GPU's memory and plain stores to the peers'
+// (mapped into this process by the host).  A persistent grid walks the pieces; when a CTA is done
+// it counts itself out on `done`, and the last one makes the launch's stores visible system-wide
+// and, if asked, adds one to every rank's arrival counter (this rank's own included).
+struct PushParams {
+    const uint4 *src;        // this rank's output at its first column
+    uint4 *dest[8];          // the ranks' outputs at the same column (own entry unused)
+    uint32_t *arrive[8];
+    uint32_t *done;          // a word of scratch, zero at first use, left zero
+    uint64_t rows, pieces_per_row, ld_pieces;
+    uint32_t world, rank, signal;
+};
+
+__global__ void __launch_bounds__(256) push_columns_kernel(const PushParams p) {
+    const uint64_t total = p.rows * p.pieces_per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = i / p.pieces_per_row, c = i - r * p.pieces_per_row;
+        const uint64_t at = r * p.ld_pieces + c;
+        const uint4 v = __ldcg(p.src + at);
+        for (uint32_t d = 0; d < p.world; ++d)
+            if (d != p.rank) p.dest[d][at] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.done, 1u) == gridDim.x - 1) {
+            *p.done = 0;
+            if (p.signal) {
+                __threadfence_system();
+                for (uint32_t d = 0; d < p.world; ++d) atomicAdd_system(p.arrive[d], 1u);
+            }
+        }
+    }
+}
+
 template <class T>
 int32_t forward_t(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, const void *a, const void *b,
                   uint32_t rank, float scale, int32_t layout, void *y, uint64_t ldy, float *t, cudaStream_t s) {
@@ -241,6 +277,38 @@ int32_t gather_slabs(const void *slab, void *gathered, void *y, uint64_t rows, u
         (uint32_t)world);
     count_launch();
     return check_cuda(cudaGetLastError(), "slab placement launch");
+}
+
+int32_t push_columns(void *const *y_full, uint32_t *const *arrive, uint32_t world, uint32_t rank, uint64_t rows,
+                     uint64_t width_bytes, uint64_t ldy_bytes, bool signal, uint32_t *done, cudaStream_t s) {
+    if (world == 0 || world > 8 || rank >= world) return fail(NF4_ERR_INVALID_ARG, "push_columns: world 1 ... 8, rank inside it");
+    if (width_bytes == 0 || width_bytes % 16 != 0 || ldy_bytes % 16 != 0 || ldy_bytes < width_bytes * world)
+        return fail(NF4_ERR_INVALID_ARG, "push_columns: the shard's width and the output's pitch must be multiples of 16 bytes");
+    if (!done) return fail(NF4_ERR_INVALID_ARG, "push_columns: needs a word of scratch");
+    PushParams p{};
+    for (uint32_t d = 0; d < world; ++d) {
+        if (!y_full[d] || (signal && !arrive[d]))
+            return fail(NF4_ERR_INVALID_ARG, "push_columns: null output or counter of rank %u", d);
+        uint8_t *base = static_cast<uint8_t *>(y_full[d]) + (size_t)rank * width_bytes;
+        if (reinterpret_cast<uintptr_t>(base) & 15u) return fail(NF4_ERR_INVALID_ARG, "push_columns: outputs must be 16-byte aligned");
+        p.dest[d] = reinterpret_cast<uint4 *>(base);
+        p.arrive[d] = arrive[d];
+    }
+    p.src = p.dest[rank];
+    p.done = done;
+    p.rows = rows;
+    p.pieces_per_row = width_bytes / 16;
+    p.ld_pieces = ldy_bytes / 16;
+    p.world = world;
+    p.rank = rank;
+    p.signal = signal ? 1u : 0u;
+    if (rows == 0) return NF4_OK;
+    const uint64_t pieces = rows * p.pieces_per_row;
+    uint64_t ctas = (pieces + 255) / 256;
+    if (ctas > (uint64_t)kNumSMs * 8) ctas = (uint64_t)kNumSMs * 8;
+    push_columns_kernel<<<(unsigned)ctas, 256, 0, s>>>(p);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "push_columns_kernel launch");
 }
 
 }  // namespace nf4

@@ -138,12 +138,13 @@ class ShardedNf4Linear:
 
 
 class PeerStorePlan:
-    """A decode-sized sharded forward without a collective: ``run()`` enqueues this rank's forward,
-    whose kernel stores its columns into every rank's ``y [rows, d_out]`` over NVLink and (with
-    ``signal``) adds one arrival to every rank's counter ``arrivals[counter_index]`` when it is
-    done; ``wait(n)`` enqueues the bounded wait for ``n`` arrivals on this rank's own counter
-    (one per rank and signalling forward).  Equal shards, rows <= 16, a shape the decode kernel
-    takes.  ``y`` and ``arrivals`` are allocated here, on every rank alike, and mapped into the
+    """A sharded forward without a collective: ``run()`` enqueues this rank's forward and gets its
+    columns into every rank's ``y [rows, d_out]`` over NVLink -- at decode sizes the kernel's own
+    epilogue stores them there (``nf4_linear_forward_scatter_dev``), otherwise the forward writes
+    them into this rank's ``y`` in place and ``nf4_peer_push_columns_dev`` pushes them to the
+    peers -- and (with ``signal``) adds one arrival to every rank's counter
+    ``arrivals[counter_index]`` when they are out; ``wait(n)`` enqueues the bounded wait for ``n``
+    arrivals on this rank's own counter (one per rank and signalling forward).  Equal shards.  ``y`` and ``arrivals`` are allocated here, on every rank alike, and mapped into the
     peers with :func:`map_peer_tensors` (``arrivals`` may be shared between plans: pass the list
     a previous plan returned in ``peer_arrivals``)."""
 
@@ -192,6 +193,15 @@ class PeerStorePlan:
         args.lora_b = self.lb.data_ptr() if rank else None
         args.lora_rank, args.lora_scale = rank, float(lin.lora_scale)
         args.workspace, args.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+        # the decode kernel stores into the peers itself; other shapes write in place and push
+        self.in_kernel = rows <= 16 and lin.d_in % 256 == 0 and lin.d_in <= 32768
+        if not self.in_kernel:
+            if wait_for:
+                raise ValueError("PeerStorePlan: only the decode-sized forward waits inside the kernel")
+            args.y = self.y.data_ptr() + lin.rank * width * 2
+            args.ldy = lin.d_out
+            self.push_word = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.rows, self.width = rows, width
         po = _lib.PeerOutputs()
         po.struct_bytes = ctypes.sizeof(_lib.PeerOutputs)
         po.world, po.rank, po.ldy_full = world, lin.rank, lin.d_out
@@ -207,7 +217,12 @@ class PeerStorePlan:
 
     def run(self) -> torch.Tensor:
         stream = self._vp(torch.cuda.current_stream(self.x.device).cuda_stream)
-        self._check(self.lib.nf4_linear_forward_scatter_dev(self._a, self._p, stream))
+        if self.in_kernel:
+            self._check(self.lib.nf4_linear_forward_scatter_dev(self._a, self._p, stream))
+        else:
+            self._check(self.lib.nf4_linear_forward_dev(self._a, stream))
+            self._check(self.lib.nf4_peer_push_columns_dev(self._p, self.rows, self.width, 2,
+                                                           self._vp(self.push_word.data_ptr()), stream))
         return self.y
 
     def wait(self, arrivals: int, timeout_ns: int = 2_000_000_000) -> None:
