@@ -956,6 +956,27 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
     ms_local = timed(plan.run_local)
     ms_all = timed(plan.run)
     flops = 2.0 * pm * pn * pk + 2.0 * pm * pr * (pk + pn)
+    peer = {}
+    if peer_stores:
+        # the same without a collective: the GEMM writes its columns into this rank's output in
+        # place, one kernel pushes them into every rank's output over NVLink and signals, a wait
+        # for all ranks' arrivals closes the forward
+        pp = lin.peer_store_plan(x, signal=True)
+
+        def run_peer():
+            pp.run()
+            pp.wait(world)
+
+        run_peer()
+        torch.cuda.synchronize()
+        dist.barrier()
+        peer_verdict = check(pp.y, plan.run().clone(), pk)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms_peer = timed(run_peer)
+        peer = {"ms_with_peer_stores": ms_peer, "peer_store_check": peer_verdict,
+                "TFLOP/s_with_peer_stores": flops / (ms_peer * 1e-3) / 1e12}
+        del pp
     out["prefill_sharded"] = {
         "workload": f"QLoRA prefill GEMM x bf16 [2048, 4096], W NF4 [14336, 4096] in {world} column shards "
                     f"of {pn // world}, rank 64; all-gather of y (58.7 MB in all) into [2048, 14336]",
@@ -967,6 +988,13 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
         "gather_share": max(0.0, (ms_all - ms_local) / ms_all), "n_gpus": world,
         "limiter": "the all-gather and the permuting copy of y follow the GEMM on the same stream",
     }
+    if peer:  # the section's figure is the faster exchange; the all-gather's stays beside it
+        sec = out["prefill_sharded"]
+        sec["TFLOP/s_with_gather"] = sec["TFLOP/s"]
+        sec["TFLOP/s"] = peer.pop("TFLOP/s_with_peer_stores")
+        sec.update(peer)
+        sec["limiter"] = ("with peer stores: the push of the shard's columns (NVLink) follows the GEMM on the same "
+                          "stream; with the all-gather: the gather and the permuting copy do")
     del full, la, lb, x, lin, plan
     torch.cuda.empty_cache()
 
@@ -1033,11 +1061,39 @@ def sharded_sections(torch, dist, lib, _lib, dev, rank: int, world: int, iters: 
             del pplans
         else:
             fl = sum(2.0 * m * k * n + 2.0 * m * 16 * (k + n) for _nm, k, n in QWEN2_7B_BLOCK)
+            peer = {}
+            if peer_stores:
+                pplans, arr = [], None
+                for i, pl in enumerate(plans):
+                    pp = pl.lin.peer_store_plan(pl.x, signal=(i == len(plans) - 1), peer_arrivals=arr)
+                    arr = pp.peer_arrivals
+                    pplans.append(pp)
+
+                def run_peer():
+                    for pp in pplans:
+                        pp.run()
+                    pplans[0].wait(world)
+
+                run_peer()
+                torch.cuda.synchronize()
+                dist.barrier()
+                pchecks = [check(pp.y, pl.run().clone(), k) for (_nm, k, _n), pl, pp in zip(QWEN2_7B_BLOCK, plans, pplans)]
+                torch.cuda.synchronize()
+                dist.barrier()
+                ms_peer = timed(run_peer)
+                peer = {"ms_with_peer_stores": ms_peer, "TFLOP/s_with_peer_stores": fl / (ms_peer * 1e-3) / 1e12,
+                        "peer_store_check": "MISMATCH" if "MISMATCH" in pchecks else (
+                            "ok" if all(v == "ok" for v in pchecks) else "ok_within_one_bf16_ulp")}
+                del pplans
             blk[label] = {"ms_local": ms_local, "ms_with_gather": ms_all,
                           "TFLOP/s": fl / (ms_all * 1e-3) / 1e12,
                           "TFLOP/s_per_gpu_local": fl / world / (ms_local * 1e-3) / 1e12,
                           "frac_per_gpu_local": fl / world / (ms_local * 1e-3) / 1e12 / tf_peak,
                           "gather_check": worst, "per_projection": checks}
+            if peer:
+                blk[label]["TFLOP/s_with_gather"] = blk[label]["TFLOP/s"]
+                blk[label]["TFLOP/s"] = peer.pop("TFLOP/s_with_peer_stores")
+                blk[label].update(peer)
         del plans
         torch.cuda.empty_cache()
     blk["workload"] = (f"Qwen2-7B-shaped block, 7 NF4 linears in {world} column shards each "
