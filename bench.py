@@ -697,8 +697,9 @@ def reference_orientation_section(torch, lib, _lib, dev, iters: int = 20):
     stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
     out = {"workload": "x f32 [M, 4096], W NF4 [4096, 11008] (blocks along d_out), LoRA rank 16 in f32; "
-                       "CUDA-core strip kernel, f32 dequantisation and sums; 160 MB flush write before every "
-                       "forward, outside the timed events"}
+                       "up to 64 rows the CUDA-core strip kernel (f32 dequantisation and sums), more rows the "
+                       "tensor-core GEMM over the repacked weight; 160 MB flush write before every forward, "
+                       "outside the timed events"}
     for m in MS:
         x = torch.randn(m, K, device=dev, generator=g)
         y = torch.zeros(m, N, device=dev)
@@ -717,6 +718,25 @@ def reference_orientation_section(torch, lib, _lib, dev, iters: int = 20):
         gbs = by / (ms * 1e-3) / 1e9
         out[f"M={m}"] = {"us": ms * 1e3, "GB/s": gbs, "algorithmic_bytes": by, "frac": gbs / hbm_peak,
                          "peak_kind": f"of {peak_kind}"}
+    # more than 64 rows: nibbles and scales repacked into the workspace, then the tensor-core GEMM
+    pm = 2048
+    x = torch.randn(pm, K, device=dev, generator=g)
+    y = torch.zeros(pm, N, device=dev)
+    ws = torch.zeros(max(int(lib.nf4_linear_workspace_bytes(pm, K, N, RANK)), 256), dtype=torch.uint8, device=dev)
+    a = _lib.LinearArgs()
+    a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+    a.layout, a.io_dtype = _lib.LAYOUT_IN_OUT, _lib.DTYPE_F32
+    a.rows, a.d_in, a.d_out = pm, K, N
+    a.x, a.packed, a.absmax = x.data_ptr(), wq.codes.data_ptr(), wq.absmax.data_ptr()
+    a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb.data_ptr(), RANK, SCALE
+    a.y, a.ldy = y.data_ptr(), N
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    ms, _ = time_flushed(torch, lambda _i: _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), stream())),
+                         flush, iters)
+    flops = 2.0 * pm * N * K + 2.0 * pm * RANK * (K + N)
+    out[f"M={pm}"] = {"ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "flops": flops,
+                      "frac": flops / (ms * 1e-3) / 1e12 / _tf, "peak_kind": f"of {peak_kind} (burst)",
+                      "path": "repacking kernels + f16 conversion + tcgen05 GEMM, f32 in and out"}
     return out
 
 

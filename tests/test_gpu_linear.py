@@ -213,6 +213,47 @@ def test_reference_orientation_at_decode_sizes(oracle, rows, d_in, d_out, r, dq,
         assert np.array_equal(y16, torch.from_numpy(got).bfloat16().float().numpy())
 
 
+@pytest.mark.parametrize("rows,d_in,d_out,r,dq,f32,bias", [
+    (65, 128, 64, 0, False, True, False),     # the smallest shape: one tile, half of its weight rows empty
+    (200, 512, 320, 4, True, True, True),     # d_out = 2.5 tiles; f32 factors enter as rank 8
+    (300, 1024, 768, 8, False, False, True),  # bf16 activations and factors
+    (257, 4096, 1024, 64, False, True, False),  # rank 64 in f32: two 64-rank chunks per half of T
+    (1000, 2048, 2048, 16, True, False, False),
+])
+def test_reference_orientation_at_prefill_sizes(oracle, rows, d_in, d_out, r, dq, f32, bias):
+    # W [d_in, d_out] at more than 64 activation rows: nibbles and scales are repacked into the
+    # workspace and the tensor-core GEMM multiplies (f16 operands, f32 sums): rel. L2 <= 1e-3
+    rng = np.random.default_rng(800 + rows + d_in + d_out)
+    w = (rng.standard_normal((d_in, d_out)) * 0.02).astype(np.float32)
+    packed, absmax = oracle.quantize_packed(w)
+    sc = sos = None
+    if dq:
+        sc, sos = oracle.double_quantize(absmax)
+    x = rng.standard_normal((rows, d_in)).astype(np.float32)
+    x[3] *= 2.0 ** 18      # rows outside f16's range on both sides
+    x[5] *= 2.0 ** -22
+    la = lb = None
+    if r:
+        la = (rng.standard_normal((d_in, r)) * 0.05).astype(np.float32)
+        lb = rng.uniform(-0.5, 0.5, (r, d_out)).astype(np.float32)   # an adapter term as large as the base term
+    b = rng.standard_normal(d_out).astype(np.float32) if bias else None
+    if not f32:
+        x = bf16_round(oracle, x)
+        if r:
+            la, lb = bf16_round(oracle, la), bf16_round(oracle, lb)
+    ref = oracle.qlora_forward_burn(x, packed, None if dq else absmax, d_in, d_out, la, lb, 2.0, b, sc,
+                                    sos if dq else 0.0)
+    dt = _lib.DTYPE_F32 if f32 else _lib.DTYPE_BF16
+    kw = dict(bias=b, lora_a=la, lora_b=lb, scale=2.0, scale_codes=sc, sos=sos)
+    got = run_forward(_lib.LAYOUT_IN_OUT, dt, x, packed, None if dq else absmax, d_in, d_out, y_f32=True, calls=2, **kw)
+    assert rel_l2(got, ref) <= 1e-3
+    for rows_ in (slice(0, 3), slice(3, 4), slice(5, 6), slice(rows - 1, rows)):   # every row on its own scale
+        assert rel_l2(got[rows_], ref[rows_]) <= 1e-3, rows_
+    if not f32:
+        y16 = run_forward(_lib.LAYOUT_IN_OUT, dt, x, packed, None if dq else absmax, d_in, d_out, **kw)
+        assert rel_l2(y16, ref) <= REL_L2_BF16 + 2.0 ** -9
+
+
 def test_layout_kat_minus_three(oracle):
     # qwennet.rs:2196-2211: y[o] = sum_i x[i] W[i][o] with W = [[1,2,3],[4,5,6]] (values on a
     # grid NF4 cannot hold exactly, so compare against the oracle's own dequantized weight)

@@ -438,7 +438,7 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     if (decode2_supported(*args)) {
         return decode2_forward(*args, s);
     }
-    if (prefill_supported(*args)) {
+    if (prefill_supported(*args) || prefill_in_out_supported(*args)) {
         return prefill_forward(*args, s);
     }
     return generic_forward(*args, s);

@@ -35,9 +35,18 @@
 // activation rows its N (256 accumulator columns).  Both operands are f16 with f32 accumulation:
 // rounding the dequantised weight to bf16 instead would cost ~1.6e-3 relative error, above the
 // 1e-3 parity bar, while f16 costs ~3e-4.  The bf16 activations are converted to f16 by a
-// pre-pass (exact for every value inside f16's range; a row whose magnitude exceeds 32768 is
-// divided by a power of two that the epilogue multiplies back), which also produces the LoRA
-// intermediate.
+// pre-pass (exact for every value inside f16's range; a row whose largest magnitude exceeds 32768
+// or lies below 2^-8 is divided by a power of two that the epilogue multiplies back), which also
+// produces the LoRA intermediate.
+//
+// The other orientation (W [K][N] with the 64-blocks along N, the reference's own; f32 or bf16
+// activations) comes through the same GEMM at more than 64 rows: three small kernels first write the
+// transposed nibbles, the scales as f16 [N / 64][K] and the adapter factors in this kernel's
+// orientation into the workspace (the nibbles exactly; the scales with the rounding the dequantisers
+// apply anyway).  A weight row's scale then changes with every k: a lane loads the pair of scales of
+// k = 2 lane, 2 lane + 1 of its stage (one 128-byte line per warp) and the warp hands them round
+// with shuffles while it multiplies (template parameter PERK).  f32 activations are converted to f16
+// directly, every row divided by its own power of two.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -72,6 +81,7 @@ constexpr int kThreads = 27 * 32;
 constexpr int kFirstExpanderWarp = 7;      // sixteen warps
 constexpr int kFirstEpilogueWarpB = 23;    // the second set of four epilogue warps
 constexpr int kExpanderGroups = 4;         // of four warps (one per TMEM lane quarter) each
+constexpr uint64_t kInOutMinRows = 65;     // the other weight orientation comes here from this many rows on
 
 // barrier slots
 constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kXStages, kBarAFull = kBarXEmpty + kXStages,
@@ -86,6 +96,10 @@ struct PrefillParams {
     const float *scale_of_scales;
     const float *bias;
     const float *row_scale;       // [M] power-of-two factor each activation row was divided by
+    // Weights that came in the other orientation ([d_in][d_out], blocks along d_out) are repacked
+    // before the GEMM: `codes` then holds the transposed nibbles, and a weight's scale depends on
+    // k, not on the k-stage: scales_t[n / 64][k] as f16, already divided by the weight's power of two.
+    const __half *scales_t;
     uint32_t M, N, K, rank;
     uint32_t lora_chunks;  // ceil(rank / 64); T is [M][2 * 64 * lora_chunks] (hi halves, then lo)
     uint32_t m_tiles, n_tiles;
@@ -254,9 +268,26 @@ __device__ __forceinline__ void expand_half(const LevelTables &t, const uint4 &c
     }
 }
 
+// The same with a scale per k: lane j of the warp holds the f16 pair of scales of k = 2j, 2j + 1
+// of this stage (`pairs`); `first` is the pair that goes with out[0].
+__device__ __forceinline__ void expand_half_per_k(const LevelTables &t, const uint4 &c, uint32_t pairs,
+                                                  int first, uint32_t (&out)[16]) {
+    const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t a, b, c2, d;
+        expand4(t, w[i], a, b);
+        expand4(t, w[i] >> 16, c2, d);
+        out[4 * i + 0] = hmul2(a, __shfl_sync(0xffffffffu, pairs, first + 4 * i + 0));
+        out[4 * i + 1] = hmul2(b, __shfl_sync(0xffffffffu, pairs, first + 4 * i + 1));
+        out[4 * i + 2] = hmul2(c2, __shfl_sync(0xffffffffu, pairs, first + 4 * i + 2));
+        out[4 * i + 3] = hmul2(d, __shfl_sync(0xffffffffu, pairs, first + 4 * i + 3));
+    }
+}
+
 struct RowStage {
     uint4 c0, c1;  // the row's 64 packed codes of one k-stage
-    float scale;
+    float scale;   // PERK: the bits of this lane's pair of f16 scales
 };
 
 // The tensor-core GEMM scales the expanded levels in f16, so block scales must sit inside f16's
@@ -273,7 +304,7 @@ __device__ __forceinline__ int weight_exponent(const float *absmax, const uint8_
     return min(max(e, -100), 100);
 }
 
-template <bool YF32>
+template <bool YF32, bool PERK>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t,
                const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_y,
@@ -664,16 +695,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 p.codes + (size_t)n * (p.K / 2) + (size_t)ks * 32);
             rs.c0 = __ldg(src);
             rs.c1 = __ldg(src + 1);
-            const size_t blk = (size_t)n * blocks_per_row + ks;
-            rs.scale = (p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos)) * w_down;
+            if constexpr (PERK) {
+                // the warp's 32 weight rows lie in one 64-block of the original rows: one 128-byte
+                // line of scales for the stage, a pair per lane
+                const uint32_t *line = reinterpret_cast<const uint32_t *>(
+                    p.scales_t + (size_t)((n - lane) >> 6) * p.K + (size_t)ks * BK);
+                rs.scale = __uint_as_float(__ldg(line + lane));
+            } else {
+                const size_t blk = (size_t)n * blocks_per_row + ks;
+                rs.scale = (p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos)) * w_down;
+            }
         };
         auto emit = [&](const Pos &pos, const RowStage &rs) -> bool {
             const uint32_t cnt = pos.cnt;
             const uint32_t s = cnt % kAStages, ph = (cnt / kAStages) & 1u;
             const uint32_t dst = lane_base + s * kAStageCols;
             uint32_t lo[16], hi[16];
-            expand_half(tables, rs.c0, rs.scale, lo);
-            expand_half(tables, rs.c1, rs.scale, hi);
+            if constexpr (PERK) {
+                expand_half_per_k(tables, rs.c0, __float_as_uint(rs.scale), 0, lo);
+                expand_half_per_k(tables, rs.c1, __float_as_uint(rs.scale), 16, hi);
+            } else {
+                expand_half(tables, rs.c0, rs.scale, lo);
+                expand_half(tables, rs.c1, rs.scale, hi);
+            }
             if (!ptx::mbar_wait_suspended(bar(kBarAEmpty + s), ph ^ 1u)) return false;
             ptx::tc_fence_after();
             tmem_st32(dst, lo, hi);
@@ -726,8 +770,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 // One CTA per 16 rows of x, sixteen warps splitting K.  x is read once:
 //   1. xh[m][k] = f16(x[m][k]) is written at once (exact inside f16's range) while the row
 //      maxima are collected; row_scale[m] = 1, or the power of two that brings a row whose
-//      magnitude exceeds 32768 back under it, in which case that row is converted again as
-//      f16(x / row_scale) at the end (rare).
+//      largest magnitude exceeds 32768 or lies below 2^-8 to [16384, 32768), in which case that
+//      row is converted again as f16(x / row_scale) at the end (rare).
 //   2. with an adapter: T = lora_scale * (x A^T) / row_scale, written as bf16 hi / lo halves:
 //      T[m][c] for c < 64*chunks holds bf16(T), T[m][64*chunks + c] holds bf16(T - bf16(T));
 //      columns beyond the rank are zero.  The same registers of x feed warp MMAs against A.
@@ -762,6 +806,9 @@ __device__ __forceinline__ uint4 bf16x8_to_f16x8(const uint4 &v, float is) {
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// XH_READY: the activations arrive as the f16 copy itself (made, with the row scales, by
+// x_f32_to_f16_kernel) and the adapter factor as f16: only T is computed, with f16 MMAs.
+template <bool XH_READY>
 __global__ void __launch_bounds__(kTThreads)
 prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
                        uint32_t M, uint32_t K, uint32_t rank, uint32_t chunks, float scale,
@@ -801,7 +848,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
         auto k_of = [&](uint32_t it) { return (warp + kTWarps * it) * 32 + 8 * t; };
         auto load = [&](PrepassPiece &pc, uint32_t it) {
             const uint32_t k = k_of(it);
-            const bool in = it < n_it && k + 8 <= K;
+            const bool in = it < n_it && k + 8 <= K && (!XH_READY || rank != 0);
             pc.xa = pc.xb = make_uint4(0, 0, 0, 0);
             if (in && row_a) pc.xa = __ldg(reinterpret_cast<const uint4 *>(x + off_a + k));
             if (in && row_b) pc.xb = __ldg(reinterpret_cast<const uint4 *>(x + off_b + k));
@@ -814,7 +861,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
         };
         auto process = [&](const PrepassPiece &pc, uint32_t it) {
             const uint32_t k = k_of(it);
-            if (chunk == 0 && it < n_it && k + 8 <= K) {
+            if (!XH_READY && chunk == 0 && it < n_it && k + 8 <= K) {
                 if (row_a) {
                     mx_a = bf16x2_absmax_bits(pc.xa.x, bf16x2_absmax_bits(pc.xa.y, mx_a));
                     mx_a = bf16x2_absmax_bits(pc.xa.z, bf16x2_absmax_bits(pc.xa.w, mx_a));
@@ -829,8 +876,13 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             if (rank) {
                 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    ptx::mma_16816_bf16(acc[u], pc.xa.x, pc.xb.x, pc.xa.y, pc.xb.y, pc.bv[u].x, pc.bv[u].y);
-                    ptx::mma_16816_bf16(acc[u], pc.xa.z, pc.xb.z, pc.xa.w, pc.xb.w, pc.bv[u].z, pc.bv[u].w);
+                    if (XH_READY) {
+                        ptx::mma_16816_f16(acc[u], pc.xa.x, pc.xb.x, pc.xa.y, pc.xb.y, pc.bv[u].x, pc.bv[u].y);
+                        ptx::mma_16816_f16(acc[u], pc.xa.z, pc.xb.z, pc.xa.w, pc.xb.w, pc.bv[u].z, pc.bv[u].w);
+                    } else {
+                        ptx::mma_16816_bf16(acc[u], pc.xa.x, pc.xb.x, pc.xa.y, pc.xb.y, pc.bv[u].x, pc.bv[u].y);
+                        ptx::mma_16816_bf16(acc[u], pc.xa.z, pc.xb.z, pc.xa.w, pc.xb.w, pc.bv[u].z, pc.bv[u].w);
+                    }
                 }
             }
         };
@@ -843,7 +895,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             process(p1, it + 1);
         }
 
-        if (chunk == 0) {
+        if (!XH_READY && chunk == 0) {
             atomicMax(&row_max_bits[g], mx_a);
             atomicMax(&row_max_bits[g + 8], mx_b);
         }
@@ -857,14 +909,18 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             }
         }
         __syncthreads();
-        if (chunk == 0) {
+        if (XH_READY && chunk == 0) {
+            if (threadIdx.x < 16) inv_scale[threadIdx.x] = 1.0f;  // the rows arrive scaled
+            __syncthreads();
+        }
+        if (!XH_READY && chunk == 0) {
             if (threadIdx.x < 16) {
                 const float mx = __uint_as_float(row_max_bits[threadIdx.x]);
                 float sc = 1.0f;
-                if (mx > 32768.0f && mx < __int_as_float(0x7f800000)) {
+                if ((mx > 32768.0f || (mx < 0.00390625f && mx >= 1.1754944e-38f)) && mx < __int_as_float(0x7f800000)) {
                     int e;
                     frexpf(mx, &e);             // mx = f * 2^e with f in [0.5, 1)
-                    sc = ldexpf(1.0f, e - 15);  // mx / sc lands in [16384, 32768)
+                    sc = ldexpf(1.0f, e - 15 < -100 ? -100 : e - 15);  // mx / sc lands in [16384, 32768)
                 }
                 inv_scale[threadIdx.x] = 1.0f / sc;  // exact: sc is a power of two
                 if (threadIdx.x < rows) row_scale[m0 + threadIdx.x] = sc * w_up;  // both factors of the outputs
@@ -894,6 +950,147 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             }
         }
         __syncthreads();
+    }
+}
+
+// ---- weights in the other orientation: repacking before the GEMM ---------------------------
+// W [d_in][d_out] with the 64-blocks along d_out (the reference's Burn layout) is brought into the
+// form the GEMM's dequantisers read: codes_t[n][k / 2] (the same nibbles, transposed, so exact) and
+// scales_t[n / 64][k] (f16 of scale / 2^e, the rounding the GEMM applies to a scale anyway).
+
+// One CTA: 64 rows (k) x 128 columns (n) of nibbles through shared memory.
+__global__ void __launch_bounds__(256)
+repack_codes_kernel(const uint8_t *__restrict__ codes, uint8_t *__restrict__ codes_t, uint32_t K, uint32_t N) {
+    __shared__ __align__(16) uint8_t tile[64][80];  // 64 packed bytes of a row, padded
+    const uint32_t n0 = blockIdx.x * 128, k0 = blockIdx.y * 64, t = threadIdx.x;
+    {
+        const uint32_t r = t >> 2, seg = t & 3u;  // 16 bytes = 32 columns per thread
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (n0 + seg * 32 < N)
+            v = __ldg(reinterpret_cast<const uint4 *>(codes + (size_t)(k0 + r) * (N / 2) + n0 / 2 + seg * 16));
+        *reinterpret_cast<uint4 *>(&tile[r][seg * 16]) = v;
+    }
+    __syncthreads();
+    const uint32_t n = t & 127u, kh = t >> 7;  // a column and half of the rows: 32 nibbles = 16 bytes out
+    if (n0 + n >= N) return;
+    const uint32_t byte = n >> 1, sh = (n & 1u) * 4;
+    uint32_t w[4];
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t acc = 0;
+        #pragma unroll
+        for (int j = 0; j < 8; ++j)
+            acc |= ((uint32_t)(tile[kh * 32 + i * 8 + j][byte] >> sh) & 15u) << (4 * j);
+        w[i] = acc;
+    }
+    *reinterpret_cast<uint4 *>(codes_t + (size_t)(n0 + n) * (K / 2) + (k0 + kh * 32) / 2) =
+        make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// scales_t[b][k] = f16(scale(k, b) / 2^e), scale(k, b) the scale of block k * (N / 64) + b.
+__global__ void __launch_bounds__(256)
+repack_scales_kernel(const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
+                     const float *__restrict__ scale_of_scales, __half *__restrict__ scales_t, uint32_t K,
+                     uint32_t blocks_per_row) {
+    __shared__ float tile[32][33];
+    const int w_exp = weight_exponent(absmax, scale_codes, scale_of_scales);
+    const float w_down = ldexpf(1.0f, -w_exp);
+    const float sos = scale_codes ? __ldg(scale_of_scales) : 0.0f;
+    const uint32_t b0 = blockIdx.x * 32, k0 = blockIdx.y * 32, tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+    for (uint32_t r = ty; r < 32; r += 8) {
+        const uint32_t k = k0 + r, b = b0 + tx;
+        float v = 0.0f;
+        if (k < K && b < blocks_per_row) {
+            const size_t blk = (size_t)k * blocks_per_row + b;
+            v = (absmax ? __ldg(absmax + blk) : dq_scale(__ldg(scale_codes + blk), sos)) * w_down;
+        }
+        tile[r][tx] = v;
+    }
+    __syncthreads();
+    for (uint32_t r = ty; r < 32; r += 8) {
+        const uint32_t b = b0 + r, k = k0 + tx;
+        if (k < K && b < blocks_per_row) scales_t[(size_t)b * K + k] = __float2half_rn(tile[tx][r]);
+    }
+}
+
+// The adapter factors in the orientation and types the pre-pass and the GEMM read them in.
+// From A [d_in][r], B [r][d_out] of type T:
+//   bf16: a_t[j][k] = A[k][j], b_t[n][j] = B[j][n] (rank_out = r): exact.
+//   f32:  a_t[j][k] = a_t[r + j][k] = f16(A[k][j]); b_t[n][j] = bf16(B[j][n]), b_t[n][r + j] = the
+//         bf16 of what that rounding left: as an adapter of rank 2 r whose intermediate holds every
+//         column twice, B enters the product with sixteen bits of mantissa.
+template <class T>
+__global__ void __launch_bounds__(256)
+repack_adapter_kernel(const T *__restrict__ a, const T *__restrict__ b, uint16_t *__restrict__ a_t,
+                      __nv_bfloat16 *__restrict__ b_t, uint32_t K, uint32_t N, uint32_t r) {
+    constexpr bool kF32 = sizeof(T) == 4;
+    const uint32_t rank_out = kF32 ? 2 * r : r;
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t na = (uint64_t)r * K, nb = (uint64_t)N * r;
+    if (i < na) {
+        const uint32_t j = (uint32_t)(i / K), k = (uint32_t)(i % K);
+        if constexpr (kF32) {
+            const __half h = __float2half_rn(a[(size_t)k * r + j]);
+            a_t[i] = __half_as_ushort(h);
+            a_t[na + i] = __half_as_ushort(h);
+        } else {
+            a_t[i] = reinterpret_cast<const uint16_t *>(a)[(size_t)k * r + j];
+        }
+    } else if (i < na + nb) {
+        const uint64_t e = i - na;
+        const uint32_t n = (uint32_t)(e / r), j = (uint32_t)(e % r);
+        if constexpr (kF32) {
+            const float v = b[(size_t)j * N + n];
+            const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+            b_t[(size_t)n * rank_out + j] = hi;
+            b_t[(size_t)n * rank_out + r + j] = __float2bfloat16_rn(v - __bfloat162float(hi));
+        } else {
+            b_t[(size_t)n * rank_out + j] = b[(size_t)j * N + n];
+        }
+    }
+}
+
+// f32 activations: xh[m][k] = f16(x[m][k] / sc), sc the power of two that brings the row's largest
+// finite magnitude into [16384, 32768) (any row, so small activations keep their bits too);
+// row_scale[m] = sc * 2^e with e the weight's exponent.  One CTA per row.
+__global__ void __launch_bounds__(256)
+x_f32_to_f16_kernel(const float *__restrict__ x, uint32_t K, __half *__restrict__ xh, float *__restrict__ row_scale,
+                    const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
+                    const float *__restrict__ scale_of_scales) {
+    __shared__ uint32_t mx_bits;
+    const uint32_t m = blockIdx.x;
+    const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)m * K);
+    if (threadIdx.x == 0) mx_bits = 0;
+    __syncthreads();
+    uint32_t mx = 0;
+    for (uint32_t c = threadIdx.x; c < K / 4; c += 256) {
+        const float4 v = __ldg(row + c);
+        const uint32_t b[4] = {__float_as_uint(v.x) & 0x7fffffffu, __float_as_uint(v.y) & 0x7fffffffu,
+                               __float_as_uint(v.z) & 0x7fffffffu, __float_as_uint(v.w) & 0x7fffffffu};
+        #pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (b[q] < 0x7f800000u) mx = max(mx, b[q]);
+    }
+    #pragma unroll
+    for (int s = 16; s > 0; s >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    if ((threadIdx.x & 31u) == 0) atomicMax(&mx_bits, mx);
+    __syncthreads();
+    const float largest = __uint_as_float(mx_bits);
+    float sc = 1.0f;
+    if (largest >= 1.1754944e-38f) {  // a normal number
+        int e;
+        frexpf(largest, &e);
+        e = e - 15 < -100 ? -100 : e - 15;  // 1 / sc stays finite
+        sc = ldexpf(1.0f, e);
+    }
+    const float is = 1.0f / sc;
+    if (threadIdx.x == 0)
+        row_scale[m] = sc * ldexpf(1.0f, weight_exponent(absmax, scale_codes, scale_of_scales));
+    uint2 *out = reinterpret_cast<uint2 *>(xh + (size_t)m * K);
+    for (uint32_t c = threadIdx.x; c < K / 4; c += 256) {
+        const float4 v = __ldg(row + c);
+        const __half2 lo = __floats2half2_rn(v.x * is, v.y * is), hi = __floats2half2_rn(v.z * is, v.w * is);
+        out[c] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
     }
 }
 
@@ -987,10 +1184,12 @@ Sharing share_tiles(uint64_t rows, uint64_t d_in, uint64_t d_out) {
 
 struct WorkspaceLayout {
     uint64_t off_xh, off_scale, off_t, off_flags, off_partial, bytes;
+    uint64_t off_codes_t, off_scales_t, off_a_t, off_b_t;  // the repacked weight and adapter (other orientation only)
 };
 // f16 copy of x | row scales | T (bf16 hi/lo) | flags and partial sums of the split tiles; d_in is
 // bounded so that rows * d_in * 2 fits
-WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
+WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank,
+                                 bool repacked = false) {
     auto up = [](uint64_t v) { return (v + 255) / 256 * 256; };
     WorkspaceLayout w;
     w.off_xh = 0;
@@ -1000,17 +1199,55 @@ WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint64_t d_out, u
     const Sharing sh = share_tiles(rows, d_in, d_out);
     w.off_partial = w.off_flags + up((uint64_t)sh.grid * 4);
     w.bytes = w.off_partial + (sh.sk_tiles ? (uint64_t)sh.grid * BM * BN * 4 : 0);
+    w.off_codes_t = w.off_scales_t = w.off_a_t = w.off_b_t = 0;
+    if (repacked) {  // `lora_rank` is the rank the GEMM sees (twice the adapter's for f32 factors)
+        w.off_codes_t = up(w.bytes);
+        w.off_scales_t = w.off_codes_t + up(d_in * d_out / 2);
+        w.off_a_t = w.off_scales_t + up((d_out / 64) * d_in * 2);
+        w.off_b_t = w.off_a_t + up((uint64_t)lora_rank * d_in * 2);
+        w.bytes = w.off_b_t + up(d_out * (uint64_t)lora_rank * 2);
+    }
     return w;
 }
 }  // namespace
 
 uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
     if (rows <= 16 || d_in % 64 != 0 || d_in == 0 || d_out == 0) return 0;
-    return workspace_layout(rows, d_in, d_out, lora_rank).bytes;
+    uint64_t need = workspace_layout(rows, d_in, d_out, lora_rank).bytes;
+    if (rows >= kInOutMinRows && d_out % 64 == 0) {  // the other orientation, f32 factors at worst
+        const uint64_t other = workspace_layout(rows, d_in, d_out, 2 * lora_rank, true).bytes;
+        if (other > need) need = other;
+    }
+    return need;
+}
+
+// The reference's orientation (W [d_in][d_out], blocks along d_out) at more than 64 rows: repacked
+// into the workspace, then the same GEMM.  Fewer rows stay with the CUDA-core strip kernel, whose
+// f32 arithmetic is the reference's own.
+bool prefill_in_out_supported(const nf4_linear_args &a) {
+    if (a.layout != NF4_LAYOUT_IN_OUT) return false;
+    if (a.io_dtype != NF4_DTYPE_BF16 && a.io_dtype != NF4_DTYPE_F32) return false;
+    if (a.rows < kInOutMinRows) return false;
+    if (a.d_in % 64 != 0 || a.d_out % 64 != 0 || a.d_in >= (1ull << 31) || a.d_out >= (1ull << 31) ||
+        a.rows >= (1ull << 31))
+        return false;
+    const bool f32 = a.io_dtype == NF4_DTYPE_F32;
+    const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
+    const uint64_t ybytes = (a.y_f32 || f32) ? 4 : 2;
+    if ((ldy * ybytes) % 16 != 0 || !aligned16(a.y) || !aligned16(a.x) || !aligned16(a.packed)) return false;
+    if (a.lora_a) {
+        const uint32_t rank = f32 ? 2 * a.lora_rank : a.lora_rank;  // as the GEMM sees it
+        if (rank > 256 || rank % 8 != 0) return false;
+    }
+    return true;
 }
 
 int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
-    if (!prefill_supported(a)) return fail(NF4_ERR_UNSUPPORTED, "prefill_forward: unsupported shape");
+    const bool repacked = a.layout == NF4_LAYOUT_IN_OUT;
+    if (!(repacked ? prefill_in_out_supported(a) : prefill_supported(a)))
+        return fail(NF4_ERR_UNSUPPORTED, "prefill_forward: unsupported shape");
+    const bool x_f32 = a.io_dtype == NF4_DTYPE_F32;  // only in the other orientation
+    const bool y_f32 = a.y_f32 || x_f32;
     PrefillParams p{};
     p.codes = a.packed;
     p.absmax = a.absmax;
@@ -1021,12 +1258,14 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.N = (uint32_t)a.d_out;
     p.K = (uint32_t)a.d_in;
     p.rank = a.lora_a ? a.lora_rank : 0;
+    if (repacked && x_f32) p.rank *= 2;  // see repack_adapter_kernel
     p.lora_chunks = lora_chunks_of(p.rank);
     p.m_tiles = (p.M + BN - 1) / BN;
     p.n_tiles = (p.N + BM - 1) / BM;
     const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
 
-    const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.N, p.rank);
+    const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.N, p.rank, repacked);
+    if (a.workspace_bytes < wl.bytes) return fail(NF4_ERR_INVALID_ARG, "prefill_forward: workspace too small");
     const Sharing sh = share_tiles(p.M, p.K, p.N);
     p.sk_tiles = sh.sk_tiles;
     p.dp_rounds = sh.dp_rounds;
@@ -1038,10 +1277,49 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.row_scale = row_scale;
     p.sk_flags = reinterpret_cast<uint32_t *>(ws + wl.off_flags);
     p.partial = reinterpret_cast<float *>(ws + wl.off_partial);
-    prefill_prepass_kernel<<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
-        static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(a.lora_a), p.M, p.K,
-        p.rank, p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales,
-        p.sk_flags, sh.grid);
+    const void *lora_a = a.lora_a, *lora_b = a.lora_b;
+    if (repacked) {
+        uint8_t *codes_t = ws + wl.off_codes_t;
+        __half *scales_t = reinterpret_cast<__half *>(ws + wl.off_scales_t);
+        repack_codes_kernel<<<dim3((p.N + 127) / 128, p.K / 64), 256, 0, stream>>>(a.packed, codes_t, p.K, p.N);
+        repack_scales_kernel<<<dim3((p.N / 64 + 31) / 32, (p.K + 31) / 32), 256, 0, stream>>>(
+            a.absmax, a.scale_codes, a.scale_of_scales, scales_t, p.K, p.N / 64);
+        count_launch();
+        count_launch();
+        p.codes = codes_t;
+        p.scales_t = scales_t;
+        if (p.rank) {
+            uint16_t *a_t = reinterpret_cast<uint16_t *>(ws + wl.off_a_t);
+            __nv_bfloat16 *b_t = reinterpret_cast<__nv_bfloat16 *>(ws + wl.off_b_t);
+            const uint64_t n = (uint64_t)a.lora_rank * (p.K + p.N);
+            if (x_f32)
+                repack_adapter_kernel<float><<<(uint32_t)((n + 255) / 256), 256, 0, stream>>>(
+                    static_cast<const float *>(a.lora_a), static_cast<const float *>(a.lora_b), a_t, b_t, p.K, p.N,
+                    a.lora_rank);
+            else
+                repack_adapter_kernel<__nv_bfloat16><<<(uint32_t)((n + 255) / 256), 256, 0, stream>>>(
+                    static_cast<const __nv_bfloat16 *>(a.lora_a), static_cast<const __nv_bfloat16 *>(a.lora_b), a_t,
+                    b_t, p.K, p.N, a.lora_rank);
+            count_launch();
+            lora_a = a_t;
+            lora_b = b_t;
+        }
+        NF4_CUDA_TRY(cudaGetLastError());
+    }
+    if (x_f32) {
+        x_f32_to_f16_kernel<<<p.M, 256, 0, stream>>>(static_cast<const float *>(a.x), p.K, xh, row_scale, a.absmax,
+                                                   a.scale_codes, a.scale_of_scales);
+        count_launch();
+        prefill_prepass_kernel<true><<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
+            reinterpret_cast<const __nv_bfloat16 *>(xh), static_cast<const __nv_bfloat16 *>(lora_a), p.M, p.K, p.rank,
+            p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales, p.sk_flags,
+            sh.grid);
+    } else {
+        prefill_prepass_kernel<false><<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
+            static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(lora_a), p.M, p.K, p.rank,
+            p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales, p.sk_flags,
+            sh.grid);
+    }
     count_launch();
     NF4_CUDA_TRY(cudaGetLastError());
 
@@ -1054,10 +1332,10 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
         NF4_TRY(make_map(&map_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t, p.M, ld_t, (uint64_t)ld_t * 2, BN,
                          BK, CU_TENSOR_MAP_SWIZZLE_128B));
         // LoRA B [N][rank]: columns beyond the rank and rows beyond N read as zero
-        NF4_TRY(make_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b, p.N, p.rank,
+        NF4_TRY(make_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lora_b, p.N, p.rank,
                          (uint64_t)p.rank * 2, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B));
     }
-    if (a.y_f32)
+    if (y_f32)
         NF4_TRY(make_map(&map_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.y, p.M, p.N, ldy * 4, kEpiBytes / (BM * 4), BM,
                          CU_TENSOR_MAP_SWIZZLE_NONE));
     else
@@ -1067,15 +1345,13 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     const uint32_t grid = sh.grid;
     const size_t smem = 1024 + kXStages * kXTileBytes + kLoraStages * kLoraTileBytes + kEpiBytes +
                         kNumBars * 8 + 16 + BN * 4 + 64;
-    if (a.y_f32) {
-        NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_kernel<true>), (int)smem));
-        NF4_TRY(launch_maybe_overlapped(prefill_kernel<true>, dim3(grid), dim3(kThreads), smem, stream,
-                                        true, map_x, map_t, map_b, map_y, p));
-    } else {
-        NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_kernel<false>), (int)smem));
-        NF4_TRY(launch_maybe_overlapped(prefill_kernel<false>, dim3(grid), dim3(kThreads), smem, stream,
-                                        true, map_x, map_t, map_b, map_y, p));
-    }
+    auto go = [&](auto kernel) -> int32_t {
+        NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kernel), (int)smem));
+        return launch_maybe_overlapped(kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_x, map_t, map_b,
+                                       map_y, p);
+    };
+    if (repacked) NF4_TRY(y_f32 ? go(prefill_kernel<true, true>) : go(prefill_kernel<false, true>));
+    else NF4_TRY(y_f32 ? go(prefill_kernel<true, false>) : go(prefill_kernel<false, false>));
     count_launch();
     return check_cuda(cudaGetLastError(), "prefill_kernel launch");
 }
