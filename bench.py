@@ -697,7 +697,7 @@ def reference_orientation_section(torch, lib, _lib, dev, iters: int = 20):
     stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
     out = {"workload": "x f32 [M, 4096], W NF4 [4096, 11008] (blocks along d_out), LoRA rank 16 in f32; "
-                       "up to 64 rows the CUDA-core strip kernel (f32 dequantisation and sums), more rows the "
+                       "up to 16 rows the CUDA-core strip kernel (f32 dequantisation and sums), more rows the "
                        "tensor-core GEMM over the repacked weight; 160 MB flush write before every forward, "
                        "outside the timed events"}
     for m in MS:
@@ -718,7 +718,7 @@ def reference_orientation_section(torch, lib, _lib, dev, iters: int = 20):
         gbs = by / (ms * 1e-3) / 1e9
         out[f"M={m}"] = {"us": ms * 1e3, "GB/s": gbs, "algorithmic_bytes": by, "frac": gbs / hbm_peak,
                          "peak_kind": f"of {peak_kind}"}
-    # more than 64 rows: nibbles and scales repacked into the workspace, then the tensor-core GEMM
+    # more than 16 rows: nibbles and scales repacked into the workspace, then the tensor-core GEMM
     pm = 2048
     x = torch.randn(pm, K, device=dev, generator=g)
     y = torch.zeros(pm, N, device=dev)

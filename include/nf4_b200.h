@@ -185,7 +185,15 @@ NF4_API int32_t nf4_quantize_dequantize_host(const float *values, uint64_t len,
  *     y = x * dequant(W)^T (+ bias) (+ lora_scale * (x * A^T) * B^T).
  * Replaces Nf4Linear::forward, src/qwennet.rs:238-241, and QloraLinear::forward,
  * src/qwennet.rs:325-344 (adapter: LoraAdapter::forward, src/quantize.rs:620-624).
- * All pointers are device pointers. */
+ * All pointers are device pointers.
+ *
+ * Arithmetic by shape.  NF4_LAYOUT_OUT_IN with bf16 activations, and NF4_LAYOUT_IN_OUT at more than
+ * 16 rows (bf16 or f32 activations, d_in and d_out multiples of 64, adapter rank a multiple of 8 for
+ * bf16 and of 4 for f32 factors), multiply on the tensor cores: f16 operands (activations per row
+ * and block scales per weight brought into f16's range by powers of two), f32 sums: relative L2 error
+ * <= 1e-3 against the reference's f32 result (measured: 4e-4).  NF4_LAYOUT_IN_OUT at up to 16 rows
+ * (and up to 64 rows of shapes the tensor-core path does not take) and every other shape multiply
+ * exactly dequantized f32 weights with f32 sums as the reference does: <= 1e-5. */
 typedef struct nf4_linear_args {
     uint32_t struct_bytes;      /* sizeof(nf4_linear_args), checked */
     int32_t layout;             /* NF4_LAYOUT_* */
@@ -218,8 +226,10 @@ typedef struct nf4_linear_args {
  * power-of-two scales that the tensor-core kernel reads (plus a 128 x 256 f32 accumulator per SM
  * where it splits tiles between CTAs); for at most 16 rows also the partial sums of the parts of K
  * when d_in exceeds 4096, or, in the reference's weight orientation, of the pieces of K its kernel
- * works in.  One workspace serves one stream: calls that may overlap on the GPU need a workspace
- * each. */
+ * works in; for more than 16 rows in that orientation the weight's nibbles transposed, its scales
+ * as f16 and the adapter factors in the tensor-core kernel's orientation (about d_in * d_out / 2
+ * bytes more; the value returned covers either orientation).  One workspace serves one stream: calls
+ * that may overlap on the GPU need a workspace each. */
 NF4_API uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
                                     uint32_t lora_rank);
 

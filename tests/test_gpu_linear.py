@@ -177,7 +177,7 @@ def test_general_kernel_in_out_layout_f32(oracle):
     (1, 4096, 11008, 16, False, True),     # the decode configuration in the reference's orientation and types
     (4, 4096, 11008, 16, True, False),     # bf16 activations, double-quantized scales
     (16, 1024, 4096, 8, False, True),      # two launches of eight activation rows
-    (40, 512, 320, 4, True, True),         # five launches; strip narrower than 256 columns at the end
+    (40, 512, 320, 3, True, True),         # five launches (rank 3: not for the tensor-core path); strip narrower than 256 columns at the end
     (3, 100, 64, 0, False, True),          # one strip, K shorter than two pieces
     (8, 18944, 3584, 16, False, False),    # the block's down projection
 ])
@@ -214,14 +214,14 @@ def test_reference_orientation_at_decode_sizes(oracle, rows, d_in, d_out, r, dq,
 
 
 @pytest.mark.parametrize("rows,d_in,d_out,r,dq,f32,bias", [
-    (65, 128, 64, 0, False, True, False),     # the smallest shape: one tile, half of its weight rows empty
+    (17, 128, 64, 0, False, True, False),     # the smallest shape: one tile, half of its weight rows empty
     (200, 512, 320, 4, True, True, True),     # d_out = 2.5 tiles; f32 factors enter as rank 8
     (300, 1024, 768, 8, False, False, True),  # bf16 activations and factors
     (257, 4096, 1024, 64, False, True, False),  # rank 64 in f32: two 64-rank chunks per half of T
     (1000, 2048, 2048, 16, True, False, False),
 ])
 def test_reference_orientation_at_prefill_sizes(oracle, rows, d_in, d_out, r, dq, f32, bias):
-    # W [d_in, d_out] at more than 64 activation rows: nibbles and scales are repacked into the
+    # W [d_in, d_out] at more than 16 activation rows: nibbles and scales are repacked into the
     # workspace and the tensor-core GEMM multiplies (f16 operands, f32 sums): rel. L2 <= 1e-3
     rng = np.random.default_rng(800 + rows + d_in + d_out)
     w = (rng.standard_normal((d_in, d_out)) * 0.02).astype(np.float32)

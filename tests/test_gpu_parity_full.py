@@ -85,6 +85,37 @@ def test_config5_prefill_4096_tokens_shards(oracle, k, n):
     _check_slices(oracle, packed, a, b, x, y, k, n, cols, [slice(0, 8), slice(2048, 2056), slice(4088, 4096)])
 
 
+@pytest.mark.parametrize("f32", [True, False])
+def test_config3_in_the_reference_orientation(oracle, f32):
+    # the prefill configuration as the reference itself would hold it: x [2048, 4096], W [4096, 14336]
+    # with the 64-blocks along d_out, A [4096, 64], B [64, 14336], f32 (its own types) or bf16.  The
+    # oracle dequantizes the whole weight; scattered column slices are multiplied in f64.
+    from unifur_b200.quantize import PackedNf4Tensor, linear_forward
+
+    m, k, n, r = 2048, 4096, 14336, 64
+    tdt = torch.float32 if f32 else torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(31)
+    w = torch.randn(k * n, device=DEV, generator=g) * 0.02
+    packed = PackedNf4Tensor.quantize(w)
+    del w
+    a = (torch.randn(k, r, device=DEV, generator=g) * 0.01).to(tdt)
+    b = (torch.randn(r, n, device=DEV, generator=g) * 0.01).to(tdt)
+    x = torch.randn(m, k, device=DEV, generator=g).to(tdt)
+    y = linear_forward(x, packed, k, n, _lib.LAYOUT_IN_OUT, lora_a=a, lora_b=b, lora_scale=2.0)
+    torch.cuda.synchronize()
+    wd = oracle.dequantize_packed(packed.codes.cpu().numpy(), k * n, packed.absmax.cpu().numpy()).reshape(k, n)
+    a64, b64 = a.double().cpu().numpy(), b.double().cpu().numpy()
+    tol = 1e-3 if f32 else TOL
+    for rows in (slice(0, 16), slice(1000, 1016), slice(2040, 2048)):
+        xs = x[rows].double().cpu().numpy()
+        t = xs @ a64
+        for c0 in (0, 1792, 5000, 7168 - 64, 9999, n - 128):
+            ref = xs @ wd[:, c0:c0 + 128].astype(np.float64) + 2.0 * t @ b64[:, c0:c0 + 128]
+            got = y[rows, c0:c0 + 128].double().cpu().numpy()
+            err = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+            assert err <= tol, (rows, c0, err)
+
+
 @pytest.mark.parametrize("rows,cols", [(4096, 14336), (14336, 4096)])
 def test_config4_the_two_long_matrices_bit_exact(oracle, rows, cols):
     # the 58.7 M-element members of the sweep, heavy-tailed values: codes and absmax bit-exact

@@ -111,7 +111,7 @@ int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream);
 
 // prefill_gemm.cu: tcgen05 GEMM, NF4_LAYOUT_OUT_IN, bf16 activations.
 bool prefill_supported(const nf4_linear_args &a);
-// NF4_LAYOUT_IN_OUT at more than 64 rows, bf16 or f32 activations: repacked into the workspace, same GEMM
+// NF4_LAYOUT_IN_OUT at more than 16 rows, bf16 or f32 activations: repacked into the workspace, same GEMM
 bool prefill_in_out_supported(const nf4_linear_args &a);
 uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
 int32_t prefill_share_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t cta, uint32_t *ctas,

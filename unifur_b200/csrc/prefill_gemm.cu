@@ -40,7 +40,7 @@
 // produces the LoRA intermediate.
 //
 // The other orientation (W [K][N] with the 64-blocks along N, the reference's own; f32 or bf16
-// activations) comes through the same GEMM at more than 64 rows: three small kernels first write the
+// activations) comes through the same GEMM at more than 16 rows: three small kernels first write the
 // transposed nibbles, the scales as f16 [N / 64][K] and the adapter factors in this kernel's
 // orientation into the workspace (the nibbles exactly; the scales with the rounding the dequantisers
 // apply anyway).  A weight row's scale then changes with every k: a lane loads the pair of scales of
@@ -81,7 +81,7 @@ constexpr int kThreads = 27 * 32;
 constexpr int kFirstExpanderWarp = 7;      // sixteen warps
 constexpr int kFirstEpilogueWarpB = 23;    // the second set of four epilogue warps
 constexpr int kExpanderGroups = 4;         // of four warps (one per TMEM lane quarter) each
-constexpr uint64_t kInOutMinRows = 65;     // the other weight orientation comes here from this many rows on
+constexpr uint64_t kInOutMinRows = 17;     // the other weight orientation comes here from this many rows on
 
 // barrier slots
 constexpr int kBarXFull = 0, kBarXEmpty = kBarXFull + kXStages, kBarAFull = kBarXEmpty + kXStages,
@@ -1221,7 +1221,7 @@ uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, u
     return need;
 }
 
-// The reference's orientation (W [d_in][d_out], blocks along d_out) at more than 64 rows: repacked
+// The reference's orientation (W [d_in][d_out], blocks along d_out) at more than 16 rows: repacked
 // into the workspace, then the same GEMM.  Fewer rows stay with the CUDA-core strip kernel, whose
 // f32 arithmetic is the reference's own.
 bool prefill_in_out_supported(const nf4_linear_args &a) {
