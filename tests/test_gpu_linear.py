@@ -86,8 +86,8 @@ def make_case(oracle, seed, M, K, N, r, dq=False, bias=False, w_std=0.02, ab_std
 def check_out_in(oracle, c, M, K, N, scale, tol=REL_L2_BF16):
     """bf16 activations, W [N, K].  The kernel's own error is measured on its f32 output (bar:
     rel. L2 <= 1e-3); the bf16 output must then be that result rounded once to bf16, up to one
-    bf16 ulp where the f32 sums differ in their last bits (partial sums meet through
-    shared-memory adds whose order is not fixed)."""
+    bf16 ulp where the f32 sums differ in their last bits (the decode kernel's split-K shapes
+    add partial sums in another order than one pass over K would)."""
     ref = oracle.qlora_forward_bnb(c["x"], c["packed"], c["absmax"], N, K, c["la"], c["lb"], scale,
                                    c["bias"], c["sc"], c["sos"] if c["sos"] is not None else 0.0)
     kw = dict(bias=c["bias"], lora_a=c["la"], lora_b=c["lb"], scale=scale, scale_codes=c["sc"],
@@ -249,6 +249,8 @@ def test_reference_orientation_at_prefill_sizes(oracle, rows, d_in, d_out, r, dq
     assert rel_l2(got, ref) <= 1e-3
     for rows_ in (slice(0, 3), slice(3, 4), slice(5, 6), slice(rows - 1, rows)):   # every row on its own scale
         assert rel_l2(got[rows_], ref[rows_]) <= 1e-3, rows_
+    again = run_forward(_lib.LAYOUT_IN_OUT, dt, x, packed, None if dq else absmax, d_in, d_out, y_f32=True, **kw)
+    assert np.array_equal(got, again)   # every sum in a fixed order: the same bits from run to run
     if not f32:
         y16 = run_forward(_lib.LAYOUT_IN_OUT, dt, x, packed, None if dq else absmax, d_in, d_out, **kw)
         assert rel_l2(y16, ref) <= REL_L2_BF16 + 2.0 ** -9
@@ -449,7 +451,8 @@ def test_prefill_linearity_at_full_config3_size(oracle):
 def test_qlora_backward_matches_f64_reference(oracle, layout_name, M, K, N, r):
     # Gradients with the NF4 base frozen (what the reference's autodiff sees through the detached
     # weight, src/qwennet.rs:226-241): grad_x runs through the NF4 kernels on the same packed
-    # bytes in the other orientation, grad_a / grad_b are dense.  f32 activations: 1e-5.
+    # bytes in the other orientation, grad_a / grad_b are dense.  f32 activations: 1e-5 (grad_x at
+    # more than 16 rows: 1e-3).
     from unifur_b200.quantize import PackedNf4Tensor
     from unifur_b200.qwennet import Nf4Linear, QloraLinear
 
@@ -476,7 +479,8 @@ def test_qlora_backward_matches_f64_reference(oracle, layout_name, M, K, N, r):
     base = Nf4Linear(PackedNf4Tensor.quantize(torch.from_numpy(w.reshape(-1)).to(DEV)), K, N, None, lay)
     q = QloraLinear(base, torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV), s)
     gx, ga, gb = q.backward(torch.from_numpy(x).to(DEV), torch.from_numpy(gy).to(DEV))
-    assert rel_l2(gx.cpu().numpy(), gx_ref) <= REL_L2_F32
+    # more than 16 rows: grad_x of the out_in layout is a forward in the other orientation on the tensor cores
+    assert rel_l2(gx.cpu().numpy(), gx_ref) <= (1e-3 if (out_in and M > 16) else REL_L2_F32)
     assert rel_l2(ga.cpu().numpy(), ga_ref) <= REL_L2_F32
     assert rel_l2(gb.cpu().numpy(), gb_ref) <= REL_L2_F32
     # and the forward it differentiates: finite differences along one direction

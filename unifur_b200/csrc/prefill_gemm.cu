@@ -780,18 +780,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 // of the next piece are in flight while a piece is multiplied.
 constexpr int kTThreads = 512;
 constexpr int kTWarps = kTThreads / 32;
+constexpr int kTPartStride = 72;  // floats per row of a warp's partial sums (64 + padding against bank conflicts)
+constexpr int kTPartBytes = kTWarps * 16 * kTPartStride * 4;
 
 struct PrepassPiece {
     uint4 xa, xb;   // rows g and g + 8 of the slab
     uint4 bv[8];    // rows 8u + g of this 64-rank chunk of A
 };
 
-__device__ __forceinline__ uint32_t bf16x2_absmax_bits(uint32_t w, uint32_t mx) {
-    // |bf16| as the top half of an f32 pattern; NaNs are left out of the maximum
-    const uint32_t lo = (w << 16) & 0x7fff0000u, hi = w & 0x7fff0000u;
-    if (lo <= 0x7f800000u) mx = max(mx, lo);
-    if (hi <= 0x7f800000u) mx = max(mx, hi);
-    return mx;
+// Running maxima of |bf16|, a pair at a time; a NaN leaves the maximum as it is (max.bf16x2
+// returns the other operand).
+__device__ __forceinline__ uint32_t bf16x2_absmax(uint32_t w, uint32_t mx) {
+    uint32_t d;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(w & 0x7fff7fffu), "r"(mx));
+    return d;
+}
+// The larger half of such a pair as an f32 pattern; 0 if only NaNs were seen.
+__device__ __forceinline__ uint32_t bf16x2_larger_bits(uint32_t mx) {
+    const uint32_t lo = mx << 16, hi = mx & 0xffff0000u;
+    const uint32_t a = lo <= 0x7f800000u ? lo : 0u, b = hi <= 0x7f800000u ? hi : 0u;
+    return max(a, b);
 }
 
 __device__ __forceinline__ uint4 bf16x8_to_f16x8(const uint4 &v, float is) {
@@ -816,7 +824,8 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
                        __nv_bfloat16 *__restrict__ t_out, const float *__restrict__ absmax,
                        const uint8_t *__restrict__ scale_codes, const float *__restrict__ scale_of_scales,
                        uint32_t *__restrict__ sk_flags, uint32_t n_flags) {
-    __shared__ float red[16][64 + 1];
+    // the warps' partial sums of T: [warp][16 rows][64 ranks, padded to 72], summed in warp order
+    extern __shared__ __align__(16) float part[];
     __shared__ uint32_t row_max_bits[16];
     __shared__ float inv_scale[16];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -834,12 +843,11 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
     const size_t off_a = (size_t)(m0 + g) * K, off_b = (size_t)(m0 + g + 8) * K;
 
     if (threadIdx.x < 16) row_max_bits[threadIdx.x] = 0;
+    __syncthreads();
     uint32_t mx_a = 0, mx_b = 0;
 
     const uint32_t passes = chunks ? chunks : 1u;
     for (uint32_t chunk = 0; chunk < passes; ++chunk) {
-        for (uint32_t i = threadIdx.x; i < 16 * 65; i += kTThreads) (&red[0][0])[i] = 0.0f;
-        __syncthreads();
         float acc[8][4];
         #pragma unroll
         for (int u = 0; u < 8; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.0f;
@@ -863,13 +871,13 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             const uint32_t k = k_of(it);
             if (!XH_READY && chunk == 0 && it < n_it && k + 8 <= K) {
                 if (row_a) {
-                    mx_a = bf16x2_absmax_bits(pc.xa.x, bf16x2_absmax_bits(pc.xa.y, mx_a));
-                    mx_a = bf16x2_absmax_bits(pc.xa.z, bf16x2_absmax_bits(pc.xa.w, mx_a));
+                    mx_a = bf16x2_absmax(pc.xa.x, bf16x2_absmax(pc.xa.y, mx_a));
+                    mx_a = bf16x2_absmax(pc.xa.z, bf16x2_absmax(pc.xa.w, mx_a));
                     *reinterpret_cast<uint4 *>(xh + off_a + k) = bf16x8_to_f16x8(pc.xa, 1.0f);
                 }
                 if (row_b) {
-                    mx_b = bf16x2_absmax_bits(pc.xb.x, bf16x2_absmax_bits(pc.xb.y, mx_b));
-                    mx_b = bf16x2_absmax_bits(pc.xb.z, bf16x2_absmax_bits(pc.xb.w, mx_b));
+                    mx_b = bf16x2_absmax(pc.xb.x, bf16x2_absmax(pc.xb.y, mx_b));
+                    mx_b = bf16x2_absmax(pc.xb.z, bf16x2_absmax(pc.xb.w, mx_b));
                     *reinterpret_cast<uint4 *>(xh + off_b + k) = bf16x8_to_f16x8(pc.xb, 1.0f);
                 }
             }
@@ -896,16 +904,16 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
         }
 
         if (!XH_READY && chunk == 0) {
-            atomicMax(&row_max_bits[g], mx_a);
-            atomicMax(&row_max_bits[g + 8], mx_b);
+            atomicMax(&row_max_bits[g], bf16x2_larger_bits(mx_a));
+            atomicMax(&row_max_bits[g + 8], bf16x2_larger_bits(mx_b));
         }
         if (rank) {
             #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                atomicAdd(&red[g][8 * u + 2 * t], acc[u][0]);
-                atomicAdd(&red[g][8 * u + 2 * t + 1], acc[u][1]);
-                atomicAdd(&red[g + 8][8 * u + 2 * t], acc[u][2]);
-                atomicAdd(&red[g + 8][8 * u + 2 * t + 1], acc[u][3]);
+                float *mine = part + warp * (16 * kTPartStride);
+                *reinterpret_cast<float2 *>(mine + g * kTPartStride + 8 * u + 2 * t) = make_float2(acc[u][0], acc[u][1]);
+                *reinterpret_cast<float2 *>(mine + (g + 8) * kTPartStride + 8 * u + 2 * t) =
+                    make_float2(acc[u][2], acc[u][3]);
             }
         }
         __syncthreads();
@@ -941,7 +949,10 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             for (uint32_t i = threadIdx.x; i < 16 * 64; i += kTThreads) {
                 const uint32_t r = i >> 6, c = i & 63u;
                 if (m0 + r < M) {
-                    const float v = red[r][c] * scale * inv_scale[r] * w_down;
+                    float sum = 0.0f;
+                    #pragma unroll
+                    for (int w = 0; w < kTWarps; ++w) sum += part[w * (16 * kTPartStride) + r * kTPartStride + c];
+                    const float v = sum * scale * inv_scale[r] * w_down;
                     const __nv_bfloat16 hi = __float2bfloat16_rn(v);
                     const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
                     t_out[(size_t)(m0 + r) * ld_t + chunk * 64 + c] = hi;
@@ -1306,16 +1317,18 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
         }
         NF4_CUDA_TRY(cudaGetLastError());
     }
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<true>), kTPartBytes));
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<false>), kTPartBytes));
     if (x_f32) {
         x_f32_to_f16_kernel<<<p.M, 256, 0, stream>>>(static_cast<const float *>(a.x), p.K, xh, row_scale, a.absmax,
                                                    a.scale_codes, a.scale_of_scales);
         count_launch();
-        prefill_prepass_kernel<true><<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
+        prefill_prepass_kernel<true><<<(p.M + 15) / 16, kTThreads, kTPartBytes, stream>>>(
             reinterpret_cast<const __nv_bfloat16 *>(xh), static_cast<const __nv_bfloat16 *>(lora_a), p.M, p.K, p.rank,
             p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales, p.sk_flags,
             sh.grid);
     } else {
-        prefill_prepass_kernel<false><<<(p.M + 15) / 16, kTThreads, 0, stream>>>(
+        prefill_prepass_kernel<false><<<(p.M + 15) / 16, kTThreads, kTPartBytes, stream>>>(
             static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(lora_a), p.M, p.K, p.rank,
             p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales, p.sk_flags,
             sh.grid);
