@@ -969,58 +969,82 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
 // form the GEMM's dequantisers read: codes_t[n][k / 2] (the same nibbles, transposed, so exact) and
 // scales_t[n / 64][k] (f16 of scale / 2^e, the rounding the GEMM applies to a scale anyway).
 
-// One CTA: 64 rows (k) x 128 columns (n) of nibbles through shared memory.
-__global__ void __launch_bounds__(256)
-repack_codes_kernel(const uint8_t *__restrict__ codes, uint8_t *__restrict__ codes_t, uint32_t K, uint32_t N) {
-    __shared__ __align__(16) uint8_t tile[64][80];  // 64 packed bytes of a row, padded
-    const uint32_t n0 = blockIdx.x * 128, k0 = blockIdx.y * 64, t = threadIdx.x;
-    {
-        const uint32_t r = t >> 2, seg = t & 3u;  // 16 bytes = 32 columns per thread
+struct RepackParams {
+    const uint8_t *codes;
+    const float *absmax;
+    const uint8_t *scale_codes;
+    const float *scale_of_scales;
+    const void *a, *b;          // adapter factors A [K][r], B [r][N], or null
+    uint8_t *codes_t;
+    __half *scales_t;
+    uint16_t *a_t;
+    __nv_bfloat16 *b_t;
+    uint32_t K, N, r;
+    uint32_t code_cols, code_rows, code_blocks;   // CTAs of the nibbles: columns of 128 n x groups of kRepackTiles k-tiles
+    uint32_t scale_cols, scale_blocks;            // CTAs of the scales: 32 x 32 tiles
+};
+constexpr uint32_t kRepackTiles = 4;  // 64-row tiles of nibbles one CTA walks, the next one's loads in flight
+
+// Nibbles: 64 rows (k) x 128 columns (n) per tile through shared memory; a thread turns 16 rows of
+// one byte column (two n) into the 8 bytes each of those two weight rows gets.
+__device__ __forceinline__ void repack_codes_block(const RepackParams &p, uint32_t block, uint8_t (*tile)[64][80]) {
+    const uint32_t n0 = (block % p.code_cols) * 128, kt0 = (block / p.code_cols) * kRepackTiles, t = threadIdx.x;
+    const uint32_t k_tiles = p.K / 64;
+    const uint32_t n_it = min(kRepackTiles, k_tiles - kt0);
+    const uint32_t r = t >> 2, seg = t & 3u;  // loads: 16 bytes = 32 columns of row r per thread
+    const bool in = n0 + seg * 32 < p.N;
+    auto load = [&](uint32_t it) {
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (n0 + seg * 32 < N)
-            v = __ldg(reinterpret_cast<const uint4 *>(codes + (size_t)(k0 + r) * (N / 2) + n0 / 2 + seg * 16));
-        *reinterpret_cast<uint4 *>(&tile[r][seg * 16]) = v;
+        if (in)
+            v = __ldg(reinterpret_cast<const uint4 *>(p.codes + (size_t)((kt0 + it) * 64 + r) * (p.N / 2) + n0 / 2 +
+                                                      seg * 16));
+        return v;
+    };
+    const uint32_t bc = t & 63u, kq = t >> 6;  // byte column and quarter of the rows
+    uint4 v = load(0);
+    for (uint32_t it = 0; it < n_it; ++it) {
+        uint8_t(*cur)[80] = tile[it & 1u];
+        *reinterpret_cast<uint4 *>(&cur[r][seg * 16]) = v;
+        __syncthreads();
+        if (it + 1 < n_it) v = load(it + 1);
+        if (n0 + 2 * bc < p.N) {
+            uint32_t e0 = 0, e1 = 0, o0 = 0, o1 = 0;  // even column: k 0..7, 8..15 of the quarter; odd column
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t b0 = cur[kq * 16 + j][bc], b1 = cur[kq * 16 + 8 + j][bc];
+                e0 |= (b0 & 15u) << (4 * j);
+                o0 |= (b0 >> 4) << (4 * j);
+                e1 |= (b1 & 15u) << (4 * j);
+                o1 |= (b1 >> 4) << (4 * j);
+            }
+            const size_t at = (size_t)(n0 + 2 * bc) * (p.K / 2) + ((kt0 + it) * 64 + kq * 16) / 2;
+            *reinterpret_cast<uint2 *>(p.codes_t + at) = make_uint2(e0, e1);
+            *reinterpret_cast<uint2 *>(p.codes_t + at + p.K / 2) = make_uint2(o0, o1);
+        }
     }
-    __syncthreads();
-    const uint32_t n = t & 127u, kh = t >> 7;  // a column and half of the rows: 32 nibbles = 16 bytes out
-    if (n0 + n >= N) return;
-    const uint32_t byte = n >> 1, sh = (n & 1u) * 4;
-    uint32_t w[4];
-    #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t acc = 0;
-        #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            acc |= ((uint32_t)(tile[kh * 32 + i * 8 + j][byte] >> sh) & 15u) << (4 * j);
-        w[i] = acc;
-    }
-    *reinterpret_cast<uint4 *>(codes_t + (size_t)(n0 + n) * (K / 2) + (k0 + kh * 32) / 2) =
-        make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // scales_t[b][k] = f16(scale(k, b) / 2^e), scale(k, b) the scale of block k * (N / 64) + b.
-__global__ void __launch_bounds__(256)
-repack_scales_kernel(const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
-                     const float *__restrict__ scale_of_scales, __half *__restrict__ scales_t, uint32_t K,
-                     uint32_t blocks_per_row) {
-    __shared__ float tile[32][33];
-    const int w_exp = weight_exponent(absmax, scale_codes, scale_of_scales);
+__device__ __forceinline__ void repack_scales_block(const RepackParams &p, uint32_t block, float (*tile)[33]) {
+    const uint32_t blocks_per_row = p.N / 64;
+    const int w_exp = weight_exponent(p.absmax, p.scale_codes, p.scale_of_scales);
     const float w_down = ldexpf(1.0f, -w_exp);
-    const float sos = scale_codes ? __ldg(scale_of_scales) : 0.0f;
-    const uint32_t b0 = blockIdx.x * 32, k0 = blockIdx.y * 32, tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+    const float sos = p.scale_codes ? __ldg(p.scale_of_scales) : 0.0f;
+    const uint32_t b0 = (block % p.scale_cols) * 32, k0 = (block / p.scale_cols) * 32;
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
     for (uint32_t r = ty; r < 32; r += 8) {
         const uint32_t k = k0 + r, b = b0 + tx;
         float v = 0.0f;
-        if (k < K && b < blocks_per_row) {
+        if (k < p.K && b < blocks_per_row) {
             const size_t blk = (size_t)k * blocks_per_row + b;
-            v = (absmax ? __ldg(absmax + blk) : dq_scale(__ldg(scale_codes + blk), sos)) * w_down;
+            v = (p.absmax ? __ldg(p.absmax + blk) : dq_scale(__ldg(p.scale_codes + blk), sos)) * w_down;
         }
         tile[r][tx] = v;
     }
     __syncthreads();
     for (uint32_t r = ty; r < 32; r += 8) {
         const uint32_t b = b0 + r, k = k0 + tx;
-        if (k < K && b < blocks_per_row) scales_t[(size_t)b * K + k] = __float2half_rn(tile[tx][r]);
+        if (k < p.K && b < blocks_per_row) p.scales_t[(size_t)b * p.K + k] = __float2half_rn(tile[tx][r]);
     }
 }
 
@@ -1031,34 +1055,46 @@ repack_scales_kernel(const float *__restrict__ absmax, const uint8_t *__restrict
 //         bf16 of what that rounding left: as an adapter of rank 2 r whose intermediate holds every
 //         column twice, B enters the product with sixteen bits of mantissa.
 template <class T>
-__global__ void __launch_bounds__(256)
-repack_adapter_kernel(const T *__restrict__ a, const T *__restrict__ b, uint16_t *__restrict__ a_t,
-                      __nv_bfloat16 *__restrict__ b_t, uint32_t K, uint32_t N, uint32_t r) {
+__device__ __forceinline__ void repack_adapter_block(const RepackParams &p, uint32_t block) {
     constexpr bool kF32 = sizeof(T) == 4;
-    const uint32_t rank_out = kF32 ? 2 * r : r;
-    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint64_t na = (uint64_t)r * K, nb = (uint64_t)N * r;
+    const T *a = static_cast<const T *>(p.a), *b = static_cast<const T *>(p.b);
+    const uint32_t r = p.r, rank_out = kF32 ? 2 * r : r;
+    const uint64_t i = (uint64_t)block * blockDim.x + threadIdx.x;
+    const uint64_t na = (uint64_t)r * p.K, nb = (uint64_t)p.N * r;
     if (i < na) {
-        const uint32_t j = (uint32_t)(i / K), k = (uint32_t)(i % K);
+        const uint32_t j = (uint32_t)(i / p.K), k = (uint32_t)(i % p.K);
         if constexpr (kF32) {
             const __half h = __float2half_rn(a[(size_t)k * r + j]);
-            a_t[i] = __half_as_ushort(h);
-            a_t[na + i] = __half_as_ushort(h);
+            p.a_t[i] = __half_as_ushort(h);
+            p.a_t[na + i] = __half_as_ushort(h);
         } else {
-            a_t[i] = reinterpret_cast<const uint16_t *>(a)[(size_t)k * r + j];
+            p.a_t[i] = reinterpret_cast<const uint16_t *>(a)[(size_t)k * r + j];
         }
     } else if (i < na + nb) {
         const uint64_t e = i - na;
         const uint32_t n = (uint32_t)(e / r), j = (uint32_t)(e % r);
         if constexpr (kF32) {
-            const float v = b[(size_t)j * N + n];
+            const float v = b[(size_t)j * p.N + n];
             const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-            b_t[(size_t)n * rank_out + j] = hi;
-            b_t[(size_t)n * rank_out + r + j] = __float2bfloat16_rn(v - __bfloat162float(hi));
+            p.b_t[(size_t)n * rank_out + j] = hi;
+            p.b_t[(size_t)n * rank_out + r + j] = __float2bfloat16_rn(v - __bfloat162float(hi));
         } else {
-            b_t[(size_t)n * rank_out + j] = b[(size_t)j * N + n];
+            p.b_t[(size_t)n * rank_out + j] = b[(size_t)j * p.N + n];
         }
     }
+}
+
+// One launch for the three: the first code_blocks CTAs take the nibbles, the next scale_blocks the
+// scales, the rest the adapter.
+template <class T>
+__global__ void __launch_bounds__(256) repack_kernel(const RepackParams p) {
+    __shared__ __align__(16) uint8_t smem[2 * 64 * 80];
+    if (blockIdx.x < p.code_blocks)
+        repack_codes_block(p, blockIdx.x, reinterpret_cast<uint8_t(*)[64][80]>(smem));
+    else if (blockIdx.x < p.code_blocks + p.scale_blocks)
+        repack_scales_block(p, blockIdx.x - p.code_blocks, reinterpret_cast<float(*)[33]>(smem));
+    else
+        repack_adapter_block<T>(p, blockIdx.x - p.code_blocks - p.scale_blocks);
 }
 
 // f32 activations: xh[m][k] = f16(x[m][k] / sc), sc the power of two that brings the row's largest
@@ -1290,31 +1326,37 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.partial = reinterpret_cast<float *>(ws + wl.off_partial);
     const void *lora_a = a.lora_a, *lora_b = a.lora_b;
     if (repacked) {
-        uint8_t *codes_t = ws + wl.off_codes_t;
-        __half *scales_t = reinterpret_cast<__half *>(ws + wl.off_scales_t);
-        repack_codes_kernel<<<dim3((p.N + 127) / 128, p.K / 64), 256, 0, stream>>>(a.packed, codes_t, p.K, p.N);
-        repack_scales_kernel<<<dim3((p.N / 64 + 31) / 32, (p.K + 31) / 32), 256, 0, stream>>>(
-            a.absmax, a.scale_codes, a.scale_of_scales, scales_t, p.K, p.N / 64);
-        count_launch();
-        count_launch();
-        p.codes = codes_t;
-        p.scales_t = scales_t;
+        RepackParams rp{};
+        rp.codes = a.packed;
+        rp.absmax = a.absmax;
+        rp.scale_codes = a.scale_codes;
+        rp.scale_of_scales = a.scale_of_scales;
+        rp.codes_t = ws + wl.off_codes_t;
+        rp.scales_t = reinterpret_cast<__half *>(ws + wl.off_scales_t);
+        rp.K = p.K;
+        rp.N = p.N;
+        rp.code_cols = (p.N + 127) / 128;
+        rp.code_rows = (p.K / 64 + kRepackTiles - 1) / kRepackTiles;
+        rp.code_blocks = rp.code_cols * rp.code_rows;
+        rp.scale_cols = (p.N / 64 + 31) / 32;
+        rp.scale_blocks = rp.scale_cols * ((p.K + 31) / 32);
+        uint32_t adapter_blocks = 0;
         if (p.rank) {
-            uint16_t *a_t = reinterpret_cast<uint16_t *>(ws + wl.off_a_t);
-            __nv_bfloat16 *b_t = reinterpret_cast<__nv_bfloat16 *>(ws + wl.off_b_t);
-            const uint64_t n = (uint64_t)a.lora_rank * (p.K + p.N);
-            if (x_f32)
-                repack_adapter_kernel<float><<<(uint32_t)((n + 255) / 256), 256, 0, stream>>>(
-                    static_cast<const float *>(a.lora_a), static_cast<const float *>(a.lora_b), a_t, b_t, p.K, p.N,
-                    a.lora_rank);
-            else
-                repack_adapter_kernel<__nv_bfloat16><<<(uint32_t)((n + 255) / 256), 256, 0, stream>>>(
-                    static_cast<const __nv_bfloat16 *>(a.lora_a), static_cast<const __nv_bfloat16 *>(a.lora_b), a_t,
-                    b_t, p.K, p.N, a.lora_rank);
-            count_launch();
-            lora_a = a_t;
-            lora_b = b_t;
+            rp.a = a.lora_a;
+            rp.b = a.lora_b;
+            rp.r = a.lora_rank;
+            rp.a_t = reinterpret_cast<uint16_t *>(ws + wl.off_a_t);
+            rp.b_t = reinterpret_cast<__nv_bfloat16 *>(ws + wl.off_b_t);
+            adapter_blocks = (uint32_t)(((uint64_t)a.lora_rank * (p.K + p.N) + 255) / 256);
+            lora_a = rp.a_t;
+            lora_b = rp.b_t;
         }
+        const uint32_t blocks = rp.code_blocks + rp.scale_blocks + adapter_blocks;
+        if (x_f32) repack_kernel<float><<<blocks, 256, 0, stream>>>(rp);
+        else repack_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(rp);
+        count_launch();
+        p.codes = rp.codes_t;
+        p.scales_t = rp.scales_t;
         NF4_CUDA_TRY(cudaGetLastError());
     }
     NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<true>), kTPartBytes));
