@@ -678,6 +678,7 @@ def aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind):
     del vals, packed, absmax
     out["prefill"] = prefill_section(torch, lib, _lib, dev)
     out["reference_orientation"] = reference_orientation_section(torch, lib, _lib, dev)
+    out["backward"] = backward_section(torch, lib, _lib, dev)
     return out
 
 
@@ -738,6 +739,51 @@ def reference_orientation_section(torch, lib, _lib, dev, iters: int = 20):
                       "frac": flops / (ms * 1e-3) / 1e12 / _tf, "peak_kind": f"of {peak_kind} (burst)",
                       "path": "repacking kernels + f16 conversion + tcgen05 GEMM, f32 in and out"}
     return out
+
+
+def backward_section(torch, lib, _lib, dev, iters: int = 10):
+    """Backward of the QLoRA linear of configuration 3 (base weight frozen): grad_x = grad_y W + s (grad_y B) A
+    over the same packed bytes read in the other orientation (tensor cores), grad_A and grad_B as
+    small dense products (nf4_qlora_backward_dev; used by src/qwentrain.rs:421-470 through
+    src/qwennet.rs:226-241)."""
+    from unifur_b200.quantize import PackedNf4Tensor
+
+    pm, pk, pn, pr = 2048, 4096, 14336, 64
+    _hbm, tf_peak, peak_kind = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(15)
+    w = torch.randn(pn * pk, device=dev, generator=g) * 0.02
+    wq = PackedNf4Tensor.quantize(w)
+    del w
+    la = (torch.randn(pr, pk, device=dev, generator=g) * 0.01).bfloat16()
+    lb = (torch.randn(pn, pr, device=dev, generator=g) * 0.01).bfloat16()
+    x = torch.randn(pm, pk, device=dev, generator=g).bfloat16()
+    gy = torch.randn(pm, pn, device=dev, generator=g).bfloat16()
+    gx = torch.empty_like(x)
+    ga, gb = torch.empty_like(la), torch.empty_like(lb)
+    ws = torch.zeros(max(int(lib.nf4_qlora_backward_workspace_bytes(pm, pk, pn, pr)), 256), dtype=torch.uint8, device=dev)
+    a = _lib.LinearArgs()
+    a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+    a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_BF16
+    a.rows, a.d_in, a.d_out = pm, pk, pn
+    a.x, a.packed, a.absmax = x.data_ptr(), wq.codes.data_ptr(), wq.absmax.data_ptr()
+    a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb.data_ptr(), pr, SCALE
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    vp = ctypes.c_void_p
+    stream = lambda: vp(torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def run(_i):
+        _lib.check(lib.nf4_qlora_backward_dev(ctypes.byref(a), vp(gy.data_ptr()), vp(gx.data_ptr()), vp(ga.data_ptr()),
+                                              vp(gb.data_ptr()), stream()))
+
+    ms, ms_min = time_flushed(torch, run, flush, iters)
+    # grad_x: 2 M N K and its adapter term; U = grad_y B^T and T = x A; grad_A and grad_B
+    flops = 2.0 * pm * pn * pk + 2.0 * pm * pr * (pk + pn) + 2.0 * pm * pr * (pk + pn) + 2.0 * pm * pr * (pk + pn)
+    return {"workload": "backward of configuration 3's layer: x, grad_y bf16 [2048, 4096] / [2048, 14336], W NF4 "
+                        "[14336, 4096] frozen, rank 64; grad_x, grad_A, grad_B",
+            "ms": ms, "ms_min": ms_min, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "flops": flops,
+            "frac": flops / (ms * 1e-3) / 1e12 / tf_peak, "peak_kind": f"of {peak_kind} (burst)",
+            "cache": "160 MB flush write before every call, outside the timed events"}
 
 
 def prefill_section(torch, lib, _lib, dev, pn: int = 14336, iters: int = 20):

@@ -447,7 +447,9 @@ def test_prefill_linearity_at_full_config3_size(oracle):
 
 
 @pytest.mark.parametrize("layout_name,M,K,N,r", [("out_in", 8, 256, 192, 16), ("out_in", 40, 512, 320, 8),
-                                                 ("in_out", 6, 128, 96, 4)])
+                                                 ("in_out", 6, 128, 96, 4),
+                                                 ("out_in", 300, 448, 576, 24),   # several pieces of rows, ragged tiles of columns
+                                                 ("in_out", 130, 320, 200, 72)])  # more than 64 ranks: two passes over them
 def test_qlora_backward_matches_f64_reference(oracle, layout_name, M, K, N, r):
     # Gradients with the NF4 base frozen (what the reference's autodiff sees through the detached
     # weight, src/qwennet.rs:226-241): grad_x runs through the NF4 kernels on the same packed

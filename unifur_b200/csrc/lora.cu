@@ -95,19 +95,139 @@ lora_delta_kernel(const T *__restrict__ a, const T *__restrict__ b, const uint8_
     out[flat] = v;
 }
 
-// out(p, j) = scale * sum_m X[m][p] * R[m][j]: the adapter gradients (X = x or grad_y in the io type,
-// R = the f32 intermediate of the other factor).  One thread per (p, j), p fastest in memory reads.
-// `p_major`: out is [P][rank] (else [rank][P]).
+// The same T for a factor stored k-major (A(k, j) = a[k * rank + j]: the reference's A [d_in][r], or
+// B [d_out][r] of the other orientation read as the factor of U = grad_y B^T), where the kernel above
+// would read 32 sectors per load.  A CTA takes eight rows of x; x passes through shared memory in
+// pieces of 256 k; warp w multiplies the k of its 32-wide part of the piece, eight k at a time with
+// their factor rows loaded first; lanes own ranks (lane, lane + 32, ...: coalesced rows of the
+// factor); the warps' sums meet in warp order.  KJ: ranks per lane and pass.
+template <class T, int KJ>
+__global__ void __launch_bounds__(256)
+lora_xa_kmajor_kernel(const T *__restrict__ x, const T *__restrict__ a, float *__restrict__ t, uint64_t rows,
+                      uint64_t d_in, uint32_t rank) {
+    constexpr int kRows = 8, kPiece = 256, kStep = 8;
+    __shared__ float xs[kRows][kPiece];
+    __shared__ float red[8][kRows][32 * KJ + 1];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint64_t m0 = (uint64_t)blockIdx.x * kRows;
+    for (uint32_t j0 = 0; j0 < rank; j0 += 32 * KJ) {
+        float acc[kRows][KJ];
+        #pragma unroll
+        for (int m = 0; m < kRows; ++m)
+            #pragma unroll
+            for (int q = 0; q < KJ; ++q) acc[m][q] = 0.0f;
+        for (uint64_t k0 = 0; k0 < d_in; k0 += kPiece) {
+            __syncthreads();
+            #pragma unroll
+            for (int m = 0; m < kRows; ++m) {
+                const uint64_t k = k0 + threadIdx.x;
+                xs[m][threadIdx.x] = (m0 + m < rows && k < d_in) ? to_f32<T>(x[(m0 + m) * d_in + k]) : 0.0f;
+            }
+            __syncthreads();
+            const uint64_t kw = k0 + warp * 32;
+            #pragma unroll 1
+            for (uint32_t kk = 0; kk < 32; kk += kStep) {
+                float av[kStep][KJ];
+                #pragma unroll
+                for (int i = 0; i < kStep; ++i)
+                    #pragma unroll
+                    for (int q = 0; q < KJ; ++q) {
+                        const uint32_t j = j0 + lane + 32 * q;
+                        av[i][q] = (j < rank && kw + kk + i < d_in) ? to_f32<T>(a[(kw + kk + i) * rank + j]) : 0.0f;
+                    }
+                #pragma unroll
+                for (int i = 0; i < kStep; ++i)
+                    #pragma unroll
+                    for (int m = 0; m < kRows; ++m) {
+                        const float xv = xs[m][warp * 32 + kk + i];
+                        #pragma unroll
+                        for (int q = 0; q < KJ; ++q) acc[m][q] = fmaf(xv, av[i][q], acc[m][q]);
+                    }
+            }
+        }
+        __syncthreads();
+        #pragma unroll
+        for (int m = 0; m < kRows; ++m)
+            #pragma unroll
+            for (int q = 0; q < KJ; ++q) red[warp][m][lane + 32 * q] = acc[m][q];
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < kRows * 32 * KJ; i += 256) {
+            const uint32_t m = i / (32 * KJ), jj = i % (32 * KJ);
+            float v = 0.0f;
+            #pragma unroll
+            for (int w = 0; w < 8; ++w) v += red[w][m][jj];
+            if (m0 + m < rows && j0 + jj < rank) t[(m0 + m) * rank + j0 + jj] = v;
+        }
+    }
+}
+
+// The adapter gradients: out(p, j) = scale * sum_m X[m][p] R[m][j] (X = x or grad_y in the io type,
+// R = the f32 intermediate of the other factor).  A CTA takes 32 columns p and up to 64 ranks; X and R
+// pass through shared memory in pieces of 128 rows m; the eight warps split the rows of a piece; a
+// thread owns one p and all the ranks (64 accumulators), reads X[m][p] and R[m][.] (every lane the
+// same address) from shared memory.  The warps' sums meet in warp order.  `p_major`: out is
+// [P][rank] (else [rank][P]).
+constexpr int kXtrP = 32, kXtrJ = 64, kXtrM = 128;
+template <class T>
+constexpr size_t xtr_smem_bytes() { return (size_t)kXtrM * kXtrJ * 4 + (size_t)kXtrM * kXtrP * sizeof(T); }
+
 template <class T>
 __global__ void __launch_bounds__(256)
-lora_xtr_kernel(const T *__restrict__ x, const float *__restrict__ r, T *__restrict__ out, uint64_t rows,
-                uint64_t P, uint32_t rank, float scale, int p_major) {
-    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= P * rank) return;
-    const uint64_t j = i / P, pp = i % P;
-    float acc = 0.0f;
-    for (uint64_t m = 0; m < rows; ++m) acc = fmaf(to_f32<T>(x[m * P + pp]), r[m * rank + j], acc);
-    out[p_major ? pp * rank + j : j * P + pp] = from_f32<T>(__fmul_rn(acc, scale));
+lora_xtr_tile_kernel(const T *__restrict__ x, const float *__restrict__ r, T *__restrict__ out, uint64_t rows,
+                     uint64_t P, uint32_t rank, float scale, int p_major) {
+    constexpr int kP = kXtrP, kJ = kXtrJ, kM = kXtrM;
+    extern __shared__ __align__(16) unsigned char xtr_smem[];
+    float (*rs)[kJ] = reinterpret_cast<float(*)[kJ]>(xtr_smem);                     // 32 KB; afterwards the sums
+    T (*xs)[kP] = reinterpret_cast<T(*)[kP]>(xtr_smem + (size_t)kM * kJ * 4);      // the piece of X
+    const uint32_t pl = threadIdx.x & 31u, grp = threadIdx.x >> 5;
+    const uint64_t p0 = (uint64_t)blockIdx.x * kP;
+    for (uint32_t j0 = 0; j0 < rank; j0 += kJ) {
+        float acc[kJ];
+        #pragma unroll
+        for (int j = 0; j < kJ; ++j) acc[j] = 0.0f;
+        for (uint64_t m0 = 0; m0 < rows; m0 += kM) {
+            __syncthreads();
+            for (uint32_t i = threadIdx.x; i < kM * kJ; i += 256) {
+                const uint32_t m = i / kJ, j = i % kJ;
+                rs[m][j] = (m0 + m < rows && j0 + j < rank) ? r[(m0 + m) * rank + j0 + j] : 0.0f;
+            }
+            for (uint32_t i = threadIdx.x; i < kM * kP; i += 256) {
+                const uint32_t m = i / kP, q = i % kP;
+                xs[m][q] = (m0 + m < rows && p0 + q < P) ? x[(m0 + m) * P + p0 + q] : from_f32<T>(0.0f);
+            }
+            __syncthreads();
+            #pragma unroll 2
+            for (uint32_t mm = 0; mm < kM / 8; ++mm) {
+                const uint32_t m = grp * (kM / 8) + mm;
+                const float xv = to_f32<T>(xs[m][pl]);
+                #pragma unroll
+                for (int j4 = 0; j4 < kJ / 4; ++j4) {
+                    const float4 rv = *reinterpret_cast<const float4 *>(&rs[m][4 * j4]);
+                    acc[4 * j4 + 0] = fmaf(xv, rv.x, acc[4 * j4 + 0]);
+                    acc[4 * j4 + 1] = fmaf(xv, rv.y, acc[4 * j4 + 1]);
+                    acc[4 * j4 + 2] = fmaf(xv, rv.z, acc[4 * j4 + 2]);
+                    acc[4 * j4 + 3] = fmaf(xv, rv.w, acc[4 * j4 + 3]);
+                }
+            }
+        }
+        // the eight warps add up in turn through shared memory
+        float (*sum)[kJ + 1] = reinterpret_cast<float(*)[kJ + 1]>(xtr_smem);
+        for (uint32_t turn = 0; turn < 8; ++turn) {
+            __syncthreads();
+            if (grp == turn) {
+                #pragma unroll
+                for (int j = 0; j < kJ; ++j) sum[pl][j] = turn ? sum[pl][j] + acc[j] : acc[j];
+            }
+        }
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < kP * kJ; i += 256) {
+            // p fastest for [rank][P] outputs, j fastest for [P][rank]
+            const uint32_t q = p_major ? i / kJ : i % kP, j = p_major ? i % kJ : i / kP;
+            const uint64_t pp = p0 + q;
+            if (pp < P && j0 + j < rank)
+                out[p_major ? pp * rank + j0 + j : (uint64_t)(j0 + j) * P + pp] = from_f32<T>(__fmul_rn(sum[q][j], scale));
+        }
+    }
 }
 
 // y[r][rank * width + c] = gathered[rank][r][c]: the ranks' slabs side by side.  16-byte pieces.
@@ -157,12 +277,22 @@ __global__ void __launch_bounds__(256) push_columns_kernel(const PushParams p) {
     }
 }
 
+// T = X F with the factor F(k, j) in either orientation
+template <class T>
+void launch_xa(const T *x, const T *f, float *t, uint64_t rows, uint64_t d_in, uint32_t rank, int32_t layout,
+               cudaStream_t s) {
+    if (layout == NF4_LAYOUT_OUT_IN)
+        lora_xa_kernel<T><<<(unsigned)((rows * rank * 32 + 255) / 256), 256, 0, s>>>(x, f, t, rows, d_in, rank, layout);
+    else if (rank <= 32)
+        lora_xa_kmajor_kernel<T, 1><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(x, f, t, rows, d_in, rank);
+    else
+        lora_xa_kmajor_kernel<T, 2><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(x, f, t, rows, d_in, rank);
+}
+
 template <class T>
 int32_t forward_t(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, const void *a, const void *b,
                   uint32_t rank, float scale, int32_t layout, void *y, uint64_t ldy, float *t, cudaStream_t s) {
-    const uint64_t warps = rows * rank;
-    lora_xa_kernel<T><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>(
-        static_cast<const T *>(x), static_cast<const T *>(a), t, rows, d_in, rank, layout);
+    launch_xa<T>(static_cast<const T *>(x), static_cast<const T *>(a), t, rows, d_in, rank, layout, s);
     lora_tb_kernel<T><<<(unsigned)((rows * d_out + 255) / 256), 256, 0, s>>>(
         t, static_cast<const T *>(b), static_cast<T *>(y), rows, d_out, ldy, rank, scale, layout);
     count_launch(2);
@@ -174,15 +304,15 @@ int32_t grads_t(const void *x, const void *gy, const void *a, const void *b, uin
                 uint64_t d_out, uint32_t rank, float scale, int32_t layout, void *ga, void *gb, float *t,
                 float *u, cudaStream_t s) {
     const T *xx = static_cast<const T *>(x), *gg = static_cast<const T *>(gy);
-    const unsigned wgrid = (unsigned)((rows * rank * 32 + 255) / 256);
     // T = x A (as in the forward) and U = grad_y B^T (B read as an "A" of the other orientation)
-    lora_xa_kernel<T><<<wgrid, 256, 0, s>>>(xx, static_cast<const T *>(a), t, rows, d_in, rank, layout);
-    lora_xa_kernel<T><<<wgrid, 256, 0, s>>>(gg, static_cast<const T *>(b), u, rows, d_out, rank,
-                                          layout == NF4_LAYOUT_OUT_IN ? NF4_LAYOUT_IN_OUT : NF4_LAYOUT_OUT_IN);
+    launch_xa<T>(xx, static_cast<const T *>(a), t, rows, d_in, rank, layout, s);
+    launch_xa<T>(gg, static_cast<const T *>(b), u, rows, d_out, rank,
+                 layout == NF4_LAYOUT_OUT_IN ? NF4_LAYOUT_IN_OUT : NF4_LAYOUT_OUT_IN, s);
     // grad_A(k, j) = s sum_m x[m][k] U[m][j];  grad_B(j, n) = s sum_m T[m][j] grad_y[m][n]
-    lora_xtr_kernel<T><<<(unsigned)((d_in * rank + 255) / 256), 256, 0, s>>>(
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(lora_xtr_tile_kernel<T>), (int)xtr_smem_bytes<T>()));
+    lora_xtr_tile_kernel<T><<<(unsigned)((d_in + kXtrP - 1) / kXtrP), 256, xtr_smem_bytes<T>(), s>>>(
         xx, u, static_cast<T *>(ga), rows, d_in, rank, scale, layout == NF4_LAYOUT_IN_OUT);
-    lora_xtr_kernel<T><<<(unsigned)((d_out * rank + 255) / 256), 256, 0, s>>>(
+    lora_xtr_tile_kernel<T><<<(unsigned)((d_out + kXtrP - 1) / kXtrP), 256, xtr_smem_bytes<T>(), s>>>(
         gg, t, static_cast<T *>(gb), rows, d_out, rank, scale, layout == NF4_LAYOUT_OUT_IN);
     count_launch(4);
     return check_cuda(cudaGetLastError(), "lora gradient launch");
