@@ -446,6 +446,45 @@ def test_prefill_linearity_at_full_config3_size(oracle):
         assert ((got - ref).norm() / ref.norm()).item() < 1e-3 + 2.0 ** -9
 
 
+@pytest.mark.parametrize("layout_name,M,K,N,r", [("out_in", 300, 448, 576, 24), ("in_out", 130, 320, 200, 72),
+                                                 ("out_in", 9, 200, 100, 5)])   # the last: shapes the MMA product declines
+def test_qlora_backward_bf16(oracle, layout_name, M, K, N, r):
+    # bf16 tensors: the adapter intermediates come from warp MMAs (exact products, f32 sums), grad_x at
+    # more than 16 rows from the tensor-core GEMM; outputs are bf16 (one rounding: 2^-9)
+    from unifur_b200.quantize import PackedNf4Tensor
+    from unifur_b200.qwennet import Nf4Linear, QloraLinear
+
+    rng = np.random.default_rng(950 + M + K + N)
+    out_in = layout_name == "out_in"
+    w = (rng.standard_normal((N, K) if out_in else (K, N)) * 0.02).astype(np.float32)
+    packed, absmax = oracle.quantize_packed(w)
+    wd = oracle.dequantize_packed(packed, w.size, absmax).reshape(w.shape).astype(np.float64)
+    a = bf16_round(oracle, rng.standard_normal((r, K) if out_in else (K, r)) * 0.1)
+    b = bf16_round(oracle, rng.standard_normal((N, r) if out_in else (r, N)) * 0.1)
+    x = bf16_round(oracle, rng.standard_normal((M, K)))
+    gy = bf16_round(oracle, rng.standard_normal((M, N)))
+    s = 1.5
+    X, GY, A, B = (t.astype(np.float64) for t in (x, gy, a, b))
+    if out_in:
+        gx_ref = GY @ wd + s * (GY @ B) @ A
+        ga_ref = s * (GY @ B).T @ X
+        gb_ref = s * GY.T @ (X @ A.T)
+    else:
+        gx_ref = GY @ wd.T + s * (GY @ B.T) @ A.T
+        ga_ref = s * X.T @ (GY @ B.T)
+        gb_ref = s * (X @ A).T @ GY
+    lay = _lib.LAYOUT_OUT_IN if out_in else _lib.LAYOUT_IN_OUT
+    bf = lambda t: torch.from_numpy(t).to(DEV).bfloat16()
+    base = Nf4Linear(PackedNf4Tensor.quantize(torch.from_numpy(w.reshape(-1)).to(DEV)), K, N, None, lay)
+    q = QloraLinear(base, bf(a), bf(b), s)
+    gx, ga, gb = q.backward(bf(x), bf(gy))
+    assert gx.dtype == torch.bfloat16
+    tol = 1e-3 + 2.0 ** -8
+    assert rel_l2(gx.float().cpu().numpy(), gx_ref) <= tol
+    assert rel_l2(ga.float().cpu().numpy(), ga_ref) <= tol
+    assert rel_l2(gb.float().cpu().numpy(), gb_ref) <= tol
+
+
 @pytest.mark.parametrize("layout_name,M,K,N,r", [("out_in", 8, 256, 192, 16), ("out_in", 40, 512, 320, 8),
                                                  ("in_out", 6, 128, 96, 4),
                                                  ("out_in", 300, 448, 576, 24),   # several pieces of rows, ragged tiles of columns

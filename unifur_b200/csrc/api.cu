@@ -600,7 +600,10 @@ int32_t nf4_qlora_merge_dev(const uint8_t *packed, const float *absmax, const ui
 
 uint64_t nf4_qlora_backward_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
     // grad_x is a forward with d_in and d_out exchanged; then two [rows][rank] f32 intermediates
-    return nf4_linear_workspace_bytes(rows, d_out, d_in, lora_rank) + 2 * lora_workspace_bytes(rows, lora_rank);
+    // ... and one adapter factor transposed (bf16)
+    const uint64_t widest = d_in > d_out ? d_in : d_out;
+    return nf4_linear_workspace_bytes(rows, d_out, d_in, lora_rank) + 2 * lora_workspace_bytes(rows, lora_rank) +
+           align_up((uint64_t)lora_rank * widest * 2, 256);
 }
 
 int32_t nf4_qlora_backward_dev(const nf4_linear_args *fwd, const void *grad_y, void *grad_x, void *grad_a,
@@ -637,8 +640,9 @@ int32_t nf4_qlora_backward_dev(const nf4_linear_args *fwd, const void *grad_y, v
     uint8_t *ws = static_cast<uint8_t *>(fwd->workspace) + fw;
     float *t = reinterpret_cast<float *>(ws);
     float *u = reinterpret_cast<float *>(ws + lora_workspace_bytes(fwd->rows, r));
+    void *factor_t = ws + 2 * lora_workspace_bytes(fwd->rows, r);
     return lora_grads(fwd->x, grad_y, fwd->lora_a, fwd->lora_b, fwd->rows, fwd->d_in, fwd->d_out, r,
-                      fwd->lora_scale, fwd->layout, fwd->io_dtype, grad_a, grad_b, t, u,
+                      fwd->lora_scale, fwd->layout, fwd->io_dtype, grad_a, grad_b, t, u, factor_t,
                       static_cast<cudaStream_t>(stream));
 }
 

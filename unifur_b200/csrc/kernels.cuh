@@ -36,7 +36,7 @@ int32_t lora_delta(const void *a, const void *b, const uint8_t *packed, const fl
                    uint32_t rank, float scale, int32_t layout, int32_t io_dtype, float *out, cudaStream_t s);
 int32_t lora_grads(const void *x, const void *gy, const void *a, const void *b, uint64_t rows, uint64_t d_in,
                    uint64_t d_out, uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *ga,
-                   void *gb, float *t, float *u, cudaStream_t s);
+                   void *gb, float *t, float *u, void *scratch, cudaStream_t s);
 int32_t push_columns(void *const *y_full, uint32_t *const *arrive, uint32_t world, uint32_t rank, uint64_t rows,
                      uint64_t width_bytes, uint64_t ldy_bytes, bool signal, uint32_t *done, cudaStream_t s);
 int32_t gather_slabs(const void *slab, void *gathered, void *y, uint64_t rows, uint64_t width_bytes,
@@ -117,5 +117,8 @@ uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, u
 int32_t prefill_share_plan(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t cta, uint32_t *ctas,
                            uint32_t *segments, uint32_t cap);
 int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream);
+// t32[m][j] = sum_k x[m][k] F(k, j), bf16 operands on warp MMAs; NF4_ERR_UNSUPPORTED (no message) for shapes it declines
+int32_t adapter_intermediate_bf16(const void *x, const void *f, bool k_major, uint64_t rows, uint64_t k, uint32_t rank,
+                                  float *t32, void *scratch, cudaStream_t stream);
 
 }  // namespace nf4

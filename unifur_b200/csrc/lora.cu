@@ -302,12 +302,23 @@ int32_t forward_t(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, c
 template <class T>
 int32_t grads_t(const void *x, const void *gy, const void *a, const void *b, uint64_t rows, uint64_t d_in,
                 uint64_t d_out, uint32_t rank, float scale, int32_t layout, void *ga, void *gb, float *t,
-                float *u, cudaStream_t s) {
+                float *u, void *scratch, cudaStream_t s) {
     const T *xx = static_cast<const T *>(x), *gg = static_cast<const T *>(gy);
-    // T = x A (as in the forward) and U = grad_y B^T (B read as an "A" of the other orientation)
-    launch_xa<T>(xx, static_cast<const T *>(a), t, rows, d_in, rank, layout, s);
-    launch_xa<T>(gg, static_cast<const T *>(b), u, rows, d_out, rank,
-                 layout == NF4_LAYOUT_OUT_IN ? NF4_LAYOUT_IN_OUT : NF4_LAYOUT_OUT_IN, s);
+    // T = x A (as in the forward) and U = grad_y B^T (B read as an "A" of the other orientation).
+    // bf16: on warp MMAs (products of bf16 values are exact in f32, so the sums differ from the
+    // CUDA-core kernels' only in their order); shapes that path declines, and f32, on CUDA cores.
+    const int32_t other = layout == NF4_LAYOUT_OUT_IN ? NF4_LAYOUT_IN_OUT : NF4_LAYOUT_OUT_IN;
+    bool t_done = false, u_done = false;
+    if (sizeof(T) == 2) {
+        int32_t rc = adapter_intermediate_bf16(x, a, layout == NF4_LAYOUT_IN_OUT, rows, d_in, rank, t, scratch, s);
+        if (rc == NF4_OK) t_done = true;
+        else if (rc != NF4_ERR_UNSUPPORTED) return rc;
+        rc = adapter_intermediate_bf16(gy, b, other == NF4_LAYOUT_IN_OUT, rows, d_out, rank, u, scratch, s);
+        if (rc == NF4_OK) u_done = true;
+        else if (rc != NF4_ERR_UNSUPPORTED) return rc;
+    }
+    if (!t_done) launch_xa<T>(xx, static_cast<const T *>(a), t, rows, d_in, rank, layout, s);
+    if (!u_done) launch_xa<T>(gg, static_cast<const T *>(b), u, rows, d_out, rank, other, s);
     // grad_A(k, j) = s sum_m x[m][k] U[m][j];  grad_B(j, n) = s sum_m T[m][j] grad_y[m][n]
     NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(lora_xtr_tile_kernel<T>), (int)xtr_smem_bytes<T>()));
     lora_xtr_tile_kernel<T><<<(unsigned)((d_in + kXtrP - 1) / kXtrP), 256, xtr_smem_bytes<T>(), s>>>(
@@ -378,15 +389,16 @@ int32_t lora_delta(const void *a, const void *b, const uint8_t *packed, const fl
     return check_cuda(cudaGetLastError(), "lora delta launch");
 }
 
-// grad_A and grad_B of y = x W + s (x A) B with W frozen; t and u are [rows][rank] f32 scratch.
+// grad_A and grad_B of y = x W + s (x A) B with W frozen; t and u are [rows][rank] f32 scratch,
+// `scratch` rank * max(d_in, d_out) * 2 bytes (a factor transposed; used one product at a time).
 int32_t lora_grads(const void *x, const void *gy, const void *a, const void *b, uint64_t rows, uint64_t d_in,
                    uint64_t d_out, uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *ga,
-                   void *gb, float *t, float *u, cudaStream_t s) {
+                   void *gb, float *t, float *u, void *scratch, cudaStream_t s) {
     if (rows * rank >= (1ull << 40) || (d_in + d_out) * rank >= (1ull << 40))
         return fail(NF4_ERR_UNSUPPORTED, "lora gradients: shape too large");
     return io_dtype == NF4_DTYPE_F32
-               ? grads_t<float>(x, gy, a, b, rows, d_in, d_out, rank, scale, layout, ga, gb, t, u, s)
-               : grads_t<__nv_bfloat16>(x, gy, a, b, rows, d_in, d_out, rank, scale, layout, ga, gb, t, u, s);
+               ? grads_t<float>(x, gy, a, b, rows, d_in, d_out, rank, scale, layout, ga, gb, t, u, scratch, s)
+               : grads_t<__nv_bfloat16>(x, gy, a, b, rows, d_in, d_out, rank, scale, layout, ga, gb, t, u, scratch, s);
 }
 
 // All-gather of the ranks' [rows, width_bytes] slabs into `gathered` ([world][rows][width_bytes]),

@@ -814,16 +814,19 @@ __device__ __forceinline__ uint4 bf16x8_to_f16x8(const uint4 &v, float is) {
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-// XH_READY: the activations arrive as the f16 copy itself (made, with the row scales, by
+// MODE 1 (XH_READY): the activations arrive as the f16 copy itself (made, with the row scales, by
 // x_f32_to_f16_kernel) and the adapter factor as f16: only T is computed, with f16 MMAs.
-template <bool XH_READY>
+// MODE 2 (T_ONLY): the product alone, t32[m][j] = sum_k x[m][k] a[j][k] in f32, for callers outside
+// the GEMM (the adapter's gradients): no copy of x, no scales.
+template <int MODE>
 __global__ void __launch_bounds__(kTThreads)
 prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
                        uint32_t M, uint32_t K, uint32_t rank, uint32_t chunks, float scale,
                        __half *__restrict__ xh, float *__restrict__ row_scale,
                        __nv_bfloat16 *__restrict__ t_out, const float *__restrict__ absmax,
                        const uint8_t *__restrict__ scale_codes, const float *__restrict__ scale_of_scales,
-                       uint32_t *__restrict__ sk_flags, uint32_t n_flags) {
+                       uint32_t *__restrict__ sk_flags, uint32_t n_flags, float *__restrict__ t32) {
+    constexpr bool XH_READY = MODE == 1, T_ONLY = MODE == 2;
     // the warps' partial sums of T: [warp][16 rows][64 ranks, padded to 72], summed in warp order
     extern __shared__ __align__(16) float part[];
     __shared__ uint32_t row_max_bits[16];
@@ -836,7 +839,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
     // the GEMM's CTAs raise these once this kernel has completed (their readers and writers wait for that)
     if (blockIdx.x == 0)
         for (uint32_t i = threadIdx.x; i < n_flags; i += kTThreads) sk_flags[i] = 0;
-    const int w_exp = weight_exponent(absmax, scale_codes, scale_of_scales);
+    const int w_exp = T_ONLY ? 0 : weight_exponent(absmax, scale_codes, scale_of_scales);
     const float w_up = ldexpf(1.0f, w_exp), w_down = ldexpf(1.0f, -w_exp);
     const bool row_a = g < rows, row_b = g + 8 < rows;
     const uint32_t pieces = (K + 31) / 32, n_it = (pieces + kTWarps - 1) / kTWarps;
@@ -869,7 +872,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
         };
         auto process = [&](const PrepassPiece &pc, uint32_t it) {
             const uint32_t k = k_of(it);
-            if (!XH_READY && chunk == 0 && it < n_it && k + 8 <= K) {
+            if (MODE == 0 && chunk == 0 && it < n_it && k + 8 <= K) {
                 if (row_a) {
                     mx_a = bf16x2_absmax(pc.xa.x, bf16x2_absmax(pc.xa.y, mx_a));
                     mx_a = bf16x2_absmax(pc.xa.z, bf16x2_absmax(pc.xa.w, mx_a));
@@ -903,7 +906,7 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             process(p1, it + 1);
         }
 
-        if (!XH_READY && chunk == 0) {
+        if (MODE == 0 && chunk == 0) {
             atomicMax(&row_max_bits[g], bf16x2_larger_bits(mx_a));
             atomicMax(&row_max_bits[g + 8], bf16x2_larger_bits(mx_b));
         }
@@ -917,11 +920,11 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
             }
         }
         __syncthreads();
-        if (XH_READY && chunk == 0) {
-            if (threadIdx.x < 16) inv_scale[threadIdx.x] = 1.0f;  // the rows arrive scaled
+        if (MODE != 0 && chunk == 0) {
+            if (threadIdx.x < 16) inv_scale[threadIdx.x] = 1.0f;  // the rows arrive scaled, or stay as they are
             __syncthreads();
         }
-        if (!XH_READY && chunk == 0) {
+        if (MODE == 0 && chunk == 0) {
             if (threadIdx.x < 16) {
                 const float mx = __uint_as_float(row_max_bits[threadIdx.x]);
                 float sc = 1.0f;
@@ -952,6 +955,10 @@ prefill_prepass_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 
                     float sum = 0.0f;
                     #pragma unroll
                     for (int w = 0; w < kTWarps; ++w) sum += part[w * (16 * kTPartStride) + r * kTPartStride + c];
+                    if (T_ONLY) {
+                        if (chunk * 64 + c < rank) t32[(size_t)(m0 + r) * rank + chunk * 64 + c] = sum;
+                        continue;
+                    }
                     const float v = sum * scale * inv_scale[r] * w_down;
                     const __nv_bfloat16 hi = __float2bfloat16_rn(v);
                     const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
@@ -1359,21 +1366,21 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
         p.scales_t = rp.scales_t;
         NF4_CUDA_TRY(cudaGetLastError());
     }
-    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<true>), kTPartBytes));
-    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<false>), kTPartBytes));
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<1>), kTPartBytes));
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<0>), kTPartBytes));
     if (x_f32) {
         x_f32_to_f16_kernel<<<p.M, 256, 0, stream>>>(static_cast<const float *>(a.x), p.K, xh, row_scale, a.absmax,
                                                    a.scale_codes, a.scale_of_scales);
         count_launch();
-        prefill_prepass_kernel<true><<<(p.M + 15) / 16, kTThreads, kTPartBytes, stream>>>(
+        prefill_prepass_kernel<1><<<(p.M + 15) / 16, kTThreads, kTPartBytes, stream>>>(
             reinterpret_cast<const __nv_bfloat16 *>(xh), static_cast<const __nv_bfloat16 *>(lora_a), p.M, p.K, p.rank,
             p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales, p.sk_flags,
-            sh.grid);
+            sh.grid, nullptr);
     } else {
-        prefill_prepass_kernel<false><<<(p.M + 15) / 16, kTThreads, kTPartBytes, stream>>>(
+        prefill_prepass_kernel<0><<<(p.M + 15) / 16, kTThreads, kTPartBytes, stream>>>(
             static_cast<const __nv_bfloat16 *>(a.x), static_cast<const __nv_bfloat16 *>(lora_a), p.M, p.K, p.rank,
             p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales, p.sk_flags,
-            sh.grid);
+            sh.grid, nullptr);
     }
     count_launch();
     NF4_CUDA_TRY(cudaGetLastError());
@@ -1411,6 +1418,39 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     return check_cuda(cudaGetLastError(), "prefill_kernel launch");
 }
 
+
+namespace {
+// dst[j][k] = src[k][j] for a bf16 factor [K][r]
+__global__ void __launch_bounds__(256)
+transpose_factor_kernel(const uint16_t *__restrict__ src, uint16_t *__restrict__ dst, uint64_t K, uint32_t r) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= K * r) return;
+    const uint64_t j = i / K, k = i % K;
+    dst[i] = src[k * r + j];
+}
+}  // namespace
+
+// t32[m][j] = sum_k x[m][k] F(k, j) for bf16 x [rows][k] on the warp MMAs of the pre-pass; the factor is
+// f [rank][k] (`k_major` false) or f [k][rank], which is transposed into `scratch` (rank * k * 2 bytes)
+// first.  Declines shapes its 16-byte loads do not cover.
+int32_t adapter_intermediate_bf16(const void *x, const void *f, bool k_major, uint64_t rows, uint64_t k, uint32_t rank,
+                                  float *t32, void *scratch, cudaStream_t stream) {
+    if (k % 8 != 0 || rows == 0 || rows >= (1ull << 31) || k >= (1ull << 31) || rank == 0 || !aligned16(x) ||
+        (k_major ? !scratch || !aligned16(scratch) : !aligned16(f)))
+        return NF4_ERR_UNSUPPORTED;
+    if (k_major) {
+        transpose_factor_kernel<<<(unsigned)((k * rank + 255) / 256), 256, 0, stream>>>(
+            static_cast<const uint16_t *>(f), static_cast<uint16_t *>(scratch), k, rank);
+        count_launch();
+        f = scratch;
+    }
+    NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<2>), kTPartBytes));
+    prefill_prepass_kernel<2><<<(unsigned)((rows + 15) / 16), kTThreads, kTPartBytes, stream>>>(
+        static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(f), (uint32_t)rows, (uint32_t)k, rank,
+        lora_chunks_of(rank), 1.0f, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, t32);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "adapter intermediate launch");
+}
 
 int32_t prefill_set_host_flag(int *mapped) {
     return check_cuda(cudaMemcpyToSymbol(g_prefill_error_host, &mapped, sizeof(mapped)), "setting the mapped failure word");
