@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "kernels.cuh"
+#include "ptx.cuh"
 
 namespace nf4 {
 namespace {
@@ -230,6 +231,94 @@ lora_xtr_tile_kernel(const T *__restrict__ x, const float *__restrict__ r, T *__
     }
 }
 
+// The same gradients for bf16 tensors on warp MMAs: out(p, j) = scale * sum_m X[m][p] R[m][j] as
+// D[p][j] += A[p][m] B[m][j] with m16n8k16.  A CTA takes 64 columns p and up to 64 ranks; pieces of
+// 64 rows m pass through shared memory transposed (X as it is; R split into bf16 high and low parts,
+// so that its f32 value survives: two MMAs per tile), which makes every fragment one 32-bit load;
+// warp w takes the 16 columns (w & 3) and the two k-steps (w >> 2) of a piece; the two halves meet
+// in a fixed order.  P must be even (pairs of columns are read as words).
+__global__ void __launch_bounds__(256)
+lora_xtr_mma_kernel(const __nv_bfloat16 *__restrict__ x, const float *__restrict__ r, __nv_bfloat16 *__restrict__ out,
+                    uint64_t rows, uint64_t P, uint32_t rank, float scale, int p_major) {
+    constexpr int kP = 64, kJ = 64, kM = 64, kS = 72;  // kS: halves per transposed row (fragment loads hit 32 banks)
+    __shared__ __align__(16) uint16_t xs_t[kP][kS];
+    __shared__ __align__(16) uint16_t rh[kJ][kS], rl[kJ][kS];
+    __shared__ float sum[kP][kJ + 1];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t pt = warp & 3u, h = warp >> 2;
+    const uint64_t p0 = (uint64_t)blockIdx.x * kP;
+    const uint32_t lo = threadIdx.x & 31u, hi = threadIdx.x >> 5;  // staging: 8 columns x 4 rows per warp and step
+    for (uint32_t j0 = 0; j0 < rank; j0 += kJ) {
+        float acc[8][4];
+        #pragma unroll
+        for (int jt = 0; jt < 8; ++jt) acc[jt][0] = acc[jt][1] = acc[jt][2] = acc[jt][3] = 0.0f;
+        for (uint64_t m0 = 0; m0 < rows; m0 += kM) {
+            __syncthreads();
+            #pragma unroll
+            for (int it = 0; it < 8; ++it) {   // X: 64 rows x 32 pairs of columns
+                const uint32_t hh = hi + 8 * it;  // 0 .. 63
+                const uint32_t pair = (lo & 7u) + 8 * (hh & 3u), m = (lo >> 3) + 4 * (hh >> 2);
+                uint32_t v = 0;
+                if (m0 + m < rows && p0 + 2 * pair < P)
+                    v = __ldg(reinterpret_cast<const uint32_t *>(x + (m0 + m) * P + p0 + 2 * pair));
+                xs_t[2 * pair][m] = (uint16_t)(v & 0xffffu);
+                xs_t[2 * pair + 1][m] = (uint16_t)(v >> 16);
+            }
+            #pragma unroll
+            for (int it = 0; it < 16; ++it) {  // R: 64 rows x 64 ranks
+                const uint32_t hh = hi + 8 * it;  // 0 .. 127
+                const uint32_t j = (lo & 7u) + 8 * (hh & 7u), m = (lo >> 3) + 4 * (hh >> 3);
+                float v = 0.0f;
+                if (m0 + m < rows && j0 + j < rank) v = __ldg(r + (m0 + m) * rank + j0 + j);
+                const __nv_bfloat16 vh = __float2bfloat16_rn(v);
+                const __nv_bfloat16 vl = __float2bfloat16_rn(v - __bfloat162float(vh));
+                rh[j][m] = __bfloat16_as_ushort(vh);
+                rl[j][m] = __bfloat16_as_ushort(vl);
+            }
+            __syncthreads();
+            #pragma unroll
+            for (int ks2 = 0; ks2 < 2; ++ks2) {
+                const uint32_t mb = (2 * h + ks2) * 16 + 2 * t;
+                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(&xs_t[pt * 16 + g][mb]);
+                const uint32_t a1 = *reinterpret_cast<const uint32_t *>(&xs_t[pt * 16 + g + 8][mb]);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(&xs_t[pt * 16 + g][mb + 8]);
+                const uint32_t a3 = *reinterpret_cast<const uint32_t *>(&xs_t[pt * 16 + g + 8][mb + 8]);
+                #pragma unroll
+                for (int jt = 0; jt < 8; ++jt) {
+                    const uint32_t bh0 = *reinterpret_cast<const uint32_t *>(&rh[jt * 8 + g][mb]);
+                    const uint32_t bh1 = *reinterpret_cast<const uint32_t *>(&rh[jt * 8 + g][mb + 8]);
+                    const uint32_t bl0 = *reinterpret_cast<const uint32_t *>(&rl[jt * 8 + g][mb]);
+                    const uint32_t bl1 = *reinterpret_cast<const uint32_t *>(&rl[jt * 8 + g][mb + 8]);
+                    ptx::mma_16816_bf16(acc[jt], a0, a1, a2, a3, bh0, bh1);
+                    ptx::mma_16816_bf16(acc[jt], a0, a1, a2, a3, bl0, bl1);
+                }
+            }
+        }
+        // the two halves of the rows, in order
+        for (uint32_t turn = 0; turn < 2; ++turn) {
+            __syncthreads();
+            if (h == turn) {
+                #pragma unroll
+                for (int jt = 0; jt < 8; ++jt) {
+                    float *s0 = &sum[pt * 16 + g][jt * 8 + 2 * t], *s1 = &sum[pt * 16 + g + 8][jt * 8 + 2 * t];
+                    s0[0] = turn ? s0[0] + acc[jt][0] : acc[jt][0];
+                    s0[1] = turn ? s0[1] + acc[jt][1] : acc[jt][1];
+                    s1[0] = turn ? s1[0] + acc[jt][2] : acc[jt][2];
+                    s1[1] = turn ? s1[1] + acc[jt][3] : acc[jt][3];
+                }
+            }
+        }
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < kP * kJ; i += 256) {
+            // p fastest for [rank][P] outputs, j fastest for [P][rank]
+            const uint32_t q = p_major ? i / kJ : i % kP, j = p_major ? i % kJ : i / kP;
+            const uint64_t pp = p0 + q;
+            if (pp < P && j0 + j < rank)
+                out[p_major ? pp * rank + j0 + j : (uint64_t)(j0 + j) * P + pp] = __float2bfloat16_rn(__fmul_rn(sum[q][j], scale));
+        }
+    }
+}
+
 // y[r][rank * width + c] = gathered[rank][r][c]: the ranks' slabs side by side.  16-byte pieces.
 __global__ void __launch_bounds__(256)
 place_slabs_kernel(const uint4 *__restrict__ gathered, uint4 *__restrict__ y, uint64_t rows, uint64_t pieces_per_row,
@@ -321,10 +410,16 @@ int32_t grads_t(const void *x, const void *gy, const void *a, const void *b, uin
     if (!u_done) launch_xa<T>(gg, static_cast<const T *>(b), u, rows, d_out, rank, other, s);
     // grad_A(k, j) = s sum_m x[m][k] U[m][j];  grad_B(j, n) = s sum_m T[m][j] grad_y[m][n]
     NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(lora_xtr_tile_kernel<T>), (int)xtr_smem_bytes<T>()));
-    lora_xtr_tile_kernel<T><<<(unsigned)((d_in + kXtrP - 1) / kXtrP), 256, xtr_smem_bytes<T>(), s>>>(
-        xx, u, static_cast<T *>(ga), rows, d_in, rank, scale, layout == NF4_LAYOUT_IN_OUT);
-    lora_xtr_tile_kernel<T><<<(unsigned)((d_out + kXtrP - 1) / kXtrP), 256, xtr_smem_bytes<T>(), s>>>(
-        gg, t, static_cast<T *>(gb), rows, d_out, rank, scale, layout == NF4_LAYOUT_OUT_IN);
+    auto xtr = [&](const void *X, const float *R, void *out, uint64_t P, int p_major) {
+        if (sizeof(T) == 2 && P % 2 == 0 && (reinterpret_cast<uintptr_t>(X) & 3u) == 0)
+            lora_xtr_mma_kernel<<<(unsigned)((P + 63) / 64), 256, 0, s>>>(
+                static_cast<const __nv_bfloat16 *>(X), R, static_cast<__nv_bfloat16 *>(out), rows, P, rank, scale, p_major);
+        else
+            lora_xtr_tile_kernel<T><<<(unsigned)((P + kXtrP - 1) / kXtrP), 256, xtr_smem_bytes<T>(), s>>>(
+                static_cast<const T *>(X), R, static_cast<T *>(out), rows, P, rank, scale, p_major);
+    };
+    xtr(x, u, ga, d_in, layout == NF4_LAYOUT_IN_OUT);
+    xtr(gy, t, gb, d_out, layout == NF4_LAYOUT_OUT_IN);
     count_launch(4);
     return check_cuda(cudaGetLastError(), "lora gradient launch");
 }
