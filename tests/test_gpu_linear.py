@@ -256,6 +256,35 @@ def test_reference_orientation_at_prefill_sizes(oracle, rows, d_in, d_out, r, dq
         assert rel_l2(y16, ref) <= REL_L2_BF16 + 2.0 ** -9
 
 
+@pytest.mark.parametrize("rows,d_in,d_out,r,dq,bias", [
+    (33, 256, 200, 4, False, True),      # d_out no multiple of the tile: the last tile's rows beyond N
+    (500, 1024, 1536, 16, True, False),
+    (257, 4096, 640, 64, False, False),  # f32 factors of rank 64 enter as rank 128: two chunks per half of T
+])
+def test_f32_tensors_at_prefill_sizes(oracle, rows, d_in, d_out, r, dq, bias):
+    # W [d_out, d_in] with f32 activations and factors (the reference's tensor type) at more than 16
+    # rows: activations to f16 per row, factors converted into the workspace, the tensor-core GEMM
+    rng = np.random.default_rng(860 + rows + d_in + d_out)
+    w = (rng.standard_normal((d_out, d_in)) * 0.02).astype(np.float32)
+    packed, absmax = oracle.quantize_packed(w)
+    sc = sos = None
+    if dq:
+        sc, sos = oracle.double_quantize(absmax)
+    x = rng.standard_normal((rows, d_in)).astype(np.float32)
+    x[1] *= 2.0 ** 19
+    x[2] *= 2.0 ** -21
+    la = (rng.standard_normal((r, d_in)) * 0.05).astype(np.float32)
+    lb = rng.uniform(-0.5, 0.5, (d_out, r)).astype(np.float32)
+    b = rng.standard_normal(d_out).astype(np.float32) if bias else None
+    ref = oracle.qlora_forward_bnb(x, packed, None if dq else absmax, d_out, d_in, la, lb, 2.0, b, sc,
+                                   sos if dq else 0.0)
+    kw = dict(bias=b, lora_a=la, lora_b=lb, scale=2.0, scale_codes=sc, sos=sos)
+    got = run_forward(_lib.LAYOUT_OUT_IN, _lib.DTYPE_F32, x, packed, None if dq else absmax, d_in, d_out, calls=2, **kw)
+    assert rel_l2(got, ref) <= 1e-3
+    for rows_ in (slice(0, 1), slice(1, 2), slice(2, 3), slice(rows - 1, rows)):
+        assert rel_l2(got[rows_], ref[rows_]) <= 1e-3, rows_
+
+
 def test_layout_kat_minus_three(oracle):
     # qwennet.rs:2196-2211: y[o] = sum_i x[i] W[i][o] with W = [[1,2,3],[4,5,6]] (values on a
     # grid NF4 cannot hold exactly, so compare against the oracle's own dequantized weight)
@@ -524,6 +553,8 @@ def test_qlora_backward_matches_f64_reference(oracle, layout_name, M, K, N, r):
     assert rel_l2(gx.cpu().numpy(), gx_ref) <= (1e-3 if (out_in and M > 16) else REL_L2_F32)
     assert rel_l2(ga.cpu().numpy(), ga_ref) <= REL_L2_F32
     assert rel_l2(gb.cpu().numpy(), gb_ref) <= REL_L2_F32
+    if M > 16:
+        return   # the forward of more than 16 rows rounds the activations to f16: too coarse for a difference quotient
     # and the forward it differentiates: finite differences along one direction
     dx = rng.standard_normal((M, K)).astype(np.float32) * 1e-2
     y0 = q.forward(torch.from_numpy(x).to(DEV)).double().cpu().numpy()

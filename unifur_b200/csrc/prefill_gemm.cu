@@ -987,6 +987,7 @@ struct RepackParams {
     uint16_t *a_t;
     __nv_bfloat16 *b_t;
     uint32_t K, N, r;
+    int32_t factors_out_in;     // the factors come as A [r][K], B [N][r] (else A [K][r], B [r][N])
     uint32_t code_cols, code_rows, code_blocks;   // CTAs of the nibbles: columns of 128 n x groups of kRepackTiles k-tiles
     uint32_t scale_cols, scale_blocks;            // CTAs of the scales: 32 x 32 tiles
 };
@@ -1070,23 +1071,25 @@ __device__ __forceinline__ void repack_adapter_block(const RepackParams &p, uint
     const uint64_t na = (uint64_t)r * p.K, nb = (uint64_t)p.N * r;
     if (i < na) {
         const uint32_t j = (uint32_t)(i / p.K), k = (uint32_t)(i % p.K);
+        const size_t at = p.factors_out_in ? (size_t)j * p.K + k : (size_t)k * r + j;
         if constexpr (kF32) {
-            const __half h = __float2half_rn(a[(size_t)k * r + j]);
+            const __half h = __float2half_rn(a[at]);
             p.a_t[i] = __half_as_ushort(h);
             p.a_t[na + i] = __half_as_ushort(h);
         } else {
-            p.a_t[i] = reinterpret_cast<const uint16_t *>(a)[(size_t)k * r + j];
+            p.a_t[i] = reinterpret_cast<const uint16_t *>(a)[at];
         }
     } else if (i < na + nb) {
         const uint64_t e = i - na;
         const uint32_t n = (uint32_t)(e / r), j = (uint32_t)(e % r);
+        const size_t at = p.factors_out_in ? (size_t)n * r + j : (size_t)j * p.N + n;
         if constexpr (kF32) {
-            const float v = b[(size_t)j * p.N + n];
+            const float v = b[at];
             const __nv_bfloat16 hi = __float2bfloat16_rn(v);
             p.b_t[(size_t)n * rank_out + j] = hi;
             p.b_t[(size_t)n * rank_out + r + j] = __float2bfloat16_rn(v - __bfloat162float(hi));
         } else {
-            p.b_t[(size_t)n * rank_out + j] = b[(size_t)j * p.N + n];
+            p.b_t[(size_t)n * rank_out + j] = b[at];
         }
     }
 }
@@ -1190,15 +1193,20 @@ uint32_t lora_chunks_of(uint32_t rank) { return (rank + 63) / 64; }
 }  // namespace
 
 bool prefill_supported(const nf4_linear_args &a) {
-    if (a.layout != NF4_LAYOUT_OUT_IN || a.io_dtype != NF4_DTYPE_BF16) return false;
+    if (a.layout != NF4_LAYOUT_OUT_IN) return false;
+    if (a.io_dtype != NF4_DTYPE_BF16 && a.io_dtype != NF4_DTYPE_F32) return false;
+    const bool f32 = a.io_dtype == NF4_DTYPE_F32;
     if (a.rows <= 16) return false;  // the decode kernel's territory
     if (a.d_in % 64 != 0 || a.d_in >= (1ull << 31) || a.d_out >= (1ull << 31) || a.rows >= (1ull << 31))
         return false;
     const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
-    const uint64_t ybytes = a.y_f32 ? 4 : 2;
+    const uint64_t ybytes = (a.y_f32 || f32) ? 4 : 2;
     if ((ldy * ybytes) % 16 != 0 || !aligned16(a.y) || !aligned16(a.x) || !aligned16(a.packed))
         return false;
-    if (a.lora_a) {
+    if (a.lora_a && f32) {
+        // f32 factors are converted into the workspace and enter as an adapter of twice the rank
+        if (2 * a.lora_rank > 256 || (2 * a.lora_rank) % 8 != 0) return false;
+    } else if (a.lora_a) {
         // LoRA B is read by TMA: rows (rank * 2 bytes) must be a multiple of 16 bytes
         if (a.lora_rank > 256 || a.lora_rank % 8 != 0 || !aligned16(a.lora_b)) return false;
         if (a.d_in % 8 != 0 || !aligned16(a.lora_a)) return false;
@@ -1238,12 +1246,14 @@ Sharing share_tiles(uint64_t rows, uint64_t d_in, uint64_t d_out) {
 
 struct WorkspaceLayout {
     uint64_t off_xh, off_scale, off_t, off_flags, off_partial, bytes;
-    uint64_t off_codes_t, off_scales_t, off_a_t, off_b_t;  // the repacked weight and adapter (other orientation only)
+    uint64_t off_a_t, off_b_t;             // the adapter factors as the GEMM reads them (f32 factors, other orientation)
+    uint64_t off_codes_t, off_scales_t;    // the repacked weight (other orientation)
 };
+enum Extra { kPlain = 0, kFactors = 1, kFactorsAndWeight = 2 };
 // f16 copy of x | row scales | T (bf16 hi/lo) | flags and partial sums of the split tiles; d_in is
 // bounded so that rows * d_in * 2 fits
 WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank,
-                                 bool repacked = false) {
+                                 Extra extra = kPlain) {
     auto up = [](uint64_t v) { return (v + 255) / 256 * 256; };
     WorkspaceLayout w;
     w.off_xh = 0;
@@ -1254,12 +1264,15 @@ WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint64_t d_out, u
     w.off_partial = w.off_flags + up((uint64_t)sh.grid * 4);
     w.bytes = w.off_partial + (sh.sk_tiles ? (uint64_t)sh.grid * BM * BN * 4 : 0);
     w.off_codes_t = w.off_scales_t = w.off_a_t = w.off_b_t = 0;
-    if (repacked) {  // `lora_rank` is the rank the GEMM sees (twice the adapter's for f32 factors)
-        w.off_codes_t = up(w.bytes);
-        w.off_scales_t = w.off_codes_t + up(d_in * d_out / 2);
-        w.off_a_t = w.off_scales_t + up((d_out / 64) * d_in * 2);
+    if (extra >= kFactors) {  // `lora_rank` is the rank the GEMM sees (twice the adapter's for f32 factors)
+        w.off_a_t = up(w.bytes);
         w.off_b_t = w.off_a_t + up((uint64_t)lora_rank * d_in * 2);
         w.bytes = w.off_b_t + up(d_out * (uint64_t)lora_rank * 2);
+    }
+    if (extra >= kFactorsAndWeight) {
+        w.off_codes_t = up(w.bytes);
+        w.off_scales_t = w.off_codes_t + up(d_in * d_out / 2);
+        w.bytes = w.off_scales_t + up((d_out / 64) * d_in * 2);
     }
     return w;
 }
@@ -1267,12 +1280,8 @@ WorkspaceLayout workspace_layout(uint64_t rows, uint64_t d_in, uint64_t d_out, u
 
 uint64_t prefill_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank) {
     if (rows <= 16 || d_in % 64 != 0 || d_in == 0 || d_out == 0) return 0;
-    uint64_t need = workspace_layout(rows, d_in, d_out, lora_rank).bytes;
-    if (rows >= kInOutMinRows && d_out % 64 == 0) {  // the other orientation, f32 factors at worst
-        const uint64_t other = workspace_layout(rows, d_in, d_out, 2 * lora_rank, true).bytes;
-        if (other > need) need = other;
-    }
-    return need;
+    // f32 factors at worst; the other orientation where its shapes allow it
+    return workspace_layout(rows, d_in, d_out, 2 * lora_rank, d_out % 64 == 0 ? kFactorsAndWeight : kFactors).bytes;
 }
 
 // The reference's orientation (W [d_in][d_out], blocks along d_out) at more than 16 rows: repacked
@@ -1300,8 +1309,9 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     const bool repacked = a.layout == NF4_LAYOUT_IN_OUT;
     if (!(repacked ? prefill_in_out_supported(a) : prefill_supported(a)))
         return fail(NF4_ERR_UNSUPPORTED, "prefill_forward: unsupported shape");
-    const bool x_f32 = a.io_dtype == NF4_DTYPE_F32;  // only in the other orientation
+    const bool x_f32 = a.io_dtype == NF4_DTYPE_F32;
     const bool y_f32 = a.y_f32 || x_f32;
+    const Extra extra = repacked ? kFactorsAndWeight : x_f32 ? kFactors : kPlain;
     PrefillParams p{};
     p.codes = a.packed;
     p.absmax = a.absmax;
@@ -1312,13 +1322,13 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.N = (uint32_t)a.d_out;
     p.K = (uint32_t)a.d_in;
     p.rank = a.lora_a ? a.lora_rank : 0;
-    if (repacked && x_f32) p.rank *= 2;  // see repack_adapter_kernel
+    if (x_f32) p.rank *= 2;  // see repack_adapter_block
     p.lora_chunks = lora_chunks_of(p.rank);
     p.m_tiles = (p.M + BN - 1) / BN;
     p.n_tiles = (p.N + BM - 1) / BM;
     const uint64_t ldy = a.ldy ? a.ldy : a.d_out;
 
-    const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.N, p.rank, repacked);
+    const WorkspaceLayout wl = workspace_layout(p.M, p.K, p.N, p.rank, extra);
     if (a.workspace_bytes < wl.bytes) return fail(NF4_ERR_INVALID_ARG, "prefill_forward: workspace too small");
     const Sharing sh = share_tiles(p.M, p.K, p.N);
     p.sk_tiles = sh.sk_tiles;
@@ -1332,8 +1342,9 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.sk_flags = reinterpret_cast<uint32_t *>(ws + wl.off_flags);
     p.partial = reinterpret_cast<float *>(ws + wl.off_partial);
     const void *lora_a = a.lora_a, *lora_b = a.lora_b;
-    if (repacked) {
+    if (extra != kPlain && (repacked || p.rank)) {
         RepackParams rp{};
+        rp.factors_out_in = !repacked;
         rp.codes = a.packed;
         rp.absmax = a.absmax;
         rp.scale_codes = a.scale_codes;
@@ -1344,9 +1355,9 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
         rp.N = p.N;
         rp.code_cols = (p.N + 127) / 128;
         rp.code_rows = (p.K / 64 + kRepackTiles - 1) / kRepackTiles;
-        rp.code_blocks = rp.code_cols * rp.code_rows;
+        rp.code_blocks = repacked ? rp.code_cols * rp.code_rows : 0;
         rp.scale_cols = (p.N / 64 + 31) / 32;
-        rp.scale_blocks = rp.scale_cols * ((p.K + 31) / 32);
+        rp.scale_blocks = repacked ? rp.scale_cols * ((p.K + 31) / 32) : 0;
         uint32_t adapter_blocks = 0;
         if (p.rank) {
             rp.a = a.lora_a;
@@ -1362,8 +1373,10 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
         if (x_f32) repack_kernel<float><<<blocks, 256, 0, stream>>>(rp);
         else repack_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(rp);
         count_launch();
-        p.codes = rp.codes_t;
-        p.scales_t = rp.scales_t;
+        if (repacked) {
+            p.codes = rp.codes_t;
+            p.scales_t = rp.scales_t;
+        }
         NF4_CUDA_TRY(cudaGetLastError());
     }
     NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<1>), kTPartBytes));
