@@ -678,6 +678,7 @@ def aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind):
     del vals, packed, absmax
     out["prefill"] = prefill_section(torch, lib, _lib, dev)
     out["reference_orientation"] = reference_orientation_section(torch, lib, _lib, dev)
+    out["f32_tensors"] = f32_tensors_section(torch, lib, _lib, dev)
     out["backward"] = backward_section(torch, lib, _lib, dev)
     return out
 
@@ -738,6 +739,49 @@ def reference_orientation_section(torch, lib, _lib, dev, iters: int = 20):
     out[f"M={pm}"] = {"ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "flops": flops,
                       "frac": flops / (ms * 1e-3) / 1e12 / _tf, "peak_kind": f"of {peak_kind} (burst)",
                       "path": "repacking kernels + f16 conversion + tcgen05 GEMM, f32 in and out"}
+    return out
+
+
+def f32_tensors_section(torch, lib, _lib, dev, iters: int = 20):
+    """The decode configuration's layer in the measured layout (W [11008, 4096]) called with f32 tensors,
+    the reference's own tensor type: up to 16 rows go through the decode kernel as bf16 high / low
+    halves of every row, 2048 rows through the tensor-core GEMM after a conversion to f16."""
+    from unifur_b200.quantize import PackedNf4Tensor
+
+    hbm_peak, tf_peak, peak_kind = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(13)
+    w = torch.randn(K * N, device=dev, generator=g) * 0.02
+    wq = PackedNf4Tensor.quantize(w)
+    del w
+    la = torch.randn(RANK, K, device=dev, generator=g) * 0.01
+    lb = torch.randn(N, RANK, device=dev, generator=g) * 0.01
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    out = {"workload": "x f32 [M, 4096], W NF4 [11008, 4096] (blocks along d_in), LoRA rank 16 in f32, f32 out; "
+                       "160 MB flush write before every forward, outside the timed events"}
+    for m in list(MS) + [2048]:
+        x = torch.randn(m, K, device=dev, generator=g)
+        y = torch.zeros(m, N, device=dev)
+        ws = torch.zeros(max(int(lib.nf4_linear_workspace_bytes(m, K, N, RANK)), 256), dtype=torch.uint8, device=dev)
+        a = _lib.LinearArgs()
+        a.struct_bytes = ctypes.sizeof(_lib.LinearArgs)
+        a.layout, a.io_dtype = _lib.LAYOUT_OUT_IN, _lib.DTYPE_F32
+        a.rows, a.d_in, a.d_out = m, K, N
+        a.x, a.packed, a.absmax = x.data_ptr(), wq.codes.data_ptr(), wq.absmax.data_ptr()
+        a.lora_a, a.lora_b, a.lora_rank, a.lora_scale = la.data_ptr(), lb.data_ptr(), RANK, SCALE
+        a.y, a.ldy = y.data_ptr(), N
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        ms, _ = time_flushed(torch, lambda _i: _lib.check(lib.nf4_linear_forward_dev(ctypes.byref(a), stream())),
+                             flush, iters)
+        if m <= 16:
+            by = K * N // 2 + K * N // 64 * 4 + RANK * (K + N) * 4 + m * (K + N) * 4
+            gbs = by / (ms * 1e-3) / 1e9
+            out[f"M={m}"] = {"us": ms * 1e3, "GB/s": gbs, "algorithmic_bytes": by, "frac": gbs / hbm_peak,
+                             "peak_kind": f"of {peak_kind}"}
+        else:
+            flops = 2.0 * m * N * K + 2.0 * m * RANK * (K + N)
+            out[f"M={m}"] = {"ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "flops": flops,
+                             "frac": flops / (ms * 1e-3) / 1e12 / tf_peak, "peak_kind": f"of {peak_kind} (burst)"}
     return out
 
 

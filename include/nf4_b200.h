@@ -187,14 +187,15 @@ NF4_API int32_t nf4_quantize_dequantize_host(const float *values, uint64_t len,
  * src/qwennet.rs:325-344 (adapter: LoraAdapter::forward, src/quantize.rs:620-624).
  * All pointers are device pointers.
  *
- * Arithmetic by shape.  NF4_LAYOUT_OUT_IN with bf16 activations at any number of rows, and either
- * layout at more than 16 rows with bf16 or f32 tensors (d_in a multiple of 64, for NF4_LAYOUT_IN_OUT
- * d_out too; adapter rank a multiple of 8 for bf16 and of 4 for f32 factors), multiply on the tensor
+ * Arithmetic by shape.  NF4_LAYOUT_OUT_IN at any number of rows, and NF4_LAYOUT_IN_OUT at more than
+ * 16 rows, with bf16 or f32 tensors (d_in a multiple of 64, for NF4_LAYOUT_IN_OUT d_out too; adapter
+ * rank a multiple of 8 for bf16 and of 4 for f32 factors at more than 16 rows), multiply on the tensor
  * cores: f16 operands (activations per row and block scales per weight brought into f16's range by
- * powers of two), f32 sums: relative L2 error <= 1e-3 against the reference's f32 result (measured:
- * 4e-4).  Up to 16 rows of NF4_LAYOUT_IN_OUT or of f32 tensors (and up to 64 rows of
- * NF4_LAYOUT_IN_OUT shapes the tensor-core path does not take) and every other shape multiply exactly
- * dequantized f32 weights with f32 sums as the reference does: <= 1e-5. */
+ * powers of two; f32 activations of up to 16 rows enter as the bf16 high and low part of every row,
+ * their adapter term is added in f32), f32 sums: relative L2 error <= 1e-3 against the reference's f32
+ * result (measured: 4e-4).  Up to 16 rows of NF4_LAYOUT_IN_OUT (and up to 64 rows of its shapes the
+ * tensor-core path does not take) and every other shape multiply exactly dequantized f32 weights
+ * with f32 sums as the reference does: <= 1e-5. */
 typedef struct nf4_linear_args {
     uint32_t struct_bytes;      /* sizeof(nf4_linear_args), checked */
     int32_t layout;             /* NF4_LAYOUT_* */

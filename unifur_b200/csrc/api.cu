@@ -420,9 +420,11 @@ uint64_t nf4_linear_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out
     const uint64_t b = prefill_workspace_bytes(rows, d_in, d_out, lora_rank);
     const uint64_t c = generic_workspace_bytes(rows, d_in, d_out, lora_rank);
     const uint64_t d = decode2_workspace_bytes(rows, d_in, d_out, lora_rank);
+    const uint64_t e = f32_rows_workspace_bytes(rows, d_in, d_out, lora_rank);
     if (d > need) need = d;
     if (b > need) need = b;
     if (c > need) need = c;
+    if (e > need) need = e;
     return need;
 }
 
@@ -440,6 +442,9 @@ int32_t nf4_linear_forward_dev(const nf4_linear_args *args, void *stream) {
     }
     if (prefill_supported(*args) || prefill_in_out_supported(*args)) {
         return prefill_forward(*args, s);
+    }
+    if (f32_rows_supported(*args)) {
+        return f32_rows_forward(*args, s);
     }
     return generic_forward(*args, s);
 }

@@ -31,6 +31,8 @@ uint64_t lora_workspace_bytes(uint64_t rows, uint32_t rank);
 int32_t lora_forward(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out, const void *a, const void *b,
                      uint32_t rank, float scale, int32_t layout, int32_t io_dtype, void *y, uint64_t ldy,
                      float *t, cudaStream_t s);
+int32_t lora_intermediate(const void *x, const void *a, float *t, uint64_t rows, uint64_t d_in, uint32_t rank,
+                          int32_t layout, int32_t io_dtype, cudaStream_t s);
 int32_t lora_delta(const void *a, const void *b, const uint8_t *packed, const float *absmax,
                    const uint8_t *scale_codes, const float *scale_of_scales, uint64_t d_in, uint64_t d_out,
                    uint32_t rank, float scale, int32_t layout, int32_t io_dtype, float *out, cudaStream_t s);
@@ -108,6 +110,11 @@ int32_t decode2_forward(const nf4_linear_args &a, cudaStream_t stream);
 // generic_linear.cu: any layout / dtype / shape on CUDA cores (exact f32 weights).
 uint64_t generic_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
 int32_t generic_forward(const nf4_linear_args &a, cudaStream_t stream);
+
+// f32_rows.cu: f32 tensors, NF4_LAYOUT_OUT_IN, rows <= 16: rows split into bf16 halves for the decode kernels
+bool f32_rows_supported(const nf4_linear_args &a);
+uint64_t f32_rows_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out, uint32_t lora_rank);
+int32_t f32_rows_forward(const nf4_linear_args &a, cudaStream_t stream);
 
 // prefill_gemm.cu: tcgen05 GEMM, NF4_LAYOUT_OUT_IN, bf16 activations.
 bool prefill_supported(const nf4_linear_args &a);

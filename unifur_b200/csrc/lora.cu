@@ -464,6 +464,18 @@ int32_t lora_forward(const void *x, uint64_t rows, uint64_t d_in, uint64_t d_out
                : forward_t<__nv_bfloat16>(x, rows, d_in, d_out, a, b, rank, scale, layout, y, ldy, t, s);
 }
 
+// T[m][j] = sum_k x[m][k] A(k, j) alone (f32 out), for callers that finish the adapter term themselves
+int32_t lora_intermediate(const void *x, const void *a, float *t, uint64_t rows, uint64_t d_in, uint32_t rank,
+                          int32_t layout, int32_t io_dtype, cudaStream_t s) {
+    if (io_dtype == NF4_DTYPE_F32)
+        launch_xa<float>(static_cast<const float *>(x), static_cast<const float *>(a), t, rows, d_in, rank, layout, s);
+    else
+        launch_xa<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(a), t, rows,
+                                 d_in, rank, layout, s);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "lora intermediate launch");
+}
+
 int32_t lora_delta(const void *a, const void *b, const uint8_t *packed, const float *absmax,
                    const uint8_t *scale_codes, const float *scale_of_scales, uint64_t d_in, uint64_t d_out,
                    uint32_t rank, float scale, int32_t layout, int32_t io_dtype, float *out, cudaStream_t s) {
