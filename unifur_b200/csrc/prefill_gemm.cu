@@ -815,7 +815,7 @@ __device__ __forceinline__ uint4 bf16x8_to_f16x8(const uint4 &v, float is) {
 }
 
 // MODE 1 (XH_READY): the activations arrive as the f16 copy itself (made, with the row scales, by
-// x_f32_to_f16_kernel) and the adapter factor as f16: only T is computed, with f16 MMAs.
+// x_f32_to_f16_row) and the adapter factor as f16: only T is computed, with f16 MMAs.
 // MODE 2 (T_ONLY): the product alone, t32[m][j] = sum_k x[m][k] a[j][k] in f32, for callers outside
 // the GEMM (the adapter's gradients): no copy of x, no scales.
 template <int MODE>
@@ -990,6 +990,11 @@ struct RepackParams {
     int32_t factors_out_in;     // the factors come as A [r][K], B [N][r] (else A [K][r], B [r][N])
     uint32_t code_cols, code_rows, code_blocks;   // CTAs of the nibbles: columns of 128 n x groups of kRepackTiles k-tiles
     uint32_t scale_cols, scale_blocks;            // CTAs of the scales: 32 x 32 tiles
+    uint32_t adapter_blocks;
+    const float *x32;           // f32 activations [x_rows][K] to convert, or null
+    __half *xh;
+    float *row_scale;
+    uint32_t x_rows;
 };
 constexpr uint32_t kRepackTiles = 4;  // 64-row tiles of nibbles one CTA walks, the next one's loads in flight
 
@@ -1094,30 +1099,16 @@ __device__ __forceinline__ void repack_adapter_block(const RepackParams &p, uint
     }
 }
 
-// One launch for the three: the first code_blocks CTAs take the nibbles, the next scale_blocks the
-// scales, the rest the adapter.
-template <class T>
-__global__ void __launch_bounds__(256) repack_kernel(const RepackParams p) {
-    __shared__ __align__(16) uint8_t smem[2 * 64 * 80];
-    if (blockIdx.x < p.code_blocks)
-        repack_codes_block(p, blockIdx.x, reinterpret_cast<uint8_t(*)[64][80]>(smem));
-    else if (blockIdx.x < p.code_blocks + p.scale_blocks)
-        repack_scales_block(p, blockIdx.x - p.code_blocks, reinterpret_cast<float(*)[33]>(smem));
-    else
-        repack_adapter_block<T>(p, blockIdx.x - p.code_blocks - p.scale_blocks);
-}
-
 // f32 activations: xh[m][k] = f16(x[m][k] / sc), sc the power of two that brings the row's largest
 // finite magnitude into [16384, 32768) (any row, so small activations keep their bits too);
-// row_scale[m] = sc * 2^e with e the weight's exponent.  One CTA per row.
-__global__ void __launch_bounds__(256)
-x_f32_to_f16_kernel(const float *__restrict__ x, uint32_t K, __half *__restrict__ xh, float *__restrict__ row_scale,
-                    const float *__restrict__ absmax, const uint8_t *__restrict__ scale_codes,
-                    const float *__restrict__ scale_of_scales) {
-    __shared__ uint32_t mx_bits;
-    const uint32_t m = blockIdx.x;
+// row_scale[m] = sc * 2^e with e the weight's exponent.  One CTA of 256 threads per row.
+__device__ __forceinline__ void x_f32_to_f16_row(const float *__restrict__ x, uint32_t m, uint32_t K,
+                                                 __half *__restrict__ xh, float *__restrict__ row_scale,
+                                                 const float *__restrict__ absmax,
+                                                 const uint8_t *__restrict__ scale_codes,
+                                                 const float *__restrict__ scale_of_scales, uint32_t *mx_bits) {
     const float4 *row = reinterpret_cast<const float4 *>(x + (size_t)m * K);
-    if (threadIdx.x == 0) mx_bits = 0;
+    if (threadIdx.x == 0) *mx_bits = 0;
     __syncthreads();
     uint32_t mx = 0;
     for (uint32_t c = threadIdx.x; c < K / 4; c += 256) {
@@ -1130,9 +1121,9 @@ x_f32_to_f16_kernel(const float *__restrict__ x, uint32_t K, __half *__restrict_
     }
     #pragma unroll
     for (int s = 16; s > 0; s >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, s));
-    if ((threadIdx.x & 31u) == 0) atomicMax(&mx_bits, mx);
+    if ((threadIdx.x & 31u) == 0) atomicMax(mx_bits, mx);
     __syncthreads();
-    const float largest = __uint_as_float(mx_bits);
+    const float largest = __uint_as_float(*mx_bits);
     float sc = 1.0f;
     if (largest >= 1.1754944e-38f) {  // a normal number
         int e;
@@ -1149,6 +1140,23 @@ x_f32_to_f16_kernel(const float *__restrict__ x, uint32_t K, __half *__restrict_
         const __half2 lo = __floats2half2_rn(v.x * is, v.y * is), hi = __floats2half2_rn(v.z * is, v.w * is);
         out[c] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
     }
+}
+
+// One launch for everything in front of the pre-pass: the first code_blocks CTAs take the nibbles,
+// the next scale_blocks the scales, the next adapter_blocks the adapter, the last x_rows one row of
+// f32 activations each.
+template <class T>
+__global__ void __launch_bounds__(256) repack_kernel(const RepackParams p) {
+    __shared__ __align__(16) uint8_t smem[2 * 64 * 80];
+    uint32_t b = blockIdx.x;
+    if (b < p.code_blocks) return repack_codes_block(p, b, reinterpret_cast<uint8_t(*)[64][80]>(smem));
+    b -= p.code_blocks;
+    if (b < p.scale_blocks) return repack_scales_block(p, b, reinterpret_cast<float(*)[33]>(smem));
+    b -= p.scale_blocks;
+    if (b < p.adapter_blocks) return repack_adapter_block<T>(p, b);
+    b -= p.adapter_blocks;
+    x_f32_to_f16_row(p.x32, b, p.K, p.xh, p.row_scale, p.absmax, p.scale_codes, p.scale_of_scales,
+                     reinterpret_cast<uint32_t *>(smem));
 }
 
 // ---- host side -----------------------------------------------------------------------
@@ -1342,7 +1350,7 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     p.sk_flags = reinterpret_cast<uint32_t *>(ws + wl.off_flags);
     p.partial = reinterpret_cast<float *>(ws + wl.off_partial);
     const void *lora_a = a.lora_a, *lora_b = a.lora_b;
-    if (extra != kPlain && (repacked || p.rank)) {
+    if (extra != kPlain) {  // the other orientation, f32 tensors, or both: one launch in front of the pre-pass
         RepackParams rp{};
         rp.factors_out_in = !repacked;
         rp.codes = a.packed;
@@ -1358,18 +1366,23 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
         rp.code_blocks = repacked ? rp.code_cols * rp.code_rows : 0;
         rp.scale_cols = (p.N / 64 + 31) / 32;
         rp.scale_blocks = repacked ? rp.scale_cols * ((p.K + 31) / 32) : 0;
-        uint32_t adapter_blocks = 0;
         if (p.rank) {
             rp.a = a.lora_a;
             rp.b = a.lora_b;
             rp.r = a.lora_rank;
             rp.a_t = reinterpret_cast<uint16_t *>(ws + wl.off_a_t);
             rp.b_t = reinterpret_cast<__nv_bfloat16 *>(ws + wl.off_b_t);
-            adapter_blocks = (uint32_t)(((uint64_t)a.lora_rank * (p.K + p.N) + 255) / 256);
+            rp.adapter_blocks = (uint32_t)(((uint64_t)a.lora_rank * (p.K + p.N) + 255) / 256);
             lora_a = rp.a_t;
             lora_b = rp.b_t;
         }
-        const uint32_t blocks = rp.code_blocks + rp.scale_blocks + adapter_blocks;
+        if (x_f32) {
+            rp.x32 = static_cast<const float *>(a.x);
+            rp.xh = xh;
+            rp.row_scale = row_scale;
+            rp.x_rows = p.M;
+        }
+        const uint32_t blocks = rp.code_blocks + rp.scale_blocks + rp.adapter_blocks + rp.x_rows;
         if (x_f32) repack_kernel<float><<<blocks, 256, 0, stream>>>(rp);
         else repack_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(rp);
         count_launch();
@@ -1382,9 +1395,6 @@ int32_t prefill_forward(const nf4_linear_args &a, cudaStream_t stream) {
     NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<1>), kTPartBytes));
     NF4_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(prefill_prepass_kernel<0>), kTPartBytes));
     if (x_f32) {
-        x_f32_to_f16_kernel<<<p.M, 256, 0, stream>>>(static_cast<const float *>(a.x), p.K, xh, row_scale, a.absmax,
-                                                   a.scale_codes, a.scale_of_scales);
-        count_launch();
         prefill_prepass_kernel<1><<<(p.M + 15) / 16, kTThreads, kTPartBytes, stream>>>(
             reinterpret_cast<const __nv_bfloat16 *>(xh), static_cast<const __nv_bfloat16 *>(lora_a), p.M, p.K, p.rank,
             p.lora_chunks, a.lora_scale, xh, row_scale, t, a.absmax, a.scale_codes, a.scale_of_scales, p.sk_flags,
