@@ -64,6 +64,31 @@ def test_pure_host_helpers(lib):
     assert lv.tobytes() == nf4_oracle.levels().tobytes()
 
 
+def test_workspace_sizes_cover_every_route(lib):
+    # host arithmetic only: what nf4_linear_workspace_bytes reports must hold the scratch of every
+    # kernel a call of these sizes can be routed to, in either orientation and tensor type
+    ws = lambda rows, k, n, r: int(lib.nf4_linear_workspace_bytes(rows, k, n, r))
+    k, n, r = 4096, 11008, 16
+    # more than 16 rows: the f16 copy of x, T, and for the reference's orientation the weight's
+    # nibbles transposed plus its scales as f16 [n / 64][k]
+    big = ws(2048, k, n, r)
+    assert big >= 2048 * k * 2 + k * n // 2 + (n // 64) * k * 2
+    # ... which a d_out that is no multiple of 64 cannot use
+    assert ws(2048, k, n + 8, r) < ws(2048, k, n, r)
+    # at most 16 rows: flag words, T, and the halves / results of f32 rows (16 x k bf16, 16 x n f32)
+    small = ws(4, k, n, r)
+    assert small >= 256 + 16 * k * 2 + 16 * n * 4
+    assert small < 4 * 1024 * 1024
+    # d_in beyond 4096 at decode sizes: the parts' partial sums
+    assert ws(8, 18944, 3584, 16) >= 5 * 8 * 3584 * 4
+    # sizes grow with the rank, and a multiple of 256 bytes comes back
+    assert ws(2048, k, n, 64) > ws(2048, k, n, 16) and big % 256 == 0 and small % 256 == 0
+    # the backward holds a forward with d_in and d_out exchanged, two [rows][rank] f32 intermediates
+    # and one factor transposed
+    bw = int(lib.nf4_qlora_backward_workspace_bytes(2048, k, n, r))
+    assert bw >= ws(2048, n, k, r) + 2 * 2048 * r * 4 + r * n * 2
+
+
 def test_invalid_arguments_are_reported_not_fatal(lib):
     from unifur_b200 import _lib
 
