@@ -679,6 +679,7 @@ def aux_sections(torch, lib, _lib, dev, hbm_peak, peak_kind):
     out["prefill"] = prefill_section(torch, lib, _lib, dev)
     out["reference_orientation"] = reference_orientation_section(torch, lib, _lib, dev)
     out["f32_tensors"] = f32_tensors_section(torch, lib, _lib, dev)
+    out.update(load_and_embedding_section(torch, lib, _lib, dev))
     out["backward"] = backward_section(torch, lib, _lib, dev)
     return out
 
@@ -782,6 +783,47 @@ def f32_tensors_section(torch, lib, _lib, dev, iters: int = 20):
             flops = 2.0 * m * N * K + 2.0 * m * RANK * (K + N)
             out[f"M={m}"] = {"ms": ms, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "flops": flops,
                              "frac": flops / (ms * 1e-3) / 1e12 / tf_peak, "peak_kind": f"of {peak_kind} (burst)"}
+    return out
+
+
+def load_and_embedding_section(torch, lib, _lib, dev, iters: int = 10):
+    """The checkpoint load path (a bf16 [4096, 14336] matrix as a checkpoint stores it, quantized as its
+    transpose without materialising it: src/qwennet.rs:1375-1390, 1709-1711) and the embedding gather
+    (4096 ids out of a double-quantized [151936, 3584] table, f32 rows out: src/qwennet.rs:285-291, where the
+    reference rebuilds the whole f32 table per call)."""
+    hbm_peak, _tf, peak_kind = measured_peaks()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device=dev).manual_seed(21)
+    out = {}
+    rows, cols = 4096, 14336
+    w = (torch.randn(rows, cols, device=dev, generator=g) * 0.02).bfloat16()
+    n = rows * cols
+    codes = torch.empty(n // 2, dtype=torch.uint8, device=dev)
+    absmax = torch.empty(n // 64, dtype=torch.float32, device=dev)
+    ws = torch.empty(max(int(lib.nf4_quantize_transposed_workspace_bytes(rows, cols)), 16), dtype=torch.uint8, device=dev)
+    ms, _ = time_flushed(torch, lambda _i: _lib.check(lib.nf4_quantize_transposed_dev(
+        p(w), _lib.DTYPE_BF16, rows, cols, p(codes), p(absmax), p(ws), ws.numel(), stream())), flush, iters)
+    by = n * 2 + n // 2 + n // 64 * 4
+    out["load_path"] = {"workload": "bf16 [4096, 14336] -> packed NF4 of its transpose", "us": ms * 1e3,
+                        "GB/s": by / (ms * 1e-3) / 1e9, "algorithmic_bytes": by, "frac": by / (ms * 1e-3) / 1e9 / hbm_peak,
+                        "peak_kind": f"of {peak_kind}"}
+    del w, codes, absmax, ws
+    from unifur_b200.quantize import PackedNf4Tensor
+
+    n_emb, d_model, n_ids = 151936, 3584, 4096
+    table = PackedNf4Tensor.quantize(torch.randn(n_emb * d_model, device=dev, generator=g) * 0.02).with_double_quantization()
+    ids = torch.randint(0, n_emb, (n_ids,), device=dev, generator=g, dtype=torch.int64)
+    rows_out = torch.empty(n_ids, d_model, device=dev)
+    ms, _ = time_flushed(torch, lambda _i: _lib.check(lib.nf4_embedding_gather_dev(
+        p(table.codes), None, p(table.scale_codes), p(table.scale_of_scales), n_emb, d_model, p(ids), n_ids,
+        p(rows_out), _lib.DTYPE_F32, stream())), flush, iters)
+    by = n_ids * (d_model // 2 + d_model // 64 + d_model * 4 + 8)
+    out["embedding_gather"] = {"workload": "4096 ids, table [151936, 3584] NF4 with u8 scales, f32 rows out",
+                               "us": ms * 1e3, "GB/s": by / (ms * 1e-3) / 1e9, "algorithmic_bytes": by,
+                               "frac": by / (ms * 1e-3) / 1e9 / hbm_peak, "peak_kind": f"of {peak_kind}",
+                               "whole_table_f32_bytes_the_reference_rebuilds": n_emb * d_model * 4}
     return out
 
 
