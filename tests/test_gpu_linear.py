@@ -363,6 +363,14 @@ def test_host_weight_handle_forward(oracle):
         ref = oracle.qlora_forward_bnb(x, packed, None, N, K, la, lb, 2.0, None, sc, sos)
         # the result has been rounded to bf16 once (2^-9 relative at most per element)
         assert rel_l2(got, ref) <= REL_L2_BF16 + 2.0 ** -9
+        # a page-locked output is written by the kernel itself (no copy back): the same bits
+        y_locked = torch.full((M, N), 7.0, dtype=torch.bfloat16).pin_memory()
+        x_locked = torch.from_numpy(x).bfloat16().pin_memory()
+        for _ in range(2):
+            _lib.check(L.nf4_weight_linear_forward_host(h, ctypes.c_void_p(x_locked.data_ptr()), M, _lib.DTYPE_BF16, None,
+                                                        vp(lab), vp(lbb), r, 2.0, ctypes.c_void_p(y_locked.data_ptr())))
+            assert np.array_equal(y_locked.view(torch.int16).numpy(), yb)
+            y_locked.fill_(7.0)
     finally:
         L.nf4_weight_free(h)
 

@@ -90,21 +90,29 @@ thread_local Arena t_arena;
 // A small zero-filled device buffer per host thread and device: the decode kernel's workspace
 // (flag words that must be zero at first use and are left zero, then the adapter intermediate).
 struct ZeroScratch {
-    static constexpr size_t kBytes = 8192;
+    static constexpr size_t kMaxBytes = 16u << 20;  // larger workspaces are zeroed per call instead
     void *ptr = nullptr;
+    size_t cap = 0;
     int device = -1;
-    int32_t get(void **out) {
+    // `need` bytes whose first 256 are zero (the decode kernels leave them zero); grows when asked for more
+    int32_t get(void **out, size_t need) {
         int dev = 0;
         NF4_CUDA_TRY(cudaGetDevice(&dev));
-        if (!ptr || dev != device) {
+        if (!ptr || dev != device || need > cap) {
             if (ptr) cudaFree(ptr);
             ptr = nullptr;
-            NF4_CUDA_TRY(cudaMalloc(&ptr, kBytes));
-            NF4_CUDA_TRY(cudaMemset(ptr, 0, kBytes));
+            cap = need > 8192 ? align_up_pow2(need) : 8192;
+            NF4_CUDA_TRY(cudaMalloc(&ptr, cap));
+            NF4_CUDA_TRY(cudaMemset(ptr, 0, 8192));
             device = dev;
         }
         *out = ptr;
         return NF4_OK;
+    }
+    static size_t align_up_pow2(size_t v) {
+        size_t p = 8192;
+        while (p < v) p <<= 1;
+        return p;
     }
     ~ZeroScratch() {
         if (ptr) cudaFree(ptr);
@@ -977,21 +985,35 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
     a.lora_rank = r;
     a.lora_scale = lora_scale;
     a.y = d_y;
+    // At decode sizes the two copies are half of the call's latency.  When y is page-locked memory
+    // the device can address (cudaHostAlloc, cudaHostRegister with the mapped flag), the kernel
+    // stores its results there itself: the copy back, a separate operation of some ten microseconds, goes.
+    // (Not for the tensor-core GEMM of more rows, which stores through a tensor map, and where the
+    // copies do not matter.)
+    void *y_mapped = nullptr;
+    if (rows <= 16) {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, y) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer)
+            y_mapped = attr.devicePointer;
+        else
+            (void)cudaGetLastError();  // pageable memory is reported as an error by older drivers: not one here
+    }
+    if (y_mapped) a.y = y_mapped;
     a.ldy = w->d_out;
     a.workspace = ws ? d_ws : nullptr;
     a.workspace_bytes = ws;
-    if (ws && ws <= ZeroScratch::kBytes) {
+    void *kept = nullptr;
+    if (ws && rows <= 16 && ws <= ZeroScratch::kMaxBytes) {
         // the decode workspace starts with flag words that must be zero: a buffer kept for it
-        void *zs = nullptr;
-        NF4_TRY(t_zero_scratch.get(&zs));
-        a.workspace = zs;
+        NF4_TRY(t_zero_scratch.get(&kept, ws));
+        a.workspace = kept;
     } else if (ws) {
         NF4_CUDA_TRY(cudaMemsetAsync(d_ws, 0, 256, kHostStream));
     }
     volatile int *failed = nullptr;
     NF4_TRY(host_flag_words(&failed));  // (before the launch: the kernels write their failure codes there too)
     NF4_TRY(nf4_linear_forward_dev(&a, kHostStream));
-    NF4_CUDA_TRY(cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, kHostStream));
+    if (!y_mapped) NF4_CUDA_TRY(cudaMemcpyAsync(y, d_y, yb, cudaMemcpyDeviceToHost, kHostStream));
     NF4_TRY(check_cuda(cudaStreamSynchronize(kHostStream), "nf4_weight_linear_forward_host sync"));
     // ... and a wait that gave up in a kernel must not pass for a result
     if (failed[0] | failed[1] | failed[2]) {
@@ -999,6 +1021,7 @@ int32_t nf4_weight_linear_forward_host(const nf4_weight *w, const void *x, uint6
         NF4_TRY(flag_ptrs(ptrs));
         const int v[3] = {failed[0], failed[1], failed[2]};
         failed[0] = failed[1] = failed[2] = 0;
+        if (kept) (void)cudaMemset(kept, 0, 256);  // a kernel that gave up may have left its flag words set
         return report_flags(ptrs, v);
     }
     return NF4_OK;
