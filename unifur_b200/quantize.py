@@ -419,8 +419,10 @@ def _linear_args(lib, x2: torch.Tensor, packed: PackedNf4Tensor, d_in: int, d_ou
         lora_b = lora_b.to(x2.dtype).contiguous()
     y = out if out is not None else torch.empty(rows, d_out, dtype=x2.dtype, device=dev)
     ws_bytes = int(lib.nf4_linear_workspace_bytes(rows, d_in, d_out, rank))
-    # zero-filled: the decode kernel's flag words at the start of the workspace must start at zero
-    ws = torch.zeros(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    # the decode kernel's flag words at the start of the workspace must start at zero; the rest
+    # (tens of megabytes at prefill sizes) needs no initialisation
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    ws[:256].zero_()
     bias32 = bias.to(torch.float32).contiguous() if bias is not None else None
     a = LinearArgs()
     a.struct_bytes = ctypes.sizeof(LinearArgs)

@@ -115,8 +115,9 @@ class QloraLinear:
         rank = la.shape[0] if self.base.layout == LAYOUT_OUT_IN else la.shape[1]
         gx = torch.empty(rows, d_in, dtype=x2.dtype, device=dev)
         ga, gb = torch.empty_like(la), torch.empty_like(lb)
-        ws = torch.zeros(max(int(lib.nf4_qlora_backward_workspace_bytes(rows, d_in, d_out, rank)), 256),
+        ws = torch.empty(max(int(lib.nf4_qlora_backward_workspace_bytes(rows, d_in, d_out, rank)), 256),
                          dtype=torch.uint8, device=dev)
+        ws[:256].zero_()   # the flag words; the rest needs no initialisation
         pk = self.base.packed()
         dq = pk.is_double_quantized()
         a = _lib.LinearArgs()
