@@ -270,6 +270,9 @@ NF4_API int32_t nf4_qlora_merge_dev(const uint8_t *packed, const float *absmax, 
  *   grad_x [rows, d_in]  = grad_y W^T + s (grad_y B^T) A^T   (one more NF4 linear over the same packed
  *                          bytes read in the other orientation),
  *   grad_a, grad_b with the shapes of lora_a, lora_b: s x^T (grad_y B^T) and s (x A)^T grad_y.
+ * At more than 16 rows grad_x runs on the tensor cores (rel. L2 <= 1e-3 like that forward); with bf16
+ * tensors the four rank-r products behind grad_a and grad_b run on warp MMAs with f32 sums (exact
+ * products; the outputs are rounded to bf16 once), with f32 tensors on CUDA cores in f32.
  * fwd->workspace must hold nf4_qlora_backward_workspace_bytes() bytes, 256-byte aligned, its first 256
  * bytes zero at the first use like any forward workspace (every call leaves them zero). */
 NF4_API uint64_t nf4_qlora_backward_workspace_bytes(uint64_t rows, uint64_t d_in, uint64_t d_out,
